@@ -1,0 +1,202 @@
+/*
+ * lucid_cuda.h -- C ABI of liblucid_cuda.so, the sm_100a (B200) backend for the
+ * int8 quantized-inference path of the `lucid` framework.
+ *
+ * The library replaces, for this path only, the reference's pybind11 engine
+ * boundary `lucid._C.engine.quantized` (lucid/_C/bindings/bind_quantized.cpp:17-27,
+ * registered at lucid/_C/bindings/bind.cpp:215-217) and the eager op chains the
+ * Python layer builds on the engine for `lucid.quantization`
+ * (lucid/quantization/_functional.py, _qparams.py, observer.py).
+ *
+ * Conventions
+ *  - every pointer named in a signature is a DEVICE pointer unless the name
+ *    starts with `host_`; the library allocates nothing, the caller owns all
+ *    buffers (outputs and scratch included);
+ *  - `stream` is a cudaStream_t passed as void*; calls are asynchronous on it;
+ *  - the return value is 0 on success and negative on failure (LC_ERR_*), with
+ *    a thread-local message available from lc_last_error();
+ *  - tensors are dense row-major; a "channel layout" is the triple
+ *    (outer, channels, inner): element (o, c, i) lives at (o*channels + c)*inner + i,
+ *    which covers ch_axis = 0 (outer = 1), a middle axis, and the last axis
+ *    (inner = 1).  Per-tensor work uses outer = channels = 1;
+ *  - there is no CPU fallback anywhere behind this interface.
+ */
+#ifndef LUCID_CUDA_H_
+#define LUCID_CUDA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LC_OK 0
+#define LC_ERR_INVALID_ARG (-1)
+#define LC_ERR_UNSUPPORTED (-2)
+#define LC_ERR_CUDA (-3)
+#define LC_ERR_TIMEOUT (-4)
+#define LC_ERR_WORKSPACE (-5)
+
+/* element types understood by the entry points */
+#define LC_F32 0
+#define LC_BF16 1
+#define LC_F16 2
+#define LC_S8 3
+#define LC_U8 4
+#define LC_S16 5
+#define LC_S32 6
+
+/* ---- library / device ------------------------------------------------- */
+int32_t lc_version(void);
+/* copies the calling thread's last error text into buf (NUL terminated) */
+int32_t lc_last_error(char* host_buf, int32_t n);
+/* compute capability (major*10+minor) and SM count of `device` */
+int32_t lc_device_info(int32_t device, int32_t* host_sm, int32_t* host_sm_count);
+
+/* ---- observers --------------------------------------------------------
+ * MinMaxObserver.forward: running global min and max
+ * (lucid/quantization/observer.py:408-414).  If accumulate != 0 the result is
+ * merged into the values already in min_out/max_out (the running statistic),
+ * otherwise it overwrites them.  Needs lc_observe_tensor_workspace_bytes()
+ * bytes of scratch that must be zero-filled before its first use; the kernel
+ * leaves it zero-filled again.  If scale_out is not NULL the last CTA also
+ * evaluates calculate_qparams (lucid/quantization/_qparams.py:186-205) on the
+ * merged range and writes one scale and one zero-point. */
+int64_t lc_observe_tensor_workspace_bytes(void);
+int32_t lc_observe_tensor_f32(const float* x, int64_t n, float* min_out, float* max_out,
+                              int32_t accumulate, int32_t symmetric, int32_t quant_min,
+                              int32_t quant_max, int32_t is_signed, float eps,
+                              float* scale_out, float* zp_out, void* workspace,
+                              int64_t workspace_bytes, void* stream);
+
+/* PerChannelMinMaxObserver.forward: per-channel min and max over every other
+ * axis (lucid/quantization/observer.py:672-686). */
+int32_t lc_observe_channel_f32(const float* x, int64_t outer, int64_t channels, int64_t inner,
+                               float* min_out, float* max_out, int32_t accumulate, void* stream);
+
+/* calculate_qparams on n (min,max) pairs (lucid/quantization/_qparams.py:186-205):
+ * range widened to include 0; symmetric: s = max(|min|,|max|)/((qmax-qmin)/2),
+ * z = 0 (signed) or (qmax+qmin+1)/2; affine: s = (max-min)/(qmax-qmin),
+ * z = clip(qmin - rint(min/s), qmin, qmax); s floored at eps.  IEEE fp32 per step. */
+int32_t lc_calculate_qparams_f32(const float* min_val, const float* max_val, int64_t n,
+                                 int32_t symmetric, int32_t quant_min, int32_t quant_max,
+                                 int32_t is_signed, float eps, float* scale_out, float* zp_out,
+                                 void* stream);
+
+/* ---- quantize / dequantize / fake_quantize ----------------------------
+ * quantize (lucid/quantization/_functional.py:59-69,179-197):
+ *   q = cast(clip(rint(x * inv) + z, qmin, qmax)),  inv = 1/scale.
+ * scale: device array of n_scale (1 or `channels`) floats, inverted on the
+ * device with an IEEE fp32 division -- the reference's `1.0 / s` for a tensor
+ * scale; or NULL, in which case host_inv_scale (the double-precision 1.0/s
+ * rounded once to fp32, the reference's Python-float case) is used.
+ * zero_point: device array of n_zp (1 or `channels`) floats, or NULL to use
+ * host_zero_point.  out_dtype: LC_S8, LC_U8, LC_S16 or LC_S32 (the storage
+ * dtypes of qint8/qint4, the GEMM's u8 operand, quint8, qint32). */
+int32_t lc_quantize_f32(const float* x, int64_t outer, int64_t channels, int64_t inner,
+                        const float* scale, int64_t n_scale, const float* zero_point,
+                        int64_t n_zp, float host_inv_scale, float host_zero_point,
+                        int32_t quant_min, int32_t quant_max, void* out, int32_t out_dtype,
+                        void* stream);
+
+/* dequantize (lucid/quantization/_functional.py:281-293): (f32(q) - z) * s.
+ * q_dtype: LC_S8, LC_U8, LC_S16 or LC_S32.  out_dtype: LC_F32 (the reference's
+ * result type) or LC_BF16. */
+int32_t lc_dequantize(const void* q, int32_t q_dtype, int64_t outer, int64_t channels,
+                      int64_t inner, const float* scale, int64_t n_scale,
+                      const float* zero_point, int64_t n_zp, float host_scale,
+                      float host_zero_point, void* out, int32_t out_dtype, void* stream);
+
+/* forward of fake_quantize (lucid/quantization/_functional.py:304-333):
+ *   out = (clip(rint(x*inv)+z, qmin, qmax) - z) * s
+ * and, if mask_out is not NULL, the straight-through mask (1.0 where the
+ * unclamped code is inside [qmin, qmax]). */
+int32_t lc_fake_quantize_f32(const float* x, int64_t outer, int64_t channels, int64_t inner,
+                             const float* scale, int64_t n_scale, const float* zero_point,
+                             int64_t n_zp, float host_inv_scale, float host_scale,
+                             float host_zero_point, int32_t quant_min, int32_t quant_max,
+                             float* out, float* mask_out, void* stream);
+
+/* ---- fused dynamic activation quantization ---------------------------
+ * One pass per row: observer + calculate_qparams + quantize for a [rows, cols]
+ * fp32 matrix with row stride ldx (elements); writes codes with row stride ldq
+ * (bytes == elements), one scale and one zero-point per row.  This is the
+ * per-token form of the dynamic Linear's activation quantization
+ * (lucid/nn/quantized/dynamic/linear.py:87-88 generalised to a per-row range)
+ * and the fused form of PerChannelMinMaxObserver(ch_axis=0) + quantize. */
+int32_t lc_dynamic_quantize_rows_f32(const float* x, int64_t rows, int64_t cols, int64_t ldx,
+                                     int32_t symmetric, int32_t quant_min, int32_t quant_max,
+                                     int32_t is_signed, float eps, void* q_out,
+                                     int32_t out_dtype, int64_t ldq, float* scale_out,
+                                     float* zp_out, void* stream);
+
+/* Per-tensor dynamic quantization of a [rows, cols] matrix, the activation
+ * step of the dynamic Linear (lucid/nn/quantized/dynamic/linear.py:87-88):
+ * global min/max -> calculate_qparams -> quantize, scale and zero-point stay
+ * on the device.  Two launches (the global range is a true dependency).
+ * Scratch as for lc_observe_tensor_f32.  minmax_out receives {min, max}. */
+int32_t lc_dynamic_quantize_tensor_f32(const float* x, int64_t rows, int64_t cols, int64_t ldx,
+                                       int32_t symmetric, int32_t quant_min,
+                                       int32_t quant_max, int32_t is_signed, float eps,
+                                       void* q_out, int32_t out_dtype, int64_t ldq,
+                                       float* scale_out, float* zp_out, float* minmax_out,
+                                       void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ---- int8 Linear: tcgen05 kind::i8 GEMM with fused dequant epilogue ----
+ * Integer form of the dynamic Linear forward
+ * (lucid/nn/quantized/dynamic/linear.py:85-92; float GEMM it replaces:
+ * lucid/_C/nn/Linear.cpp:74-136 -> backend/cpu/methods/Matmul.cpp:80-122):
+ *   acc[m,n] = sum_k a[m,k] * b[n,k]                         (int32, exact)
+ *   acc'     = acc - zx * wsum[n]            if zx and wsum are given
+ *   out      = f32(acc') * sx[m or 0] * sw[n] + bias[n]      (out_dtype F32/BF16)
+ *   out      = acc'                                          (out_dtype S32)
+ * a: [M,K] int8 or uint8 codes (a_unsigned), row stride lda bytes;
+ * b: [N,K] int8 codes (the reference's (out,in) weight layout), row stride ldb.
+ * lda and ldb must be multiples of 16 and the bases 16-byte aligned (TMA).
+ * sx: one float (sx_per_row = 0) or M floats; zx: one float holding an integer
+ * value, or NULL; wsum[n] = sum_k b[n,k] as int32, or NULL; sw: N floats or
+ * NULL (treated as 1); bias: N floats or NULL.  ldo in elements.
+ * status: optional device int32 that receives a non-zero code if a bounded
+ * device-side wait ran out (the output is then invalid). */
+int32_t lc_qlinear_i8(const void* a, int32_t a_unsigned, int64_t lda, const int8_t* b,
+                      int64_t ldb, int64_t M, int64_t N, int64_t K, const float* sx,
+                      int32_t sx_per_row, const float* zx, const int32_t* wsum,
+                      const float* sw, const float* bias, void* out, int32_t out_dtype,
+                      int64_t ldo, int32_t* status, void* stream);
+
+/* row sums of an int8 matrix as int32 (the zero-point correction term) */
+int32_t lc_rowsum_s8(const int8_t* b, int64_t rows, int64_t cols, int64_t ldb, int32_t* out,
+                     void* stream);
+
+/* ---- weight-only int8 Linear for decode batch sizes --------------------
+ * Per-output-channel symmetric int8 weights, float activations, fp32
+ * accumulation: y[b,n] = (sum_k x[b,k] * wq[n,k]) * sw[n] + bias[n].
+ * Replaces the dequantize-then-F.linear forward of the quantized Linear at
+ * small batch (lucid/nn/quantized/linear.py:206-214) and is the per-channel
+ * counterpart of quantized_matmul_op (lucid/_C/ops/quantized/QuantizedMatmul.cpp:143-207).
+ * x_dtype / y dtype: LC_F32, LC_BF16 or LC_F16; batch <= 32. */
+int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
+                        const int8_t* wq, int64_t ldw, int64_t N, const float* sw,
+                        const float* bias, void* y, int64_t ldy, void* stream);
+
+/* ---- group-wise affine weight-only format ------------------------------
+ * engine.quantized.{quantize,dequantize,quantized_matmul}
+ * (lucid/_C/ops/quantized/QuantizedMatmul.cpp:111-121, 123-141, 143-207):
+ * per (row, group of group_size columns): s = (max-min)/(2^bits-1), bias = min,
+ * code = clip(rint((w-bias)/s), 0, 2^bits-1), 32/bits codes per 32-bit word,
+ * first code in the low bits.  bits in {4, 8}; group_size in {32, 64, 128}. */
+int32_t lc_group_quantize_f32(const float* w, int64_t N, int64_t K, int32_t group_size,
+                              int32_t bits, int32_t* packed, float* scales, float* biases,
+                              void* stream);
+int32_t lc_group_dequantize(const int32_t* packed, const float* scales, const float* biases,
+                            int64_t N, int64_t K, int32_t group_size, int32_t bits, float* out,
+                            void* stream);
+/* y[b,n] = sum_k x[b,k] * (code[n,k]*s[n,g] + bias[n,g]); x and y of x_dtype */
+int32_t lc_group_matmul(const void* x, int32_t x_dtype, int64_t batch, int64_t K,
+                        const int32_t* packed, const float* scales, const float* biases,
+                        int64_t N, int32_t group_size, int32_t bits, void* y, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUCID_CUDA_H_ */

@@ -1,0 +1,72 @@
+// Library-level entry points and the host helpers shared by all kernels files.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace lc {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int32_t fail(int32_t code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int32_t check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(LC_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return LC_OK;
+}
+
+// Read-only after its first fill per device, so concurrent callers are safe.
+int sm_count() {
+  constexpr int kMaxDevices = 64;
+  static int counts[kMaxDevices] = {0};
+  static std::once_flag flags[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  std::call_once(flags[dev], [dev]() {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    counts[dev] = n;
+  });
+  return counts[dev];
+}
+
+}  // namespace lc
+
+extern "C" int32_t lc_version(void) { return 100; }
+
+extern "C" int32_t lc_last_error(char* host_buf, int32_t n) {
+  if (!host_buf || n <= 0) return LC_ERR_INVALID_ARG;
+  strncpy(host_buf, lc::g_error, static_cast<size_t>(n));
+  host_buf[n - 1] = '\0';
+  return LC_OK;
+}
+
+extern "C" int32_t lc_device_info(int32_t device, int32_t* host_sm, int32_t* host_sm_count) {
+  int major = 0, minor = 0, sms = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+    cudaGetLastError();
+    return lc::fail(LC_ERR_CUDA, "device %d is not usable", device);
+  }
+  if (host_sm) *host_sm = major * 10 + minor;
+  if (host_sm_count) *host_sm_count = sms;
+  return LC_OK;
+}

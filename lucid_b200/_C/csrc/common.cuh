@@ -1,0 +1,167 @@
+// Shared host/device helpers for liblucid_cuda (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "lucid_cuda.h"
+
+namespace lc {
+
+// ---- host side: error text and launch checking ---------------------------
+void set_error(const char* fmt, ...);
+int32_t fail(int32_t code, const char* fmt, ...);
+int32_t check_launch(const char* what);
+int sm_count();  // SM count of the current device (cached per device)
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// ---- device side: the quantization grid, one IEEE fp32 step at a time ------
+// The reference evaluates round(x * (1/s)) + z as separate eager fp32 ops
+// (lucid/quantization/_functional.py:59-69); the explicit _rn intrinsics stop
+// the compiler from contracting the multiply and the add into an FMA.
+__device__ __forceinline__ float grid_code(float x, float inv, float z) {
+  return __fadd_rn(rintf(__fmul_rn(x, inv)), z);
+}
+
+// clip(code, qmin, qmax) followed by the reference's saturating float->int
+// cast, which maps NaN to 0 (lucid/_C/backend/cpu/methods/Factory.cpp:103-135).
+__device__ __forceinline__ int code_to_int(float c, float qmin, float qmax) {
+  float cl = fminf(fmaxf(c, qmin), qmax);
+  return (c != c) ? 0 : __float2int_rn(cl);
+}
+
+// calculate_qparams for one (min, max) pair (lucid/quantization/_qparams.py:186-205).
+// The host fills the constants exactly as the reference's Python does:
+// half = (qmax-qmin)/2.0 and range = qmax-qmin rounded once to fp32,
+// sym_zp = 0 for a signed grid else (qmax+qmin+1)//2.
+struct QParamSpec {
+  int symmetric;
+  float half;
+  float sym_zp;
+  float range;
+  float qmin;
+  float qmax;
+  float eps;
+};
+
+inline QParamSpec make_qparam_spec(int symmetric, int quant_min, int quant_max, int is_signed,
+                                   float eps) {
+  QParamSpec sp;
+  sp.symmetric = symmetric;
+  sp.half = static_cast<float>((static_cast<double>(quant_max) - static_cast<double>(quant_min)) / 2.0);
+  long long mid = (static_cast<long long>(quant_max) + static_cast<long long>(quant_min) + 1);
+  mid = (mid >= 0) ? mid / 2 : -((-mid + 1) / 2);  // floor division
+  sp.sym_zp = is_signed ? 0.0f : static_cast<float>(mid);
+  sp.range = static_cast<float>(static_cast<double>(quant_max) - static_cast<double>(quant_min));
+  sp.qmin = static_cast<float>(quant_min);
+  sp.qmax = static_cast<float>(quant_max);
+  sp.eps = eps;
+  return sp;
+}
+
+__device__ __forceinline__ void qparams_from_range(float mn, float mx, const QParamSpec& sp,
+                                                   float& scale, float& zp) {
+  mn = fminf(mn, 0.0f);
+  mx = fmaxf(mx, 0.0f);
+  if (sp.symmetric) {
+    float max_abs = fmaxf(fabsf(mn), fabsf(mx));
+    scale = fmaxf(__fdiv_rn(max_abs, sp.half), sp.eps);
+    zp = sp.sym_zp;
+  } else {
+    scale = fmaxf(__fdiv_rn(__fsub_rn(mx, mn), sp.range), sp.eps);
+    float r = rintf(__fdiv_rn(mn, scale));
+    zp = fminf(fmaxf(__fsub_rn(sp.qmin, r), sp.qmin), sp.qmax);
+  }
+}
+
+// ---- warp / block reductions ----------------------------------------------
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide min and max; every thread returns the result.  `red` is 2*32 floats.
+__device__ __forceinline__ void block_minmax(float& mn, float& mx, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  mn = warp_min(mn);
+  mx = warp_max(mx);
+  __syncthreads();  // protects `red` against a previous use
+  if (lane == 0) {
+    red[warp] = mn;
+    red[32 + warp] = mx;
+  }
+  __syncthreads();
+  float a = (lane < nwarps) ? red[lane] : INFINITY;
+  float b = (lane < nwarps) ? red[32 + lane] : -INFINITY;
+  mn = warp_min(a);
+  mx = warp_max(b);
+}
+
+// float atomic min/max through integer atomics on the float's bit pattern
+// (ordering of IEEE bit patterns: as signed int for >= 0, reversed as unsigned
+// for < 0).  -0.0 is canonicalised to +0.0 first.
+__device__ __forceinline__ void atomic_min_float(float* addr, float v) {
+  v = v + 0.0f;
+  if (v >= 0.0f)
+    atomicMin(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else
+    atomicMax(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+__device__ __forceinline__ void atomic_max_float(float* addr, float v) {
+  v = v + 0.0f;
+  if (v >= 0.0f)
+    atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else
+    atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+
+// ---- vector store of four codes -------------------------------------------
+template <typename T>
+struct Vec4;
+template <>
+struct Vec4<int8_t> {
+  using type = char4;
+};
+template <>
+struct Vec4<uint8_t> {
+  using type = uchar4;
+};
+template <>
+struct Vec4<int16_t> {
+  using type = short4;
+};
+template <>
+struct Vec4<int32_t> {
+  using type = int4;
+};
+
+template <typename T>
+__device__ __forceinline__ void store4(T* p, int a, int b, int c, int d) {
+  typename Vec4<T>::type v;
+  v.x = static_cast<decltype(v.x)>(a);
+  v.y = static_cast<decltype(v.y)>(b);
+  v.z = static_cast<decltype(v.z)>(c);
+  v.w = static_cast<decltype(v.w)>(d);
+  *reinterpret_cast<typename Vec4<T>::type*>(p) = v;
+}
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, int& a, int& b, int& c, int& d) {
+  typename Vec4<T>::type v = *reinterpret_cast<const typename Vec4<T>::type*>(p);
+  a = v.x;
+  b = v.y;
+  c = v.z;
+  d = v.w;
+}
+
+}  // namespace lc

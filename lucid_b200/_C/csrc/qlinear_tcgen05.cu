@@ -1,0 +1,558 @@
+// int8 Linear for B200: tcgen05.mma kind::i8 (s8 x s8 or u8 x s8 -> s32 in TMEM),
+// TMA-fed 128B-swizzled operand tiles, persistent warp-specialised CTAs and a
+// fused dequantize(+zero-point)(+bias) epilogue.
+//
+//   acc[m,n] = sum_k a[m,k] * b[n,k]        both operands K-major, exactly the
+//                                           reference's (out,in) weight layout
+//   out      = f32(acc - zx*wsum[n]) * sx[m] * sw[n] + bias[n]
+//
+// CTA = 192 threads: warp 0 issues TMA loads, warp 1 owns TMEM and issues the
+// MMAs, warps 2..5 drain the accumulator (one TMEM lane quadrant each).  The
+// accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of
+// tile i overlaps the main loop of tile i+1.  No multicast is used anywhere.
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the waiting role
+// records a code in the caller's status word, leaves its loop, the CTA waits
+// (bounded) for its own TMA copies in flight, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace lc {
+namespace gemm {
+
+constexpr int BM = 128;          // rows of A per tile  (UMMA M)
+constexpr int BN = 256;          // rows of B per tile  (UMMA N)
+constexpr int BK = 128;          // bytes of K per stage = one 128B swizzle atom
+constexpr int UMMA_K = 32;       // K per tcgen05.mma for 8-bit operands
+constexpr int STAGES = 4;
+constexpr int ACC_STAGES = 2;
+constexpr int TMEM_COLS = ACC_STAGES * BN;  // 512 = all of TMEM
+constexpr int A_BYTES = BM * BK;
+constexpr int B_BYTES = BN * BK;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+constexpr int GROUP_M = 16;      // tile rasterisation: bands of 16 M-tiles share B in L2
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
+
+enum : int { ST_PRODUCER = 1, ST_MMA = 2, ST_EPILOGUE = 3 };
+
+struct Params {
+  int64_t M, N, K;
+  const float* sx;      // 1 or M
+  int sx_per_row;
+  const float* zx;      // device scalar holding an integer value, or null
+  const int32_t* wsum;  // [N] or null
+  const float* sw;      // [N] or null
+  const float* bias;    // [N] or null
+  void* out;
+  int out_dtype;
+  int64_t ldo;
+  int out_vec;          // rows of `out` allow 16-byte stores
+  int32_t* status;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait: false when the bound was hit
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kWaitCycles) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// barrier over the 128 epilogue threads that also ANDs a predicate, so that all
+// four warps take the same decision after a bounded wait
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred pin, pout;\n\t"
+      "setp.ne.u32 pin, %1, 0;\n\t"
+      "bar.red.and.pred pout, 1, %2, pin;\n\t"
+      "selp.u32 %0, 1, 0, pout;\n\t}"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(ok)), "n"(EPI_THREADS)
+      : "memory");
+  return out != 0;
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile stored as 128-byte rows with
+// the 128B swizzle (what a SWIZZLE_128B TMA box of 128 bytes x rows produces):
+// start address >> 4 in bits [0,14), leading byte offset (unused by swizzled
+// K-major layouts, canonical value 1) in [16,30), stride byte offset = 1024 B
+// between 8-row groups in [32,46), descriptor version 1 in [46,48), layout
+// type 2 (SWIZZLE_128B) in [61,64).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::i8: D format s32 (2) in bits [4,6), A format
+// in [7,10) and B format in [10,13) (0 = u8, 1 = s8), both operands K-major
+// (bits 15, 16 = 0), N >> 3 in [17,23), M >> 4 in [24,29).
+__host__ __device__ constexpr uint32_t make_idesc(bool a_unsigned) {
+  return (2u << 4) | ((a_unsigned ? 0u : 1u) << 7) | (1u << 10) |
+         (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tile_coords(int64_t t, int64_t tiles_m, int64_t tiles_n, int64_t& tm,
+                                            int64_t& tn) {
+  const int64_t group = static_cast<int64_t>(GROUP_M) * tiles_n;
+  const int64_t g = t / group;
+  const int64_t first_m = g * GROUP_M;
+  const int64_t gm = (tiles_m - first_m < GROUP_M) ? (tiles_m - first_m) : GROUP_M;
+  const int64_t r = t % group;
+  tm = first_m + r % gm;
+  tn = r / gm;
+}
+
+__device__ __forceinline__ void report(int32_t* status, int code) {
+  if (status) atomicCAS(status, 0, code);
+}
+
+template <typename T>
+__device__ __forceinline__ void store_chunk(const Params& p, int64_t row, int64_t col0, const float* v);
+
+// 32 consecutive outputs of one row
+template <>
+__device__ __forceinline__ void store_chunk<float>(const Params& p, int64_t row, int64_t col0,
+                                                   const float* v) {
+  float* o = static_cast<float*>(p.out) + row * p.ldo + col0;
+  if (p.out_vec && col0 + 32 <= p.N) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) o[j] = v[j];
+  }
+}
+template <>
+__device__ __forceinline__ void store_chunk<__nv_bfloat16>(const Params& p, int64_t row,
+                                                           int64_t col0, const float* v) {
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
+  if (p.out_vec && col0 + 32 <= p.N) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+      __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+      __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+      uint4 w;
+      w.x = *reinterpret_cast<uint32_t*>(&h0);
+      w.y = *reinterpret_cast<uint32_t*>(&h1);
+      w.z = *reinterpret_cast<uint32_t*>(&h2);
+      w.w = *reinterpret_cast<uint32_t*>(&h3);
+      *reinterpret_cast<uint4*>(o + j) = w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+  }
+}
+
+__device__ __forceinline__ void store_chunk_s32(const Params& p, int64_t row, int64_t col0,
+                                                const int* v) {
+  int32_t* o = static_cast<int32_t*>(p.out) + row * p.ldo + col0;
+  if (p.out_vec && col0 + 32 <= p.N) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      *reinterpret_cast<int4*>(o + j) = make_int4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) o[j] = v[j];
+  }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                  const __grid_constant__ CUtensorMap tmap_b, const Params p, const uint32_t idesc) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ float s_sw[BN];
+  __shared__ float s_bias[BN];
+  __shared__ int s_corr[BN];
+  __shared__ uint32_t s_tmem_base;
+
+  const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = tiles_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + ACC_STAGES + s); };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int64_t tiles_m = (p.M + BM - 1) / BM;
+  const int64_t tiles_n = (p.N + BN - 1) / BN;
+  const int64_t num_tiles = tiles_m * tiles_n;
+  const int num_kb = static_cast<int>((p.K + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < ACC_STAGES; ++s) {
+      mbar_init(acc_full_bar(s), 1);
+      mbar_init(acc_empty_bar(s), EPI_THREADS / 32);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&s_tmem_base)),
+                 "r"(static_cast<uint32_t>(TMEM_COLS))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      uint32_t armed_parity[STAGES];
+      bool armed[STAGES];
+      for (int s = 0; s < STAGES; ++s) armed[s] = false;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int64_t tm, tn;
+        tile_coords(t, tiles_m, tiles_n, tm, tn);
+        const int m0 = static_cast<int>(tm * BM), n0 = static_cast<int>(tn * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+            report(p.status, ST_PRODUCER);
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, kb * BK, m0, full_bar(stage));
+          tma_load_2d(a_dst + A_BYTES, &tmap_b, kb * BK, n0, full_bar(stage));
+          armed[stage] = true;
+          armed_parity[stage] = phase;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      // do not leave while one of this CTA's bulk copies may still be landing
+      for (int s = 0; s < STAGES; ++s)
+        if (armed[s]) mbar_wait(full_bar(s), armed_parity[s]);
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int64_t it = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int as = static_cast<int>(it & 1);
+        const uint32_t aphase = static_cast<uint32_t>((it >> 1) & 1);
+        if (!mbar_wait(acc_empty_bar(as), aphase ^ 1u)) {
+          report(p.status, ST_MMA);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase)) {
+            report(p.status, ST_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_src = tiles_base + stage * STAGE_BYTES;
+          const uint64_t a_desc = make_smem_desc(a_src);
+          const uint64_t b_desc = make_smem_desc(a_src + A_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; ++j) {
+            // advancing K inside the swizzle atom = advancing the start address
+            const uint64_t koff = static_cast<uint64_t>((j * UMMA_K) >> 4);
+            tc_mma_i8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));  // frees the smem slot once these MMAs retire
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tc_commit(acc_full_bar(as));
+      }
+    }
+  } else {
+    // ===================== epilogue (warps 2..5) =====================
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int et = threadIdx.x - 64;        // 0..127
+    const float sx_scalar = (p.sx && !p.sx_per_row) ? __ldg(p.sx) : 1.0f;
+    const int zx_i = p.zx ? __float2int_rn(__ldg(p.zx)) : 0;
+    int64_t it = 0;
+    for (int64_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      int64_t tm, tn;
+      tile_coords(t, tiles_m, tiles_n, tm, tn);
+      const int64_t m0 = tm * BM, n0 = tn * BN;
+      // per-column epilogue constants of this tile, staged once for all rows
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+      for (int j = et; j < BN; j += EPI_THREADS) {
+        const int64_t n = n0 + j;
+        const bool in = n < p.N;
+        s_sw[j] = (in && p.sw) ? __ldg(p.sw + n) : 1.0f;
+        s_bias[j] = (in && p.bias) ? __ldg(p.bias + n) : 0.0f;
+        s_corr[j] = (in && p.wsum) ? zx_i * __ldg(p.wsum + n) : 0;
+      }
+      const int as = static_cast<int>(it & 1);
+      const uint32_t aphase = static_cast<uint32_t>((it >> 1) & 1);
+      // also publishes the staged constants to the other epilogue warps
+      if (!epilogue_all(mbar_wait(acc_full_bar(as), aphase))) {
+        report(p.status, ST_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const int64_t row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float sxr = p.sx_per_row ? (row_ok ? __ldg(p.sx + row) : 0.0f) : sx_scalar;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                             static_cast<uint32_t>(as * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tc_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
+        tc_wait_ld();
+        const int64_t col0 = n0 + c * 32;
+        if (row_ok && col0 < p.N) {
+          if (p.out_dtype == LC_S32) {
+            int v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = static_cast<int>(r[j]) - s_corr[c * 32 + j];
+            store_chunk_s32(p, row, col0, v);
+          } else {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int a = static_cast<int>(r[j]) - s_corr[c * 32 + j];
+              const float f = __fmul_rn(__fmul_rn(static_cast<float>(a), sxr), s_sw[c * 32 + j]);
+              v[j] = __fadd_rn(f, s_bias[c * 32 + j]);
+            }
+            if (p.out_dtype == LC_F32)
+              store_chunk<float>(p, row, col0, v);
+            else
+              store_chunk<__nv_bfloat16>(p, row, col0, v);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(as));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(TMEM_COLS))
+                 : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+// 2-D uint8 tensor [rows, K] with row stride ld, box = 128 bytes x box_rows, 128B swizzle,
+// out-of-bounds elements read as zero (so M, N and K tails need no special code).
+static int32_t make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld,
+                        int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(LC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LC_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return LC_OK;
+}
+
+static int32_t ensure_smem_attr() {
+  constexpr int kMaxDevices = 64;
+  static std::once_flag flags[kMaxDevices];
+  static cudaError_t results[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(LC_ERR_CUDA, "no current CUDA device");
+  std::call_once(flags[dev], [dev]() {
+    results[dev] = cudaFuncSetAttribute(qlinear_i8_kernel,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  });
+  if (results[dev] != cudaSuccess)
+    return fail(LC_ERR_CUDA, "cannot reserve %d bytes of shared memory: %s", SMEM_BYTES,
+                cudaGetErrorString(results[dev]));
+  return LC_OK;
+}
+
+}  // namespace gemm
+}  // namespace lc
+
+using namespace lc;
+
+extern "C" int32_t lc_qlinear_i8(const void* a, int32_t a_unsigned, int64_t lda, const int8_t* b,
+                                 int64_t ldb, int64_t M, int64_t N, int64_t K, const float* sx,
+                                 int32_t sx_per_row, const float* zx, const int32_t* wsum,
+                                 const float* sw, const float* bias, void* out, int32_t out_dtype,
+                                 int64_t ldo, int32_t* status, void* stream) {
+  using namespace lc::gemm;
+  if (M < 0 || N < 0 || K <= 0) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: bad shape");
+  if (M == 0 || N == 0) return LC_OK;
+  if (!a || !b || !out) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: null pointer");
+  if (lda < K || ldb < K || ldo < N) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: leading dimension too small");
+  if (lda % 16 || ldb % 16 || !aligned(a, 16) || !aligned(b, 16))
+    return fail(LC_ERR_UNSUPPORTED,
+                "qlinear_i8: operand rows must start on 16-byte boundaries (pad lda/ldb to 16)");
+  if ((zx == nullptr) != (wsum == nullptr))
+    return fail(LC_ERR_INVALID_ARG, "qlinear_i8: zx and wsum go together");
+  if (out_dtype != LC_F32 && out_dtype != LC_BF16 && out_dtype != LC_S32)
+    return fail(LC_ERR_UNSUPPORTED, "qlinear_i8: out_dtype %d not supported", out_dtype);
+  if (out_dtype != LC_S32 && !sx) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: sx is required");
+  if (M > 0x7fffffffLL - BM || N > 0x7fffffffLL - BN || K > 0x7fffffffLL - BK)
+    return fail(LC_ERR_UNSUPPORTED, "qlinear_i8: dimension exceeds the TMA coordinate range");
+
+  CUtensorMap map_a, map_b;
+  if (int32_t rc = make_map(&map_a, a, M, K, lda, BM)) return rc;
+  if (int32_t rc = make_map(&map_b, b, N, K, ldb, BN)) return rc;
+  if (int32_t rc = ensure_smem_attr()) return rc;
+
+  Params p;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.sx = sx;
+  p.sx_per_row = sx_per_row;
+  p.zx = zx;
+  p.wsum = wsum;
+  p.sw = sw;
+  p.bias = bias;
+  p.out = out;
+  p.out_dtype = out_dtype;
+  p.ldo = ldo;
+  const size_t esz = (out_dtype == LC_BF16) ? 2 : 4;
+  p.out_vec = (aligned(out, 16) && (ldo * esz) % 16 == 0) ? 1 : 0;
+  p.status = status;
+
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int64_t sms = sm_count();
+  const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+  qlinear_i8_kernel<<<grid, NUM_THREADS, SMEM_BYTES, as_stream(stream)>>>(
+      map_a, map_b, p, make_idesc(a_unsigned != 0));
+  return check_launch("qlinear_i8");
+}

@@ -1,0 +1,506 @@
+// Weight-only quantized Linear for decode batch sizes (HBM-bound: the weight
+// matrix is read once, activations stay in floating point).
+//
+//  * per-output-channel symmetric int8 weights (lc_wo_linear_s8):
+//      - 16-bit activations: the int8 weights are widened to bf16/f16 in
+//        registers and contracted on the tensor cores with mma.sync m16n8k16
+//        (weights are the 16-row operand, the batch is the 8-column operand).
+//        tcgen05 needs both operands in shared memory and a 128-row tile, which
+//        buys nothing for a memory-bound 1..32-column product;
+//      - fp32 activations: fp32 FMA, one warp per output row;
+//  * the group-wise affine format of engine.quantized.{quantize,dequantize,
+//    quantized_matmul} (lucid/_C/ops/quantized/QuantizedMatmul.cpp:111-207).
+#include "common.cuh"
+
+namespace lc {
+
+// streaming 16-byte load that does not displace the activations held in L1
+__device__ __forceinline__ int4 ld_stream_v4(const void* p) {
+  int4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// ---- int8 -> 16-bit float pairs ---------------------------------------------
+// `u` holds four offset-binary bytes (s8 ^ 0x80).  Returns bytes (lo, lo+1) as a
+// packed pair of XT.
+template <typename XT>
+__device__ __forceinline__ uint32_t widen_pair(uint32_t u, int lo);
+
+// f16: 0x6400 | byte is 1024 + byte exactly; subtracting 1152 gives the s8 value.
+template <>
+__device__ __forceinline__ uint32_t widen_pair<__half>(uint32_t u, int lo) {
+  const uint32_t sel = lo == 0 ? 0x7170u : 0x7372u;  // {0x64, b[lo+1], 0x64, b[lo]}
+  uint32_t h = __byte_perm(u, 0x64646464u, sel);
+  const uint32_t magic = 0x64806480u;  // 1152.0 in both halves
+  __half2 r = __hsub2(*reinterpret_cast<__half2*>(&h), *reinterpret_cast<const __half2*>(&magic));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// bf16: 0x4B000000 | byte is 2^23 + byte in fp32; subtracting 2^23 + 128 gives the
+// s8 value exactly, whose upper 16 bits are its bf16 encoding.
+template <>
+__device__ __forceinline__ uint32_t widen_pair<__nv_bfloat16>(uint32_t u, int lo) {
+  const uint32_t m = 0x4B000000u;
+  float f0 = __uint_as_float(__byte_perm(u, m, lo == 0 ? 0x7650u : 0x7652u)) - 8388736.0f;
+  float f1 = __uint_as_float(__byte_perm(u, m, lo == 0 ? 0x7651u : 0x7653u)) - 8388736.0f;
+  return __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632u);
+}
+
+template <typename XT>
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1,
+                                                         uint32_t a2, uint32_t a3, uint32_t b0,
+                                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_16816<__half>(float (&c)[4], uint32_t a0, uint32_t a1,
+                                                  uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename XT>
+__device__ __forceinline__ XT from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+
+template <typename XT>
+__device__ __forceinline__ float to_float(XT v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+
+constexpr int kWoWarps = 8;
+constexpr int kWoThreads = kWoWarps * 32;
+
+// CTA = 16*RT output rows, the K range split over 8 warps in interleaved 64-byte
+// steps (so the 8 warps together read 512 contiguous bytes of every row per
+// round), NT batch tiles of 8.  Lane (g = lane/4, t = lane%4) loads 16 weight
+// bytes of rows g and g+8 at k = 64*step + 16*t; MMA sub-step j consumes bytes
+// 4j..4j+3 of that chunk, and the activation fragment is loaded with the same
+// permutation of k, so the sum over k is unchanged.
+template <typename XT, int RT, int NT>
+__global__ void __launch_bounds__(kWoThreads)
+wo_linear_mma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx,
+                     const int8_t* __restrict__ w, int64_t ldw, int64_t N,
+                     const float* __restrict__ sw, const float* __restrict__ bias,
+                     XT* __restrict__ y, int64_t ldy) {
+  __shared__ float red[kWoWarps][RT * 16][NT * 8 + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.x) * (16 * RT);
+  const int64_t ksteps = (K + 63) >> 6;
+
+  float acc[RT][NT][4];
+#pragma unroll
+  for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[rt][nt][i] = 0.0f;
+
+#pragma unroll 2
+  for (int64_t s = warp; s < ksteps; s += kWoWarps) {
+    const int64_t k = (s << 6) + t * 16;
+    const bool k_ok = k < K;  // K is a multiple of 16, so a chunk is in or out as a whole
+    int4 wa[RT][2];
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int64_t row = n0 + rt * 16 + g + 8 * h;
+        wa[rt][h] = (k_ok && row < N) ? ld_stream_v4(w + row * ldw + k) : make_int4(0, 0, 0, 0);
+      }
+    uint32_t xa[NT][8];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int64_t b = nt * 8 + g;
+      if (k_ok && b < B) {
+        const uint4* px = reinterpret_cast<const uint4*>(x + b * ldx + k);
+        uint4 lo = __ldg(px), hi = __ldg(px + 1);
+        xa[nt][0] = lo.x; xa[nt][1] = lo.y; xa[nt][2] = lo.z; xa[nt][3] = lo.w;
+        xa[nt][4] = hi.x; xa[nt][5] = hi.y; xa[nt][6] = hi.z; xa[nt][7] = hi.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xa[nt][i] = 0u;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+        const int* w0 = reinterpret_cast<const int*>(&wa[rt][0]);
+        const int* w1 = reinterpret_cast<const int*>(&wa[rt][1]);
+        const uint32_t u0 = static_cast<uint32_t>(w0[j]) ^ 0x80808080u;
+        const uint32_t u1 = static_cast<uint32_t>(w1[j]) ^ 0x80808080u;
+        const uint32_t a0 = widen_pair<XT>(u0, 0), a2 = widen_pair<XT>(u0, 2);
+        const uint32_t a1 = widen_pair<XT>(u1, 0), a3 = widen_pair<XT>(u1, 2);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+          mma_16816<XT>(acc[rt][nt], a0, a1, a2, a3, xa[nt][2 * j], xa[nt][2 * j + 1]);
+      }
+    }
+  }
+
+  // split-K reduction across the 8 warps, then scale + bias
+#pragma unroll
+  for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      red[warp][rt * 16 + g][nt * 8 + 2 * t] = acc[rt][nt][0];
+      red[warp][rt * 16 + g][nt * 8 + 2 * t + 1] = acc[rt][nt][1];
+      red[warp][rt * 16 + g + 8][nt * 8 + 2 * t] = acc[rt][nt][2];
+      red[warp][rt * 16 + g + 8][nt * 8 + 2 * t + 1] = acc[rt][nt][3];
+    }
+  __syncthreads();
+  constexpr int ROWS = RT * 16, COLS = NT * 8;
+  for (int o = threadIdx.x; o < ROWS * COLS; o += kWoThreads) {
+    const int r = o % ROWS, bcol = o / ROWS;
+    const int64_t n = n0 + r;
+    if (n < N && bcol < B) {
+      float sum = 0.0f;
+#pragma unroll
+      for (int wp = 0; wp < kWoWarps; ++wp) sum += red[wp][r][bcol];
+      float v = sum * (sw ? __ldg(sw + n) : 1.0f);
+      if (bias) v += __ldg(bias + n);
+      y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(v);
+    }
+  }
+}
+
+// generic path (any activation type, any K): one warp per output row, fp32 FMA,
+// the batch handled in chunks of BT
+template <typename XT, int BT>
+__global__ void __launch_bounds__(kWoThreads)
+wo_linear_fma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx,
+                     const int8_t* __restrict__ w, int64_t ldw, int64_t N,
+                     const float* __restrict__ sw, const float* __restrict__ bias,
+                     XT* __restrict__ y, int64_t ldy) {
+  const int lane = threadIdx.x & 31;
+  const int64_t n = static_cast<int64_t>(blockIdx.x) * kWoWarps + (threadIdx.x >> 5);
+  if (n >= N) return;
+  const int8_t* wr = w + n * ldw;
+  for (int64_t b0 = 0; b0 < B; b0 += BT) {
+    float acc[BT];
+#pragma unroll
+    for (int i = 0; i < BT; ++i) acc[i] = 0.0f;
+    for (int64_t k = lane; k < K; k += 32) {
+      const float wv = static_cast<float>(wr[k]);
+#pragma unroll
+      for (int i = 0; i < BT; ++i)
+        if (b0 + i < B) acc[i] = fmaf(to_float<XT>(x[(b0 + i) * ldx + k]), wv, acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < BT; ++i) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+      if (lane == 0 && b0 + i < B) {
+        float v = acc[i] * (sw ? __ldg(sw + n) : 1.0f);
+        if (bias) v += __ldg(bias + n);
+        y[(b0 + i) * ldy + n] = from_float<XT>(v);
+      }
+    }
+  }
+}
+
+// ---- group-wise affine format -------------------------------------------------
+// one thread per packed 32-bit word; the threads of a group reduce min/max with
+// shuffles (a group spans gs / (32/bits) in {4, 8, 16, 32} adjacent lanes)
+template <int BITS>
+__global__ void __launch_bounds__(256)
+group_quantize_kernel(const float* __restrict__ w, int64_t words_total, int words_per_row, int64_t K,
+                      int group_size, uint32_t* __restrict__ packed, float* __restrict__ scales,
+                      float* __restrict__ biases) {
+  constexpr int PER = 32 / BITS;
+  const int64_t word = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const bool live = word < words_total;
+  const int64_t row = live ? word / words_per_row : 0;
+  const int wcol = live ? static_cast<int>(word % words_per_row) : 0;
+  float v[PER];
+  float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    v[i] = live ? __ldg(w + row * K + static_cast<int64_t>(wcol) * PER + i) : 0.0f;
+    if (live) {
+      mn = fminf(mn, v[i]);
+      mx = fmaxf(mx, v[i]);
+    }
+  }
+  const int lanes = group_size / PER;  // power of two, <= 32; groups never straddle a warp
+  for (int o = lanes >> 1; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if (!live) return;
+  const float levels = static_cast<float>((1 << BITS) - 1);
+  const float scale = __fdiv_rn(__fsub_rn(mx, mn), levels);
+  const float safe = scale > 0.0f ? scale : 1.0f;
+  uint32_t word_bits = 0;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    float tq = rintf(__fdiv_rn(__fsub_rn(v[i], mn), safe));
+    tq = fminf(fmaxf(tq, 0.0f), levels);
+    word_bits |= static_cast<uint32_t>(__float2int_rn(tq)) << (BITS * i);
+  }
+  packed[word] = word_bits;
+  const int64_t first = static_cast<int64_t>(wcol) * PER;
+  if (first % group_size == 0) {
+    const int64_t gidx = row * (K / group_size) + first / group_size;
+    scales[gidx] = scale;
+    biases[gidx] = mn;
+  }
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(256)
+group_dequantize_kernel(const uint32_t* __restrict__ packed, const float* __restrict__ scales,
+                        const float* __restrict__ biases, int64_t words_total, int words_per_row,
+                        int64_t K, int group_size, float* __restrict__ out) {
+  constexpr int PER = 32 / BITS;
+  const int64_t word = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (word >= words_total) return;
+  const int64_t row = word / words_per_row;
+  const int64_t first = (word % words_per_row) * PER;
+  const int64_t gidx = row * (K / group_size) + first / group_size;
+  const float s = __ldg(scales + gidx), b = __ldg(biases + gidx);
+  const uint32_t bits = __ldg(packed + word);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const float c = static_cast<float>((bits >> (BITS * i)) & ((1u << BITS) - 1u));
+    out[row * K + first + i] = __fadd_rn(__fmul_rn(c, s), b);
+  }
+}
+
+// y[b,n] = sum_k x[b,k] * (c[n,k]*s + bias): one warp per output row, lanes stride
+// over packed words, fp32 accumulation, batch in chunks of BT
+template <typename XT, int BITS, int BT>
+__global__ void __launch_bounds__(kWoThreads)
+group_matmul_kernel(const XT* __restrict__ x, int64_t B, int64_t K, const uint32_t* __restrict__ packed,
+                    const float* __restrict__ scales, const float* __restrict__ biases, int64_t N,
+                    int group_size, XT* __restrict__ y) {
+  constexpr int PER = 32 / BITS;
+  const int lane = threadIdx.x & 31;
+  const int64_t n = static_cast<int64_t>(blockIdx.x) * kWoWarps + (threadIdx.x >> 5);
+  if (n >= N) return;
+  const int64_t words = K / PER;
+  const int64_t groups = K / group_size;
+  const uint32_t* pr = packed + n * words;
+  for (int64_t b0 = 0; b0 < B; b0 += BT) {
+    float acc[BT];
+#pragma unroll
+    for (int i = 0; i < BT; ++i) acc[i] = 0.0f;
+    for (int64_t wd = lane; wd < words; wd += 32) {
+      const uint32_t bits = __ldg(pr + wd);
+      const int64_t k0 = wd * PER;
+      const int64_t gidx = n * groups + k0 / group_size;
+      const float s = __ldg(scales + gidx), bb = __ldg(biases + gidx);
+#pragma unroll
+      for (int e = 0; e < PER; ++e) {
+        const float c = static_cast<float>((bits >> (BITS * e)) & ((1u << BITS) - 1u));
+        const float wv = fmaf(c, s, bb);
+#pragma unroll
+        for (int i = 0; i < BT; ++i)
+          if (b0 + i < B) acc[i] = fmaf(to_float<XT>(x[(b0 + i) * K + k0 + e]), wv, acc[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < BT; ++i) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+      if (lane == 0 && b0 + i < B) y[(b0 + i) * N + n] = from_float<XT>(acc[i]);
+    }
+  }
+}
+
+// ---- launchers ------------------------------------------------------------------
+template <typename XT>
+static int32_t launch_wo_mma(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
+                             int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
+                             int64_t ldy, cudaStream_t st) {
+  // enough CTAs to cover every SM at least twice before widening the row tile
+  const bool wide = (N / 32) >= 2 * static_cast<int64_t>(sm_count());
+  const int rows = wide ? 32 : 16;
+  const unsigned grid = static_cast<unsigned>((N + rows - 1) / rows);
+#define LC_WO(RT, NT) \
+  wo_linear_mma_kernel<XT, RT, NT><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy)
+  if (wide) {
+    if (B <= 8) LC_WO(2, 1);
+    else if (B <= 16) LC_WO(2, 2);
+    else LC_WO(2, 4);
+  } else {
+    if (B <= 8) LC_WO(1, 1);
+    else if (B <= 16) LC_WO(1, 2);
+    else LC_WO(1, 4);
+  }
+#undef LC_WO
+  return check_launch("wo_linear_s8 (mma)");
+}
+
+template <typename XT>
+static int32_t launch_wo_fma(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
+                             int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
+                             int64_t ldy, cudaStream_t st) {
+  const unsigned grid = static_cast<unsigned>((N + kWoWarps - 1) / kWoWarps);
+  if (B <= 1)
+    wo_linear_fma_kernel<XT, 1><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy);
+  else if (B <= 4)
+    wo_linear_fma_kernel<XT, 4><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy);
+  else
+    wo_linear_fma_kernel<XT, 8><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy);
+  return check_launch("wo_linear_s8 (fma)");
+}
+
+template <typename XT>
+static int32_t wo_linear_typed(const void* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
+                               int64_t ldw, int64_t N, const float* sw, const float* bias, void* y,
+                               int64_t ldy, cudaStream_t st) {
+  const XT* xt = static_cast<const XT*>(x);
+  XT* yt = static_cast<XT*>(y);
+  const bool mma_ok = sizeof(XT) == 2 && K % 16 == 0 && ldw % 16 == 0 && ldx % 8 == 0 &&
+                      aligned(w, 16) && aligned(x, 16);
+  for (int64_t b0 = 0; b0 < B; b0 += 32) {
+    const int64_t bc = (B - b0 < 32) ? (B - b0) : 32;
+    int32_t rc;
+    if constexpr (sizeof(XT) == 2) {
+      rc = mma_ok ? launch_wo_mma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st)
+                  : launch_wo_fma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st);
+    } else {
+      rc = launch_wo_fma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st);
+    }
+    if (rc) return rc;
+  }
+  return LC_OK;
+}
+
+template <typename XT, int BITS>
+static int32_t launch_group_matmul(const XT* x, int64_t B, int64_t K, const uint32_t* packed,
+                                   const float* scales, const float* biases, int64_t N, int gs, XT* y,
+                                   cudaStream_t st) {
+  const unsigned grid = static_cast<unsigned>((N + kWoWarps - 1) / kWoWarps);
+  if (B <= 1)
+    group_matmul_kernel<XT, BITS, 1><<<grid, kWoThreads, 0, st>>>(x, B, K, packed, scales, biases, N, gs, y);
+  else if (B <= 4)
+    group_matmul_kernel<XT, BITS, 4><<<grid, kWoThreads, 0, st>>>(x, B, K, packed, scales, biases, N, gs, y);
+  else
+    group_matmul_kernel<XT, BITS, 8><<<grid, kWoThreads, 0, st>>>(x, B, K, packed, scales, biases, N, gs, y);
+  return check_launch("group_matmul");
+}
+
+static int32_t check_group_args(int64_t N, int64_t K, int32_t gs, int32_t bits) {
+  if (bits != 4 && bits != 8) return fail(LC_ERR_UNSUPPORTED, "group format: bits must be 4 or 8, got %d", bits);
+  if (gs != 32 && gs != 64 && gs != 128)
+    return fail(LC_ERR_UNSUPPORTED, "group format: group_size must be 32, 64 or 128, got %d", gs);
+  if (N < 0 || K <= 0 || K % gs != 0)
+    return fail(LC_ERR_INVALID_ARG, "group format: K=%lld must be a positive multiple of group_size=%d",
+                (long long)K, gs);
+  return LC_OK;
+}
+
+}  // namespace lc
+
+using namespace lc;
+
+extern "C" int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K,
+                                   int64_t ldx, const int8_t* wq, int64_t ldw, int64_t N,
+                                   const float* sw, const float* bias, void* y, int64_t ldy,
+                                   void* stream) {
+  if (batch < 0 || N < 0 || K <= 0 || ldx < K || ldw < K || ldy < N)
+    return fail(LC_ERR_INVALID_ARG, "wo_linear_s8: bad shape");
+  if (batch == 0 || N == 0) return LC_OK;
+  if (!x || !wq || !y) return fail(LC_ERR_INVALID_ARG, "wo_linear_s8: null pointer");
+  cudaStream_t st = as_stream(stream);
+  switch (x_dtype) {
+    case LC_F32:
+      return wo_linear_typed<float>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, st);
+    case LC_BF16:
+      return wo_linear_typed<__nv_bfloat16>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, st);
+    case LC_F16:
+      return wo_linear_typed<__half>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, st);
+  }
+  return fail(LC_ERR_UNSUPPORTED, "wo_linear_s8: x_dtype %d not supported", x_dtype);
+}
+
+extern "C" int32_t lc_group_quantize_f32(const float* w, int64_t N, int64_t K, int32_t group_size,
+                                         int32_t bits, int32_t* packed, float* scales,
+                                         float* biases, void* stream) {
+  if (int32_t rc = check_group_args(N, K, group_size, bits)) return rc;
+  if (N == 0) return LC_OK;
+  if (!w || !packed || !scales || !biases) return fail(LC_ERR_INVALID_ARG, "group_quantize: null pointer");
+  const int per = 32 / bits;
+  const int words_per_row = static_cast<int>(K / per);
+  const int64_t total = N * words_per_row;
+  const unsigned grid = static_cast<unsigned>((total + 255) / 256);
+  uint32_t* pk = reinterpret_cast<uint32_t*>(packed);
+  if (bits == 8)
+    group_quantize_kernel<8><<<grid, 256, 0, as_stream(stream)>>>(w, total, words_per_row, K, group_size, pk, scales, biases);
+  else
+    group_quantize_kernel<4><<<grid, 256, 0, as_stream(stream)>>>(w, total, words_per_row, K, group_size, pk, scales, biases);
+  return check_launch("group_quantize");
+}
+
+extern "C" int32_t lc_group_dequantize(const int32_t* packed, const float* scales,
+                                       const float* biases, int64_t N, int64_t K,
+                                       int32_t group_size, int32_t bits, float* out, void* stream) {
+  if (int32_t rc = check_group_args(N, K, group_size, bits)) return rc;
+  if (N == 0) return LC_OK;
+  if (!packed || !scales || !biases || !out) return fail(LC_ERR_INVALID_ARG, "group_dequantize: null pointer");
+  const int per = 32 / bits;
+  const int words_per_row = static_cast<int>(K / per);
+  const int64_t total = N * words_per_row;
+  const unsigned grid = static_cast<unsigned>((total + 255) / 256);
+  const uint32_t* pk = reinterpret_cast<const uint32_t*>(packed);
+  if (bits == 8)
+    group_dequantize_kernel<8><<<grid, 256, 0, as_stream(stream)>>>(pk, scales, biases, total, words_per_row, K, group_size, out);
+  else
+    group_dequantize_kernel<4><<<grid, 256, 0, as_stream(stream)>>>(pk, scales, biases, total, words_per_row, K, group_size, out);
+  return check_launch("group_dequantize");
+}
+
+extern "C" int32_t lc_group_matmul(const void* x, int32_t x_dtype, int64_t batch, int64_t K,
+                                   const int32_t* packed, const float* scales, const float* biases,
+                                   int64_t N, int32_t group_size, int32_t bits, void* y,
+                                   void* stream) {
+  if (int32_t rc = check_group_args(N, K, group_size, bits)) return rc;
+  if (batch < 0) return fail(LC_ERR_INVALID_ARG, "group_matmul: bad batch");
+  if (batch == 0 || N == 0) return LC_OK;
+  if (!x || !packed || !scales || !biases || !y) return fail(LC_ERR_INVALID_ARG, "group_matmul: null pointer");
+  cudaStream_t st = as_stream(stream);
+  const uint32_t* pk = reinterpret_cast<const uint32_t*>(packed);
+#define LC_GM(XT)                                                                                     \
+  (bits == 8 ? launch_group_matmul<XT, 8>(static_cast<const XT*>(x), batch, K, pk, scales, biases, N, \
+                                          group_size, static_cast<XT*>(y), st)                        \
+             : launch_group_matmul<XT, 4>(static_cast<const XT*>(x), batch, K, pk, scales, biases, N, \
+                                          group_size, static_cast<XT*>(y), st))
+  switch (x_dtype) {
+    case LC_F32:
+      return LC_GM(float);
+    case LC_BF16:
+      return LC_GM(__nv_bfloat16);
+    case LC_F16:
+      return LC_GM(__half);
+  }
+#undef LC_GM
+  return fail(LC_ERR_UNSUPPORTED, "group_matmul: x_dtype %d not supported", x_dtype);
+}

@@ -1,0 +1,393 @@
+"""torch-tensor front end of the C ABI: allocates outputs with torch, passes raw
+device pointers and the current CUDA stream to liblucid_cuda.
+
+PyTorch is used here for device memory and streams only; all arithmetic on the
+quantized path happens in the library's kernels.  Every function requires CUDA
+tensors and raises otherwise -- there is no CPU fallback.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import (LC_BF16, LC_F16, LC_F32, LC_S8, LC_S16, LC_S32, LC_U8, LucidCudaError, check, lib)
+
+_DTYPE = {
+    torch.float32: LC_F32,
+    torch.bfloat16: LC_BF16,
+    torch.float16: LC_F16,
+    torch.int8: LC_S8,
+    torch.uint8: LC_U8,
+    torch.int16: LC_S16,
+    torch.int32: LC_S32,
+}
+
+
+def _lc_dtype(dt: torch.dtype) -> int:
+    try:
+        return _DTYPE[dt]
+    except KeyError:
+        raise TypeError(f"dtype {dt} is not supported by liblucid_cuda") from None
+
+
+def _need_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(
+                "liblucid_cuda kernels take CUDA tensors only (there is no CPU fallback); "
+                f"got a tensor on {t.device}"
+            )
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"tensors on different devices: {dev} and {t.device}")
+    return dev
+
+
+def _stream(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _f32c(t: torch.Tensor) -> torch.Tensor:
+    if t.dtype != torch.float32:
+        t = t.to(torch.float32)
+    return t.contiguous()
+
+
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def observe_workspace(dev: torch.device) -> torch.Tensor:
+    """Zero-filled scratch for the global-range kernels, one per (device, stream):
+    calls on the same stream are ordered, so they can share it."""
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev))
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        ws = torch.zeros(int(lib.lc_observe_tensor_workspace_bytes()), dtype=torch.uint8, device=dev)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def channel_layout(shape, ch_axis: int | None) -> tuple[int, int, int]:
+    """(outer, channels, inner) of a contiguous tensor split at ``ch_axis``."""
+    if ch_axis is None:
+        return 1, 1, math.prod(shape)
+    ax = ch_axis % len(shape)
+    return math.prod(shape[:ax]), shape[ax], math.prod(shape[ax + 1:])
+
+
+# ----------------------------------------------------------------------------
+# observers / qparams
+# ----------------------------------------------------------------------------
+def observe_tensor(x, min_out, max_out, accumulate: bool, qspec=None):
+    """Global running min/max of ``x`` into the 0-d buffers ``min_out``/``max_out``.
+
+    ``qspec = (symmetric, qmin, qmax, signed, eps)`` additionally returns the
+    ``(scale, zero_point)`` of the merged range, computed in the same launch.
+    """
+    dev = _need_cuda(x, min_out, max_out)
+    x = _f32c(x)
+    scale = zp = None
+    sym, qmin, qmax, signed, eps = (0, 0, 255, 0, 1e-8)
+    if qspec is not None:
+        sym, qmin, qmax, signed, eps = qspec
+        scale = torch.empty((), dtype=torch.float32, device=dev)
+        zp = torch.empty((), dtype=torch.float32, device=dev)
+    ws = observe_workspace(dev)
+    with torch.cuda.device(dev):
+        check(lib.lc_observe_tensor_f32(x.data_ptr(), x.numel(), min_out.data_ptr(), max_out.data_ptr(),
+                                        int(accumulate), int(sym), int(qmin), int(qmax), int(signed),
+                                        float(eps), _ptr(scale), _ptr(zp), ws.data_ptr(), ws.numel(),
+                                        _stream(dev)))
+    return (scale, zp) if qspec is not None else None
+
+
+def observe_channel(x, ch_axis: int, min_out, max_out, accumulate: bool) -> None:
+    dev = _need_cuda(x, min_out, max_out)
+    x = _f32c(x)
+    outer, ch, inner = channel_layout(x.shape, ch_axis)
+    if min_out.numel() != ch or max_out.numel() != ch:
+        raise ValueError(f"running buffers hold {min_out.numel()} channels, input has {ch}")
+    with torch.cuda.device(dev):
+        check(lib.lc_observe_channel_f32(x.data_ptr(), outer, ch, inner, min_out.data_ptr(),
+                                         max_out.data_ptr(), int(accumulate), _stream(dev)))
+
+
+def calculate_qparams(min_t, max_t, symmetric: bool, qmin: int, qmax: int, signed: bool, eps: float):
+    dev = _need_cuda(min_t, max_t)
+    mn, mx = _f32c(min_t), _f32c(max_t)
+    if mn.shape != mx.shape:
+        mn, mx = torch.broadcast_tensors(mn, mx)
+        mn, mx = mn.contiguous(), mx.contiguous()
+    scale, zp = torch.empty_like(mn), torch.empty_like(mn)
+    with torch.cuda.device(dev):
+        check(lib.lc_calculate_qparams_f32(mn.data_ptr(), mx.data_ptr(), mn.numel(), int(symmetric),
+                                           int(qmin), int(qmax), int(signed), float(eps),
+                                           scale.data_ptr(), zp.data_ptr(), _stream(dev)))
+    return scale, zp
+
+
+# ----------------------------------------------------------------------------
+# quantize / dequantize / fake_quantize
+# ----------------------------------------------------------------------------
+def _params(scale, zero_point, dev, channels: int, per_channel: bool):
+    """Split (scale, zero_point) into device tensors and host scalars.
+
+    A tensor scale is inverted on the device (fp32 IEEE division); a Python
+    number is inverted here in double precision and rounded once to fp32 when
+    ctypes narrows it, exactly as the reference's dispatcher does with
+    ``1.0 / s`` for a Python float (``lucid/_dispatch.py:154-170``).
+    """
+    s_t = z_t = None
+    h_inv = h_s = h_z = 0.0
+    if isinstance(scale, torch.Tensor):
+        s_t = _f32c(scale.to(dev)).reshape(-1)
+        if s_t.numel() != 1 and not (per_channel and s_t.numel() == channels):
+            raise ValueError(f"scale has {s_t.numel()} entries; expected 1 or {channels} along ch_axis")
+    else:
+        h_s = float(scale)
+        h_inv = 1.0 / h_s
+    if isinstance(zero_point, torch.Tensor):
+        z_t = _f32c(zero_point.to(dev)).reshape(-1)
+        if z_t.numel() != 1 and not (per_channel and z_t.numel() == channels):
+            raise ValueError(f"zero_point has {z_t.numel()} entries; expected 1 or {channels}")
+    else:
+        h_z = float(zero_point)
+    return s_t, z_t, h_inv, h_s, h_z
+
+
+def quantize(x, scale, zero_point, qmin: int, qmax: int, storage: torch.dtype, ch_axis=None):
+    dev = _need_cuda(x)
+    x = _f32c(x)
+    per_channel = ch_axis is not None and isinstance(scale, torch.Tensor) and scale.numel() > 1
+    outer, ch, inner = channel_layout(x.shape, ch_axis if per_channel else None)
+    s_t, z_t, h_inv, _, h_z = _params(scale, zero_point, dev, ch, per_channel)
+    out = torch.empty(x.shape, dtype=storage, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.lc_quantize_f32(x.data_ptr(), outer, ch, inner, _ptr(s_t), 0 if s_t is None else s_t.numel(),
+                                  _ptr(z_t), 0 if z_t is None else z_t.numel(), h_inv, h_z, int(qmin),
+                                  int(qmax), out.data_ptr(), _lc_dtype(storage), _stream(dev)))
+    return out
+
+
+def dequantize(q, scale, zero_point, ch_axis=None, out_dtype: torch.dtype = torch.float32):
+    dev = _need_cuda(q)
+    q = q.contiguous()
+    per_channel = ch_axis is not None and isinstance(scale, torch.Tensor) and scale.numel() > 1
+    outer, ch, inner = channel_layout(q.shape, ch_axis if per_channel else None)
+    s_t, z_t, _, h_s, h_z = _params(scale, zero_point, dev, ch, per_channel)
+    out = torch.empty(q.shape, dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.lc_dequantize(q.data_ptr(), _lc_dtype(q.dtype), outer, ch, inner, _ptr(s_t),
+                                0 if s_t is None else s_t.numel(), _ptr(z_t),
+                                0 if z_t is None else z_t.numel(), h_s, h_z, out.data_ptr(),
+                                _lc_dtype(out_dtype), _stream(dev)))
+    return out
+
+
+def fake_quantize(x, scale, zero_point, qmin: int, qmax: int, ch_axis=None, want_mask: bool = False):
+    dev = _need_cuda(x)
+    x = _f32c(x)
+    per_channel = ch_axis is not None and isinstance(scale, torch.Tensor) and scale.numel() > 1
+    outer, ch, inner = channel_layout(x.shape, ch_axis if per_channel else None)
+    s_t, z_t, h_inv, h_s, h_z = _params(scale, zero_point, dev, ch, per_channel)
+    out = torch.empty_like(x)
+    mask = torch.empty_like(x) if want_mask else None
+    with torch.cuda.device(dev):
+        check(lib.lc_fake_quantize_f32(x.data_ptr(), outer, ch, inner, _ptr(s_t),
+                                       0 if s_t is None else s_t.numel(), _ptr(z_t),
+                                       0 if z_t is None else z_t.numel(), h_inv, h_s, h_z, int(qmin),
+                                       int(qmax), out.data_ptr(), _ptr(mask), _stream(dev)))
+    return out, mask
+
+
+# ----------------------------------------------------------------------------
+# fused dynamic activation quantization
+# ----------------------------------------------------------------------------
+def _pad16(k: int) -> int:
+    return (k + 15) // 16 * 16
+
+
+def dynamic_quantize_rows(x2d, symmetric: bool, qmin: int, qmax: int, signed: bool, eps: float = 1e-8,
+                          out_dtype: torch.dtype = torch.int8, pad_rows_to_16: bool = False):
+    """Per-row observer + qparams + quantize in one pass.  Returns ``(q, scale, zp)``;
+    with ``pad_rows_to_16`` the code matrix is a view into storage whose row stride
+    is a multiple of 16 bytes (what the TMA-fed GEMM needs)."""
+    dev = _need_cuda(x2d)
+    x2d = _f32c(x2d)
+    rows, cols = x2d.shape
+    ldq = _pad16(cols) if pad_rows_to_16 else cols
+    store = torch.empty((rows, ldq), dtype=out_dtype, device=dev)
+    scale = torch.empty(rows, dtype=torch.float32, device=dev)
+    zp = torch.empty(rows, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.lc_dynamic_quantize_rows_f32(x2d.data_ptr(), rows, cols, cols, int(symmetric), int(qmin),
+                                               int(qmax), int(signed), float(eps), store.data_ptr(),
+                                               _lc_dtype(out_dtype), ldq, scale.data_ptr(), zp.data_ptr(),
+                                               _stream(dev)))
+    return store[:, :cols], scale, zp
+
+
+def dynamic_quantize_tensor(x2d, symmetric: bool, qmin: int, qmax: int, signed: bool, eps: float = 1e-8,
+                            out_dtype: torch.dtype = torch.uint8, pad_rows_to_16: bool = False):
+    """Global range -> qparams -> quantize, everything staying on the device.
+    Returns ``(q, scale, zp, minmax)`` with 0-d ``scale``/``zp`` and ``minmax = [min, max]``."""
+    dev = _need_cuda(x2d)
+    x2d = _f32c(x2d)
+    rows, cols = x2d.shape
+    ldq = _pad16(cols) if pad_rows_to_16 else cols
+    store = torch.empty((rows, ldq), dtype=out_dtype, device=dev)
+    scale = torch.empty((), dtype=torch.float32, device=dev)
+    zp = torch.empty((), dtype=torch.float32, device=dev)
+    minmax = torch.empty(2, dtype=torch.float32, device=dev)
+    ws = observe_workspace(dev)
+    with torch.cuda.device(dev):
+        check(lib.lc_dynamic_quantize_tensor_f32(x2d.data_ptr(), rows, cols, cols, int(symmetric), int(qmin),
+                                                 int(qmax), int(signed), float(eps), store.data_ptr(),
+                                                 _lc_dtype(out_dtype), ldq, scale.data_ptr(), zp.data_ptr(),
+                                                 minmax.data_ptr(), ws.data_ptr(), ws.numel(), _stream(dev)))
+    return store[:, :cols], scale, zp, minmax
+
+
+# ----------------------------------------------------------------------------
+# int8 GEMM
+# ----------------------------------------------------------------------------
+def pad_rows_to_16(codes: torch.Tensor) -> torch.Tensor:
+    """[R, K] int8/uint8 codes -> a view [R, K] into storage with a 16-byte row pitch."""
+    r, k = codes.shape
+    if codes.stride(1) == 1 and codes.stride(0) % 16 == 0 and codes.data_ptr() % 16 == 0:
+        return codes
+    store = torch.zeros((r, _pad16(k)), dtype=codes.dtype, device=codes.device)
+    store[:, :k] = codes
+    return store[:, :k]
+
+
+def rowsum_s8(b: torch.Tensor) -> torch.Tensor:
+    dev = _need_cuda(b)
+    if b.dtype != torch.int8 or b.dim() != 2 or b.stride(1) != 1:
+        raise TypeError("rowsum_s8 expects a 2-D int8 matrix with unit column stride")
+    out = torch.empty(b.shape[0], dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.lc_rowsum_s8(b.data_ptr(), b.shape[0], b.shape[1], b.stride(0), out.data_ptr(), _stream(dev)))
+    return out
+
+
+def qlinear_i8(a, b, sx, sw, bias=None, zx=None, wsum=None, out_dtype: torch.dtype = torch.float32,
+               status: torch.Tensor | None = None):
+    """``out = f32(a @ b^T - zx*wsum) * sx * sw + bias`` on the tcgen05 int8 path.
+
+    ``a``: [M,K] int8 or uint8 codes, ``b``: [N,K] int8 codes, both with unit
+    column stride and a 16-byte row pitch (see :func:`pad_rows_to_16`).
+    ``sx``: 0-d / 1-element (per tensor) or [M] (per row) fp32.  With
+    ``out_dtype=torch.int32`` the raw (zero-point corrected) accumulator is returned.
+    """
+    dev = _need_cuda(a, b, sx, sw, bias, zx, wsum, status)
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise ValueError(f"qlinear_i8: shapes {tuple(a.shape)} x {tuple(b.shape)}^T do not contract")
+    if a.dtype not in (torch.int8, torch.uint8) or b.dtype != torch.int8:
+        raise TypeError("qlinear_i8: a must be int8/uint8 and b int8")
+    if a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("qlinear_i8: operands need unit column stride")
+    M, K = a.shape
+    N = b.shape[0]
+    out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    per_row = 0
+    if sx is not None:
+        sx = _f32c(sx).reshape(-1)
+        if sx.numel() == M and M != 1:
+            per_row = 1
+        elif sx.numel() != 1:
+            raise ValueError(f"qlinear_i8: sx has {sx.numel()} entries, expected 1 or {M}")
+    for name, t in (("sw", sw), ("bias", bias), ("wsum", wsum)):
+        if t is not None and t.numel() != N:
+            raise ValueError(f"qlinear_i8: {name} has {t.numel()} entries, expected {N}")
+    sw_c = None if sw is None else _f32c(sw)
+    bias_c = None if bias is None else _f32c(bias)
+    zx_c = None if zx is None else _f32c(zx).reshape(-1)
+    wsum_c = None if wsum is None else wsum.to(torch.int32).contiguous()
+    with torch.cuda.device(dev):
+        check(lib.lc_qlinear_i8(a.data_ptr(), int(a.dtype == torch.uint8), a.stride(0), b.data_ptr(),
+                                b.stride(0), M, N, K, _ptr(sx), per_row, _ptr(zx_c), _ptr(wsum_c),
+                                _ptr(sw_c), _ptr(bias_c), out.data_ptr(), _lc_dtype(out_dtype), N,
+                                _ptr(status), _stream(dev)))
+    return out
+
+
+# ----------------------------------------------------------------------------
+# weight-only paths
+# ----------------------------------------------------------------------------
+def wo_linear_s8(x2d, wq, sw, bias=None):
+    """``y = (x @ wq^T) * sw + bias`` with float activations; ``y`` has ``x``'s dtype."""
+    dev = _need_cuda(x2d, wq, sw, bias)
+    if x2d.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+        raise TypeError(f"wo_linear_s8: activations must be fp32/bf16/fp16, got {x2d.dtype}")
+    x2d = x2d.contiguous()
+    if wq.dtype != torch.int8 or wq.stride(1) != 1:
+        raise TypeError("wo_linear_s8: weights must be int8 with unit column stride")
+    B, K = x2d.shape
+    N = wq.shape[0]
+    if wq.shape[1] != K:
+        raise ValueError(f"wo_linear_s8: in_features mismatch {wq.shape[1]} vs {K}")
+    y = torch.empty((B, N), dtype=x2d.dtype, device=dev)
+    sw_c = None if sw is None else _f32c(sw)
+    bias_c = None if bias is None else _f32c(bias)
+    with torch.cuda.device(dev):
+        check(lib.lc_wo_linear_s8(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq.data_ptr(),
+                                  wq.stride(0), N, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N, _stream(dev)))
+    return y
+
+
+def group_quantize(w, group_size: int = 64, bits: int = 8):
+    dev = _need_cuda(w)
+    if w.dim() != 2:
+        raise ValueError("group_quantize expects a 2-D weight")
+    w = _f32c(w)
+    N, K = w.shape
+    if bits not in (4, 8) or K % group_size != 0:
+        raise ValueError(f"group_quantize: bits={bits}, group_size={group_size}, K={K} not supported")
+    packed = torch.empty((N, K * bits // 32), dtype=torch.int32, device=dev)
+    scales = torch.empty((N, K // group_size), dtype=torch.float32, device=dev)
+    biases = torch.empty((N, K // group_size), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.lc_group_quantize_f32(w.data_ptr(), N, K, group_size, bits, packed.data_ptr(),
+                                        scales.data_ptr(), biases.data_ptr(), _stream(dev)))
+    return packed, scales, biases
+
+
+def group_dequantize(packed, scales, biases, group_size: int = 64, bits: int = 8):
+    dev = _need_cuda(packed, scales, biases)
+    packed = packed.contiguous()
+    N = packed.shape[0]
+    K = packed.shape[1] * 32 // bits
+    out = torch.empty((N, K), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.lc_group_dequantize(packed.data_ptr(), _f32c(scales).data_ptr(), _f32c(biases).data_ptr(),
+                                      N, K, group_size, bits, out.data_ptr(), _stream(dev)))
+    return out
+
+
+def group_matmul(x2d, packed, scales, biases, group_size: int = 64, bits: int = 8):
+    dev = _need_cuda(x2d, packed, scales, biases)
+    x2d = x2d.contiguous()
+    packed = packed.contiguous()
+    B, K = x2d.shape
+    N = packed.shape[0]
+    if packed.shape[1] * 32 // bits != K:
+        raise ValueError("group_matmul: packed weight does not match x's inner dimension")
+    y = torch.empty((B, N), dtype=x2d.dtype, device=dev)
+    sc, bi = _f32c(scales), _f32c(biases)
+    with torch.cuda.device(dev):
+        check(lib.lc_group_matmul(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, packed.data_ptr(), sc.data_ptr(),
+                                  bi.data_ptr(), N, group_size, bits, y.data_ptr(), _stream(dev)))
+    return y
+
+
+__all__ = [n for n in dir() if not n.startswith("_")] + ["LucidCudaError"]

@@ -157,7 +157,7 @@ def saturating_cast(codes: np.ndarray, storage: str) -> np.ndarray:
     """float -> int cast that saturates and maps NaN to 0
     (``lucid/_C/backend/cpu/methods/Factory.cpp:103-135``)."""
     info = np.iinfo(storage)
-    c = np.where(np.isnan(codes), F32(0.0), codes)
+    c = np.where(np.isnan(codes), 0.0, np.asarray(codes, dtype=np.float64))
     c = np.clip(c, float(info.min), float(info.max))
     return np.trunc(c).astype(storage)
 

@@ -1,0 +1,75 @@
+"""CPU checks of the C-ABI boundary: the shared library loads, exports every
+symbol include/lucid_cuda.h declares, and rejects bad arguments without a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "lucid_cuda.h")
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from lucid_b200._C import build as B
+
+    B.build()
+    import lucid_b200._C as capi
+
+    return capi
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(lc_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_expected_entry_points():
+    names = declared_symbols()
+    for required in ("lc_quantize_f32", "lc_dequantize", "lc_qlinear_i8", "lc_wo_linear_s8",
+                     "lc_observe_tensor_f32", "lc_group_matmul"):
+        assert required in names
+
+
+def test_library_exports_every_declared_symbol(capi):
+    lib = ctypes.CDLL(capi.LIB_PATH)
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} declared in lucid_cuda.h but not exported"
+    assert set(declared_symbols()) == set(capi.SIGNATURES), "ctypes table out of sync with the header"
+
+
+def test_version_and_error_text(capi):
+    assert capi.lib.lc_version() >= 100
+    rc = capi.lib.lc_quantize_f32(None, 1, 1, 8, None, 0, None, 0, 1.0, 0.0, -128, 127, None, capi.LC_S8, None)
+    assert rc == capi.LC_ERR_INVALID_ARG
+    assert "null pointer" in capi.last_error()
+    with pytest.raises(capi.LucidCudaError):
+        capi.check(rc)
+
+
+def test_argument_validation_without_gpu(capi):
+    L = capi.lib
+    # empty tensors are a no-op success
+    assert L.lc_quantize_f32(None, 0, 1, 0, None, 0, None, 0, 1.0, 0.0, -128, 127, None, capi.LC_S8, None) == 0
+    # group format rejects unsupported bit widths and ragged K
+    assert L.lc_group_quantize_f32(None, 4, 64, 64, 3, None, None, None, None) == capi.LC_ERR_UNSUPPORTED
+    assert L.lc_group_quantize_f32(None, 4, 65, 64, 8, None, None, None, None) == capi.LC_ERR_INVALID_ARG
+    # the GEMM wants 16-byte row pitches
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.addressof(buf)
+    p = (p + 15) // 16 * 16
+    rc = L.lc_qlinear_i8(p, 0, 24, p, 32, 1, 1, 24, p, 0, None, None, None, None, p, capi.LC_F32, 1, None, None)
+    assert rc == capi.LC_ERR_UNSUPPORTED and "16-byte" in capi.last_error()
+    rc = L.lc_wo_linear_s8(p, 99, 1, 16, 16, p, 16, 1, None, None, p, 1, None)
+    assert rc == capi.LC_ERR_UNSUPPORTED
+
+
+def test_ops_refuse_cpu_tensors(capi):
+    import torch
+
+    from lucid_b200._C import ops
+
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        ops.quantize(torch.zeros(4), 0.1, 0.0, -128, 127, torch.int8)

@@ -1,0 +1,105 @@
+"""GPU parity of the weight-only paths: per-channel int8 GEMV-shaped Linear and the
+group-wise affine format (tolerance parity: float activations, fp32 accumulation)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from lucid_b200._C import ops
+
+    return ops
+
+
+def dev(a, dtype=None):
+    t = torch.tensor(np.ascontiguousarray(a), device="cuda")
+    return t if dtype is None else t.to(dtype)
+
+
+def host(t):
+    torch.cuda.synchronize()
+    return t.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("B", [1, 2, 4, 8, 16, 17, 32, 40])
+@pytest.mark.parametrize("N,K", [(64, 64), (100, 144), (4096, 1024), (1000, 4096), (300, 200)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_wo_linear_per_channel(ops, B, N, K, dtype):
+    r = np.random.default_rng(B * 1000 + N + K)
+    w = (r.standard_normal((N, K)) * 0.02).astype(np.float32)
+    wq, sw, _ = O.quantize_weight_per_channel(w)
+    bias = (r.standard_normal(N) * 0.01).astype(np.float32)
+    x = dev(r.standard_normal((B, K)).astype(np.float32), dtype)
+    wq_t = ops.pad_rows_to_16(dev(wq))
+    y = ops.wo_linear_s8(x, wq_t, dev(sw), dev(bias))
+    assert y.dtype == dtype and y.shape == (B, N)
+    ref = O.weight_only_linear_perchannel(host(x), wq, sw, bias)
+    # the exact product rounded to the activation type; fp32 accumulation error is far below
+    tol = {torch.bfloat16: 1e-2, torch.float16: 2e-3, torch.float32: 2e-5}[dtype]
+    np.testing.assert_allclose(host(y), ref, rtol=tol, atol=tol * np.abs(ref).max())
+
+
+def test_decode_mlp_shapes(ops):
+    """hidden 4096 <-> FFN 14336 at batch 1/4/16 with bf16 activations."""
+    torch.manual_seed(0)
+    for N, K in ((14336, 4096), (4096, 14336)):
+        w = torch.randn(N, K, device="cuda") * 0.02
+        wq, sw, _ = ops.dynamic_quantize_rows(w, True, -128, 127, True)
+        for B in (1, 4, 16):
+            x = torch.randn(B, K, device="cuda").to(torch.bfloat16)
+            y = ops.wo_linear_s8(x, wq, sw)
+            ref = (x.double() @ wq.double().T) * sw.double()[None, :]
+            assert torch.allclose(y.double(), ref, rtol=1e-2, atol=1e-2 * float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("gs", [32, 64, 128])
+def test_group_format_matches_oracle(ops, bits, gs):
+    w = np.random.default_rng(bits + gs).standard_normal((64, 256)).astype(np.float32)
+    w[3, :gs] = 0.25  # a constant group
+    p, s, b = ops.group_quantize(dev(w), gs, bits)
+    po, so, bo = O.group_quantize(w, gs, bits)
+    assert p.dtype == torch.int32 and tuple(p.shape) == (64, 256 * bits // 32)
+    np.testing.assert_array_equal(p.cpu().numpy(), po)
+    np.testing.assert_array_equal(host(s), so)
+    np.testing.assert_array_equal(host(b), bo)
+    wh = ops.group_dequantize(p, s, b, gs, bits)
+    np.testing.assert_array_equal(host(wh), O.group_dequantize(po, so, bo, gs, bits))
+    assert (np.abs(host(wh) - w) <= np.repeat(so, gs, axis=1) / 2 + 1e-5).all()
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("rows", [1, 2, 8, 32])
+def test_group_matmul_reference_cases(ops, bits, rows):
+    """lucid/test/unit/quantization/test_real_gemm.py:92-107: kernel vs own dequant
+    path, atol 1e-3, W [64,128], group 64; and the bench's 1e-4 relative gate."""
+    r = np.random.default_rng(rows)
+    w = r.standard_normal((64, 128)).astype(np.float32)
+    x = r.standard_normal((rows, 128)).astype(np.float32)
+    p, s, b = ops.group_quantize(dev(w), 64, bits)
+    y = ops.group_matmul(dev(x), p, s, b, 64, bits)
+    dense = ops.group_dequantize(p, s, b, 64, bits)
+    expected = host(dev(x) @ dense.T)
+    np.testing.assert_allclose(host(y), expected, atol=1e-3)
+    assert np.abs(host(y) - expected).max() / max(np.abs(expected).max(), 1e-12) <= 1e-4
+    ref = O.group_matmul(x, p.cpu().numpy(), host(s), host(b), 64, bits)
+    np.testing.assert_allclose(host(y), ref, rtol=1e-4, atol=1e-4)
+
+
+def test_group_matmul_bench_width(ops):
+    """tools/bench_quantized_dispatch.py:29-54: N = K = 1024, M in {1,2,8,32}, gs 64."""
+    torch.manual_seed(20260920)
+    for bits in (4, 8):
+        w = torch.randn(1024, 1024, device="cuda")
+        p, s, b = ops.group_quantize(w, 64, bits)
+        dense = ops.group_dequantize(p, s, b, 64, bits)
+        for m in (1, 2, 8, 32):
+            x = torch.randn(m, 1024, device="cuda")
+            expected = x.double() @ dense.double().T
+            actual = ops.group_matmul(x, p, s, b, 64, bits).double()
+            assert float((expected - actual).abs().max()) / max(float(expected.abs().max()), 1e-12) <= 1e-4
