@@ -1,9 +1,9 @@
 """Access to the CUDA kernel front end (``lucid_b200._C.ops``) and device helpers.
 
-The quantized path has exactly one implementation: the sm_100a kernels behind
-the C ABI.  ``ops()`` imports it on first use and raises if the shared library
-is missing.  ``_set_ops_for_testing`` lets the CPU test-suite exercise the
-host-side module logic with a stand-in; product code never calls it.
+The quantized path has exactly one implementation: the sm_100a kernels behind the
+C ABI.  ``ops()`` imports the front end on first use and raises if the shared library
+has not been built.  Callers reach these helpers as attributes of this module
+(``_backend.ops()``, ``_backend.on_cuda(t)``).
 """
 from __future__ import annotations
 
@@ -15,15 +15,10 @@ _OPS = None
 def ops():
     global _OPS
     if _OPS is None:
-        from lucid_b200._C import ops as _ops  # raises ImportError if the library is not built
+        from lucid_b200._C import ops as _ops  # ImportError if liblucid_cuda.so is missing
 
         _OPS = _ops
     return _OPS
-
-
-def _set_ops_for_testing(module) -> None:
-    global _OPS
-    _OPS = module
 
 
 def cuda_device(index: int | None = None) -> torch.device:

@@ -1,0 +1,104 @@
+"""Dynamically quantized Linear (API and buffers of
+``lucid/nn/quantized/dynamic/linear.py:36-113``).
+
+Weights are quantized once, per output row, symmetric int8.  The reference's forward
+fake-quantizes ``x`` on a per-tensor affine ``quint8`` grid, dequantizes the weight and
+runs a float GEMM; here the same quantities go through the integer form
+
+    acc[m,n] = sum_k xq[m,k] * wq[n,k]           (u8 x s8 -> s32, tcgen05)
+    y        = f32(acc - zx*rowsum(wq)[n]) * sx * sw[n] + b[n]
+
+which equals the reference's result up to fp32 summation order.  ``act_scheme``
+selects the activation grid: ``"tensor_affine"`` (reference default),
+``"tensor_symmetric"`` or ``"token_symmetric"`` (one scale per row of ``x``).
+Range, qparams and codes of the activations stay on the device: the forward contains
+no host synchronisation.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from lucid_b200 import _backend
+from lucid_b200.nn.quantized._utils import Int8WeightCache
+from lucid_b200.quantization._functional import quantize
+from lucid_b200.quantization._qscheme import QDtype, per_channel_symmetric, qint8, quint8
+
+_ACT_SCHEMES = ("tensor_affine", "tensor_symmetric", "token_symmetric")
+
+
+class Linear(nn.Module):
+    def __init__(self, in_features: int, out_features: int, bias: bool = True) -> None:
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.weight_ch_axis = 0
+        self.act_qdtype: QDtype = quint8
+        self.act_scheme = "tensor_affine"
+        self.out_dtype = torch.float32
+        self.register_buffer("weight_int8", torch.zeros((out_features, in_features), dtype=torch.int8))
+        self.register_buffer("weight_scale", torch.ones(out_features))
+        self.register_buffer("weight_zero_point", torch.zeros(out_features))
+        if bias:
+            self.register_buffer("bias", torch.zeros(out_features))
+        else:
+            self.bias = None
+        self._cache = Int8WeightCache()
+
+    def set_activation_scheme(self, scheme: str, qdtype: QDtype | None = None) -> "Linear":
+        """Choose the activation grid; symmetric schemes default to ``qint8``."""
+        if scheme not in _ACT_SCHEMES:
+            raise ValueError(f"act_scheme must be one of {_ACT_SCHEMES}, got {scheme!r}")
+        self.act_scheme = scheme
+        self.act_qdtype = qdtype if qdtype is not None else (quint8 if scheme == "tensor_affine" else qint8)
+        return self
+
+    def _quantize_activations(self, x2: torch.Tensor):
+        qd = self.act_qdtype
+        code_dtype = torch.int8 if qd.signed else torch.uint8
+        if self.act_scheme == "token_symmetric":
+            xq, sx, _ = _backend.ops().dynamic_quantize_rows(x2, True, qd.quant_min, qd.quant_max, qd.signed, 1e-8,
+                                                    code_dtype, pad_rows_to_16=True)
+            return xq, sx, None
+        symmetric = self.act_scheme == "tensor_symmetric"
+        xq, sx, zx, _ = _backend.ops().dynamic_quantize_tensor(x2, symmetric, qd.quant_min, qd.quant_max, qd.signed, 1e-8,
+                                                      code_dtype, pad_rows_to_16=True)
+        needs_zp = not (symmetric and qd.signed)
+        return xq, sx, (zx if needs_zp else None)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.weight_zero_point.is_cuda and x.is_cuda and x.device != self.weight_int8.device:
+            raise RuntimeError(f"input on {x.device} but weights on {self.weight_int8.device}")
+        xd = _backend.on_cuda(x)
+        x2 = xd.reshape(-1, self.in_features)
+        if x2.dtype != torch.float32:
+            x2 = x2.float()
+        wq, wsum = self._cache.get(_backend.on_cuda(self.weight_int8))
+        if x2.shape[0] == 0:
+            y = torch.zeros((0, self.out_features), dtype=self.out_dtype, device=xd.device)
+        else:
+            xq, sx, zx = self._quantize_activations(x2)
+            y = _backend.ops().qlinear_i8(xq, wq, sx, _backend.on_cuda(self.weight_scale),
+                                 bias=None if self.bias is None else _backend.on_cuda(self.bias), zx=zx,
+                                 wsum=wsum if zx is not None else None, out_dtype=self.out_dtype)
+        y = y.reshape(*xd.shape[:-1], self.out_features)
+        return y if x.is_cuda else y.to(x.device)
+
+    @classmethod
+    def from_float(cls, mod: nn.Module, dtype: QDtype = qint8) -> "Linear":
+        from lucid_b200.quantization.observer import PerChannelMinMaxObserver
+
+        qmod = cls(mod.in_features, mod.out_features, bias=mod.bias is not None)
+        weight = _backend.on_cuda(mod.weight.detach())
+        obs = PerChannelMinMaxObserver(ch_axis=0, qscheme=per_channel_symmetric, qdtype=dtype)
+        obs(weight)
+        scale, zero_point = obs.calculate_qparams()
+        qmod.register_buffer("weight_int8", quantize(weight, scale, zero_point, dtype, ch_axis=0))
+        qmod.register_buffer("weight_scale", scale)
+        qmod.register_buffer("weight_zero_point", zero_point)
+        if mod.bias is not None:
+            qmod.register_buffer("bias", _backend.on_cuda(mod.bias.detach()).clone())
+        return qmod
+
+    def extra_repr(self) -> str:
+        return f"in_features={self.in_features}, out_features={self.out_features}, dynamic=True"

@@ -1,0 +1,51 @@
+"""Group-wise affine weight-only primitives, the Python face of the engine boundary
+``lucid._C.engine.quantized`` (API of ``lucid/quantization/_qgemm.py:24-314``;
+engine side ``lucid/_C/ops/quantized/QuantizedMatmul.cpp:111-207``), served here by
+``lc_group_quantize_f32`` / ``lc_group_dequantize`` / ``lc_group_matmul``.
+
+Format: per (row, group of ``group_size`` input columns) ``scale = (max-min)/(2^bits-1)``
+and ``bias = min``; codes are unsigned, packed ``32/bits`` per 32-bit word (first code
+in the low bits) and carried in an ``int32`` tensor as the reference does.
+"""
+from __future__ import annotations
+
+import torch
+
+from lucid_b200 import _backend
+
+
+def is_available() -> bool:
+    try:
+        _backend.ops()
+    except ImportError:
+        return False
+    return torch.cuda.is_available()
+
+
+def quantize(w, group_size: int = 64, bits: int = 8):
+    """``(packed, scales, biases)`` of a 2-D weight ``[out, in]``."""
+    return _backend.ops().group_quantize(_backend.on_cuda(w), group_size, bits)
+
+
+def dequantize(wq, scales, biases, group_size: int = 64, bits: int = 8):
+    """Dense float32 ``[out, in]`` reconstruction ``code * scale + bias``."""
+    return _backend.ops().group_dequantize(_backend.on_cuda(wq), _backend.on_cuda(scales), _backend.on_cuda(biases), group_size, bits)
+
+
+def quantized_matmul(x, wq, scales, biases, transpose: bool = True, group_size: int = 64, bits: int = 8):
+    """``x @ w_hat.T`` (``transpose=True``, the Linear form) or ``x @ w_hat`` with the
+    weight decoded inside the kernel; float activations, result in ``x``'s dtype."""
+    xd = _backend.on_cuda(x)
+    wq, scales, biases = _backend.on_cuda(wq), _backend.on_cuda(scales), _backend.on_cuda(biases)
+    lead = xd.shape[:-1]
+    x2 = xd.reshape(-1, xd.shape[-1])
+    if not transpose:
+        dense = _backend.ops().group_dequantize(wq, scales, biases, group_size, bits).to(xd.dtype)
+        return (x2 @ dense).reshape(*lead, dense.shape[1])
+    if x2.shape[0] <= 32:
+        y = _backend.ops().group_matmul(x2, wq, scales, biases, group_size, bits)
+    else:
+        # compute-bound shapes: decode the weight once, then a dense product
+        dense = _backend.ops().group_dequantize(wq, scales, biases, group_size, bits).to(xd.dtype)
+        y = x2 @ dense.T
+    return y.reshape(*lead, wq.shape[0])

@@ -1,0 +1,190 @@
+"""Eager-mode workflows: ``prepare`` -> calibrate -> ``convert`` (static PTQ) and
+``quantize_dynamic`` (behaviour of ``lucid/quantization/_quantize.py:199-620``) for the
+Linear layers this backend accelerates.  Children are replaced with ``setattr`` so they
+keep their slot and order in the parent."""
+from __future__ import annotations
+
+import copy
+import warnings
+
+from torch import nn
+
+from lucid_b200 import backends
+from lucid_b200.quantization._propagate import (QConfigResolver, Resolved, normalize_dynamic_spec, weight_dtype)
+from lucid_b200.quantization._qscheme import QDtype, qint8
+from lucid_b200.quantization.qconfig import (get_default_qat_qconfig_mapping, get_default_qconfig_mapping)
+
+
+def _is_linear_relu(m: nn.Module) -> bool:
+    return (isinstance(m, nn.Sequential) and len(m) == 2 and isinstance(m[0], nn.Linear)
+            and isinstance(m[1], nn.ReLU) and getattr(m, "_lucid_fused", False))
+
+
+def _observed_types() -> tuple[type, ...]:
+    return (nn.Linear,)
+
+
+# ---- group-wise (engine "mlx_group") builders --------------------------------
+def _group_weight_bits(mod: nn.Module) -> int:
+    qcfg = getattr(mod, "qconfig", None)
+    if qcfg is not None:
+        bits = getattr(getattr(qcfg.weight(), "qdtype", None), "bits", None)
+        if isinstance(bits, int) and bits in (4, 8):
+            return bits
+    return 8
+
+
+def _group_size_for(in_features: int):
+    for gs in (64, 128, 32):
+        if in_features % gs == 0:
+            return gs
+    return None
+
+
+def _group_linear_builder(child: nn.Module) -> nn.Module:
+    from lucid_b200.nn.quantized import Linear as QLinear
+    from lucid_b200.nn.quantized import QuantizedLinearMLX
+
+    gs = _group_size_for(child.in_features)
+    if gs is None:  # no group size divides in_features: keep the per-channel int8 module
+        return QLinear.from_float(child)
+    return QuantizedLinearMLX.from_float(child, bits=_group_weight_bits(child), group_size=gs)
+
+
+def _group_dynamic_builder(child: nn.Module, dtype: QDtype) -> nn.Module:
+    import lucid_b200.nn.quantized.dynamic as nnqd
+    from lucid_b200.nn.quantized import QuantizedLinearMLX
+
+    gs = _group_size_for(child.in_features)
+    if gs is None:
+        return nnqd.Linear.from_float(child, dtype)
+    return QuantizedLinearMLX.from_float(child, bits=dtype.bits, group_size=gs)
+
+
+# ---- static PTQ ------------------------------------------------------------------
+def _observer_hook(obs: nn.Module):
+    def hook(_module, _args, output) -> None:
+        obs(output)
+
+    return hook
+
+
+def prepare(model: nn.Module, qconfig=None, inplace: bool = False) -> nn.Module:
+    """Attach an activation observer (as a forward hook) to every quantizable module the
+    qconfig resolution selects; returns the model ready for calibration."""
+    resolver = QConfigResolver.from_argument(qconfig, get_default_qconfig_mapping)
+    model = model if inplace else copy.deepcopy(model)
+    model.eval()
+    matched = 0
+    for entry in map(resolver.stamp, resolver.walk(model)):
+        mod, qcfg = entry.module, entry.qconfig
+        if qcfg is None or not isinstance(mod, _observed_types()):
+            continue
+        obs = qcfg.activation()
+        mod.activation_post_process = obs
+        mod.register_forward_hook(_observer_hook(obs))
+        matched += 1
+    if matched == 0:
+        warnings.warn("prepare(): the QConfigMapping matched no quantizable modules — convert() will "
+                      "leave this model unchanged.", stacklevel=2)
+    return model
+
+
+def convert(model: nn.Module, inplace: bool = False) -> nn.Module:
+    """Swap every calibrated module for its quantized counterpart and drop the
+    ``qconfig`` stamps."""
+    from lucid_b200.nn.quantized import Linear as QLinear
+
+    model = model if inplace else copy.deepcopy(model)
+    build = _group_linear_builder if backends.quantized.use_mlx() else QLinear.from_float
+    _convert_children(model, {nn.Linear: build})
+    QConfigResolver.strip(model)
+    model.eval()
+    return model
+
+
+def _convert_children(module: nn.Module, mapping) -> None:
+    for name, child in list(module.named_children()):
+        build = mapping.get(type(child))
+        if build is not None and hasattr(child, "activation_post_process"):
+            child._forward_hooks.clear()
+            setattr(module, name, build(child))
+        else:
+            _convert_children(child, mapping)
+
+
+# ---- dynamic PTQ -------------------------------------------------------------------
+def _dynamic_builders():
+    import lucid_b200.nn.quantized.dynamic as nnqd
+
+    builders = {nn.Linear: nnqd.Linear.from_float}
+    if backends.quantized.use_mlx():
+        builders[nn.Linear] = _group_dynamic_builder
+    return builders
+
+
+def quantize_dynamic(model: nn.Module, qconfig_spec=None, dtype: QDtype = qint8, inplace: bool = False):
+    """Replace the targeted float layers by dynamically quantized ones; no calibration.
+
+    ``qconfig_spec``: ``None`` (every supported type), a set of module types / dotted names,
+    or a dict mapping those to a ``QConfig``, a ``QDtype`` or ``None`` (skip)."""
+    model = model if inplace else copy.deepcopy(model)
+    model.eval()
+    builders = _dynamic_builders()
+    spec = normalize_dynamic_spec(qconfig_spec, dtype, tuple(builders))
+    return _DynamicSwapper(spec, builders, dtype).apply(model)
+
+
+class _DynamicSwapper:
+    def __init__(self, spec, builders, dtype: QDtype) -> None:
+        self.resolver = QConfigResolver(spec.mapping)
+        self._targets = spec.targets
+        self._builders = builders
+        self._dtype = dtype
+        self._swapped = 0
+        self._no_dynamic_form: set[type] = set()
+
+    def apply(self, model: nn.Module) -> nn.Module:
+        root = self.resolver.root(model)
+        if root.qconfig is not None and type(model) in self._builders:
+            out = self._build(model, root.qconfig)  # the model itself is a bare layer
+        else:
+            self._descend(root)
+            self._report()
+            out = model
+        QConfigResolver.strip(out)
+        return out
+
+    def _build(self, module: nn.Module, qconfig) -> nn.Module:
+        self._swapped += 1
+        return self._builders[type(module)](module, weight_dtype(qconfig, self._dtype))
+
+    def _descend(self, parent: Resolved) -> None:
+        for entry in self.resolver.children(parent.module, parent.path, parent.qconfig):
+            if entry.qconfig is not None and type(entry.module) in self._builders:
+                setattr(parent.module, entry.name, self._build(entry.module, entry.qconfig))
+                continue
+            is_leaf = next(entry.module.children(), None) is None
+            if entry.qconfig is not None and is_leaf and self.resolver.is_targeted(entry.module, entry.path):
+                self._no_dynamic_form.add(type(entry.module))
+            self._descend(entry)
+
+    def _report(self) -> None:
+        if self._no_dynamic_form:
+            left = ", ".join(sorted(t.__name__ for t in self._no_dynamic_form))
+            have = ", ".join(sorted(t.__name__ for t in self._builders))
+            warnings.warn(f"quantize_dynamic(): {left} has no dynamically quantized form and stays float; "
+                          f"dynamic quantization covers {have}.", stacklevel=4)
+        elif self._swapped == 0:
+            warnings.warn("quantize_dynamic(): no module of a targeted type "
+                          f"({', '.join(self._targets) or 'none'}) found — the model is returned unchanged.",
+                          stacklevel=4)
+
+
+# ---- training-time entry points: outside this backend's scope -------------------------
+def prepare_qat(model: nn.Module, qconfig=None, inplace: bool = False):
+    """Quantization-aware training swaps float layers for ``nn.qat`` layers, which are
+    training-time float composites and not part of the inference path built here."""
+    raise NotImplementedError(
+        "prepare_qat is not provided by the CUDA inference backend: QAT layers are training-time float "
+        "composites (use FakeQuantize modules directly, or train with the reference and convert here)")
