@@ -1,0 +1,475 @@
+"""Benchmark of the int8 quantized-inference path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras] [--profile-case NAME]
+
+Headline workload ("prefill"): the prefill-shaped dynamic int8 Linear, x fp32 [16384, 8192]
+~N(0,1) quantized per token, W [28672, 8192] ~N(0,0.02) quantized per output channel, int32
+accumulation, fp32 dequantized output; over N GPUs the weight is sharded by output
+columns and the output shards are all-gathered with NCCL.  One step = quantize
+activations + GEMM (+ all-gather).  metric: int8 qLinear TOPS = 2*M*N*K / step time,
+whole job.  At N = 1 the line also carries the HBM-bound companions of the metric (the
+[8192, 8192] quantize / dequantize roundtrip and the decode-shaped weight-only MLP) under
+"extras", the roofline of the dominant kernel and a CPU baseline timed on this host.
+
+Inputs are seeded synthetic tensors of the configured shapes and distributions.
+Timing: CUDA events on the launching stream after >= 3 warm-up steps, barrier +
+synchronize on both sides, max over ranks; inputs are larger than L2 (126 MB).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M_PREFILL, N_PREFILL, K_PREFILL = 16384, 28672, 8192
+NOMINAL_INT8_TOPS = 4500.0   # dense int8, datasheet
+NOMINAL_HBM_GBS = 8000.0
+
+
+# ----------------------------------------------------------------------------------------
+# measured peaks and clocks
+# ----------------------------------------------------------------------------------------
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a timed region runs."""
+
+    BAD = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+           "hw_power_brake_slowdown": 0x80}
+    NOTED = {"sw_power_cap": 0x4}
+
+    def __init__(self, index: int) -> None:
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _run(self) -> None:
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                for name, bit in {**self.BAD, **self.NOTED}.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------------------
+# CPU reference arm (the reference's own formulation, restated in oracle/, on host cores)
+# ----------------------------------------------------------------------------------------
+def cpu_prefill_reference(steps: int, warmup: int, sample_rows: int = 512) -> dict:
+    """Times the reference's dynamic Linear forward (fake-quantize x per row, dequantize the
+    whole weight, fp32 GEMM) on `sample_rows` rows of the prefill workload against the full
+    [28672, 8192] weight, with all host threads NumPy's BLAS takes."""
+    import numpy as np
+
+    from oracle import oracle as O
+
+    rng = np.random.default_rng(20260925)
+    x = rng.standard_normal((sample_rows, K_PREFILL), dtype=np.float32)
+    w = rng.standard_normal((N_PREFILL, K_PREFILL), dtype=np.float32)
+    w *= np.float32(0.02)
+    wq, sw, zw = O.quantize_weight_per_channel(w)
+    del w
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        y = O.dynamic_linear_float(x, wq, sw, zw, None, "token_symmetric", O.qint8)
+        float(y[0, 0])
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    ops = 2.0 * sample_rows * N_PREFILL * K_PREFILL
+    return {"value": ops / t / 1e12, "unit": "TOPS", "cores": len(os.sched_getaffinity(0)), "kind": "port",
+            "sample": f"{sample_rows} of {M_PREFILL} rows of x against the full W [{N_PREFILL},{K_PREFILL}], "
+                      f"reference float formulation (per-forward weight dequantize + sgemm), median of {steps}",
+            "seconds_per_sample": t}
+
+
+def run_reference_arm(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    steps = max(1, min(args.steps, 3))
+    warmup = max(1, min(args.warmup, 1))
+    base = cpu_prefill_reference(steps, warmup)
+    line = {
+        "impl": "reference", "metric": "int8_qlinear_tops", "value": base["value"], "unit": "TOPS",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": base["seconds_per_sample"] * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "prefill_qlinear_16384x28672x8192_per_token_int8",
+                   "note": "reference engine is Apple-only; its Python-level CPU formulation restated in "
+                           "oracle/ is timed on a bounded row sample"},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ----------------------------------------------------------------------------------------
+# GPU side
+# ----------------------------------------------------------------------------------------
+def _events(torch):
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def time_loop(torch, fn, steps: int, warmup: int) -> float:
+    """Average milliseconds per call, CUDA events on the current stream."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = _events(torch)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def extras_single_gpu(torch, ops, peaks) -> dict:
+    """HBM-bound companions of the metric, measured on one GPU after the headline run."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = {}
+    hbm = peaks["hbm_gbs"]
+    g = torch.Generator(device=dev).manual_seed(20260922)
+    # ---- standalone roundtrip: fp32 [8192, 8192] ~N(0,1), 0.1 % outliers x50 (268 MB > L2)
+    x = torch.randn(8192, 8192, device=dev, generator=g)
+    idx = torch.randint(0, x.numel(), (x.numel() // 1000,), device=dev, generator=g)
+    x.view(-1)[idx] *= 50.0
+    q, s, z = ops.dynamic_quantize_rows(x, True, -128, 127, True)
+    cases = {
+        "quantize_per_channel_fused": (lambda: ops.dynamic_quantize_rows(x, True, -128, 127, True),
+                                       x.numel() * 5 + 8192 * 4),
+        "quantize_per_tensor_fused": (lambda: ops.dynamic_quantize_tensor(x, True, -128, 127, True, 1e-8, torch.int8),
+                                      x.numel() * 9),
+        "dequantize_per_channel": (lambda: ops.dequantize(q, s, z, ch_axis=0), x.numel() * 5),
+        "quantize_per_channel_given_scale": (lambda: ops.quantize(x, s, z, -128, 127, torch.int8, ch_axis=0),
+                                             x.numel() * 5),
+    }
+    rt = {}
+    for name, (fn, nbytes) in cases.items():
+        ms = time_loop(torch, fn, 30, 5)
+        gbs = nbytes / ms / 1e6
+        rt[name] = {"ms": ms, "GB/s": gbs, "algorithmic_bytes": nbytes, "frac_of_measured_hbm": gbs / hbm,
+                    "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS}
+    out["roundtrip_8192x8192"] = rt
+    del x, q, s, z
+    # ---- decode-shaped weight-only SwiGLU MLP: hidden 4096, FFN 14336, bf16 activations
+    H, F = 4096, 14336
+    sets = []
+    for i in range(3):  # 3 x 176 MB of weights rotate so that no step finds its weights in L2
+        ws = []
+        for (n, k) in ((F, H), (F, H), (H, F)):
+            w = torch.randn(n, k, device=dev, generator=g) * 0.02
+            wq, sw, _ = ops.dynamic_quantize_rows(w, True, -128, 127, True)
+            ws.append((wq, sw))
+            del w
+        sets.append(ws)
+    dec = {}
+    for batch in (1, 4, 16):
+        xb = torch.randn(batch, H, device=dev, generator=g).to(torch.bfloat16)
+        counter = [0]
+
+        def mlp_step():
+            (wg, sg), (wu, su), (wd, sd) = sets[counter[0] % 3]
+            counter[0] += 1
+            gate = ops.wo_linear_s8(xb, wg, sg)
+            up = ops.wo_linear_s8(xb, wu, su)
+            h = torch.nn.functional.silu(gate) * up
+            return ops.wo_linear_s8(h, wd, sd)
+
+        ms = time_loop(torch, mlp_step, 60, 6)
+        nbytes = 3 * H * F + (2 * F + H) * 4
+        dec[f"batch_{batch}"] = {"us": ms * 1e3, "GB/s": nbytes / ms / 1e6, "algorithmic_bytes": nbytes,
+                                 "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}
+    out["decode_mlp_4096x14336_w8a16"] = dec
+    del sets
+    # ---- the single dynamic Linear (x [64,1024], W [4096,1024]) through the module API
+    try:
+        import lucid_b200.quantization as Q
+
+        lin = torch.nn.Linear(1024, 4096).to(dev)
+        with torch.no_grad():
+            lin.weight.normal_(0, 0.02, generator=g)
+            lin.bias.normal_(0, 0.01, generator=g)
+        qlin = Q.quantize_dynamic(lin)
+        x1 = torch.randn(64, 1024, device=dev, generator=g)
+        ms = time_loop(torch, lambda: qlin(x1), 200, 20)
+        out["single_dynamic_linear_64x4096x1024"] = {"us_per_forward": ms * 1e3,
+                                                     "TOPS": 2 * 64 * 4096 * 1024 / ms / 1e9}
+    except Exception as e:  # reported, never hidden
+        out["single_dynamic_linear_64x4096x1024"] = {"error": repr(e)[:200]}
+    return out
+
+
+def run_profile_case(args) -> int:
+    """A small, fixed case of one kernel (inputs larger than L2, a few hundred MB on the
+    device) run a handful of times: the target of `ncu --set full` captures."""
+    import torch
+
+    from lucid_b200._C import ops
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(1)
+    case = args.profile_case
+    if case == "gemm":
+        M, N, K = 4096, 7168, 8192
+        a = torch.randint(-128, 128, (M, K), device=dev, dtype=torch.int8, generator=g)
+        b = torch.randint(-128, 128, (N, K), device=dev, dtype=torch.int8, generator=g)
+        sx, sw = torch.rand(M, device=dev), torch.rand(N, device=dev)
+        fn = lambda: ops.qlinear_i8(a, b, sx, sw)  # noqa: E731
+    elif case in ("quantize_rows", "quantize_tensor", "dequantize", "quantize_given_scale"):
+        x = torch.randn(8192, 8192, device=dev, generator=g)
+        q, s, z = ops.dynamic_quantize_rows(x, True, -128, 127, True)
+        fn = {"quantize_rows": lambda: ops.dynamic_quantize_rows(x, True, -128, 127, True),
+              "quantize_tensor": lambda: ops.dynamic_quantize_tensor(x, True, -128, 127, True, 1e-8, torch.int8),
+              "dequantize": lambda: ops.dequantize(q, s, z, ch_axis=0),
+              "quantize_given_scale": lambda: ops.quantize(x, s, z, -128, 127, torch.int8, ch_axis=0)}[case]
+    elif case == "wo_gemv":
+        ws = []
+        for _ in range(4):
+            w = torch.randn(14336, 4096, device=dev, generator=g) * 0.02
+            wq, sw, _ = ops.dynamic_quantize_rows(w, True, -128, 127, True)
+            ws.append((wq, sw))
+        xb = torch.randn(int(args.profile_batch), 4096, device=dev, generator=g).to(torch.bfloat16)
+        i = [0]
+
+        def fn():
+            wq, sw = ws[i[0] % 4]
+            i[0] += 1
+            return ops.wo_linear_s8(xb, wq, sw)
+    else:
+        raise SystemExit(f"unknown profile case {case!r}")
+    for _ in range(6):
+        fn()
+    torch.cuda.synchronize()
+    print(f"profile case {case}: ok")
+    return 0
+
+
+def run_ours(args) -> int:
+    import torch
+    import torch.distributed as dist
+
+    from lucid_b200._C import ops  # fails loudly if liblucid_cuda.so is missing
+    import lucid_b200.quantization as Q
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference "
+                         "for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = measured_peaks()
+    M, N, K = M_PREFILL, N_PREFILL, K_PREFILL
+    if N % world:
+        raise SystemExit(f"N={N} does not split over {world} ranks")
+    n_local = N // world
+
+    # seeded synthetic data: x replicated on every rank, W rows [rank*n_local, (rank+1)*n_local)
+    gx = torch.Generator(device=dev).manual_seed(20260925)
+    x = torch.randn(M, K, device=dev, generator=gx)
+    gw = torch.Generator(device=dev).manual_seed(20260926 + rank)
+    lin = torch.nn.Linear(K, n_local, bias=False, device=dev)
+    with torch.no_grad():
+        lin.weight.normal_(0.0, 0.02, generator=gw)
+    qlin = Q.quantize_dynamic(lin, inplace=True).set_activation_scheme("token_symmetric")
+    del lin
+    torch.cuda.empty_cache()
+    wq, _ = qlin._cache.get(qlin.weight_int8)
+    sw = qlin.weight_scale
+    gathered = torch.empty((world, M, n_local), dtype=torch.float32, device=dev) if world > 1 else None
+
+    gemm_ms = []
+
+    def step(record: bool = False):
+        xq, sx, _ = ops.dynamic_quantize_rows(x, True, -128, 127, True, 1e-8, torch.int8, pad_rows_to_16=True)
+        if record:
+            a, b = _events(torch)
+            a.record()
+        y = ops.qlinear_i8(xq, wq, sx, sw)
+        if record:
+            b.record()
+            gemm_ms.append((a, b))
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), y.view(-1))
+        return y
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sync_all()
+    e0, e1 = _events(torch)
+    with ClockSampler(local) as clocks:
+        sync_all()
+        e0.record()
+        for _ in range(args.steps):
+            step(record=True)
+        e1.record()
+        sync_all()
+    total_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(total_ms.item()) / args.steps
+    gemm_avg_ms = sum(a.elapsed_time(b) for a, b in gemm_ms) / len(gemm_ms)
+    value = 2.0 * M * N * K / ms_per_step / 1e9
+
+    # ---- end to end through the module API with host buffers --------------------------
+    x_host = x.cpu().pin_memory()
+    y_host = torch.empty((M, N), dtype=torch.float32).pin_memory() if rank == 0 else None
+    x_dev = torch.empty_like(x)
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        y = qlin(x_dev)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), y.contiguous().view(-1))
+            if rank == 0:
+                y_host.view(M, world, n_local).copy_(gathered.permute(1, 0, 2), non_blocking=True)
+        elif rank == 0:
+            y_host.copy_(y, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    sync_all()
+    f0, f1 = _events(torch)
+    f0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    f1.record()
+    sync_all()
+    e2e_ms = torch.tensor([f0.elapsed_time(f1)], device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_ms_per_step = float(e2e_ms.item()) / e2e_steps
+
+    if rank == 0:
+        int8_peak = 2.0 * peaks["bf16_tflops"]
+        achieved = 2.0 * M * n_local * K / gemm_avg_ms / 1e9
+        line = {
+            "metric": "int8_qlinear_tops", "value": value, "unit": "TOPS", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "s8xs8->s32",
+            "data": "synthetic",
+            "config": {"workload": "prefill_qlinear_16384x28672x8192_per_token_int8", "M": M, "N": N, "K": K,
+                       "activation_quant": "dynamic per-token symmetric int8 (absmax/127.5, [-128,127])",
+                       "weight_quant": "per-output-channel symmetric int8", "output": "fp32",
+                       "parallelism": f"column-parallel x{world}" + (" + NCCL all-gather" if world > 1 else ""),
+                       "l2": "inputs exceed L2 (x 537 MB, W 235 MB, y 1879 MB vs 126 MB)"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
+                         "frac": achieved / int8_peak, "traffic": None,
+                         "kernel": "qlinear_i8_kernel", "kernel_ms": gemm_avg_ms,
+                         "peak_source": f"2 x bf16_tflops ({peaks['source']}, burst): tcgen05 issues dense int8 at "
+                                        "twice the bf16 rate; no int8 figure is measured by the driver",
+                         "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS},
+            "e2e": {"value": 2.0 * M * N * K / e2e_ms_per_step / 1e9, "unit": "TOPS",
+                    "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4,
+                    "ms_per_step": e2e_ms_per_step, "api": "lucid_b200.nn.quantized.dynamic.Linear.forward"},
+            "gpu_launches": args.steps * 2,
+            "clocks": clocks.summary(),
+        }
+        if world == 1:
+            del x_host, y_host, x_dev
+            torch.cuda.empty_cache()
+        if world == 1 and not args.no_extras:
+            try:  # library comparator (cuBLASLt through torch), for context only
+                a8 = wq[:8192]
+                t = time_loop(torch, lambda: torch._int_mm(a8, a8.t()), 5, 2)
+                line["library_int8_gemm_tops_8192x8192x8192"] = 2 * 8192.0 ** 3 / t / 1e9
+            except Exception as e:
+                line["library_int8_gemm_tops_8192x8192x8192"] = f"unavailable: {repr(e)[:80]}"
+            line["extras"] = extras_single_gpu(torch, ops, peaks)
+            line["cpu_baseline"] = {k: v for k, v in cpu_prefill_reference(3, 1).items() if k != "seconds_per_sample"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="headline workload only: skip the companion workloads and the CPU baseline")
+    ap.add_argument("--profile-case", default=None,
+                    help="run a small fixed case of one kernel (gemm, quantize_rows, quantize_tensor, "
+                         "dequantize, quantize_given_scale, wo_gemv) for a profiler capture; prints no bench line")
+    ap.add_argument("--profile-batch", default=4)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    if args.profile_case:
+        return run_profile_case(args)
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29531", os.path.abspath(__file__),
+               "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup)]
+        return subprocess.call(cmd)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

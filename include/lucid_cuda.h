@@ -179,6 +179,12 @@ int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K
                         const int8_t* wq, int64_t ldw, int64_t N, const float* sw,
                         const float* bias, void* y, int64_t ldy, void* stream);
 
+/* Synchronises the device and reads the status word of the weight-only kernels on the
+ * current device: 0, or the code of a bounded device-side wait that ran out (the
+ * affected outputs are invalid).  clear != 0 resets it.  No counterpart in the
+ * reference, whose engine reports errors as exceptions (QuantizedMatmul.cpp:42-45). */
+int32_t lc_wo_linear_status(int32_t* host_code, int32_t clear);
+
 /* ---- group-wise affine weight-only format ------------------------------
  * engine.quantized.{quantize,dequantize,quantized_matmul}
  * (lucid/_C/ops/quantized/QuantizedMatmul.cpp:111-121, 123-141, 143-207):

@@ -11,7 +11,7 @@ import math
 
 import torch
 
-from . import (LC_BF16, LC_F16, LC_F32, LC_S8, LC_S16, LC_S32, LC_U8, LucidCudaError, check, lib)
+from ._loader import (LC_BF16, LC_F16, LC_F32, LC_S8, LC_S16, LC_S32, LC_U8, LucidCudaError, check, lib)
 
 _DTYPE = {
     torch.float32: LC_F32,

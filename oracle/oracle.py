@@ -238,6 +238,19 @@ def dynamic_linear_reference(x, wq, sw, zw, bias, act_qdtype: QDtype = quint8):
     return linear_f32(xq, w, bias)
 
 
+def dynamic_linear_float(x, wq, sw, zw, bias, mode: str = "tensor_affine", act_qdtype: QDtype = quint8):
+    """The reference's float formulation with a selectable activation grid: the op
+    sequence of ``dynamic/linear.py:85-92`` (fake-quantize ``x``, dequantize the whole
+    weight, fp32 GEMM + bias) with per-tensor or per-row (per-token) activation qparams.
+    This is what the CPU baseline times."""
+    x2 = _f32(x).reshape(-1, np.shape(x)[-1])
+    sx, zx = dynamic_act_qparams(x2, mode, act_qdtype)
+    ch = 0 if mode == "token_symmetric" else None
+    xq, _ = fake_quantize(x2, sx, zx, act_qdtype.quant_min, act_qdtype.quant_max, ch_axis=ch)
+    w = dequantize(wq, sw, zw, ch_axis=0)
+    return linear_f32(xq, w, bias)
+
+
 def dynamic_act_qparams(x, mode: str, qdtype: QDtype):
     """Activation qparams for the integer formulation.
 

@@ -255,8 +255,9 @@ def test_prepare_convert_static(device):
     prepared = Q.prepare(model)
     assert hasattr(prepared[0], "activation_post_process") and isinstance(prepared[0].qconfig, Q.QConfig)
     x = torch.randn(64, 32)
+    prepared = prepared.to(device)
     for _ in range(2):
-        prepared(x.to(device) if device == "cuda" else x)
+        prepared(x.to(device))
     qm = Q.convert(prepared)
     assert isinstance(qm[0], nnq.Linear) and isinstance(qm[2], nnq.Linear)
     assert not any(hasattr(m, "qconfig") for m in qm.modules())
