@@ -69,6 +69,29 @@ int32_t lc_observe_tensor_f32(const float* x, int64_t n, float* min_out, float* 
                               float* scale_out, float* zp_out, void* workspace,
                               int64_t workspace_bytes, void* stream);
 
+/* lc_observe_tensor_f32 for callers that cannot give it scratch memory.
+ * (This entry point has no counterpart in the reference.)
+ * Some hosts of this library cannot allocate device memory at the point where they need
+ * a global min/max: a serving process whose allocator took the whole GPU at start-up and
+ * hands nothing to plug-ins, a binding written in a language runtime that has no CUDA
+ * allocator of its own, or code that is already inside a region where cudaMalloc is not
+ * allowed.  For them the kernel's scratch (a ticket and one partial min/max per CTA, about
+ * 9.3 KB) is a static array inside the library; every GPU that loads the library holds it
+ * until the process exits.  Nothing is allocated or freed by this call, the caller still
+ * passes the input and the outputs, and results are identical to lc_observe_tensor_f32.
+ * Limits and rules:
+ *  - at most lc_observe_tensor_static_max_elems() (2^30) elements per call; larger inputs
+ *    are rejected with LC_ERR_UNSUPPORTED -- use the workspace variant for those;
+ *  - the first call on each device looks up the array's device address (with that device
+ *    current); make that first call before starting any stream capture;
+ *  - all calls on a device share the one array: two calls whose kernels can overlap on the
+ *    GPU (different streams, no dependency) race on it.  Serialise them. */
+int64_t lc_observe_tensor_static_max_elems(void);
+int32_t lc_observe_tensor_static_f32(const float* x, int64_t n, float* min_out, float* max_out,
+                                     int32_t accumulate, int32_t symmetric, int32_t quant_min,
+                                     int32_t quant_max, int32_t is_signed, float eps,
+                                     float* scale_out, float* zp_out, void* stream);
+
 /* PerChannelMinMaxObserver.forward: per-channel min and max over every other
  * axis (lucid/quantization/observer.py:672-686). */
 int32_t lc_observe_channel_f32(const float* x, int64_t outer, int64_t channels, int64_t inner,

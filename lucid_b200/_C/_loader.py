@@ -45,6 +45,8 @@ SIGNATURES = {
     "lc_device_info": (_i32, [_i32, C.POINTER(_i32), C.POINTER(_i32)]),
     "lc_observe_tensor_workspace_bytes": (_i64, []),
     "lc_observe_tensor_f32": (_i32, [_p, _i64, _p, _p, _i32, _i32, _i32, _i32, _i32, _f, _p, _p, _p, _i64, _p]),
+    "lc_observe_tensor_static_max_elems": (_i64, []),
+    "lc_observe_tensor_static_f32": (_i32, [_p, _i64, _p, _p, _i32, _i32, _i32, _i32, _i32, _f, _p, _p, _p]),
     "lc_observe_channel_f32": (_i32, [_p, _i64, _i64, _i64, _p, _p, _i32, _p]),
     "lc_calculate_qparams_f32": (_i32, [_p, _p, _i64, _i32, _i32, _i32, _i32, _f, _p, _p, _p]),
     "lc_quantize_f32": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _p, _i64, _f, _f, _i32, _i32, _p, _i32, _p]),

@@ -7,6 +7,8 @@
 // one segment, reads it with 128-bit loads, and takes its scale / zero-point
 // once per CTA.  When `inner` is short ("strided mode", e.g. ch_axis = last)
 // threads walk the flat tensor and derive the channel per element.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace lc {
@@ -679,6 +681,66 @@ extern "C" int32_t lc_observe_tensor_f32(const float* x, int64_t n, float* min_o
   QParamSpec spec = make_qparam_spec(symmetric, quant_min, quant_max, is_signed, eps);
   return launch_observe_tensor(x, n, min_out, max_out, accumulate, scale_out != nullptr, spec,
                                scale_out, zp_out, workspace, workspace_bytes, as_stream(stream));
+}
+
+// ---- observe_tensor without caller scratch -------------------------------------------
+// The scratch of the global-range kernel (ticket + per-CTA partials) lives in this
+// file-scope device array instead of a caller buffer.  Every GPU that loads the library
+// holds these sizeof(TensorObserveScratch) bytes (about 9.3 KB) until the process exits.
+// In host code the array's name is only a handle for cudaGetSymbolAddress; the device
+// address is looked up once per device and cached.
+static __device__ __align__(256) unsigned char g_observe_static_scratch[sizeof(TensorObserveScratch)];
+
+constexpr int64_t kObserveStaticMaxElems = int64_t{1} << 30;
+
+static int32_t static_scratch_address(TensorObserveScratch** out) {
+  constexpr int kMaxDevices = 64;
+  static std::once_flag flags[kMaxDevices];
+  static cudaError_t results[kMaxDevices];
+  static void* addrs[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(LC_ERR_CUDA, "observe_tensor_static: no current CUDA device");
+  std::call_once(flags[dev], [dev]() {
+    void* p = nullptr;
+    results[dev] = cudaGetSymbolAddress(&p, g_observe_static_scratch);
+    addrs[dev] = p;
+  });
+  if (results[dev] != cudaSuccess || addrs[dev] == nullptr)
+    return fail(LC_ERR_CUDA, "observe_tensor_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+                cudaGetErrorString(results[dev]));
+  *out = static_cast<TensorObserveScratch*>(addrs[dev]);
+  return LC_OK;
+}
+
+extern "C" int64_t lc_observe_tensor_static_max_elems(void) { return kObserveStaticMaxElems; }
+
+extern "C" int32_t lc_observe_tensor_static_f32(const float* x, int64_t n, float* min_out,
+                                                float* max_out, int32_t accumulate,
+                                                int32_t symmetric, int32_t quant_min,
+                                                int32_t quant_max, int32_t is_signed, float eps,
+                                                float* scale_out, float* zp_out, void* stream) {
+  if (!x || !min_out || !max_out)
+    return fail(LC_ERR_INVALID_ARG, "observe_tensor_static: null pointer");
+  if ((scale_out == nullptr) != (zp_out == nullptr))
+    return fail(LC_ERR_INVALID_ARG, "observe_tensor_static: scale_out and zp_out go together");
+  if (n <= 0) return fail(LC_ERR_INVALID_ARG, "observe_tensor_static: empty input has no min/max");
+  if (n > kObserveStaticMaxElems)
+    return fail(LC_ERR_UNSUPPORTED,
+                "observe_tensor_static: %lld elements exceed the limit of %lld of the built-in scratch; "
+                "use lc_observe_tensor_f32 with a caller workspace",
+                (long long)n, (long long)kObserveStaticMaxElems);
+  TensorObserveScratch* ws = nullptr;
+  if (int32_t rc = static_scratch_address(&ws)) return rc;
+  cudaStream_t st = as_stream(stream);
+  // the array keeps whatever the previous call left: the ticket has to start at zero
+  if (cudaMemsetAsync(ws, 0, 16, st) != cudaSuccess)
+    return fail(LC_ERR_CUDA, "observe_tensor_static: %s", cudaGetErrorString(cudaGetLastError()));
+  QParamSpec spec = make_qparam_spec(symmetric, quant_min, quant_max, is_signed, eps);
+  observe_tensor_kernel<<<observe_grid(n), kThreads, 0, st>>>(x, n, aligned(x, 16) ? 1 : 0, min_out,
+                                                              max_out, accumulate, scale_out != nullptr,
+                                                              spec, scale_out, zp_out, ws);
+  return check_launch("observe_tensor_static");
 }
 
 extern "C" int32_t lc_observe_channel_f32(const float* x, int64_t outer, int64_t channels,
