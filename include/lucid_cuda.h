@@ -187,6 +187,16 @@ int32_t lc_qlinear_i8(const void* a, int32_t a_unsigned, int64_t lda, const int8
                       const float* sw, const float* bias, void* out, int32_t out_dtype,
                       int64_t ldo, int32_t* status, void* stream);
 
+/* lc_qlinear_i8 with an explicit kernel choice: variant 0 = automatic (what lc_qlinear_i8
+ * does), 1 = single-CTA tiles (128 x 256), 2 = CTA-pair tiles (tcgen05 cta_group::2,
+ * 256 x 256 per 2-CTA cluster).  Results are identical; the variants exist for testing and
+ * tuning.  Same reference counterpart as lc_qlinear_i8. */
+int32_t lc_qlinear_i8_ex(const void* a, int32_t a_unsigned, int64_t lda, const int8_t* b,
+                         int64_t ldb, int64_t M, int64_t N, int64_t K, const float* sx,
+                         int32_t sx_per_row, const float* zx, const int32_t* wsum,
+                         const float* sw, const float* bias, void* out, int32_t out_dtype,
+                         int64_t ldo, int32_t* status, int32_t variant, void* stream);
+
 /* row sums of an int8 matrix as int32 (the zero-point correction term) */
 int32_t lc_rowsum_s8(const int8_t* b, int64_t rows, int64_t cols, int64_t ldb, int32_t* out,
                      void* stream);

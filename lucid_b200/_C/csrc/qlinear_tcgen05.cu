@@ -38,7 +38,7 @@ constexpr int EPI_THREADS = 128;
 constexpr int GROUP_M = 16;      // tile rasterisation: bands of 16 M-tiles share B in L2
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
-constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
+constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 2 GHz
 
 enum : int { ST_PRODUCER = 1, ST_MMA = 2, ST_EPILOGUE = 3 };
 
@@ -445,6 +445,284 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
+// =============================================================================================
+// CTA-pair variant: tcgen05.mma.cta_group::2, one 256 x 256 output tile per 2-CTA cluster.
+// CTA r of the pair owns rows [128r, 128r+128) of the tile (its TMEM holds that half of the
+// accumulator) and loads its own A rows plus HALF of B (rows [128r, 128r+128) of the N tile);
+// the pair's tensor cores read both halves of B.  Compared with the single-CTA kernel each
+// CTA moves 32 KB instead of 48 KB through L2 and shared memory per 128 bytes of K, which is
+// what that kernel is bound by.  No multicast loads: every TMA load is a plain per-CTA load
+// whose completion is signalled on the leader CTA's mbarrier.
+//   leader (rank 0): arms full[stage] with the bytes of both CTAs, issues the MMAs, and
+//   commits with a 2-CTA multicast arrive so both CTAs' empty[stage] / acc_full[] flip;
+//   both CTAs' epilogue warps release the accumulator on the leader's acc_empty[].
+// =============================================================================================
+namespace pair {
+constexpr int BNH = BN / 2;                 // rows of B each CTA loads
+constexpr int STAGES2 = 6;
+constexpr int A_BYTES2 = BM * BK;           // 16 KB
+constexpr int B_BYTES2 = BNH * BK;          // 16 KB
+constexpr int STAGE_BYTES2 = A_BYTES2 + B_BYTES2;
+constexpr int SMEM_BYTES2 = STAGES2 * STAGE_BYTES2 + 1024 + 256;
+}  // namespace pair
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// plain (non-multicast) TMA load whose completion is signalled on a barrier that may live in
+// the peer CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(cluster_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on the barrier at this offset in both CTAs of the pair once the MMAs issued so far retire
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .b16 m;\n\tmov.b16 m, 3;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}" ::"r"(bar)
+      : "memory");
+}
+__host__ __device__ constexpr uint32_t make_idesc_pair(bool a_unsigned) {
+  return (2u << 4) | ((a_unsigned ? 0u : 1u) << 7) | (1u << 10) |
+         (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>((2 * BM) >> 4) << 24);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                       const __grid_constant__ CUtensorMap tmap_b, const Params p, const uint32_t idesc) {
+  using namespace pair;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ float s_sw[BN];
+  __shared__ float s_bias[BN];
+  __shared__ int s_corr[BN];
+  __shared__ uint32_t s_tmem_base;
+
+  const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = tiles_base + STAGES2 * STAGE_BYTES2;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES2 + s); };
+  auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * STAGES2 + s); };
+  auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES2 + ACC_STAGES + s); };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int64_t pair_id = blockIdx.x >> 1;
+  const int64_t num_pairs = gridDim.x >> 1;
+
+  const int64_t tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int64_t tiles_n = (p.N + BN - 1) / BN;
+  const int64_t num_tiles = tiles_m * tiles_n;
+  const int num_kb = static_cast<int>((p.K + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < ACC_STAGES; ++s) {
+      mbar_init(acc_full_bar(s), 1);
+      mbar_init(acc_empty_bar(s), 2 * (EPI_THREADS / 32));  // epilogue warps of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&s_tmem_base)),
+                 "r"(static_cast<uint32_t>(TMEM_COLS))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 0) {
+    // ===================== TMA producer (both CTAs) =====================
+    if (lane == 0) {
+      uint32_t armed_parity[STAGES2];
+      bool armed[STAGES2];
+      for (int s = 0; s < STAGES2; ++s) armed[s] = false;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
+        int64_t tm, tn;
+        tile_coords(t, tiles_m, tiles_n, tm, tn);
+        const int m0 = static_cast<int>(tm * 2 * BM + rank * BM);
+        const int n0 = static_cast<int>(tn * BN + rank * BNH);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+            report(p.status, ST_PRODUCER);
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = tiles_base + stage * STAGE_BYTES2;
+          const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
+          if (leader) {
+            mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES2);
+            armed[stage] = true;
+            armed_parity[stage] = phase;
+          }
+          tma_load_2d_pair(a_dst, &tmap_a, kb * BK, m0, lead_full);
+          tma_load_2d_pair(a_dst + A_BYTES2, &tmap_b, kb * BK, n0, lead_full);
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      // the leader's full barriers count the bytes of both CTAs: once they have completed no
+      // bulk copy of the pair is still landing (the peer stays until the final cluster barrier)
+      for (int s = 0; s < STAGES2; ++s)
+        if (armed[s]) mbar_wait(full_bar(s), armed_parity[s]);
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer (leader CTA only) =====================
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int64_t it = 0;
+      bool ok = true;
+      for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
+        const int as = static_cast<int>(it & 1);
+        const uint32_t aphase = static_cast<uint32_t>((it >> 1) & 1);
+        if (!mbar_wait(acc_empty_bar(as), aphase ^ 1u)) {
+          report(p.status, ST_MMA);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase)) {
+            report(p.status, ST_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_src = tiles_base + stage * STAGE_BYTES2;
+          const uint64_t a_desc = make_smem_desc(a_src);
+          const uint64_t b_desc = make_smem_desc(a_src + A_BYTES2);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; ++j) {
+            const uint64_t koff = static_cast<uint64_t>((j * UMMA_K) >> 4);
+            tc_mma_i8_pair(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          tc_commit_pair(empty_bar(stage));
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tc_commit_pair(acc_full_bar(as));
+      }
+    }
+  } else {
+    // ===================== epilogue (warps 2..5, both CTAs) =====================
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    const float sx_scalar = (p.sx && !p.sx_per_row) ? __ldg(p.sx) : 1.0f;
+    const int zx_i = p.zx ? __float2int_rn(__ldg(p.zx)) : 0;
+    int64_t it = 0;
+    for (int64_t t = pair_id; t < num_tiles; t += num_pairs, ++it) {
+      int64_t tm, tn;
+      tile_coords(t, tiles_m, tiles_n, tm, tn);
+      const int64_t m0 = tm * 2 * BM + rank * BM, n0 = tn * BN;
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+      for (int j = et; j < BN; j += EPI_THREADS) {
+        const int64_t n = n0 + j;
+        const bool in = n < p.N;
+        s_sw[j] = (in && p.sw) ? __ldg(p.sw + n) : 1.0f;
+        s_bias[j] = (in && p.bias) ? __ldg(p.bias + n) : 0.0f;
+        s_corr[j] = (in && p.wsum) ? zx_i * __ldg(p.wsum + n) : 0;
+      }
+      const int as = static_cast<int>(it & 1);
+      const uint32_t aphase = static_cast<uint32_t>((it >> 1) & 1);
+      if (!epilogue_all(mbar_wait(acc_full_bar(as), aphase))) {
+        report(p.status, ST_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const int64_t row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float sxr = p.sx_per_row ? (row_ok ? __ldg(p.sx + row) : 0.0f) : sx_scalar;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                             static_cast<uint32_t>(as * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tc_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
+        tc_wait_ld();
+        const int64_t col0 = n0 + c * 32;
+        if (row_ok && col0 < p.N) {
+          if (p.out_dtype == LC_S32) {
+            int v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = static_cast<int>(r[j]) - s_corr[c * 32 + j];
+            store_chunk_s32(p, row, col0, v);
+          } else {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int a = static_cast<int>(r[j]) - s_corr[c * 32 + j];
+              const float f = __fmul_rn(__fmul_rn(static_cast<float>(a), sxr), s_sw[c * 32 + j]);
+              v[j] = __fadd_rn(f, s_bias[c * 32 + j]);
+            }
+            if (p.out_dtype == LC_F32)
+              store_chunk<float>(p, row, col0, v);
+            else
+              store_chunk<__nv_bfloat16>(p, row, col0, v);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(as), 0));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees TMEM or leaves while the other may still use the pair
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(TMEM_COLS))
+                 : "memory");
+  }
+}
+
 // ---- host side ---------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -494,6 +772,9 @@ static int32_t ensure_smem_attr() {
   std::call_once(flags[dev], [dev]() {
     results[dev] = cudaFuncSetAttribute(qlinear_i8_kernel,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (results[dev] == cudaSuccess)
+      results[dev] = cudaFuncSetAttribute(qlinear_i8_pair_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES2);
   });
   if (results[dev] != cudaSuccess)
     return fail(LC_ERR_CUDA, "cannot reserve %d bytes of shared memory: %s", SMEM_BYTES,
@@ -511,7 +792,17 @@ extern "C" int32_t lc_qlinear_i8(const void* a, int32_t a_unsigned, int64_t lda,
                                  int32_t sx_per_row, const float* zx, const int32_t* wsum,
                                  const float* sw, const float* bias, void* out, int32_t out_dtype,
                                  int64_t ldo, int32_t* status, void* stream) {
+  return lc_qlinear_i8_ex(a, a_unsigned, lda, b, ldb, M, N, K, sx, sx_per_row, zx, wsum, sw, bias, out,
+                          out_dtype, ldo, status, 0, stream);
+}
+
+extern "C" int32_t lc_qlinear_i8_ex(const void* a, int32_t a_unsigned, int64_t lda, const int8_t* b,
+                                    int64_t ldb, int64_t M, int64_t N, int64_t K, const float* sx,
+                                    int32_t sx_per_row, const float* zx, const int32_t* wsum,
+                                    const float* sw, const float* bias, void* out, int32_t out_dtype,
+                                    int64_t ldo, int32_t* status, int32_t variant, void* stream) {
   using namespace lc::gemm;
+  if (variant < 0 || variant > 2) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: variant must be 0, 1 or 2");
   if (M < 0 || N < 0 || K <= 0) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: bad shape");
   if (M == 0 || N == 0) return LC_OK;
   if (!a || !b || !out) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: null pointer");
@@ -527,9 +818,12 @@ extern "C" int32_t lc_qlinear_i8(const void* a, int32_t a_unsigned, int64_t lda,
   if (M > 0x7fffffffLL - BM || N > 0x7fffffffLL - BN || K > 0x7fffffffLL - BK)
     return fail(LC_ERR_UNSUPPORTED, "qlinear_i8: dimension exceeds the TMA coordinate range");
 
+  // CTA pairs pay off once there is more than one 128-row tile of A; a single row tile
+  // would leave half of every pair idle
+  const bool use_pair = variant == 2 || (variant == 0 && M > BM);
   CUtensorMap map_a, map_b;
   if (int32_t rc = make_map(&map_a, a, M, K, lda, BM)) return rc;
-  if (int32_t rc = make_map(&map_b, b, N, K, ldb, BN)) return rc;
+  if (int32_t rc = make_map(&map_b, b, N, K, ldb, use_pair ? pair::BNH : BN)) return rc;
   if (int32_t rc = ensure_smem_attr()) return rc;
 
   Params p;
@@ -549,8 +843,15 @@ extern "C" int32_t lc_qlinear_i8(const void* a, int32_t a_unsigned, int64_t lda,
   p.out_vec = (aligned(out, 16) && (ldo * esz) % 16 == 0) ? 1 : 0;
   p.status = status;
 
-  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int64_t sms = sm_count();
+  if (use_pair) {
+    const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+    qlinear_i8_pair_kernel<<<static_cast<unsigned>(2 * pairs), NUM_THREADS, pair::SMEM_BYTES2,
+                             as_stream(stream)>>>(map_a, map_b, p, make_idesc_pair(a_unsigned != 0));
+    return check_launch("qlinear_i8 (cta pair)");
+  }
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
   qlinear_i8_kernel<<<grid, NUM_THREADS, SMEM_BYTES, as_stream(stream)>>>(
       map_a, map_b, p, make_idesc(a_unsigned != 0));

@@ -192,23 +192,33 @@ wo_linear_mma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx
   }
 }
 
-// ---- TMA-staged variant for weight matrices that do not fit the caches ----------
-// One CTA owns `tiles_per_cta` consecutive 16-row tiles and streams their weights through
-// a ring of shared-memory stages filled by a producer warp with 1-D bulk copies
-// (cp.async.bulk, one per weight row and K chunk), so that ~200 KB of loads are in flight
-// per SM without holding them in registers.  16 consumer warps split each K chunk
-// (warp w takes bytes [64w, 64w+64) of every 1024-byte block), widen the int8 weights to
-// the activation type and feed mma.sync; the activation fragments of a chunk are loaded
-// from L2 once per chunk and reused for every row tile of the CTA.  The K split is
-// reduced through shared memory at the end.  Every mbarrier wait is bounded; a wait that
-// runs out records a code in g_wo_status and the CTA drains and returns.
-namespace tma_gemv {
+// ---- ring variant for weight matrices that do not fit the caches ------------------------
+// A persistent CTA owns `tiles_per_cta` consecutive 16-row tiles.  A producer warp streams
+// their weights (and, per K chunk, the activations) into shared memory with 1-D bulk copies
+// (cp.async.bulk, one per row of a 16 x 1024-byte item), so ~150 KB of loads are in flight
+// per SM without living in registers.  16 consumer warps split every item along K (warp w
+// takes bytes [64w, 64w+64) of each row), widen the int8 weights to the activation type and
+// feed mma.sync m16n8k16 with fp32 accumulation.  Row tiles are processed in passes of at
+// most TMAX tiles so the per-warp partial sums stay in registers; each pass runs over all of
+// K and ends with a split-K reduction across the warps through shared memory.
+// Every mbarrier wait is bounded; a wait that runs out records a code in g_wo_status and the
+// CTA drains its copies and returns.
+namespace ring {
 constexpr int kConsumerWarps = 16;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kSmemBudget = 225 * 1024;
-constexpr long long kWaitCycles = 4000000000LL;
-}  // namespace tma_gemv
+constexpr int KC = 1024;               // bytes of K per item (and per activation chunk)
+constexpr int W_PITCH = KC + 64;       // row pitch: LDS.128 of rows g and g+1 hit disjoint banks
+constexpr int STAGE = 16 * W_PITCH;    // 17408
+constexpr int X_PITCH = KC * 2 + 16;   // activation row pitch (16-bit elements), same reason
+constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 2 GHz
+__host__ __device__ constexpr int red_bytes(int nt) { return kConsumerWarps * 16 * (nt * 8 + 1) * 4; }
+__host__ __device__ constexpr int x_bytes(int nt) { return 2 * nt * 8 * X_PITCH; }
+__host__ __device__ constexpr int stages(int nt) {
+  return (kSmemBudget - 512 - red_bytes(nt) - x_bytes(nt)) / STAGE;
+}
+}  // namespace ring
 
 __device__ int g_wo_status = 0;
 
@@ -227,162 +237,138 @@ __device__ __forceinline__ bool wo_mbar_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     if (ok) return true;
-    if (clock64() - t0 > tma_gemv::kWaitCycles) return false;
+    if (clock64() - t0 > ring::kWaitCycles) return false;
   }
 }
-__device__ __forceinline__ int4 wo_lds128(uint32_t addr) {
-  int4 v;
-  asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(addr));
+__device__ __forceinline__ void wo_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void wo_mbar_expect(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void wo_bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ uint4 wo_lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
 
-template <typename XT, int NT, int TMAX, int STEPS>
-__global__ void __launch_bounds__(tma_gemv::kThreads, 1)
-wo_linear_tma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx,
-                     const int8_t* __restrict__ w, int64_t ldw, int64_t N,
-                     const float* __restrict__ sw, const float* __restrict__ bias,
-                     XT* __restrict__ y, int64_t ldy, int tiles_per_cta) {
-  using namespace tma_gemv;
-  constexpr int KC = 1024 * STEPS;        // bytes of K per pipeline item
-  constexpr int W_PITCH = KC + 64;        // row pitch: LDS.128 of rows g, g+1 hit disjoint banks
-  constexpr int STAGE = 16 * W_PITCH;
-  constexpr int S = (kSmemBudget - 256) / STAGE;
+// four offset-binary bytes -> two packed pairs (bytes 0,1 and bytes 2,3) of XT
+template <typename XT>
+__device__ __forceinline__ void widen_word(uint32_t u, uint32_t& p01, uint32_t& p23) {
+  p01 = widen_pair<XT>(u, 0);
+  p23 = widen_pair<XT>(u, 2);
+}
+// bf16: the four fp32 subtractions are issued as two packed f32x2 adds
+template <>
+__device__ __forceinline__ void widen_word<__nv_bfloat16>(uint32_t u, uint32_t& p01, uint32_t& p23) {
+  const uint32_t m = 0x4B000000u;
+  const uint32_t f0 = __byte_perm(u, m, 0x7650u), f1 = __byte_perm(u, m, 0x7651u);
+  const uint32_t f2 = __byte_perm(u, m, 0x7652u), f3 = __byte_perm(u, m, 0x7653u);
+  const uint32_t neg = 0xCB000080u;  // -(2^23 + 128)
+  uint32_t a0, a1, a2, a3;
+  asm("{\n\t.reg .b64 x, y, n;\n\t"
+      "mov.b64 x, {%4, %5};\n\t"
+      "mov.b64 y, {%6, %7};\n\t"
+      "mov.b64 n, {%8, %8};\n\t"
+      "add.rn.f32x2 x, x, n;\n\t"
+      "add.rn.f32x2 y, y, n;\n\t"
+      "mov.b64 {%0, %1}, x;\n\t"
+      "mov.b64 {%2, %3}, y;\n\t}"
+      : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
+      : "r"(f0), "r"(f1), "r"(f2), "r"(f3), "r"(neg));
+  p01 = __byte_perm(a0, a1, 0x7632u);
+  p23 = __byte_perm(a2, a3, 0x7632u);
+}
+
+template <typename XT, int NT, int TMAX>
+__global__ void __launch_bounds__(ring::kThreads, 1)
+wo_linear_ring_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx,
+                      const int8_t* __restrict__ w, int64_t ldw, int64_t N,
+                      const float* __restrict__ sw, const float* __restrict__ bias,
+                      XT* __restrict__ y, int64_t ldy, int tiles_per_cta) {
+  using namespace ring;
+  constexpr int S = stages(NT);
+  constexpr int COLS = NT * 8, RP = COLS + 1;
   extern __shared__ uint8_t wo_smem_raw[];
   const uint32_t base = (wo_smem_u32(wo_smem_raw) + 127u) & ~127u;
-  const uint32_t bar_base = base + S * STAGE;
+  const uint32_t x_base = base + S * STAGE;
+  const uint32_t red_base = x_base + x_bytes(NT);
+  const uint32_t bar_base = red_base + red_bytes(NT);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+  auto xfull_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
+  auto xempty_bar = [&](int s) { return bar_base + 8u * (2 * S + 2 + s); };
+  float* red = reinterpret_cast<float*>(wo_smem_raw + (red_base - wo_smem_u32(wo_smem_raw)));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t tiles_total = (N + 15) >> 4;
   const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * tiles_per_cta;
-  const int my_tiles = static_cast<int>(tiles_total - tile0 < tiles_per_cta ? tiles_total - tile0 : tiles_per_cta);
+  const int my_tiles =
+      static_cast<int>(tiles_total - tile0 < tiles_per_cta ? tiles_total - tile0 : tiles_per_cta);
   const int num_kc = static_cast<int>((K + KC - 1) / KC);
+  const int nb = static_cast<int>(B);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full_bar(s)), "r"(1) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty_bar(s)), "r"(kConsumerWarps) : "memory");
     }
+    for (int s = 0; s < 2; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(xfull_bar(s)), "r"(1) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(xempty_bar(s)), "r"(kConsumerWarps) : "memory");
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
 
-  float acc[TMAX][NT][4];
-#pragma unroll
-  for (int j = 0; j < TMAX; ++j)
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[j][nt][i] = 0.0f;
-
   if (warp == kConsumerWarps) {
     // ===================== producer =====================
-    if (lane == 0) {
-      int stage = 0;
+    // The whole warp runs this loop: lane 0 arms the barrier, then lane r issues the bulk copy
+    // of row r (a single thread issuing all 16 copies of an item serialises on their issue
+    // latency and cannot keep the ring full).
+    {
+      int stage = 0, xi = 0;
       uint32_t phase = 0;
-      uint32_t armed_parity[S];
-      bool armed[S];
-      for (int s = 0; s < S; ++s) armed[s] = false;
+      uint32_t armed_mask = 0, armed_parity = 0, xarmed_mask = 0, xarmed_parity = 0;  // bit per stage
       bool ok = true;
-      for (int kc = 0; kc < num_kc && ok; ++kc) {
-        const int64_t k0 = static_cast<int64_t>(kc) * KC;
-        const uint32_t kc_len = static_cast<uint32_t>(K - k0 < KC ? K - k0 : KC);
-        for (int j = 0; j < my_tiles; ++j) {
-          if (!wo_mbar_wait(empty_bar(stage), phase ^ 1u)) {
-            atomicCAS(&g_wo_status, 0, 1);
-            ok = false;
+      for (int t0 = 0; t0 < my_tiles && ok; t0 += TMAX) {
+        const int pass_tiles = my_tiles - t0 < TMAX ? my_tiles - t0 : TMAX;
+        for (int kc = 0; kc < num_kc && ok; ++kc, ++xi) {
+          const int64_t k0 = static_cast<int64_t>(kc) * KC;
+          const uint32_t kc_len = static_cast<uint32_t>(K - k0 < KC ? K - k0 : KC);
+          const int xb = xi & 1;
+          const uint32_t xphase = static_cast<uint32_t>((xi >> 1) & 1);
+          ok = __all_sync(0xffffffffu, wo_mbar_wait(xempty_bar(xb), xphase ^ 1u));
+          if (!ok) {
+            if (lane == 0) atomicCAS(&g_wo_status, 0, 1);
             break;
           }
-          const int64_t row0 = (tile0 + j) << 4;
-          const int rows = static_cast<int>(N - row0 < 16 ? N - row0 : 16);
-          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_bar(stage)),
-                       "r"(static_cast<uint32_t>(rows) * kc_len)
-                       : "memory");
-          const uint32_t dst = base + stage * STAGE;
-          for (int r = 0; r < rows; ++r) {
-            asm volatile(
-                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                    dst + r * W_PITCH),
-                "l"(w + (row0 + r) * ldw + k0), "r"(kc_len), "r"(full_bar(stage))
-                : "memory");
-          }
-          armed[stage] = true;
-          armed_parity[stage] = phase;
-          if (++stage == S) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-      }
-      for (int s = 0; s < S; ++s)
-        if (armed[s]) wo_mbar_wait(full_bar(s), armed_parity[s]);
-    }
-  } else {
-    // ===================== consumers =====================
-    const int g = lane >> 2, t = lane & 3;
-    uint32_t xa[STEPS][NT][8], xn[STEPS][NT][8];
-    auto load_x = [&](int kc, uint32_t (&dst)[STEPS][NT][8]) {
-#pragma unroll
-      for (int st = 0; st < STEPS; ++st) {
-        const int64_t k = static_cast<int64_t>(kc) * KC + st * 1024 + warp * 64 + t * 16;
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const int64_t b = nt * 8 + g;
-          if (k < K && b < B) {
-            const uint4* px = reinterpret_cast<const uint4*>(x + b * ldx + k);
-            const uint4 lo = __ldg(px), hi = __ldg(px + 1);
-            dst[st][nt][0] = lo.x; dst[st][nt][1] = lo.y; dst[st][nt][2] = lo.z; dst[st][nt][3] = lo.w;
-            dst[st][nt][4] = hi.x; dst[st][nt][5] = hi.y; dst[st][nt][6] = hi.z; dst[st][nt][7] = hi.w;
-          } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) dst[st][nt][i] = 0u;
-          }
-        }
-      }
-    };
-    load_x(0, xa);
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    for (int kc = 0; kc < num_kc && ok; ++kc) {
-      if (kc + 1 < num_kc) load_x(kc + 1, xn);
-      const int64_t k_left = K - static_cast<int64_t>(kc) * KC;
-#pragma unroll
-      for (int j = 0; j < TMAX; ++j) {
-        if (j < my_tiles && ok) {
-          if (!wo_mbar_wait(full_bar(stage), phase)) {
-            atomicCAS(&g_wo_status, 0, 2);
-            ok = false;
-          } else {
-            const uint32_t src = base + stage * STAGE + g * W_PITCH + warp * 64 + t * 16;
-#pragma unroll
-            for (int st = 0; st < STEPS; ++st) {
-              const bool k_ok = (st * 1024 + warp * 64 + t * 16) < k_left;
-              int4 w0 = make_int4(0, 0, 0, 0), w1 = make_int4(0, 0, 0, 0);
-              if (k_ok) {
-                w0 = wo_lds128(src + st * 1024);
-                w1 = wo_lds128(src + st * 1024 + 8 * W_PITCH);
-              }
-              const int* p0 = reinterpret_cast<const int*>(&w0);
-              const int* p1 = reinterpret_cast<const int*>(&w1);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t u0 = static_cast<uint32_t>(p0[q]) ^ 0x80808080u;
-                const uint32_t u1 = static_cast<uint32_t>(p1[q]) ^ 0x80808080u;
-                // a zero weight chunk must stay zero after the offset-binary trick
-                const uint32_t a0 = k_ok ? widen_pair<XT>(u0, 0) : 0u, a2 = k_ok ? widen_pair<XT>(u0, 2) : 0u;
-                const uint32_t a1 = k_ok ? widen_pair<XT>(u1, 0) : 0u, a3 = k_ok ? widen_pair<XT>(u1, 2) : 0u;
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-                  mma_16816<XT>(acc[j][nt], a0, a1, a2, a3, xa[st][nt][2 * q], xa[st][nt][2 * q + 1]);
-              }
+          if (lane == 0) wo_mbar_expect(xfull_bar(xb), static_cast<uint32_t>(nb) * kc_len * 2u);
+          __syncwarp();
+          if (lane < nb)
+            wo_bulk_copy(x_base + (xb * COLS + lane) * X_PITCH, x + lane * ldx + k0, kc_len * 2u, xfull_bar(xb));
+          xarmed_mask |= 1u << xb;
+          xarmed_parity = (xarmed_parity & ~(1u << xb)) | (xphase << xb);
+          for (int j = 0; j < pass_tiles; ++j) {
+            ok = __all_sync(0xffffffffu, wo_mbar_wait(empty_bar(stage), phase ^ 1u));
+            if (!ok) {
+              if (lane == 0) atomicCAS(&g_wo_status, 0, 1);
+              break;
             }
+            const int64_t row0 = (tile0 + t0 + j) << 4;
+            const int rows = static_cast<int>(N - row0 < 16 ? N - row0 : 16);
+            if (lane == 0) wo_mbar_expect(full_bar(stage), static_cast<uint32_t>(rows) * kc_len);
             __syncwarp();
-            if (lane == 0)
-              asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar(stage)) : "memory");
+            if (lane < rows)
+              wo_bulk_copy(base + stage * STAGE + lane * W_PITCH, w + (row0 + lane) * ldw + k0, kc_len,
+                           full_bar(stage));
+            armed_mask |= 1u << stage;
+            armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
             if (++stage == S) {
               stage = 0;
               phase ^= 1u;
@@ -390,43 +376,122 @@ wo_linear_tma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx
           }
         }
       }
+      // do not leave while one of this CTA's bulk copies may still be landing
+      for (int s = 0; s < S; ++s)
+        if (armed_mask & (1u << s)) wo_mbar_wait(full_bar(s), (armed_parity >> s) & 1u);
+      for (int s = 0; s < 2; ++s)
+        if (xarmed_mask & (1u << s)) wo_mbar_wait(xfull_bar(s), (xarmed_parity >> s) & 1u);
+    }
+  } else {
+    // ===================== consumers =====================
+    const int g = lane >> 2, t = lane & 3;
+    const int koff = warp * 64 + t * 16;  // this lane's byte offset inside an item row
+    int stage = 0, xi = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t0 = 0; t0 < my_tiles; t0 += TMAX) {
+      const int pass_tiles = my_tiles - t0 < TMAX ? my_tiles - t0 : TMAX;
+      float acc[TMAX][NT][4];
 #pragma unroll
-      for (int st = 0; st < STEPS; ++st)
+      for (int j = 0; j < TMAX; ++j)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-          for (int i = 0; i < 8; ++i) xa[st][nt][i] = xn[st][nt][i];
-    }
-    // ---- split-K reduction across the 16 consumer warps, one row tile at a time ----
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");  // ring no longer read
-    float* red = reinterpret_cast<float*>(wo_smem_raw + (base - wo_smem_u32(wo_smem_raw)));
-    constexpr int COLS = NT * 8, RP = COLS + 1;
-#pragma unroll
-    for (int j = 0; j < TMAX; ++j) {
-      if (j < my_tiles) {
-        float* mine = red + warp * 16 * RP;
+          for (int i = 0; i < 4; ++i) acc[j][nt][i] = 0.0f;
+
+      for (int kc = 0; kc < num_kc && ok; ++kc, ++xi) {
+        const int xb = xi & 1;
+        const uint32_t xphase = static_cast<uint32_t>((xi >> 1) & 1);
+        const bool k_ok = static_cast<int64_t>(kc) * KC + koff < K;               // this lane
+        const bool warp_k_ok = static_cast<int64_t>(kc) * KC + warp * 64 < K;     // any lane of the warp
+        if (!wo_mbar_wait(xfull_bar(xb), xphase)) {
+          atomicCAS(&g_wo_status, 0, 2);
+          ok = false;
+          break;
+        }
+        // activation fragments of this chunk: 16 consecutive elements per batch row
+        uint32_t xa[NT][8];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          mine[g * RP + nt * 8 + 2 * t] = acc[j][nt][0];
-          mine[g * RP + nt * 8 + 2 * t + 1] = acc[j][nt][1];
-          mine[(g + 8) * RP + nt * 8 + 2 * t] = acc[j][nt][2];
-          mine[(g + 8) * RP + nt * 8 + 2 * t + 1] = acc[j][nt][3];
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-        const int64_t row0 = (tile0 + j) << 4;
-        for (int o = threadIdx.x; o < 16 * COLS; o += kConsumerThreads) {
-          const int r = o & 15, bcol = o >> 4;
-          const int64_t n = row0 + r;
-          if (n < N && bcol < B) {
-            float sum = 0.0f;
+          const int b = nt * 8 + g;
+          if (k_ok && b < nb) {
+            const uint32_t xs = x_base + (xb * COLS + b) * X_PITCH + koff * 2;
+            const uint4 lo = wo_lds128(xs), hi = wo_lds128(xs + 16);
+            xa[nt][0] = lo.x; xa[nt][1] = lo.y; xa[nt][2] = lo.z; xa[nt][3] = lo.w;
+            xa[nt][4] = hi.x; xa[nt][5] = hi.y; xa[nt][6] = hi.z; xa[nt][7] = hi.w;
+          } else {
 #pragma unroll
-            for (int wp = 0; wp < kConsumerWarps; ++wp) sum += red[wp * 16 * RP + r * RP + bcol];
-            float v = sum * (sw ? __ldg(sw + n) : 1.0f);
-            if (bias) v += __ldg(bias + n);
-            y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(v);
+            for (int i = 0; i < 8; ++i) xa[nt][i] = 0u;
           }
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+#pragma unroll
+        for (int j = 0; j < TMAX; ++j) {
+          if (j < pass_tiles && ok) {
+            if (!wo_mbar_wait(full_bar(stage), phase)) {
+              atomicCAS(&g_wo_status, 0, 2);
+              ok = false;
+            } else {
+              // warp-uniform skip (mma.sync needs the whole warp); lanes past the end of K
+              // inside a live warp contribute zero weights (raw 0 is code 0 in offset binary)
+              if (warp_k_ok) {
+                const uint32_t src = base + stage * STAGE + g * W_PITCH + koff;
+                uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = make_uint4(0u, 0u, 0u, 0u);
+                if (k_ok) {
+                  w0 = wo_lds128(src);
+                  w1 = wo_lds128(src + 8 * W_PITCH);
+                }
+                const uint32_t r0[4] = {w0.x, w0.y, w0.z, w0.w}, r1[4] = {w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  uint32_t a0, a1, a2, a3;
+                  widen_word<XT>(r0[q] ^ 0x80808080u, a0, a2);
+                  widen_word<XT>(r1[q] ^ 0x80808080u, a1, a3);
+#pragma unroll
+                  for (int nt = 0; nt < NT; ++nt)
+                    mma_16816<XT>(acc[j][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                }
+              }
+              __syncwarp();
+              if (lane == 0) wo_mbar_arrive(empty_bar(stage));
+              if (++stage == S) {
+                stage = 0;
+                phase ^= 1u;
+              }
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0 && ok) wo_mbar_arrive(xempty_bar(xb));
+      }
+
+      // ---- split-K reduction of this pass across the 16 consumer warps ----
+#pragma unroll
+      for (int j = 0; j < TMAX; ++j) {
+        if (j < pass_tiles) {
+          float* mine = red + warp * 16 * RP;
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            mine[g * RP + nt * 8 + 2 * t] = acc[j][nt][0];
+            mine[g * RP + nt * 8 + 2 * t + 1] = acc[j][nt][1];
+            mine[(g + 8) * RP + nt * 8 + 2 * t] = acc[j][nt][2];
+            mine[(g + 8) * RP + nt * 8 + 2 * t + 1] = acc[j][nt][3];
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+          const int64_t row0 = (tile0 + t0 + j) << 4;
+          for (int o = threadIdx.x; o < 16 * COLS; o += kConsumerThreads) {
+            const int r = o & 15, bcol = o >> 4;
+            const int64_t n = row0 + r;
+            if (n < N && bcol < nb) {
+              float sum = 0.0f;
+#pragma unroll
+              for (int wp = 0; wp < kConsumerWarps; ++wp) sum += red[wp * 16 * RP + r * RP + bcol];
+              float v = sum * (sw ? __ldg(sw + n) : 1.0f);
+              if (bias) v += __ldg(bias + n);
+              y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(v);
+            }
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+        }
       }
     }
   }
@@ -601,38 +666,37 @@ static int32_t launch_wo_mma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
   return check_launch("wo_linear_s8 (mma)");
 }
 
-template <typename XT, int NT, int TMAX, int STEPS>
-static int32_t launch_wo_tma_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
-                                  int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
-                                  int64_t ldy, cudaStream_t st) {
-  auto kernel = wo_linear_tma_kernel<XT, NT, TMAX, STEPS>;
+template <typename XT, int NT, int TMAX>
+static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
+                                   int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
+                                   int64_t ldy, cudaStream_t st) {
+  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(LC_ERR_CUDA, "no current CUDA device");
   std::call_once(flags[dev], [&]() {
-    results[dev] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        tma_gemv::kSmemBudget);
+    results[dev] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ring::kSmemBudget);
   });
   if (results[dev] != cudaSuccess)
     return fail(LC_ERR_CUDA, "wo_linear_s8: cannot reserve shared memory: %s", cudaGetErrorString(results[dev]));
+  // an evenly divided persistent grid: every CTA gets the same number of row tiles
   const int64_t tiles = (N + 15) / 16;
   const int64_t sms = sm_count();
-  int64_t per = (tiles + sms - 1) / sms;
-  if (per > TMAX) per = TMAX;
+  const int64_t per = (tiles + sms - 1) / sms;
   const unsigned grid = static_cast<unsigned>((tiles + per - 1) / per);
-  kernel<<<grid, tma_gemv::kThreads, tma_gemv::kSmemBudget, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy,
-                                                                   static_cast<int>(per));
-  return check_launch("wo_linear_s8 (tma)");
+  kernel<<<grid, ring::kThreads, ring::kSmemBudget, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy,
+                                                          static_cast<int>(per));
+  return check_launch("wo_linear_s8 (ring)");
 }
 
 template <typename XT>
 static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w, int64_t ldw,
                              int64_t N, const float* sw, const float* bias, XT* y, int64_t ldy,
                              cudaStream_t st) {
-  if (B <= 8) return launch_wo_tma_inst<XT, 1, 8, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
-  if (B <= 16) return launch_wo_tma_inst<XT, 2, 8, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
-  return launch_wo_tma_inst<XT, 4, 4, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+  if (B <= 8) return launch_wo_ring_inst<XT, 1, 8>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+  if (B <= 16) return launch_wo_ring_inst<XT, 2, 4>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+  return launch_wo_ring_inst<XT, 4, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
 }
 
 template <typename XT>
@@ -663,7 +727,7 @@ static int32_t wo_linear_typed(const void* x, int64_t B, int64_t K, int64_t ldx,
     if constexpr (sizeof(XT) == 2) {
       // weights beyond a few MB are streamed through the shared-memory ring; small ones
       // are latency-bound and use the direct-load kernel
-      const bool big = false && N * K >= (int64_t{4} << 20);  // ring kernel not enabled yet
+      const bool big = N * K >= (int64_t{4} << 20);
       rc = !mma_ok ? launch_wo_fma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st)
            : big   ? launch_wo_tma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st)
                    : launch_wo_mma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st);

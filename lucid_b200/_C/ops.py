@@ -281,13 +281,14 @@ def rowsum_s8(b: torch.Tensor) -> torch.Tensor:
 
 
 def qlinear_i8(a, b, sx, sw, bias=None, zx=None, wsum=None, out_dtype: torch.dtype = torch.float32,
-               status: torch.Tensor | None = None):
+               status: torch.Tensor | None = None, variant: int = 0):
     """``out = f32(a @ b^T - zx*wsum) * sx * sw + bias`` on the tcgen05 int8 path.
 
     ``a``: [M,K] int8 or uint8 codes, ``b``: [N,K] int8 codes, both with unit
     column stride and a 16-byte row pitch (see :func:`pad_rows_to_16`).
     ``sx``: 0-d / 1-element (per tensor) or [M] (per row) fp32.  With
     ``out_dtype=torch.int32`` the raw (zero-point corrected) accumulator is returned.
+    ``variant``: 0 automatic, 1 single-CTA tiles, 2 CTA-pair tiles (``cta_group::2``).
     """
     dev = _need_cuda(a, b, sx, sw, bias, zx, wsum, status)
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
@@ -314,10 +315,10 @@ def qlinear_i8(a, b, sx, sw, bias=None, zx=None, wsum=None, out_dtype: torch.dty
     zx_c = None if zx is None else _f32c(zx).reshape(-1)
     wsum_c = None if wsum is None else wsum.to(torch.int32).contiguous()
     with torch.cuda.device(dev):
-        check(lib.lc_qlinear_i8(a.data_ptr(), int(a.dtype == torch.uint8), a.stride(0), b.data_ptr(),
-                                b.stride(0), M, N, K, _ptr(sx), per_row, _ptr(zx_c), _ptr(wsum_c),
-                                _ptr(sw_c), _ptr(bias_c), out.data_ptr(), _lc_dtype(out_dtype), N,
-                                _ptr(status), _stream(dev)))
+        check(lib.lc_qlinear_i8_ex(a.data_ptr(), int(a.dtype == torch.uint8), a.stride(0), b.data_ptr(),
+                                   b.stride(0), M, N, K, _ptr(sx), per_row, _ptr(zx_c), _ptr(wsum_c),
+                                   _ptr(sw_c), _ptr(bias_c), out.data_ptr(), _lc_dtype(out_dtype), N,
+                                   _ptr(status), int(variant), _stream(dev)))
     return out
 
 
@@ -343,6 +344,16 @@ def wo_linear_s8(x2d, wq, sw, bias=None):
         check(lib.lc_wo_linear_s8(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq.data_ptr(),
                                   wq.stride(0), N, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N, _stream(dev)))
     return y
+
+
+def wo_linear_status(clear: bool = True) -> int:
+    """Status word of the weight-only kernels on the current device (synchronises): 0, or the
+    code of a bounded device-side wait that ran out."""
+    import ctypes
+
+    code = ctypes.c_int32(0)
+    check(lib.lc_wo_linear_status(ctypes.byref(code), int(clear)))
+    return int(code.value)
 
 
 def group_quantize(w, group_size: int = 64, bits: int = 8):

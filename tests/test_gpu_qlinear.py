@@ -37,13 +37,14 @@ def status_word():
 @pytest.mark.parametrize("M,N,K", [(1, 1, 16), (128, 256, 128), (128, 256, 512), (64, 4096, 1024), (7, 9, 48),
                                    (129, 257, 144), (300, 520, 1040), (256, 512, 8192), (1000, 130, 80), (5, 6, 24), (33, 40, 200)])
 @pytest.mark.parametrize("a_unsigned", [False, True])
-def test_int32_accumulator_bit_exact(ops, M, N, K, a_unsigned):
+@pytest.mark.parametrize("variant", [1, 2])
+def test_int32_accumulator_bit_exact(ops, M, N, K, a_unsigned, variant):
     r = np.random.default_rng(M * 7 + N * 3 + K)
     a = r.integers(0, 256, (M, K)).astype(np.uint8) if a_unsigned else r.integers(-128, 128, (M, K)).astype(np.int8)
     b = r.integers(-128, 128, (N, K)).astype(np.int8)
     st = status_word()
     acc = ops.qlinear_i8(ops.pad_rows_to_16(dev(a)), ops.pad_rows_to_16(dev(b)), None, None,
-                         out_dtype=torch.int32, status=st)
+                         out_dtype=torch.int32, status=st, variant=variant)
     np.testing.assert_array_equal(host(acc), O.int_gemm_exact(a, b))
     assert int(host(st)[0]) == 0
 
@@ -127,6 +128,9 @@ def test_prefill_shape_properties(ops):
     # sharding over N (column-parallel) reproduces the same columns bit for bit
     shard = ops.qlinear_i8(xq, wq[1792:], None, None, out_dtype=torch.int32)
     assert torch.equal(shard, acc[:, 1792:])
+    # single-CTA and CTA-pair tiles give the same accumulator
+    for variant in (1, 2):
+        assert torch.equal(ops.qlinear_i8(xq, wq, None, None, out_dtype=torch.int32, variant=variant), acc)
     y = ops.qlinear_i8(xq, wq, sx, sw)
     y64 = acc.to(torch.float64) * sx.to(torch.float64)[:, None] * sw.to(torch.float64)[None, :]
     assert torch.allclose(y.to(torch.float64), y64, rtol=RTOL, atol=ATOL)

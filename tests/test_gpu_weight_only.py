@@ -55,6 +55,26 @@ def test_decode_mlp_shapes(ops):
             y = ops.wo_linear_s8(x, wq, sw)
             ref = (x.double() @ wq.double().T) * sw.double()[None, :]
             assert torch.allclose(y.double(), ref, rtol=1e-2, atol=1e-2 * float(ref.abs().max()))
+    assert ops.wo_linear_status() == 0, "a bounded device-side wait ran out"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,N,K", [(1, 2048, 2048), (3, 2050, 2064), (8, 4097, 1040), (9, 2400, 3072), (16, 5000, 1024),
+                                   (17, 2048, 2048), (32, 2048, 4096), (5, 16, 262144), (2, 37000, 128)])
+def test_wo_linear_ring_kernel_shapes(ops, dtype, B, N, K):
+    """Weights of 4 MB and more go through the shared-memory ring kernel: ragged N (partial row
+    tile), K not a multiple of the 1024-byte chunk, every batch-tile width, very long and very
+    short rows."""
+    g = torch.Generator(device="cuda").manual_seed(B * 7 + N + K)
+    wq = torch.randint(-128, 128, (N, K), device="cuda", dtype=torch.int8, generator=g)
+    sw = torch.rand(N, device="cuda", generator=g) * 0.01 + 0.001
+    bias = torch.randn(N, device="cuda", generator=g) * 0.1
+    x = torch.randn(B, K, device="cuda", generator=g).to(dtype)
+    y = ops.wo_linear_s8(x, wq, sw, bias)
+    ref = (x.double() @ wq.double().T) * sw.double()[None, :] + bias.double()[None, :]
+    tol = 1e-2 if dtype == torch.bfloat16 else 2e-3
+    assert torch.allclose(y.double(), ref, rtol=tol, atol=tol * float(ref.abs().max()))
+    assert ops.wo_linear_status() == 0
 
 
 @pytest.mark.parametrize("bits", [8, 4])
