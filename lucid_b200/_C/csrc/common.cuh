@@ -1,6 +1,7 @@
 // Shared host/device helpers for liblucid_cuda (sm_100a only).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -15,6 +16,13 @@ void set_error(const char* fmt, ...);
 int32_t fail(int32_t code, const char* fmt, ...);
 int32_t check_launch(const char* what);
 int sm_count();  // SM count of the current device (cached per device)
+
+// 2-D tiled TMA descriptor: `inner` x `rows` elements of `dtype`, rows `stride_bytes` apart, box
+// `box_inner` x `box_rows`, out-of-bounds elements read as zero.  The driver entry point is
+// looked up through the runtime, so the library does not link against libcuda.
+int32_t encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner,
+                             uint64_t rows, uint64_t stride_bytes, uint32_t box_inner, uint32_t box_rows,
+                             CUtensorMapSwizzle swizzle);
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

@@ -724,42 +724,13 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 // ---- host side ---------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, []() {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
-            cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    else
-      cudaGetLastError();
-  });
-  return fn;
-}
-
 // 2-D uint8 tensor [rows, K] with row stride ld, box = 128 bytes x box_rows, 128B swizzle,
 // out-of-bounds elements read as zero (so M, N and K tails need no special code).
 static int32_t make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld,
                         int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fail(LC_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(LC_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-  return LC_OK;
+  return encode_tensor_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, base, static_cast<uint64_t>(K),
+                              static_cast<uint64_t>(rows), static_cast<uint64_t>(ld), BK,
+                              static_cast<uint32_t>(box_rows), CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 static int32_t ensure_smem_attr() {

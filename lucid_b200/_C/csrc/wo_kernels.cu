@@ -193,10 +193,11 @@ wo_linear_mma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx
 }
 
 // ---- ring variant for weight matrices that do not fit the caches ------------------------
-// A persistent CTA owns `tiles_per_cta` consecutive 16-row tiles.  A producer warp streams
-// their weights (and, per K chunk, the activations) into shared memory with 1-D bulk copies
-// (cp.async.bulk, one per row of a 16 x 1024-byte item), so ~150 KB of loads are in flight
-// per SM without living in registers.  16 consumer warps split every item along K (warp w
+// A persistent CTA owns `tiles_per_cta` consecutive 16-row tiles.  A producer thread streams
+// their weights (and, per K chunk, the activations) into shared memory with tiled TMA loads
+// (one 16-row x 1024-byte box per item; per-row 1-D bulk copies were tried first and are
+// limited by the copy engine's per-request cost), so ~150 KB of loads are in flight per SM
+// without living in registers.  Rows and columns outside the matrix are zero-filled by TMA.  16 consumer warps split every item along K (warp w
 // takes bytes [64w, 64w+64) of each row), widen the int8 weights to the activation type and
 // feed mma.sync m16n8k16 with fp32 accumulation.  Row tiles are processed in passes of at
 // most TMAX tiles so the per-warp partial sums stay in registers; each pass runs over all of
@@ -209,9 +210,10 @@ constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kSmemBudget = 225 * 1024;
 constexpr int KC = 1024;               // bytes of K per item (and per activation chunk)
-constexpr int W_PITCH = KC + 64;       // row pitch: LDS.128 of rows g and g+1 hit disjoint banks
-constexpr int STAGE = 16 * W_PITCH;    // 17408
-constexpr int X_PITCH = KC * 2 + 16;   // activation row pitch (16-bit elements), same reason
+constexpr int W_PITCH = KC;            // dense TMA box rows (the 2-way bank conflict of the two
+                                       // 16-byte loads per item is not measurable)
+constexpr int STAGE = 16 * W_PITCH;    // 16384
+constexpr int X_PITCH = KC * 2;        // activation row pitch (16-bit elements)
 constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 2 GHz
 __host__ __device__ constexpr int red_bytes(int nt) { return kConsumerWarps * 16 * (nt * 8 + 1) * 4; }
 __host__ __device__ constexpr int x_bytes(int nt) { return 2 * nt * 8 * X_PITCH; }
@@ -246,10 +248,11 @@ __device__ __forceinline__ void wo_mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void wo_mbar_expect(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void wo_bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
+__device__ __forceinline__ void wo_tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
 }
 __device__ __forceinline__ uint4 wo_lds128(uint32_t addr) {
   uint4 v;
@@ -287,10 +290,9 @@ __device__ __forceinline__ void widen_word<__nv_bfloat16>(uint32_t u, uint32_t& 
 
 template <typename XT, int NT, int TMAX>
 __global__ void __launch_bounds__(ring::kThreads, 1)
-wo_linear_ring_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx,
-                      const int8_t* __restrict__ w, int64_t ldw, int64_t N,
-                      const float* __restrict__ sw, const float* __restrict__ bias,
-                      XT* __restrict__ y, int64_t ldy, int tiles_per_cta) {
+wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                      int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
+                      const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, int tiles_per_cta) {
   using namespace ring;
   constexpr int S = stages(NT);
   constexpr int COLS = NT * 8, RP = COLS + 1;
@@ -328,10 +330,7 @@ wo_linear_ring_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ld
 
   if (warp == kConsumerWarps) {
     // ===================== producer =====================
-    // The whole warp runs this loop: lane 0 arms the barrier, then lane r issues the bulk copy
-    // of row r (a single thread issuing all 16 copies of an item serialises on their issue
-    // latency and cannot keep the ring full).
-    {
+    if (lane == 0) {
       int stage = 0, xi = 0;
       uint32_t phase = 0;
       uint32_t armed_mask = 0, armed_parity = 0, xarmed_mask = 0, xarmed_parity = 0;  // bit per stage
@@ -339,34 +338,27 @@ wo_linear_ring_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ld
       for (int t0 = 0; t0 < my_tiles && ok; t0 += TMAX) {
         const int pass_tiles = my_tiles - t0 < TMAX ? my_tiles - t0 : TMAX;
         for (int kc = 0; kc < num_kc && ok; ++kc, ++xi) {
-          const int64_t k0 = static_cast<int64_t>(kc) * KC;
-          const uint32_t kc_len = static_cast<uint32_t>(K - k0 < KC ? K - k0 : KC);
           const int xb = xi & 1;
           const uint32_t xphase = static_cast<uint32_t>((xi >> 1) & 1);
-          ok = __all_sync(0xffffffffu, wo_mbar_wait(xempty_bar(xb), xphase ^ 1u));
-          if (!ok) {
-            if (lane == 0) atomicCAS(&g_wo_status, 0, 1);
+          if (!wo_mbar_wait(xempty_bar(xb), xphase ^ 1u)) {
+            atomicCAS(&g_wo_status, 0, 1);
+            ok = false;
             break;
           }
-          if (lane == 0) wo_mbar_expect(xfull_bar(xb), static_cast<uint32_t>(nb) * kc_len * 2u);
-          __syncwarp();
-          if (lane < nb)
-            wo_bulk_copy(x_base + (xb * COLS + lane) * X_PITCH, x + lane * ldx + k0, kc_len * 2u, xfull_bar(xb));
+          // activations: [COLS rows x KC elements] box of 8-byte units, rows >= B read as zero
+          wo_mbar_expect(xfull_bar(xb), COLS * X_PITCH);
+          wo_tma_load_2d(x_base + xb * COLS * X_PITCH, &tmap_x, kc * (KC / 4), 0, xfull_bar(xb));
           xarmed_mask |= 1u << xb;
           xarmed_parity = (xarmed_parity & ~(1u << xb)) | (xphase << xb);
           for (int j = 0; j < pass_tiles; ++j) {
-            ok = __all_sync(0xffffffffu, wo_mbar_wait(empty_bar(stage), phase ^ 1u));
-            if (!ok) {
-              if (lane == 0) atomicCAS(&g_wo_status, 0, 1);
+            if (!wo_mbar_wait(empty_bar(stage), phase ^ 1u)) {
+              atomicCAS(&g_wo_status, 0, 1);
+              ok = false;
               break;
             }
-            const int64_t row0 = (tile0 + t0 + j) << 4;
-            const int rows = static_cast<int>(N - row0 < 16 ? N - row0 : 16);
-            if (lane == 0) wo_mbar_expect(full_bar(stage), static_cast<uint32_t>(rows) * kc_len);
-            __syncwarp();
-            if (lane < rows)
-              wo_bulk_copy(base + stage * STAGE + lane * W_PITCH, w + (row0 + lane) * ldw + k0, kc_len,
-                           full_bar(stage));
+            const int row0 = static_cast<int>((tile0 + t0 + j) << 4);
+            wo_mbar_expect(full_bar(stage), STAGE);
+            wo_tma_load_2d(base + stage * STAGE, &tmap_w, kc * (KC / 4), row0, full_bar(stage));
             armed_mask |= 1u << stage;
             armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
             if (++stage == S) {
@@ -680,12 +672,23 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   });
   if (results[dev] != cudaSuccess)
     return fail(LC_ERR_CUDA, "wo_linear_s8: cannot reserve shared memory: %s", cudaGetErrorString(results[dev]));
+  // weights as [N, K/4] 4-byte units (box 256 x 16 = 1024 bytes x 16 rows), activations as
+  // [B, K/4] 8-byte units (box 256 x COLS = 2048 bytes per row)
+  CUtensorMap map_w, map_x;
+  if (int32_t rc = encode_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, w, static_cast<uint64_t>(K / 4),
+                                        static_cast<uint64_t>(N), static_cast<uint64_t>(ldw), ring::KC / 4, 16,
+                                        CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  if (int32_t rc = encode_tensor_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_INT64, x, static_cast<uint64_t>(K / 4),
+                                        static_cast<uint64_t>(B), static_cast<uint64_t>(ldx) * 2, ring::KC / 4,
+                                        NT * 8, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
   // an evenly divided persistent grid: every CTA gets the same number of row tiles
   const int64_t tiles = (N + 15) / 16;
   const int64_t sms = sm_count();
   const int64_t per = (tiles + sms - 1) / sms;
   const unsigned grid = static_cast<unsigned>((tiles + per - 1) / per);
-  kernel<<<grid, ring::kThreads, ring::kSmemBudget, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy,
+  kernel<<<grid, ring::kThreads, ring::kSmemBudget, st>>>(map_w, map_x, B, K, N, sw, bias, y, ldy,
                                                           static_cast<int>(per));
   return check_launch("wo_linear_s8 (ring)");
 }
