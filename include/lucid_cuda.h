@@ -197,6 +197,21 @@ int32_t lc_qlinear_i8_ex(const void* a, int32_t a_unsigned, int64_t lda, const i
                          const float* sw, const float* bias, void* out, int32_t out_dtype,
                          int64_t ldo, int32_t* status, int32_t variant, void* stream);
 
+/* lc_qlinear_i8_ex writing every output tile to n_out (1..8) buffers of identical shape and
+ * leading dimension.  host_outs is a HOST array of device pointers: the first is normally
+ * this GPU's buffer, the others may be peer GPUs' buffers mapped into this process (P2P or
+ * symmetric memory).  With each rank passing `buffer + rank * N` of every rank's full
+ * [M, P*N] result, the column-parallel Linear and the all-gather of its output shards
+ * become one kernel: tiles cross NVLink as plain stores of whole 128-byte row segments
+ * while the tensor cores work on the next tile.  No counterpart in the reference (it has
+ * no multi-device path). */
+int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_t lda, const int8_t* b,
+                            int64_t ldb, int64_t M, int64_t N, int64_t K, const float* sx,
+                            int32_t sx_per_row, const float* zx, const int32_t* wsum,
+                            const float* sw, const float* bias, void* const* host_outs,
+                            int32_t n_out, int32_t out_dtype, int64_t ldo, int32_t* status,
+                            int32_t variant, void* stream);
+
 /* row sums of an int8 matrix as int32 (the zero-point correction term) */
 int32_t lc_rowsum_s8(const int8_t* b, int64_t rows, int64_t cols, int64_t ldb, int32_t* out,
                      void* stream);

@@ -27,16 +27,19 @@ constexpr int BM = 128;          // rows of A per tile  (UMMA M)
 constexpr int BN = 256;          // rows of B per tile  (UMMA N)
 constexpr int BK = 128;          // bytes of K per stage = one 128B swizzle atom
 constexpr int UMMA_K = 32;       // K per tcgen05.mma for 8-bit operands
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
 constexpr int ACC_STAGES = 2;
 constexpr int TMEM_COLS = ACC_STAGES * BN;  // 512 = all of TMEM
 constexpr int A_BYTES = BM * BK;
 constexpr int B_BYTES = BN * BK;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int NUM_THREADS = 192;
-constexpr int EPI_THREADS = 128;
+constexpr int NUM_THREADS = 320;          // TMA warp, MMA warp, 8 epilogue warps
+constexpr int EPI_THREADS = 256;          // two warps per TMEM lane quadrant, alternating 32-column chunks
 constexpr int GROUP_M = 16;      // tile rasterisation: bands of 16 M-tiles share B in L2
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int STG_PITCH = 36;                         // words per staged row: conflict-free 16-byte access
+constexpr int STG_WARP_WORDS = 32 * STG_PITCH;
+constexpr int STG_BYTES = (EPI_THREADS / 32) * STG_WARP_WORDS * 4;  // epilogue transpose buffers
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + STG_BYTES;
 
 constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 2 GHz
 
@@ -50,7 +53,8 @@ struct Params {
   const int32_t* wsum;  // [N] or null
   const float* sw;      // [N] or null
   const float* bias;    // [N] or null
-  void* out;
+  void* outs[8];        // destinations of the output tile (this GPU's buffer first; peers' after)
+  int n_out;
   int out_dtype;
   int64_t ldo;
   int out_vec;          // rows of `out` allow 16-byte stores
@@ -188,70 +192,119 @@ __device__ __forceinline__ void report(int32_t* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
 
-template <typename T>
-__device__ __forceinline__ void store_chunk(const Params& p, int64_t row, int64_t col0, const float* v);
-
-// 32 consecutive outputs of one row
-template <>
-__device__ __forceinline__ void store_chunk<float>(const Params& p, int64_t row, int64_t col0,
-                                                   const float* v) {
-  float* o = static_cast<float*>(p.out) + row * p.ldo + col0;
-  if (p.out_vec && col0 + 32 <= p.N) {
+// One 32-row x 32-column chunk of the accumulator: lane = row computes the 32 outputs,
+// the warp transposes them through shared memory, then stores rows as whole 64/128-byte
+// segments (4 or 8 rows per instruction) to every destination buffer.  Writing whole
+// segments matters most when a destination is another GPU's memory.
+__device__ __forceinline__ void drain_chunk(const Params& p, const uint32_t (&r)[32], int c,
+                                            int64_t row_base, int64_t n0, int lane, float sxr,
+                                            const float* s_sw, const float* s_bias, const int* s_corr,
+                                            uint32_t* stg) {
+  uint32_t* mine = stg + lane * STG_PITCH;
+  const bool has_corr = p.zx != nullptr, has_bias = p.bias != nullptr, has_sw = p.sw != nullptr;
 #pragma unroll
-    for (int j = 0; j < 32; j += 4)
-      *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-  } else {
+  for (int j = 0; j < 32; j += 4) {
+    int a[4] = {static_cast<int>(r[j]), static_cast<int>(r[j + 1]), static_cast<int>(r[j + 2]),
+                static_cast<int>(r[j + 3])};
+    if (has_corr) {
+      const int4 cr = *reinterpret_cast<const int4*>(s_corr + c * 32 + j);
+      a[0] -= cr.x;
+      a[1] -= cr.y;
+      a[2] -= cr.z;
+      a[3] -= cr.w;
+    }
+    uint32_t w[4];
+    if (p.out_dtype == LC_S32) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < p.N) o[j] = v[j];
+      for (int e = 0; e < 4; ++e) w[e] = static_cast<uint32_t>(a[e]);
+    } else {
+      float f[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) f[e] = __fmul_rn(static_cast<float>(a[e]), sxr);
+      if (has_sw) {
+        const float4 sv = *reinterpret_cast<const float4*>(s_sw + c * 32 + j);
+        f[0] = __fmul_rn(f[0], sv.x);
+        f[1] = __fmul_rn(f[1], sv.y);
+        f[2] = __fmul_rn(f[2], sv.z);
+        f[3] = __fmul_rn(f[3], sv.w);
+      }
+      if (has_bias) {
+        const float4 bv = *reinterpret_cast<const float4*>(s_bias + c * 32 + j);
+        f[0] = __fadd_rn(f[0], bv.x);
+        f[1] = __fadd_rn(f[1], bv.y);
+        f[2] = __fadd_rn(f[2], bv.z);
+        f[3] = __fadd_rn(f[3], bv.w);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) w[e] = __float_as_uint(f[e]);
+    }
+    *reinterpret_cast<uint4*>(mine + j) = make_uint4(w[0], w[1], w[2], w[3]);
   }
-}
-template <>
-__device__ __forceinline__ void store_chunk<__nv_bfloat16>(const Params& p, int64_t row,
-                                                           int64_t col0, const float* v) {
-  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + row * p.ldo + col0;
-  if (p.out_vec && col0 + 32 <= p.N) {
+  __syncwarp();
+  const int64_t col0 = n0 + c * 32;
+  if (p.out_dtype == LC_BF16) {
+    const int sub = lane & 3, rr = lane >> 2;  // 4 lanes x 16 bytes per row, 8 rows per pass
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-      __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-      __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-      uint4 w;
-      w.x = *reinterpret_cast<uint32_t*>(&h0);
-      w.y = *reinterpret_cast<uint32_t*>(&h1);
-      w.z = *reinterpret_cast<uint32_t*>(&h2);
-      w.w = *reinterpret_cast<uint32_t*>(&h3);
-      *reinterpret_cast<uint4*>(o + j) = w;
+    for (int i = 0; i < 4; ++i) {
+      const int rloc = i * 8 + rr;
+      const int64_t row = row_base + rloc, col = col0 + sub * 8;
+      const float4 lo = *reinterpret_cast<const float4*>(stg + rloc * STG_PITCH + sub * 8);
+      const float4 hi = *reinterpret_cast<const float4*>(stg + rloc * STG_PITCH + sub * 8 + 4);
+      if (row < p.M && col < p.N) {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(lo.x, lo.y), h1 = __floats2bfloat162_rn(lo.z, lo.w);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(hi.x, hi.y), h3 = __floats2bfloat162_rn(hi.z, hi.w);
+        uint4 w;
+        w.x = *reinterpret_cast<uint32_t*>(&h0);
+        w.y = *reinterpret_cast<uint32_t*>(&h1);
+        w.z = *reinterpret_cast<uint32_t*>(&h2);
+        w.w = *reinterpret_cast<uint32_t*>(&h3);
+        for (int d = 0; d < p.n_out; ++d) {
+          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.outs[d]) + row * p.ldo + col;
+          if (p.out_vec && col + 8 <= p.N) {
+            *reinterpret_cast<uint4*>(o) = w;
+          } else {
+            const __nv_bfloat16* hv = reinterpret_cast<const __nv_bfloat16*>(&w);
+            for (int e = 0; e < 8; ++e)
+              if (col + e < p.N) o[e] = hv[e];
+          }
+        }
+      }
     }
   } else {
+    const int sub = lane & 7, rr = lane >> 3;  // 8 lanes x 16 bytes per row, 4 rows per pass
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+    for (int i = 0; i < 8; ++i) {
+      const int rloc = i * 4 + rr;
+      const int64_t row = row_base + rloc, col = col0 + sub * 4;
+      const uint4 w = *reinterpret_cast<const uint4*>(stg + rloc * STG_PITCH + sub * 4);
+      if (row < p.M && col < p.N) {
+        if (p.n_out == 1 && p.out_vec && col + 4 <= p.N) {
+          *reinterpret_cast<uint4*>(static_cast<uint32_t*>(p.outs[0]) + row * p.ldo + col) = w;
+          continue;
+        }
+        for (int d = 0; d < p.n_out; ++d) {
+          uint32_t* o = static_cast<uint32_t*>(p.outs[d]) + row * p.ldo + col;
+          if (p.out_vec && col + 4 <= p.N) {
+            *reinterpret_cast<uint4*>(o) = w;
+          } else {
+            const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+            for (int e = 0; e < 4; ++e)
+              if (col + e < p.N) o[e] = wv[e];
+          }
+        }
+      }
+    }
   }
-}
-
-__device__ __forceinline__ void store_chunk_s32(const Params& p, int64_t row, int64_t col0,
-                                                const int* v) {
-  int32_t* o = static_cast<int32_t*>(p.out) + row * p.ldo + col0;
-  if (p.out_vec && col0 + 32 <= p.N) {
-#pragma unroll
-    for (int j = 0; j < 32; j += 4)
-      *reinterpret_cast<int4*>(o + j) = make_int4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col0 + j < p.N) o[j] = v[j];
-  }
+  __syncwarp();
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const Params p, const uint32_t idesc) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ float s_sw[BN];
-  __shared__ float s_bias[BN];
-  __shared__ int s_corr[BN];
+  __shared__ __align__(16) float s_sw[BN];
+  __shared__ __align__(16) float s_bias[BN];
+  __shared__ __align__(16) int s_corr[BN];
   __shared__ uint32_t s_tmem_base;
 
   const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -371,7 +424,9 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // ===================== epilogue (warps 2..5) =====================
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
-    const int et = threadIdx.x - 64;        // 0..127
+    const int et = threadIdx.x - 64;        // 0..255
+    uint32_t* stg = reinterpret_cast<uint32_t*>(smem_raw + (bar_base + 256u - smem_u32(smem_raw))) +
+                    (warp - 2) * STG_WARP_WORDS;
     const float sx_scalar = (p.sx && !p.sx_per_row) ? __ldg(p.sx) : 1.0f;
     const int zx_i = p.zx ? __float2int_rn(__ldg(p.zx)) : 0;
     int64_t it = 0;
@@ -402,31 +457,12 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(as * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = (warp - 2) >> 2; c < BN / 32; c += 2) {
         uint32_t r[32];
         tc_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
         tc_wait_ld();
-        const int64_t col0 = n0 + c * 32;
-        if (row_ok && col0 < p.N) {
-          if (p.out_dtype == LC_S32) {
-            int v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = static_cast<int>(r[j]) - s_corr[c * 32 + j];
-            store_chunk_s32(p, row, col0, v);
-          } else {
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int a = static_cast<int>(r[j]) - s_corr[c * 32 + j];
-              const float f = __fmul_rn(__fmul_rn(static_cast<float>(a), sxr), s_sw[c * 32 + j]);
-              v[j] = __fadd_rn(f, s_bias[c * 32 + j]);
-            }
-            if (p.out_dtype == LC_F32)
-              store_chunk<float>(p, row, col0, v);
-            else
-              store_chunk<__nv_bfloat16>(p, row, col0, v);
-          }
-        }
+        if (n0 + c * 32 < p.N)
+          drain_chunk(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
       }
       tc_fence_before();
       __syncwarp();
@@ -459,11 +495,11 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
 // =============================================================================================
 namespace pair {
 constexpr int BNH = BN / 2;                 // rows of B each CTA loads
-constexpr int STAGES2 = 6;
+constexpr int STAGES2 = 5;
 constexpr int A_BYTES2 = BM * BK;           // 16 KB
 constexpr int B_BYTES2 = BNH * BK;          // 16 KB
 constexpr int STAGE_BYTES2 = A_BYTES2 + B_BYTES2;
-constexpr int SMEM_BYTES2 = STAGES2 * STAGE_BYTES2 + 1024 + 256;
+constexpr int SMEM_BYTES2 = STAGES2 * STAGE_BYTES2 + 1024 + 256 + STG_BYTES;
 }  // namespace pair
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -519,9 +555,9 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b, const Params p, const uint32_t idesc) {
   using namespace pair;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ float s_sw[BN];
-  __shared__ float s_bias[BN];
-  __shared__ int s_corr[BN];
+  __shared__ __align__(16) float s_sw[BN];
+  __shared__ __align__(16) float s_bias[BN];
+  __shared__ __align__(16) int s_corr[BN];
   __shared__ uint32_t s_tmem_base;
 
   const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -651,6 +687,8 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ===================== epilogue (warps 2..5, both CTAs) =====================
     const int q = warp & 3;
     const int et = threadIdx.x - 64;
+    uint32_t* stg = reinterpret_cast<uint32_t*>(smem_raw + (bar_base + 256u - smem_u32(smem_raw))) +
+                    (warp - 2) * STG_WARP_WORDS;
     const float sx_scalar = (p.sx && !p.sx_per_row) ? __ldg(p.sx) : 1.0f;
     const int zx_i = p.zx ? __float2int_rn(__ldg(p.zx)) : 0;
     int64_t it = 0;
@@ -679,31 +717,12 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(as * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = (warp - 2) >> 2; c < BN / 32; c += 2) {
         uint32_t r[32];
         tc_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
         tc_wait_ld();
-        const int64_t col0 = n0 + c * 32;
-        if (row_ok && col0 < p.N) {
-          if (p.out_dtype == LC_S32) {
-            int v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = static_cast<int>(r[j]) - s_corr[c * 32 + j];
-            store_chunk_s32(p, row, col0, v);
-          } else {
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int a = static_cast<int>(r[j]) - s_corr[c * 32 + j];
-              const float f = __fmul_rn(__fmul_rn(static_cast<float>(a), sxr), s_sw[c * 32 + j]);
-              v[j] = __fadd_rn(f, s_bias[c * 32 + j]);
-            }
-            if (p.out_dtype == LC_F32)
-              store_chunk<float>(p, row, col0, v);
-            else
-              store_chunk<__nv_bfloat16>(p, row, col0, v);
-          }
-        }
+        if (n0 + c * 32 < p.N)
+          drain_chunk(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
       }
       tc_fence_before();
       __syncwarp();
@@ -772,7 +791,23 @@ extern "C" int32_t lc_qlinear_i8_ex(const void* a, int32_t a_unsigned, int64_t l
                                     int32_t sx_per_row, const float* zx, const int32_t* wsum,
                                     const float* sw, const float* bias, void* out, int32_t out_dtype,
                                     int64_t ldo, int32_t* status, int32_t variant, void* stream) {
+  void* outs[1] = {out};
+  return lc_qlinear_i8_multi(a, a_unsigned, lda, b, ldb, M, N, K, sx, sx_per_row, zx, wsum, sw, bias, outs, 1,
+                             out_dtype, ldo, status, variant, stream);
+}
+
+extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_t lda, const int8_t* b,
+                                       int64_t ldb, int64_t M, int64_t N, int64_t K, const float* sx,
+                                       int32_t sx_per_row, const float* zx, const int32_t* wsum,
+                                       const float* sw, const float* bias, void* const* host_outs,
+                                       int32_t n_out, int32_t out_dtype, int64_t ldo, int32_t* status,
+                                       int32_t variant, void* stream) {
   using namespace lc::gemm;
+  if (!host_outs || n_out < 1 || n_out > 8)
+    return fail(LC_ERR_INVALID_ARG, "qlinear_i8: between 1 and 8 output buffers are required");
+  void* out = host_outs[0];
+  for (int i = 0; i < n_out; ++i)
+    if (!host_outs[i]) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: null output buffer %d", i);
   if (variant < 0 || variant > 2) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: variant must be 0, 1 or 2");
   if (M < 0 || N < 0 || K <= 0) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: bad shape");
   if (M == 0 || N == 0) return LC_OK;
@@ -807,11 +842,14 @@ extern "C" int32_t lc_qlinear_i8_ex(const void* a, int32_t a_unsigned, int64_t l
   p.wsum = wsum;
   p.sw = sw;
   p.bias = bias;
-  p.out = out;
+  for (int i = 0; i < 8; ++i) p.outs[i] = i < n_out ? host_outs[i] : nullptr;
+  p.n_out = n_out;
   p.out_dtype = out_dtype;
   p.ldo = ldo;
   const size_t esz = (out_dtype == LC_BF16) ? 2 : 4;
-  p.out_vec = (aligned(out, 16) && (ldo * esz) % 16 == 0) ? 1 : 0;
+  p.out_vec = ((ldo * esz) % 16 == 0) ? 1 : 0;
+  for (int i = 0; i < n_out; ++i)
+    if (!aligned(host_outs[i], 16)) p.out_vec = 0;
   p.status = status;
 
   const int64_t sms = sm_count();

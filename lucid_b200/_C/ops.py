@@ -322,6 +322,33 @@ def qlinear_i8(a, b, sx, sw, bias=None, zx=None, wsum=None, out_dtype: torch.dty
     return out
 
 
+def qlinear_i8_into(a, b, sx, sw, out_ptrs, ldo: int, out_dtype: torch.dtype = torch.float32, bias=None, zx=None,
+                    wsum=None, status: torch.Tensor | None = None, variant: int = 0) -> None:
+    """:func:`qlinear_i8` writing each output tile to every buffer in ``out_ptrs`` (1..8 raw
+    device addresses, row pitch ``ldo`` elements): the caller's own buffer and, for a
+    column-parallel Linear, the same column slice of every peer GPU's result buffer, so the
+    all-gather of the shards happens inside the GEMM's epilogue."""
+    import ctypes
+
+    dev = _need_cuda(a, b, sx, sw, bias, zx, wsum, status)
+    M, K = a.shape
+    N = b.shape[0]
+    per_row = 0
+    if sx is not None:
+        sx = _f32c(sx).reshape(-1)
+        per_row = 1 if (sx.numel() == M and M != 1) else 0
+    sw_c = None if sw is None else _f32c(sw)
+    bias_c = None if bias is None else _f32c(bias)
+    zx_c = None if zx is None else _f32c(zx).reshape(-1)
+    wsum_c = None if wsum is None else wsum.to(torch.int32).contiguous()
+    arr = (ctypes.c_void_p * len(out_ptrs))(*[int(p) for p in out_ptrs])
+    with torch.cuda.device(dev):
+        check(lib.lc_qlinear_i8_multi(a.data_ptr(), int(a.dtype == torch.uint8), a.stride(0), b.data_ptr(),
+                                      b.stride(0), M, N, K, _ptr(sx), per_row, _ptr(zx_c), _ptr(wsum_c),
+                                      _ptr(sw_c), _ptr(bias_c), arr, len(out_ptrs), _lc_dtype(out_dtype),
+                                      int(ldo), _ptr(status), int(variant), _stream(dev)))
+
+
 # ----------------------------------------------------------------------------
 # weight-only paths
 # ----------------------------------------------------------------------------

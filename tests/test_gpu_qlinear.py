@@ -134,3 +134,27 @@ def test_prefill_shape_properties(ops):
     y = ops.qlinear_i8(xq, wq, sx, sw)
     y64 = acc.to(torch.float64) * sx.to(torch.float64)[:, None] * sw.to(torch.float64)[None, :]
     assert torch.allclose(y.to(torch.float64), y64, rtol=RTOL, atol=ATOL)
+
+
+def test_multi_destination_epilogue(ops):
+    """The epilogue can write each tile to several buffers (the fused all-gather form): two
+    column slices of two wider result buffers receive exactly the single-buffer result."""
+    M, N, K = 300, 200, 256
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randint(-128, 128, (M, K), device="cuda", dtype=torch.int8, generator=g)
+    b = torch.randint(-128, 128, (N, K), device="cuda", dtype=torch.int8, generator=g)
+    sx = torch.rand(M, device="cuda", generator=g)
+    sw = torch.rand(N, device="cuda", generator=g)
+    ref = ops.qlinear_i8(a, b, sx, sw)
+    for dtype in (torch.float32, torch.bfloat16, torch.int32):
+        want = ops.qlinear_i8(a, b, sx, sw, out_dtype=dtype) if dtype != torch.int32 else ops.qlinear_i8(
+            a, b, None, None, out_dtype=dtype)
+        full0 = torch.zeros((M, 3 * N), dtype=dtype, device="cuda")
+        full1 = torch.zeros((M, 3 * N), dtype=dtype, device="cuda")
+        esz = full0.element_size()
+        ptrs = [full0.data_ptr() + N * esz, full1.data_ptr() + 2 * N * esz]
+        ops.qlinear_i8_into(a, b, sx if dtype != torch.int32 else None, sw if dtype != torch.int32 else None, ptrs,
+                            3 * N, out_dtype=dtype, variant=2)
+        assert torch.equal(full0[:, N:2 * N], want) and torch.equal(full1[:, 2 * N:], want)
+        assert not full0[:, :N].any() and not full0[:, 2 * N:].any() and not full1[:, :2 * N].any()
+    assert torch.equal(ref, ops.qlinear_i8(a, b, sx, sw, variant=1))
