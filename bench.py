@@ -5,7 +5,8 @@
 Headline workload ("prefill"): the prefill-shaped dynamic int8 Linear, x fp32 [16384, 8192]
 ~N(0,1) quantized per token, W [28672, 8192] ~N(0,0.02) quantized per output channel, int32
 accumulation, fp32 dequantized output; over N GPUs the weight is sharded by output
-columns and the output shards are all-gathered with NCCL.  One step = quantize
+columns and the output shards are exchanged inside the GEMM epilogue by peer stores over
+NVLink (symmetric memory), or with an NCCL all-gather (--gather nccl).  One step = quantize
 activations + GEMM (+ all-gather).  metric: int8 qLinear TOPS = 2*M*N*K / step time,
 whole job.  At N = 1 the line also carries the HBM-bound companions of the metric (the
 [8192, 8192] quantize / dequantize roundtrip and the decode-shaped weight-only MLP) under
@@ -175,6 +176,81 @@ def time_loop(torch, fn, steps: int, warmup: int) -> float:
     return e0.elapsed_time(e1) / steps
 
 
+def graph_time(torch, fn, reps: int = 4, replays: int = 10):
+    """Milliseconds per call of `fn` when `reps` calls are captured in one CUDA graph and the
+    graph is replayed: removes host launch overhead from latency-bound sequences."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(reps):
+                fn()
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = _events(torch)
+    e0.record()
+    for _ in range(replays):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (reps * replays)
+
+
+def encoder_extras(torch, dev, gen) -> dict:
+    """Post-norm transformer encoder (the reference's layer order, nn/modules/transformer.py:300-311)
+    with explicit q/k/v/o Linears so that quantize_dynamic swaps all 36 of them; attention,
+    LayerNorm, GELU and residual adds stay in fp32 torch ops."""
+    import lucid_b200.quantization as Q
+    from lucid_b200.nn.quantized.dynamic import Linear as DynLinear
+
+    nn, F = torch.nn, torch.nn.functional
+    D, H, FF, L, B, S = 512, 8, 2048, 6, 32, 256
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q, self.k, self.v, self.o = (nn.Linear(D, D) for _ in range(4))
+            self.linear1, self.linear2 = nn.Linear(D, FF), nn.Linear(FF, D)
+            self.norm1, self.norm2 = nn.LayerNorm(D), nn.LayerNorm(D)
+
+        def forward(self, x):
+            b, s, _ = x.shape
+            q, k, v = (m(x).view(b, s, H, D // H).transpose(1, 2) for m in (self.q, self.k, self.v))
+            a = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, s, D)
+            x = self.norm1(x + self.o(a))
+            return self.norm2(x + self.linear2(F.gelu(self.linear1(x))))
+
+    model = nn.Sequential(*[Layer() for _ in range(L)]).to(dev).eval()
+    with torch.no_grad():
+        for m in model.modules():
+            if isinstance(m, nn.Linear):
+                m.weight.normal_(0.0, 0.02, generator=gen)
+                m.bias.zero_()
+    x = torch.randn(B, S, D, device=dev, generator=gen)
+    qmodel = Q.quantize_dynamic(model)
+    n_swapped = sum(isinstance(m, DynLinear) for m in qmodel.modules())
+    res = {"quantized_linears": n_swapped, "tokens_per_forward": B * S,
+           "linear_int8_GOP": 2 * B * S * (4 * D * D + 2 * D * FF) * L / 1e9}
+    with torch.no_grad():
+        ref = model(x)
+        got = qmodel(x)
+        res["mean_rel_err_vs_float"] = float((got - ref).abs().mean() / ref.abs().mean())
+        for name, mod in (("int8_dynamic", qmodel), ("float32_torch", model)):
+            ms = time_loop(torch, lambda: mod(x), 10, 3)
+            res[name] = {"eager_ms": ms, "eager_tokens_per_s": B * S / ms * 1e3}
+            try:
+                gms = graph_time(torch, lambda: mod(x), reps=2, replays=10)
+                res[name].update({"graph_ms": gms, "graph_tokens_per_s": B * S / gms * 1e3})
+            except Exception as e:
+                res[name]["graph_error"] = repr(e)[:200]
+    return res
+
+
 def extras_single_gpu(torch, ops, peaks) -> dict:
     """HBM-bound companions of the metric, measured on one GPU after the headline run."""
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -227,12 +303,23 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
             h = torch.nn.functional.silu(gate) * up
             return ops.wo_linear_s8(h, wd, sd)
 
-        ms = time_loop(torch, mlp_step, 60, 6)
         nbytes = 3 * H * F + (2 * F + H) * 4
-        dec[f"batch_{batch}"] = {"us": ms * 1e3, "GB/s": nbytes / ms / 1e6, "algorithmic_bytes": nbytes,
-                                 "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}
+        eager_ms = time_loop(torch, mlp_step, 60, 6)
+        entry = {"eager_us": eager_ms * 1e3, "algorithmic_bytes": nbytes}
+        try:  # one MLP = 3 kernels + 2 elementwise ops of ~10 us each: host launch cost matters
+            ms = graph_time(torch, mlp_step, reps=6, replays=10)
+            entry["timing"] = "CUDA graph of 6 MLPs over 3 rotating weight sets"
+        except Exception as e:
+            ms, entry["graph_error"] = eager_ms, repr(e)[:200]
+        entry.update({"us": ms * 1e3, "GB/s": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm})
+        dec[f"batch_{batch}"] = entry
     out["decode_mlp_4096x14336_w8a16"] = dec
     del sets
+    # ---- small transformer encoder, every Linear dynamic int8 (6 layers, d 512, 8 heads, FFN 2048)
+    try:
+        out["encoder_6x512_b32_s256"] = encoder_extras(torch, dev, g)
+    except Exception as e:  # reported, never hidden
+        out["encoder_6x512_b32_s256"] = {"error": repr(e)[:300]}
     # ---- the single dynamic Linear (x [64,1024], W [4096,1024]) through the module API
     try:
         import lucid_b200.quantization as Q
@@ -332,7 +419,29 @@ def run_ours(args) -> int:
     torch.cuda.empty_cache()
     wq, _ = qlin._cache.get(qlin.weight_int8)
     sw = qlin.weight_scale
-    gathered = torch.empty((world, M, n_local), dtype=torch.float32, device=dev) if world > 1 else None
+    # ---- output exchange at N > 1 ------------------------------------------------------
+    # "fused": every rank's GEMM epilogue stores its column slice straight into every rank's
+    # [M, N] result (peer stores over NVLink through symmetric memory), so the all-gather is
+    # part of the kernel; "nccl": local shard + ncclAllGather, the plain baseline.
+    gathered = None
+    gather_mode, gather_note, out_ptrs, symm_hdl, full = "none", "", None, None, None
+    if world > 1:
+        gather_mode = args.gather
+        if gather_mode in ("auto", "fused"):
+            try:
+                import torch.distributed._symmetric_memory as symm
+
+                full = symm.empty((M, N), dtype=torch.float32, device=dev)
+                symm_hdl = symm.rendezvous(full, dist.group.WORLD)
+                order = [(rank + i) % world for i in range(world)]  # own buffer first, peers rotated
+                out_ptrs = [int(symm_hdl.buffer_ptrs[r]) + rank * n_local * 4 for r in order]
+                gather_mode = "fused"
+            except Exception as e:  # reported in the JSON line, never silent
+                if args.gather == "fused":
+                    raise
+                gather_mode, gather_note = "nccl", f"symmetric memory unavailable: {repr(e)[:120]}"
+        if gather_mode == "nccl":
+            gathered = torch.empty((world, M, n_local), dtype=torch.float32, device=dev)
 
     gemm_ms = []
 
@@ -341,11 +450,17 @@ def run_ours(args) -> int:
         if record:
             a, b = _events(torch)
             a.record()
-        y = ops.qlinear_i8(xq, wq, sx, sw)
+        if gather_mode == "fused":
+            ops.qlinear_i8_into(xq, wq, sx, sw, out_ptrs, N)
+            y = full
+        else:
+            y = ops.qlinear_i8(xq, wq, sx, sw)
         if record:
             b.record()
             gemm_ms.append((a, b))
-        if world > 1:
+        if gather_mode == "fused":
+            symm_hdl.barrier()  # every rank's slices have landed in this rank's result
+        elif gather_mode == "nccl":
             dist.all_gather_into_tensor(gathered.view(-1), y.view(-1))
         return y
 
@@ -372,6 +487,35 @@ def run_ours(args) -> int:
     gemm_avg_ms = sum(a.elapsed_time(b) for a, b in gemm_ms) / len(gemm_ms)
     value = 2.0 * M * N * K / ms_per_step / 1e9
 
+    # ---- N > 1: check the exchange, and time the GEMM phase without it ------------------
+    exchange_verified, gemm_only_ms = None, None
+    cp_module = None
+    if world > 1:
+        from lucid_b200.nn.quantized.column_parallel import ColumnParallelLinear
+
+        xq, sx, _ = ops.dynamic_quantize_rows(x, True, -128, 127, True, 1e-8, torch.int8, pad_rows_to_16=True)
+        y_local = ops.qlinear_i8(xq, wq, sx, sw)
+        result = step()
+        sync_all()
+        if gather_mode == "fused":
+            mine = result[:, rank * n_local:(rank + 1) * n_local]
+            whole = result
+        else:
+            mine = gathered[rank]
+            whole = gathered
+        ok_local = bool(torch.equal(mine, y_local))
+        checksum = whole.view(torch.int32).sum(dtype=torch.int64).reshape(1)
+        sums = [torch.zeros_like(checksum) for _ in range(world)]
+        dist.all_gather(sums, checksum)
+        flags = torch.tensor([int(ok_local)], device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        exchange_verified = bool(flags.item()) and all(int(v) == int(sums[0]) for v in sums)
+        t = torch.tensor([time_loop(torch, lambda: ops.qlinear_i8(xq, wq, sx, sw), 5, 2)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gemm_only_ms = float(t.item())
+        del y_local
+        cp_module = ColumnParallelLinear(qlin, N, gather="fused" if gather_mode == "fused" else "nccl")
+
     # ---- end to end through the module API with host buffers --------------------------
     x_host = x.cpu().pin_memory()
     y_host = torch.empty((M, N), dtype=torch.float32).pin_memory() if rank == 0 else None
@@ -379,12 +523,8 @@ def run_ours(args) -> int:
 
     def e2e_step():
         x_dev.copy_(x_host, non_blocking=True)
-        y = qlin(x_dev)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered.view(-1), y.contiguous().view(-1))
-            if rank == 0:
-                y_host.view(M, world, n_local).copy_(gathered.permute(1, 0, 2), non_blocking=True)
-        elif rank == 0:
+        y = qlin(x_dev) if world == 1 else cp_module(x_dev)
+        if rank == 0:
             y_host.copy_(y, non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 10))
@@ -413,7 +553,10 @@ def run_ours(args) -> int:
             "config": {"workload": "prefill_qlinear_16384x28672x8192_per_token_int8", "M": M, "N": N, "K": K,
                        "activation_quant": "dynamic per-token symmetric int8 (absmax/127.5, [-128,127])",
                        "weight_quant": "per-output-channel symmetric int8", "output": "fp32",
-                       "parallelism": f"column-parallel x{world}" + (" + NCCL all-gather" if world > 1 else ""),
+                       "parallelism": f"column-parallel x{world}" + (
+                           "" if world == 1 else " + all-gather fused into the GEMM epilogue (peer stores)"
+                           if gather_mode == "fused" else " + NCCL all-gather"),
+                       "gather": gather_mode, "gather_note": gather_note,
                        "l2": "inputs exceed L2 (x 537 MB, W 235 MB, y 1879 MB vs 126 MB)"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
                          "frac": achieved / int8_peak, "traffic": None,
@@ -423,8 +566,18 @@ def run_ours(args) -> int:
                          "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS},
             "e2e": {"value": 2.0 * M * N * K / e2e_ms_per_step / 1e9, "unit": "TOPS",
                     "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4,
-                    "ms_per_step": e2e_ms_per_step, "api": "lucid_b200.nn.quantized.dynamic.Linear.forward"},
+                    "ms_per_step": e2e_ms_per_step, "api": "lucid_b200.nn.quantized.dynamic.Linear.forward" if world == 1 else
+                           "lucid_b200.nn.quantized.column_parallel.ColumnParallelLinear.forward"},
             "gpu_launches": args.steps * 2,
+            "exchange": None if world == 1 else {
+                "mode": gather_mode, "bytes_out_per_gpu": (world - 1) * M * n_local * 4,
+                "GB/s_out_per_gpu_during_gemm_kernel": (world - 1) * M * n_local * 4 / gemm_avg_ms / 1e6,
+                "nvlink_peer_copy_peak_GB/s": 770.0, "verified_bit_identical_on_all_ranks": exchange_verified,
+                "gemm_phase_only": {"ms": gemm_only_ms, "aggregate_TOPS": 2.0 * M * N * K / gemm_only_ms / 1e9,
+                                    "note": "same shard GEMM writing only the local buffer (no exchange), max over ranks"},
+                "note": "fused: the GEMM kernel's duration includes the peer stores, so at large N it is "
+                        "bound by NVLink, not by the tensor cores" if gather_mode == "fused" else
+                        "nccl: the exchange runs after the GEMM kernel"},
             "clocks": clocks.summary(),
         }
         if world == 1:
@@ -458,6 +611,8 @@ def main() -> int:
                     help="run a small fixed case of one kernel (gemm, quantize_rows, quantize_tensor, "
                          "dequantize, quantize_given_scale, wo_gemv) for a profiler capture; prints no bench line")
     ap.add_argument("--profile-batch", default=4)
+    ap.add_argument("--gather", choices=("auto", "fused", "nccl"), default="auto",
+                    help="N > 1: how output shards are exchanged (auto = fused if symmetric memory works)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -466,7 +621,8 @@ def main() -> int:
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29531", os.path.abspath(__file__),
-               "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup)]
+               "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup),
+               "--gather", args.gather]
         return subprocess.call(cmd)
     return run_ours(args)
 
