@@ -284,7 +284,7 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
     sets = []
     for i in range(3):  # 3 x 176 MB of weights rotate so that no step finds its weights in L2
         ws = []
-        for (n, k) in ((F, H), (F, H), (H, F)):
+        for (n, k) in ((2 * F, H), (H, F)):  # gate and up projections stacked into one [2F, H] weight
             w = torch.randn(n, k, device=dev, generator=g) * 0.02
             wq, sw, _ = ops.dynamic_quantize_rows(w, True, -128, 127, True)
             ws.append((wq, sw))
@@ -296,11 +296,10 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
         counter = [0]
 
         def mlp_step():
-            (wg, sg), (wu, su), (wd, sd) = sets[counter[0] % 3]
+            (wgu, sgu), (wd, sd) = sets[counter[0] % 3]
             counter[0] += 1
-            gate = ops.wo_linear_s8(xb, wg, sg)
-            up = ops.wo_linear_s8(xb, wu, su)
-            h = torch.nn.functional.silu(gate) * up
+            gu = ops.wo_linear_s8(xb, wgu, sgu)
+            h = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
             return ops.wo_linear_s8(h, wd, sd)
 
         nbytes = 3 * H * F + (2 * F + H) * 4

@@ -41,14 +41,20 @@ __device__ __forceinline__ uint32_t widen_pair<__half>(uint32_t u, int lo) {
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
-// bf16: 0x4B000000 | byte is 2^23 + byte in fp32; subtracting 2^23 + 128 gives the
-// s8 value exactly, whose upper 16 bits are its bf16 encoding.
+// bf16: the 16-bit pattern 0x00uu read as bf16 is exactly u * 2^-133 for every byte u (codes
+// below 128 are subnormals, codes from 128 up are the smallest normals, and the two ranges
+// join linearly), so two exact packed bf16 operations, x * 2^120 and then fma(x, 2^13, -128),
+// give the signed weight s8 = u - 128 for two weights at once.  One byte-permute per pair
+// runs on the integer pipe; the arithmetic runs on the (twice as wide) FMA pipe.
 template <>
 __device__ __forceinline__ uint32_t widen_pair<__nv_bfloat16>(uint32_t u, int lo) {
-  const uint32_t m = 0x4B000000u;
-  float f0 = __uint_as_float(__byte_perm(u, m, lo == 0 ? 0x7650u : 0x7652u)) - 8388736.0f;
-  float f1 = __uint_as_float(__byte_perm(u, m, lo == 0 ? 0x7651u : 0x7653u)) - 8388736.0f;
-  return __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632u);
+  const uint32_t sel = lo == 0 ? 0x4140u : 0x4342u;  // {0x00, b[lo+1], 0x00, b[lo]}
+  uint32_t d = __byte_perm(u, 0u, sel);
+  const uint32_t two120 = 0x7B807B80u;  // 2^120 in both halves
+  const uint32_t two13 = 0x46004600u;   // 2^13
+  const uint32_t m128 = 0xC300C300u;    // -128
+  asm("mul.rn.bf16x2 %0, %0, %1;\n\tfma.rn.bf16x2 %0, %0, %2, %3;" : "+r"(d) : "r"(two120), "r"(two13), "r"(m128));
+  return d;
 }
 
 template <typename XT>
@@ -215,10 +221,11 @@ constexpr int W_PITCH = KC;            // dense TMA box rows (the 2-way bank con
 constexpr int STAGE = 16 * W_PITCH;    // 16384
 constexpr int X_PITCH = KC * 2;        // activation row pitch (16-bit elements)
 constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 2 GHz
-__host__ __device__ constexpr int red_bytes(int nt) { return kConsumerWarps * 16 * (nt * 8 + 1) * 4; }
+// split-K partials of a whole pass: [tile][warp][16 rows][8*nt + 1]
+__host__ __device__ constexpr int red_bytes(int nt, int tmax) { return tmax * kConsumerWarps * 16 * (nt * 8 + 1) * 4; }
 __host__ __device__ constexpr int x_bytes(int nt) { return 2 * nt * 8 * X_PITCH; }
-__host__ __device__ constexpr int stages(int nt) {
-  return (kSmemBudget - 512 - red_bytes(nt) - x_bytes(nt)) / STAGE;
+__host__ __device__ constexpr int stages(int nt, int tmax) {
+  return (kSmemBudget - 512 - red_bytes(nt, tmax) - x_bytes(nt)) / STAGE;
 }
 }  // namespace ring
 
@@ -229,7 +236,7 @@ __device__ __forceinline__ uint32_t wo_smem_u32(const void* p) {
 }
 __device__ __forceinline__ bool wo_mbar_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-  const long long t0 = clock64();
+  long long t0 = 0;  // the clock is only read once a first attempt has failed
   for (;;) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -239,7 +246,10 @@ __device__ __forceinline__ bool wo_mbar_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     if (ok) return true;
-    if (clock64() - t0 > ring::kWaitCycles) return false;
+    if (t0 == 0)
+      t0 = clock64();
+    else if (clock64() - t0 > ring::kWaitCycles)
+      return false;
   }
 }
 __device__ __forceinline__ void wo_mbar_arrive(uint32_t bar) {
@@ -266,41 +276,20 @@ __device__ __forceinline__ void widen_word(uint32_t u, uint32_t& p01, uint32_t& 
   p01 = widen_pair<XT>(u, 0);
   p23 = widen_pair<XT>(u, 2);
 }
-// bf16: the four fp32 subtractions are issued as two packed f32x2 adds
-template <>
-__device__ __forceinline__ void widen_word<__nv_bfloat16>(uint32_t u, uint32_t& p01, uint32_t& p23) {
-  const uint32_t m = 0x4B000000u;
-  const uint32_t f0 = __byte_perm(u, m, 0x7650u), f1 = __byte_perm(u, m, 0x7651u);
-  const uint32_t f2 = __byte_perm(u, m, 0x7652u), f3 = __byte_perm(u, m, 0x7653u);
-  const uint32_t neg = 0xCB000080u;  // -(2^23 + 128)
-  uint32_t a0, a1, a2, a3;
-  asm("{\n\t.reg .b64 x, y, n;\n\t"
-      "mov.b64 x, {%4, %5};\n\t"
-      "mov.b64 y, {%6, %7};\n\t"
-      "mov.b64 n, {%8, %8};\n\t"
-      "add.rn.f32x2 x, x, n;\n\t"
-      "add.rn.f32x2 y, y, n;\n\t"
-      "mov.b64 {%0, %1}, x;\n\t"
-      "mov.b64 {%2, %3}, y;\n\t}"
-      : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
-      : "r"(f0), "r"(f1), "r"(f2), "r"(f3), "r"(neg));
-  p01 = __byte_perm(a0, a1, 0x7632u);
-  p23 = __byte_perm(a2, a3, 0x7632u);
-}
-
 template <typename XT, int NT, int TMAX>
 __global__ void __launch_bounds__(ring::kThreads, 1)
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
                       const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, int tiles_per_cta) {
   using namespace ring;
-  constexpr int S = stages(NT);
+  constexpr int S = stages(NT, TMAX);
+  static_assert(S >= 3, "ring too shallow");
   constexpr int COLS = NT * 8, RP = COLS + 1;
   extern __shared__ uint8_t wo_smem_raw[];
   const uint32_t base = (wo_smem_u32(wo_smem_raw) + 127u) & ~127u;
   const uint32_t x_base = base + S * STAGE;
   const uint32_t red_base = x_base + x_bytes(NT);
-  const uint32_t bar_base = red_base + red_bytes(NT);
+  const uint32_t bar_base = red_base + red_bytes(NT, TMAX);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
   auto xfull_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
@@ -457,10 +446,13 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       }
 
       // ---- split-K reduction of this pass across the 16 consumer warps ----
+      // every warp parks its partial sums of all tiles of the pass, one barrier, then the
+      // 512 threads add the 16 partials of each output in a fixed order (deterministic)
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");  // previous pass fully summed
 #pragma unroll
       for (int j = 0; j < TMAX; ++j) {
         if (j < pass_tiles) {
-          float* mine = red + warp * 16 * RP;
+          float* mine = red + (j * kConsumerWarps + warp) * 16 * RP;
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             mine[g * RP + nt * 8 + 2 * t] = acc[j][nt][0];
@@ -468,21 +460,20 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
             mine[(g + 8) * RP + nt * 8 + 2 * t] = acc[j][nt][2];
             mine[(g + 8) * RP + nt * 8 + 2 * t + 1] = acc[j][nt][3];
           }
-          asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-          const int64_t row0 = (tile0 + t0 + j) << 4;
-          for (int o = threadIdx.x; o < 16 * COLS; o += kConsumerThreads) {
-            const int r = o & 15, bcol = o >> 4;
-            const int64_t n = row0 + r;
-            if (n < N && bcol < nb) {
-              float sum = 0.0f;
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+      for (int o = threadIdx.x; o < pass_tiles * 16 * COLS; o += kConsumerThreads) {
+        const int r = o & 15, bcol = (o >> 4) % COLS, j = (o >> 4) / COLS;
+        const int64_t n = ((tile0 + t0 + j) << 4) + r;
+        if (n < N && bcol < nb) {
+          const float* src = red + j * kConsumerWarps * 16 * RP + r * RP + bcol;
+          float sum = 0.0f;
 #pragma unroll
-              for (int wp = 0; wp < kConsumerWarps; ++wp) sum += red[wp * 16 * RP + r * RP + bcol];
-              float v = sum * (sw ? __ldg(sw + n) : 1.0f);
-              if (bias) v += __ldg(bias + n);
-              y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(v);
-            }
-          }
-          asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+          for (int wp = 0; wp < kConsumerWarps; ++wp) sum += src[wp * 16 * RP];
+          float v = sum * (sw ? __ldg(sw + n) : 1.0f);
+          if (bias) v += __ldg(bias + n);
+          y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(v);
         }
       }
     }
@@ -699,7 +690,7 @@ static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
                              cudaStream_t st) {
   if (B <= 8) return launch_wo_ring_inst<XT, 1, 8>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
   if (B <= 16) return launch_wo_ring_inst<XT, 2, 4>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
-  return launch_wo_ring_inst<XT, 4, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+  return launch_wo_ring_inst<XT, 4, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
 }
 
 template <typename XT>

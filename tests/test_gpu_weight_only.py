@@ -123,3 +123,21 @@ def test_group_matmul_bench_width(ops):
             expected = x.double() @ dense.double().T
             actual = ops.group_matmul(x, p, s, b, 64, bits).double()
             assert float((expected - actual).abs().max()) / max(float(expected.abs().max()), 1e-12) <= 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("N,K", [(256, 256), (4096, 1024)])
+def test_int8_widening_is_exact_for_every_code(ops, dtype, N, K):
+    """One-hot activations pick single weights: with unit scales the output must be the int8
+    code itself, exactly, for all 256 codes (both kernels: direct-load and ring)."""
+    n = torch.arange(N, device="cuda").view(-1, 1)
+    k = torch.arange(K, device="cuda").view(1, -1)
+    wq = (((n * 7 + k * 3) % 256) - 128).to(torch.int8)
+    assert wq.unique().numel() == 256
+    cols = [0, 1, 63, 64, 255, K - 1, K // 2, 17]
+    x = torch.zeros(len(cols), K, device="cuda", dtype=dtype)
+    for i, c in enumerate(cols):
+        x[i, c] = 1.0
+    y = ops.wo_linear_s8(x, wq, torch.ones(N, device="cuda"))
+    assert torch.equal(y.float(), wq[:, cols].T.float())
+    assert ops.wo_linear_status() == 0
