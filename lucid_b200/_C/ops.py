@@ -48,6 +48,24 @@ def _need_cuda(*tensors: torch.Tensor) -> torch.device:
     return dev
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on(dev: torch.device):
+    """Context that makes ``dev`` current for the launch; free when it already is."""
+    if dev.index is None or dev.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(dev)
+
+
 def _stream(dev: torch.device) -> int:
     return torch.cuda.current_stream(dev).cuda_stream
 
@@ -102,7 +120,7 @@ def observe_tensor(x, min_out, max_out, accumulate: bool, qspec=None):
         scale = torch.empty((), dtype=torch.float32, device=dev)
         zp = torch.empty((), dtype=torch.float32, device=dev)
     ws = observe_workspace(dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_observe_tensor_f32(x.data_ptr(), x.numel(), min_out.data_ptr(), max_out.data_ptr(),
                                         int(accumulate), int(sym), int(qmin), int(qmax), int(signed),
                                         float(eps), _ptr(scale), _ptr(zp), ws.data_ptr(), ws.numel(),
@@ -116,7 +134,7 @@ def observe_channel(x, ch_axis: int, min_out, max_out, accumulate: bool) -> None
     outer, ch, inner = channel_layout(x.shape, ch_axis)
     if min_out.numel() != ch or max_out.numel() != ch:
         raise ValueError(f"running buffers hold {min_out.numel()} channels, input has {ch}")
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_observe_channel_f32(x.data_ptr(), outer, ch, inner, min_out.data_ptr(),
                                          max_out.data_ptr(), int(accumulate), _stream(dev)))
 
@@ -128,7 +146,7 @@ def calculate_qparams(min_t, max_t, symmetric: bool, qmin: int, qmax: int, signe
         mn, mx = torch.broadcast_tensors(mn, mx)
         mn, mx = mn.contiguous(), mx.contiguous()
     scale, zp = torch.empty_like(mn), torch.empty_like(mn)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_calculate_qparams_f32(mn.data_ptr(), mx.data_ptr(), mn.numel(), int(symmetric),
                                            int(qmin), int(qmax), int(signed), float(eps),
                                            scale.data_ptr(), zp.data_ptr(), _stream(dev)))
@@ -171,7 +189,7 @@ def quantize(x, scale, zero_point, qmin: int, qmax: int, storage: torch.dtype, c
     outer, ch, inner = channel_layout(x.shape, ch_axis if per_channel else None)
     s_t, z_t, h_inv, _, h_z = _params(scale, zero_point, dev, ch, per_channel)
     out = torch.empty(x.shape, dtype=storage, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_quantize_f32(x.data_ptr(), outer, ch, inner, _ptr(s_t), 0 if s_t is None else s_t.numel(),
                                   _ptr(z_t), 0 if z_t is None else z_t.numel(), h_inv, h_z, int(qmin),
                                   int(qmax), out.data_ptr(), _lc_dtype(storage), _stream(dev)))
@@ -185,7 +203,7 @@ def dequantize(q, scale, zero_point, ch_axis=None, out_dtype: torch.dtype = torc
     outer, ch, inner = channel_layout(q.shape, ch_axis if per_channel else None)
     s_t, z_t, _, h_s, h_z = _params(scale, zero_point, dev, ch, per_channel)
     out = torch.empty(q.shape, dtype=out_dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_dequantize(q.data_ptr(), _lc_dtype(q.dtype), outer, ch, inner, _ptr(s_t),
                                 0 if s_t is None else s_t.numel(), _ptr(z_t),
                                 0 if z_t is None else z_t.numel(), h_s, h_z, out.data_ptr(),
@@ -201,7 +219,7 @@ def fake_quantize(x, scale, zero_point, qmin: int, qmax: int, ch_axis=None, want
     s_t, z_t, h_inv, h_s, h_z = _params(scale, zero_point, dev, ch, per_channel)
     out = torch.empty_like(x)
     mask = torch.empty_like(x) if want_mask else None
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_fake_quantize_f32(x.data_ptr(), outer, ch, inner, _ptr(s_t),
                                        0 if s_t is None else s_t.numel(), _ptr(z_t),
                                        0 if z_t is None else z_t.numel(), h_inv, h_s, h_z, int(qmin),
@@ -228,7 +246,7 @@ def dynamic_quantize_rows(x2d, symmetric: bool, qmin: int, qmax: int, signed: bo
     store = torch.empty((rows, ldq), dtype=out_dtype, device=dev)
     scale = torch.empty(rows, dtype=torch.float32, device=dev)
     zp = torch.empty(rows, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_dynamic_quantize_rows_f32(x2d.data_ptr(), rows, cols, cols, int(symmetric), int(qmin),
                                                int(qmax), int(signed), float(eps), store.data_ptr(),
                                                _lc_dtype(out_dtype), ldq, scale.data_ptr(), zp.data_ptr(),
@@ -249,7 +267,7 @@ def dynamic_quantize_tensor(x2d, symmetric: bool, qmin: int, qmax: int, signed: 
     zp = torch.empty((), dtype=torch.float32, device=dev)
     minmax = torch.empty(2, dtype=torch.float32, device=dev)
     ws = observe_workspace(dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_dynamic_quantize_tensor_f32(x2d.data_ptr(), rows, cols, cols, int(symmetric), int(qmin),
                                                  int(qmax), int(signed), float(eps), store.data_ptr(),
                                                  _lc_dtype(out_dtype), ldq, scale.data_ptr(), zp.data_ptr(),
@@ -275,7 +293,7 @@ def rowsum_s8(b: torch.Tensor) -> torch.Tensor:
     if b.dtype != torch.int8 or b.dim() != 2 or b.stride(1) != 1:
         raise TypeError("rowsum_s8 expects a 2-D int8 matrix with unit column stride")
     out = torch.empty(b.shape[0], dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_rowsum_s8(b.data_ptr(), b.shape[0], b.shape[1], b.stride(0), out.data_ptr(), _stream(dev)))
     return out
 
@@ -314,7 +332,7 @@ def qlinear_i8(a, b, sx, sw, bias=None, zx=None, wsum=None, out_dtype: torch.dty
     bias_c = None if bias is None else _f32c(bias)
     zx_c = None if zx is None else _f32c(zx).reshape(-1)
     wsum_c = None if wsum is None else wsum.to(torch.int32).contiguous()
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_qlinear_i8_ex(a.data_ptr(), int(a.dtype == torch.uint8), a.stride(0), b.data_ptr(),
                                    b.stride(0), M, N, K, _ptr(sx), per_row, _ptr(zx_c), _ptr(wsum_c),
                                    _ptr(sw_c), _ptr(bias_c), out.data_ptr(), _lc_dtype(out_dtype), N,
@@ -342,7 +360,7 @@ def qlinear_i8_into(a, b, sx, sw, out_ptrs, ldo: int, out_dtype: torch.dtype = t
     zx_c = None if zx is None else _f32c(zx).reshape(-1)
     wsum_c = None if wsum is None else wsum.to(torch.int32).contiguous()
     arr = (ctypes.c_void_p * len(out_ptrs))(*[int(p) for p in out_ptrs])
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_qlinear_i8_multi(a.data_ptr(), int(a.dtype == torch.uint8), a.stride(0), b.data_ptr(),
                                       b.stride(0), M, N, K, _ptr(sx), per_row, _ptr(zx_c), _ptr(wsum_c),
                                       _ptr(sw_c), _ptr(bias_c), arr, len(out_ptrs), _lc_dtype(out_dtype),
@@ -367,7 +385,7 @@ def wo_linear_s8(x2d, wq, sw, bias=None):
     y = torch.empty((B, N), dtype=x2d.dtype, device=dev)
     sw_c = None if sw is None else _f32c(sw)
     bias_c = None if bias is None else _f32c(bias)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_wo_linear_s8(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq.data_ptr(),
                                   wq.stride(0), N, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N, _stream(dev)))
     return y
@@ -394,7 +412,7 @@ def group_quantize(w, group_size: int = 64, bits: int = 8):
     packed = torch.empty((N, K * bits // 32), dtype=torch.int32, device=dev)
     scales = torch.empty((N, K // group_size), dtype=torch.float32, device=dev)
     biases = torch.empty((N, K // group_size), dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_group_quantize_f32(w.data_ptr(), N, K, group_size, bits, packed.data_ptr(),
                                         scales.data_ptr(), biases.data_ptr(), _stream(dev)))
     return packed, scales, biases
@@ -406,7 +424,7 @@ def group_dequantize(packed, scales, biases, group_size: int = 64, bits: int = 8
     N = packed.shape[0]
     K = packed.shape[1] * 32 // bits
     out = torch.empty((N, K), dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_group_dequantize(packed.data_ptr(), _f32c(scales).data_ptr(), _f32c(biases).data_ptr(),
                                       N, K, group_size, bits, out.data_ptr(), _stream(dev)))
     return out
@@ -422,7 +440,7 @@ def group_matmul(x2d, packed, scales, biases, group_size: int = 64, bits: int = 
         raise ValueError("group_matmul: packed weight does not match x's inner dimension")
     y = torch.empty((B, N), dtype=x2d.dtype, device=dev)
     sc, bi = _f32c(scales), _f32c(biases)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.lc_group_matmul(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, packed.data_ptr(), sc.data_ptr(),
                                   bi.data_ptr(), N, group_size, bits, y.data_ptr(), _stream(dev)))
     return y
