@@ -516,13 +516,18 @@ def run_ours(args) -> int:
         cp_module = ColumnParallelLinear(qlin, N, gather="fused" if gather_mode == "fused" else "nccl")
 
     # ---- end to end through the module API with host buffers --------------------------
+    from lucid_b200.nn.quantized.streaming import forward_from_host
+
     x_host = x.cpu().pin_memory()
     y_host = torch.empty((M, N), dtype=torch.float32).pin_memory() if rank == 0 else None
     x_dev = torch.empty_like(x)
 
     def e2e_step():
+        if world == 1:  # chunked: H2D of chunk i+1, layer on chunk i and D2H of chunk i-1 overlap
+            forward_from_host(qlin, x_host, y_host, chunk_rows=2048)
+            return
         x_dev.copy_(x_host, non_blocking=True)
-        y = qlin(x_dev) if world == 1 else cp_module(x_dev)
+        y = cp_module(x_dev)
         if rank == 0:
             y_host.copy_(y, non_blocking=True)
 
@@ -558,14 +563,17 @@ def run_ours(args) -> int:
                        "gather": gather_mode, "gather_note": gather_note,
                        "l2": "inputs exceed L2 (x 537 MB, W 235 MB, y 1879 MB vs 126 MB)"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
-                         "frac": achieved / int8_peak, "traffic": None,
-                         "kernel": "qlinear_i8_kernel", "kernel_ms": gemm_avg_ms,
+                         "frac": achieved / int8_peak,
+                         # dram__bytes_read+write of a 1/16-size launch of the same kernel (same K and tile
+                         # shape: profiles/qlinear_i8_pair_gemm_4096x7168x8192.md) scaled by the ops ratio
+                         "traffic": 3.41e9 if world == 1 else None,
+                         "kernel": "qlinear_i8_pair_kernel", "kernel_ms": gemm_avg_ms,
                          "peak_source": f"2 x bf16_tflops ({peaks['source']}, burst): tcgen05 issues dense int8 at "
                                         "twice the bf16 rate; no int8 figure is measured by the driver",
                          "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS},
             "e2e": {"value": 2.0 * M * N * K / e2e_ms_per_step / 1e9, "unit": "TOPS",
                     "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4,
-                    "ms_per_step": e2e_ms_per_step, "api": "lucid_b200.nn.quantized.dynamic.Linear.forward" if world == 1 else
+                    "ms_per_step": e2e_ms_per_step, "api": "lucid_b200.nn.quantized.streaming.forward_from_host(dynamic.Linear, ...), 2048-row chunks" if world == 1 else
                            "lucid_b200.nn.quantized.column_parallel.ColumnParallelLinear.forward"},
             "gpu_launches": args.steps * 2,
             "exchange": None if world == 1 else {

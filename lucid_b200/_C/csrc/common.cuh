@@ -42,6 +42,32 @@ __device__ __forceinline__ int code_to_int(float c, float qmin, float qmax) {
   return (c != c) ? 0 : __float2int_rn(cl);
 }
 
+// Fast path for grids that coincide with the storage type's own range (qint8 [-128,127] in
+// int8, [0,255] in uint8): the float->int conversion rounds to nearest even and the packing
+// instruction saturates, so clip + cast cost nothing extra; NaN converts to 0 as the
+// reference's cast does.  `t` values are x * inv; with a zero-point the code is rint(t) + z
+// (rounded first, then shifted, as the reference does), which is integral, so converting it
+// again changes nothing.  cvt.pack: d = (c << 16) | (sat(a) << 8) | sat(b).
+template <bool UNSIGNED>
+__device__ __forceinline__ uint32_t pack4_sat(float t0, float t1, float t2, float t3, float z, bool has_z) {
+  if (has_z) {
+    t0 = __fadd_rn(rintf(t0), z);
+    t1 = __fadd_rn(rintf(t1), z);
+    t2 = __fadd_rn(rintf(t2), z);
+    t3 = __fadd_rn(rintf(t3), z);
+  }
+  const int a = __float2int_rn(t0), b = __float2int_rn(t1), c = __float2int_rn(t2), d = __float2int_rn(t3);
+  uint32_t hi, r;
+  if (UNSIGNED) {
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+  } else {
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+  }
+  return r;
+}
+
 // calculate_qparams for one (min, max) pair (lucid/quantization/_qparams.py:186-205).
 // The host fills the constants exactly as the reference's Python does:
 // half = (qmax-qmin)/2.0 and range = qmax-qmin rounded once to fp32,

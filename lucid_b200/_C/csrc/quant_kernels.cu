@@ -243,14 +243,24 @@ quantize_seg_kernel(const float* __restrict__ x, OutT* __restrict__ out, int64_t
       int64_t i = base + (static_cast<int64_t>(u) * kThreads + threadIdx.x) * 4;
       if (i < inner) v[u] = __ldcs(reinterpret_cast<const float4*>(xs + i));
     }
+    constexpr bool kByte = sizeof(OutT) == 1;
+    constexpr bool kUnsigned = static_cast<OutT>(-1) > static_cast<OutT>(0);
+    const bool natural = kByte && (kUnsigned ? (qmin == 0.0f && qmax == 255.0f) : (qmin == -128.0f && qmax == 127.0f));
+    const bool has_z = z != 0.0f;
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       int64_t i = base + (static_cast<int64_t>(u) * kThreads + threadIdx.x) * 4;
       if (i < inner) {
-        store4<OutT>(os + i, code_to_int(grid_code(v[u].x, inv, z), qmin, qmax),
-                     code_to_int(grid_code(v[u].y, inv, z), qmin, qmax),
-                     code_to_int(grid_code(v[u].z, inv, z), qmin, qmax),
-                     code_to_int(grid_code(v[u].w, inv, z), qmin, qmax));
+        if (natural) {
+          *reinterpret_cast<uint32_t*>(os + i) =
+              pack4_sat<kUnsigned>(__fmul_rn(v[u].x, inv), __fmul_rn(v[u].y, inv), __fmul_rn(v[u].z, inv),
+                                   __fmul_rn(v[u].w, inv), z, has_z);
+        } else {
+          store4<OutT>(os + i, code_to_int(grid_code(v[u].x, inv, z), qmin, qmax),
+                       code_to_int(grid_code(v[u].y, inv, z), qmin, qmax),
+                       code_to_int(grid_code(v[u].z, inv, z), qmin, qmax),
+                       code_to_int(grid_code(v[u].w, inv, z), qmin, qmax));
+        }
       }
     }
   } else {
@@ -450,14 +460,25 @@ dynamic_quantize_rows_kernel(const float* __restrict__ x, int64_t cols, int64_t 
     scale_out[row] = s;
     if (zp_out) zp_out[row] = z;
   }
+  constexpr bool kByte = sizeof(OutT) == 1;
+  constexpr bool kUnsigned = static_cast<OutT>(-1) > static_cast<OutT>(0);
+  const bool natural = kByte && (kUnsigned ? (spec.qmin == 0.0f && spec.qmax == 255.0f)
+                                           : (spec.qmin == -128.0f && spec.qmax == 127.0f));
+  const bool has_z = z != 0.0f;
 #pragma unroll
   for (int u = 0; u < ITEMS; ++u) {
     int64_t i = (static_cast<int64_t>(u) * BLOCK + threadIdx.x) * 4;
     if (i < cols) {
-      store4<OutT>(qr + i, code_to_int(grid_code(v[u].x, inv, z), spec.qmin, spec.qmax),
-                   code_to_int(grid_code(v[u].y, inv, z), spec.qmin, spec.qmax),
-                   code_to_int(grid_code(v[u].z, inv, z), spec.qmin, spec.qmax),
-                   code_to_int(grid_code(v[u].w, inv, z), spec.qmin, spec.qmax));
+      if (natural) {
+        *reinterpret_cast<uint32_t*>(qr + i) =
+            pack4_sat<kUnsigned>(__fmul_rn(v[u].x, inv), __fmul_rn(v[u].y, inv), __fmul_rn(v[u].z, inv),
+                                 __fmul_rn(v[u].w, inv), z, has_z);
+      } else {
+        store4<OutT>(qr + i, code_to_int(grid_code(v[u].x, inv, z), spec.qmin, spec.qmax),
+                     code_to_int(grid_code(v[u].y, inv, z), spec.qmin, spec.qmax),
+                     code_to_int(grid_code(v[u].z, inv, z), spec.qmin, spec.qmax),
+                     code_to_int(grid_code(v[u].w, inv, z), spec.qmin, spec.qmax));
+      }
     }
   }
 }

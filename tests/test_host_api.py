@@ -304,3 +304,20 @@ def test_unsupported_front_ends_raise():
     for fn in (Q.prepare_fx, Q.convert_fx, Q.fuse_modules, Q.fuse_modules_qat, Q.prepare_qat):
         with pytest.raises(NotImplementedError):
             fn(nn.Linear(2, 2))
+
+
+@pytest.mark.gpu
+def test_forward_from_host_matches_whole_batch():
+    from lucid_b200.nn.quantized.streaming import forward_from_host
+
+    torch.manual_seed(3)
+    lin = nn.Linear(96, 80)
+    q = Q.quantize_dynamic(lin).set_activation_scheme("token_symmetric")
+    x = torch.randn(1000, 96).pin_memory()
+    out = torch.empty(1000, 80).pin_memory()
+    forward_from_host(q, x, out, chunk_rows=192)
+    torch.cuda.synchronize()
+    assert torch.equal(out, q(x.cuda()).cpu())
+    q.set_activation_scheme("tensor_affine")
+    with pytest.raises(ValueError, match="per-row"):
+        forward_from_host(q, x, out)
