@@ -223,9 +223,9 @@ constexpr int X_PITCH = KC * 2;        // activation row pitch (16-bit elements)
 constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 2 GHz
 // split-K partials of a whole pass: [tile][warp][16 rows][8*nt + 1]
 __host__ __device__ constexpr int red_bytes(int nt, int tmax) { return tmax * kConsumerWarps * 16 * (nt * 8 + 1) * 4; }
-__host__ __device__ constexpr int x_bytes(int nt) { return 2 * nt * 8 * X_PITCH; }
-__host__ __device__ constexpr int stages(int nt, int tmax) {
-  return (kSmemBudget - 512 - red_bytes(nt, tmax) - x_bytes(nt)) / STAGE;
+__host__ __device__ constexpr int x_bytes(int nt, int xb) { return xb * nt * 8 * X_PITCH; }
+__host__ __device__ constexpr int stages(int nt, int tmax, int xb) {
+  return (kSmemBudget - 512 - red_bytes(nt, tmax) - x_bytes(nt, xb)) / STAGE;
 }
 }  // namespace ring
 
@@ -270,30 +270,52 @@ __device__ __forceinline__ uint4 wo_lds128(uint32_t addr) {
   return v;
 }
 
-// four offset-binary bytes -> two packed pairs (bytes 0,1 and bytes 2,3) of XT
+// Raw-operand scheme of the ring kernel: the offset-binary byte u = s8 + 128 is fed to the
+// tensor core as the 16-bit pattern 0x00uu, which reads as u * 2^-24 in f16 and u * 2^-133 in
+// bf16 (subnormals joining the first normals linearly), so widening a pair of weights is one
+// byte-permute and no arithmetic.  The sum over k of x * 128 is obtained per K chunk from one
+// extra MMA against an all-ones operand and subtracted, with the power-of-two scale, when the
+// partial sums are parked: y = C1 * sum(x*u') - 128 * C2 * sum(x').  bf16 activations are
+// multiplied by 2^32 first (exact) so that no product falls into the fp32 subnormal range.
 template <typename XT>
-__device__ __forceinline__ void widen_word(uint32_t u, uint32_t& p01, uint32_t& p23) {
-  p01 = widen_pair<XT>(u, 0);
-  p23 = widen_pair<XT>(u, 2);
-}
-template <typename XT, int NT, int TMAX>
+struct RawOperand;
+template <>
+struct RawOperand<__half> {
+  static constexpr uint32_t kOnes = 0x3C003C00u;
+  __device__ static float acc_scale() { return __int_as_float((127 + 24) << 23); }   // 2^24
+  __device__ static float sum_scale() { return 128.0f; }
+  __device__ static void prescale(uint32_t&) {}
+};
+template <>
+struct RawOperand<__nv_bfloat16> {
+  static constexpr uint32_t kOnes = 0x3F803F80u;
+  __device__ static float acc_scale() { return __int_as_float((127 + 101) << 23); }  // 2^(133-32)
+  __device__ static float sum_scale() { return __int_as_float((127 - 25) << 23); }   // 128 * 2^-32
+  __device__ static void prescale(uint32_t& v) {
+    asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(v) : "r"(0x4F804F80u));  // x * 2^32, exact
+  }
+};
+
+// XB = number of activation-chunk buffers: with few row tiles per CTA a K chunk holds little
+// weight data, so more chunks must be in flight to keep the ring full.
+template <typename XT, int NT, int TMAX, int XB>
 __global__ void __launch_bounds__(ring::kThreads, 1)
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
                       const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, int tiles_per_cta) {
   using namespace ring;
-  constexpr int S = stages(NT, TMAX);
+  constexpr int S = stages(NT, TMAX, XB);
   static_assert(S >= 3, "ring too shallow");
   constexpr int COLS = NT * 8, RP = COLS + 1;
   extern __shared__ uint8_t wo_smem_raw[];
   const uint32_t base = (wo_smem_u32(wo_smem_raw) + 127u) & ~127u;
   const uint32_t x_base = base + S * STAGE;
-  const uint32_t red_base = x_base + x_bytes(NT);
+  const uint32_t red_base = x_base + x_bytes(NT, XB);
   const uint32_t bar_base = red_base + red_bytes(NT, TMAX);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
   auto xfull_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
-  auto xempty_bar = [&](int s) { return bar_base + 8u * (2 * S + 2 + s); };
+  auto xempty_bar = [&](int s) { return bar_base + 8u * (2 * S + XB + s); };
   float* red = reinterpret_cast<float*>(wo_smem_raw + (red_base - wo_smem_u32(wo_smem_raw)));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -309,7 +331,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full_bar(s)), "r"(1) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty_bar(s)), "r"(kConsumerWarps) : "memory");
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < XB; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(xfull_bar(s)), "r"(1) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(xempty_bar(s)), "r"(kConsumerWarps) : "memory");
     }
@@ -327,8 +349,8 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       for (int t0 = 0; t0 < my_tiles && ok; t0 += TMAX) {
         const int pass_tiles = my_tiles - t0 < TMAX ? my_tiles - t0 : TMAX;
         for (int kc = 0; kc < num_kc && ok; ++kc, ++xi) {
-          const int xb = xi & 1;
-          const uint32_t xphase = static_cast<uint32_t>((xi >> 1) & 1);
+          const int xb = xi % XB;
+          const uint32_t xphase = static_cast<uint32_t>((xi / XB) & 1);
           if (!wo_mbar_wait(xempty_bar(xb), xphase ^ 1u)) {
             atomicCAS(&g_wo_status, 0, 1);
             ok = false;
@@ -360,7 +382,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       // do not leave while one of this CTA's bulk copies may still be landing
       for (int s = 0; s < S; ++s)
         if (armed_mask & (1u << s)) wo_mbar_wait(full_bar(s), (armed_parity >> s) & 1u);
-      for (int s = 0; s < 2; ++s)
+      for (int s = 0; s < XB; ++s)
         if (xarmed_mask & (1u << s)) wo_mbar_wait(xfull_bar(s), (xarmed_parity >> s) & 1u);
     }
   } else {
@@ -379,10 +401,15 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
           for (int i = 0; i < 4; ++i) acc[j][nt][i] = 0.0f;
+      float xsum[NT][4];  // per batch column: sum over this warp's K slices of the activations
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xsum[nt][i] = 0.0f;
 
       for (int kc = 0; kc < num_kc && ok; ++kc, ++xi) {
-        const int xb = xi & 1;
-        const uint32_t xphase = static_cast<uint32_t>((xi >> 1) & 1);
+        const int xb = xi % XB;
+        const uint32_t xphase = static_cast<uint32_t>((xi / XB) & 1);
         const bool k_ok = static_cast<int64_t>(kc) * KC + koff < K;               // this lane
         const bool warp_k_ok = static_cast<int64_t>(kc) * KC + warp * 64 < K;     // any lane of the warp
         if (!wo_mbar_wait(xfull_bar(xb), xphase)) {
@@ -405,6 +432,17 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
             for (int i = 0; i < 8; ++i) xa[nt][i] = 0u;
           }
         }
+        if (warp_k_ok) {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) RawOperand<XT>::prescale(xa[nt][i]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              mma_16816<XT>(xsum[nt], RawOperand<XT>::kOnes, RawOperand<XT>::kOnes, RawOperand<XT>::kOnes,
+                            RawOperand<XT>::kOnes, xa[nt][2 * q], xa[nt][2 * q + 1]);
+          }
+        }
 #pragma unroll
         for (int j = 0; j < TMAX; ++j) {
           if (j < pass_tiles && ok) {
@@ -424,9 +462,9 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                 const uint32_t r0[4] = {w0.x, w0.y, w0.z, w0.w}, r1[4] = {w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                  uint32_t a0, a1, a2, a3;
-                  widen_word<XT>(r0[q] ^ 0x80808080u, a0, a2);
-                  widen_word<XT>(r1[q] ^ 0x80808080u, a1, a3);
+                  const uint32_t u0 = r0[q] ^ 0x80808080u, u1 = r1[q] ^ 0x80808080u;
+                  const uint32_t a0 = __byte_perm(u0, 0u, 0x4140u), a2 = __byte_perm(u0, 0u, 0x4342u);
+                  const uint32_t a1 = __byte_perm(u1, 0u, 0x4140u), a3 = __byte_perm(u1, 0u, 0x4342u);
 #pragma unroll
                   for (int nt = 0; nt < NT; ++nt)
                     mma_16816<XT>(acc[j][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
@@ -455,10 +493,11 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           float* mine = red + (j * kConsumerWarps + warp) * 16 * RP;
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            mine[g * RP + nt * 8 + 2 * t] = acc[j][nt][0];
-            mine[g * RP + nt * 8 + 2 * t + 1] = acc[j][nt][1];
-            mine[(g + 8) * RP + nt * 8 + 2 * t] = acc[j][nt][2];
-            mine[(g + 8) * RP + nt * 8 + 2 * t + 1] = acc[j][nt][3];
+            const float c1 = RawOperand<XT>::acc_scale(), c2 = RawOperand<XT>::sum_scale();
+            mine[g * RP + nt * 8 + 2 * t] = acc[j][nt][0] * c1 - xsum[nt][0] * c2;
+            mine[g * RP + nt * 8 + 2 * t + 1] = acc[j][nt][1] * c1 - xsum[nt][1] * c2;
+            mine[(g + 8) * RP + nt * 8 + 2 * t] = acc[j][nt][2] * c1 - xsum[nt][0] * c2;
+            mine[(g + 8) * RP + nt * 8 + 2 * t + 1] = acc[j][nt][3] * c1 - xsum[nt][1] * c2;
           }
         }
       }
@@ -649,11 +688,11 @@ static int32_t launch_wo_mma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
   return check_launch("wo_linear_s8 (mma)");
 }
 
-template <typename XT, int NT, int TMAX>
+template <typename XT, int NT, int TMAX, int XB>
 static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                    int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
                                    int64_t ldy, cudaStream_t st) {
-  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX>;
+  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
   int dev = 0;
@@ -688,9 +727,16 @@ template <typename XT>
 static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w, int64_t ldw,
                              int64_t N, const float* sw, const float* bias, XT* y, int64_t ldy,
                              cudaStream_t st) {
-  if (B <= 8) return launch_wo_ring_inst<XT, 1, 8>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
-  if (B <= 16) return launch_wo_ring_inst<XT, 2, 4>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
-  return launch_wo_ring_inst<XT, 4, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+  // few row tiles per CTA (short, wide matrices): small reduction buffer, more activation chunks in flight
+  const int64_t tiles = (N + 15) / 16, sms = sm_count();
+  const bool few = (tiles + sms - 1) / sms <= 2;
+  if (B <= 8)
+    return few ? launch_wo_ring_inst<XT, 1, 2, 4>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st)
+               : launch_wo_ring_inst<XT, 1, 8, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+  if (B <= 16)
+    return few ? launch_wo_ring_inst<XT, 2, 2, 3>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st)
+               : launch_wo_ring_inst<XT, 2, 4, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+  return launch_wo_ring_inst<XT, 4, 1, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
 }
 
 template <typename XT>
