@@ -227,6 +227,17 @@ int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K
                         const int8_t* wq, int64_t ldw, int64_t N, const float* sw,
                         const float* bias, void* y, int64_t ldy, void* stream);
 
+/* Gate and up projection of a SwiGLU MLP in one pass over the weights, with the activation
+ * fused: wq is [N2 = 2F, K] with rows interleaved in blocks of 8 (rows 16t..16t+7 are gate
+ * rows 8t..8t+7, rows 16t+8..16t+15 the matching up rows), sw / bias interleaved the same
+ * way; y[b, h] = silu(gate_h) * up_h in the activation type (bf16 / f16), F columns.
+ * The unfused form in the reference is two quantized Linears followed by eager silu and
+ * multiply ops (lucid/nn/quantized/linear.py:206-214; fusion listed as a follow-up of the
+ * quantized_matmul path, lucid/_C/ops/quantized/QuantizedMatmul.cpp:143-207). */
+int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
+                        const int8_t* wq, int64_t ldw, int64_t N2, const float* sw, const float* bias,
+                        void* y, int64_t ldy, void* stream);
+
 /* Synchronises the device and reads the status word of the weight-only kernels on the
  * current device: 0, or the code of a bounded device-side wait that ran out (the
  * affected outputs are invalid).  clear != 0 resets it.  No counterpart in the

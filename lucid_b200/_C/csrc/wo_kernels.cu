@@ -298,7 +298,7 @@ struct RawOperand<__nv_bfloat16> {
 
 // XB = number of activation-chunk buffers: with few row tiles per CTA a K chunk holds little
 // weight data, so more chunks must be in flight to keep the ring full.
-template <typename XT, int NT, int TMAX, int XB>
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU>
 __global__ void __launch_bounds__(ring::kThreads, 1)
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
@@ -502,17 +502,42 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         }
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-      for (int o = threadIdx.x; o < pass_tiles * 16 * COLS; o += kConsumerThreads) {
-        const int r = o & 15, bcol = (o >> 4) % COLS, j = (o >> 4) / COLS;
-        const int64_t n = ((tile0 + t0 + j) << 4) + r;
-        if (n < N && bcol < nb) {
-          const float* src = red + j * kConsumerWarps * 16 * RP + r * RP + bcol;
-          float sum = 0.0f;
+      if (SWIGLU) {
+        // rows r and r+8 of a tile are the gate and the up projection of the same hidden unit:
+        // out[b, 8*tile + r] = silu(gate) * up, one rounding to the activation type
+        for (int o = threadIdx.x; o < pass_tiles * 8 * COLS; o += kConsumerThreads) {
+          const int r = o & 7, bcol = (o >> 3) % COLS, j = (o >> 3) / COLS;
+          const int64_t tile = tile0 + t0 + j;
+          const int64_t ng = (tile << 4) + r, nu = ng + 8, h = (tile << 3) + r;
+          if (nu < N && bcol < nb) {
+            const float* src = red + j * kConsumerWarps * 16 * RP + r * RP + bcol;
+            float gs = 0.0f, us = 0.0f;
 #pragma unroll
-          for (int wp = 0; wp < kConsumerWarps; ++wp) sum += src[wp * 16 * RP];
-          float v = sum * (sw ? __ldg(sw + n) : 1.0f);
-          if (bias) v += __ldg(bias + n);
-          y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(v);
+            for (int wp = 0; wp < kConsumerWarps; ++wp) {
+              gs += src[wp * 16 * RP];
+              us += src[wp * 16 * RP + 8 * RP];
+            }
+            float gv = gs * (sw ? __ldg(sw + ng) : 1.0f), uv = us * (sw ? __ldg(sw + nu) : 1.0f);
+            if (bias) {
+              gv += __ldg(bias + ng);
+              uv += __ldg(bias + nu);
+            }
+            y[static_cast<int64_t>(bcol) * ldy + h] = from_float<XT>(gv / (1.0f + __expf(-gv)) * uv);
+          }
+        }
+      } else {
+        for (int o = threadIdx.x; o < pass_tiles * 16 * COLS; o += kConsumerThreads) {
+          const int r = o & 15, bcol = (o >> 4) % COLS, j = (o >> 4) / COLS;
+          const int64_t n = ((tile0 + t0 + j) << 4) + r;
+          if (n < N && bcol < nb) {
+            const float* src = red + j * kConsumerWarps * 16 * RP + r * RP + bcol;
+            float sum = 0.0f;
+#pragma unroll
+            for (int wp = 0; wp < kConsumerWarps; ++wp) sum += src[wp * 16 * RP];
+            float v = sum * (sw ? __ldg(sw + n) : 1.0f);
+            if (bias) v += __ldg(bias + n);
+            y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(v);
+          }
         }
       }
     }
@@ -688,11 +713,11 @@ static int32_t launch_wo_mma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
   return check_launch("wo_linear_s8 (mma)");
 }
 
-template <typename XT, int NT, int TMAX, int XB>
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU = false>
 static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                    int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
                                    int64_t ldy, cudaStream_t st) {
-  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB>;
+  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
   int dev = 0;
@@ -723,7 +748,7 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   return check_launch("wo_linear_s8 (ring)");
 }
 
-template <typename XT>
+template <typename XT, bool SWIGLU = false>
 static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w, int64_t ldw,
                              int64_t N, const float* sw, const float* bias, XT* y, int64_t ldy,
                              cudaStream_t st) {
@@ -731,12 +756,12 @@ static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
   const int64_t tiles = (N + 15) / 16, sms = sm_count();
   const bool few = (tiles + sms - 1) / sms <= 2;
   if (B <= 8)
-    return few ? launch_wo_ring_inst<XT, 1, 2, 4>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st)
-               : launch_wo_ring_inst<XT, 1, 8, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st)
+               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
   if (B <= 16)
-    return few ? launch_wo_ring_inst<XT, 2, 2, 3>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st)
-               : launch_wo_ring_inst<XT, 2, 4, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
-  return launch_wo_ring_inst<XT, 4, 1, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+    return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st)
+               : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+  return launch_wo_ring_inst<XT, 4, 1, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
 }
 
 template <typename XT>
@@ -825,6 +850,27 @@ extern "C" int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch
       return wo_linear_typed<__half>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, st);
   }
   return fail(LC_ERR_UNSUPPORTED, "wo_linear_s8: x_dtype %d not supported", x_dtype);
+}
+
+extern "C" int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
+                                   const int8_t* wq, int64_t ldw, int64_t N2, const float* sw,
+                                   const float* bias, void* y, int64_t ldy, void* stream) {
+  if (batch < 0 || N2 < 0 || K <= 0 || ldx < K || ldw < K || ldy < N2 / 2)
+    return fail(LC_ERR_INVALID_ARG, "wo_swiglu_s8: bad shape");
+  if (N2 % 16) return fail(LC_ERR_INVALID_ARG, "wo_swiglu_s8: the interleaved weight needs a multiple of 16 rows");
+  if (batch == 0 || N2 == 0) return LC_OK;
+  if (!x || !wq || !y) return fail(LC_ERR_INVALID_ARG, "wo_swiglu_s8: null pointer");
+  if (batch > 32) return fail(LC_ERR_UNSUPPORTED, "wo_swiglu_s8: batch %lld > 32", (long long)batch);
+  if (K % 16 || ldw % 16 || ldx % 8 || !aligned(wq, 16) || !aligned(x, 16))
+    return fail(LC_ERR_UNSUPPORTED, "wo_swiglu_s8: K, ldw must be multiples of 16, ldx of 8, pointers 16-byte aligned");
+  cudaStream_t st = as_stream(stream);
+  if (x_dtype == LC_BF16)
+    return launch_wo_tma<__nv_bfloat16, true>(static_cast<const __nv_bfloat16*>(x), batch, K, ldx, wq, ldw, N2, sw,
+                                              bias, static_cast<__nv_bfloat16*>(y), ldy, st);
+  if (x_dtype == LC_F16)
+    return launch_wo_tma<__half, true>(static_cast<const __half*>(x), batch, K, ldx, wq, ldw, N2, sw, bias,
+                                       static_cast<__half*>(y), ldy, st);
+  return fail(LC_ERR_UNSUPPORTED, "wo_swiglu_s8: activations must be bf16 or f16");
 }
 
 extern "C" int32_t lc_wo_linear_status(int32_t* host_code, int32_t clear) {

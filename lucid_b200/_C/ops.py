@@ -391,6 +391,34 @@ def wo_linear_s8(x2d, wq, sw, bias=None):
     return y
 
 
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Stack two [F, ...] tensors (weights, scales or biases of the gate and up projections)
+    into the [2F, ...] layout of :func:`wo_swiglu_s8`: blocks of 8 gate rows followed by the
+    matching 8 up rows."""
+    if gate.shape != up.shape or gate.shape[0] % 8:
+        raise ValueError("gate and up must have the same shape with a multiple of 8 rows")
+    f = gate.shape[0]
+    g = gate.reshape(f // 8, 8, *gate.shape[1:])
+    u = up.reshape(f // 8, 8, *up.shape[1:])
+    return torch.cat([g, u], dim=1).reshape(2 * f, *gate.shape[1:]).contiguous()
+
+
+def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None):
+    """``silu(x @ Wg^T * sg) * (x @ Wu^T * su)`` with interleaved int8 gate/up weights
+    (see :func:`interleave_gate_up`); bf16 / f16 activations, batch <= 32."""
+    dev = _need_cuda(x2d, wq_gu, sw_gu, bias_gu)
+    x2d = x2d.contiguous()
+    B, K = x2d.shape
+    N2 = wq_gu.shape[0]
+    y = torch.empty((B, N2 // 2), dtype=x2d.dtype, device=dev)
+    sw_c = None if sw_gu is None else _f32c(sw_gu)
+    bias_c = None if bias_gu is None else _f32c(bias_gu)
+    with _on(dev):
+        check(lib.lc_wo_swiglu_s8(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq_gu.data_ptr(),
+                                  wq_gu.stride(0), N2, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N2 // 2, _stream(dev)))
+    return y
+
+
 def wo_linear_status(clear: bool = True) -> int:
     """Status word of the weight-only kernels on the current device (synchronises): 0, or the
     code of a bounded device-side wait that ran out."""

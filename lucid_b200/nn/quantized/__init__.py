@@ -4,5 +4,6 @@ wrappers of the reference are float-compute composites outside this backend's sc
 from lucid_b200.nn.quantized import dynamic
 from lucid_b200.nn.quantized.linear import Linear, LinearReLU
 from lucid_b200.nn.quantized.mlx_linear import QuantizedLinearMLX
+from lucid_b200.nn.quantized.weight_only import WeightOnlyLinear, WeightOnlySwiGLU
 
-__all__ = ["Linear", "LinearReLU", "QuantizedLinearMLX", "dynamic"]
+__all__ = ["Linear", "LinearReLU", "QuantizedLinearMLX", "WeightOnlyLinear", "WeightOnlySwiGLU", "dynamic"]

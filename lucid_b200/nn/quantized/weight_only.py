@@ -1,0 +1,106 @@
+"""Weight-only int8 layers with per-output-channel symmetric scales and float activations
+(W8A16): the decode-time counterpart of the dynamic Linear.  The reference's weight-only
+layer is the group-wise ``QuantizedLinearMLX`` (``lucid/nn/quantized/mlx_linear.py:21-256``);
+this is the per-channel layout of its sidecar modules (``weight_int8`` / ``weight_scale``
+buffers as in ``lucid/nn/quantized/linear.py:189-199``) computed without dequantizing the
+weight: up to 32 rows go through the GEMV-shaped kernel that reads the int8 weight once.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from lucid_b200 import _backend
+from lucid_b200.quantization._functional import dequantize, quantize
+from lucid_b200.quantization._qscheme import QDtype, per_channel_symmetric, qint8
+
+_GEMV_MAX_ROWS = 32
+
+
+def _quantize_rows(weight: torch.Tensor, dtype: QDtype):
+    from lucid_b200.quantization.observer import PerChannelMinMaxObserver
+
+    obs = PerChannelMinMaxObserver(ch_axis=0, qscheme=per_channel_symmetric, qdtype=dtype)
+    obs(weight)
+    scale, zero_point = obs.calculate_qparams()
+    return quantize(weight, scale, zero_point, dtype, ch_axis=0), scale
+
+
+class WeightOnlyLinear(nn.Module):
+    def __init__(self, in_features: int, out_features: int, bias: bool = True) -> None:
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.register_buffer("weight_int8", torch.zeros((out_features, in_features), dtype=torch.int8))
+        self.register_buffer("weight_scale", torch.ones(out_features))
+        if bias:
+            self.register_buffer("bias", torch.zeros(out_features))
+        else:
+            self.bias = None
+
+    @classmethod
+    def from_float(cls, mod: nn.Module, dtype: QDtype = qint8) -> "WeightOnlyLinear":
+        m = cls(mod.in_features, mod.out_features, bias=mod.bias is not None)
+        codes, scale = _quantize_rows(_backend.on_cuda(mod.weight.detach().float()), dtype)
+        m.register_buffer("weight_int8", codes)
+        m.register_buffer("weight_scale", scale)
+        if mod.bias is not None:
+            m.register_buffer("bias", _backend.on_cuda(mod.bias.detach().float()).clone())
+        return m
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        xd = _backend.on_cuda(x)
+        x2 = xd.reshape(-1, self.in_features)
+        if 0 < x2.shape[0] <= _GEMV_MAX_ROWS:
+            y = _backend.ops().wo_linear_s8(x2, self.weight_int8, self.weight_scale, self.bias)
+        else:  # compute-bound batches: decode the weight once, dense product
+            w = dequantize(self.weight_int8, self.weight_scale, 0.0, ch_axis=0).to(x2.dtype)
+            y = torch.nn.functional.linear(x2, w, None if self.bias is None else self.bias.to(x2.dtype))
+        y = y.reshape(*xd.shape[:-1], self.out_features)
+        return y if x.is_cuda else y.to(x.device)
+
+    def extra_repr(self) -> str:
+        return f"in_features={self.in_features}, out_features={self.out_features}, weight_only=int8"
+
+
+class WeightOnlySwiGLU(nn.Module):
+    """``down(silu(gate(x)) * up(x))`` with int8 weights.  Gate and up rows are stored
+    interleaved (blocks of 8) so that decode batches read both matrices in one pass whose
+    epilogue applies the activation; the down projection is a :class:`WeightOnlyLinear`."""
+
+    def __init__(self, hidden: int, intermediate: int) -> None:
+        super().__init__()
+        if intermediate % 8:
+            raise ValueError("intermediate size must be a multiple of 8")
+        self.hidden, self.intermediate = hidden, intermediate
+        self.register_buffer("gate_up_int8", torch.zeros((2 * intermediate, hidden), dtype=torch.int8))
+        self.register_buffer("gate_up_scale", torch.ones(2 * intermediate))
+        self.down = WeightOnlyLinear(intermediate, hidden, bias=False)
+
+    @classmethod
+    def from_float(cls, gate: nn.Linear, up: nn.Linear, down: nn.Linear, dtype: QDtype = qint8) -> "WeightOnlySwiGLU":
+        ops = _backend.ops()
+        m = cls(gate.in_features, gate.out_features)
+        (wg, sg), (wu, su) = (_quantize_rows(_backend.on_cuda(l.weight.detach().float()), dtype) for l in (gate, up))
+        m.register_buffer("gate_up_int8", ops.interleave_gate_up(wg, wu))
+        m.register_buffer("gate_up_scale", ops.interleave_gate_up(sg, su))
+        m.down = WeightOnlyLinear.from_float(down, dtype)
+        return m
+
+    def _split(self, t: torch.Tensor):
+        blocks = t.reshape(self.intermediate // 8, 16, *t.shape[1:])
+        return blocks[:, :8].reshape(self.intermediate, *t.shape[1:]), blocks[:, 8:].reshape(self.intermediate, *t.shape[1:])
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        xd = _backend.on_cuda(x)
+        x2 = xd.reshape(-1, self.hidden)
+        fused_ok = (0 < x2.shape[0] <= _GEMV_MAX_ROWS and x2.dtype in (torch.bfloat16, torch.float16)
+                    and self.hidden % 16 == 0)
+        if fused_ok:
+            h = _backend.ops().wo_swiglu_s8(x2, self.gate_up_int8, self.gate_up_scale)
+        else:
+            (wg, wu), (sg, su) = self._split(self.gate_up_int8), self._split(self.gate_up_scale)
+            g = torch.nn.functional.linear(x2, dequantize(wg.contiguous(), sg.contiguous(), 0.0, ch_axis=0).to(x2.dtype))
+            u = torch.nn.functional.linear(x2, dequantize(wu.contiguous(), su.contiguous(), 0.0, ch_axis=0).to(x2.dtype))
+            h = torch.nn.functional.silu(g) * u
+        y = self.down(h).reshape(*xd.shape[:-1], self.hidden)
+        return y if x.is_cuda else y.to(x.device)

@@ -141,3 +141,23 @@ def test_int8_widening_is_exact_for_every_code(ops, dtype, N, K):
     y = ops.wo_linear_s8(x, wq, torch.ones(N, device="cuda"))
     assert torch.equal(y.float(), wq[:, cols].T.float())
     assert ops.wo_linear_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,F,K", [(1, 2048, 1024), (4, 14336, 4096), (16, 1000 * 8, 512), (9, 4096, 2064)])
+def test_wo_swiglu_fused(ops, dtype, B, F, K):
+    """Fused gate/up + SwiGLU against the float64 composition of the unfused definition."""
+    g = torch.Generator(device="cuda").manual_seed(F + K + B)
+    wg = torch.randint(-128, 128, (F, K), device="cuda", dtype=torch.int8, generator=g)
+    wu = torch.randint(-128, 128, (F, K), device="cuda", dtype=torch.int8, generator=g)
+    sg = torch.rand(F, device="cuda", generator=g) * 2e-3
+    su = torch.rand(F, device="cuda", generator=g) * 2e-3
+    x = torch.randn(B, K, device="cuda", generator=g).to(dtype)
+    y = ops.wo_swiglu_s8(x, ops.interleave_gate_up(wg, wu), ops.interleave_gate_up(sg, su))
+    gate = (x.double() @ wg.double().T) * sg.double()
+    up = (x.double() @ wu.double().T) * su.double()
+    ref = torch.nn.functional.silu(gate) * up
+    tol = 1e-2 if dtype == torch.bfloat16 else 2e-3
+    assert y.shape == (B, F) and y.dtype == dtype
+    assert torch.allclose(y.double(), ref, rtol=tol, atol=tol * float(ref.abs().max()))
+    assert ops.wo_linear_status() == 0

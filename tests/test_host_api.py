@@ -321,3 +321,22 @@ def test_forward_from_host_matches_whole_batch():
     q.set_activation_scheme("tensor_affine")
     with pytest.raises(ValueError, match="per-row"):
         forward_from_host(q, x, out)
+
+
+@pytest.mark.gpu
+def test_weight_only_modules():
+    torch.manual_seed(5)
+    H, F = 256, 512
+    gate, up, down = nn.Linear(H, F, bias=False), nn.Linear(H, F, bias=False), nn.Linear(F, H, bias=False)
+    mlp = nnq.WeightOnlySwiGLU.from_float(gate, up, down)
+    assert set(mlp.state_dict()) == {"gate_up_int8", "gate_up_scale", "down.weight_int8", "down.weight_scale"}
+    ref = lambda x: down(torch.nn.functional.silu(gate(x)) * up(x))
+    for rows, dtype in ((4, torch.bfloat16), (4, torch.float32), (100, torch.bfloat16)):
+        x = torch.randn(rows, H)
+        y = mlp(x.cuda().to(dtype)).float().cpu()
+        assert (y - ref(x)).abs().mean() / ref(x).abs().mean() < 0.05
+    lin = nn.Linear(H, F)
+    wo = nnq.WeightOnlyLinear.from_float(lin)
+    x = torch.randn(3, 7, H)
+    assert tuple(wo(x.cuda().bfloat16()).shape) == (3, 7, F)
+    assert (wo(x.cuda()).cpu() - lin(x)).abs().mean() / lin(x).abs().mean() < 0.02
