@@ -251,6 +251,53 @@ def encoder_extras(torch, dev, gen) -> dict:
     return res
 
 
+def dispatch_rows(torch, dev, width: int = 1024, n_iter: int = 20) -> list:
+    """Row schema and timing contract of the reference's dispatch benchmark: bits in {4, 8},
+    M in {1, 2, 8, 32}, N = K = width, group 64; paths packed / cached_dense / dequant_each_call;
+    a call is timed with its output materialised (`.sum().item()`) and the device synchronised
+    (tools/_bench_timing.py:33-52); a 1e-4 relative parity gate precedes timing."""
+    from lucid_b200.quantization import _qgemm
+
+    def cold_ms(call):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        call().sum().item()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) * 1e3
+
+    torch.manual_seed(20260920)
+    rows = []
+    with torch.no_grad():
+        for bits in (4, 8):
+            weight = torch.randn(width, width, device=dev)
+            packed, scales, biases = _qgemm.quantize(weight, group_size=64, bits=bits)
+            dense = _qgemm.dequantize(packed, scales, biases, group_size=64, bits=bits)
+            for m in (1, 2, 8, 32):
+                x = torch.randn(m, width, device=dev)
+                calls = {
+                    "packed": lambda: _qgemm.quantized_matmul(x, packed, scales, biases, transpose=True,
+                                                              group_size=64, bits=bits),
+                    "cached_dense": lambda: torch.matmul(x, dense.mT),
+                    "dequant_each_call": lambda: torch.matmul(
+                        x, _qgemm.dequantize(packed, scales, biases, group_size=64, bits=bits).mT),
+                }
+                expected, actual = calls["cached_dense"](), calls["packed"]()
+                err = float((expected - actual).abs().max()) / max(float(expected.abs().max()), 1e-12)
+                if not err <= 1e-4:
+                    raise RuntimeError(f"parity failure for bits={bits}, M={m}: {err}")
+                for name, call in calls.items():
+                    first = cold_ms(call)
+                    for _ in range(5):
+                        call().sum().item()
+                    samples = sorted(cold_ms(call) for _ in range(n_iter))
+                    rows.append({"bits": bits, "m": m, "n": width, "k": width, "path": name,
+                                 "first_ms": round(first, 4), "median_ms": round(statistics.median(samples), 4),
+                                 "p5_ms": round(samples[int(n_iter * 0.05)], 4),
+                                 "p95_ms": round(samples[min(n_iter - 1, int(n_iter * 0.95))], 4),
+                                 "parity_relative_error": err})
+    return rows
+
+
 def extras_single_gpu(torch, ops, peaks) -> dict:
     """HBM-bound companions of the metric, measured on one GPU after the headline run."""
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -322,6 +369,11 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
         out["encoder_6x512_b32_s256"] = encoder_extras(torch, dev, g)
     except Exception as e:  # reported, never hidden
         out["encoder_6x512_b32_s256"] = {"error": repr(e)[:300]}
+    # ---- the reference's own dispatch benchmark rows (tools/bench_quantized_dispatch.py:26-75)
+    try:
+        out["quantized_dispatch_rows"] = dispatch_rows(torch, dev)
+    except Exception as e:
+        out["quantized_dispatch_rows"] = {"error": repr(e)[:300]}
     # ---- the single dynamic Linear (x [64,1024], W [4096,1024]) through the module API
     try:
         import lucid_b200.quantization as Q

@@ -648,6 +648,32 @@ group_dequantize_kernel(const uint32_t* __restrict__ packed, const float* __rest
   }
 }
 
+// N consecutive elements starting at an address aligned to N elements, as floats
+template <typename XT, int N>
+__device__ __forceinline__ void load_run(const XT* p, float (&out)[N]);
+template <>
+__device__ __forceinline__ void load_run<float, 4>(const float* p, float (&o)[4]) {
+  const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+  o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+template <>
+__device__ __forceinline__ void load_run<float, 8>(const float* p, float (&o)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <typename XT, int N>
+__device__ __forceinline__ void load_run(const XT* p, float (&o)[N]) {  // 16-bit types
+  static_assert(sizeof(XT) == 2 && (N == 4 || N == 8), "unsupported run");
+  XT tmp[N];
+  if (N == 4) {
+    *reinterpret_cast<uint2*>(tmp) = __ldg(reinterpret_cast<const uint2*>(p));
+  } else {
+    *reinterpret_cast<uint4*>(tmp) = __ldg(reinterpret_cast<const uint4*>(p));
+  }
+#pragma unroll
+  for (int e = 0; e < N; ++e) o[e] = to_float<XT>(tmp[e]);
+}
+
 // y[b,n] = sum_k x[b,k] * (c[n,k]*s + bias): one warp per output row, lanes stride
 // over packed words, fp32 accumulation, batch in chunks of BT
 template <typename XT, int BITS, int BT>
@@ -662,7 +688,9 @@ group_matmul_kernel(const XT* __restrict__ x, int64_t B, int64_t K, const uint32
   const int64_t words = K / PER;
   const int64_t groups = K / group_size;
   const uint32_t* pr = packed + n * words;
-  for (int64_t b0 = 0; b0 < B; b0 += BT) {
+  // batch tiles of BT are spread over blockIdx.y: they run concurrently, the 1 MB-scale
+  // weight is re-read from L2
+  for (int64_t b0 = static_cast<int64_t>(blockIdx.y) * BT; b0 < B; b0 += static_cast<int64_t>(gridDim.y) * BT) {
     float acc[BT];
 #pragma unroll
     for (int i = 0; i < BT; ++i) acc[i] = 0.0f;
@@ -671,14 +699,26 @@ group_matmul_kernel(const XT* __restrict__ x, int64_t B, int64_t K, const uint32
       const int64_t k0 = wd * PER;
       const int64_t gidx = n * groups + k0 / group_size;
       const float s = __ldg(scales + gidx), bb = __ldg(biases + gidx);
+      float wv[PER];
 #pragma unroll
-      for (int e = 0; e < PER; ++e) {
-        const float c = static_cast<float>((bits >> (BITS * e)) & ((1u << BITS) - 1u));
-        const float wv = fmaf(c, s, bb);
+      for (int e = 0; e < PER; ++e)
+        wv[e] = fmaf(static_cast<float>((bits >> (BITS * e)) & ((1u << BITS) - 1u)), s, bb);
+      // PER (4 or 8) consecutive activations of each batch row with 16-byte loads; all loads
+      // of the tile are issued before the first FMA needs one
+      float xv[BT][PER];
 #pragma unroll
-        for (int i = 0; i < BT; ++i)
-          if (b0 + i < B) acc[i] = fmaf(to_float<XT>(x[(b0 + i) * K + k0 + e]), wv, acc[i]);
+      for (int i = 0; i < BT; ++i) {
+        if (b0 + i < B) {
+          load_run<XT, PER>(x + (b0 + i) * K + k0, xv[i]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < PER; ++e) xv[i][e] = 0.0f;
+        }
       }
+#pragma unroll
+      for (int i = 0; i < BT; ++i)
+#pragma unroll
+        for (int e = 0; e < PER; ++e) acc[i] = fmaf(xv[i][e], wv[e], acc[i]);
     }
 #pragma unroll
     for (int i = 0; i < BT; ++i) {
@@ -808,13 +848,15 @@ template <typename XT, int BITS>
 static int32_t launch_group_matmul(const XT* x, int64_t B, int64_t K, const uint32_t* packed,
                                    const float* scales, const float* biases, int64_t N, int gs, XT* y,
                                    cudaStream_t st) {
-  const unsigned grid = static_cast<unsigned>((N + kWoWarps - 1) / kWoWarps);
-  if (B <= 1)
-    group_matmul_kernel<XT, BITS, 1><<<grid, kWoThreads, 0, st>>>(x, B, K, packed, scales, biases, N, gs, y);
-  else if (B <= 4)
-    group_matmul_kernel<XT, BITS, 4><<<grid, kWoThreads, 0, st>>>(x, B, K, packed, scales, biases, N, gs, y);
-  else
+  const unsigned gx = static_cast<unsigned>((N + kWoWarps - 1) / kWoWarps);
+  if (B <= 1) {
+    group_matmul_kernel<XT, BITS, 1><<<gx, kWoThreads, 0, st>>>(x, B, K, packed, scales, biases, N, gs, y);
+  } else if (B <= 4) {
+    group_matmul_kernel<XT, BITS, 4><<<gx, kWoThreads, 0, st>>>(x, B, K, packed, scales, biases, N, gs, y);
+  } else {
+    const dim3 grid(gx, static_cast<unsigned>((B + 7) / 8 < 64 ? (B + 7) / 8 : 64));
     group_matmul_kernel<XT, BITS, 8><<<grid, kWoThreads, 0, st>>>(x, B, K, packed, scales, biases, N, gs, y);
+  }
   return check_launch("group_matmul");
 }
 

@@ -1,0 +1,110 @@
+"""Parity on the five benchmark configurations, by name.  C1, C2 and C5 also have dedicated
+cases in test_gpu_qlinear.py / test_gpu_quant.py; here every configuration is exercised
+through the public module API and every quantized Linear inside it is checked against the
+oracle on exactly the tensors it saw."""
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+import lucid_b200.quantization as Q
+from lucid_b200.nn import quantized as nnq
+from lucid_b200.nn.quantized import dynamic as nnqd
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 1e-5, 1e-6
+
+
+def check_dynamic_linears(model, x):
+    """Run `model(x)`; for each dynamic Linear compare its output with the oracle's integer
+    formulation evaluated on the input that layer received (codes exact, fp32 rtol 1e-5)."""
+    seen = []
+    hooks = [m.register_forward_hook(lambda mod, args, out: seen.append((mod, args[0].detach(), out.detach())))
+             for m in model.modules() if isinstance(m, nnqd.Linear)]
+    with torch.no_grad():
+        y = model(x)
+    for h in hooks:
+        h.remove()
+    assert seen
+    for mod, xin, out in seen:
+        x2 = xin.reshape(-1, mod.in_features).float().cpu().numpy()
+        wq = mod.weight_int8.cpu().numpy()
+        sw = mod.weight_scale.cpu().numpy()
+        b = None if mod.bias is None else mod.bias.cpu().numpy()
+        _, y_o, _, _, _ = O.dynamic_linear_int(x2, wq, sw, b, mod.act_scheme, O.QDtype(
+            mod.act_qdtype.name, 8, mod.act_qdtype.signed, mod.act_qdtype.quant_min, mod.act_qdtype.quant_max,
+            mod.act_qdtype.storage))
+        np.testing.assert_allclose(out.reshape(-1, mod.out_features).cpu().numpy(), y_o, rtol=RTOL, atol=ATOL)
+    return y, len(seen)
+
+
+def test_config1_single_dynamic_linear_module():
+    x, w, b = O.synth_config1()
+    lin = nn.Linear(1024, 4096)
+    with torch.no_grad():
+        lin.weight.copy_(torch.tensor(w))
+        lin.bias.copy_(torch.tensor(b))
+    narrow = Q.QDtype("qint8", 8, True, -127, 127, "int8")  # scale = absmax/127, clamp [-127,127]
+    q = Q.quantize_dynamic(lin, dtype=narrow).set_activation_scheme("tensor_symmetric", narrow)
+    wq_o, sw_o, _ = O.quantize_weight_per_channel(w, O.qint8_narrow)
+    np.testing.assert_array_equal(q.weight_int8.cpu().numpy(), wq_o)
+    np.testing.assert_array_equal(q.weight_scale.cpu().numpy(), sw_o)
+    _, n = check_dynamic_linears(q, torch.tensor(x, device="cuda"))
+    assert n == 1
+
+
+def test_config3_encoder_every_linear():
+    """One post-norm encoder layer of the benchmark's shape family (d 512, 8 heads, FFN 2048):
+    six dynamic int8 Linears, each checked on the activations it actually received."""
+    torch.manual_seed(0)
+    D, H, FF = 512, 8, 2048
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q, self.k, self.v, self.o = (nn.Linear(D, D) for _ in range(4))
+            self.linear1, self.linear2 = nn.Linear(D, FF), nn.Linear(FF, D)
+            self.norm1, self.norm2 = nn.LayerNorm(D), nn.LayerNorm(D)
+
+        def forward(self, x):
+            b, s, _ = x.shape
+            q, k, v = (m(x).view(b, s, H, D // H).transpose(1, 2) for m in (self.q, self.k, self.v))
+            a = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, s, D)
+            x = self.norm1(x + self.o(a))
+            return self.norm2(x + self.linear2(torch.nn.functional.gelu(self.linear1(x))))
+
+    model = Layer().cuda().eval()
+    for m in model.modules():
+        if isinstance(m, nn.Linear):
+            nn.init.normal_(m.weight, 0.0, 0.02)
+    qmodel = Q.quantize_dynamic(model)
+    x = torch.randn(4, 64, D, device="cuda")
+    y, n = check_dynamic_linears(qmodel, x)
+    assert n == 6
+    with torch.no_grad():
+        ref = model(x)
+    assert float((y - ref).abs().mean() / ref.abs().mean()) < 0.05
+
+
+def test_config4_decode_mlp_module():
+    torch.manual_seed(1)
+    Hd, F = 4096, 14336
+    gate, up, down = (nn.Linear(Hd, F, bias=False), nn.Linear(Hd, F, bias=False), nn.Linear(F, Hd, bias=False))
+    for l in (gate, up, down):
+        nn.init.normal_(l.weight, 0.0, 0.02)
+    mlp = nnq.WeightOnlySwiGLU.from_float(gate, up, down)
+    # weights: bit-exact per-channel symmetric int8 against the oracle
+    wq_o, sw_o, _ = O.quantize_weight_per_channel(down.weight.detach().numpy())
+    np.testing.assert_array_equal(mlp.down.weight_int8.cpu().numpy(), wq_o)
+    np.testing.assert_array_equal(mlp.down.weight_scale.cpu().numpy(), sw_o)
+    wg, wu = mlp._split(mlp.gate_up_int8)
+    sg, su = mlp._split(mlp.gate_up_scale)
+    for batch in (1, 4, 16):
+        x = torch.randn(batch, Hd, device="cuda").to(torch.bfloat16)
+        y = mlp(x)
+        g = (x.double() @ wg.double().T) * sg.double()
+        u = (x.double() @ wu.double().T) * su.double()
+        h = (torch.nn.functional.silu(g) * u).to(torch.bfloat16).double()
+        ref = (h @ mlp.down.weight_int8.double().T) * mlp.down.weight_scale.double()
+        assert torch.allclose(y.double(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
