@@ -222,10 +222,16 @@ int32_t lc_rowsum_s8(const int8_t* b, int64_t rows, int64_t cols, int64_t ldb, i
  * Replaces the dequantize-then-F.linear forward of the quantized Linear at
  * small batch (lucid/nn/quantized/linear.py:206-214) and is the per-channel
  * counterpart of quantized_matmul_op (lucid/_C/ops/quantized/QuantizedMatmul.cpp:143-207).
- * x_dtype / y dtype: LC_F32, LC_BF16 or LC_F16; batch <= 32. */
+ * x_dtype / y dtype: LC_F32, LC_BF16 or LC_F16.
+ * flags: LC_WO_OVERLAP_PREVIOUS lets the kernel start while the kernel before it on the
+ * stream is still draining (programmatic dependent launch): it prefetches weights into
+ * shared memory and waits for that kernel before it reads x or writes y.  The caller asserts that wq, sw and bias were completely written before that
+ * previous kernel started.  Ignored by the paths that do not stream weights through
+ * shared memory. */
+#define LC_WO_OVERLAP_PREVIOUS 1
 int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
                         const int8_t* wq, int64_t ldw, int64_t N, const float* sw,
-                        const float* bias, void* y, int64_t ldy, void* stream);
+                        const float* bias, void* y, int64_t ldy, int32_t flags, void* stream);
 
 /* Gate and up projection of a SwiGLU MLP in one pass over the weights, with the activation
  * fused: wq is [N2 = 2F, K] with rows interleaved in blocks of 8 (rows 16t..16t+7 are gate
@@ -233,10 +239,11 @@ int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K
  * way; y[b, h] = silu(gate_h) * up_h in the activation type (bf16 / f16), F columns.
  * The unfused form in the reference is two quantized Linears followed by eager silu and
  * multiply ops (lucid/nn/quantized/linear.py:206-214; fusion listed as a follow-up of the
- * quantized_matmul path, lucid/_C/ops/quantized/QuantizedMatmul.cpp:143-207). */
+ * quantized_matmul path, lucid/_C/ops/quantized/QuantizedMatmul.cpp:143-207).
+ * flags as for lc_wo_linear_s8; batch <= 32. */
 int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
                         const int8_t* wq, int64_t ldw, int64_t N2, const float* sw, const float* bias,
-                        void* y, int64_t ldy, void* stream);
+                        void* y, int64_t ldy, int32_t flags, void* stream);
 
 /* Synchronises the device and reads the status word of the weight-only kernels on the
  * current device: 0, or the code of a bounded device-side wait that ran out (the

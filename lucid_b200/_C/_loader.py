@@ -59,8 +59,8 @@ SIGNATURES = {
     "lc_qlinear_i8_multi": (_i32, [_p, _i32, _i64, _p, _i64, _i64, _i64, _i64, _p, _i32, _p, _p, _p, _p,
                                    C.POINTER(C.c_void_p), _i32, _i32, _i64, _p, _i32, _p]),
     "lc_rowsum_s8": (_i32, [_p, _i64, _i64, _i64, _p, _p]),
-    "lc_wo_linear_s8": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _p]),
-    "lc_wo_swiglu_s8": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _p]),
+    "lc_wo_linear_s8": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _i32, _p]),
+    "lc_wo_swiglu_s8": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _i32, _p]),
     "lc_wo_linear_status": (_i32, [C.POINTER(_i32), _i32]),
     "lc_group_quantize_f32": (_i32, [_p, _i64, _i64, _i32, _i32, _p, _p, _p, _p]),
     "lc_group_dequantize": (_i32, [_p, _p, _p, _i64, _i64, _i32, _i32, _p, _p]),

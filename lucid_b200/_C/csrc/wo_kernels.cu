@@ -302,7 +302,8 @@ template <typename XT, int NT, int TMAX, int XB, bool SWIGLU>
 __global__ void __launch_bounds__(ring::kThreads, 1)
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
-                      const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, int tiles_per_cta) {
+                      const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, int tiles_per_cta,
+                      int overlap) {
   using namespace ring;
   constexpr int S = stages(NT, TMAX, XB);
   static_assert(S >= 3, "ring too shallow");
@@ -339,6 +340,10 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   }
   __syncthreads();
 
+  // Programmatic dependent launch: let the next kernel on the stream be scheduled onto SMs as
+  // this grid's CTAs leave them (it orders itself with griddepcontrol.wait where it needs to).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
   if (warp == kConsumerWarps) {
     // ===================== producer =====================
     if (lane == 0) {
@@ -346,6 +351,24 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       uint32_t phase = 0;
       uint32_t armed_mask = 0, armed_parity = 0, xarmed_mask = 0, xarmed_parity = 0;  // bit per stage
       bool ok = true;
+      // Weights do not depend on the kernel before this one: when the launch may overlap it,
+      // fill the ring with the first items of the first pass (in consumption order), and only
+      // then wait for the preceding grid, whose output the activations are.  Without overlap
+      // the wait returns at once and loads are issued in consumption order (the first
+      // activation chunk must not queue behind a ring-full of weights).
+      int prefilled = 0;
+      if (overlap) {
+        const int pass0 = my_tiles < TMAX ? my_tiles : TMAX;
+        for (int kc = 0; kc < num_kc && prefilled < S; ++kc)
+          for (int j = 0; j < pass0 && prefilled < S; ++j, ++prefilled) {
+            wo_mbar_expect(full_bar(prefilled), STAGE);
+            wo_tma_load_2d(base + prefilled * STAGE, &tmap_w, kc * (KC / 4), static_cast<int>((tile0 + j) << 4),
+                           full_bar(prefilled));
+            armed_mask |= 1u << prefilled;  // parity 0
+          }
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      int issued = 0;  // weight items walked so far (the first `prefilled` are already in flight)
       for (int t0 = 0; t0 < my_tiles && ok; t0 += TMAX) {
         const int pass_tiles = my_tiles - t0 < TMAX ? my_tiles - t0 : TMAX;
         for (int kc = 0; kc < num_kc && ok; ++kc, ++xi) {
@@ -361,17 +384,19 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           wo_tma_load_2d(x_base + xb * COLS * X_PITCH, &tmap_x, kc * (KC / 4), 0, xfull_bar(xb));
           xarmed_mask |= 1u << xb;
           xarmed_parity = (xarmed_parity & ~(1u << xb)) | (xphase << xb);
-          for (int j = 0; j < pass_tiles; ++j) {
-            if (!wo_mbar_wait(empty_bar(stage), phase ^ 1u)) {
-              atomicCAS(&g_wo_status, 0, 1);
-              ok = false;
-              break;
+          for (int j = 0; j < pass_tiles; ++j, ++issued) {
+            if (issued >= prefilled) {
+              if (!wo_mbar_wait(empty_bar(stage), phase ^ 1u)) {
+                atomicCAS(&g_wo_status, 0, 1);
+                ok = false;
+                break;
+              }
+              const int row0 = static_cast<int>((tile0 + t0 + j) << 4);
+              wo_mbar_expect(full_bar(stage), STAGE);
+              wo_tma_load_2d(base + stage * STAGE, &tmap_w, kc * (KC / 4), row0, full_bar(stage));
+              armed_mask |= 1u << stage;
+              armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
             }
-            const int row0 = static_cast<int>((tile0 + t0 + j) << 4);
-            wo_mbar_expect(full_bar(stage), STAGE);
-            wo_tma_load_2d(base + stage * STAGE, &tmap_w, kc * (KC / 4), row0, full_bar(stage));
-            armed_mask |= 1u << stage;
-            armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
             if (++stage == S) {
               stage = 0;
               phase ^= 1u;
@@ -387,6 +412,9 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     }
   } else {
     // ===================== consumers =====================
+    // nothing to do before the activations exist; the bounded waits below start counting
+    // only once the preceding grid is complete
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int g = lane >> 2, t = lane & 3;
     const int koff = warp * 64 + t * 16;  // this lane's byte offset inside an item row
     int stage = 0, xi = 0;
@@ -756,7 +784,7 @@ static int32_t launch_wo_mma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
 template <typename XT, int NT, int TMAX, int XB, bool SWIGLU = false>
 static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                    int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
-                                   int64_t ldy, cudaStream_t st) {
+                                   int64_t ldy, bool overlap, cudaStream_t st) {
   auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
@@ -783,25 +811,36 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   const int64_t sms = sm_count();
   const int64_t per = (tiles + sms - 1) / sms;
   const unsigned grid = static_cast<unsigned>((tiles + per - 1) / per);
-  kernel<<<grid, ring::kThreads, ring::kSmemBudget, st>>>(map_w, map_x, B, K, N, sw, bias, y, ldy,
-                                                          static_cast<int>(per));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(ring::kThreads);
+  cfg.dynamicSmemBytes = ring::kSmemBudget;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap ? 1 : 0;
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, B, K, N, sw, bias, y, ldy,
+                                             static_cast<int>(per), overlap ? 1 : 0);
+  if (err != cudaSuccess) return fail(LC_ERR_CUDA, "wo_linear_s8 (ring): %s", cudaGetErrorString(err));
   return check_launch("wo_linear_s8 (ring)");
 }
 
 template <typename XT, bool SWIGLU = false>
 static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w, int64_t ldw,
                              int64_t N, const float* sw, const float* bias, XT* y, int64_t ldy,
-                             cudaStream_t st) {
+                             bool overlap, cudaStream_t st) {
   // few row tiles per CTA (short, wide matrices): small reduction buffer, more activation chunks in flight
   const int64_t tiles = (N + 15) / 16, sms = sm_count();
   const bool few = (tiles + sms - 1) / sms <= 2;
   if (B <= 8)
-    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st)
-               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st)
+               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
   if (B <= 16)
-    return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st)
-               : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
-  return launch_wo_ring_inst<XT, 4, 1, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, st);
+    return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st)
+               : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
+  return launch_wo_ring_inst<XT, 4, 1, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
 }
 
 template <typename XT>
@@ -821,7 +860,7 @@ static int32_t launch_wo_fma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
 template <typename XT>
 static int32_t wo_linear_typed(const void* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                int64_t ldw, int64_t N, const float* sw, const float* bias, void* y,
-                               int64_t ldy, cudaStream_t st) {
+                               int64_t ldy, bool overlap, cudaStream_t st) {
   const XT* xt = static_cast<const XT*>(x);
   XT* yt = static_cast<XT*>(y);
   const bool mma_ok = sizeof(XT) == 2 && K % 16 == 0 && ldw % 16 == 0 && ldx % 8 == 0 &&
@@ -834,7 +873,7 @@ static int32_t wo_linear_typed(const void* x, int64_t B, int64_t K, int64_t ldx,
       // are latency-bound and use the direct-load kernel
       const bool big = N * K >= (int64_t{4} << 20);
       rc = !mma_ok ? launch_wo_fma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st)
-           : big   ? launch_wo_tma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st)
+           : big   ? launch_wo_tma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, overlap, st)
                    : launch_wo_mma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st);
     } else {
       rc = launch_wo_fma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st);
@@ -877,7 +916,8 @@ using namespace lc;
 extern "C" int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K,
                                    int64_t ldx, const int8_t* wq, int64_t ldw, int64_t N,
                                    const float* sw, const float* bias, void* y, int64_t ldy,
-                                   void* stream) {
+                                   int32_t flags, void* stream) {
+  const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;
   if (batch < 0 || N < 0 || K <= 0 || ldx < K || ldw < K || ldy < N)
     return fail(LC_ERR_INVALID_ARG, "wo_linear_s8: bad shape");
   if (batch == 0 || N == 0) return LC_OK;
@@ -885,18 +925,19 @@ extern "C" int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch
   cudaStream_t st = as_stream(stream);
   switch (x_dtype) {
     case LC_F32:
-      return wo_linear_typed<float>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, st);
+      return wo_linear_typed<float>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, st);
     case LC_BF16:
-      return wo_linear_typed<__nv_bfloat16>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, st);
+      return wo_linear_typed<__nv_bfloat16>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, st);
     case LC_F16:
-      return wo_linear_typed<__half>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, st);
+      return wo_linear_typed<__half>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, st);
   }
   return fail(LC_ERR_UNSUPPORTED, "wo_linear_s8: x_dtype %d not supported", x_dtype);
 }
 
 extern "C" int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
                                    const int8_t* wq, int64_t ldw, int64_t N2, const float* sw,
-                                   const float* bias, void* y, int64_t ldy, void* stream) {
+                                   const float* bias, void* y, int64_t ldy, int32_t flags, void* stream) {
+  const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;
   if (batch < 0 || N2 < 0 || K <= 0 || ldx < K || ldw < K || ldy < N2 / 2)
     return fail(LC_ERR_INVALID_ARG, "wo_swiglu_s8: bad shape");
   if (N2 % 16) return fail(LC_ERR_INVALID_ARG, "wo_swiglu_s8: the interleaved weight needs a multiple of 16 rows");
@@ -908,10 +949,10 @@ extern "C" int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch
   cudaStream_t st = as_stream(stream);
   if (x_dtype == LC_BF16)
     return launch_wo_tma<__nv_bfloat16, true>(static_cast<const __nv_bfloat16*>(x), batch, K, ldx, wq, ldw, N2, sw,
-                                              bias, static_cast<__nv_bfloat16*>(y), ldy, st);
+                                              bias, static_cast<__nv_bfloat16*>(y), ldy, overlap, st);
   if (x_dtype == LC_F16)
     return launch_wo_tma<__half, true>(static_cast<const __half*>(x), batch, K, ldx, wq, ldw, N2, sw, bias,
-                                       static_cast<__half*>(y), ldy, st);
+                                       static_cast<__half*>(y), ldy, overlap, st);
   return fail(LC_ERR_UNSUPPORTED, "wo_swiglu_s8: activations must be bf16 or f16");
 }
 

@@ -370,8 +370,12 @@ def qlinear_i8_into(a, b, sx, sw, out_ptrs, ldo: int, out_dtype: torch.dtype = t
 # ----------------------------------------------------------------------------
 # weight-only paths
 # ----------------------------------------------------------------------------
-def wo_linear_s8(x2d, wq, sw, bias=None):
-    """``y = (x @ wq^T) * sw + bias`` with float activations; ``y`` has ``x``'s dtype."""
+def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous: bool = False):
+    """``y = (x @ wq^T) * sw + bias`` with float activations; ``y`` has ``x``'s dtype.
+
+    ``overlap_previous`` lets the kernel start (and prefetch weights) while the kernel before
+    it on the stream drains; the caller asserts that ``wq``, ``sw`` and ``bias`` were complete
+    before that kernel started."""
     dev = _need_cuda(x2d, wq, sw, bias)
     if x2d.dtype not in (torch.float32, torch.bfloat16, torch.float16):
         raise TypeError(f"wo_linear_s8: activations must be fp32/bf16/fp16, got {x2d.dtype}")
@@ -387,7 +391,8 @@ def wo_linear_s8(x2d, wq, sw, bias=None):
     bias_c = None if bias is None else _f32c(bias)
     with _on(dev):
         check(lib.lc_wo_linear_s8(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq.data_ptr(),
-                                  wq.stride(0), N, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N, _stream(dev)))
+                                  wq.stride(0), N, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N,
+                                  1 if overlap_previous else 0, _stream(dev)))
     return y
 
 
@@ -403,9 +408,10 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.cat([g, u], dim=1).reshape(2 * f, *gate.shape[1:]).contiguous()
 
 
-def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None):
+def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None, overlap_previous: bool = False):
     """``silu(x @ Wg^T * sg) * (x @ Wu^T * su)`` with interleaved int8 gate/up weights
-    (see :func:`interleave_gate_up`); bf16 / f16 activations, batch <= 32."""
+    (see :func:`interleave_gate_up`); bf16 / f16 activations, batch <= 32.
+    ``overlap_previous`` as for :func:`wo_linear_s8`."""
     dev = _need_cuda(x2d, wq_gu, sw_gu, bias_gu)
     x2d = x2d.contiguous()
     B, K = x2d.shape
@@ -415,7 +421,8 @@ def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None):
     bias_c = None if bias_gu is None else _f32c(bias_gu)
     with _on(dev):
         check(lib.lc_wo_swiglu_s8(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq_gu.data_ptr(),
-                                  wq_gu.stride(0), N2, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N2 // 2, _stream(dev)))
+                                  wq_gu.stride(0), N2, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N2 // 2,
+                                  1 if overlap_previous else 0, _stream(dev)))
     return y
 
 

@@ -103,7 +103,7 @@ def qlinear_i8(a, b, sx, sw, bias=None, zx=None, wsum=None, out_dtype=torch.floa
     return torch.tensor(y.astype(np.float32)).to(out_dtype)
 
 
-def wo_linear_s8(x2d, wq, sw, bias=None):
+def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous=False):
     y = O.weight_only_linear_perchannel(_np(x2d.float()), _np(wq), _np(sw), None if bias is None else _np(bias))
     return torch.tensor(y).to(x2d.dtype)
 

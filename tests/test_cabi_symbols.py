@@ -62,7 +62,7 @@ def test_argument_validation_without_gpu(capi):
     p = (p + 15) // 16 * 16
     rc = L.lc_qlinear_i8(p, 0, 24, p, 32, 1, 1, 24, p, 0, None, None, None, None, p, capi.LC_F32, 1, None, None)
     assert rc == capi.LC_ERR_UNSUPPORTED and "16-byte" in capi.last_error()
-    rc = L.lc_wo_linear_s8(p, 99, 1, 16, 16, p, 16, 1, None, None, p, 1, None)
+    rc = L.lc_wo_linear_s8(p, 99, 1, 16, 16, p, 16, 1, None, None, p, 1, 0, None)
     assert rc == capi.LC_ERR_UNSUPPORTED
 
 

@@ -161,3 +161,62 @@ def test_wo_swiglu_fused(ops, dtype, B, F, K):
     assert y.shape == (B, F) and y.dtype == dtype
     assert torch.allclose(y.double(), ref, rtol=tol, atol=tol * float(ref.abs().max()))
     assert ops.wo_linear_status() == 0
+
+
+@pytest.mark.parametrize("B", [1, 16])
+def test_launch_overlap_is_bit_identical(ops, B):
+    """A chain of MLPs in which every kernel may start while its predecessor drains
+    (weights prefetched early, activations read only after the predecessor is complete)
+    gives the same bits as the fully serialised chain, eagerly and as a replayed graph."""
+    H, F = 4096, 14336
+    g = torch.Generator(device="cuda").manual_seed(7 + B)
+    wgu = torch.randint(-128, 128, (2 * F, H), device="cuda", dtype=torch.int8, generator=g)
+    sgu = torch.rand(2 * F, device="cuda", generator=g) * 4e-4
+    wd = torch.randint(-128, 128, (H, F), device="cuda", dtype=torch.int8, generator=g)
+    sd = torch.rand(H, device="cuda", generator=g) * 4e-4
+    x0 = torch.randn(B, H, device="cuda", generator=g).to(torch.bfloat16)
+    torch.cuda.synchronize()
+
+    def chain(overlap, depth=3):
+        x = x0 * 1.0  # an ordinary kernel writes the first input right before the chain
+        outs = []
+        for _ in range(depth):
+            h = ops.wo_swiglu_s8(x, wgu, sgu, overlap_previous=overlap)
+            x = ops.wo_linear_s8(h, wd, sd, overlap_previous=overlap)
+            outs.append(x)
+        return torch.stack(outs)
+
+    want = chain(False)
+    got = chain(True)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert float(want[0].float().abs().max()) > 0.0
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        chain(True)  # warm-up outside capture
+        with torch.cuda.graph(graph, stream=side):
+            captured = chain(True)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured.view(torch.int16), want.view(torch.int16))
+    assert ops.wo_linear_status() == 0
+
+
+@pytest.mark.parametrize("B,N,K", [(1, 4096, 14336), (4, 14336, 4096), (16, 512, 65536), (32, 6000, 3000 * 16 // 16 * 16)])
+def test_streaming_kernel_is_deterministic(ops, B, N, K):
+    """The split-K sums of the streaming kernel are added in a fixed order: 25 back-to-back
+    launches, alternately serialised and overlapping their predecessor, give identical bits."""
+    g = torch.Generator(device="cuda").manual_seed(B + N + K)
+    wq = torch.randint(-128, 128, (N, K), device="cuda", dtype=torch.int8, generator=g)
+    sw = torch.rand(N, device="cuda", generator=g) * 0.01 + 0.001
+    x = torch.randn(B, K, device="cuda", generator=g).to(torch.bfloat16)
+    first = ops.wo_linear_s8(x, wq, sw)
+    ref = (x.double() @ wq.double().T) * sw.double()[None, :]
+    assert torch.allclose(first.double(), ref, rtol=1e-2, atol=1e-2 * float(ref.abs().max()))
+    for i in range(24):
+        again = ops.wo_linear_s8(x, wq, sw, overlap_previous=bool(i & 1))
+        assert torch.equal(again.view(torch.int16), first.view(torch.int16)), f"launch {i + 2} differs"
+    assert ops.wo_linear_status() == 0
