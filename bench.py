@@ -317,6 +317,8 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
         "dequantize_per_channel": (lambda: ops.dequantize(q, s, z, ch_axis=0), x.numel() * 5),
         "quantize_per_channel_given_scale": (lambda: ops.quantize(x, s, z, -128, 127, torch.int8, ch_axis=0),
                                              x.numel() * 5),
+        # calibration pass of the histogram observer: 2048 bins over the data range
+        "histc_2048_bins": (lambda: ops.histc(x, 2048, -60.0, 60.0), x.numel() * 4),
     }
     rt = {}
     for name, (fn, nbytes) in cases.items():
@@ -416,6 +418,9 @@ def run_profile_case(args) -> int:
         b = torch.randint(-128, 128, (N, K), device=dev, dtype=torch.int8, generator=g)
         sx, sw = torch.rand(M, device=dev), torch.rand(N, device=dev)
         fn = lambda: ops.qlinear_i8(a, b, sx, sw)  # noqa: E731
+    elif case == "histc":
+        x = torch.randn(8192, 8192, device=dev, generator=g)
+        fn = lambda: ops.histc(x, 2048, -6.0, 6.0)  # noqa: E731
     elif case in ("quantize_rows", "quantize_tensor", "dequantize", "quantize_given_scale"):
         x = torch.randn(8192, 8192, device=dev, generator=g)
         q, s, z = ops.dynamic_quantize_rows(x, True, -128, 127, True)
@@ -678,7 +683,7 @@ def main() -> int:
                     help="headline workload only: skip the companion workloads and the CPU baseline")
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed case of one kernel (gemm, quantize_rows, quantize_tensor, "
-                         "dequantize, quantize_given_scale, wo_gemv) for a profiler capture; prints no bench line")
+                         "dequantize, quantize_given_scale, histc, wo_gemv) for a profiler capture; prints no bench line")
     ap.add_argument("--profile-batch", default=4)
     ap.add_argument("--gather", choices=("auto", "fused", "nccl"), default="auto",
                     help="N > 1: how output shards are exchanged (auto = fused if symmetric memory works)")

@@ -92,6 +92,19 @@ int32_t lc_observe_tensor_static_f32(const float* x, int64_t n, float* min_out, 
                                      int32_t quant_max, int32_t is_signed, float eps,
                                      float* scale_out, float* zp_out, void* stream);
 
+/* lucid.histc as the histogram observer calls it (lucid/quantization/observer.py:852-870):
+ * counts of x in `bins` equal-width bins over [lo, hi], lo < hi finite (the caller resolves
+ * the lo == hi conventions of lucid/_ops/_adapters.py:1256-1279).  Bucketing in float64 like
+ * the reference's CPU kernel (lucid/_C/backend/cpu/methods/Reduction.cpp:839-888): values
+ * outside the range and NaN are skipped, bin = trunc((x - lo) / ((hi - lo) / bins)), the
+ * right edge falls into the last bin; counts are exact integers converted to fp32 once
+ * (lucid/_C/ops/composite/Stats.cpp:78-89).  accumulate != 0 adds the counts to `out`.
+ * workspace: lc_histc_workspace_bytes(bins) bytes, 16-byte aligned, zero-filled once by the
+ * caller; the kernel leaves it zero.  bins <= 16384. */
+int64_t lc_histc_workspace_bytes(int32_t bins);
+int32_t lc_histc_f32(const float* x, int64_t n, int32_t bins, double lo, double hi, float* out,
+                     int32_t accumulate, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* PerChannelMinMaxObserver.forward: per-channel min and max over every other
  * axis (lucid/quantization/observer.py:672-686). */
 int32_t lc_observe_channel_f32(const float* x, int64_t outer, int64_t channels, int64_t inner,
@@ -139,6 +152,18 @@ int32_t lc_fake_quantize_f32(const float* x, int64_t outer, int64_t channels, in
                              int64_t n_zp, float host_inv_scale, float host_scale,
                              float host_zero_point, int32_t quant_min, int32_t quant_max,
                              float* out, float* mask_out, void* stream);
+
+/* fake_quantize of an element-wise merge in one pass: out = fq(a + b), fq(a * b) or
+ * fq(relu(a + b)) on a per-tensor grid; b == NULL merges with host_scalar instead.  The
+ * converted residual add of the reference (QFunctional.add / mul / add_relu / add_scalar /
+ * mul_scalar, lucid/nn/quantized/functional_module.py:125-330, on _QuantizedGridModule._fake_quant,
+ * lucid/nn/quantized/_utils.py:29-45), which runs the merge and the fake-quantize chain as
+ * separate eager ops.  op: 0 add, 1 mul, 2 add + ReLU.  scale / zero_point: device scalars,
+ * or NULL for the host values (as in lc_fake_quantize_f32). */
+int32_t lc_fake_quantize_merge_f32(const float* a, const float* b, float host_scalar, int32_t op,
+                                   int64_t n, const float* scale, const float* zero_point,
+                                   float host_inv_scale, float host_scale, float host_zero_point,
+                                   int32_t quant_min, int32_t quant_max, float* out, void* stream);
 
 /* ---- fused dynamic activation quantization ---------------------------
  * One pass per row: observer + calculate_qparams + quantize for a [rows, cols]

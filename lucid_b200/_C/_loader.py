@@ -47,6 +47,9 @@ SIGNATURES = {
     "lc_observe_tensor_f32": (_i32, [_p, _i64, _p, _p, _i32, _i32, _i32, _i32, _i32, _f, _p, _p, _p, _i64, _p]),
     "lc_observe_tensor_static_max_elems": (_i64, []),
     "lc_observe_tensor_static_f32": (_i32, [_p, _i64, _p, _p, _i32, _i32, _i32, _i32, _i32, _f, _p, _p, _p]),
+    "lc_fake_quantize_merge_f32": (_i32, [_p, _p, _f, _i32, _i64, _p, _p, _f, _f, _f, _i32, _i32, _p, _p]),
+    "lc_histc_workspace_bytes": (_i64, [_i32]),
+    "lc_histc_f32": (_i32, [_p, _i64, _i32, C.c_double, C.c_double, _p, _i32, _p, _i64, _p]),
     "lc_observe_channel_f32": (_i32, [_p, _i64, _i64, _i64, _p, _p, _i32, _p]),
     "lc_calculate_qparams_f32": (_i32, [_p, _p, _i64, _i32, _i32, _i32, _i32, _f, _p, _p, _p]),
     "lc_quantize_f32": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _p, _i64, _f, _f, _i32, _i32, _p, _i32, _p]),

@@ -410,6 +410,58 @@ fake_quantize_seg_kernel(const float* __restrict__ x, float* __restrict__ out,
   }
 }
 
+// fake_quantize of an element-wise merge, the converted form of a residual add
+// (lucid/nn/quantized/functional_module.py QFunctional.add / mul / add_relu and the scalar
+// variants): t = a (+|*) b in fp32, optional ReLU that lets NaN through, then the per-tensor
+// grid.  One pass over two inputs and one output (12 B/elem) instead of the eager
+// merge (12 B) followed by the eager fake-quantize chain.
+enum : int { kMergeAdd = 0, kMergeMul = 1, kMergeAddRelu = 2 };
+
+template <int OP>
+__device__ __forceinline__ float merge_one(float a, float b) {
+  float t = OP == kMergeMul ? __fmul_rn(a, b) : __fadd_rn(a, b);
+  if (OP == kMergeAddRelu) t = (t < 0.0f) ? 0.0f : t;  // NaN compares false and stays
+  return t;
+}
+
+template <int OP, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+fake_quantize_merge_kernel(const float* __restrict__ a, const float* __restrict__ b, float scalar,
+                           float* __restrict__ out, int64_t n, ChannelParams p, float qmin, float qmax) {
+  float s, inv, z, m;
+  load_params(p, 0, s, inv, z);
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kChunk;
+  if (VEC) {
+    float4 va[kUnroll], vb[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + (static_cast<int64_t>(u) * kThreads + threadIdx.x) * 4;
+      if (i < n) {
+        va[u] = __ldcs(reinterpret_cast<const float4*>(a + i));
+        vb[u] = b ? __ldcs(reinterpret_cast<const float4*>(b + i)) : make_float4(scalar, scalar, scalar, scalar);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + (static_cast<int64_t>(u) * kThreads + threadIdx.x) * 4;
+      if (i < n) {
+        float4 r;
+        r.x = fake_one(merge_one<OP>(va[u].x, vb[u].x), s, inv, z, qmin, qmax, m);
+        r.y = fake_one(merge_one<OP>(va[u].y, vb[u].y), s, inv, z, qmin, qmax, m);
+        r.z = fake_one(merge_one<OP>(va[u].z, vb[u].z), s, inv, z, qmin, qmax, m);
+        r.w = fake_one(merge_one<OP>(va[u].w, vb[u].w), s, inv, z, qmin, qmax, m);
+        __stcs(reinterpret_cast<float4*>(out + i), r);
+      }
+    }
+  } else {
+#pragma unroll 4
+    for (int u = 0; u < 4 * kUnroll; ++u) {
+      const int64_t i = base + static_cast<int64_t>(u) * kThreads + threadIdx.x;
+      if (i < n) out[i] = fake_one(merge_one<OP>(__ldg(a + i), b ? __ldg(b + i) : scalar), s, inv, z, qmin, qmax, m);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
 fake_quantize_strided_kernel(const float* __restrict__ x, float* __restrict__ out,
                              float* __restrict__ mask_out, int64_t total, int64_t channels,
@@ -866,6 +918,35 @@ extern "C" int32_t lc_dequantize(const void* q, int32_t q_dtype, int64_t outer, 
                                      out_dtype, st);
   }
   return fail(LC_ERR_UNSUPPORTED, "dequantize: q_dtype %d not supported", q_dtype);
+}
+
+extern "C" int32_t lc_fake_quantize_merge_f32(const float* a, const float* b, float host_scalar, int32_t op,
+                                              int64_t n, const float* scale, const float* zero_point,
+                                              float host_inv_scale, float host_scale, float host_zero_point,
+                                              int32_t quant_min, int32_t quant_max, float* out, void* stream) {
+  if (n < 0 || op < kMergeAdd || op > kMergeAddRelu) return fail(LC_ERR_INVALID_ARG, "fake_quantize_merge: bad arguments");
+  if (n == 0) return LC_OK;
+  if (!a || !out) return fail(LC_ERR_INVALID_ARG, "fake_quantize_merge: null pointer");
+  ChannelParams p{scale, zero_point, 1, 1, host_inv_scale, host_scale, host_zero_point};
+  const float qmin = static_cast<float>(quant_min), qmax = static_cast<float>(quant_max);
+  const int64_t grid = (n + kChunk - 1) / kChunk;
+  if (grid > 0x7fffffffLL) return fail(LC_ERR_UNSUPPORTED, "tensor too large for one launch");
+  const bool vec = n % 4 == 0 && aligned(a, 16) && aligned(out, 16) && (!b || aligned(b, 16));
+  cudaStream_t st = as_stream(stream);
+#define LC_MERGE(OP)                                                                                          \
+  do {                                                                                                        \
+    if (vec)                                                                                                  \
+      fake_quantize_merge_kernel<OP, true><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(a, b, host_scalar, out, \
+                                                                                             n, p, qmin, qmax);     \
+    else                                                                                                      \
+      fake_quantize_merge_kernel<OP, false><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(a, b, host_scalar,    \
+                                                                                              out, n, p, qmin, qmax); \
+  } while (0)
+  if (op == kMergeAdd) LC_MERGE(kMergeAdd);
+  else if (op == kMergeMul) LC_MERGE(kMergeMul);
+  else LC_MERGE(kMergeAddRelu);
+#undef LC_MERGE
+  return check_launch("fake_quantize_merge");
 }
 
 extern "C" int32_t lc_fake_quantize_f32(const float* x, int64_t outer, int64_t channels,

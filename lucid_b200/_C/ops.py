@@ -94,6 +94,31 @@ def observe_workspace(dev: torch.device) -> torch.Tensor:
     return ws
 
 
+_HIST_WORKSPACES: dict[tuple[int, int, int], torch.Tensor] = {}
+
+
+def histc(x: torch.Tensor, bins: int, lo: float, hi: float, out: torch.Tensor | None = None,
+          accumulate: bool = False) -> torch.Tensor:
+    """fp32 counts of ``x`` in ``bins`` equal-width bins over the finite range ``lo < hi``
+    (float64 bucketing, NaN and out-of-range values skipped); ``accumulate`` adds to ``out``."""
+    dev = _need_cuda(x, out)
+    x = _f32c(x)
+    if out is None:
+        out = torch.empty(bins, dtype=torch.float32, device=dev)
+        accumulate = False
+    if out.dtype != torch.float32 or out.numel() != bins or not out.is_contiguous():
+        raise TypeError("histc: out must be a contiguous fp32 tensor of `bins` elements")
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev), int(bins))
+    ws = _HIST_WORKSPACES.get(key)
+    if ws is None:
+        ws = torch.zeros(int(lib.lc_histc_workspace_bytes(int(bins))), dtype=torch.uint8, device=dev)
+        _HIST_WORKSPACES[key] = ws
+    with _on(dev):
+        check(lib.lc_histc_f32(x.data_ptr(), x.numel(), int(bins), float(lo), float(hi), out.data_ptr(),
+                               int(accumulate), ws.data_ptr(), ws.numel(), _stream(dev)))
+    return out
+
+
 def channel_layout(shape, ch_axis: int | None) -> tuple[int, int, int]:
     """(outer, channels, inner) of a contiguous tensor split at ``ch_axis``."""
     if ch_axis is None:
@@ -225,6 +250,30 @@ def fake_quantize(x, scale, zero_point, qmin: int, qmax: int, ch_axis=None, want
                                        0 if z_t is None else z_t.numel(), h_inv, h_s, h_z, int(qmin),
                                        int(qmax), out.data_ptr(), _ptr(mask), _stream(dev)))
     return out, mask
+
+
+_MERGE_OPS = {"add": 0, "mul": 1, "add_relu": 2}
+
+
+def fake_quantize_merge(a, b, op: str, scale, zero_point, qmin: int, qmax: int):
+    """``fake_quantize(a + b)`` / ``(a * b)`` / ``relu(a + b)`` on a per-tensor grid in one pass;
+    ``b`` is a same-shape tensor or a Python scalar."""
+    dev = _need_cuda(a, b if isinstance(b, torch.Tensor) else None)
+    a = _f32c(a)
+    scalar = 0.0
+    if isinstance(b, torch.Tensor):
+        if b.shape != a.shape:
+            raise ValueError(f"fake_quantize_merge: shapes differ, {tuple(a.shape)} vs {tuple(b.shape)}")
+        b = _f32c(b)
+    else:
+        scalar, b = float(b), None
+    s_t, z_t, h_inv, h_s, h_z = _params(scale, zero_point, dev, 1, False)
+    out = torch.empty_like(a)
+    with _on(dev):
+        check(lib.lc_fake_quantize_merge_f32(a.data_ptr(), _ptr(b), scalar, _MERGE_OPS[op], a.numel(), _ptr(s_t),
+                                             _ptr(z_t), h_inv, h_s, h_z, int(qmin), int(qmax), out.data_ptr(),
+                                             _stream(dev)))
+    return out
 
 
 # ----------------------------------------------------------------------------

@@ -57,13 +57,43 @@ randn, rand, arange = (_factory(f) for f in (_torch.randn, _torch.rand, _torch.a
 # free functions used by observers / qparams / modules
 round, clip, abs, maximum, minimum = _torch.round, _torch.clip, _torch.abs, _torch.maximum, _torch.minimum  # noqa: A001
 amin, amax, moveaxis, isinf, where = _torch.amin, _torch.amax, _torch.moveaxis, _torch.isinf, _torch.where
-histc, scatter_add, stack, matmul = _torch.histc, _torch.scatter_add, _torch.stack, _torch.matmul
+scatter_add, stack, matmul = _torch.scatter_add, _torch.stack, _torch.matmul
+
+
+def histc(input, bins=100, min=0.0, max=0.0):  # noqa: A002 - the reference's keywords
+    """``lucid.histc``: counts over ``[min, max]`` in ``bins`` equal-width bins, in the input's
+    dtype.  Range conventions of the reference's adapter (``lucid/_ops/_adapters.py:1256-1279``):
+    ``min == max`` takes the range from the data, a single-point range widens to
+    ``[v - 1, v + 1]``, a non-finite range is refused, NaN lies in no bin.  CUDA tensors are
+    counted by the library's histogram kernel; CPU tensors by ``torch.histc``, whose results the
+    reference's own tests pin it to (``lucid/test/unit/ops/test_adapter_index_stats.py:107-127``)."""
+    import math
+
+    lo, hi = float(min), float(max)
+    if lo > hi:
+        raise ValueError(f"histc: max must be at least min, got [{lo}, {hi}]")
+    if not input.is_floating_point():
+        raise NotImplementedError(f"histc: input must be a floating-point dtype, got {input.dtype}")
+    if lo == hi and input.numel() > 0:
+        lo, hi = float(input.min()), float(input.max())
+    if not (math.isfinite(lo) and math.isfinite(hi)):
+        raise ValueError(f"histc: range of [{lo}, {hi}] is not finite")
+    if lo == hi:
+        lo, hi = lo - 1.0, hi + 1.0
+    if not input.is_cuda:
+        return _torch.histc(input, bins=bins, min=lo, max=hi)
+    from lucid_b200 import _backend
+
+    return _backend.ops().histc(input.reshape(-1), int(bins), lo, hi).to(input.dtype)
+
 
 from lucid_b200 import backends, cuda  # noqa: E402
 from lucid_b200 import nn  # noqa: E402
 from lucid_b200 import quantization  # noqa: E402
+from lucid_b200 import serialization  # noqa: E402
+from lucid_b200.serialization import load, save  # noqa: E402
 
 __all__ = [
     "Tensor", "dtype", "device", "tensor", "zeros", "ones", "full", "empty", "zeros_like", "ones_like",
-    "full_like", "randn", "rand", "arange", "no_grad", "manual_seed", "backends", "cuda", "nn", "quantization",
+    "full_like", "randn", "rand", "arange", "histc", "no_grad", "manual_seed", "backends", "cuda", "nn", "quantization", "serialization", "save", "load",
 ]

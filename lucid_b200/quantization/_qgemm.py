@@ -32,11 +32,7 @@ def dequantize(wq, scales, biases, group_size: int = 64, bits: int = 8):
     return _backend.ops().group_dequantize(_backend.on_cuda(wq), _backend.on_cuda(scales), _backend.on_cuda(biases), group_size, bits)
 
 
-def quantized_matmul(x, wq, scales, biases, transpose: bool = True, group_size: int = 64, bits: int = 8):
-    """``x @ w_hat.T`` (``transpose=True``, the Linear form) or ``x @ w_hat`` with the
-    weight decoded inside the kernel; float activations, result in ``x``'s dtype."""
-    xd = _backend.on_cuda(x)
-    wq, scales, biases = _backend.on_cuda(wq), _backend.on_cuda(scales), _backend.on_cuda(biases)
+def _forward(xd, wq, scales, biases, transpose: bool, group_size: int, bits: int):
     lead = xd.shape[:-1]
     x2 = xd.reshape(-1, xd.shape[-1])
     if not transpose:
@@ -49,3 +45,39 @@ def quantized_matmul(x, wq, scales, biases, transpose: bool = True, group_size: 
         dense = _backend.ops().group_dequantize(wq, scales, biases, group_size, bits).to(xd.dtype)
         y = x2 @ dense.T
     return y.reshape(*lead, wq.shape[0])
+
+
+class _QuantizedMatmul(torch.autograd.Function):
+    """Differentiable in ``x`` only, like the engine's node: the backward decodes the packed
+    weight and multiplies, ``dX = dY @ w_hat`` for the Linear form and ``dY @ w_hat.T``
+    otherwise (``QuantizedMatmulBackward::apply``, ``lucid/_C/ops/quantized/QuantizedMatmul.cpp:73-90``).
+    This is what a LoRA adapter on a frozen quantized base layer trains through
+    (``lucid/peft/tuners/lora/_layer.py:988-1018``)."""
+
+    @staticmethod
+    def forward(ctx, xd, wq, scales, biases, transpose, group_size, bits):
+        ctx.save_for_backward(wq, scales, biases)
+        ctx.cfg = (transpose, group_size, bits)
+        return _forward(xd, wq, scales, biases, transpose, group_size, bits)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        wq, scales, biases = ctx.saved_tensors
+        transpose, group_size, bits = ctx.cfg
+        dense = _backend.ops().group_dequantize(wq, scales, biases, group_size, bits)
+        if not transpose:
+            dense = dense.T
+        if dense.dtype != grad_out.dtype:
+            dense = dense.to(grad_out.dtype)
+        return grad_out @ dense, None, None, None, None, None, None
+
+
+def quantized_matmul(x, wq, scales, biases, transpose: bool = True, group_size: int = 64, bits: int = 8):
+    """``x @ w_hat.T`` (``transpose=True``, the Linear form) or ``x @ w_hat`` with the
+    weight decoded inside the kernel; float activations, result in ``x``'s dtype.
+    Differentiable with respect to ``x``."""
+    xd = _backend.on_cuda(x)
+    wq, scales, biases = _backend.on_cuda(wq), _backend.on_cuda(scales), _backend.on_cuda(biases)
+    if xd.requires_grad and torch.is_grad_enabled():
+        return _QuantizedMatmul.apply(xd, wq, scales, biases, transpose, group_size, bits)
+    return _forward(xd, wq, scales, biases, transpose, group_size, bits)

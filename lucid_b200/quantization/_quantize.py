@@ -21,7 +21,9 @@ def _is_linear_relu(m: nn.Module) -> bool:
 
 
 def _observed_types() -> tuple[type, ...]:
-    return (nn.Linear,)
+    import lucid_b200.nn.quantized as nnq
+
+    return (nn.Linear, nnq.QuantStub, nnq.FloatFunctional)
 
 
 # ---- group-wise (engine "mlx_group") builders --------------------------------
@@ -93,31 +95,38 @@ def prepare(model: nn.Module, qconfig=None, inplace: bool = False) -> nn.Module:
 def convert(model: nn.Module, inplace: bool = False) -> nn.Module:
     """Swap every calibrated module for its quantized counterpart and drop the
     ``qconfig`` stamps."""
-    from lucid_b200.nn.quantized import Linear as QLinear
+    import lucid_b200.nn.quantized as nnq
 
     model = model if inplace else copy.deepcopy(model)
-    build = _group_linear_builder if backends.quantized.use_mlx() else QLinear.from_float
-    _convert_children(model, {nn.Linear: build})
+    build = _group_linear_builder if backends.quantized.use_mlx() else nnq.Linear.from_float
+    mapping = {nn.Linear: build, nnq.QuantStub: nnq.Quantize.from_float, nnq.DeQuantStub: nnq.DeQuantize.from_float,
+               nnq.FloatFunctional: nnq.QFunctional.from_float}
+    _convert_children(model, mapping, always=(nnq.DeQuantStub,))
     QConfigResolver.strip(model)
     model.eval()
     return model
 
 
-def _convert_children(module: nn.Module, mapping) -> None:
+def _convert_children(module: nn.Module, mapping, always: tuple[type, ...] = ()) -> None:
+    """Swap calibrated children (and the ``always`` types, which carry no state to calibrate,
+    unless ``prepare`` stamped them ``qconfig = None``) in their original slots."""
     for name, child in list(module.named_children()):
         build = mapping.get(type(child))
-        if build is not None and hasattr(child, "activation_post_process"):
+        stateless = isinstance(child, always) and getattr(child, "qconfig", True) is not None
+        if build is not None and (hasattr(child, "activation_post_process") or stateless):
             child._forward_hooks.clear()
             setattr(module, name, build(child))
         else:
-            _convert_children(child, mapping)
+            _convert_children(child, mapping, always)
 
 
 # ---- dynamic PTQ -------------------------------------------------------------------
 def _dynamic_builders():
     import lucid_b200.nn.quantized.dynamic as nnqd
 
-    builders = {nn.Linear: nnqd.Linear.from_float}
+    builders = {nn.Linear: nnqd.Linear.from_float, nn.LSTM: nnqd.LSTM.from_float, nn.GRU: nnqd.GRU.from_float,
+                nn.LSTMCell: nnqd.LSTMCell.from_float, nn.GRUCell: nnqd.GRUCell.from_float,
+                nn.RNNCell: nnqd.RNNCell.from_float}
     if backends.quantized.use_mlx():
         builders[nn.Linear] = _group_dynamic_builder
     return builders

@@ -192,19 +192,30 @@ class HistogramObserver(ObserverBase):
         dst = torch.clip((centres - new_lo) / new_w, 0.0, float(self.bins - 1)).to(torch.int64)
         return torch.zeros(self.bins, device=hist.device).scatter_add(0, dst, hist)
 
+    def _count(self, xd, lo: float, hi: float):
+        """``lucid.histc(x, bins, lo, hi)`` of the batch (``observer.py:861,864`` in the reference)."""
+        if lo == hi:  # the adapter's single-point convention
+            lo, hi = lo - 1.0, hi + 1.0
+        return _backend.ops().histc(xd.reshape(-1), self.bins, lo, hi)
+
     @torch.no_grad()
     def forward(self, x):
         xd = self._observed(x)
         if not xd.numel():
             return x
-        lo, hi = float(xd.min()), float(xd.max())
+        # the running range decides the bins, so it is read back (a sanctioned host round trip,
+        # lucid/quantization/observer.py:855-856); one fused min/max pass instead of two
+        mn = torch.empty((), dtype=torch.float32, device=xd.device)
+        mx = torch.empty((), dtype=torch.float32, device=xd.device)
+        _backend.ops().observe_tensor(xd, mn, mx, accumulate=False)
+        lo, hi = float(mn), float(mx)
         old_lo, old_hi = float(self.min_val), float(self.max_val)
         if old_lo == _INF:
             new_lo, new_hi = lo, hi
-            hist = torch.histc(xd, bins=self.bins, min=new_lo, max=new_hi)
+            hist = self._count(xd, new_lo, new_hi)
         else:
             new_lo, new_hi = min(old_lo, lo), max(old_hi, hi)
-            hist = torch.histc(xd, bins=self.bins, min=new_lo, max=new_hi)
+            hist = self._count(xd, new_lo, new_hi)
             if (new_lo, new_hi) == (old_lo, old_hi):
                 hist = hist + self.histogram
             else:

@@ -369,6 +369,34 @@ def group_matmul(x, packed, scales, biases, group_size: int = 64, bits: int = 8)
 # seeded synthetic workloads (shapes and value distributions of the five
 # benchmark configurations)
 # --------------------------------------------------------------------------
+def histc(x, bins: int = 100, lo: float = 0.0, hi: float = 0.0) -> np.ndarray:
+    """Counts of ``x`` in ``bins`` equal-width bins over ``[lo, hi]``, in ``x``'s dtype.
+
+    Range handling of the Python adapter (lucid/_ops/_adapters.py:1256-1279): ``lo == hi``
+    takes the range from the data, a range that is still one point widens to
+    ``[v - 1, v + 1]``, a non-finite range is refused, NaN is sent below the range.
+    Bucketing of the CPU kernel (lucid/_C/backend/cpu/methods/Reduction.cpp:839-888) in
+    float64: ``step = (hi - lo) / bins``, values outside ``[lo, hi]`` are skipped,
+    ``bin = trunc((v - lo) / step)`` with the right edge clamped into the last bin; counts
+    are cast to the input dtype once (lucid/_C/ops/composite/Stats.cpp:78-89)."""
+    x = np.asarray(x)
+    lo, hi = float(lo), float(hi)
+    if lo > hi:
+        raise ValueError(f"histc: max must be at least min, got [{lo}, {hi}]")
+    if lo == hi and x.size:
+        lo, hi = float(x.min()), float(x.max())
+    if not (np.isfinite(lo) and np.isfinite(hi)):
+        raise ValueError(f"histc: range of [{lo}, {hi}] is not finite")
+    if lo == hi:
+        lo, hi = lo - 1.0, hi + 1.0
+    v = x.astype(np.float64).ravel()
+    v = np.where(np.isnan(v), -np.inf, v)
+    step = (hi - lo) / float(bins)
+    v = v[(v >= lo) & (v <= hi)]
+    b = np.minimum(((v - lo) / step).astype(np.int64), bins - 1)
+    return np.bincount(b, minlength=bins).astype(np.float64).astype(x.dtype if x.dtype.kind == "f" else np.float32)
+
+
 def synth_config1(seed: int = 20260921):
     r = np.random.default_rng(seed)
     x = r.standard_normal((64, 1024), dtype=F32)

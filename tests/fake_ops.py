@@ -19,6 +19,25 @@ def _qd(qmin, qmax, storage="int8", signed=None):
 _STORE = {torch.int8: "int8", torch.uint8: "uint8", torch.int16: "int16", torch.int32: "int32"}
 
 
+def fake_quantize_merge(a, b, op, scale, zero_point, qmin, qmax):
+    an = _np(a.float())
+    bn = _np(b.float()) if isinstance(b, torch.Tensor) else np.float32(b)
+    t = (an * bn if op == "mul" else an + bn).astype(np.float32)
+    if op == "add_relu":
+        t = np.where(t < 0, np.float32(0), t)
+    s = _np(scale) if isinstance(scale, torch.Tensor) else float(scale)
+    z = _np(zero_point) if isinstance(zero_point, torch.Tensor) else float(zero_point)
+    return torch.tensor(O.fake_quantize(t, s, z, qmin, qmax)[0])
+
+
+def histc(x, bins, lo, hi, out=None, accumulate=False):
+    h = torch.tensor(O.histc(_np(x.float()), bins, lo, hi))
+    if out is None:
+        return h
+    out.copy_(out + h if accumulate else h)
+    return out
+
+
 def observe_tensor(x, min_out, max_out, accumulate, qspec=None):
     mn, mx = O.minmax_tensor(_np(x))
     if accumulate:

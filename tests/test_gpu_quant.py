@@ -219,3 +219,35 @@ def test_full_size_roundtrip_properties(ops):
     qt, st, zt, mm = ops.dynamic_quantize_tensor(x, True, -128, 127, True, 1e-8, torch.int8)
     assert float(mm[0]) == float(x.min()) and float(mm[1]) == float(x.max())
     np.testing.assert_array_equal(host(qt[rows]), O.quantize(xs, host(st), 0.0 + host(zt), O.qint8))
+
+
+@pytest.mark.parametrize("n", [1, 5, 4096, 4099, 1 << 20])
+@pytest.mark.parametrize("op", ["add", "mul", "add_relu"])
+def test_fake_quantize_merge_matches_oracle(n, op):
+    """One-pass merge + fake-quantize against the oracle's composition of the eager ops
+    (bit-exact: both round the merge once in fp32), tensor and scalar operands, device and
+    host qparams, NaN passing through the ReLU."""
+    from lucid_b200._C import ops
+
+    r = np.random.default_rng(n)
+    a = (r.standard_normal(n) * 3).astype(np.float32)
+    b = (r.standard_normal(n) * 3).astype(np.float32)
+    if n > 4:
+        a[2], b[3] = np.nan, np.inf
+    s, z = np.float32(0.043), np.float32(101.0)
+
+    def want(bb):
+        t = (a * bb if op == "mul" else a + bb).astype(np.float32)
+        if op == "add_relu":
+            t = np.where(t < 0, np.float32(0), t)
+        return O.fake_quantize(t, s, z, 0, 255)[0]
+
+    at, bt = torch.tensor(a, device="cuda"), torch.tensor(b, device="cuda")
+    got = ops.fake_quantize_merge(at, bt, op, torch.tensor(s, device="cuda"), torch.tensor(z, device="cuda"), 0, 255)
+    np.testing.assert_array_equal(got.cpu().numpy(), want(b))
+    got = ops.fake_quantize_merge(at, 0.75, op, float(s), float(z), 0, 255)
+    np.testing.assert_array_equal(got.cpu().numpy(), O.fake_quantize(
+        (lambda t: np.where(t < 0, np.float32(0), t) if op == "add_relu" else t)(
+            (a * np.float32(0.75) if op == "mul" else a + np.float32(0.75)).astype(np.float32)), float(s), float(z), 0, 255)[0])
+    got = ops.fake_quantize_merge(at[1:], bt[1:], op, float(s), float(z), 0, 255)  # unaligned views
+    np.testing.assert_array_equal(got.cpu().numpy(), want(b)[1:])

@@ -220,3 +220,28 @@ def test_streaming_kernel_is_deterministic(ops, B, N, K):
         again = ops.wo_linear_s8(x, wq, sw, overlap_previous=bool(i & 1))
         assert torch.equal(again.view(torch.int16), first.view(torch.int16)), f"launch {i + 2} differs"
     assert ops.wo_linear_status() == 0
+
+
+@pytest.mark.parametrize("transpose", [True, False])
+@pytest.mark.parametrize("bits", [8, 4])
+def test_quantized_matmul_backward(transpose, bits):
+    """d/dx of quantized_matmul is grad @ dequant(w) (or its transpose): checked against
+    autograd through the dense reconstruction."""
+    import lucid_b200.quantization._qgemm as G
+
+    torch.manual_seed(bits)
+    w = torch.randn(96, 128, device="cuda")
+    wq, sc, bi = G.quantize(w, 64, bits)
+    dense = G.dequantize(wq, sc, bi, 64, bits)
+    for rows in (3, 40):  # GEMV-shaped kernel and dense route
+        x = torch.randn(rows, 128 if transpose else 96, device="cuda", requires_grad=True)
+        y = G.quantized_matmul(x, wq, sc, bi, transpose=transpose, group_size=64, bits=bits)
+        g = torch.randn_like(y)
+        (gx,) = torch.autograd.grad(y, x, g)
+        x2 = x.detach().clone().requires_grad_(True)
+        y2 = x2 @ (dense.T if transpose else dense)
+        (gx2,) = torch.autograd.grad(y2, x2, g)
+        assert torch.allclose(y, y2, rtol=1e-4, atol=1e-4 * float(y2.abs().max()))
+        assert torch.allclose(gx, gx2, rtol=1e-4, atol=1e-4 * float(gx2.abs().max()))
+    with torch.no_grad():
+        assert not G.quantized_matmul(torch.randn(2, 128, device="cuda"), wq, sc, bi, group_size=64, bits=bits).requires_grad

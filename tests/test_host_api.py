@@ -340,3 +340,90 @@ def test_weight_only_modules():
     x = torch.randn(3, 7, H)
     assert tuple(wo(x.cuda().bfloat16()).shape) == (3, 7, F)
     assert (wo(x.cuda()).cpu() - lin(x)).abs().mean() / lin(x).abs().mean() < 0.02
+
+
+# ---- stubs, functional merges, differentiable quantized_matmul ---------------------------
+class _ResidualBlock(nn.Module):
+    """quant -> fc1 -> relu -> fc2 -> (+ skip, relu) -> dequant, the shape of the reference's
+    FloatFunctional example (lucid/nn/quantized/functional_module.py)."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.quant, self.dequant = nnq.QuantStub(), nnq.DeQuantStub()
+        self.fc1, self.act, self.fc2 = nn.Linear(32, 32), nn.ReLU(), nn.Linear(32, 32)
+        self.skip = nnq.FloatFunctional()
+
+    def forward(self, x):
+        x = self.quant(x)
+        return self.dequant(self.skip.add_relu(self.fc2(self.act(self.fc1(x))), x))
+
+
+def test_static_workflow_with_stubs_and_functional(device):
+    torch.manual_seed(0)
+    model = _ResidualBlock()
+    ff = nnq.FloatFunctional()
+    a, b = torch.randn(4), torch.randn(4)
+    assert torch.equal(ff.add(a, b), a + b) and torch.equal(ff.mul_scalar(a, 2.0), a * 2.0)  # passthrough
+    x = torch.randn(48, 32)
+    ref = model(x)
+    prepared = Q.prepare(model).to(device)
+    assert all(hasattr(m, "activation_post_process") for m in (prepared.quant, prepared.skip, prepared.fc1))
+    assert not hasattr(prepared.dequant, "activation_post_process")
+    for _ in range(2):
+        prepared(x.to(device))
+    qm = Q.convert(prepared)
+    assert isinstance(qm.quant, nnq.Quantize) and isinstance(qm.dequant, nnq.DeQuantize)
+    assert isinstance(qm.skip, nnq.QFunctional) and isinstance(qm.fc1, nnq.Linear)
+    assert set(qm.skip.state_dict()) == {"scale", "zero_point"} == set(qm.quant.state_dict())
+    out = qm(x.to(device)).cpu()
+    assert (out - ref).abs().mean() / ref.abs().mean() < 0.1
+    # every output of the merge lies on its calibrated grid
+    s, z = float(qm.skip.scale), float(qm.skip.zero_point)
+    codes = out / s + z
+    assert float((codes - codes.round()).abs().max()) < 1e-3 and float(out.min()) >= 0.0
+    # integer inputs pass the Quantize marker untouched
+    idx = torch.arange(6)
+    assert torch.equal(qm.quant(idx), idx)
+    wrapped = nnq.QuantWrapper(nn.Linear(4, 4))
+    assert isinstance(wrapped.quant, nnq.QuantStub) and isinstance(wrapped.dequant, nnq.DeQuantStub)
+
+
+def test_qfunctional_merges_match_unfused_definition(device):
+    torch.manual_seed(3)
+    qf = nnq.QFunctional(torch.tensor(0.05), torch.tensor(12.0)).to(device)
+    a, b = torch.randn(7, 33).to(device), torch.randn(7, 33).to(device)
+    fq = lambda t: Q.fake_quantize(t, qf.scale, qf.zero_point, 0, 255)  # noqa: E731
+    assert torch.equal(qf.add(a, b), fq(a + b))
+    assert torch.equal(qf.mul(a, b), fq(a * b))
+    assert torch.equal(qf.add_relu(a, b), fq(torch.relu(a + b)))
+    assert torch.equal(qf.add_scalar(a, 0.3), fq(a + 0.3))
+    assert torch.equal(qf.mul_scalar(a, -1.7), fq(a * -1.7))
+    assert torch.equal(qf.cat([a, b], dim=1), fq(torch.cat([a, b], dim=1)))
+    row = torch.randn(33).to(device)  # broadcasting merge
+    assert torch.equal(qf.add(a, row), fq(a + row))
+
+
+@pytest.mark.parametrize("kind", ["LSTM", "GRU", "LSTMCell", "GRUCell", "RNNCell"])
+def test_dynamic_recurrent(device, kind):
+    """int8 weight buffers under the float module's flat names, float biases, the float shell
+    outside state_dict; output within weight-quantization error of the float module."""
+    torch.manual_seed(2)
+    cell = kind.endswith("Cell")
+    fl = getattr(nn, kind)(16, 24) if cell else getattr(nn, kind)(16, 24, num_layers=2, batch_first=True)
+    q = getattr(nnqd, kind).from_float(fl)
+    keys = set(q.state_dict())
+    names = [n for n, _ in fl.named_parameters()]
+    want = {n + "_int8" for n in names if n.startswith("weight")} | {n + "_scale" for n in names if n.startswith("weight")} \
+        | {n for n in names if n.startswith("bias")}
+    assert keys == want
+    assert all(q.state_dict()[k].dtype is torch.int8 for k in keys if k.endswith("_int8"))
+    x = torch.randn(5, 16) if cell else torch.randn(3, 7, 16)
+    ref = fl(x)
+    out = q(x.to(device))
+    ref0, out0 = (ref[0], out[0]) if isinstance(ref, tuple) else (ref, out)
+    assert out0.shape == ref0.shape
+    assert (out0.cpu() - ref0).abs().max() < 0.05
+    with pytest.raises(TypeError, match="expects an nn."):
+        getattr(nnqd, kind).from_float(nn.Linear(2, 2))
+    swapped = Q.quantize_dynamic(nn.Sequential(fl) if cell else nn.ModuleDict({"rnn": fl}))
+    assert isinstance(next(swapped.children()), getattr(nnqd, kind))

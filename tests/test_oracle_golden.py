@@ -184,3 +184,46 @@ def test_committed_golden_vectors_match_oracle():
     np.testing.assert_array_equal(np.array([st, zt], np.float32), g["qparams_affine"])
     np.testing.assert_array_equal(O.quantize(x, st, zt, O.quint8), g["q_affine"])
     assert meta["seed"] == 0
+
+
+# ---- histc: the reference pins lucid.histc to torch.histc on these cases
+# (lucid/test/unit/ops/test_adapter_index_stats.py:107-127, refusals :130-144)
+_NAN, _INFTY = float("nan"), float("inf")
+_HISTC_CASES = [
+    ([_NAN, 1.0, 2.0], 2, 0.0, 2.0),
+    ([3.0, 3.0], 4, 0.0, 0.0),
+    ([3.0], 3, 5.0, 5.0),
+    ([1.0, 3.0], 4, 2.0, 2.0),
+    ([_INFTY, 1.0, 2.0], 2, 0.0, 2.0),
+    ([-_INFTY, _NAN, 0.5], 2, 0.0, 1.0),
+    ([5.0, -1.0, 1.0], 2, 0.0, 2.0),
+    ([], 3, 0.0, 0.0),
+    ([0.25, 0.5, 0.75, 1.0], 4, 0.0, 0.0),
+]
+
+
+@pytest.mark.parametrize("data,bins,lo,hi", _HISTC_CASES, ids=str)
+def test_histc_matches_the_references_pin(data, bins, lo, hi):
+    torch = pytest.importorskip("torch")
+    got = O.histc(np.array(data, dtype=np.float32), bins, lo, hi)
+    want = torch.histc(torch.tensor(data, dtype=torch.float32), bins, lo, hi).numpy()
+    assert got.dtype == np.float32 and np.array_equal(got, want)
+
+
+def test_histc_refusals_and_bulk():
+    torch = pytest.importorskip("torch")
+    with pytest.raises(ValueError, match="not finite"):
+        O.histc(np.array([_NAN, 1.0], dtype=np.float32), 2, 0.0, 0.0)
+    with pytest.raises(ValueError, match="not finite"):
+        O.histc(np.array([1.0], dtype=np.float32), 2, 0.0, _INFTY)
+    with pytest.raises(ValueError, match="at least min"):
+        O.histc(np.array([1.0], dtype=np.float32), 2, 3.0, 1.0)
+    x = np.random.default_rng(5).standard_normal(200_000).astype(np.float32)
+    x[::1000] *= 50.0
+    for bins in (7, 256, 2048):
+        lo, hi = float(x.min()), float(x.max())
+        got = O.histc(x, bins, lo, hi)
+        assert got.sum() == x.size  # both edges are inside
+        # torch buckets in float32; away from bin edges the two agree, and the totals always do
+        want = torch.histc(torch.tensor(x), bins, lo, hi).numpy()
+        assert np.abs(got - want).sum() <= 4
