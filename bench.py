@@ -394,8 +394,18 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
         qlin = Q.quantize_dynamic(lin)
         x1 = torch.randn(64, 1024, device=dev, generator=g)
         ms = time_loop(torch, lambda: qlin(x1), 200, 20)
-        out["single_dynamic_linear_64x4096x1024"] = {"us_per_forward": ms * 1e3,
-                                                     "TOPS": 2 * 64 * 4096 * 1024 / ms / 1e9}
+        entry = {"us_per_forward": ms * 1e3, "TOPS": 2 * 64 * 4096 * 1024 / ms / 1e9,
+                 "note": "eager: the host prepares three launches per forward"}
+        try:  # the same module captured in a CUDA graph (one launch per forward, input copied in)
+            import lucid_b200
+
+            gl = lucid_b200.cuda.make_graphed(qlin, x1)
+            assert torch.equal(gl(x1), qlin(x1))
+            gms = time_loop(torch, lambda: gl(x1), 400, 40)
+            entry.update({"graphed_us_per_forward": gms * 1e3, "graphed_TOPS": 2 * 64 * 4096 * 1024 / gms / 1e9})
+        except Exception as e:
+            entry["graphed_error"] = repr(e)[:200]
+        out["single_dynamic_linear_64x4096x1024"] = entry
     except Exception as e:  # reported, never hidden
         out["single_dynamic_linear_64x4096x1024"] = {"error": repr(e)[:200]}
     return out

@@ -31,7 +31,7 @@ struct HistSpec {
   double lo, hi, step;
   float lo32, inv32, delta, top;  // top = bins - delta
   int bins;
-  int copies;  // private histograms per CTA (a power of two); lanes are dealt over them
+  int lo_exact;  // lo32 == lo: a value equal to lo32 is exactly the left end (bin 0)
 };
 
 __device__ __forceinline__ void count_one(float v, const HistSpec& h, unsigned int* sh) {
@@ -40,6 +40,11 @@ __device__ __forceinline__ void count_one(float v, const HistSpec& h, unsigned i
   const float fr = q - fl;
   if (q >= h.delta && q <= h.top && fr > h.delta && fr < 1.0f - h.delta) {  // false for NaN
     atomicAdd(sh + static_cast<int>(fl), 1u);
+    return;
+  }
+  // the left end of the range is where a ReLU's zeros (half of all activations) land
+  if (v == h.lo32 && h.lo_exact) {
+    atomicAdd(sh, 1u);
     return;
   }
   const double d = static_cast<double>(v);
@@ -56,11 +61,9 @@ histc_kernel(const float* __restrict__ x, int64_t n, int vec_ok, const HistSpec 
   extern __shared__ unsigned int sh[];
   __shared__ int is_last;
   const int bins = h.bins;
-  // Activations after a ReLU put half of all values into one bin: lanes of a warp are dealt
-  // over `copies` private histograms so that such a pile-up serialises copies-fold less.
-  for (int b = threadIdx.x; b < bins * h.copies; b += kHistThreads) sh[b] = 0u;
+  for (int b = threadIdx.x; b < bins; b += kHistThreads) sh[b] = 0u;
   __syncthreads();
-  unsigned int* const mine = sh + (threadIdx.x & (h.copies - 1)) * bins;
+  unsigned int* const mine = sh;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * kHistThreads + threadIdx.x;
   const int64_t nthreads = static_cast<int64_t>(gridDim.x) * kHistThreads;
   if (vec_ok) {
@@ -92,8 +95,7 @@ histc_kernel(const float* __restrict__ x, int64_t n, int vec_ok, const HistSpec 
   }
   __syncthreads();
   for (int b = threadIdx.x; b < bins; b += kHistThreads) {
-    unsigned int c = 0;
-    for (int k = 0; k < h.copies; ++k) c += sh[k * bins + b];
+    const unsigned int c = sh[b];
     if (c) atomicAdd(gcounts + b, static_cast<unsigned long long>(c));
   }
   __threadfence();
@@ -153,18 +155,17 @@ extern "C" int32_t lc_histc_f32(const float* x, int64_t n, int32_t bins, double 
   const double delta = ldexp(mag, -22) + 1e-6;
   h.delta = delta < 0.25 && h.lo32 > -INFINITY && h.inv32 < INFINITY ? static_cast<float>(delta) : 2.0f;  // 2: never fast
   h.top = static_cast<float>(bins) - h.delta;
-  h.copies = 1;
-  while (h.copies < 8 && 2 * h.copies * bins <= kHistMaxBins) h.copies *= 2;
+  h.lo_exact = static_cast<double>(h.lo32) == lo ? 1 : 0;
   // enough CTAs to fill the machine a few times over, few enough that clearing and flushing
   // the shared histograms (up to 64 KB each) stays cheap
   int64_t grid = (n + kHistThreads * 16 - 1) / (kHistThreads * 16);
-  const int64_t per_sm = h.copies * bins * 4 <= 16 * 1024 ? 8 : (h.copies * bins * 4 <= 32 * 1024 ? 4 : 2);
+  const int64_t per_sm = bins * 4 <= 16 * 1024 ? 8 : (bins * 4 <= 32 * 1024 ? 4 : 2);
   const int64_t cap = static_cast<int64_t>(sm_count()) * per_sm;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   unsigned int* ticket = static_cast<unsigned int*>(workspace);
   unsigned long long* gcounts = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(workspace) + 16);
-  histc_kernel<<<static_cast<unsigned>(grid), kHistThreads, h.copies * bins * 4, st>>>(
+  histc_kernel<<<static_cast<unsigned>(grid), kHistThreads, bins * 4, st>>>(
       x, n, aligned(x, 16) ? 1 : 0, h, gcounts, ticket, out, accumulate);
   return check_launch("histc");
 }

@@ -57,6 +57,56 @@ def stream(s):
     return torch.cuda.stream(s)
 
 
+class GraphedModule(torch.nn.Module):
+    """``module`` with its forward captured in a CUDA graph for one input signature.
+
+    The quantized layers launch a handful of short kernels per forward (observe, quantize,
+    GEMM or GEMV); at decode and small-batch shapes the host spends longer preparing those
+    launches than the GPU spends running them.  Nothing on the quantized path reads device
+    values back on the host (dynamic scales stay on the device), so a forward is capturable:
+    replaying the graph costs one launch.  Inputs are copied into the captured input buffers;
+    the returned tensors are the captured output buffers (overwritten by the next call) unless
+    ``clone_outputs`` is set.  Parameters and buffers of ``module`` are read in place at replay
+    time, so weight updates that keep their storage are seen."""
+
+    def __init__(self, module: torch.nn.Module, *example_inputs: torch.Tensor, warmup: int = 3,
+                 clone_outputs: bool = False) -> None:
+        super().__init__()
+        if not example_inputs or not all(isinstance(t, torch.Tensor) and t.is_cuda for t in example_inputs):
+            raise ValueError("GraphedModule needs CUDA example inputs")
+        self.module = module
+        self._clone = clone_outputs
+        self._inputs = [t.detach().clone() for t in example_inputs]
+        side = torch.cuda.Stream(device=self._inputs[0].device)
+        side.wait_stream(torch.cuda.current_stream(self._inputs[0].device))
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(max(1, warmup)):  # first-use work (workspaces, padded weights) stays outside the graph
+                module(*self._inputs)
+            side.synchronize()
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph, stream=side):
+                self._outputs = module(*self._inputs)
+        torch.cuda.current_stream(self._inputs[0].device).wait_stream(side)
+
+    def forward(self, *inputs: torch.Tensor):
+        if len(inputs) != len(self._inputs):
+            raise ValueError(f"captured for {len(self._inputs)} inputs, got {len(inputs)}")
+        for dst, src in zip(self._inputs, inputs):
+            if src.shape != dst.shape or src.dtype != dst.dtype:
+                raise ValueError(f"captured for {tuple(dst.shape)} {dst.dtype}, got {tuple(src.shape)} {src.dtype}")
+            dst.copy_(src, non_blocking=True)
+        self._graph.replay()
+        if not self._clone:
+            return self._outputs
+        return (self._outputs.clone() if isinstance(self._outputs, torch.Tensor)
+                else type(self._outputs)(o.clone() for o in self._outputs))
+
+
+def make_graphed(module: torch.nn.Module, *example_inputs: torch.Tensor, **kwargs) -> GraphedModule:
+    """Capture ``module(*example_inputs)`` in a CUDA graph; see :class:`GraphedModule`."""
+    return GraphedModule(module, *example_inputs, **kwargs)
+
+
 def kernel_library_info() -> dict:
     """Version of liblucid_cuda and the compute capability / SM count of the current device."""
     import ctypes

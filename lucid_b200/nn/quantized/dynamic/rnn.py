@@ -54,8 +54,10 @@ class _DynamicRecurrent(nn.Module):
         dev = first.device if first.is_cuda else _backend.cuda_device()
         if next(shell.parameters()).device != dev:
             shell.to(dev)
-            if hasattr(shell, "flatten_parameters"):
+        if getattr(self, "_flat_for", None) != id(shell):  # a moved or deep-copied shell lost its fused layout
+            if dev.type == "cuda" and hasattr(shell, "flatten_parameters"):
                 shell.flatten_parameters()
+            object.__setattr__(self, "_flat_for", id(shell))
         for path, key in self._weight_names:
             deq = dequantize(self._buffer(key + "_int8"), self._buffer(key + "_scale"), 0.0, ch_axis=0)
             shell.get_parameter(path).copy_(deq)

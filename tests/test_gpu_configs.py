@@ -108,3 +108,23 @@ def test_config4_decode_mlp_module():
         h = (torch.nn.functional.silu(g) * u).to(torch.bfloat16).double()
         ref = (h @ mlp.down.weight_int8.double().T) * mlp.down.weight_scale.double()
         assert torch.allclose(y.double(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
+
+
+def test_graphed_module_replays_the_quantized_forward():
+    """A dynamic Linear captured in a CUDA graph returns the eager result for new inputs of the
+    captured shape, sees in-place weight updates, and refuses other shapes."""
+    import lucid_b200
+    import lucid_b200.quantization as Q
+
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(1024, 4096).cuda()
+    qlin = Q.quantize_dynamic(lin)
+    x = torch.randn(64, 1024, device="cuda")
+    g = lucid_b200.cuda.make_graphed(qlin, x, clone_outputs=True)
+    for _ in range(3):
+        x = torch.randn(64, 1024, device="cuda")
+        assert torch.equal(g(x), qlin(x))
+    qlin.bias.add_(1.0)  # same storage: the replay reads the new values
+    assert torch.equal(g(x), qlin(x))
+    with pytest.raises(ValueError, match="captured for"):
+        g(torch.randn(8, 1024, device="cuda"))
