@@ -172,10 +172,22 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 // Instruction descriptor for kind::i8: D format s32 (2) in bits [4,6), A format
 // in [7,10) and B format in [10,13) (0 = u8, 1 = s8), both operands K-major
 // (bits 15, 16 = 0), N >> 3 in [17,23), M >> 4 in [24,29).
-__host__ __device__ constexpr uint32_t make_idesc(bool a_unsigned) {
+__host__ __device__ constexpr uint32_t make_idesc(bool a_unsigned, int n = BN) {
   return (2u << 4) | ((a_unsigned ? 0u : 1u) << 7) | (1u << 10) |
-         (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
 }
+
+// The single-CTA kernel comes in tile widths BNT = 256, 64 and 32 columns: one row tile of A
+// (M <= 128, the single quantized Linear of a small batch) gives only N / 256 CTAs at the full
+// width, each pulling its slice of the weight through one TMA queue; narrower tiles spread the
+// same weight over up to 148 SMs.  Stage and TMEM budgets follow the width.
+template <int BNT>
+struct NarrowCfg {
+  static constexpr int kStages = BNT == 256 ? 3 : 6;
+  static constexpr int kStageBytes = A_BYTES + BNT * BK;
+  static constexpr int kTmemCols = ACC_STAGES * BNT;  // 512, 128 or 64: powers of two >= 32
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + STG_BYTES;
+};
 
 __device__ __forceinline__ void tile_coords(int64_t t, int64_t tiles_m, int64_t tiles_n, int64_t& tm,
                                             int64_t& tn) {
@@ -298,9 +310,14 @@ __device__ __forceinline__ void drain_chunk(const Params& p, const uint32_t (&r)
   __syncwarp();
 }
 
+template <int BNT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const Params p, const uint32_t idesc) {
+  // tile width and what follows from it (these shadow the full-width constants of the namespace)
+  constexpr int BN = BNT, STAGES = NarrowCfg<BNT>::kStages, STAGE_BYTES = NarrowCfg<BNT>::kStageBytes,
+                TMEM_COLS = NarrowCfg<BNT>::kTmemCols;
+  static_assert(2 * STAGES * 8 + 4 * ACC_STAGES * 8 <= 256, "barrier area");
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(16) float s_sw[BN];
   __shared__ __align__(16) float s_bias[BN];
@@ -760,8 +777,14 @@ static int32_t ensure_smem_attr() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return fail(LC_ERR_CUDA, "no current CUDA device");
   std::call_once(flags[dev], [dev]() {
-    results[dev] = cudaFuncSetAttribute(qlinear_i8_kernel,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    results[dev] = cudaFuncSetAttribute(qlinear_i8_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        NarrowCfg<256>::kSmemBytes);
+    if (results[dev] == cudaSuccess)
+      results[dev] = cudaFuncSetAttribute(qlinear_i8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          NarrowCfg<64>::kSmemBytes);
+    if (results[dev] == cudaSuccess)
+      results[dev] = cudaFuncSetAttribute(qlinear_i8_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          NarrowCfg<32>::kSmemBytes);
     if (results[dev] == cudaSuccess)
       results[dev] = cudaFuncSetAttribute(qlinear_i8_pair_kernel,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES2);
@@ -827,9 +850,20 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
   // CTA pairs pay off once there is more than one 128-row tile of A; a single row tile
   // would leave half of every pair idle
   const bool use_pair = variant == 2 || (variant == 0 && M > BM);
+  // tile width of the single-CTA kernel (variant 1 forces the full width): weights of up to
+  // 8 MB are latency-bound, and the widest of 64 / 32 columns that still gives every SM a tile
+  // spreads them over the machine (C1: 16 CTAs x 11.1 us -> 128 CTAs x 6.8 us); every narrower
+  // tile re-reads its 128 rows of A, so larger weights keep the full width (measured: 58 MB at
+  // 64 columns takes 31 us against 19 us)
+  const int64_t sms = sm_count();
+  int bnt = BN;
+  if (!use_pair && variant == 0 && N * K <= (int64_t{8} << 20)) {
+    const int64_t tiles_m = (M + BM - 1) / BM;
+    if (tiles_m * ((N + 255) / 256) < sms) bnt = tiles_m * ((N + 63) / 64) >= sms ? 64 : 32;
+  }
   CUtensorMap map_a, map_b;
   if (int32_t rc = make_map(&map_a, a, M, K, lda, BM)) return rc;
-  if (int32_t rc = make_map(&map_b, b, N, K, ldb, use_pair ? pair::BNH : BN)) return rc;
+  if (int32_t rc = make_map(&map_b, b, N, K, ldb, use_pair ? pair::BNH : bnt)) return rc;
   if (int32_t rc = ensure_smem_attr()) return rc;
 
   Params p;
@@ -852,7 +886,6 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
     if (!aligned(host_outs[i], 16)) p.out_vec = 0;
   p.status = status;
 
-  const int64_t sms = sm_count();
   if (use_pair) {
     const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
     const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
@@ -860,9 +893,14 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
                              as_stream(stream)>>>(map_a, map_b, p, make_idesc_pair(a_unsigned != 0));
     return check_launch("qlinear_i8 (cta pair)");
   }
-  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + bnt - 1) / bnt);
   const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
-  qlinear_i8_kernel<<<grid, NUM_THREADS, SMEM_BYTES, as_stream(stream)>>>(
-      map_a, map_b, p, make_idesc(a_unsigned != 0));
+  const uint32_t idesc = make_idesc(a_unsigned != 0, bnt);
+  if (bnt == 256)
+    qlinear_i8_kernel<256><<<grid, NUM_THREADS, NarrowCfg<256>::kSmemBytes, as_stream(stream)>>>(map_a, map_b, p, idesc);
+  else if (bnt == 64)
+    qlinear_i8_kernel<64><<<grid, NUM_THREADS, NarrowCfg<64>::kSmemBytes, as_stream(stream)>>>(map_a, map_b, p, idesc);
+  else
+    qlinear_i8_kernel<32><<<grid, NUM_THREADS, NarrowCfg<32>::kSmemBytes, as_stream(stream)>>>(map_a, map_b, p, idesc);
   return check_launch("qlinear_i8");
 }
