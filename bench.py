@@ -431,6 +431,15 @@ def run_profile_case(args) -> int:
     elif case == "histc":
         x = torch.randn(8192, 8192, device=dev, generator=g)
         fn = lambda: ops.histc(x, 2048, -6.0, 6.0)  # noqa: E731
+    elif case == "merge":
+        x = torch.randn(8192, 8192, device=dev, generator=g)
+        y = torch.randn(8192, 8192, device=dev, generator=g)
+        fn = lambda: ops.fake_quantize_merge(x, y, "add_relu", 0.05, 12.0, 0, 255)  # noqa: E731
+    elif case == "gemm_small":
+        a = torch.randint(-128, 128, (64, 1024), device=dev, dtype=torch.int8, generator=g)
+        b = torch.randint(-128, 128, (4096, 1024), device=dev, dtype=torch.int8, generator=g)
+        sx, sw = torch.rand(64, device=dev), torch.rand(4096, device=dev)
+        fn = lambda: ops.qlinear_i8(a, b, sx, sw)  # noqa: E731
     elif case in ("quantize_rows", "quantize_tensor", "dequantize", "quantize_given_scale"):
         x = torch.randn(8192, 8192, device=dev, generator=g)
         q, s, z = ops.dynamic_quantize_rows(x, True, -128, 127, True)
@@ -693,7 +702,7 @@ def main() -> int:
                     help="headline workload only: skip the companion workloads and the CPU baseline")
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed case of one kernel (gemm, quantize_rows, quantize_tensor, "
-                         "dequantize, quantize_given_scale, histc, wo_gemv) for a profiler capture; prints no bench line")
+                         "dequantize, quantize_given_scale, histc, merge, gemm_small, wo_gemv) for a profiler capture; prints no bench line")
     ap.add_argument("--profile-batch", default=4)
     ap.add_argument("--gather", choices=("auto", "fused", "nccl"), default="auto",
                     help="N > 1: how output shards are exchanged (auto = fused if symmetric memory works)")
