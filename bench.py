@@ -393,7 +393,9 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
             lin.bias.normal_(0, 0.01, generator=g)
         qlin = Q.quantize_dynamic(lin)
         x1 = torch.randn(64, 1024, device=dev, generator=g)
-        ms = time_loop(torch, lambda: qlin(x1), 200, 20)
+        # a fresh tensor object per call, as in real use (the layer reuses the codes of an input it
+        # has just seen, which a loop over one tensor object would turn into a no-op)
+        ms = time_loop(torch, lambda: qlin(x1.detach()), 200, 20)
         entry = {"us_per_forward": ms * 1e3, "TOPS": 2 * 64 * 4096 * 1024 / ms / 1e9,
                  "note": "eager: the host prepares three launches per forward"}
         try:  # the same module captured in a CUDA graph (one launch per forward, input copied in)
@@ -403,6 +405,9 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
             assert torch.equal(gl(x1), qlin(x1))
             gms = time_loop(torch, lambda: gl(x1), 400, 40)
             entry.update({"graphed_us_per_forward": gms * 1e3, "graphed_TOPS": 2 * 64 * 4096 * 1024 / gms / 1e9})
+            # device time alone: ten forwards in one graph (per-tensor quantize kernel + GEMM each)
+            dms = graph_time(torch, lambda: qlin(x1.detach()), reps=10, replays=20)
+            entry.update({"device_us_per_forward": dms * 1e3, "device_TOPS": 2 * 64 * 4096 * 1024 / dms / 1e9})
         except Exception as e:
             entry["graphed_error"] = repr(e)[:200]
         out["single_dynamic_linear_64x4096x1024"] = entry

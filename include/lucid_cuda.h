@@ -52,6 +52,10 @@ int32_t lc_version(void);
 int32_t lc_last_error(char* host_buf, int32_t n);
 /* compute capability (major*10+minor) and SM count of `device` */
 int32_t lc_device_info(int32_t device, int32_t* host_sm, int32_t* host_sm_count);
+/* 0 when `stream` is not being captured into a CUDA graph, else the id of that capture (unique
+ * per capture sequence).  Host code that reuses device results between calls keys them by it:
+ * a kernel recorded in one capture has not run, and will not run with another graph. */
+int32_t lc_stream_capture_id(void* stream, uint64_t* host_id);
 
 /* ---- observers --------------------------------------------------------
  * MinMaxObserver.forward: running global min and max

@@ -42,6 +42,7 @@ _p, _i32, _i64, _f = C.c_void_p, C.c_int32, C.c_int64, C.c_float
 SIGNATURES = {
     "lc_version": (_i32, []),
     "lc_last_error": (_i32, [C.c_char_p, _i32]),
+    "lc_stream_capture_id": (_i32, [_p, C.POINTER(C.c_uint64)]),
     "lc_device_info": (_i32, [_i32, C.POINTER(_i32), C.POINTER(_i32)]),
     "lc_observe_tensor_workspace_bytes": (_i64, []),
     "lc_observe_tensor_f32": (_i32, [_p, _i64, _p, _p, _i32, _i32, _i32, _i32, _i32, _f, _p, _p, _p, _i64, _p]),

@@ -105,3 +105,13 @@ extern "C" int32_t lc_device_info(int32_t device, int32_t* host_sm, int32_t* hos
   if (host_sm_count) *host_sm_count = sms;
   return LC_OK;
 }
+
+extern "C" int32_t lc_stream_capture_id(void* stream, uint64_t* host_id) {
+  if (!host_id) return lc::fail(LC_ERR_INVALID_ARG, "stream_capture_id: null pointer");
+  cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+  unsigned long long id = 0;
+  if (cudaStreamGetCaptureInfo(reinterpret_cast<cudaStream_t>(stream), &status, &id) != cudaSuccess)
+    return lc::fail(LC_ERR_CUDA, "stream_capture_id: %s", cudaGetErrorString(cudaGetLastError()));
+  *host_id = status == cudaStreamCaptureStatusActive ? static_cast<uint64_t>(id) : 0;
+  return LC_OK;
+}

@@ -27,6 +27,35 @@ int32_t encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
+// ---- programmatic dependent launch ----------------------------------------------------
+// A kernel launched with launch_overlapped() may be scheduled while the kernel before it on the
+// stream is still running; it must execute pdl_wait() before it reads anything that kernel
+// wrote or writes anything that kernel reads (the wait returns when that grid has completed
+// and its memory is visible).  What precedes the wait may only touch the kernel's own shared
+// memory, TMEM and registers.  pdl_launch_dependents() in the earlier kernel lets the next
+// grid take SM resources as they free up instead of after this grid has drained; it is a
+// no-op when nothing overlapped is queued.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename Kernel, typename... Args>
+inline cudaError_t launch_overlapped(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 // ---- device side: the quantization grid, one IEEE fp32 step at a time ------
 // The reference evaluates round(x * (1/s)) + z as separate eager fp32 ops
 // (lucid/quantization/_functional.py:59-69); the explicit _rn intrinsics stop

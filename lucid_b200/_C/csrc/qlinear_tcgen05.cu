@@ -324,6 +324,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ __align__(16) int s_corr[BN];
   __shared__ uint32_t s_tmem_base;
 
+  pdl_launch_dependents();
   const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = tiles_base + STAGES * STAGE_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -361,6 +362,9 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
+  // barriers, TMEM and descriptors are set up: everything from here on reads what the kernel
+  // before this one produced (the quantized activations, their scales) or writes the output
+  pdl_wait();
 
   if (warp == 0) {
     // ===================== TMA producer =====================
@@ -577,6 +581,7 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ __align__(16) int s_corr[BN];
   __shared__ uint32_t s_tmem_base;
 
+  pdl_launch_dependents();
   const uint32_t tiles_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = tiles_base + STAGES2 * STAGE_BYTES2;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -619,6 +624,9 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   cluster_sync_all();  // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
+  // barriers, TMEM and descriptors are set up: everything from here on reads what the kernel
+  // before this one produced (the quantized activations, their scales) or writes the output
+  pdl_wait();
 
   if (warp == 0) {
     // ===================== TMA producer (both CTAs) =====================
@@ -889,18 +897,27 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
   if (use_pair) {
     const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
     const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
-    qlinear_i8_pair_kernel<<<static_cast<unsigned>(2 * pairs), NUM_THREADS, pair::SMEM_BYTES2,
-                             as_stream(stream)>>>(map_a, map_b, p, make_idesc_pair(a_unsigned != 0));
+    // launched so that its set-up (barriers, TMEM allocation) may overlap the tail of the kernel
+    // that produced its operands; it waits for that kernel before its first load
+    const cudaError_t err = launch_overlapped(qlinear_i8_pair_kernel, dim3(static_cast<unsigned>(2 * pairs)),
+                                              dim3(NUM_THREADS), pair::SMEM_BYTES2, as_stream(stream), map_a, map_b, p,
+                                              make_idesc_pair(a_unsigned != 0));
+    if (err != cudaSuccess) return fail(LC_ERR_CUDA, "qlinear_i8 (cta pair): %s", cudaGetErrorString(err));
     return check_launch("qlinear_i8 (cta pair)");
   }
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + bnt - 1) / bnt);
   const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
   const uint32_t idesc = make_idesc(a_unsigned != 0, bnt);
+  cudaError_t err;
   if (bnt == 256)
-    qlinear_i8_kernel<256><<<grid, NUM_THREADS, NarrowCfg<256>::kSmemBytes, as_stream(stream)>>>(map_a, map_b, p, idesc);
+    err = launch_overlapped(qlinear_i8_kernel<256>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<256>::kSmemBytes,
+                            as_stream(stream), map_a, map_b, p, idesc);
   else if (bnt == 64)
-    qlinear_i8_kernel<64><<<grid, NUM_THREADS, NarrowCfg<64>::kSmemBytes, as_stream(stream)>>>(map_a, map_b, p, idesc);
+    err = launch_overlapped(qlinear_i8_kernel<64>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<64>::kSmemBytes,
+                            as_stream(stream), map_a, map_b, p, idesc);
   else
-    qlinear_i8_kernel<32><<<grid, NUM_THREADS, NarrowCfg<32>::kSmemBytes, as_stream(stream)>>>(map_a, map_b, p, idesc);
+    err = launch_overlapped(qlinear_i8_kernel<32>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<32>::kSmemBytes,
+                            as_stream(stream), map_a, map_b, p, idesc);
+  if (err != cudaSuccess) return fail(LC_ERR_CUDA, "qlinear_i8: %s", cudaGetErrorString(err));
   return check_launch("qlinear_i8");
 }

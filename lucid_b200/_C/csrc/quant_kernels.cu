@@ -36,6 +36,7 @@ __global__ void __launch_bounds__(kThreads)
 observe_tensor_kernel(const float* __restrict__ x, int64_t n, int vec_ok, float* min_out,
                       float* max_out, int accumulate, int with_qparams, QParamSpec spec,
                       float* scale_out, float* zp_out, TensorObserveScratch* ws) {
+  pdl_launch_dependents();
   __shared__ float red[64];
   __shared__ int is_last;
   float mn = INFINITY, mx = -INFINITY;
@@ -228,6 +229,7 @@ __global__ void __launch_bounds__(kThreads)
 quantize_seg_kernel(const float* __restrict__ x, OutT* __restrict__ out, int64_t channels,
                     int64_t inner, int64_t in_stride, int64_t out_stride, int chunks_per_seg,
                     ChannelParams p, float qmin, float qmax, int reverse) {
+  pdl_launch_dependents();
   const int64_t bid = reverse ? (static_cast<int64_t>(gridDim.x) - 1 - blockIdx.x) : blockIdx.x;
   const int64_t seg = bid / chunks_per_seg;
   const int chunk = static_cast<int>(bid % chunks_per_seg);
@@ -485,6 +487,7 @@ __global__ void __launch_bounds__(BLOCK)
 dynamic_quantize_rows_kernel(const float* __restrict__ x, int64_t cols, int64_t ldx,
                              QParamSpec spec, OutT* __restrict__ q, int64_t ldq,
                              float* __restrict__ scale_out, float* __restrict__ zp_out) {
+  pdl_launch_dependents();
   __shared__ float red[64];
   const int64_t row = blockIdx.x;
   const float* xr = x + row * ldx;
@@ -533,6 +536,112 @@ dynamic_quantize_rows_kernel(const float* __restrict__ x, int64_t cols, int64_t 
       }
     }
   }
+}
+
+// Per-tensor dynamic quantization of a small tensor in ONE launch: the activations of a
+// single Linear on a small batch (64 x 1024 at C1) are too few for the two-kernel form
+// (global range, then quantize) to be anything but two launch latencies.  A cluster of up
+// to 8 CTAs keeps the whole tensor in registers, exchanges the eight partial ranges through
+// distributed shared memory behind a hardware cluster barrier, and every CTA then derives the
+// same qparams and quantizes its share.  x is dense [rows, cols], cols % 4 == 0; the codes go
+// to a matrix with leading dimension ldq.
+constexpr int kSmallThreads = 512;
+constexpr int kSmallItems = 8;                                      // float4 per thread
+constexpr int kSmallMaxCluster = 8;
+constexpr int64_t kSmallPerCta = int64_t{kSmallThreads} * kSmallItems * 4;  // 16384 elements
+constexpr int64_t kSmallMaxElems = kSmallPerCta * kSmallMaxCluster;          // 131072
+
+template <typename OutT>
+__global__ void __launch_bounds__(kSmallThreads)
+dynamic_quantize_tensor_small_kernel(const float* __restrict__ x, int64_t n, int64_t cols, QParamSpec spec,
+                                     OutT* __restrict__ q, int64_t ldq, float* __restrict__ scale_out,
+                                     float* __restrict__ zp_out, float* __restrict__ minmax_out) {
+  pdl_launch_dependents();
+  __shared__ float red[64];
+  __shared__ float part[2];
+  uint32_t rank, nctas;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nctas));
+  const int64_t base = static_cast<int64_t>(rank) * kSmallPerCta;
+  float4 v[kSmallItems];
+  float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+  for (int u = 0; u < kSmallItems; ++u) {
+    const int64_t i = base + (static_cast<int64_t>(u) * kSmallThreads + threadIdx.x) * 4;
+    if (i < n) v[u] = __ldg(reinterpret_cast<const float4*>(x + i));
+  }
+#pragma unroll
+  for (int u = 0; u < kSmallItems; ++u) {
+    const int64_t i = base + (static_cast<int64_t>(u) * kSmallThreads + threadIdx.x) * 4;
+    if (i < n) {
+      mn = fminf(fminf(mn, fminf(v[u].x, v[u].y)), fminf(v[u].z, v[u].w));
+      mx = fmaxf(fmaxf(mx, fmaxf(v[u].x, v[u].y)), fmaxf(v[u].z, v[u].w));
+    }
+  }
+  block_minmax(mn, mx, red);
+  if (threadIdx.x == 0) {
+    part[0] = mn;
+    part[1] = mx;
+  }
+  // all CTAs of the cluster have published their range (release / acquire at cluster scope)
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  mn = INFINITY;
+  mx = -INFINITY;
+  const uint32_t mine = static_cast<uint32_t>(__cvta_generic_to_shared(part));
+  for (uint32_t r = 0; r < nctas; ++r) {
+    uint32_t remote;
+    float a, b;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(mine), "r"(r));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(a) : "r"(remote));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(b) : "r"(remote + 4));
+    mn = fminf(mn, a);
+    mx = fmaxf(mx, b);
+  }
+  // nobody leaves (and frees its shared memory) while a peer may still be reading it
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  float s, z;
+  qparams_from_range(mn, mx, spec, s, z);
+  const float inv = __fdiv_rn(1.0f, s);
+  if (rank == 0 && threadIdx.x == 0) {
+    scale_out[0] = s;
+    zp_out[0] = z;
+    minmax_out[0] = mn;
+    minmax_out[1] = mx;
+  }
+#pragma unroll
+  for (int u = 0; u < kSmallItems; ++u) {
+    const int64_t i = base + (static_cast<int64_t>(u) * kSmallThreads + threadIdx.x) * 4;
+    if (i < n) {
+      const int64_t row = i / cols, col = i - row * cols;  // cols % 4 == 0: the four stay in one row
+      store4<OutT>(q + row * ldq + col, code_to_int(grid_code(v[u].x, inv, z), spec.qmin, spec.qmax),
+                   code_to_int(grid_code(v[u].y, inv, z), spec.qmin, spec.qmax),
+                   code_to_int(grid_code(v[u].z, inv, z), spec.qmin, spec.qmax),
+                   code_to_int(grid_code(v[u].w, inv, z), spec.qmin, spec.qmax));
+    }
+  }
+}
+
+template <typename OutT>
+static int32_t launch_dynamic_quantize_small(const float* x, int64_t rows, int64_t cols, const QParamSpec& spec,
+                                             OutT* q, int64_t ldq, float* scale_out, float* zp_out,
+                                             float* minmax_out, cudaStream_t st) {
+  const int64_t n = rows * cols;
+  const unsigned ctas = static_cast<unsigned>((n + kSmallPerCta - 1) / kSmallPerCta);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctas);
+  cfg.blockDim = dim3(kSmallThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = ctas;  // the whole grid is one cluster (<= 8 CTAs)
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, dynamic_quantize_tensor_small_kernel<OutT>, x, n, cols, spec, q, ldq,
+                                             scale_out, zp_out, minmax_out);
+  if (err != cudaSuccess) return fail(LC_ERR_CUDA, "dynamic_quantize_tensor (small): %s", cudaGetErrorString(err));
+  return check_launch("dynamic_quantize_tensor (small)");
 }
 
 // any row length / alignment: two passes over the row (the second one is
@@ -1023,6 +1132,21 @@ extern "C" int32_t lc_dynamic_quantize_tensor_f32(const float* x, int64_t rows, 
     return fail(LC_ERR_INVALID_ARG, "dynamic_quantize_tensor: null pointer");
   QParamSpec spec = make_qparam_spec(symmetric, quant_min, quant_max, is_signed, eps);
   cudaStream_t st = as_stream(stream);
+  if (rows * cols <= kSmallMaxElems && cols % 4 == 0 && aligned(x, 16) && ldq % 4 == 0 &&
+      aligned(q_out, out_dtype == LC_S16 ? 8 : 4)) {
+    switch (out_dtype) {
+      case LC_S8:
+        return launch_dynamic_quantize_small<int8_t>(x, rows, cols, spec, static_cast<int8_t*>(q_out), ldq, scale_out,
+                                                     zp_out, minmax_out, st);
+      case LC_U8:
+        return launch_dynamic_quantize_small<uint8_t>(x, rows, cols, spec, static_cast<uint8_t*>(q_out), ldq, scale_out,
+                                                      zp_out, minmax_out, st);
+      case LC_S16:
+        return launch_dynamic_quantize_small<int16_t>(x, rows, cols, spec, static_cast<int16_t*>(q_out), ldq, scale_out,
+                                                      zp_out, minmax_out, st);
+    }
+    return fail(LC_ERR_UNSUPPORTED, "dynamic_quantize_tensor: out_dtype %d not supported", out_dtype);
+  }
   if (int32_t rc = launch_observe_tensor(x, rows * cols, minmax_out, minmax_out + 1, 0, 1, spec,
                                          scale_out, zp_out, workspace, workspace_bytes, st))
     return rc;

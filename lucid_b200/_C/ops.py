@@ -70,6 +70,16 @@ def _stream(dev: torch.device) -> int:
     return torch.cuda.current_stream(dev).cuda_stream
 
 
+def capture_id(dev: torch.device) -> int:
+    """0 outside CUDA-graph capture, else the id of the capture the current stream records into."""
+    import ctypes
+
+    out = ctypes.c_uint64(0)
+    with _on(dev):
+        check(lib.lc_stream_capture_id(_stream(dev), ctypes.byref(out)))
+    return int(out.value)
+
+
 def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 

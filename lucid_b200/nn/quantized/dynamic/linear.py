@@ -16,6 +16,8 @@ no host synchronisation.
 """
 from __future__ import annotations
 
+import weakref
+
 import torch
 from torch import nn
 
@@ -25,6 +27,39 @@ from lucid_b200.quantization._functional import quantize
 from lucid_b200.quantization._qscheme import QDtype, per_channel_symmetric, qint8, quint8
 
 _ACT_SCHEMES = ("tensor_affine", "tensor_symmetric", "token_symmetric")
+
+
+class _LastQuantizedInput:
+    """The codes of the most recently quantized activation tensor, so that sibling layers fed
+    the same tensor (the q / k / v projections of an attention block, the gate and up
+    projections of an MLP) quantize it once.  A hit needs the same tensor object (held weakly:
+    a tensor that has died can never match, whatever memory a new one is given) at the same
+    in-place version and the same grid, in the same execution context: codes recorded while
+    a CUDA graph is being captured exist only inside that graph, so entries carry the id of the
+    capture they were made in (0: eager) and only match there.  One entry; it is dropped when
+    the tensor dies or the next input replaces it."""
+
+    def __init__(self) -> None:
+        self._key = self._src = self._val = None
+
+    def get(self, x: torch.Tensor, grid):
+        if self._src is not None and self._src() is x and self._key == (x._version, tuple(x.shape), x.dtype, grid):
+            return self._val
+        return None
+
+    def put(self, x: torch.Tensor, grid, val) -> None:
+        self._src = weakref.ref(x, self._dropped)
+        self._key, self._val = (x._version, tuple(x.shape), x.dtype, grid), val
+
+    def _dropped(self, ref) -> None:
+        if self._src is ref:
+            self.clear()
+
+    def clear(self) -> None:
+        self._key = self._src = self._val = None
+
+
+_last_input = _LastQuantizedInput()
 
 
 class Linear(nn.Module):
@@ -77,7 +112,14 @@ class Linear(nn.Module):
         if x2.shape[0] == 0:
             y = torch.zeros((0, self.out_features), dtype=self.out_dtype, device=xd.device)
         else:
-            xq, sx, zx = self._quantize_activations(x2)
+            grid = (self.act_scheme, self.act_qdtype.name, self.in_features,
+                    _backend.ops().capture_id(xd.device) if x.is_cuda else 0)
+            hit = _last_input.get(x, grid) if x.is_cuda else None
+            if hit is None:
+                hit = self._quantize_activations(x2)
+                if x.is_cuda:
+                    _last_input.put(x, grid, hit)
+            xq, sx, zx = hit
             y = _backend.ops().qlinear_i8(xq, wq, sx, _backend.on_cuda(self.weight_scale),
                                  bias=None if self.bias is None else _backend.on_cuda(self.bias), zx=zx,
                                  wsum=wsum if zx is not None else None, out_dtype=self.out_dtype)

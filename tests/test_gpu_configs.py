@@ -128,3 +128,44 @@ def test_graphed_module_replays_the_quantized_forward():
     assert torch.equal(g(x), qlin(x))
     with pytest.raises(ValueError, match="captured for"):
         g(torch.randn(8, 1024, device="cuda"))
+
+
+def test_sibling_layers_share_one_activation_quantization():
+    """q / k / v style siblings fed the same tensor reuse its codes; a new tensor, an in-place
+    change or another grid does not."""
+    from lucid_b200.nn.quantized.dynamic import linear as dl
+
+    torch.manual_seed(0)
+    a, b = (Q.quantize_dynamic(nn.Linear(256, 128).cuda()) for _ in range(2))
+    x = torch.randn(64, 256, device="cuda")
+    calls = []
+    orig = nnqd.Linear._quantize_activations
+
+    def counting(self, x2):
+        calls.append(1)
+        return orig(self, x2)
+
+    nnqd.Linear._quantize_activations = counting
+    try:
+        dl._last_input.clear()
+        ya, yb = a(x), b(x)
+        assert len(calls) == 1
+        x.mul_(2.0)  # in-place change: new version
+        ya2 = a(x)
+        assert len(calls) == 2
+        a(x.clone())  # another tensor
+        assert len(calls) == 3
+        b.set_activation_scheme("token_symmetric")
+        b(x)  # same tensor, other grid (replaces the entry)
+        a(x)
+        assert len(calls) == 5
+    finally:
+        nnqd.Linear._quantize_activations = orig
+        dl._last_input.clear()
+    fresh_a = Q.quantize_dynamic  # results are those of independent quantization
+    dl._last_input.clear()
+    assert torch.equal(a(x), ya2)
+    xb = x / 2.0
+    dl._last_input.clear()
+    b.set_activation_scheme("tensor_affine")
+    assert torch.allclose(b(xb), yb, rtol=1e-5, atol=1e-6)

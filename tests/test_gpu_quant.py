@@ -174,7 +174,7 @@ def test_dynamic_quantize_rows(ops, rows, cols, mode):
         np.testing.assert_array_equal(host(q).astype(np.int32), O.quantize(x, os_, oz, qdt, ch_axis=0).astype(np.int32))
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 1), (64, 1024), (257, 300), (100, 4099)])
+@pytest.mark.parametrize("rows,cols", [(1, 1), (2, 4), (33, 64), (64, 1024), (128, 1024), (129, 1024), (257, 300), (100, 4099)])
 @pytest.mark.parametrize("mode", ["sym_s8", "affine_u8"])
 def test_dynamic_quantize_tensor(ops, rows, cols, mode):
     x = rand((rows, cols), rows + cols) * 1.7
