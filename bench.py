@@ -440,6 +440,13 @@ def run_profile_case(args) -> int:
         x = torch.randn(8192, 8192, device=dev, generator=g)
         y = torch.randn(8192, 8192, device=dev, generator=g)
         fn = lambda: ops.fake_quantize_merge(x, y, "add_relu", 0.05, 12.0, 0, 255)  # noqa: E731
+    elif case == "gemm_shortk":
+        M, N, K = 8192, 2048, 512  # an encoder FFN projection: little K per output, epilogue-heavy
+        a = torch.randint(0, 256, (M, K), device=dev, dtype=torch.uint8, generator=g)
+        b = torch.randint(-128, 128, (N, K), device=dev, dtype=torch.int8, generator=g)
+        sx, sw, bias = torch.rand((), device=dev), torch.rand(N, device=dev), torch.randn(N, device=dev)
+        zx, wsum = torch.tensor(7.0, device=dev), ops.rowsum_s8(b)
+        fn = lambda: ops.qlinear_i8(a, b, sx, sw, bias=bias, zx=zx, wsum=wsum)  # noqa: E731
     elif case == "gemm_small":
         a = torch.randint(-128, 128, (64, 1024), device=dev, dtype=torch.int8, generator=g)
         b = torch.randint(-128, 128, (4096, 1024), device=dev, dtype=torch.int8, generator=g)
@@ -707,7 +714,7 @@ def main() -> int:
                     help="headline workload only: skip the companion workloads and the CPU baseline")
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed case of one kernel (gemm, quantize_rows, quantize_tensor, "
-                         "dequantize, quantize_given_scale, histc, merge, gemm_small, wo_gemv) for a profiler capture; prints no bench line")
+                         "dequantize, quantize_given_scale, histc, merge, gemm_small, gemm_shortk, wo_gemv) for a profiler capture; prints no bench line")
     ap.add_argument("--profile-batch", default=4)
     ap.add_argument("--gather", choices=("auto", "fused", "nccl"), default="auto",
                     help="N > 1: how output shards are exchanged (auto = fused if symmetric memory works)")
