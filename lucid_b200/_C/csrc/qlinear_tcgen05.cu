@@ -58,6 +58,7 @@ struct Params {
   int out_dtype;
   int64_t ldo;
   int out_vec;          // rows of `out` allow 16-byte stores
+  int fast_f32;         // 0, or 1 + (zero-point correction) + 2 * (bias): the compiled-in fp32 epilogue applies
   int32_t* status;
 };
 
@@ -310,6 +311,72 @@ __device__ __forceinline__ void drain_chunk(const Params& p, const uint32_t (&r)
   __syncwarp();
 }
 
+// The common case of drain_chunk with everything that can be decided per launch compiled in:
+// fp32 output to one buffer with 16-byte aligned rows, per-column weight scales, chunk fully
+// inside N.  Short-K products (an encoder's projections) are bound by this epilogue, and the
+// general form spends about half of its instructions on launch-invariant branches and 64-bit
+// index arithmetic.
+template <bool CORR, bool BIAS>
+__device__ __forceinline__ void drain_chunk_f32(const Params& p, const uint32_t (&r)[32], int c,
+                                                int64_t row_base, int64_t n0, int lane, float sxr,
+                                                const float* s_sw, const float* s_bias, const int* s_corr,
+                                                uint32_t* stg) {
+  uint32_t* mine = stg + lane * STG_PITCH;
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    int a[4] = {static_cast<int>(r[j]), static_cast<int>(r[j + 1]), static_cast<int>(r[j + 2]),
+                static_cast<int>(r[j + 3])};
+    if (CORR) {
+      const int4 cr = *reinterpret_cast<const int4*>(s_corr + c * 32 + j);
+      a[0] -= cr.x;
+      a[1] -= cr.y;
+      a[2] -= cr.z;
+      a[3] -= cr.w;
+    }
+    const float4 sv = *reinterpret_cast<const float4*>(s_sw + c * 32 + j);
+    float f[4] = {__fmul_rn(__fmul_rn(static_cast<float>(a[0]), sxr), sv.x),
+                  __fmul_rn(__fmul_rn(static_cast<float>(a[1]), sxr), sv.y),
+                  __fmul_rn(__fmul_rn(static_cast<float>(a[2]), sxr), sv.z),
+                  __fmul_rn(__fmul_rn(static_cast<float>(a[3]), sxr), sv.w)};
+    if (BIAS) {
+      const float4 bv = *reinterpret_cast<const float4*>(s_bias + c * 32 + j);
+      f[0] = __fadd_rn(f[0], bv.x);
+      f[1] = __fadd_rn(f[1], bv.y);
+      f[2] = __fadd_rn(f[2], bv.z);
+      f[3] = __fadd_rn(f[3], bv.w);
+    }
+    *reinterpret_cast<float4*>(mine + j) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+  __syncwarp();
+  const int sub = lane & 7, rr = lane >> 3;  // 8 lanes x 16 bytes per row, 4 rows per pass
+  float* o = static_cast<float*>(p.outs[0]) + (row_base + rr) * p.ldo + (n0 + c * 32 + sub * 4);
+  const int64_t step = 4 * p.ldo;
+  const int64_t rows_left = p.M - row_base - rr;  // row i*4 + rr exists while i*4 < rows_left
+  const uint32_t* src = stg + rr * STG_PITCH + sub * 4;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint4 w = *reinterpret_cast<const uint4*>(src + i * 4 * STG_PITCH);
+    if (i * 4 < rows_left) *reinterpret_cast<uint4*>(o) = w;
+    o += step;
+  }
+  __syncwarp();
+}
+
+// picks the compiled-in form when the launch and the chunk allow it
+__device__ __forceinline__ void drain(const Params& p, const uint32_t (&r)[32], int c, int64_t row_base,
+                                      int64_t n0, int lane, float sxr, const float* s_sw, const float* s_bias,
+                                      const int* s_corr, uint32_t* stg) {
+  if (p.fast_f32 && n0 + c * 32 + 32 <= p.N) {
+    switch (p.fast_f32) {
+      case 1: drain_chunk_f32<false, false>(p, r, c, row_base, n0, lane, sxr, s_sw, s_bias, s_corr, stg); return;
+      case 2: drain_chunk_f32<true, false>(p, r, c, row_base, n0, lane, sxr, s_sw, s_bias, s_corr, stg); return;
+      case 3: drain_chunk_f32<false, true>(p, r, c, row_base, n0, lane, sxr, s_sw, s_bias, s_corr, stg); return;
+      default: drain_chunk_f32<true, true>(p, r, c, row_base, n0, lane, sxr, s_sw, s_bias, s_corr, stg); return;
+    }
+  }
+  drain_chunk(p, r, c, row_base, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
+}
+
 template <int BNT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -483,7 +550,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tc_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
         tc_wait_ld();
         if (n0 + c * 32 < p.N)
-          drain_chunk(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
+          drain(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
       }
       tc_fence_before();
       __syncwarp();
@@ -747,7 +814,7 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tc_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
         tc_wait_ld();
         if (n0 + c * 32 < p.N)
-          drain_chunk(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
+          drain(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
       }
       tc_fence_before();
       __syncwarp();
@@ -893,6 +960,7 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
   for (int i = 0; i < n_out; ++i)
     if (!aligned(host_outs[i], 16)) p.out_vec = 0;
   p.status = status;
+  p.fast_f32 = (out_dtype == LC_F32 && sw && n_out == 1 && p.out_vec) ? 1 + (zx ? 1 : 0) + (bias ? 2 : 0) : 0;
 
   if (use_pair) {
     const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
