@@ -40,23 +40,24 @@ class _LastQuantizedInput:
     the tensor dies or the next input replaces it."""
 
     def __init__(self) -> None:
-        self._key = self._src = self._val = None
+        self._entry = None  # (weak reference, key, value): replaced as a whole, so readers in other threads see one entry
 
     def get(self, x: torch.Tensor, grid):
-        if self._src is not None and self._src() is x and self._key == (x._version, tuple(x.shape), x.dtype, grid):
-            return self._val
+        entry = self._entry
+        if entry is not None and entry[0]() is x and entry[1] == (x._version, tuple(x.shape), x.dtype, grid):
+            return entry[2]
         return None
 
     def put(self, x: torch.Tensor, grid, val) -> None:
-        self._src = weakref.ref(x, self._dropped)
-        self._key, self._val = (x._version, tuple(x.shape), x.dtype, grid), val
+        self._entry = (weakref.ref(x, self._dropped), (x._version, tuple(x.shape), x.dtype, grid), val)
 
     def _dropped(self, ref) -> None:
-        if self._src is ref:
-            self.clear()
+        entry = self._entry
+        if entry is not None and entry[0] is ref:
+            self._entry = None
 
     def clear(self) -> None:
-        self._key = self._src = self._val = None
+        self._entry = None
 
 
 _last_input = _LastQuantizedInput()
