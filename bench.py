@@ -328,6 +328,33 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
                     "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS}
     out["roundtrip_8192x8192"] = rt
     del x, q, s, z
+    # ---- int8 embedding table [131072, 4096] (537 MB > L2), 16384 looked-up tokens: 1 byte read
+    # and 4 bytes written per element (the reference's formulation decodes the whole table first)
+    try:
+        V, D, n = 131072, 4096, 16384
+        table = torch.randint(-128, 128, (V, D), dtype=torch.int8, device=dev, generator=g)
+        ts = torch.rand(V, device=dev, generator=g) * 0.05 + 1e-3
+        toks = [torch.randint(0, V, (n,), device=dev, generator=g) for _ in range(5)]  # 5 x 67 MB of rows rotate
+        turn = [0]
+
+        def next_tok():
+            turn[0] += 1
+            return toks[turn[0] % len(toks)]
+
+        ms = time_loop(torch, lambda: ops.embedding_s8(table, ts, None, next_tok()), 30, 5)
+        nbytes = n * D * 5 + n * 12
+        bag_off = torch.arange(0, n, 32, device=dev)
+        ms_bag = time_loop(torch, lambda: ops.embedding_bag_s8(table, ts, None, next_tok(), bag_off, "sum"), 30, 5)
+        bag_bytes = n * D + (n // 32) * D * 4 + n * 12
+        out["embedding_int8_131072x4096"] = {
+            "lookup_16384_tokens": {"ms": ms, "GB/s": nbytes / ms / 1e6, "algorithmic_bytes": nbytes,
+                                    "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm},
+            "bag_sum_512_bags_of_32": {"ms": ms_bag, "GB/s": bag_bytes / ms_bag / 1e6, "algorithmic_bytes": bag_bytes,
+                                       "frac_of_measured_hbm": bag_bytes / ms_bag / 1e6 / hbm},
+            "decode_whole_table_then_gather_bytes": V * D * 5 + n * D * 8}
+        del table, ts, toks, bag_off
+    except Exception as e:  # noqa: BLE001
+        out["embedding_int8_131072x4096"] = {"error": repr(e)[:200]}
     # ---- decode-shaped weight-only SwiGLU MLP: hidden 4096, FFN 14336, bf16 activations
     H, F = 4096, 14336
     sets = []
@@ -436,6 +463,15 @@ def run_profile_case(args) -> int:
     elif case == "histc":
         x = torch.randn(8192, 8192, device=dev, generator=g)
         fn = lambda: ops.histc(x, 2048, -6.0, 6.0)  # noqa: E731
+    elif case == "embedding":
+        table = torch.randint(-128, 128, (131072, 4096), dtype=torch.int8, device=dev, generator=g)
+        ts = torch.rand(131072, device=dev, generator=g) * 0.05 + 1e-3
+        toks = [torch.randint(0, 131072, (16384,), device=dev, generator=g) for _ in range(5)]
+        turn = [0]
+
+        def fn():
+            turn[0] += 1
+            return ops.embedding_s8(table, ts, None, toks[turn[0] % 5])
     elif case == "merge":
         x = torch.randn(8192, 8192, device=dev, generator=g)
         y = torch.randn(8192, 8192, device=dev, generator=g)
@@ -714,7 +750,7 @@ def main() -> int:
                     help="headline workload only: skip the companion workloads and the CPU baseline")
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed case of one kernel (gemm, quantize_rows, quantize_tensor, "
-                         "dequantize, quantize_given_scale, histc, merge, gemm_small, gemm_shortk, wo_gemv) for a profiler capture; prints no bench line")
+                         "dequantize, quantize_given_scale, histc, merge, embedding, gemm_small, gemm_shortk, wo_gemv) for a profiler capture; prints no bench line")
     ap.add_argument("--profile-batch", default=4)
     ap.add_argument("--gather", choices=("auto", "fused", "nccl"), default="auto",
                     help="N > 1: how output shards are exchanged (auto = fused if symmetric memory works)")

@@ -297,6 +297,34 @@ int32_t lc_group_matmul(const void* x, int32_t x_dtype, int64_t batch, int64_t K
                         const int32_t* packed, const float* scales, const float* biases,
                         int64_t N, int32_t group_size, int32_t bits, void* y, void* stream);
 
+/* ---- int8 embedding tables ---------------------------------------------
+ * Forward of the quantized Embedding (lucid/nn/quantized/sparse.py:140-143): the reference
+ * dequantizes the whole [V, D] table per call (lucid/quantization/_functional.py:281-293) and
+ * gathers from the fp32 copy (F.embedding, lucid/nn/functional/sparse.py:70); here
+ * out[i, :] = (f32(table[indices[i], :]) - zero_point[indices[i]]) * scale[indices[i]] for the
+ * looked-up rows only.  zero_point may be NULL (symmetric table).  An index outside
+ * [0, num_embeddings) yields a row of zeros and sets *status to 1 (status: device int32,
+ * cleared by the caller, may be NULL); the reference refuses such an index on the host
+ * (lucid/_C/backend/cpu/IndexBounds.h:89-93), which would need a device-to-host read here. */
+int32_t lc_embedding_s8_f32(const int8_t* table, const float* scale, const float* zero_point,
+                            const int64_t* indices, int64_t n, int64_t num_embeddings,
+                            int64_t embedding_dim, float* out, int32_t* status, void* stream);
+
+/* Forward of the quantized EmbeddingBag (lucid/nn/quantized/sparse.py:284-304) with the pooling
+ * of lucid/_C/backend/cpu/methods/Sequence.cpp:44-85: bag b covers indices[offsets[b] ..
+ * offsets[b+1]) (the last one runs to n unless include_last_offset, in which case offsets has
+ * one entry more than there are bags); entries equal to padding_idx (>= 0) are skipped; rows are
+ * decoded as above and added in index order starting from zero (mode 0), divided by the number
+ * of entries kept (mode 1), or reduced with max starting from the lowest float (mode 2); an
+ * empty bag gives zeros.  per_sample_weights (mode 0 only, may be NULL) multiplies each decoded
+ * row before it is added.  out: [bags, embedding_dim] fp32. */
+int32_t lc_embedding_bag_s8_f32(const int8_t* table, const float* scale, const float* zero_point,
+                                const int64_t* indices, int64_t n, const int64_t* offsets,
+                                int64_t n_offsets, const float* per_sample_weights,
+                                int64_t num_embeddings, int64_t embedding_dim, int32_t mode,
+                                int64_t padding_idx, int32_t include_last_offset, float* out,
+                                int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -69,6 +69,8 @@ SIGNATURES = {
     "lc_group_quantize_f32": (_i32, [_p, _i64, _i64, _i32, _i32, _p, _p, _p, _p]),
     "lc_group_dequantize": (_i32, [_p, _p, _p, _i64, _i64, _i32, _i32, _p, _p]),
     "lc_group_matmul": (_i32, [_p, _i32, _i64, _i64, _p, _p, _p, _i64, _i32, _i32, _p, _p]),
+    "lc_embedding_s8_f32": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _p, _p, _p]),
+    "lc_embedding_bag_s8_f32": (_i32, [_p, _p, _p, _p, _i64, _p, _i64, _p, _i64, _i64, _i32, _i64, _i32, _p, _p, _p]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -540,4 +540,69 @@ def group_matmul(x2d, packed, scales, biases, group_size: int = 64, bits: int = 
     return y
 
 
+# ----------------------------------------------------------------------------
+# int8 embedding tables
+# ----------------------------------------------------------------------------
+BAG_MODES = {"sum": 0, "mean": 1, "max": 2}
+
+
+def _table_args(table, scale, zero_point):
+    if table.dtype != torch.int8 or table.dim() != 2:
+        raise TypeError("embedding: the table must be a 2-D int8 tensor")
+    table = table.contiguous()
+    sc = _f32c(scale).reshape(-1)
+    if sc.numel() != table.shape[0]:
+        raise ValueError("embedding: one scale per table row is required")
+    zp = None if zero_point is None else _f32c(zero_point).reshape(-1)
+    if zp is not None and zp.numel() != table.shape[0]:
+        raise ValueError("embedding: one zero-point per table row is required")
+    return table, sc, zp
+
+
+def embedding_s8(table, scale, zero_point, indices, status=None):
+    """fp32 rows ``(f32(table[i]) - zero_point[i]) * scale[i]`` for every ``i`` in ``indices``
+    (any shape, integer dtype); result ``indices.shape + (D,)``.  ``status``: optional int32
+    device scalar set to 1 when an index lies outside the table (that row reads as zeros)."""
+    dev = _need_cuda(table, scale, indices)
+    table, sc, zp = _table_args(table, scale, zero_point)
+    idx = indices.to(torch.int64).contiguous()
+    V, D = table.shape
+    out = torch.empty(tuple(idx.shape) + (D,), dtype=torch.float32, device=dev)
+    with _on(dev):
+        check(lib.lc_embedding_s8_f32(table.data_ptr(), sc.data_ptr(), zp.data_ptr() if zp is not None else None,
+                                      idx.data_ptr(), idx.numel(), V, D, out.data_ptr(),
+                                      status.data_ptr() if status is not None else None, _stream(dev)))
+    return out
+
+
+def embedding_bag_s8(table, scale, zero_point, indices, offsets, mode: str = "mean", padding_idx=None,
+                     per_sample_weights=None, include_last_offset: bool = False, status=None):
+    """Pooled lookups: bag ``b`` covers ``indices[offsets[b]:offsets[b+1]]`` (1-D indices), rows
+    decoded like :func:`embedding_s8` and reduced in index order; result ``[bags, D]`` fp32."""
+    dev = _need_cuda(table, scale, indices, offsets)
+    if mode not in BAG_MODES:
+        raise ValueError(f"embedding_bag: mode must be one of {sorted(BAG_MODES)}, got {mode!r}")
+    table, sc, zp = _table_args(table, scale, zero_point)
+    idx = indices.to(torch.int64).contiguous().reshape(-1)
+    off = offsets.to(torch.int64).contiguous().reshape(-1)
+    psw = None
+    if per_sample_weights is not None:
+        if mode != "sum":
+            raise ValueError("embedding_bag: per_sample_weights is only supported with mode='sum'")
+        psw = _f32c(per_sample_weights).reshape(-1)
+        if psw.numel() != idx.numel():
+            raise ValueError("embedding_bag: per_sample_weights must have one weight per index")
+    V, D = table.shape
+    bags = off.numel() - 1 if include_last_offset else off.numel()
+    out = torch.empty((max(bags, 0), D), dtype=torch.float32, device=dev)
+    with _on(dev):
+        check(lib.lc_embedding_bag_s8_f32(table.data_ptr(), sc.data_ptr(), zp.data_ptr() if zp is not None else None,
+                                          idx.data_ptr(), idx.numel(), off.data_ptr(), off.numel(),
+                                          psw.data_ptr() if psw is not None else None, V, D, BAG_MODES[mode],
+                                          -1 if padding_idx is None else int(padding_idx), int(include_last_offset),
+                                          out.data_ptr(), status.data_ptr() if status is not None else None,
+                                          _stream(dev)))
+    return out
+
+
 __all__ = [n for n in dir() if not n.startswith("_")] + ["LucidCudaError"]

@@ -44,6 +44,18 @@ def activation_qparams(mod):
     return _backend.on_cuda(scale), _backend.on_cuda(zero_point), obs.qdtype
 
 
+def wire_inner(mod):
+    """The weighted layer carrying the qparams: a fused float module is a ``Sequential`` whose
+    observer sits after the pair, so its qconfig and observer replace whatever ``mod[0]``
+    carries (``lucid/nn/quantized/intrinsic.py:23-37``); any other module is returned as is."""
+    if not isinstance(mod, torch.nn.Sequential):
+        return mod
+    inner = mod[0]
+    inner.qconfig = mod.qconfig
+    inner.activation_post_process = mod.activation_post_process
+    return inner
+
+
 class Int8WeightCache:
     """GEMM-ready views of a layer's int8 weight, rebuilt when the buffer changes:
     a copy whose rows start on 16-byte boundaries (what TMA needs; the buffer itself

@@ -11,7 +11,7 @@ import torch
 from torch import nn
 
 from lucid_b200 import _backend
-from lucid_b200.nn.quantized._utils import activation_qparams, quantize_weight
+from lucid_b200.nn.quantized._utils import activation_qparams, quantize_weight, wire_inner
 from lucid_b200.quantization._functional import dequantize, fake_quantize
 from lucid_b200.quantization._qscheme import QDtype, quint8
 
@@ -92,8 +92,4 @@ class LinearReLU(Linear):
 
     @classmethod
     def from_float(cls, mod: nn.Module) -> "LinearReLU":
-        inner = mod[0] if isinstance(mod, nn.Sequential) else mod
-        for attr in ("qconfig", "activation_post_process"):
-            if not hasattr(inner, attr) and hasattr(mod, attr):
-                setattr(inner, attr, getattr(mod, attr))
-        return super().from_float(inner)
+        return super().from_float(wire_inner(mod))

@@ -15,15 +15,35 @@ from lucid_b200.quantization._qscheme import QDtype, qint8
 from lucid_b200.quantization.qconfig import (get_default_qat_qconfig_mapping, get_default_qconfig_mapping)
 
 
-def _is_linear_relu(m: nn.Module) -> bool:
-    return (isinstance(m, nn.Sequential) and len(m) == 2 and isinstance(m[0], nn.Linear)
-            and isinstance(m[1], nn.ReLU) and getattr(m, "_lucid_fused", False))
-
-
 def _observed_types() -> tuple[type, ...]:
+    """Float module types whose output ``prepare`` observes (``_quantize.py:46-71``)."""
+    import lucid_b200.nn.intrinsic as nni
     import lucid_b200.nn.quantized as nnq
 
-    return (nn.Linear, nnq.QuantStub, nnq.FloatFunctional)
+    return (nn.Linear, nn.Conv1d, nn.Conv2d, nn.Conv3d, nn.ConvTranspose1d, nn.ConvTranspose2d, nn.ConvTranspose3d,
+            nni.ConvReLU1d, nni.ConvReLU2d, nni.ConvReLU3d, nni.LinearReLU, nn.Sigmoid, nn.Hardswish,
+            nn.Hardsigmoid, nn.Tanh, nn.ELU, nn.LeakyReLU, nnq.QuantStub, nnq.FloatFunctional)
+
+
+def _quant_mapping() -> dict:
+    """Float module type -> ``from_float`` builder of its quantized form (``_quantize.py:74-121``)."""
+    import lucid_b200.nn.intrinsic as nni
+    import lucid_b200.nn.quantized as nnq
+
+    return {
+        nn.Linear: nnq.Linear.from_float,
+        nn.Conv1d: nnq.Conv1d.from_float, nn.Conv2d: nnq.Conv2d.from_float, nn.Conv3d: nnq.Conv3d.from_float,
+        nn.ConvTranspose1d: nnq.ConvTranspose1d.from_float, nn.ConvTranspose2d: nnq.ConvTranspose2d.from_float,
+        nn.ConvTranspose3d: nnq.ConvTranspose3d.from_float,
+        nn.Embedding: nnq.Embedding.from_float, nn.EmbeddingBag: nnq.EmbeddingBag.from_float,
+        nn.Sigmoid: nnq.Sigmoid.from_float, nn.Hardswish: nnq.Hardswish.from_float,
+        nn.Hardsigmoid: nnq.Hardsigmoid.from_float, nn.Tanh: nnq.Tanh.from_float, nn.ELU: nnq.ELU.from_float,
+        nn.LeakyReLU: nnq.LeakyReLU.from_float,
+        nni.ConvReLU1d: nnq.ConvReLU1d.from_float, nni.ConvReLU2d: nnq.ConvReLU2d.from_float,
+        nni.ConvReLU3d: nnq.ConvReLU3d.from_float, nni.LinearReLU: nnq.LinearReLU.from_float,
+        nnq.QuantStub: nnq.Quantize.from_float, nnq.DeQuantStub: nnq.DeQuantize.from_float,
+        nnq.FloatFunctional: nnq.QFunctional.from_float,
+    }
 
 
 # ---- group-wise (engine "mlx_group") builders --------------------------------
@@ -43,14 +63,24 @@ def _group_size_for(in_features: int):
     return None
 
 
-def _group_linear_builder(child: nn.Module) -> nn.Module:
-    from lucid_b200.nn.quantized import Linear as QLinear
-    from lucid_b200.nn.quantized import QuantizedLinearMLX
+def _group_linear_builder(relu: bool = False):
+    """Builder routing a (fused) Linear to the group-wise weight-only GEMM; a fused pair hands
+    over its inner Linear with the ReLU folded into the kernel's epilogue (``_quantize.py:148-185``)."""
 
-    gs = _group_size_for(child.in_features)
-    if gs is None:  # no group size divides in_features: keep the per-channel int8 module
-        return QLinear.from_float(child)
-    return QuantizedLinearMLX.from_float(child, bits=_group_weight_bits(child), group_size=gs)
+    def build(child: nn.Module) -> nn.Module:
+        from lucid_b200.nn.quantized import Linear as QLinear
+        from lucid_b200.nn.quantized import LinearReLU as QLinearReLU
+        from lucid_b200.nn.quantized import QuantizedLinearMLX
+
+        inner = child[0] if isinstance(child, nn.Sequential) else child
+        gs = _group_size_for(inner.in_features)
+        if gs is None:  # no group size divides in_features: keep the per-channel int8 module
+            return (QLinearReLU if relu else QLinear).from_float(child)
+        if inner is not child and getattr(inner, "qconfig", None) is None:
+            inner.qconfig = getattr(child, "qconfig", None)
+        return QuantizedLinearMLX.from_float(inner, bits=_group_weight_bits(inner), group_size=gs, relu=relu)
+
+    return build
 
 
 def _group_dynamic_builder(child: nn.Module, dtype: QDtype) -> nn.Module:
@@ -98,10 +128,14 @@ def convert(model: nn.Module, inplace: bool = False) -> nn.Module:
     import lucid_b200.nn.quantized as nnq
 
     model = model if inplace else copy.deepcopy(model)
-    build = _group_linear_builder if backends.quantized.use_mlx() else nnq.Linear.from_float
-    mapping = {nn.Linear: build, nnq.QuantStub: nnq.Quantize.from_float, nnq.DeQuantStub: nnq.DeQuantize.from_float,
-               nnq.FloatFunctional: nnq.QFunctional.from_float}
-    _convert_children(model, mapping, always=(nnq.DeQuantStub,))
+    import lucid_b200.nn.intrinsic as nni
+
+    mapping = _quant_mapping()
+    if backends.quantized.use_mlx():
+        mapping[nn.Linear] = _group_linear_builder()
+        mapping[nni.LinearReLU] = _group_linear_builder(relu=True)
+    # the stub leaving the quantized region and embedding tables need no calibration
+    _convert_children(model, mapping, always=(nnq.DeQuantStub, nn.Embedding, nn.EmbeddingBag))
     QConfigResolver.strip(model)
     model.eval()
     return model

@@ -366,8 +366,55 @@ def group_matmul(x, packed, scales, biases, group_size: int = 64, bits: int = 8)
 
 
 # --------------------------------------------------------------------------
-# seeded synthetic workloads (shapes and value distributions of the five
-# benchmark configurations)
+# int8 embedding tables (lucid/nn/quantized/sparse.py)
+# --------------------------------------------------------------------------
+def embedding_s8(table, scale, zero_point, indices) -> np.ndarray:
+    """Quantized ``Embedding.forward`` (lucid/nn/quantized/sparse.py:140-143): dequantize the
+    whole table per row (``ch_axis=0``), then gather the rows ``indices`` names."""
+    w = dequantize(np.asarray(table), scale, zero_point, ch_axis=0)
+    idx = np.asarray(indices, dtype=np.int64)
+    if idx.size and (idx.min() < 0 or idx.max() >= w.shape[0]):
+        raise IndexError("embedding: index out of range")
+    return w[idx]
+
+
+def embedding_bag_s8(table, scale, zero_point, indices, offsets, mode: str = "mean", padding_idx=None,
+                     per_sample_weights=None, include_last_offset: bool = False) -> np.ndarray:
+    """Quantized ``EmbeddingBag.forward`` (lucid/nn/quantized/sparse.py:284-304) with the CPU
+    pooling loop of lucid/_C/backend/cpu/methods/Sequence.cpp:44-85: fp32 accumulation in index
+    order from zero, ``padding_idx`` entries skipped, mean over the entries kept, max seeded with
+    the lowest float, an empty bag gives zeros.  ``per_sample_weights`` (sum only) scales each
+    looked-up row before it is added."""
+    w = dequantize(np.asarray(table), scale, zero_point, ch_axis=0)
+    idx = np.asarray(indices, dtype=np.int64).ravel()
+    off = np.asarray(offsets, dtype=np.int64).ravel()
+    bags = off.size - 1 if include_last_offset else off.size
+    out = np.zeros((max(bags, 0), w.shape[1]), dtype=np.float32)
+    psw = None if per_sample_weights is None else _f32(per_sample_weights).ravel()
+    for b in range(bags):
+        start = int(off[b])
+        end = int(off[b + 1]) if (b + 1 < bags or include_last_offset) else idx.size
+        acc = np.full(w.shape[1], np.finfo(np.float32).min if mode == "max" else 0, dtype=np.float32)
+        count = 0
+        for k in range(start, end):
+            row = int(idx[k])
+            if padding_idx is not None and padding_idx >= 0 and row == padding_idx:
+                continue
+            if row < 0 or row >= w.shape[0]:
+                raise IndexError("embedding_bag: index out of range")
+            v = w[row] if psw is None else (w[row] * psw[k]).astype(np.float32)
+            acc = np.where(v > acc, v, acc) if mode == "max" else (acc + v).astype(np.float32)
+            count += 1
+        if mode == "max" and count == 0:
+            acc[:] = 0
+        if mode == "mean" and count > 0:
+            acc = (acc / np.float32(count)).astype(np.float32)
+        out[b] = acc
+    return out
+
+
+# --------------------------------------------------------------------------
+# lucid.histc
 # --------------------------------------------------------------------------
 def histc(x, bins: int = 100, lo: float = 0.0, hi: float = 0.0) -> np.ndarray:
     """Counts of ``x`` in ``bins`` equal-width bins over ``[lo, hi]``, in ``x``'s dtype.
@@ -397,6 +444,10 @@ def histc(x, bins: int = 100, lo: float = 0.0, hi: float = 0.0) -> np.ndarray:
     return np.bincount(b, minlength=bins).astype(np.float64).astype(x.dtype if x.dtype.kind == "f" else np.float32)
 
 
+# --------------------------------------------------------------------------
+# seeded synthetic workloads (shapes and value distributions of the five
+# benchmark configurations)
+# --------------------------------------------------------------------------
 def synth_config1(seed: int = 20260921):
     r = np.random.default_rng(seed)
     x = r.standard_normal((64, 1024), dtype=F32)

@@ -143,3 +143,16 @@ def group_dequantize(packed, scales, biases, group_size=64, bits=8):
 def group_matmul(x2d, packed, scales, biases, group_size=64, bits=8):
     y = O.group_matmul(_np(x2d.float()), _np(packed), _np(scales), _np(biases), group_size, bits)
     return torch.tensor(y).to(x2d.dtype)
+
+
+def embedding_s8(table, scale, zero_point, indices, status=None):
+    z = np.zeros(table.shape[0], np.float32) if zero_point is None else _np(zero_point)
+    return torch.tensor(O.embedding_s8(_np(table), _np(scale), z, _np(indices)))
+
+
+def embedding_bag_s8(table, scale, zero_point, indices, offsets, mode="mean", padding_idx=None,
+                     per_sample_weights=None, include_last_offset=False, status=None):
+    z = np.zeros(table.shape[0], np.float32) if zero_point is None else _np(zero_point)
+    psw = None if per_sample_weights is None else _np(per_sample_weights)
+    return torch.tensor(O.embedding_bag_s8(_np(table), _np(scale), z, _np(indices), _np(offsets), mode, padding_idx,
+                                           psw, include_last_offset))

@@ -227,3 +227,37 @@ def test_histc_refusals_and_bulk():
         # torch buckets in float32; away from bin edges the two agree, and the totals always do
         want = torch.histc(torch.tensor(x), bins, lo, hi).numpy()
         assert np.abs(got - want).sum() <= 4
+
+
+@pytest.mark.parametrize("mode", ["sum", "mean", "max"])
+def test_embedding_oracle_against_torch(mode):
+    """The quantized table forwards are 'dequantize the table, then the float lookup'; torch
+    implements the float lookups with the semantics the reference mirrors (padding entries
+    skipped, mean over the entries kept, empty bags zero), on the index pattern of the
+    reference's own case (lucid/test/unit/quantization/test_module_breadth.py:96-108)."""
+    import torch
+
+    r = np.random.default_rng(0)
+    q = r.integers(-128, 128, size=(50, 16), dtype=np.int8)
+    s = (r.random(50).astype(np.float32) + 0.01) * np.float32(0.02)
+    z = r.integers(-5, 5, size=50).astype(np.float32)
+    w = torch.tensor(O.dequantize(q, s, z, ch_axis=0))
+    idx = np.array([1, 5, 9, 3, 7, 2, 8, 9, 9])
+    off = np.array([0, 3, 5, 5, 7])
+    assert np.array_equal(O.embedding_s8(q, s, z, idx.reshape(3, 3)),
+                          torch.nn.functional.embedding(torch.tensor(idx.reshape(3, 3)), w).numpy())
+    for pad in (None, 9):
+        want = torch.nn.functional.embedding_bag(torch.tensor(idx), w, torch.tensor(off), mode=mode, padding_idx=pad)
+        got = O.embedding_bag_s8(q, s, z, idx, off, mode, pad)
+        assert np.allclose(got, want.numpy(), rtol=1e-6, atol=1e-7)
+    want = torch.nn.functional.embedding_bag(torch.tensor(idx), w, torch.tensor(np.append(off, 9)), mode=mode,
+                                             include_last_offset=True)
+    assert np.allclose(O.embedding_bag_s8(q, s, z, idx, np.append(off, 9), mode, None, None, True), want.numpy(),
+                       rtol=1e-6, atol=1e-7)
+    if mode == "sum":
+        psw = r.standard_normal(9).astype(np.float32)
+        want = torch.nn.functional.embedding_bag(torch.tensor(idx), w, torch.tensor(off), mode="sum",
+                                                 per_sample_weights=torch.tensor(psw))
+        assert np.allclose(O.embedding_bag_s8(q, s, z, idx, off, "sum", None, psw), want.numpy(), rtol=1e-5, atol=1e-6)
+    with pytest.raises(IndexError):
+        O.embedding_s8(q, s, z, np.array([50]))
