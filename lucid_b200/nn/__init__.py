@@ -9,9 +9,9 @@ from torch.nn import (ELU, GELU, BatchNorm1d, BatchNorm2d, BatchNorm3d, Conv1d, 
                       Softmax, Tanh)
 from torch.nn import functional  # noqa: F401
 
-from lucid_b200.nn import intrinsic, quantized  # noqa: E402,F401
+from lucid_b200.nn import intrinsic, qat, quantized  # noqa: E402,F401
 
 __all__ = ["Module", "Parameter", "Sequential", "ModuleList", "Linear", "Conv1d", "Conv2d", "Conv3d",
            "ConvTranspose1d", "ConvTranspose2d", "ConvTranspose3d", "BatchNorm1d", "BatchNorm2d", "BatchNorm3d",
            "Embedding", "EmbeddingBag", "ReLU", "GELU", "SiLU", "Sigmoid", "Tanh", "ELU", "LeakyReLU", "Hardswish",
-           "Hardsigmoid", "LayerNorm", "Identity", "Softmax", "functional", "intrinsic", "quantized"]
+           "Hardsigmoid", "LayerNorm", "Identity", "Softmax", "functional", "intrinsic", "qat", "quantized"]

@@ -44,6 +44,15 @@ def activation_qparams(mod):
     return _backend.on_cuda(scale), _backend.on_cuda(zero_point), obs.qdtype
 
 
+def ieee_fp32():
+    """Context for a float library call (convolution, recurrent layer) that must compute in IEEE
+    fp32 as the reference does: by default the CUDA library runs them on TF32 tensor cores
+    (10-bit mantissa), which moves results across grid steps of a following requantization."""
+    cudnn = torch.backends.cudnn
+    return cudnn.flags(enabled=cudnn.enabled, benchmark=cudnn.benchmark, deterministic=cudnn.deterministic,
+                       allow_tf32=False)
+
+
 def wire_inner(mod):
     """The weighted layer carrying the qparams: a fused float module is a ``Sequential`` whose
     observer sits after the pair, so its qconfig and observer replace whatever ``mod[0]``

@@ -12,7 +12,7 @@ from torch import nn
 from torch.nn import functional as F
 
 from lucid_b200 import _backend
-from lucid_b200.nn.quantized._utils import activation_qparams, quantize_weight, wire_inner
+from lucid_b200.nn.quantized._utils import activation_qparams, ieee_fp32, quantize_weight, wire_inner
 from lucid_b200.quantization._functional import dequantize, fake_quantize, quantize
 from lucid_b200.quantization._qscheme import QDtype, per_channel_symmetric, qint8, quint8
 from lucid_b200.quantization.observer import PerChannelMinMaxObserver
@@ -76,7 +76,8 @@ class _QuantizedConvNd(nn.Module):
         weight = dequantize(_backend.on_cuda(self.weight_int8), _backend.on_cuda(self.weight_scale),
                             _backend.on_cuda(self.weight_zero_point), ch_axis=self.weight_ch_axis)
         bias = None if self.bias is None else _backend.on_cuda(self.bias)
-        y = self._activation(self._float_shell()._conv_forward(x, weight, bias))
+        with ieee_fp32():
+            y = self._activation(self._float_shell()._conv_forward(x, weight, bias))
         y = fake_quantize(y, _backend.on_cuda(self.scale), _backend.on_cuda(self.zero_point),
                           self.out_qdtype.quant_min, self.out_qdtype.quant_max)
         return y if input.is_cuda else y.to(input.device)
@@ -172,8 +173,10 @@ class _QuantizedConvTransposeNd(nn.Module):
                             _backend.on_cuda(self.weight_zero_point), ch_axis=self.weight_ch_axis)
         bias = None if self.bias is None else _backend.on_cuda(self.bias)
         rank = self._rank
-        y = _CONV_TRANSPOSE[rank](x, weight, bias, _as_tuple(self.stride, rank), _as_tuple(self.padding, rank),
-                                  _as_tuple(self.output_padding, rank), self.groups, _as_tuple(self.dilation, rank))
+        with ieee_fp32():
+            y = _CONV_TRANSPOSE[rank](x, weight, bias, _as_tuple(self.stride, rank), _as_tuple(self.padding, rank),
+                                      _as_tuple(self.output_padding, rank), self.groups,
+                                      _as_tuple(self.dilation, rank))
         y = fake_quantize(y, _backend.on_cuda(self.scale), _backend.on_cuda(self.zero_point),
                           self.out_qdtype.quant_min, self.out_qdtype.quant_max)
         return y if input.is_cuda else y.to(input.device)

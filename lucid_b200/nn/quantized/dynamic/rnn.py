@@ -13,6 +13,7 @@ import torch
 from torch import nn
 
 from lucid_b200 import _backend
+from lucid_b200.nn.quantized._utils import ieee_fp32
 from lucid_b200.quantization._functional import dequantize, quantize
 from lucid_b200.quantization._qscheme import QDtype, per_channel_symmetric, qint8
 
@@ -92,8 +93,10 @@ class _DynamicRecurrent(nn.Module):
             xd = _backend.on_cuda(x)
             rest = tuple(None if r is None else (tuple(_backend.on_cuda(t) for t in r) if isinstance(r, tuple)
                                                   else _backend.on_cuda(r)) for r in rest)
-            return self._loaded()(xd, *rest)
-        return self._loaded()(x, *rest)  # a PackedSequence goes straight to the shell
+            with ieee_fp32():
+                return self._loaded()(xd, *rest)
+        with ieee_fp32():
+            return self._loaded()(x, *rest)  # a PackedSequence goes straight to the shell
 
     def extra_repr(self) -> str:
         return f"{object.__getattribute__(self, '_shell').extra_repr()}, dynamic=True"

@@ -1,9 +1,9 @@
 """``lucid.quantization`` on the CUDA backend: the reference's public names
 (``lucid/quantization/__init__.py:74-125``) with the hot path on sm_100a kernels.
 
-Graph-mode (``prepare_fx`` / ``convert_fx``) and QAT preparation / fusion are tracing /
-training front ends that contain no kernels; they are exported for name compatibility and
-raise ``NotImplementedError`` here.
+Graph mode (``prepare_fx`` / ``convert_fx``) and the trainable Conv+BatchNorm fusion
+(``fuse_modules_qat``) are tracing / training front ends that contain no kernels; they are
+exported for name compatibility and raise ``NotImplementedError`` here.
 """
 from lucid_b200.quantization import _qgemm, observer, qconfig  # noqa: F401
 from lucid_b200.quantization._fake_quantize import FakeQuantize

@@ -28,6 +28,7 @@ def _observed_types() -> tuple[type, ...]:
 def _quant_mapping() -> dict:
     """Float module type -> ``from_float`` builder of its quantized form (``_quantize.py:74-121``)."""
     import lucid_b200.nn.intrinsic as nni
+    import lucid_b200.nn.qat as nnqat
     import lucid_b200.nn.quantized as nnq
 
     return {
@@ -43,6 +44,11 @@ def _quant_mapping() -> dict:
         nni.ConvReLU3d: nnq.ConvReLU3d.from_float, nni.LinearReLU: nnq.LinearReLU.from_float,
         nnq.QuantStub: nnq.Quantize.from_float, nnq.DeQuantStub: nnq.DeQuantize.from_float,
         nnq.FloatFunctional: nnq.QFunctional.from_float,
+        # trained QAT layers become the same inference layers
+        nnqat.Linear: nnq.Linear.from_float, nnqat.LinearReLU: nnq.LinearReLU.from_float,
+        nnqat.Conv1d: nnq.Conv1d.from_float, nnqat.Conv2d: nnq.Conv2d.from_float, nnqat.Conv3d: nnq.Conv3d.from_float,
+        nnqat.ConvReLU1d: nnq.ConvReLU1d.from_float, nnqat.ConvReLU2d: nnq.ConvReLU2d.from_float,
+        nnqat.ConvReLU3d: nnq.ConvReLU3d.from_float, nnqat.Embedding: nnq.Embedding.from_float,
     }
 
 
@@ -224,10 +230,40 @@ class _DynamicSwapper:
                           stacklevel=4)
 
 
-# ---- training-time entry points: outside this backend's scope -------------------------
-def prepare_qat(model: nn.Module, qconfig=None, inplace: bool = False):
-    """Quantization-aware training swaps float layers for ``nn.qat`` layers, which are
-    training-time float composites and not part of the inference path built here."""
-    raise NotImplementedError(
-        "prepare_qat is not provided by the CUDA inference backend: QAT layers are training-time float "
-        "composites (use FakeQuantize modules directly, or train with the reference and convert here)")
+# ---- quantization-aware training ----------------------------------------------------------
+def _qat_mapping() -> dict:
+    """Float module type -> builder of its trainable fake-quantized form (``_quantize.py:622-640``)."""
+    import lucid_b200.nn.intrinsic as nni
+    import lucid_b200.nn.qat as nnqat
+
+    return {nn.Linear: nnqat.Linear.from_float, nn.Conv1d: nnqat.Conv1d.from_float,
+            nn.Conv2d: nnqat.Conv2d.from_float, nn.Conv3d: nnqat.Conv3d.from_float,
+            nn.Embedding: nnqat.Embedding.from_float, nni.LinearReLU: nnqat.LinearReLU.from_float,
+            nni.ConvReLU1d: nnqat.ConvReLU1d.from_float, nni.ConvReLU2d: nnqat.ConvReLU2d.from_float,
+            nni.ConvReLU3d: nnqat.ConvReLU3d.from_float}
+
+
+def prepare_qat(model: nn.Module, qconfig=None, inplace: bool = False) -> nn.Module:
+    """Swap every weighted layer the qconfig resolution selects for its ``nn.qat`` form and
+    give every ``QuantStub`` a fake-quantizer; the model is returned in ``train`` mode, ready
+    to be fine-tuned and then handed to :func:`convert` (``_quantize.py:643-737``)."""
+    resolver = QConfigResolver.from_argument(qconfig, get_default_qat_qconfig_mapping)
+    model = model if inplace else copy.deepcopy(model)
+    model.train()
+    _prepare_qat_children(resolver, model, resolver.stamp(resolver.root(model)), _qat_mapping())
+    return model
+
+
+def _prepare_qat_children(resolver: QConfigResolver, parent: nn.Module, parent_entry: Resolved, qat_map) -> None:
+    import lucid_b200.nn.quantized as nnq
+
+    for entry in resolver.children(parent, parent_entry.path, parent_entry.qconfig):
+        child, qcfg = entry.module, entry.qconfig
+        resolver.stamp(entry)
+        build = qat_map.get(type(child))
+        if qcfg is not None and build is not None:
+            setattr(parent, entry.name, build(child))
+        elif qcfg is not None and isinstance(child, nnq.QuantStub):
+            child.activation_post_process = qcfg.activation()
+        else:
+            _prepare_qat_children(resolver, child, entry, qat_map)

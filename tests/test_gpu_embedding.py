@@ -95,6 +95,26 @@ def test_embedding_bag_matches_oracle(ops, mode, V, D):
     assert not got.cpu().numpy().any()
 
 
+@pytest.mark.parametrize("mode", ["sum", "mean", "max"])
+def test_embedding_bag_many_bags_wide_pieces(ops, mode):
+    """Enough (bag, column piece) items that the kernel takes its 16-byte-per-thread form."""
+    r = np.random.default_rng(77)
+    V, D, bags = 300, 256, 6000
+    q, s, z = _table(r, V, D, affine=True)
+    lengths = r.integers(0, 9, size=bags)
+    off = np.concatenate([[0], np.cumsum(lengths)[:-1]])
+    n = int(lengths.sum())
+    idx = r.integers(0, V, size=n)
+    w = r.standard_normal(n).astype(np.float32) if mode == "sum" else None
+    tq, ts, tz = _dev(q, s, z)
+    got = ops.embedding_bag_s8(tq, ts, tz, torch.tensor(idx, device="cuda"), torch.tensor(off, device="cuda"), mode, 7)
+    assert np.array_equal(got.cpu().numpy(), O.embedding_bag_s8(q, s, z, idx, off, mode, 7))
+    if w is not None:
+        got = ops.embedding_bag_s8(tq, ts, tz, torch.tensor(idx, device="cuda"), torch.tensor(off, device="cuda"), mode,
+                                   None, torch.tensor(w, device="cuda"))
+        assert np.allclose(got.cpu().numpy(), O.embedding_bag_s8(q, s, z, idx, off, mode, None, w), rtol=1e-6, atol=1e-7)
+
+
 def test_embedding_bag_per_sample_weights_and_refusals(ops):
     r = np.random.default_rng(9)
     q, s, z = _table(r, 40, 96)

@@ -160,7 +160,7 @@ def test_activation_quantizes(device, float_cls, q_cls):
     torch.manual_seed(0)
     m = nn.Sequential(nn.Linear(64, 64), float_cls()).eval()
     x = torch.randn(8, 64)
-    want = m(x)
+    want = m(x).detach()
     prepared = Q.prepare(m, Q.get_default_qconfig_mapping())
     for _ in range(5):
         prepared(torch.randn(8, 64))
@@ -286,3 +286,76 @@ def test_excluded_embedding_stays_float_and_qint4_recipe_reaches_the_table(devic
     codes = converted[0].weight_int8
     assert isinstance(converted[0], nnq.Embedding) and int(codes.min()) >= -8 and int(codes.max()) <= 7
     assert converted[0](torch.tensor([3, 4]).to(device)).shape == (2, 4)
+
+
+# ---- quantization-aware training (test_qat.py, test_safety.py TestQConfigGuards) --------
+class _QatNet(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.quant = nnq.QuantStub()
+        self.fc1 = nn.Linear(16, 32)
+        self.act = nn.ReLU()
+        self.fc2 = nn.Linear(32, 4)
+        self.dequant = nnq.DeQuantStub()
+
+    def forward(self, x):
+        return self.dequant(self.fc2(self.act(self.fc1(self.quant(x)))))
+
+
+def test_prepare_qat_trains_through_the_ste_and_converts(device):
+    import lucid_b200.nn.qat as nnqat
+
+    torch.manual_seed(2)
+    float_net = _QatNet()
+    qat = Q.prepare_qat(float_net).to(device)
+    assert isinstance(qat.fc1, nnqat.Linear) and qat.training and type(float_net.fc1) is nn.Linear
+    assert isinstance(qat.fc1.weight_fake_quant, Q.FakeQuantize)
+    assert isinstance(qat.quant.activation_post_process, Q.FakeQuantize)
+    w0 = qat.fc1.weight.detach().clone()
+    opt = torch.optim.SGD(qat.parameters(), lr=0.05)
+    g = torch.Generator().manual_seed(2)
+    for _ in range(5):
+        loss = (qat(torch.randn(16, 16, generator=g).to(device)) ** 2).mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    assert not torch.allclose(w0, qat.fc1.weight.detach())  # the gradient reached the float weight
+    qat.eval()
+    qm = Q.convert(qat)
+    assert isinstance(qm.fc1, nnq.Linear) and qm.fc1.weight_int8.dtype is torch.int8
+    assert isinstance(qm.quant, nnq.Quantize) and isinstance(qm.dequant, nnq.DeQuantize)
+    x = torch.randn(64, 16, generator=g).to(device)
+    with torch.no_grad():
+        want, got = qat(x).cpu(), qm(x).cpu()
+    assert float((want - got).abs().mean() / (want.abs().mean() + 1e-9)) < 0.1
+
+
+def test_qat_layers_need_a_qconfig_and_cover_conv_and_embedding(device):
+    import lucid_b200.nn.qat as nnqat
+
+    with pytest.raises(ValueError, match="qconfig"):
+        nnqat.Linear(8, 8)
+    with pytest.raises(ValueError, match="qconfig"):
+        nnqat.Conv2d(3, 8, 3)
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Conv2d(2, 4, 3, padding=1), nn.ReLU(), nn.Flatten(), nn.Linear(4 * 6 * 6, 5))
+    fused = Q.fuse_modules(model, [["0", "1"]])
+    qat = Q.prepare_qat(fused).to(device)
+    assert isinstance(qat[0], nnqat.ConvReLU2d) and isinstance(qat[3], nnqat.Linear)
+    x = torch.randn(3, 2, 6, 6).to(device)
+    qat(x).sum().backward()
+    assert qat[0].weight.grad is not None and float(qat[0].weight.grad.abs().sum()) > 0
+    qat.eval()
+    qm = Q.convert(qat)
+    assert isinstance(qm[0], nnq.ConvReLU2d) and isinstance(qm[3], nnq.Linear)
+    with torch.no_grad():
+        assert _rel(qat(x), qm(x)) < 0.1
+    emb = Q.prepare_qat(nn.Sequential(nn.Embedding(20, 8))).to(device)
+    assert isinstance(emb[0], nnqat.Embedding)
+    idx = torch.tensor([1, 5, 7]).to(device)
+    emb(idx).sum().backward()
+    assert emb[0].weight.grad is not None
+    qe = Q.convert(emb.eval())
+    assert isinstance(qe[0], nnq.Embedding)
+    with torch.no_grad():
+        assert _rel(emb(idx), qe(idx)) < 0.02
