@@ -224,8 +224,9 @@ constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 2 GHz
 // split-K partials of a whole pass: [tile][warp][16 rows][8*nt + 1]
 __host__ __device__ constexpr int red_bytes(int nt, int tmax) { return tmax * kConsumerWarps * 16 * (nt * 8 + 1) * 4; }
 __host__ __device__ constexpr int x_bytes(int nt, int xb) { return xb * nt * 8 * X_PITCH; }
-__host__ __device__ constexpr int stages(int nt, int tmax, int xb) {
-  return (kSmemBudget - 512 - red_bytes(nt, tmax) - x_bytes(nt, xb)) / STAGE;
+// a ring stage holds `grp` vertically adjacent 16-row tiles of one K chunk, fetched by one TMA box
+__host__ __device__ constexpr int stages(int nt, int tmax, int xb, int grp) {
+  return (kSmemBudget - 512 - red_bytes(nt, tmax) - x_bytes(nt, xb)) / (STAGE * grp);
 }
 }  // namespace ring
 
@@ -298,19 +299,25 @@ struct RawOperand<__nv_bfloat16> {
 
 // XB = number of activation-chunk buffers: with few row tiles per CTA a K chunk holds little
 // weight data, so more chunks must be in flight to keep the ring full.
-template <typename XT, int NT, int TMAX, int XB, bool SWIGLU>
+// GRP = row tiles per TMA box (1 or 2): the copy engine of an SM completes boxes one after the
+// other at a rate that hardly depends on their size, so 32-row boxes double what one SM can pull
+// from DRAM.  tmap_w has GRP*16-row boxes; tmap_w1 has 16-row boxes for the odd last tile of a pass.
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP>
 __global__ void __launch_bounds__(ring::kThreads, 1)
-wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w1,
+                      const __grid_constant__ CUtensorMap tmap_x,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
                       const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, int tiles_per_cta,
                       int overlap) {
   using namespace ring;
-  constexpr int S = stages(NT, TMAX, XB);
+  constexpr int S = stages(NT, TMAX, XB, GRP);
+  constexpr int GSTAGE = STAGE * GRP;
   static_assert(S >= 3, "ring too shallow");
+  static_assert(GRP == 1 || GRP == 2, "one or two row tiles per box");
   constexpr int COLS = NT * 8, RP = COLS + 1;
   extern __shared__ uint8_t wo_smem_raw[];
   const uint32_t base = (wo_smem_u32(wo_smem_raw) + 127u) & ~127u;
-  const uint32_t x_base = base + S * STAGE;
+  const uint32_t x_base = base + S * GSTAGE;
   const uint32_t red_base = x_base + x_bytes(NT, XB);
   const uint32_t bar_base = red_base + red_bytes(NT, TMAX);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -360,10 +367,11 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       if (overlap) {
         const int pass0 = my_tiles < TMAX ? my_tiles : TMAX;
         for (int kc = 0; kc < num_kc && prefilled < S; ++kc)
-          for (int j = 0; j < pass0 && prefilled < S; ++j, ++prefilled) {
-            wo_mbar_expect(full_bar(prefilled), STAGE);
-            wo_tma_load_2d(base + prefilled * STAGE, &tmap_w, kc * (KC / 4), static_cast<int>((tile0 + j) << 4),
-                           full_bar(prefilled));
+          for (int j = 0; j < pass0 && prefilled < S; j += GRP, ++prefilled) {
+            const bool whole = j + GRP <= pass0;
+            wo_mbar_expect(full_bar(prefilled), whole ? GSTAGE : STAGE);
+            wo_tma_load_2d(base + prefilled * GSTAGE, whole ? &tmap_w : &tmap_w1, kc * (KC / 4),
+                           static_cast<int>((tile0 + j) << 4), full_bar(prefilled));
             armed_mask |= 1u << prefilled;  // parity 0
           }
       }
@@ -384,7 +392,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           wo_tma_load_2d(x_base + xb * COLS * X_PITCH, &tmap_x, kc * (KC / 4), 0, xfull_bar(xb));
           xarmed_mask |= 1u << xb;
           xarmed_parity = (xarmed_parity & ~(1u << xb)) | (xphase << xb);
-          for (int j = 0; j < pass_tiles; ++j, ++issued) {
+          for (int j = 0; j < pass_tiles; j += GRP, ++issued) {
             if (issued >= prefilled) {
               if (!wo_mbar_wait(empty_bar(stage), phase ^ 1u)) {
                 atomicCAS(&g_wo_status, 0, 1);
@@ -392,8 +400,9 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                 break;
               }
               const int row0 = static_cast<int>((tile0 + t0 + j) << 4);
-              wo_mbar_expect(full_bar(stage), STAGE);
-              wo_tma_load_2d(base + stage * STAGE, &tmap_w, kc * (KC / 4), row0, full_bar(stage));
+              const bool whole = j + GRP <= pass_tiles;
+              wo_mbar_expect(full_bar(stage), whole ? GSTAGE : STAGE);
+              wo_tma_load_2d(base + stage * GSTAGE, whole ? &tmap_w : &tmap_w1, kc * (KC / 4), row0, full_bar(stage));
               armed_mask |= 1u << stage;
               armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
             }
@@ -474,14 +483,15 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
 #pragma unroll
         for (int j = 0; j < TMAX; ++j) {
           if (j < pass_tiles && ok) {
-            if (!wo_mbar_wait(full_bar(stage), phase)) {
+            // the first tile of a box waits for it, the last one (or the last of the pass) frees it
+            if (j % GRP == 0 && !wo_mbar_wait(full_bar(stage), phase)) {
               atomicCAS(&g_wo_status, 0, 2);
               ok = false;
             } else {
               // warp-uniform skip (mma.sync needs the whole warp); lanes past the end of K
               // inside a live warp contribute zero weights (raw 0 is code 0 in offset binary)
               if (warp_k_ok) {
-                const uint32_t src = base + stage * STAGE + g * W_PITCH + koff;
+                const uint32_t src = base + stage * GSTAGE + (j % GRP) * STAGE + g * W_PITCH + koff;
                 uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = make_uint4(0u, 0u, 0u, 0u);
                 if (k_ok) {
                   w0 = wo_lds128(src);
@@ -498,11 +508,13 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                     mma_16816<XT>(acc[j][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
                 }
               }
-              __syncwarp();
-              if (lane == 0) wo_mbar_arrive(empty_bar(stage));
-              if (++stage == S) {
-                stage = 0;
-                phase ^= 1u;
+              if (j % GRP == GRP - 1 || j == pass_tiles - 1) {
+                __syncwarp();
+                if (lane == 0) wo_mbar_arrive(empty_bar(stage));
+                if (++stage == S) {
+                  stage = 0;
+                  phase ^= 1u;
+                }
               }
             }
           }
@@ -781,11 +793,11 @@ static int32_t launch_wo_mma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
   return check_launch("wo_linear_s8 (mma)");
 }
 
-template <typename XT, int NT, int TMAX, int XB, bool SWIGLU = false>
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP>
 static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                    int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
                                    int64_t ldy, bool overlap, cudaStream_t st) {
-  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU>;
+  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU, GRP>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
   int dev = 0;
@@ -795,10 +807,14 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   });
   if (results[dev] != cudaSuccess)
     return fail(LC_ERR_CUDA, "wo_linear_s8: cannot reserve shared memory: %s", cudaGetErrorString(results[dev]));
-  // weights as [N, K/4] 4-byte units (box 256 x 16 = 1024 bytes x 16 rows), activations as
+  // weights as [N, K/4] 4-byte units (box 256 x 16*GRP = 1024 bytes x 16*GRP rows), activations as
   // [B, K/4] 8-byte units (box 256 x COLS = 2048 bytes per row)
-  CUtensorMap map_w, map_x;
+  CUtensorMap map_w, map_w1, map_x;
   if (int32_t rc = encode_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, w, static_cast<uint64_t>(K / 4),
+                                        static_cast<uint64_t>(N), static_cast<uint64_t>(ldw), ring::KC / 4, 16 * GRP,
+                                        CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  if (int32_t rc = encode_tensor_map_2d(&map_w1, CU_TENSOR_MAP_DATA_TYPE_UINT32, w, static_cast<uint64_t>(K / 4),
                                         static_cast<uint64_t>(N), static_cast<uint64_t>(ldw), ring::KC / 4, 16,
                                         CU_TENSOR_MAP_SWIZZLE_NONE))
     return rc;
@@ -821,7 +837,7 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = overlap ? 1 : 0;
-  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, B, K, N, sw, bias, y, ldy,
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_w1, map_x, B, K, N, sw, bias, y, ldy,
                                              static_cast<int>(per), overlap ? 1 : 0);
   if (err != cudaSuccess) return fail(LC_ERR_CUDA, "wo_linear_s8 (ring): %s", cudaGetErrorString(err));
   return check_launch("wo_linear_s8 (ring)");
@@ -834,13 +850,14 @@ static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
   // few row tiles per CTA (short, wide matrices): small reduction buffer, more activation chunks in flight
   const int64_t tiles = (N + 15) / 16, sms = sm_count();
   const bool few = (tiles + sms - 1) / sms <= 2;
+  // two row tiles per TMA box where the ring stays at least three boxes deep
   if (B <= 8)
-    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st)
-               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
+    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st)
+               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
   if (B <= 16)
-    return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st)
-               : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
-  return launch_wo_ring_inst<XT, 4, 1, 2, SWIGLU>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
+    return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st)
+               : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
+  return launch_wo_ring_inst<XT, 4, 1, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
 }
 
 template <typename XT>

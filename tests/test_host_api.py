@@ -427,3 +427,23 @@ def test_dynamic_recurrent(device, kind):
         getattr(nnqd, kind).from_float(nn.Linear(2, 2))
     swapped = Q.quantize_dynamic(nn.Sequential(fl) if cell else nn.ModuleDict({"rnn": fl}))
     assert isinstance(next(swapped.children()), getattr(nnqd, kind))
+
+
+def test_reference_module_paths_resolve_to_the_same_modules():
+    """Code written against the reference imports ``lucid...``; each such path must be the
+    package's own module object (a second copy would break isinstance checks in convert)."""
+    import importlib
+
+    import lucid as alias
+
+    assert alias is lucid
+    for path in ("quantization", "quantization._qgemm", "quantization.observer", "quantization.fuse_modules",
+                 "nn.quantized", "nn.quantized.dynamic", "nn.quantized.sparse", "nn.qat", "nn.intrinsic",
+                 "backends", "serialization"):
+        assert importlib.import_module(f"lucid.{path}") is importlib.import_module(f"lucid_b200.{path}"), path
+    from lucid.nn.qat import Linear as AliasQatLinear
+    from lucid_b200.nn.qat import Linear as QatLinear
+
+    assert AliasQatLinear is QatLinear
+    with pytest.raises(ModuleNotFoundError):
+        importlib.import_module("lucid.no_such_module")
