@@ -30,3 +30,5 @@ class ConvReLU3d(_FusedModule):
 
 
 __all__ = ["LinearReLU", "ConvReLU1d", "ConvReLU2d", "ConvReLU3d"]
+
+from lucid_b200.nn.intrinsic import qat  # noqa: E402,F401  (trainable Conv + BatchNorm fusion)

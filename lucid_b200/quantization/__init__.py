@@ -1,9 +1,8 @@
 """``lucid.quantization`` on the CUDA backend: the reference's public names
 (``lucid/quantization/__init__.py:74-125``) with the hot path on sm_100a kernels.
 
-Graph mode (``prepare_fx`` / ``convert_fx``) and the trainable Conv+BatchNorm fusion
-(``fuse_modules_qat``) are tracing / training front ends that contain no kernels; they are
-exported for name compatibility and raise ``NotImplementedError`` here.
+Graph mode (``prepare_fx`` / ``convert_fx``) is a tracing front end over the reference's own
+graph capture; the names are exported for compatibility and raise ``NotImplementedError``.
 """
 from lucid_b200.quantization import _qgemm, observer, qconfig  # noqa: F401
 from lucid_b200.quantization._fake_quantize import FakeQuantize
@@ -13,7 +12,7 @@ from lucid_b200.quantization._qscheme import (QDtype, QScheme, per_channel_affin
                                               per_tensor_affine, per_tensor_symmetric, qint4, qint8, qint32,
                                               quint8)
 from lucid_b200.quantization._quantize import convert, prepare, prepare_qat, quantize_dynamic
-from lucid_b200.quantization.fuse_modules import fuse_modules
+from lucid_b200.quantization.fuse_modules import fuse_modules, fuse_modules_qat
 from lucid_b200.quantization.observer import (FixedQParamsObserver, HistogramObserver, MinMaxObserver,
                                               MovingAverageMinMaxObserver,
                                               MovingAveragePerChannelMinMaxObserver, NoopObserver, ObserverBase,
@@ -35,7 +34,6 @@ def _not_on_this_backend(name: str):
 
 prepare_fx = _not_on_this_backend("prepare_fx")
 convert_fx = _not_on_this_backend("convert_fx")
-fuse_modules_qat = _not_on_this_backend("fuse_modules_qat")
 
 __all__ = [
     "QScheme", "per_tensor_affine", "per_tensor_symmetric", "per_channel_affine", "per_channel_symmetric",

@@ -28,6 +28,7 @@ def _observed_types() -> tuple[type, ...]:
 def _quant_mapping() -> dict:
     """Float module type -> ``from_float`` builder of its quantized form (``_quantize.py:74-121``)."""
     import lucid_b200.nn.intrinsic as nni
+    import lucid_b200.nn.intrinsic.qat as nniqat
     import lucid_b200.nn.qat as nnqat
     import lucid_b200.nn.quantized as nnq
 
@@ -45,6 +46,9 @@ def _quant_mapping() -> dict:
         nnq.QuantStub: nnq.Quantize.from_float, nnq.DeQuantStub: nnq.DeQuantize.from_float,
         nnq.FloatFunctional: nnq.QFunctional.from_float,
         # trained QAT layers become the same inference layers
+        nniqat.ConvBn1d: nniqat.convbn_to_quantized, nniqat.ConvBn2d: nniqat.convbn_to_quantized,
+        nniqat.ConvBn3d: nniqat.convbn_to_quantized, nniqat.ConvBnReLU1d: nniqat.convbn_to_quantized,
+        nniqat.ConvBnReLU2d: nniqat.convbn_to_quantized, nniqat.ConvBnReLU3d: nniqat.convbn_to_quantized,
         nnqat.Linear: nnq.Linear.from_float, nnqat.LinearReLU: nnq.LinearReLU.from_float,
         nnqat.Conv1d: nnq.Conv1d.from_float, nnqat.Conv2d: nnq.Conv2d.from_float, nnqat.Conv3d: nnq.Conv3d.from_float,
         nnqat.ConvReLU1d: nnq.ConvReLU1d.from_float, nnqat.ConvReLU2d: nnq.ConvReLU2d.from_float,
@@ -256,11 +260,14 @@ def prepare_qat(model: nn.Module, qconfig=None, inplace: bool = False) -> nn.Mod
 
 def _prepare_qat_children(resolver: QConfigResolver, parent: nn.Module, parent_entry: Resolved, qat_map) -> None:
     import lucid_b200.nn.quantized as nnq
+    from lucid_b200.nn.intrinsic.qat import _ConvBnNd
 
     for entry in resolver.children(parent, parent_entry.path, parent_entry.qconfig):
         child, qcfg = entry.module, entry.qconfig
         resolver.stamp(entry)
         build = qat_map.get(type(child))
+        if isinstance(child, _ConvBnNd):
+            continue  # fuse_modules_qat already made it trainable; its conv is used through the fused forward
         if qcfg is not None and build is not None:
             setattr(parent, entry.name, build(child))
         elif qcfg is not None and isinstance(child, nnq.QuantStub):

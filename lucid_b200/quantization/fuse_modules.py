@@ -1,4 +1,4 @@
-"""``fuse_modules`` (``lucid/quantization/fuse_modules.py:86-203``): collapse named runs of
+"""``fuse_modules`` / ``fuse_modules_qat`` (``lucid/quantization/fuse_modules.py:86-247``): collapse named runs of
 Conv (+ BatchNorm) (+ ReLU) or Linear + ReLU into one module before ``prepare``.  The first
 member of a run is replaced by the fused module, the others by ``Identity``, each in its own
 slot, so a hand-written ``forward`` keeps working.  BatchNorm is folded into the convolution's
@@ -49,5 +49,39 @@ def fuse_modules(model: nn.Module, modules_to_fuse: Sequence[Sequence[str]], inp
     for group in modules_to_fuse:
         mods = [model.get_submodule(name) for name in group]
         for name, repl in zip(group, _fuse_run(mods), strict=True):
+            _set_module(model, name, repl)
+    return model
+
+
+def _fuse_run_qat(mods: Sequence[nn.Module], qconfig) -> list[nn.Module]:
+    from lucid_b200.nn.intrinsic import qat as nniqat
+
+    ids: list[nn.Module] = [nn.Identity() for _ in range(len(mods) - 1)]
+    first = mods[0]
+    if isinstance(first, _CONV_TYPES):
+        rank = _CONV_TYPES.index(type(first))
+        rest = list(mods[1:])
+        if rest and isinstance(rest[0], _BN_TYPES):
+            bn = rest.pop(0)
+            relu = bool(rest and isinstance(rest[0], nn.ReLU))
+            cls = ((nniqat.ConvBnReLU1d, nniqat.ConvBnReLU2d, nniqat.ConvBnReLU3d) if relu
+                   else (nniqat.ConvBn1d, nniqat.ConvBn2d, nniqat.ConvBn3d))[rank]
+            return [cls(first, bn, qconfig=qconfig), *ids]
+        if rest and isinstance(rest[0], nn.ReLU):  # no BatchNorm: the plain fused pair; prepare_qat makes it trainable
+            return [_CONV_RELU[type(first)](first, nn.ReLU()), *ids]
+        return [first, *ids]
+    if isinstance(first, nn.Linear) and len(mods) == 2 and isinstance(mods[1], nn.ReLU):
+        return [nni.LinearReLU(first, nn.ReLU()), *ids]
+    raise ValueError(f"fuse_modules_qat: unsupported pattern {[type(m).__name__ for m in mods]}")
+
+
+def fuse_modules_qat(model: nn.Module, modules_to_fuse: Sequence[Sequence[str]], qconfig, inplace: bool = False):
+    """Fusion for quantization-aware training: a Conv followed by a BatchNorm becomes a trainable
+    ``nn.intrinsic.qat.ConvBn*`` layer that folds the BatchNorm on every forward (run before
+    ``prepare_qat``, which leaves those layers as they are)."""
+    model = model if inplace else copy.deepcopy(model)
+    for group in modules_to_fuse:
+        mods = [model.get_submodule(name) for name in group]
+        for name, repl in zip(group, _fuse_run_qat(mods, qconfig), strict=True):
             _set_module(model, name, repl)
     return model

@@ -301,7 +301,7 @@ def test_group_engine_routing(device):
 
 
 def test_unsupported_front_ends_raise():
-    for fn in (Q.prepare_fx, Q.convert_fx, Q.fuse_modules_qat):
+    for fn in (Q.prepare_fx, Q.convert_fx):
         with pytest.raises(NotImplementedError):
             fn(nn.Linear(2, 2))
 

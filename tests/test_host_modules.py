@@ -206,7 +206,7 @@ def test_quantized_embedding_bag(device):
         m = nn.Sequential(nn.EmbeddingBag(50, 16, mode=mode))
         idx = torch.tensor([1, 5, 9, 3, 7, 2, 8])
         off = torch.tensor([0, 3, 5])
-        want = m[0](idx, off)
+        want = m[0](idx, off).detach()
         qm = Q.convert(m)
         assert isinstance(qm[0], nnq.EmbeddingBag) and qm[0].weight_int8.dtype is torch.int8
         got = qm[0](idx.to(device), off.to(device)).cpu()
@@ -359,3 +359,45 @@ def test_qat_layers_need_a_qconfig_and_cover_conv_and_embedding(device):
     assert isinstance(qe[0], nnq.Embedding)
     with torch.no_grad():
         assert _rel(emb(idx), qe(idx)) < 0.02
+
+
+# ---- trainable Conv + BatchNorm fusion (test_qat.py TestConvBnReLUQAT, test_qat_fused.py) ----
+def test_fuse_modules_qat_trains_batchnorm_and_converts(device):
+    import lucid_b200.nn.intrinsic.qat as nniqat
+
+    torch.manual_seed(4)
+    net = _ConvNet()
+    qcfg = Q.get_default_qat_qconfig()
+    fused = Q.fuse_modules_qat(net, [["conv", "bn", "relu"]], qcfg)
+    assert isinstance(fused.conv, nniqat.ConvBnReLU2d) and isinstance(fused.bn, nn.Identity)
+    assert isinstance(net.bn, nn.BatchNorm2d)  # a copy was fused
+    qat = Q.prepare_qat(fused, qcfg).to(device)
+    assert isinstance(qat.conv, nniqat.ConvBnReLU2d) and type(qat.conv.conv) is nn.Conv2d
+    w, b = qat.conv._fold()
+    assert w.shape == (8, 3, 3, 3) and b.shape == (8,)
+    mean0 = qat.conv.bn.running_mean.clone()
+    opt = torch.optim.SGD(qat.parameters(), lr=0.01)
+    for _ in range(4):
+        loss = (qat(torch.randn(2, 3, 8, 8).to(device)) ** 2).mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    assert qat.conv.conv.weight.grad is not None and qat.conv.bn.weight.grad is not None
+    assert not torch.equal(mean0, qat.conv.bn.running_mean)  # batch statistics kept updating
+    qat.conv.freeze_bn_stats()
+    frozen = qat.conv.bn.running_mean.clone()
+    qat.train()
+    qat(torch.randn(2, 3, 8, 8).to(device))
+    assert torch.equal(frozen, qat.conv.bn.running_mean) and not qat.conv.bn.training
+    qat.eval()
+    qm = Q.convert(qat)
+    assert isinstance(qm.conv, nnq.ConvReLU2d) and qm.conv.weight_int8.dtype is torch.int8
+    x = torch.randn(4, 3, 8, 8).to(device)
+    with torch.no_grad():
+        assert qm(x).shape == (4, 10) and _rel(qat(x), qm(x)) < 0.1
+    with pytest.raises(ValueError, match="qconfig"):
+        nniqat.ConvBn2d(nn.Conv2d(3, 8, 3), nn.BatchNorm2d(8))
+    with pytest.raises(ValueError, match="running statistics"):
+        nniqat.ConvBn2d(nn.Conv2d(3, 8, 3), nn.BatchNorm2d(8, track_running_stats=False), qconfig=qcfg)
+    with pytest.raises(ValueError, match="unsupported pattern"):
+        Q.fuse_modules_qat(net, [["bn", "relu"]], qcfg)
