@@ -852,8 +852,8 @@ static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
   const bool few = (tiles + sms - 1) / sms <= 2;
   // (the kernel can fetch two row tiles per TMA box, GRP = 2; one per box is the measured default)
   if (B <= 8)
-    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st)
-               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
+    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st)
+               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
   if (B <= 16)
     return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st)
                : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
