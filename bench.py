@@ -472,6 +472,16 @@ def run_profile_case(args) -> int:
         def fn():
             turn[0] += 1
             return ops.embedding_s8(table, ts, None, toks[turn[0] % 5])
+    elif case == "embedding_bag":
+        table = torch.randint(-128, 128, (131072, 4096), dtype=torch.int8, device=dev, generator=g)
+        ts = torch.rand(131072, device=dev, generator=g) * 0.05 + 1e-3
+        toks = [torch.randint(0, 131072, (16384,), device=dev, generator=g) for _ in range(5)]
+        off = torch.arange(0, 16384, 32, device=dev)
+        turn = [0]
+
+        def fn():
+            turn[0] += 1
+            return ops.embedding_bag_s8(table, ts, None, toks[turn[0] % 5], off, "sum")
     elif case == "merge":
         x = torch.randn(8192, 8192, device=dev, generator=g)
         y = torch.randn(8192, 8192, device=dev, generator=g)
@@ -750,7 +760,7 @@ def main() -> int:
                     help="headline workload only: skip the companion workloads and the CPU baseline")
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed case of one kernel (gemm, quantize_rows, quantize_tensor, "
-                         "dequantize, quantize_given_scale, histc, merge, embedding, gemm_small, gemm_shortk, wo_gemv) for a profiler capture; prints no bench line")
+                         "dequantize, quantize_given_scale, histc, merge, embedding, embedding_bag, gemm_small, gemm_shortk, wo_gemv) for a profiler capture; prints no bench line")
     ap.add_argument("--profile-batch", default=4)
     ap.add_argument("--gather", choices=("auto", "fused", "nccl"), default="auto",
                     help="N > 1: how output shards are exchanged (auto = fused if symmetric memory works)")

@@ -66,7 +66,15 @@ def _on(dev: torch.device):
     return torch.cuda.device(dev)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(dev: torch.device) -> int:
+    """The current stream of ``dev`` as a raw ``cudaStream_t`` value (the binding's direct query
+    when it has one: building a ``torch.cuda.Stream`` object per launch costs several
+    microseconds of host time)."""
+    if _raw_stream is not None:
+        return _raw_stream(dev.index if dev.index is not None else torch.cuda.current_device())
     return torch.cuda.current_stream(dev).cuda_stream
 
 
