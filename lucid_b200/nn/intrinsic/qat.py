@@ -136,4 +136,8 @@ def convbn_to_quantized(mod: nn.Module) -> nn.Module:
     return q
 
 
+# names the reference uses for the same builder
+_convbn_to_quantized = convbn_to_quantized
+convbnrelu2d_to_quantized = convbn_to_quantized
+
 __all__ = ["ConvBn1d", "ConvBn2d", "ConvBn3d", "ConvBnReLU1d", "ConvBnReLU2d", "ConvBnReLU3d"]
