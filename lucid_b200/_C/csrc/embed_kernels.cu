@@ -88,7 +88,7 @@ __device__ __forceinline__ float pool1(float acc, float v) {
 // time and the indices of the next batch are requested before the current one is reduced.
 // CW = 16 / 4 need embedding_dim % CW == 0 and a table aligned to CW bytes; CW = 1 takes anything.
 template <int CW, int DEPTH, int MODE>
-__global__ void __launch_bounds__(kEmbThreads)
+__global__ void __launch_bounds__(kEmbThreads, 4)
 embedding_bag_s8_kernel(const int8_t* __restrict__ table, const float* __restrict__ scale,
                         const float* __restrict__ zero_point, const int64_t* __restrict__ idx,
                         const int64_t* __restrict__ offsets, const float* __restrict__ weights, const BagSpec sp,
