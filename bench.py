@@ -424,7 +424,7 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
         # has just seen, which a loop over one tensor object would turn into a no-op)
         ms = time_loop(torch, lambda: qlin(x1.detach()), 200, 20)
         entry = {"us_per_forward": ms * 1e3, "TOPS": 2 * 64 * 4096 * 1024 / ms / 1e9,
-                 "note": "eager: the host prepares three launches per forward"}
+                 "note": "eager: host-bound (two launches per forward, their output allocations and argument checks)"}
         try:  # the same module captured in a CUDA graph (one launch per forward, input copied in)
             import lucid_b200
 
