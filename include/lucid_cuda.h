@@ -241,6 +241,20 @@ int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_t lda, cons
                             int32_t n_out, int32_t out_dtype, int64_t ldo, int32_t* status,
                             int32_t variant, void* stream);
 
+/* Bit of `variant` (lc_qlinear_i8_ex, lc_qlinear_i8_multi, lc_wo_gemm_16) that turns a launch into
+ * a test of the kernels' bounded waits: the producer role issues no loads and every wait gives up
+ * after a few thousand cycles, so each role records its code in `status` (required), the CTAs free
+ * their TMEM and the kernel returns without having written a valid output.  Nothing traps or
+ * spins without a bound; the next ordinary launch is unaffected. */
+#define LC_QLINEAR_WAIT_TEST 256
+
+/* Reads the device status word of the kernels above on the host: synchronises `stream`, returns
+ * LC_OK when the word is 0 and LC_ERR_TIMEOUT (with the role that gave up in lc_last_error) when a
+ * bounded device-side wait ran out; clear != 0 resets the word.  The reference's engine reports
+ * failures as exceptions from a synchronous call (lucid/_C/ops/quantized/QuantizedMatmul.cpp:42-45);
+ * this is the asynchronous counterpart. */
+int32_t lc_qlinear_check_status(const int32_t* status, int32_t clear, void* stream);
+
 /* row sums of an int8 matrix as int32 (the zero-point correction term) */
 int32_t lc_rowsum_s8(const int8_t* b, int64_t rows, int64_t cols, int64_t ldb, int32_t* out,
                      void* stream);
@@ -262,6 +276,15 @@ int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K
                         const int8_t* wq, int64_t ldw, int64_t N, const float* sw,
                         const float* bias, void* y, int64_t ldy, int32_t flags, void* stream);
 
+/* lc_wo_linear_s8 followed, in the same kernel, by what the statically quantized Linear applies
+ * to its output (lucid/nn/quantized/linear.py:206-214; LinearReLU, lucid/nn/quantized/intrinsic.py:40):
+ * y = max(y, 0) if relu, then y = (clip(rint(y * (1/S)) + Z, quant_min, quant_max) - Z) * S with
+ * the calibrated S = *out_scale, Z = *out_zp (device scalars; both NULL: no requantization). */
+int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
+                           const int8_t* wq, int64_t ldw, int64_t N, const float* sw, const float* bias,
+                           int32_t relu, const float* out_scale, const float* out_zp, int32_t quant_min,
+                           int32_t quant_max, void* y, int64_t ldy, int32_t flags, void* stream);
+
 /* Gate and up projection of a SwiGLU MLP in one pass over the weights, with the activation
  * fused: wq is [N2 = 2F, K] with rows interleaved in blocks of 8 (rows 16t..16t+7 are gate
  * rows 8t..8t+7, rows 16t+8..16t+15 the matching up rows), sw / bias interleaved the same
@@ -273,6 +296,46 @@ int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K
 int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
                         const int8_t* wq, int64_t ldw, int64_t N2, const float* sw, const float* bias,
                         void* y, int64_t ldy, int32_t flags, void* stream);
+
+/* ---- weight-only Linear on the tensor cores, for more rows than a GEMV handles ----
+ * The statically quantized Linear's forward, dequantize(W) -> F.linear -> (ReLU) -> fake_quantize
+ * (lucid/nn/quantized/linear.py:206-214, LinearReLU in lucid/nn/quantized/intrinsic.py:40), and
+ * the weight-only product of quantized_matmul_op (lucid/_C/ops/quantized/QuantizedMatmul.cpp:143-207)
+ * for per-channel int8 weights, as ONE tcgen05 kind::f16 GEMM with fp32 accumulation:
+ *   acc[m,n] = sum_t sum_k a_t[m,k] * w16[n,k]
+ *   y        = acc * sw[n] + rowsum[m] * colcorr[n] + bias[n]      (each step one fp32 operation)
+ *   y        = max(y, 0)                                           if relu
+ *   out      = (clip(rint(y * (1/S)) + Z, quant_min, quant_max) - Z) * S   if out_scale / out_zp
+ * a: [M, n_terms * K] bf16 (or f16 with n_terms = 1): the n_terms addends of the activation side
+ * by side, row stride lda elements.  An fp32 activation is the exact sum of three bf16 terms
+ * (lc_split_f32_bf16x3), so every product is exact and only the accumulation rounds, as in an
+ * fp32 GEMM; a bf16 / f16 activation is its own single term.  w16: [N, K] the int8 codes widened
+ * exactly to a_dtype (lc_widen_s8), row stride ldw elements; no fp32 copy of the weight is ever
+ * made.  lda, ldw and K are multiples of 8; with n_terms > 1, K is a multiple of 64 (zero-padded).
+ * sw: N floats or NULL; bias: N floats or NULL; rowsum [M] and colcorr [N] (= -zw[n] * sw[n], the
+ * weight zero-point term) both or neither; out_scale / out_zp: device scalars of the calibrated
+ * output grid, both or neither.  out_dtype: LC_F32, LC_BF16 or LC_F16, ldo in elements.
+ * status, variant: as for lc_qlinear_i8_ex. */
+int32_t lc_wo_gemm_16(const void* a, int32_t a_dtype, int32_t n_terms, int64_t lda, const void* w16,
+                      int64_t ldw, int64_t M, int64_t N, int64_t K, const float* sw, const float* bias,
+                      const float* rowsum, const float* colcorr, int32_t relu, const float* out_scale,
+                      const float* out_zp, int32_t quant_min, int32_t quant_max, void* out,
+                      int32_t out_dtype, int64_t ldo, int32_t* status, int32_t variant, void* stream);
+
+/* int8 codes [rows, cols] (row stride ld_in) -> the same integers as bf16 or f16 (exact for every
+ * code), row stride ld_out >= cols elements, columns [cols, ld_out) zero-filled.  The operand
+ * layout of lc_wo_gemm_16; made once per weight (the conversion step of
+ * lucid/nn/quantized/linear.py:216-235 from_float, extended by one cached copy). */
+int32_t lc_widen_s8(const int8_t* q, int64_t rows, int64_t cols, int64_t ld_in, void* out, int32_t out_dtype,
+                    int64_t ld_out, void* stream);
+
+/* x fp32 [rows, cols] (row stride ldx) -> terms bf16 [rows, 3 * kp]: x1 = bf16(x), x2 = bf16(x - x1),
+ * x3 = bf16(x - x1 - x2) in columns [0, kp), [kp, 2kp), [2kp, 3kp), zero-filled beyond `cols`; x1 + x2 + x3
+ * == x exactly for every normal fp32 value.  kp >= cols, a multiple of 64.  rowsum (may be NULL)
+ * receives sum_k x[m,k] in fp32.  The activation operand of lc_wo_gemm_16 for fp32 inputs
+ * (the reference feeds fp32 activations to its float GEMM, lucid/_C/nn/Linear.cpp:74-136). */
+int32_t lc_split_f32_bf16x3(const float* x, int64_t rows, int64_t cols, int64_t ldx, void* terms, int64_t kp,
+                            float* rowsum, void* stream);
 
 /* Synchronises the device and reads the status word of the weight-only kernels on the
  * current device: 0, or the code of a bounded device-side wait that ran out (the

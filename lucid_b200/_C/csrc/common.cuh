@@ -71,6 +71,14 @@ __device__ __forceinline__ int code_to_int(float c, float qmin, float qmax) {
   return (c != c) ? 0 : __float2int_rn(cl);
 }
 
+// fake_quantize of one value onto a per-tensor grid: (clip(round(x * inv) + z) - z) * s, NaN
+// passing through (lucid/quantization/_functional.py:326-333); inv = 1 / s by IEEE division.
+__device__ __forceinline__ float fake_quant_value(float x, float s, float inv, float z, float qmin, float qmax) {
+  const float pre = grid_code(x, inv, z);
+  const float q = (pre != pre) ? pre : fminf(fmaxf(pre, qmin), qmax);
+  return __fmul_rn(__fsub_rn(q, z), s);
+}
+
 // Fast path for grids that coincide with the storage type's own range (qint8 [-128,127] in
 // int8, [0,255] in uint8): the float->int conversion rounds to nearest even and the packing
 // instruction saturates, so clip + cast cost nothing extra; NaN converts to 0 as the

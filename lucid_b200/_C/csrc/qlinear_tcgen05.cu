@@ -11,6 +11,15 @@
 // accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of
 // tile i overlaps the main loop of tile i+1.  No multicast is used anywhere.
 //
+// The same kernels, instantiated with WO = true, run the weight-only Linear for more rows than a
+// GEMV handles: tcgen05.mma kind::f16 on 16-bit operands with fp32 accumulation in TMEM.  The int8
+// weight codes are exact in bf16 / f16; an fp32 activation is the exact sum of three bf16 terms
+// (x = x1 + x2 + x3, each the bf16 rounding of what the previous ones left), stored side by side
+// along K, so the product runs as three passes over the weight's K blocks into ONE accumulator:
+// every partial product is exact in fp32 and only the accumulation rounds, as in an fp32 GEMM.
+// The epilogue applies the per-channel weight scale, an optional weight zero-point term, the
+// bias, an optional ReLU and an optional requantization onto a calibrated per-tensor grid.
+//
 // Every wait on an mbarrier is bounded: when the bound is hit the waiting role
 // records a code in the caller's status word, leaves its loop, the CTA waits
 // (bounded) for its own TMA copies in flight, frees its TMEM and returns.
@@ -60,6 +69,15 @@ struct Params {
   int out_vec;          // rows of `out` allow 16-byte stores
   int fast_f32;         // 0, or 1 + (zero-point correction) + 2 * (bias): the compiled-in fp32 epilogue applies
   int32_t* status;
+  int wait_test;        // test hook: the producer role issues nothing and every wait gives up after a few thousand cycles
+  // weight-only (WO) instantiation only
+  int kb_wrap;          // K blocks of the weight; A holds n_terms times as many and B's K coordinate wraps
+  const float* rowsum;  // [M] sum_k x[m,k] or null   } weight zero-point term rowsum[m] * colcorr[n]
+  const float* colcorr; // [N] -zw[n]*sw[n] or null   }
+  int relu;
+  const float* fq_scale;  // device scalars of the output grid, or null: no requantization
+  const float* fq_zp;
+  float fq_min, fq_max;
 };
 
 // ---- PTX wrappers ----------------------------------------------------------
@@ -88,11 +106,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // bounded wait: false when the bound was hit
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long budget = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kWaitCycles) return false;
+    if (clock64() - t0 > budget) return false;
   }
   return true;
 }
@@ -120,6 +138,15 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -205,6 +232,119 @@ __device__ __forceinline__ void report(int32_t* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
 
+// Second half of every epilogue chunk: the warp's 32 x 32 staged values (row-major, STG_PITCH
+// words per row; floats unless the output is int32) go out as whole 64- or 128-byte row
+// segments (4 or 8 rows per instruction) to every destination buffer.  Writing whole segments
+// matters most when a destination is another GPU's memory.
+__device__ __forceinline__ void store_staged(const Params& p, const uint32_t* stg, int c, int64_t row_base,
+                                             int64_t n0, int lane) {
+  const int64_t col0 = n0 + c * 32;
+  if (p.out_dtype == LC_BF16 || p.out_dtype == LC_F16) {
+    const int sub = lane & 3, rr = lane >> 2;  // 4 lanes x 16 bytes per row, 8 rows per pass
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int rloc = i * 8 + rr;
+      const int64_t row = row_base + rloc, col = col0 + sub * 8;
+      const float4 lo = *reinterpret_cast<const float4*>(stg + rloc * STG_PITCH + sub * 8);
+      const float4 hi = *reinterpret_cast<const float4*>(stg + rloc * STG_PITCH + sub * 8 + 4);
+      if (row < p.M && col < p.N) {
+        uint4 w;
+        if (p.out_dtype == LC_BF16) {
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(lo.x, lo.y), h1 = __floats2bfloat162_rn(lo.z, lo.w);
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(hi.x, hi.y), h3 = __floats2bfloat162_rn(hi.z, hi.w);
+          w.x = *reinterpret_cast<uint32_t*>(&h0);
+          w.y = *reinterpret_cast<uint32_t*>(&h1);
+          w.z = *reinterpret_cast<uint32_t*>(&h2);
+          w.w = *reinterpret_cast<uint32_t*>(&h3);
+        } else {
+          __half2 h0 = __floats2half2_rn(lo.x, lo.y), h1 = __floats2half2_rn(lo.z, lo.w);
+          __half2 h2 = __floats2half2_rn(hi.x, hi.y), h3 = __floats2half2_rn(hi.z, hi.w);
+          w.x = *reinterpret_cast<uint32_t*>(&h0);
+          w.y = *reinterpret_cast<uint32_t*>(&h1);
+          w.z = *reinterpret_cast<uint32_t*>(&h2);
+          w.w = *reinterpret_cast<uint32_t*>(&h3);
+        }
+        for (int d = 0; d < p.n_out; ++d) {
+          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.outs[d]) + row * p.ldo + col;
+          if (p.out_vec && col + 8 <= p.N) {
+            *reinterpret_cast<uint4*>(o) = w;
+          } else {
+            const __nv_bfloat16* hv = reinterpret_cast<const __nv_bfloat16*>(&w);
+            for (int e = 0; e < 8; ++e)
+              if (col + e < p.N) o[e] = hv[e];
+          }
+        }
+      }
+    }
+  } else {
+    const int sub = lane & 7, rr = lane >> 3;  // 8 lanes x 16 bytes per row, 4 rows per pass
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rloc = i * 4 + rr;
+      const int64_t row = row_base + rloc, col = col0 + sub * 4;
+      const uint4 w = *reinterpret_cast<const uint4*>(stg + rloc * STG_PITCH + sub * 4);
+      if (row < p.M && col < p.N) {
+        if (p.n_out == 1 && p.out_vec && col + 4 <= p.N) {
+          *reinterpret_cast<uint4*>(static_cast<uint32_t*>(p.outs[0]) + row * p.ldo + col) = w;
+          continue;
+        }
+        for (int d = 0; d < p.n_out; ++d) {
+          uint32_t* o = static_cast<uint32_t*>(p.outs[d]) + row * p.ldo + col;
+          if (p.out_vec && col + 4 <= p.N) {
+            *reinterpret_cast<uint4*>(o) = w;
+          } else {
+            const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+            for (int e = 0; e < 4; ++e)
+              if (col + e < p.N) o[e] = wv[e];
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+}
+
+// Epilogue chunk of the weight-only instantiation: the accumulator holds fp32 sums of
+// x[m,k] * code[n,k]; out = requant(relu(acc * sw[n] + rowsum[m] * colcorr[n] + bias[n])), every
+// step one IEEE fp32 operation as in the reference's eager epilogue
+// (lucid/nn/quantized/linear.py:206-214: linear, activation, fake_quantize).
+__device__ __forceinline__ void drain_chunk_wo(const Params& p, const uint32_t (&r)[32], int c, int64_t row_base,
+                                               int64_t n0, int lane, float rs, const float* s_sw,
+                                               const float* s_bias, const float* s_cc, float fq_s, float fq_inv,
+                                               float fq_z, uint32_t* stg) {
+  uint32_t* mine = stg + lane * STG_PITCH;
+  const bool has_cc = p.colcorr != nullptr, has_bias = p.bias != nullptr, relu = p.relu != 0,
+             fq = p.fq_scale != nullptr;
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 sv = *reinterpret_cast<const float4*>(s_sw + c * 32 + j);
+    float f[4] = {__fmul_rn(__uint_as_float(r[j]), sv.x), __fmul_rn(__uint_as_float(r[j + 1]), sv.y),
+                  __fmul_rn(__uint_as_float(r[j + 2]), sv.z), __fmul_rn(__uint_as_float(r[j + 3]), sv.w)};
+    if (has_cc) {
+      const float4 cv = *reinterpret_cast<const float4*>(s_cc + c * 32 + j);
+      f[0] = __fadd_rn(f[0], __fmul_rn(rs, cv.x));
+      f[1] = __fadd_rn(f[1], __fmul_rn(rs, cv.y));
+      f[2] = __fadd_rn(f[2], __fmul_rn(rs, cv.z));
+      f[3] = __fadd_rn(f[3], __fmul_rn(rs, cv.w));
+    }
+    if (has_bias) {
+      const float4 bv = *reinterpret_cast<const float4*>(s_bias + c * 32 + j);
+      f[0] = __fadd_rn(f[0], bv.x);
+      f[1] = __fadd_rn(f[1], bv.y);
+      f[2] = __fadd_rn(f[2], bv.z);
+      f[3] = __fadd_rn(f[3], bv.w);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (relu) f[e] = f[e] < 0.0f ? 0.0f : f[e];  // NaN compares false and stays
+      if (fq) f[e] = fake_quant_value(f[e], fq_s, fq_inv, fq_z, p.fq_min, p.fq_max);
+    }
+    *reinterpret_cast<float4*>(mine + j) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+  __syncwarp();
+  store_staged(p, stg, c, row_base, n0, lane);
+}
+
 // One 32-row x 32-column chunk of the accumulator: lane = row computes the 32 outputs,
 // the warp transposes them through shared memory, then stores rows as whole 64/128-byte
 // segments (4 or 8 rows per instruction) to every destination buffer.  Writing whole
@@ -254,61 +394,7 @@ __device__ __forceinline__ void drain_chunk(const Params& p, const uint32_t (&r)
     *reinterpret_cast<uint4*>(mine + j) = make_uint4(w[0], w[1], w[2], w[3]);
   }
   __syncwarp();
-  const int64_t col0 = n0 + c * 32;
-  if (p.out_dtype == LC_BF16) {
-    const int sub = lane & 3, rr = lane >> 2;  // 4 lanes x 16 bytes per row, 8 rows per pass
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int rloc = i * 8 + rr;
-      const int64_t row = row_base + rloc, col = col0 + sub * 8;
-      const float4 lo = *reinterpret_cast<const float4*>(stg + rloc * STG_PITCH + sub * 8);
-      const float4 hi = *reinterpret_cast<const float4*>(stg + rloc * STG_PITCH + sub * 8 + 4);
-      if (row < p.M && col < p.N) {
-        __nv_bfloat162 h0 = __floats2bfloat162_rn(lo.x, lo.y), h1 = __floats2bfloat162_rn(lo.z, lo.w);
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(hi.x, hi.y), h3 = __floats2bfloat162_rn(hi.z, hi.w);
-        uint4 w;
-        w.x = *reinterpret_cast<uint32_t*>(&h0);
-        w.y = *reinterpret_cast<uint32_t*>(&h1);
-        w.z = *reinterpret_cast<uint32_t*>(&h2);
-        w.w = *reinterpret_cast<uint32_t*>(&h3);
-        for (int d = 0; d < p.n_out; ++d) {
-          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.outs[d]) + row * p.ldo + col;
-          if (p.out_vec && col + 8 <= p.N) {
-            *reinterpret_cast<uint4*>(o) = w;
-          } else {
-            const __nv_bfloat16* hv = reinterpret_cast<const __nv_bfloat16*>(&w);
-            for (int e = 0; e < 8; ++e)
-              if (col + e < p.N) o[e] = hv[e];
-          }
-        }
-      }
-    }
-  } else {
-    const int sub = lane & 7, rr = lane >> 3;  // 8 lanes x 16 bytes per row, 4 rows per pass
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int rloc = i * 4 + rr;
-      const int64_t row = row_base + rloc, col = col0 + sub * 4;
-      const uint4 w = *reinterpret_cast<const uint4*>(stg + rloc * STG_PITCH + sub * 4);
-      if (row < p.M && col < p.N) {
-        if (p.n_out == 1 && p.out_vec && col + 4 <= p.N) {
-          *reinterpret_cast<uint4*>(static_cast<uint32_t*>(p.outs[0]) + row * p.ldo + col) = w;
-          continue;
-        }
-        for (int d = 0; d < p.n_out; ++d) {
-          uint32_t* o = static_cast<uint32_t*>(p.outs[d]) + row * p.ldo + col;
-          if (p.out_vec && col + 4 <= p.N) {
-            *reinterpret_cast<uint4*>(o) = w;
-          } else {
-            const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
-            for (int e = 0; e < 4; ++e)
-              if (col + e < p.N) o[e] = wv[e];
-          }
-        }
-      }
-    }
-  }
-  __syncwarp();
+  store_staged(p, stg, c, row_base, n0, lane);
 }
 
 // The common case of drain_chunk with everything that can be decided per launch compiled in:
@@ -377,7 +463,7 @@ __device__ __forceinline__ void drain(const Params& p, const uint32_t (&r)[32], 
   drain_chunk(p, r, c, row_base, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
 }
 
-template <int BNT>
+template <int BNT, bool WO>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const Params p, const uint32_t idesc) {
@@ -401,6 +487,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const long long budget = p.wait_test ? 20000LL : kWaitCycles;
 
   const int64_t tiles_m = (p.M + BM - 1) / BM;
   const int64_t tiles_n = (p.N + BN - 1) / BN;
@@ -442,12 +529,13 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      // under the wait test the producer issues nothing, so every consumer wait runs out
+      for (int64_t t = blockIdx.x; t < num_tiles && ok && !p.wait_test; t += gridDim.x) {
         int64_t tm, tn;
         tile_coords(t, tiles_m, tiles_n, tm, tn);
         const int m0 = static_cast<int>(tm * BM), n0 = static_cast<int>(tn * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, budget)) {
             report(p.status, ST_PRODUCER);
             ok = false;
             break;
@@ -455,7 +543,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           tma_load_2d(a_dst, &tmap_a, kb * BK, m0, full_bar(stage));
-          tma_load_2d(a_dst + A_BYTES, &tmap_b, kb * BK, n0, full_bar(stage));
+          tma_load_2d(a_dst + A_BYTES, &tmap_b, (WO ? kb % p.kb_wrap : kb) * BK, n0, full_bar(stage));
           armed[stage] = true;
           armed_parity[stage] = phase;
           if (++stage == STAGES) {
@@ -478,14 +566,14 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
         const int as = static_cast<int>(it & 1);
         const uint32_t aphase = static_cast<uint32_t>((it >> 1) & 1);
-        if (!mbar_wait(acc_empty_bar(as), aphase ^ 1u)) {
+        if (!mbar_wait(acc_empty_bar(as), aphase ^ 1u, budget)) {
           report(p.status, ST_MMA);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase)) {
+          if (!mbar_wait(full_bar(stage), phase, budget)) {
             report(p.status, ST_MMA);
             ok = false;
             break;
@@ -498,7 +586,10 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int j = 0; j < BK / UMMA_K; ++j) {
             // advancing K inside the swizzle atom = advancing the start address
             const uint64_t koff = static_cast<uint64_t>((j * UMMA_K) >> 4);
-            tc_mma_i8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
+            if constexpr (WO)
+              tc_mma_f16(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
+            else
+              tc_mma_i8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
           }
           tc_commit(empty_bar(stage));  // frees the smem slot once these MMAs retire
           if (++stage == STAGES) {
@@ -517,6 +608,11 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     (warp - 2) * STG_WARP_WORDS;
     const float sx_scalar = (p.sx && !p.sx_per_row) ? __ldg(p.sx) : 1.0f;
     const int zx_i = p.zx ? __float2int_rn(__ldg(p.zx)) : 0;
+    // output grid of the weight-only epilogue (device scalars; 1 / s by IEEE division as the
+    // reference's fake_quantize computes it for a tensor scale)
+    const float fq_s = (WO && p.fq_scale) ? __ldg(p.fq_scale) : 1.0f;
+    const float fq_inv = __fdiv_rn(1.0f, fq_s);
+    const float fq_z = (WO && p.fq_zp) ? __ldg(p.fq_zp) : 0.0f;
     int64_t it = 0;
     for (int64_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
       int64_t tm, tn;
@@ -529,19 +625,23 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool in = n < p.N;
         s_sw[j] = (in && p.sw) ? __ldg(p.sw + n) : 1.0f;
         s_bias[j] = (in && p.bias) ? __ldg(p.bias + n) : 0.0f;
-        s_corr[j] = (in && p.wsum) ? zx_i * __ldg(p.wsum + n) : 0;
+        if constexpr (WO)
+          reinterpret_cast<float*>(s_corr)[j] = (in && p.colcorr) ? __ldg(p.colcorr + n) : 0.0f;
+        else
+          s_corr[j] = (in && p.wsum) ? zx_i * __ldg(p.wsum + n) : 0;
       }
       const int as = static_cast<int>(it & 1);
       const uint32_t aphase = static_cast<uint32_t>((it >> 1) & 1);
       // also publishes the staged constants to the other epilogue warps
-      if (!epilogue_all(mbar_wait(acc_full_bar(as), aphase))) {
+      if (!epilogue_all(mbar_wait(acc_full_bar(as), aphase, budget))) {
         report(p.status, ST_EPILOGUE);
         break;
       }
       tc_fence_after();
       const int64_t row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const float sxr = p.sx_per_row ? (row_ok ? __ldg(p.sx + row) : 0.0f) : sx_scalar;
+      const float sxr = WO ? ((p.rowsum && row_ok) ? __ldg(p.rowsum + row) : 0.0f)
+                           : (p.sx_per_row ? (row_ok ? __ldg(p.sx + row) : 0.0f) : sx_scalar);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(as * BN);
 #pragma unroll 1
@@ -549,8 +649,13 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t r[32];
         tc_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
         tc_wait_ld();
-        if (n0 + c * 32 < p.N)
-          drain(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
+        if (n0 + c * 32 < p.N) {
+          if constexpr (WO)
+            drain_chunk_wo(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, reinterpret_cast<const float*>(s_corr),
+                           fq_s, fq_inv, fq_z, stg);
+          else
+            drain(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -633,11 +738,21 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
       "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}" ::"r"(bar)
       : "memory");
 }
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __host__ __device__ constexpr uint32_t make_idesc_pair(bool a_unsigned) {
   return (2u << 4) | ((a_unsigned ? 0u : 1u) << 7) | (1u << 10) |
          (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>((2 * BM) >> 4) << 24);
 }
 
+template <bool WO>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b, const Params p, const uint32_t idesc) {
@@ -658,6 +773,7 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const long long budget = p.wait_test ? 20000LL : kWaitCycles;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int64_t pair_id = blockIdx.x >> 1;
@@ -704,13 +820,14 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs) {
+      // under the wait test the producers issue nothing, so every consumer wait runs out
+      for (int64_t t = pair_id; t < num_tiles && ok && !p.wait_test; t += num_pairs) {
         int64_t tm, tn;
         tile_coords(t, tiles_m, tiles_n, tm, tn);
         const int m0 = static_cast<int>(tm * 2 * BM + rank * BM);
         const int n0 = static_cast<int>(tn * BN + rank * BNH);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, budget)) {
             report(p.status, ST_PRODUCER);
             ok = false;
             break;
@@ -723,7 +840,7 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             armed_parity[stage] = phase;
           }
           tma_load_2d_pair(a_dst, &tmap_a, kb * BK, m0, lead_full);
-          tma_load_2d_pair(a_dst + A_BYTES2, &tmap_b, kb * BK, n0, lead_full);
+          tma_load_2d_pair(a_dst + A_BYTES2, &tmap_b, (WO ? kb % p.kb_wrap : kb) * BK, n0, lead_full);
           if (++stage == STAGES2) {
             stage = 0;
             phase ^= 1u;
@@ -745,14 +862,14 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int64_t t = pair_id; t < num_tiles && ok; t += num_pairs, ++it) {
         const int as = static_cast<int>(it & 1);
         const uint32_t aphase = static_cast<uint32_t>((it >> 1) & 1);
-        if (!mbar_wait(acc_empty_bar(as), aphase ^ 1u)) {
+        if (!mbar_wait(acc_empty_bar(as), aphase ^ 1u, budget)) {
           report(p.status, ST_MMA);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(as * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase)) {
+          if (!mbar_wait(full_bar(stage), phase, budget)) {
             report(p.status, ST_MMA);
             ok = false;
             break;
@@ -764,7 +881,10 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int j = 0; j < BK / UMMA_K; ++j) {
             const uint64_t koff = static_cast<uint64_t>((j * UMMA_K) >> 4);
-            tc_mma_i8_pair(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
+            if constexpr (WO)
+              tc_mma_f16_pair(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
+            else
+              tc_mma_i8_pair(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
           }
           tc_commit_pair(empty_bar(stage));
           if (++stage == STAGES2) {
@@ -783,6 +903,11 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     (warp - 2) * STG_WARP_WORDS;
     const float sx_scalar = (p.sx && !p.sx_per_row) ? __ldg(p.sx) : 1.0f;
     const int zx_i = p.zx ? __float2int_rn(__ldg(p.zx)) : 0;
+    // output grid of the weight-only epilogue (device scalars; 1 / s by IEEE division as the
+    // reference's fake_quantize computes it for a tensor scale)
+    const float fq_s = (WO && p.fq_scale) ? __ldg(p.fq_scale) : 1.0f;
+    const float fq_inv = __fdiv_rn(1.0f, fq_s);
+    const float fq_z = (WO && p.fq_zp) ? __ldg(p.fq_zp) : 0.0f;
     int64_t it = 0;
     for (int64_t t = pair_id; t < num_tiles; t += num_pairs, ++it) {
       int64_t tm, tn;
@@ -794,18 +919,22 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool in = n < p.N;
         s_sw[j] = (in && p.sw) ? __ldg(p.sw + n) : 1.0f;
         s_bias[j] = (in && p.bias) ? __ldg(p.bias + n) : 0.0f;
-        s_corr[j] = (in && p.wsum) ? zx_i * __ldg(p.wsum + n) : 0;
+        if constexpr (WO)
+          reinterpret_cast<float*>(s_corr)[j] = (in && p.colcorr) ? __ldg(p.colcorr + n) : 0.0f;
+        else
+          s_corr[j] = (in && p.wsum) ? zx_i * __ldg(p.wsum + n) : 0;
       }
       const int as = static_cast<int>(it & 1);
       const uint32_t aphase = static_cast<uint32_t>((it >> 1) & 1);
-      if (!epilogue_all(mbar_wait(acc_full_bar(as), aphase))) {
+      if (!epilogue_all(mbar_wait(acc_full_bar(as), aphase, budget))) {
         report(p.status, ST_EPILOGUE);
         break;
       }
       tc_fence_after();
       const int64_t row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const float sxr = p.sx_per_row ? (row_ok ? __ldg(p.sx + row) : 0.0f) : sx_scalar;
+      const float sxr = WO ? ((p.rowsum && row_ok) ? __ldg(p.rowsum + row) : 0.0f)
+                           : (p.sx_per_row ? (row_ok ? __ldg(p.sx + row) : 0.0f) : sx_scalar);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(as * BN);
 #pragma unroll 1
@@ -813,8 +942,13 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t r[32];
         tc_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
         tc_wait_ld();
-        if (n0 + c * 32 < p.N)
-          drain(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
+        if (n0 + c * 32 < p.N) {
+          if constexpr (WO)
+            drain_chunk_wo(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, reinterpret_cast<const float*>(s_corr),
+                           fq_s, fq_inv, fq_z, stg);
+          else
+            drain(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -844,6 +978,11 @@ static int32_t make_map(CUtensorMap* map, const void* base, int64_t rows, int64_
                               static_cast<uint32_t>(box_rows), CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+template <typename Kernel>
+static cudaError_t reserve_smem(Kernel kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
 static int32_t ensure_smem_attr() {
   constexpr int kMaxDevices = 64;
   static std::once_flag flags[kMaxDevices];
@@ -852,22 +991,81 @@ static int32_t ensure_smem_attr() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return fail(LC_ERR_CUDA, "no current CUDA device");
   std::call_once(flags[dev], [dev]() {
-    results[dev] = cudaFuncSetAttribute(qlinear_i8_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        NarrowCfg<256>::kSmemBytes);
-    if (results[dev] == cudaSuccess)
-      results[dev] = cudaFuncSetAttribute(qlinear_i8_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          NarrowCfg<64>::kSmemBytes);
-    if (results[dev] == cudaSuccess)
-      results[dev] = cudaFuncSetAttribute(qlinear_i8_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          NarrowCfg<32>::kSmemBytes);
-    if (results[dev] == cudaSuccess)
-      results[dev] = cudaFuncSetAttribute(qlinear_i8_pair_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES2);
+    cudaError_t e = reserve_smem(qlinear_i8_kernel<256, false>, NarrowCfg<256>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<64, false>, NarrowCfg<64>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<32, false>, NarrowCfg<32>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_pair_kernel<false>, pair::SMEM_BYTES2);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<256, true>, NarrowCfg<256>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<64, true>, NarrowCfg<64>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<32, true>, NarrowCfg<32>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_pair_kernel<true>, pair::SMEM_BYTES2);
+    results[dev] = e;
   });
   if (results[dev] != cudaSuccess)
     return fail(LC_ERR_CUDA, "cannot reserve %d bytes of shared memory: %s", SMEM_BYTES,
                 cudaGetErrorString(results[dev]));
   return LC_OK;
+}
+
+// Instruction descriptor for kind::f16 with fp32 accumulation: D format f32 (1) in bits [4,6),
+// A and B formats in [7,10) and [10,13) (0 = f16, 1 = bf16), both K-major, N >> 3 in [17,23),
+// M >> 4 in [24,29).
+__host__ __device__ constexpr uint32_t make_idesc_f16(bool bf16, int n, int m) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// Picks the kernel (CTA pair or single CTA at one of three tile widths) and launches it; shared
+// by the int8 and the weight-only entry points.  `weight_bytes` decides between latency-bound and
+// bandwidth-bound tile widths of the single-CTA kernel.
+template <bool WO>
+static int32_t launch_gemm(const void* a, int64_t a_row_bytes, int64_t lda_bytes, const void* b,
+                           int64_t b_row_bytes, int64_t ldb_bytes, Params& p, int variant, uint32_t idesc_pair,
+                           bool idesc_a_flag, int64_t weight_bytes, cudaStream_t st, const char* what) {
+  const int64_t M = p.M, N = p.N;
+  // CTA pairs pay off once there is more than one 128-row tile of A; a single row tile
+  // would leave half of every pair idle
+  const bool use_pair = variant == 2 || (variant == 0 && M > BM);
+  // tile width of the single-CTA kernel (variant 1 forces the full width): weights of up to
+  // 8 MB are latency-bound, and the widest of 64 / 32 columns that still gives every SM a tile
+  // spreads them over the machine (C1: 16 CTAs x 11.1 us -> 128 CTAs x 6.8 us); every narrower
+  // tile re-reads its 128 rows of A, so larger weights keep the full width (measured: 58 MB at
+  // 64 columns takes 31 us against 19 us)
+  const int64_t sms = sm_count();
+  int bnt = BN;
+  if (!use_pair && variant == 0 && weight_bytes <= (int64_t{8} << 20)) {
+    const int64_t tiles_m = (M + BM - 1) / BM;
+    if (tiles_m * ((N + 255) / 256) < sms) bnt = tiles_m * ((N + 63) / 64) >= sms ? 64 : 32;
+  }
+  CUtensorMap map_a, map_b;
+  if (int32_t rc = make_map(&map_a, a, M, a_row_bytes, lda_bytes, BM)) return rc;
+  if (int32_t rc = make_map(&map_b, b, N, b_row_bytes, ldb_bytes, use_pair ? pair::BNH : bnt)) return rc;
+  if (int32_t rc = ensure_smem_attr()) return rc;
+  if (use_pair) {
+    const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+    // launched so that its set-up (barriers, TMEM allocation) may overlap the tail of the kernel
+    // that produced its operands; it waits for that kernel before its first load
+    const cudaError_t err = launch_overlapped(qlinear_i8_pair_kernel<WO>, dim3(static_cast<unsigned>(2 * pairs)),
+                                              dim3(NUM_THREADS), pair::SMEM_BYTES2, st, map_a, map_b, p, idesc_pair);
+    if (err != cudaSuccess) return fail(LC_ERR_CUDA, "%s (cta pair): %s", what, cudaGetErrorString(err));
+    return check_launch(what);
+  }
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + bnt - 1) / bnt);
+  const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+  const uint32_t idesc = WO ? make_idesc_f16(idesc_a_flag, bnt, BM) : make_idesc(idesc_a_flag, bnt);
+  cudaError_t err;
+  if (bnt == 256)
+    err = launch_overlapped(qlinear_i8_kernel<256, WO>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<256>::kSmemBytes, st,
+                            map_a, map_b, p, idesc);
+  else if (bnt == 64)
+    err = launch_overlapped(qlinear_i8_kernel<64, WO>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<64>::kSmemBytes, st,
+                            map_a, map_b, p, idesc);
+  else
+    err = launch_overlapped(qlinear_i8_kernel<32, WO>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<32>::kSmemBytes, st,
+                            map_a, map_b, p, idesc);
+  if (err != cudaSuccess) return fail(LC_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
+  return check_launch(what);
 }
 
 }  // namespace gemm
@@ -906,6 +1104,11 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
   void* out = host_outs[0];
   for (int i = 0; i < n_out; ++i)
     if (!host_outs[i]) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: null output buffer %d", i);
+  // bit 8 of `variant` is the wait test: the producer role issues no loads and every wait gives up
+  // after a few thousand cycles, so the kernel records a code in `status` and returns
+  const int wait_test = (variant & LC_QLINEAR_WAIT_TEST) ? 1 : 0;
+  variant &= ~LC_QLINEAR_WAIT_TEST;
+  if (wait_test && !status) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: the wait test needs a status word");
   if (variant < 0 || variant > 2) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: variant must be 0, 1 or 2");
   if (M < 0 || N < 0 || K <= 0) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: bad shape");
   if (M == 0 || N == 0) return LC_OK;
@@ -921,25 +1124,6 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
   if (out_dtype != LC_S32 && !sx) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: sx is required");
   if (M > 0x7fffffffLL - BM || N > 0x7fffffffLL - BN || K > 0x7fffffffLL - BK)
     return fail(LC_ERR_UNSUPPORTED, "qlinear_i8: dimension exceeds the TMA coordinate range");
-
-  // CTA pairs pay off once there is more than one 128-row tile of A; a single row tile
-  // would leave half of every pair idle
-  const bool use_pair = variant == 2 || (variant == 0 && M > BM);
-  // tile width of the single-CTA kernel (variant 1 forces the full width): weights of up to
-  // 8 MB are latency-bound, and the widest of 64 / 32 columns that still gives every SM a tile
-  // spreads them over the machine (C1: 16 CTAs x 11.1 us -> 128 CTAs x 6.8 us); every narrower
-  // tile re-reads its 128 rows of A, so larger weights keep the full width (measured: 58 MB at
-  // 64 columns takes 31 us against 19 us)
-  const int64_t sms = sm_count();
-  int bnt = BN;
-  if (!use_pair && variant == 0 && N * K <= (int64_t{8} << 20)) {
-    const int64_t tiles_m = (M + BM - 1) / BM;
-    if (tiles_m * ((N + 255) / 256) < sms) bnt = tiles_m * ((N + 63) / 64) >= sms ? 64 : 32;
-  }
-  CUtensorMap map_a, map_b;
-  if (int32_t rc = make_map(&map_a, a, M, K, lda, BM)) return rc;
-  if (int32_t rc = make_map(&map_b, b, N, K, ldb, use_pair ? pair::BNH : bnt)) return rc;
-  if (int32_t rc = ensure_smem_attr()) return rc;
 
   Params p;
   p.M = M;
@@ -962,30 +1146,95 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
   p.status = status;
   p.fast_f32 = (out_dtype == LC_F32 && sw && n_out == 1 && p.out_vec) ? 1 + (zx ? 1 : 0) + (bias ? 2 : 0) : 0;
 
-  if (use_pair) {
-    const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
-    const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
-    // launched so that its set-up (barriers, TMEM allocation) may overlap the tail of the kernel
-    // that produced its operands; it waits for that kernel before its first load
-    const cudaError_t err = launch_overlapped(qlinear_i8_pair_kernel, dim3(static_cast<unsigned>(2 * pairs)),
-                                              dim3(NUM_THREADS), pair::SMEM_BYTES2, as_stream(stream), map_a, map_b, p,
-                                              make_idesc_pair(a_unsigned != 0));
-    if (err != cudaSuccess) return fail(LC_ERR_CUDA, "qlinear_i8 (cta pair): %s", cudaGetErrorString(err));
-    return check_launch("qlinear_i8 (cta pair)");
-  }
-  const int64_t tiles = ((M + BM - 1) / BM) * ((N + bnt - 1) / bnt);
-  const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
-  const uint32_t idesc = make_idesc(a_unsigned != 0, bnt);
-  cudaError_t err;
-  if (bnt == 256)
-    err = launch_overlapped(qlinear_i8_kernel<256>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<256>::kSmemBytes,
-                            as_stream(stream), map_a, map_b, p, idesc);
-  else if (bnt == 64)
-    err = launch_overlapped(qlinear_i8_kernel<64>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<64>::kSmemBytes,
-                            as_stream(stream), map_a, map_b, p, idesc);
-  else
-    err = launch_overlapped(qlinear_i8_kernel<32>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<32>::kSmemBytes,
-                            as_stream(stream), map_a, map_b, p, idesc);
-  if (err != cudaSuccess) return fail(LC_ERR_CUDA, "qlinear_i8: %s", cudaGetErrorString(err));
-  return check_launch("qlinear_i8");
+  p.wait_test = wait_test;
+  p.kb_wrap = 1;
+  p.rowsum = nullptr;
+  p.colcorr = nullptr;
+  p.relu = 0;
+  p.fq_scale = nullptr;
+  p.fq_zp = nullptr;
+  p.fq_min = p.fq_max = 0.0f;
+  return launch_gemm<false>(a, K, lda, b, K, ldb, p, variant, make_idesc_pair(a_unsigned != 0), a_unsigned != 0,
+                            N * K, as_stream(stream), "qlinear_i8");
+}
+
+// Status word of lc_qlinear_i8* / lc_wo_gemm_16 read back on the host.
+extern "C" int32_t lc_qlinear_check_status(const int32_t* status, int32_t clear, void* stream) {
+  if (!status) return fail(LC_ERR_INVALID_ARG, "qlinear_check_status: null pointer");
+  cudaStream_t st = as_stream(stream);
+  int32_t code = 0;
+  cudaError_t err = cudaMemcpyAsync(&code, status, sizeof(code), cudaMemcpyDeviceToHost, st);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+  if (err == cudaSuccess && clear && code != 0)
+    err = cudaMemsetAsync(const_cast<int32_t*>(status), 0, sizeof(code), st);
+  if (err != cudaSuccess) return fail(LC_ERR_CUDA, "qlinear_check_status: %s", cudaGetErrorString(err));
+  if (code == 0) return LC_OK;
+  static const char* const kRole[] = {"", "the TMA producer", "the MMA issuer", "an epilogue warp"};
+  return fail(LC_ERR_TIMEOUT, "a bounded device-side wait of %s ran out (status %d); the kernel returned early and "
+                              "its output is incomplete", code >= 1 && code <= 3 ? kRole[code] : "a kernel role", code);
+}
+
+// Weight-only Linear on the tensor cores (see the header of this file).
+extern "C" int32_t lc_wo_gemm_16(const void* a, int32_t a_dtype, int32_t n_terms, int64_t lda, const void* w16,
+                                 int64_t ldw, int64_t M, int64_t N, int64_t K, const float* sw, const float* bias,
+                                 const float* rowsum, const float* colcorr, int32_t relu, const float* out_scale,
+                                 const float* out_zp, int32_t quant_min, int32_t quant_max, void* out,
+                                 int32_t out_dtype, int64_t ldo, int32_t* status, int32_t variant, void* stream) {
+  using namespace lc::gemm;
+  if (M < 0 || N < 0 || K <= 0) return fail(LC_ERR_INVALID_ARG, "wo_gemm_16: bad shape");
+  if (M == 0 || N == 0) return LC_OK;
+  if (!a || !w16 || !out) return fail(LC_ERR_INVALID_ARG, "wo_gemm_16: null pointer");
+  if (a_dtype != LC_BF16 && a_dtype != LC_F16)
+    return fail(LC_ERR_UNSUPPORTED, "wo_gemm_16: operands must be bf16 or f16 (dtype %d)", a_dtype);
+  if (n_terms < 1 || n_terms > 3) return fail(LC_ERR_INVALID_ARG, "wo_gemm_16: n_terms must be 1, 2 or 3");
+  const int wait_test = (variant & LC_QLINEAR_WAIT_TEST) ? 1 : 0;
+  variant &= ~LC_QLINEAR_WAIT_TEST;
+  if (wait_test && !status) return fail(LC_ERR_INVALID_ARG, "wo_gemm_16: the wait test needs a status word");
+  if (variant < 0 || variant > 2) return fail(LC_ERR_INVALID_ARG, "wo_gemm_16: variant must be 0, 1 or 2");
+  // one K block = 64 elements = one 128-byte swizzle atom; with several terms every term starts
+  // on a block boundary, so K must then be a whole number of blocks (the caller zero-pads)
+  const int64_t kblocks = (K + 63) / 64;
+  if (n_terms > 1 && K % 64) return fail(LC_ERR_INVALID_ARG, "wo_gemm_16: with several terms K must be a multiple of 64");
+  if (lda < n_terms * K || ldw < K || ldo < N) return fail(LC_ERR_INVALID_ARG, "wo_gemm_16: leading dimension too small");
+  if (lda % 8 || ldw % 8 || K % 8 || !aligned(a, 16) || !aligned(w16, 16))
+    return fail(LC_ERR_UNSUPPORTED, "wo_gemm_16: operand rows must start on 16-byte boundaries and K be a multiple of 8");
+  if (out_dtype != LC_F32 && out_dtype != LC_BF16 && out_dtype != LC_F16)
+    return fail(LC_ERR_UNSUPPORTED, "wo_gemm_16: out_dtype %d not supported", out_dtype);
+  if ((rowsum == nullptr) != (colcorr == nullptr))
+    return fail(LC_ERR_INVALID_ARG, "wo_gemm_16: rowsum and colcorr go together");
+  if ((out_scale == nullptr) != (out_zp == nullptr))
+    return fail(LC_ERR_INVALID_ARG, "wo_gemm_16: out_scale and out_zp go together");
+  if (M > 0x7fffffffLL - BM || N > 0x7fffffffLL - BN || n_terms * K * 2 > 0x7fffffffLL - BK)
+    return fail(LC_ERR_UNSUPPORTED, "wo_gemm_16: dimension exceeds the TMA coordinate range");
+
+  Params p;
+  p.M = M;
+  p.N = N;
+  p.K = n_terms * kblocks * BK;  // bytes of K the main loop walks (A side)
+  p.sx = nullptr;
+  p.sx_per_row = 0;
+  p.zx = nullptr;
+  p.wsum = nullptr;
+  p.sw = sw;
+  p.bias = bias;
+  for (int i = 0; i < 8; ++i) p.outs[i] = i == 0 ? out : nullptr;
+  p.n_out = 1;
+  p.out_dtype = out_dtype;
+  p.ldo = ldo;
+  const size_t esz = (out_dtype == LC_F32) ? 4 : 2;
+  p.out_vec = ((ldo * esz) % 16 == 0 && aligned(out, 16)) ? 1 : 0;
+  p.fast_f32 = 0;
+  p.status = status;
+  p.wait_test = wait_test;
+  p.kb_wrap = static_cast<int>(kblocks);
+  p.rowsum = rowsum;
+  p.colcorr = colcorr;
+  p.relu = relu ? 1 : 0;
+  p.fq_scale = out_scale;
+  p.fq_zp = out_zp;
+  p.fq_min = static_cast<float>(quant_min);
+  p.fq_max = static_cast<float>(quant_max);
+  const bool bf16 = a_dtype == LC_BF16;
+  return launch_gemm<true>(a, n_terms * K * 2, lda * 2, w16, K * 2, ldw * 2, p, variant,
+                           make_idesc_f16(bf16, BN, 2 * BM), bf16, N * K * 2, as_stream(stream), "wo_gemm_16");
 }

@@ -100,6 +100,24 @@ __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { retu
 template <>
 __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
 
+// What follows the scale and the bias in the statically quantized Linear
+// (lucid/nn/quantized/linear.py:206-214, lucid/nn/quantized/intrinsic.py:40): an optional ReLU and
+// the fake-quantize onto the calibrated per-tensor output grid (device scalars; null = none).
+struct WoEpilogue {
+  int relu;
+  const float* fq_scale;
+  const float* fq_zp;
+  float qmin, qmax;
+};
+__device__ __forceinline__ float wo_finish(float v, const WoEpilogue& e) {
+  if (e.relu) v = v < 0.0f ? 0.0f : v;  // NaN stays
+  if (e.fq_scale) {
+    const float s = __ldg(e.fq_scale);
+    v = fake_quant_value(v, s, __fdiv_rn(1.0f, s), __ldg(e.fq_zp), e.qmin, e.qmax);
+  }
+  return v;
+}
+
 constexpr int kWoWarps = 8;
 constexpr int kWoThreads = kWoWarps * 32;
 
@@ -114,7 +132,7 @@ __global__ void __launch_bounds__(kWoThreads)
 wo_linear_mma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx,
                      const int8_t* __restrict__ w, int64_t ldw, int64_t N,
                      const float* __restrict__ sw, const float* __restrict__ bias,
-                     XT* __restrict__ y, int64_t ldy) {
+                     XT* __restrict__ y, int64_t ldy, const WoEpilogue epi) {
   __shared__ float red[kWoWarps][RT * 16][NT * 8 + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -193,7 +211,7 @@ wo_linear_mma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx
       for (int wp = 0; wp < kWoWarps; ++wp) sum += red[wp][r][bcol];
       float v = sum * (sw ? __ldg(sw + n) : 1.0f);
       if (bias) v += __ldg(bias + n);
-      y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(v);
+      y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(wo_finish(v, epi));
     }
   }
 }
@@ -308,7 +326,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                       const __grid_constant__ CUtensorMap tmap_x,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
                       const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, int tiles_per_cta,
-                      int overlap) {
+                      int overlap, const WoEpilogue epi) {
   using namespace ring;
   constexpr int S = stages(NT, TMAX, XB, GRP);
   constexpr int GSTAGE = STAGE * GRP;
@@ -576,7 +594,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
             for (int wp = 0; wp < kConsumerWarps; ++wp) sum += src[wp * 16 * RP];
             float v = sum * (sw ? __ldg(sw + n) : 1.0f);
             if (bias) v += __ldg(bias + n);
-            y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(v);
+            y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(wo_finish(v, epi));
           }
         }
       }
@@ -592,7 +610,7 @@ __global__ void __launch_bounds__(kWoThreads)
 wo_linear_fma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx,
                      const int8_t* __restrict__ w, int64_t ldw, int64_t N,
                      const float* __restrict__ sw, const float* __restrict__ bias,
-                     XT* __restrict__ y, int64_t ldy) {
+                     XT* __restrict__ y, int64_t ldy, const WoEpilogue epi) {
   const int lane = threadIdx.x & 31;
   const int64_t n = static_cast<int64_t>(blockIdx.x) * kWoWarps + (threadIdx.x >> 5);
   if (n >= N) return;
@@ -614,7 +632,7 @@ wo_linear_fma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx
       if (lane == 0 && b0 + i < B) {
         float v = acc[i] * (sw ? __ldg(sw + n) : 1.0f);
         if (bias) v += __ldg(bias + n);
-        y[(b0 + i) * ldy + n] = from_float<XT>(v);
+        y[(b0 + i) * ldy + n] = from_float<XT>(wo_finish(v, epi));
       }
     }
   }
@@ -773,13 +791,13 @@ group_matmul_kernel(const XT* __restrict__ x, int64_t B, int64_t K, const uint32
 template <typename XT>
 static int32_t launch_wo_mma(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                              int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
-                             int64_t ldy, cudaStream_t st) {
+                             int64_t ldy, const WoEpilogue& epi, cudaStream_t st) {
   // enough CTAs to cover every SM at least twice before widening the row tile
   const bool wide = (N / 32) >= 2 * static_cast<int64_t>(sm_count());
   const int rows = wide ? 32 : 16;
   const unsigned grid = static_cast<unsigned>((N + rows - 1) / rows);
 #define LC_WO(RT, NT) \
-  wo_linear_mma_kernel<XT, RT, NT><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy)
+  wo_linear_mma_kernel<XT, RT, NT><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, epi)
   if (wide) {
     if (B <= 8) LC_WO(2, 1);
     else if (B <= 16) LC_WO(2, 2);
@@ -796,7 +814,7 @@ static int32_t launch_wo_mma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
 template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP>
 static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                    int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
-                                   int64_t ldy, bool overlap, cudaStream_t st) {
+                                   int64_t ldy, bool overlap, const WoEpilogue& epi, cudaStream_t st) {
   auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU, GRP>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
@@ -838,7 +856,7 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   cfg.attrs = attr;
   cfg.numAttrs = overlap ? 1 : 0;
   const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_w1, map_x, B, K, N, sw, bias, y, ldy,
-                                             static_cast<int>(per), overlap ? 1 : 0);
+                                             static_cast<int>(per), overlap ? 1 : 0, epi);
   if (err != cudaSuccess) return fail(LC_ERR_CUDA, "wo_linear_s8 (ring): %s", cudaGetErrorString(err));
   return check_launch("wo_linear_s8 (ring)");
 }
@@ -846,39 +864,39 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
 template <typename XT, bool SWIGLU = false>
 static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w, int64_t ldw,
                              int64_t N, const float* sw, const float* bias, XT* y, int64_t ldy,
-                             bool overlap, cudaStream_t st) {
+                             bool overlap, const WoEpilogue& epi, cudaStream_t st) {
   // few row tiles per CTA (short, wide matrices): small reduction buffer, more activation chunks in flight
   const int64_t tiles = (N + 15) / 16, sms = sm_count();
   const bool few = (tiles + sms - 1) / sms <= 2;
   // two row tiles per TMA box where the ring stays at least three boxes deep (batches up to 8);
   // measured on the decode MLP: 40.8 us against 41.6 us with one tile per box
   if (B <= 8)
-    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st)
-               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
+    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, st)
+               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, st);
   if (B <= 16)
-    return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st)
-               : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
-  return launch_wo_ring_inst<XT, 4, 1, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, st);
+    return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, st)
+               : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, st);
+  return launch_wo_ring_inst<XT, 4, 1, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, st);
 }
 
 template <typename XT>
 static int32_t launch_wo_fma(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                              int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
-                             int64_t ldy, cudaStream_t st) {
+                             int64_t ldy, const WoEpilogue& epi, cudaStream_t st) {
   const unsigned grid = static_cast<unsigned>((N + kWoWarps - 1) / kWoWarps);
   if (B <= 1)
-    wo_linear_fma_kernel<XT, 1><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy);
+    wo_linear_fma_kernel<XT, 1><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, epi);
   else if (B <= 4)
-    wo_linear_fma_kernel<XT, 4><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy);
+    wo_linear_fma_kernel<XT, 4><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, epi);
   else
-    wo_linear_fma_kernel<XT, 8><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy);
+    wo_linear_fma_kernel<XT, 8><<<grid, kWoThreads, 0, st>>>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, epi);
   return check_launch("wo_linear_s8 (fma)");
 }
 
 template <typename XT>
 static int32_t wo_linear_typed(const void* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                int64_t ldw, int64_t N, const float* sw, const float* bias, void* y,
-                               int64_t ldy, bool overlap, cudaStream_t st) {
+                               int64_t ldy, bool overlap, const WoEpilogue& epi, cudaStream_t st) {
   const XT* xt = static_cast<const XT*>(x);
   XT* yt = static_cast<XT*>(y);
   const bool mma_ok = sizeof(XT) == 2 && K % 16 == 0 && ldw % 16 == 0 && ldx % 8 == 0 &&
@@ -890,11 +908,11 @@ static int32_t wo_linear_typed(const void* x, int64_t B, int64_t K, int64_t ldx,
       // weights beyond a few MB are streamed through the shared-memory ring; small ones
       // are latency-bound and use the direct-load kernel
       const bool big = N * K >= (int64_t{4} << 20);
-      rc = !mma_ok ? launch_wo_fma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st)
-           : big   ? launch_wo_tma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, overlap, st)
-                   : launch_wo_mma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st);
+      rc = !mma_ok ? launch_wo_fma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, epi, st)
+           : big   ? launch_wo_tma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, overlap, epi, st)
+                   : launch_wo_mma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, epi, st);
     } else {
-      rc = launch_wo_fma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, st);
+      rc = launch_wo_fma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, epi, st);
     }
     if (rc) return rc;
   }
@@ -935,19 +953,31 @@ extern "C" int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch
                                    int64_t ldx, const int8_t* wq, int64_t ldw, int64_t N,
                                    const float* sw, const float* bias, void* y, int64_t ldy,
                                    int32_t flags, void* stream) {
+  return lc_wo_linear_s8_ex(x, x_dtype, batch, K, ldx, wq, ldw, N, sw, bias, 0, nullptr, nullptr, 0, 0, y, ldy, flags,
+                            stream);
+}
+
+extern "C" int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
+                                      const int8_t* wq, int64_t ldw, int64_t N, const float* sw, const float* bias,
+                                      int32_t relu, const float* out_scale, const float* out_zp, int32_t quant_min,
+                                      int32_t quant_max, void* y, int64_t ldy, int32_t flags, void* stream) {
   const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;
   if (batch < 0 || N < 0 || K <= 0 || ldx < K || ldw < K || ldy < N)
     return fail(LC_ERR_INVALID_ARG, "wo_linear_s8: bad shape");
+  if ((out_scale == nullptr) != (out_zp == nullptr))
+    return fail(LC_ERR_INVALID_ARG, "wo_linear_s8: out_scale and out_zp go together");
   if (batch == 0 || N == 0) return LC_OK;
   if (!x || !wq || !y) return fail(LC_ERR_INVALID_ARG, "wo_linear_s8: null pointer");
   cudaStream_t st = as_stream(stream);
+  const WoEpilogue epi = {relu ? 1 : 0, out_scale, out_zp, static_cast<float>(quant_min),
+                          static_cast<float>(quant_max)};
   switch (x_dtype) {
     case LC_F32:
-      return wo_linear_typed<float>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, st);
+      return wo_linear_typed<float>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, epi, st);
     case LC_BF16:
-      return wo_linear_typed<__nv_bfloat16>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, st);
+      return wo_linear_typed<__nv_bfloat16>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, epi, st);
     case LC_F16:
-      return wo_linear_typed<__half>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, st);
+      return wo_linear_typed<__half>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, epi, st);
   }
   return fail(LC_ERR_UNSUPPORTED, "wo_linear_s8: x_dtype %d not supported", x_dtype);
 }
@@ -965,12 +995,13 @@ extern "C" int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch
   if (K % 16 || ldw % 16 || ldx % 8 || !aligned(wq, 16) || !aligned(x, 16))
     return fail(LC_ERR_UNSUPPORTED, "wo_swiglu_s8: K, ldw must be multiples of 16, ldx of 8, pointers 16-byte aligned");
   cudaStream_t st = as_stream(stream);
+  const WoEpilogue none = {0, nullptr, nullptr, 0.0f, 0.0f};
   if (x_dtype == LC_BF16)
     return launch_wo_tma<__nv_bfloat16, true>(static_cast<const __nv_bfloat16*>(x), batch, K, ldx, wq, ldw, N2, sw,
-                                              bias, static_cast<__nv_bfloat16*>(y), ldy, overlap, st);
+                                              bias, static_cast<__nv_bfloat16*>(y), ldy, overlap, none, st);
   if (x_dtype == LC_F16)
     return launch_wo_tma<__half, true>(static_cast<const __half*>(x), batch, K, ldx, wq, ldw, N2, sw, bias,
-                                       static_cast<__half*>(y), ldy, overlap, st);
+                                       static_cast<__half*>(y), ldy, overlap, none, st);
   return fail(LC_ERR_UNSUPPORTED, "wo_swiglu_s8: activations must be bf16 or f16");
 }
 

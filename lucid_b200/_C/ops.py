@@ -11,7 +11,8 @@ import math
 
 import torch
 
-from ._loader import (LC_BF16, LC_F16, LC_F32, LC_S8, LC_S16, LC_S32, LC_U8, LucidCudaError, check, lib)
+from ._loader import (LC_BF16, LC_F16, LC_F32, LC_QLINEAR_WAIT_TEST, LC_S8, LC_S16, LC_S32, LC_U8, LucidCudaError, check,
+                      lib)
 
 _DTYPE = {
     torch.float32: LC_F32,
@@ -434,16 +435,98 @@ def qlinear_i8_into(a, b, sx, sw, out_ptrs, ldo: int, out_dtype: torch.dtype = t
                                       int(ldo), _ptr(status), int(variant), _stream(dev)))
 
 
+def qlinear_check_status(status: torch.Tensor, clear: bool = True) -> None:
+    """Synchronise the current stream and raise :class:`LucidCudaError` (code ``LC_ERR_TIMEOUT``)
+    if a bounded device-side wait of a GEMM launch that was given ``status`` ran out."""
+    dev = _need_cuda(status)
+    with _on(dev):
+        check(lib.lc_qlinear_check_status(status.data_ptr(), 1 if clear else 0, _stream(dev)))
+
+
+# ----------------------------------------------------------------------------
+# weight-only Linear on the tensor cores
+# ----------------------------------------------------------------------------
+def _round_up(v: int, m: int) -> int:
+    return (v + m - 1) // m * m
+
+
+def widen_s8(codes: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """int8 codes ``[N, K]`` as the same integers in ``dtype`` (bf16 / f16, exact), ``[N, Kp]`` with
+    ``Kp`` = K rounded up to 64 and the padding zero: the weight operand of :func:`wo_gemm_16`."""
+    dev = _need_cuda(codes)
+    if codes.dtype != torch.int8 or codes.dim() != 2 or codes.stride(1) != 1:
+        raise TypeError("widen_s8: expected a 2-D int8 tensor with unit column stride")
+    n, k = codes.shape
+    out = torch.empty((n, _round_up(k, 64)), dtype=dtype, device=dev)
+    with _on(dev):
+        check(lib.lc_widen_s8(codes.data_ptr(), n, k, codes.stride(0), out.data_ptr(), _lc_dtype(dtype), out.stride(0),
+                              _stream(dev)))
+    return out
+
+
+def split_f32_bf16x3(x2d: torch.Tensor, want_rowsum: bool = False):
+    """fp32 ``[M, K]`` -> ``(terms [M, 3 * Kp] bf16, rowsum [M] or None)``; the three terms of a
+    row add up to the fp32 values exactly.  ``Kp`` = K rounded up to 64, padding zero."""
+    dev = _need_cuda(x2d)
+    if x2d.dtype != torch.float32 or x2d.dim() != 2:
+        raise TypeError("split_f32_bf16x3: expected a 2-D fp32 tensor")
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    m, k = x2d.shape
+    kp = _round_up(k, 64)
+    terms = torch.empty((m, 3 * kp), dtype=torch.bfloat16, device=dev)
+    rowsum = torch.empty((m,), dtype=torch.float32, device=dev) if want_rowsum else None
+    with _on(dev):
+        check(lib.lc_split_f32_bf16x3(x2d.data_ptr(), m, k, x2d.stride(0), terms.data_ptr(), kp, _ptr(rowsum),
+                                      _stream(dev)))
+    return terms, rowsum
+
+
+def wo_gemm_16(a: torch.Tensor, n_terms: int, w16: torch.Tensor, sw=None, bias=None, rowsum=None, colcorr=None,
+               relu: bool = False, out_scale=None, out_zp=None, quant_min: int = 0, quant_max: int = 255,
+               out_dtype: torch.dtype = torch.float32, status=None, variant: int = 0, wait_test: bool = False):
+    """Tensor-core weight-only Linear: ``a`` holds ``n_terms`` addends of the activations side by
+    side (``[M, n_terms * K]``, bf16, or f16 with one term), ``w16`` the widened codes ``[N, K]``.
+    Returns ``requant(relu(acc * sw + rowsum x colcorr + bias))`` as ``[M, N]`` of ``out_dtype``;
+    ``out_scale`` / ``out_zp`` are device scalars of the output grid (both or neither)."""
+    dev = _need_cuda(a, w16, sw, bias, rowsum, colcorr, out_scale, out_zp, status)
+    if a.dtype not in (torch.bfloat16, torch.float16) or w16.dtype != a.dtype:
+        raise TypeError("wo_gemm_16: a and w16 must both be bf16 or both f16")
+    if a.stride(1) != 1 or w16.stride(1) != 1:
+        raise ValueError("wo_gemm_16: operands need unit column stride")
+    m, ka = a.shape
+    n, k = w16.shape
+    if ka != n_terms * k:
+        raise ValueError(f"wo_gemm_16: a has {ka} columns, expected {n_terms} x {k}")
+    out = torch.empty((m, n), dtype=out_dtype, device=dev)
+    sw_c = None if sw is None else _f32c(sw)
+    bias_c = None if bias is None else _f32c(bias)
+    rs_c = None if rowsum is None else _f32c(rowsum)
+    cc_c = None if colcorr is None else _f32c(colcorr)
+    os_c = None if out_scale is None else _f32c(out_scale)
+    oz_c = None if out_zp is None else _f32c(out_zp)
+    with _on(dev):
+        check(lib.lc_wo_gemm_16(a.data_ptr(), _lc_dtype(a.dtype), n_terms, a.stride(0), w16.data_ptr(), w16.stride(0),
+                                m, n, k, _ptr(sw_c), _ptr(bias_c), _ptr(rs_c), _ptr(cc_c), 1 if relu else 0,
+                                _ptr(os_c), _ptr(oz_c), int(quant_min), int(quant_max), out.data_ptr(),
+                                _lc_dtype(out_dtype), n, _ptr(status), int(variant) | (LC_QLINEAR_WAIT_TEST if wait_test else 0),
+                                _stream(dev)))
+    return out
+
+
 # ----------------------------------------------------------------------------
 # weight-only paths
 # ----------------------------------------------------------------------------
-def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous: bool = False):
-    """``y = (x @ wq^T) * sw + bias`` with float activations; ``y`` has ``x``'s dtype.
+def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous: bool = False, relu: bool = False, out_scale=None,
+                 out_zp=None, quant_min: int = 0, quant_max: int = 255):
+    """``y = (x @ wq^T) * sw + bias`` with float activations; ``y`` has ``x``'s dtype.  With
+    ``relu`` / ``out_scale`` and ``out_zp`` (device scalars) the same kernel goes on to apply the
+    ReLU and the fake-quantize onto the calibrated output grid of a static Linear.
 
     ``overlap_previous`` lets the kernel start (and prefetch weights) while the kernel before
     it on the stream drains; the caller asserts that ``wq``, ``sw`` and ``bias`` were complete
     before that kernel started."""
-    dev = _need_cuda(x2d, wq, sw, bias)
+    dev = _need_cuda(x2d, wq, sw, bias, out_scale, out_zp)
     if x2d.dtype not in (torch.float32, torch.bfloat16, torch.float16):
         raise TypeError(f"wo_linear_s8: activations must be fp32/bf16/fp16, got {x2d.dtype}")
     x2d = x2d.contiguous()
@@ -453,13 +536,18 @@ def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous: bool = False):
     N = wq.shape[0]
     if wq.shape[1] != K:
         raise ValueError(f"wo_linear_s8: in_features mismatch {wq.shape[1]} vs {K}")
+    if (out_scale is None) != (out_zp is None):
+        raise ValueError("wo_linear_s8: out_scale and out_zp go together")
     y = torch.empty((B, N), dtype=x2d.dtype, device=dev)
     sw_c = None if sw is None else _f32c(sw)
     bias_c = None if bias is None else _f32c(bias)
+    os_c = None if out_scale is None else _f32c(out_scale)
+    oz_c = None if out_zp is None else _f32c(out_zp)
     with _on(dev):
-        check(lib.lc_wo_linear_s8(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq.data_ptr(),
-                                  wq.stride(0), N, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N,
-                                  1 if overlap_previous else 0, _stream(dev)))
+        check(lib.lc_wo_linear_s8_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq.data_ptr(),
+                                     wq.stride(0), N, _ptr(sw_c), _ptr(bias_c), 1 if relu else 0, _ptr(os_c),
+                                     _ptr(oz_c), int(quant_min), int(quant_max), y.data_ptr(), N,
+                                     1 if overlap_previous else 0, _stream(dev)))
     return y
 
 

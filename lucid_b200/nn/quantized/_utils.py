@@ -65,6 +65,51 @@ def wire_inner(mod):
     return inner
 
 
+class StaticWeightCache:
+    """Launch-ready views of a statically quantized layer's weight buffers, rebuilt when one of
+    them changes (new storage or in-place version): the scale as one value per output row, the
+    zero-point term of the epilogue (``None`` for the usual symmetric weights; the one
+    device-to-host read that decides this happens here, once per weight, never in a forward), and
+    -- made on first use by a batch too large for the GEMV kernel -- the codes widened to bf16."""
+
+    def __init__(self) -> None:
+        self._key = None
+        self._w16 = None
+
+    def get(self, codes: torch.Tensor, scale: torch.Tensor, zero_point: torch.Tensor, ch_axis: int):
+        key = tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in (codes, scale, zero_point)) + (ch_axis,)
+        if key != self._key:
+            n, k = codes.shape
+            scale = scale.reshape(-1).float()
+            zero_point = zero_point.reshape(-1).float()
+            self.col_scale = self.col_zp = None
+            if scale.numel() == 1 or (ch_axis == 0 and scale.numel() == n):
+                self.row_scale = scale.expand(n).contiguous()
+                zp = zero_point.expand(n) if zero_point.numel() in (1, n) else None
+                if zp is None:
+                    raise ValueError("weight_zero_point does not match weight_scale")
+                self.colcorr = (-(zp * self.row_scale)).contiguous() if bool((zp != 0).any()) else None
+            elif ch_axis == 1 and scale.numel() == k:
+                # per input column: the scale moves onto the activations, x' = x * s[k], and the
+                # zero-point term becomes one value per row, sum_k x'[m,k] * z[k], subtracted from every column
+                self.row_scale = None
+                self.col_scale = scale.contiguous()
+                self.col_zp = zero_point.expand(k).contiguous() if bool((zero_point != 0).any()) else None
+                self.colcorr = None if self.col_zp is None else torch.full((n,), -1.0, device=codes.device)
+            else:
+                raise ValueError(f"weight_scale of {scale.numel()} entries does not fit a [{n}, {k}] weight "
+                                 f"quantized along axis {ch_axis}")
+            self.gemv_ok = self.col_scale is None and self.colcorr is None
+            self._w16 = None
+            self._key = key
+        return self
+
+    def w16(self, codes: torch.Tensor) -> torch.Tensor:
+        if self._w16 is None:
+            self._w16 = _backend.ops().widen_s8(codes, torch.bfloat16)
+        return self._w16
+
+
 class Int8WeightCache:
     """GEMM-ready views of a layer's int8 weight, rebuilt when the buffer changes:
     a copy whose rows start on 16-byte boundaries (what TMA needs; the buffer itself

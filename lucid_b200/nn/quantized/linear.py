@@ -1,9 +1,12 @@
 """Statically quantized Linear (API and buffers of ``lucid/nn/quantized/linear.py:37-242``):
 int8 weights with a per-channel scale, float input, and the output fake-quantized onto
 the calibrated activation grid.  The reference dequantizes the whole weight on every
-forward and calls a float GEMM; here decode batches go through the weight-only GEMV
-kernel (the weight is read once as int8) and larger batches decode the weight with
-``lc_dequantize`` before a dense product.  The output requantization is one kernel.
+forward, calls a float GEMM and then runs the fake-quantize chain
+(``linear.py:206-214``); here the whole forward is one kernel: decode batches go
+through the weight-only GEMV kernel (the weight is read once as int8), larger ones
+through the tensor-core kernel on the exact three-term bf16 split of the fp32
+activations (``lc_wo_gemm_16``), and in both the scale, bias, ReLU and output
+requantization are the kernel's epilogue.  No fp32 copy of the weight is made.
 """
 from __future__ import annotations
 
@@ -11,8 +14,7 @@ import torch
 from torch import nn
 
 from lucid_b200 import _backend
-from lucid_b200.nn.quantized._utils import activation_qparams, quantize_weight, wire_inner
-from lucid_b200.quantization._functional import dequantize, fake_quantize
+from lucid_b200.nn.quantized._utils import StaticWeightCache, activation_qparams, quantize_weight, wire_inner
 from lucid_b200.quantization._qscheme import QDtype, quint8
 
 _GEMV_MAX_ROWS = 32
@@ -34,32 +36,37 @@ class Linear(nn.Module):
             self.bias = None
         self.register_buffer("scale", torch.tensor(1.0))
         self.register_buffer("zero_point", torch.tensor(0.0))
+        self._weights = StaticWeightCache()
 
-    def _activation(self, y: torch.Tensor) -> torch.Tensor:
-        return y
-
-    def _weight_is_symmetric_per_row(self) -> bool:
-        return self.weight_ch_axis == 0 and self.weight_scale.numel() == self.out_features
+    _relu = False  # LinearReLU: a ReLU between the bias and the output requantization
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        ops = _backend.ops()
         xd = _backend.on_cuda(x)
         x2 = xd.reshape(-1, self.in_features)
+        if x2.dtype != torch.float32:  # the reference computes this layer in fp32
+            x2 = x2.float()
         wq = _backend.on_cuda(self.weight_int8)
         bias = None if self.bias is None else _backend.on_cuda(self.bias)
-        if 0 < x2.shape[0] <= _GEMV_MAX_ROWS and self._weight_is_symmetric_per_row():
-            y = _backend.ops().wo_linear_s8(x2, wq, _backend.on_cuda(self.weight_scale), bias)
-            # a non-zero weight zero-point (affine weight observers) shifts every output by
-            # -z[n]*s[n]*sum_k x[m,k]
-            wz = _backend.on_cuda(self.weight_zero_point)
-            if bool((wz != 0).any()):
-                y = y - (x2.float().sum(1, keepdim=True) * (wz * _backend.on_cuda(self.weight_scale))[None, :]).to(y.dtype)
+        w = self._weights.get(wq, _backend.on_cuda(self.weight_scale), _backend.on_cuda(self.weight_zero_point),
+                              self.weight_ch_axis)
+        grid = dict(relu=self._relu, out_scale=_backend.on_cuda(self.scale), out_zp=_backend.on_cuda(self.zero_point),
+                    quant_min=self.out_qdtype.quant_min, quant_max=self.out_qdtype.quant_max)
+        rows = x2.shape[0]
+        if rows == 0:
+            y = torch.zeros((0, self.out_features), dtype=torch.float32, device=x2.device)
+        elif rows <= _GEMV_MAX_ROWS and w.gemv_ok:
+            y = ops.wo_linear_s8(x2, wq, w.row_scale, bias, **grid)
         else:
-            w = dequantize(wq, _backend.on_cuda(self.weight_scale), _backend.on_cuda(self.weight_zero_point),
-                           ch_axis=self.weight_ch_axis)
-            y = torch.nn.functional.linear(x2.to(w.dtype), w, bias)
-        y = self._activation(y.reshape(*xd.shape[:-1], self.out_features))
-        y = fake_quantize(y.float(), _backend.on_cuda(self.scale), _backend.on_cuda(self.zero_point), self.out_qdtype.quant_min,
-                          self.out_qdtype.quant_max)
+            rowsum = None
+            if w.col_scale is not None:
+                x2 = x2 * w.col_scale
+                if w.col_zp is not None:
+                    rowsum = (x2 * w.col_zp).sum(1)
+            terms, rs = ops.split_f32_bf16x3(x2, want_rowsum=w.colcorr is not None and rowsum is None)
+            y = ops.wo_gemm_16(terms, 3, w.w16(wq), sw=w.row_scale, bias=bias,
+                               rowsum=rowsum if rowsum is not None else rs, colcorr=w.colcorr, **grid)
+        y = y.reshape(*xd.shape[:-1], self.out_features)
         return y if x.is_cuda else y.to(x.device)
 
     @classmethod
@@ -87,8 +94,7 @@ class LinearReLU(Linear):
     """Static Linear with a ReLU applied before the output requantization
     (``lucid/nn/quantized/intrinsic.py``)."""
 
-    def _activation(self, y: torch.Tensor) -> torch.Tensor:
-        return torch.relu(y)
+    _relu = True
 
     @classmethod
     def from_float(cls, mod: nn.Module) -> "LinearReLU":

@@ -271,32 +271,40 @@ def dynamic_act_qparams(x, mode: str, qdtype: QDtype):
     raise ValueError(mode)
 
 
-def dynamic_linear_int(x, wq, sw, bias, mode: str = "tensor_affine", act_qdtype: QDtype = quint8):
+def dynamic_linear_int(x, wq, sw, bias, mode: str = "tensor_affine", act_qdtype: QDtype = quint8, rows=None):
     """Integer formulation the CUDA path computes.
 
     ``acc[m,n] = sum_k (xq[m,k]-zx) * wq[n,k]`` exactly in int32, then
     ``y = f32(acc) * sx * sw[n] + b[n]`` evaluated in float64 and rounded once
     (the fp32 kernel result must be within rtol 1e-5 of this).  Returns
-    ``(acc, y, xq, sx, zx)``.
+    ``(acc, y, xq, sx, zx)``.  ``rows`` (an index array) restricts the product to those
+    rows of ``x``: the activation qparams still come from the whole tensor, ``xq`` and a
+    per-row ``sx`` are returned whole, ``acc`` and ``y`` have ``len(rows)`` rows.
     """
     x2 = _f32(x).reshape(-1, np.shape(x)[-1])
     sx, zx = dynamic_act_qparams(x2, mode, act_qdtype)
     ch = 0 if mode == "token_symmetric" else None
     xq = quantize(x2, sx, zx, act_qdtype, ch_axis=ch)
-    xi = xq.astype(np.int64) - (zx.astype(np.int64).reshape(-1, 1) if ch == 0 else int(zx))
+    sel = slice(None) if rows is None else np.asarray(rows, dtype=np.int64)
+    xi = xq[sel].astype(np.int64) - (zx.astype(np.int64).reshape(-1, 1)[sel] if ch == 0 else int(zx))
     acc = (xi.astype(np.float64) @ np.asarray(wq, dtype=np.float64).T).astype(np.int64).astype(np.int32)
-    sx64 = sx.astype(np.float64).reshape(-1, 1) if ch == 0 else float(sx)
+    sx64 = sx.astype(np.float64).reshape(-1, 1)[sel] if ch == 0 else float(sx)
     y = acc.astype(np.float64) * sx64 * _f32(sw).astype(np.float64)[None, :]
     if bias is not None:
         y = y + _f32(bias).astype(np.float64)[None, :]
     return acc, y.astype(F32), xq, sx, zx
 
 
-def static_linear_reference(x, wq, sw, zw, bias, out_scale, out_zp, out_qdtype: QDtype = quint8):
+def static_linear_reference(x, wq, sw, zw, bias, out_scale, out_zp, out_qdtype: QDtype = quint8, relu: bool = False,
+                            ch_axis: int = 0):
     """Static PTQ Linear forward (``nn/quantized/linear.py:206-214``):
-    dequantize W, fp32 linear, fake-quantize the output onto the calibrated grid."""
-    w = dequantize(wq, sw, zw, ch_axis=0)
+    dequantize W, fp32 linear, fake-quantize the output onto the calibrated grid;
+    ``relu`` inserts the activation of the fused ``LinearReLU`` (``nn/quantized/intrinsic.py:40``)
+    between the linear and the fake-quantize."""
+    w = dequantize(wq, sw, zw, ch_axis=None if np.ndim(sw) == 0 or np.size(sw) == 1 else ch_axis)
     y = linear_f32(x, w, bias)
+    if relu:
+        y = np.where(y < 0, F32(0), y).astype(F32)
     return fake_quantize(y, out_scale, out_zp, out_qdtype.quant_min, out_qdtype.quant_max)[0]
 
 

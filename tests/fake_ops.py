@@ -126,9 +126,53 @@ def qlinear_i8(a, b, sx, sw, bias=None, zx=None, wsum=None, out_dtype=torch.floa
     return torch.tensor(y.astype(np.float32)).to(out_dtype)
 
 
-def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous=False):
+def _finish(y, relu, out_scale, out_zp, quant_min, quant_max):
+    y = y.astype(np.float32)
+    if relu:
+        y = np.where(y < 0, np.float32(0), y)
+    if out_scale is not None:
+        y = O.fake_quantize(y, _p(out_scale), _p(out_zp), quant_min, quant_max)[0]
+    return y
+
+
+def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous=False, relu=False, out_scale=None, out_zp=None,
+                 quant_min=0, quant_max=255):
     y = O.weight_only_linear_perchannel(_np(x2d.float()), _np(wq), _np(sw), None if bias is None else _np(bias))
-    return torch.tensor(y).to(x2d.dtype)
+    return torch.tensor(_finish(y, relu, out_scale, out_zp, quant_min, quant_max)).to(x2d.dtype)
+
+
+def widen_s8(codes, dtype=torch.bfloat16):
+    n, k = codes.shape
+    out = torch.zeros((n, (k + 63) // 64 * 64), dtype=dtype)
+    out[:, :k] = codes.to(dtype)
+    return out
+
+
+def split_f32_bf16x3(x2d, want_rowsum=False):
+    m, k = x2d.shape
+    kp = (k + 63) // 64 * 64
+    terms = torch.zeros((m, 3 * kp), dtype=torch.bfloat16)
+    rest = x2d.float()
+    for t in range(3):
+        part = rest.to(torch.bfloat16)
+        terms[:, t * kp:t * kp + k] = part
+        rest = rest - part.float()
+    return terms, (x2d.float().sum(1) if want_rowsum else None)
+
+
+def wo_gemm_16(a, n_terms, w16, sw=None, bias=None, rowsum=None, colcorr=None, relu=False, out_scale=None,
+               out_zp=None, quant_min=0, quant_max=255, out_dtype=torch.float32, status=None, variant=0,
+               wait_test=False):
+    k = w16.shape[1]
+    x = sum(_np(a[:, t * k:(t + 1) * k].float()).astype(np.float64) for t in range(n_terms))
+    y = x @ _np(w16.float()).astype(np.float64).T
+    if sw is not None:
+        y = y * _np(sw).astype(np.float64)[None, :]
+    if rowsum is not None:
+        y = y + _np(rowsum).astype(np.float64)[:, None] * _np(colcorr).astype(np.float64)[None, :]
+    if bias is not None:
+        y = y + _np(bias).astype(np.float64)[None, :]
+    return torch.tensor(_finish(y, relu, out_scale, out_zp, quant_min, quant_max)).to(out_dtype)
 
 
 def group_quantize(w, group_size=64, bits=8):
