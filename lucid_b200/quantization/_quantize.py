@@ -10,7 +10,8 @@ import warnings
 from torch import nn
 
 from lucid_b200 import backends
-from lucid_b200.quantization._propagate import (QConfigResolver, Resolved, normalize_dynamic_spec, weight_dtype)
+from lucid_b200.quantization._propagate import (QConfigResolver, QConfigTable, clear_stamps, normalize_dynamic_spec,
+                                                 weight_dtype)
 from lucid_b200.quantization._qscheme import QDtype, qint8
 from lucid_b200.quantization.qconfig import (get_default_qat_qconfig_mapping, get_default_qconfig_mapping)
 
@@ -117,14 +118,14 @@ def prepare(model: nn.Module, qconfig=None, inplace: bool = False) -> nn.Module:
     resolver = QConfigResolver.from_argument(qconfig, get_default_qconfig_mapping)
     model = model if inplace else copy.deepcopy(model)
     model.eval()
+    observed = _observed_types()
     matched = 0
-    for entry in map(resolver.stamp, resolver.walk(model)):
-        mod, qcfg = entry.module, entry.qconfig
-        if qcfg is None or not isinstance(mod, _observed_types()):
+    for row in resolver.table(model).stamp():
+        if row.qconfig is None or not isinstance(row.module, observed):
             continue
-        obs = qcfg.activation()
-        mod.activation_post_process = obs
-        mod.register_forward_hook(_observer_hook(obs))
+        obs = row.qconfig.activation()
+        row.module.activation_post_process = obs
+        row.module.register_forward_hook(_observer_hook(obs))
         matched += 1
     if matched == 0:
         warnings.warn("prepare(): the QConfigMapping matched no quantizable modules — convert() will "
@@ -146,7 +147,7 @@ def convert(model: nn.Module, inplace: bool = False) -> nn.Module:
         mapping[nni.LinearReLU] = _group_linear_builder(relu=True)
     # the stub leaving the quantized region and embedding tables need no calibration
     _convert_children(model, mapping, always=(nnq.DeQuantStub, nn.Embedding, nn.EmbeddingBag))
-    QConfigResolver.strip(model)
+    clear_stamps(model)
     model.eval()
     return model
 
@@ -180,58 +181,49 @@ def quantize_dynamic(model: nn.Module, qconfig_spec=None, dtype: QDtype = qint8,
     """Replace the targeted float layers by dynamically quantized ones; no calibration.
 
     ``qconfig_spec``: ``None`` (every supported type), a set of module types / dotted names,
-    or a dict mapping those to a ``QConfig``, a ``QDtype`` or ``None`` (skip)."""
-    model = model if inplace else copy.deepcopy(model)
-    model.eval()
+    or a dict mapping those to a ``QConfig``, a ``QDtype`` or ``None`` (skip).
+
+    Two phases: the whole tree is resolved first (which module gets which recipe), then the
+    selected layers are swapped in their parents' slots.  Nothing is touched when the spec is
+    malformed, because resolution happens before the first swap."""
     builders = _dynamic_builders()
     spec = normalize_dynamic_spec(qconfig_spec, dtype, tuple(builders))
-    return _DynamicSwapper(spec, builders, dtype).apply(model)
+    model = model if inplace else copy.deepcopy(model)
+    model.eval()
+    table = QConfigResolver(spec.mapping).table(model)
 
+    def build(row):
+        return builders[type(row.module)](row.module, weight_dtype(row.qconfig, dtype))
 
-class _DynamicSwapper:
-    def __init__(self, spec, builders, dtype: QDtype) -> None:
-        self.resolver = QConfigResolver(spec.mapping)
-        self._targets = spec.targets
-        self._builders = builders
-        self._dtype = dtype
-        self._swapped = 0
-        self._no_dynamic_form: set[type] = set()
-
-    def apply(self, model: nn.Module) -> nn.Module:
-        root = self.resolver.root(model)
-        if root.qconfig is not None and type(model) in self._builders:
-            out = self._build(model, root.qconfig)  # the model itself is a bare layer
-        else:
-            self._descend(root)
-            self._report()
-            out = model
-        QConfigResolver.strip(out)
+    root = table.root
+    if root.qconfig is not None and type(root.module) in builders:  # the model is itself one bare layer
+        out = build(root)
+        clear_stamps(out)
         return out
 
-    def _build(self, module: nn.Module, qconfig) -> nn.Module:
-        self._swapped += 1
-        return self._builders[type(module)](module, weight_dtype(qconfig, self._dtype))
-
-    def _descend(self, parent: Resolved) -> None:
-        for entry in self.resolver.children(parent.module, parent.path, parent.qconfig):
-            if entry.qconfig is not None and type(entry.module) in self._builders:
-                setattr(parent.module, entry.name, self._build(entry.module, entry.qconfig))
-                continue
-            is_leaf = next(entry.module.children(), None) is None
-            if entry.qconfig is not None and is_leaf and self.resolver.is_targeted(entry.module, entry.path):
-                self._no_dynamic_form.add(type(entry.module))
-            self._descend(entry)
-
-    def _report(self) -> None:
-        if self._no_dynamic_form:
-            left = ", ".join(sorted(t.__name__ for t in self._no_dynamic_form))
-            have = ", ".join(sorted(t.__name__ for t in self._builders))
-            warnings.warn(f"quantize_dynamic(): {left} has no dynamically quantized form and stays float; "
-                          f"dynamic quantization covers {have}.", stacklevel=4)
-        elif self._swapped == 0:
-            warnings.warn("quantize_dynamic(): no module of a targeted type "
-                          f"({', '.join(self._targets) or 'none'}) found — the model is returned unchanged.",
-                          stacklevel=4)
+    swapped_prefixes: list[str] = []   # subtrees that have been replaced as a whole
+    stays_float: set[type] = set()     # asked for by a rule, but no dynamic form exists
+    for row in table:
+        if row.path == "" or row.qconfig is None:
+            continue
+        if any(row.path.startswith(prefix) for prefix in swapped_prefixes):
+            continue
+        if type(row.module) in builders:
+            setattr(table.parent_module(row), row.name, build(row))
+            swapped_prefixes.append(row.path + ".")
+        elif row.by_rule and next(row.module.children(), None) is None:
+            stays_float.add(type(row.module))
+    if stays_float:
+        left = ", ".join(sorted(t.__name__ for t in stays_float))
+        have = ", ".join(sorted(t.__name__ for t in builders))
+        warnings.warn(f"quantize_dynamic(): {left} has no dynamically quantized form and stays float; "
+                      f"dynamic quantization covers {have}.", stacklevel=2)
+    elif not swapped_prefixes:
+        warnings.warn("quantize_dynamic(): no module of a targeted type "
+                      f"({', '.join(spec.targets) or 'none'}) found — the model is returned unchanged.",
+                      stacklevel=2)
+    clear_stamps(model)
+    return model
 
 
 # ---- quantization-aware training ----------------------------------------------------------
@@ -251,26 +243,25 @@ def prepare_qat(model: nn.Module, qconfig=None, inplace: bool = False) -> nn.Mod
     """Swap every weighted layer the qconfig resolution selects for its ``nn.qat`` form and
     give every ``QuantStub`` a fake-quantizer; the model is returned in ``train`` mode, ready
     to be fine-tuned and then handed to :func:`convert` (``_quantize.py:643-737``)."""
-    resolver = QConfigResolver.from_argument(qconfig, get_default_qat_qconfig_mapping)
-    model = model if inplace else copy.deepcopy(model)
-    model.train()
-    _prepare_qat_children(resolver, model, resolver.stamp(resolver.root(model)), _qat_mapping())
-    return model
-
-
-def _prepare_qat_children(resolver: QConfigResolver, parent: nn.Module, parent_entry: Resolved, qat_map) -> None:
     import lucid_b200.nn.quantized as nnq
     from lucid_b200.nn.intrinsic.qat import _ConvBnNd
 
-    for entry in resolver.children(parent, parent_entry.path, parent_entry.qconfig):
-        child, qcfg = entry.module, entry.qconfig
-        resolver.stamp(entry)
-        build = qat_map.get(type(child))
+    resolver = QConfigResolver.from_argument(qconfig, get_default_qat_qconfig_mapping)
+    model = model if inplace else copy.deepcopy(model)
+    model.train()
+    qat_map = _qat_mapping()
+    table = resolver.table(model).stamp()
+    closed: list[str] = []  # subtrees already made trainable as a whole: nothing below them is visited
+    for row in table:
+        if row.path == "" or any(row.path.startswith(prefix) for prefix in closed):
+            continue
+        child, build = row.module, qat_map.get(type(row.module))
         if isinstance(child, _ConvBnNd):
-            continue  # fuse_modules_qat already made it trainable; its conv is used through the fused forward
-        if qcfg is not None and build is not None:
-            setattr(parent, entry.name, build(child))
-        elif qcfg is not None and isinstance(child, nnq.QuantStub):
-            child.activation_post_process = qcfg.activation()
-        else:
-            _prepare_qat_children(resolver, child, entry, qat_map)
+            closed.append(row.path + ".")  # fuse_modules_qat made it trainable; its conv runs through the fused forward
+        elif row.qconfig is not None and build is not None:
+            setattr(table.parent_module(row), row.name, build(child))
+            closed.append(row.path + ".")
+        elif row.qconfig is not None and isinstance(child, nnq.QuantStub):
+            child.activation_post_process = row.qconfig.activation()
+            closed.append(row.path + ".")
+    return model

@@ -24,22 +24,31 @@ def _set_module(root: nn.Module, dotted: str, value: nn.Module) -> None:
     setattr(parent, name, value)
 
 
+def _kind(mod: nn.Module) -> str:
+    """One letter per member of a run: C conv, B batch norm, R ReLU, L linear, ? anything else."""
+    if isinstance(mod, _CONV_TYPES):
+        return "C"
+    if isinstance(mod, _BN_TYPES):
+        return "B"
+    if isinstance(mod, nn.ReLU):
+        return "R"
+    return "L" if isinstance(mod, nn.Linear) else "?"
+
+
+# signature of a run -> the module that replaces its first member
+_FUSED_HEAD = {
+    "CB": lambda m: fuse_conv_bn_eval(m[0], m[1]),
+    "CBR": lambda m: _CONV_RELU[type(m[0])](fuse_conv_bn_eval(m[0], m[1]), nn.ReLU()),
+    "CR": lambda m: _CONV_RELU[type(m[0])](m[0], nn.ReLU()),
+    "LR": lambda m: nni.LinearReLU(m[0], nn.ReLU()),
+}
+
+
 def _fuse_run(mods: Sequence[nn.Module]) -> list[nn.Module]:
-    ids: list[nn.Module] = [nn.Identity() for _ in range(len(mods) - 1)]
-    first = mods[0]
-    if isinstance(first, _CONV_TYPES):
-        conv, rest = first, list(mods[1:])
-        if rest and isinstance(rest[0], _BN_TYPES):
-            conv = fuse_conv_bn_eval(first, rest.pop(0))
-        if rest and isinstance(rest[0], nn.ReLU):
-            rest.pop(0)
-            if not rest:
-                return [_CONV_RELU[type(first)](conv, nn.ReLU()), *ids]
-        if not rest:
-            return [conv, *ids]
-    if isinstance(first, nn.Linear) and len(mods) == 2 and isinstance(mods[1], nn.ReLU):
-        return [nni.LinearReLU(first, nn.ReLU()), *ids]
-    raise ValueError(f"fuse_modules: unsupported fusion pattern {[type(m).__name__ for m in mods]}")
+    make_head = _FUSED_HEAD.get("".join(_kind(m) for m in mods))
+    if make_head is None:
+        raise ValueError(f"fuse_modules: unsupported fusion pattern {[type(m).__name__ for m in mods]}")
+    return [make_head(mods)] + [nn.Identity() for _ in mods[1:]]
 
 
 def fuse_modules(model: nn.Module, modules_to_fuse: Sequence[Sequence[str]], inplace: bool = False) -> nn.Module:
@@ -56,23 +65,21 @@ def fuse_modules(model: nn.Module, modules_to_fuse: Sequence[Sequence[str]], inp
 def _fuse_run_qat(mods: Sequence[nn.Module], qconfig) -> list[nn.Module]:
     from lucid_b200.nn.intrinsic import qat as nniqat
 
-    ids: list[nn.Module] = [nn.Identity() for _ in range(len(mods) - 1)]
-    first = mods[0]
-    if isinstance(first, _CONV_TYPES):
-        rank = _CONV_TYPES.index(type(first))
-        rest = list(mods[1:])
-        if rest and isinstance(rest[0], _BN_TYPES):
-            bn = rest.pop(0)
-            relu = bool(rest and isinstance(rest[0], nn.ReLU))
-            cls = ((nniqat.ConvBnReLU1d, nniqat.ConvBnReLU2d, nniqat.ConvBnReLU3d) if relu
-                   else (nniqat.ConvBn1d, nniqat.ConvBn2d, nniqat.ConvBn3d))[rank]
-            return [cls(first, bn, qconfig=qconfig), *ids]
-        if rest and isinstance(rest[0], nn.ReLU):  # no BatchNorm: the plain fused pair; prepare_qat makes it trainable
-            return [_CONV_RELU[type(first)](first, nn.ReLU()), *ids]
-        return [first, *ids]
-    if isinstance(first, nn.Linear) and len(mods) == 2 and isinstance(mods[1], nn.ReLU):
-        return [nni.LinearReLU(first, nn.ReLU()), *ids]
-    raise ValueError(f"fuse_modules_qat: unsupported pattern {[type(m).__name__ for m in mods]}")
+    signature = "".join(_kind(m) for m in mods)
+    rank = _CONV_TYPES.index(type(mods[0])) if signature.startswith("C") else 0
+    heads = {
+        # a BatchNorm after the conv: the trainable layer that folds it on every forward
+        "CB": lambda: (nniqat.ConvBn1d, nniqat.ConvBn2d, nniqat.ConvBn3d)[rank](mods[0], mods[1], qconfig=qconfig),
+        "CBR": lambda: (nniqat.ConvBnReLU1d, nniqat.ConvBnReLU2d, nniqat.ConvBnReLU3d)[rank](mods[0], mods[1],
+                                                                                           qconfig=qconfig),
+        # no BatchNorm: the plain fused pair; prepare_qat makes it trainable
+        "CR": lambda: _CONV_RELU[type(mods[0])](mods[0], nn.ReLU()),
+        "C": lambda: mods[0],
+        "LR": lambda: nni.LinearReLU(mods[0], nn.ReLU()),
+    }
+    if signature not in heads:
+        raise ValueError(f"fuse_modules_qat: unsupported pattern {[type(m).__name__ for m in mods]}")
+    return [heads[signature]()] + [nn.Identity() for _ in mods[1:]]
 
 
 def fuse_modules_qat(model: nn.Module, modules_to_fuse: Sequence[Sequence[str]], qconfig, inplace: bool = False):
