@@ -307,9 +307,11 @@ int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K
  *   y        = max(y, 0)                                           if relu
  *   out      = (clip(rint(y * (1/S)) + Z, quant_min, quant_max) - Z) * S   if out_scale / out_zp
  * a: [M, n_terms * K] bf16 (or f16 with n_terms = 1): the n_terms addends of the activation side
- * by side, row stride lda elements.  An fp32 activation is the exact sum of three bf16 terms
- * (lc_split_f32_bf16x3), so every product is exact and only the accumulation rounds, as in an
- * fp32 GEMM; a bf16 / f16 activation is its own single term.  w16: [N, K] the int8 codes widened
+ * by side, row stride lda elements.  A bf16 / f16 activation is its own single term.  An fp32
+ * activation is the exact sum of three bf16 terms (lc_split_f32_bf16x3), so every product is exact;
+ * the tensor core however truncates when it adds into the fp32 accumulator (error 2.3e-6 of the
+ * output RMS at K = 512, growing linearly with K), so fp32 activations should use
+ * lc_wo_gemm_digits below, which is exact and faster.  w16: [N, K] the int8 codes widened
  * exactly to a_dtype (lc_widen_s8), row stride ldw elements; no fp32 copy of the weight is ever
  * made.  lda, ldw and K are multiples of 8; with n_terms > 1, K is a multiple of 64 (zero-padded).
  * sw: N floats or NULL; bias: N floats or NULL; rowsum [M] and colcorr [N] (= -zw[n] * sw[n], the
@@ -321,6 +323,28 @@ int32_t lc_wo_gemm_16(const void* a, int32_t a_dtype, int32_t n_terms, int64_t l
                       const float* rowsum, const float* colcorr, int32_t relu, const float* out_scale,
                       const float* out_zp, int32_t quant_min, int32_t quant_max, void* out,
                       int32_t out_dtype, int64_t ldo, int32_t* status, int32_t variant, void* stream);
+
+/* The same Linear for fp32 activations on EXACT integer arithmetic (tcgen05 kind::i8).  Every row of
+ * x is scaled by a power of two so that its largest magnitude lies in [2^29, 2^30), rounded to an
+ * integer X and cut into four signed base-256 digits (lc_split_f32_digits): entries within 2^-6 of
+ * the row maximum keep all 24 bits, the absolute error of smaller ones is below 2^-31 of the row
+ * maximum.  The four digit planes ride through one int8 GEMM with int32 accumulation and are put
+ * back together in 64-bit integers in the epilogue, so sum_k X[m,k] * wq[n,k] is exact and
+ *   y = f32(sum) * row_scale[m] * sw[n] + rowsum[m] * colcorr[n] + bias[n]
+ * rounds the dot product once; ReLU and requantization as for lc_wo_gemm_16.  This is what the
+ * statically quantized Linear runs for more than 32 rows; it is more accurate than the fp32 GEMM of
+ * the reference (lucid/_C/nn/Linear.cpp:74-136), whose accumulation rounds at every step.
+ * digits: [lc_wo_digit_rows(M), K] int8, row stride ldd (multiple of 16), laid out by
+ * lc_split_f32_digits; row_scale: [M]; wq: [N, K] int8 codes, ldw a multiple of 16; out: fp32.
+ * K <= 131072.  status, variant: as for lc_qlinear_i8_ex. */
+int64_t lc_wo_digit_rows(int64_t rows);
+int32_t lc_split_f32_digits(const float* x, int64_t rows, int64_t cols, int64_t ldx, int8_t* digits,
+                            int64_t ldd, float* row_scale, float* rowsum, void* stream);
+int32_t lc_wo_gemm_digits(const int8_t* digits, int64_t ldd, const float* row_scale, const int8_t* wq,
+                          int64_t ldw, int64_t M, int64_t N, int64_t K, const float* sw, const float* bias,
+                          const float* rowsum, const float* colcorr, int32_t relu, const float* out_scale,
+                          const float* out_zp, int32_t quant_min, int32_t quant_max, float* out, int64_t ldo,
+                          int32_t* status, int32_t variant, void* stream);
 
 /* int8 codes [rows, cols] (row stride ld_in) -> the same integers as bf16 or f16 (exact for every
  * code), row stride ld_out >= cols elements, columns [cols, ld_out) zero-filled.  The operand

@@ -67,6 +67,10 @@ SIGNATURES = {
     "lc_rowsum_s8": (_i32, [_p, _i64, _i64, _i64, _p, _p]),
     "lc_wo_gemm_16": (_i32, [_p, _i32, _i32, _i64, _p, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _i32, _p, _p, _i32, _i32,
                              _p, _i32, _i64, _p, _i32, _p]),
+    "lc_wo_digit_rows": (_i64, [_i64]),
+    "lc_split_f32_digits": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _p, _p, _p]),
+    "lc_wo_gemm_digits": (_i32, [_p, _i64, _p, _p, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _i32, _p, _p, _i32, _i32, _p,
+                                 _i64, _p, _i32, _p]),
     "lc_widen_s8": (_i32, [_p, _i64, _i64, _i64, _p, _i32, _i64, _p]),
     "lc_split_f32_bf16x3": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _p, _p]),
     "lc_wo_linear_s8": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _i32, _p]),

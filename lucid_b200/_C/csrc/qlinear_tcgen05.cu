@@ -11,14 +11,23 @@
 // accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of
 // tile i overlaps the main loop of tile i+1.  No multicast is used anywhere.
 //
-// The same kernels, instantiated with WO = true, run the weight-only Linear for more rows than a
-// GEMV handles: tcgen05.mma kind::f16 on 16-bit operands with fp32 accumulation in TMEM.  The int8
-// weight codes are exact in bf16 / f16; an fp32 activation is the exact sum of three bf16 terms
-// (x = x1 + x2 + x3, each the bf16 rounding of what the previous ones left), stored side by side
-// along K, so the product runs as three passes over the weight's K blocks into ONE accumulator:
-// every partial product is exact in fp32 and only the accumulation rounds, as in an fp32 GEMM.
-// The epilogue applies the per-channel weight scale, an optional weight zero-point term, the
-// bias, an optional ReLU and an optional requantization onto a calibrated per-tensor grid.
+// The same kernels run the weight-only Linear (float activations, int8 weight codes) for more
+// rows than a GEMV handles, in two more instantiations:
+//  * kModeDigits, for fp32 activations: every row of x is scaled by a power of two (exact) so that
+//    its largest entry lies in [2^29, 2^30), rounded to an integer (every entry within 2^-6 of the
+//    row maximum keeps all 24 bits; the absolute error of the rest is below 2^-31 of the row maximum)
+//    and cut into four signed base-256 digits.  The digit planes of 32 rows form one 128-row tile of
+//    A (lanes 32d .. 32d+31 of the accumulator hold digit d), the product runs on kind::i8 with exact
+//    int32 accumulation, and the epilogue recombines ((a3*256 + a2)*256 + a1)*256 + a0 in 64-bit
+//    integers: the whole dot product is exact and is rounded to fp32 once.
+//  * kModeF16, for bf16 / f16 activations: tcgen05.mma kind::f16 with fp32 accumulation; the int8
+//    codes are exact in either type.  (The kernel also accepts up to three bf16 addends of an fp32
+//    activation side by side along K.  Every product is then exact, but the tensor core truncates
+//    when it adds into the fp32 accumulator: measured 2.3e-6 of the output RMS at K = 512 and
+//    3.5e-5 at K = 8192, against ~5e-7 of an IEEE fp32 GEMM -- which is why fp32 activations take
+//    the digit form.)
+// The epilogue of both applies the per-channel weight scale, an optional weight zero-point term,
+// the bias, an optional ReLU and an optional requantization onto a calibrated per-tensor grid.
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the waiting role
 // records a code in the caller's status word, leaves its loop, the CTA waits
@@ -52,6 +61,11 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256
 
 constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 2 GHz
 
+// what the kernels are instantiated for
+constexpr int kModeI8 = 0;      // int8 x int8 -> int32, dequantizing epilogue (dynamic Linear)
+constexpr int kModeF16 = 1;     // 16-bit float operands, fp32 accumulation, weight-only epilogue
+constexpr int kModeDigits = 2;  // int8 digit planes of fp32 activations x int8 codes, exact, weight-only epilogue
+
 enum : int { ST_PRODUCER = 1, ST_MMA = 2, ST_EPILOGUE = 3 };
 
 struct Params {
@@ -70,7 +84,8 @@ struct Params {
   int fast_f32;         // 0, or 1 + (zero-point correction) + 2 * (bias): the compiled-in fp32 epilogue applies
   int32_t* status;
   int wait_test;        // test hook: the producer role issues nothing and every wait gives up after a few thousand cycles
-  // weight-only (WO) instantiation only
+  // weight-only instantiations (kModeF16, kModeDigits) only
+  int64_t rows_out;     // kModeDigits: rows of the output (M counts digit-plane rows, 4 per output row)
   int kb_wrap;          // K blocks of the weight; A holds n_terms times as many and B's K coordinate wraps
   const float* rowsum;  // [M] sum_k x[m,k] or null   } weight zero-point term rowsum[m] * colcorr[n]
   const float* colcorr; // [N] -zw[n]*sw[n] or null   }
@@ -345,6 +360,44 @@ __device__ __forceinline__ void drain_chunk_wo(const Params& p, const uint32_t (
   store_staged(p, stg, c, row_base, n0, lane);
 }
 
+// Epilogue chunk of the digit instantiation.  The four epilogue warps that share a column chunk
+// hold the four digit planes of the same 32 output rows (warp q: lanes 32q .. 32q+31 = digit q).
+// Each parks its raw int32 sums in its staging buffer; after a barrier over the four warps, warp q
+// recombines output rows 8q .. 8q+7 (lane = column), applies the epilogue and stores 128-byte row
+// segments.  `group_stg` is the first of the group's four staging buffers, `bar` its barrier id.
+__device__ __forceinline__ void drain_chunk_digits(const Params& p, const uint32_t (&r)[32], int c, int64_t row_base,
+                                                   int64_t n0, int q, int lane, const float* s_sw,
+                                                   const float* s_bias, const float* s_cc, float fq_s, float fq_inv,
+                                                   float fq_z, uint32_t* group_stg, int bar) {
+  uint32_t* mine = group_stg + q * STG_WARP_WORDS + lane * STG_PITCH;
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(mine + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+  asm volatile("bar.sync %0, 128;" ::"r"(bar) : "memory");
+  const int64_t col = n0 + c * 32 + lane;
+  const bool col_ok = col < p.N;
+  const float swv = s_sw[c * 32 + lane], bv = s_bias[c * 32 + lane], cv = s_cc[c * 32 + lane];
+  const bool has_cc = p.colcorr != nullptr, has_bias = p.bias != nullptr, relu = p.relu != 0,
+             fq = p.fq_scale != nullptr;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = q * 8 + i;
+    const int64_t row = row_base + rr;
+    const int* src = reinterpret_cast<const int*>(group_stg) + rr * STG_PITCH + lane;
+    const long long v = ((static_cast<long long>(src[3 * STG_WARP_WORDS]) * 256 + src[2 * STG_WARP_WORDS]) * 256 +
+                         src[STG_WARP_WORDS]) * 256 + src[0];
+    if (row < p.rows_out && col_ok) {
+      // one rounding of the exact integer sum; the row scale is a power of two
+      float f = __fmul_rn(__fmul_rn(__ll2float_rn(v), __ldg(p.sx + row)), swv);
+      if (has_cc) f = __fadd_rn(f, __fmul_rn(__ldg(p.rowsum + row), cv));
+      if (has_bias) f = __fadd_rn(f, bv);
+      if (relu) f = f < 0.0f ? 0.0f : f;  // NaN compares false and stays
+      if (fq) f = fake_quant_value(f, fq_s, fq_inv, fq_z, p.fq_min, p.fq_max);
+      static_cast<float*>(p.outs[0])[row * p.ldo + col] = f;
+    }
+  }
+  asm volatile("bar.sync %0, 128;" ::"r"(bar) : "memory");  // the buffers are free for the next chunk
+}
+
 // One 32-row x 32-column chunk of the accumulator: lane = row computes the 32 outputs,
 // the warp transposes them through shared memory, then stores rows as whole 64/128-byte
 // segments (4 or 8 rows per instruction) to every destination buffer.  Writing whole
@@ -463,7 +516,7 @@ __device__ __forceinline__ void drain(const Params& p, const uint32_t (&r)[32], 
   drain_chunk(p, r, c, row_base, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
 }
 
-template <int BNT, bool WO>
+template <int BNT, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const Params p, const uint32_t idesc) {
@@ -543,7 +596,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t a_dst = tiles_base + stage * STAGE_BYTES;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           tma_load_2d(a_dst, &tmap_a, kb * BK, m0, full_bar(stage));
-          tma_load_2d(a_dst + A_BYTES, &tmap_b, (WO ? kb % p.kb_wrap : kb) * BK, n0, full_bar(stage));
+          tma_load_2d(a_dst + A_BYTES, &tmap_b, (MODE == kModeF16 ? kb % p.kb_wrap : kb) * BK, n0, full_bar(stage));
           armed[stage] = true;
           armed_parity[stage] = phase;
           if (++stage == STAGES) {
@@ -586,7 +639,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int j = 0; j < BK / UMMA_K; ++j) {
             // advancing K inside the swizzle atom = advancing the start address
             const uint64_t koff = static_cast<uint64_t>((j * UMMA_K) >> 4);
-            if constexpr (WO)
+            if constexpr (MODE == kModeF16)
               tc_mma_f16(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
             else
               tc_mma_i8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
@@ -610,9 +663,9 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int zx_i = p.zx ? __float2int_rn(__ldg(p.zx)) : 0;
     // output grid of the weight-only epilogue (device scalars; 1 / s by IEEE division as the
     // reference's fake_quantize computes it for a tensor scale)
-    const float fq_s = (WO && p.fq_scale) ? __ldg(p.fq_scale) : 1.0f;
+    const float fq_s = (MODE != kModeI8 && p.fq_scale) ? __ldg(p.fq_scale) : 1.0f;
     const float fq_inv = __fdiv_rn(1.0f, fq_s);
-    const float fq_z = (WO && p.fq_zp) ? __ldg(p.fq_zp) : 0.0f;
+    const float fq_z = (MODE != kModeI8 && p.fq_zp) ? __ldg(p.fq_zp) : 0.0f;
     int64_t it = 0;
     for (int64_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
       int64_t tm, tn;
@@ -625,7 +678,7 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool in = n < p.N;
         s_sw[j] = (in && p.sw) ? __ldg(p.sw + n) : 1.0f;
         s_bias[j] = (in && p.bias) ? __ldg(p.bias + n) : 0.0f;
-        if constexpr (WO)
+        if constexpr (MODE != kModeI8)
           reinterpret_cast<float*>(s_corr)[j] = (in && p.colcorr) ? __ldg(p.colcorr + n) : 0.0f;
         else
           s_corr[j] = (in && p.wsum) ? zx_i * __ldg(p.wsum + n) : 0;
@@ -640,8 +693,9 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after();
       const int64_t row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const float sxr = WO ? ((p.rowsum && row_ok) ? __ldg(p.rowsum + row) : 0.0f)
-                           : (p.sx_per_row ? (row_ok ? __ldg(p.sx + row) : 0.0f) : sx_scalar);
+      const float sxr = MODE == kModeDigits ? 0.0f  // per-row values are read where the digits are combined
+                        : MODE == kModeF16 ? ((p.rowsum && row_ok) ? __ldg(p.rowsum + row) : 0.0f)
+                                           : (p.sx_per_row ? (row_ok ? __ldg(p.sx + row) : 0.0f) : sx_scalar);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(as * BN);
 #pragma unroll 1
@@ -650,9 +704,13 @@ qlinear_i8_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tc_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
         tc_wait_ld();
         if (n0 + c * 32 < p.N) {
-          if constexpr (WO)
+          if constexpr (MODE == kModeF16)
             drain_chunk_wo(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, reinterpret_cast<const float*>(s_corr),
                            fq_s, fq_inv, fq_z, stg);
+          else if constexpr (MODE == kModeDigits)
+            drain_chunk_digits(p, r, c, m0 >> 2, n0, q, lane, s_sw, s_bias, reinterpret_cast<const float*>(s_corr), fq_s,
+                               fq_inv, fq_z, stg - (warp - 2) * STG_WARP_WORDS + ((warp - 2) >> 2) * 4 * STG_WARP_WORDS,
+                               2 + ((warp - 2) >> 2));
           else
             drain(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
         }
@@ -752,7 +810,7 @@ __host__ __device__ constexpr uint32_t make_idesc_pair(bool a_unsigned) {
          (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>((2 * BM) >> 4) << 24);
 }
 
-template <bool WO>
+template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b, const Params p, const uint32_t idesc) {
@@ -840,7 +898,7 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             armed_parity[stage] = phase;
           }
           tma_load_2d_pair(a_dst, &tmap_a, kb * BK, m0, lead_full);
-          tma_load_2d_pair(a_dst + A_BYTES2, &tmap_b, (WO ? kb % p.kb_wrap : kb) * BK, n0, lead_full);
+          tma_load_2d_pair(a_dst + A_BYTES2, &tmap_b, (MODE == kModeF16 ? kb % p.kb_wrap : kb) * BK, n0, lead_full);
           if (++stage == STAGES2) {
             stage = 0;
             phase ^= 1u;
@@ -881,7 +939,7 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int j = 0; j < BK / UMMA_K; ++j) {
             const uint64_t koff = static_cast<uint64_t>((j * UMMA_K) >> 4);
-            if constexpr (WO)
+            if constexpr (MODE == kModeF16)
               tc_mma_f16_pair(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
             else
               tc_mma_i8_pair(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | j) != 0 ? 1u : 0u);
@@ -905,9 +963,9 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int zx_i = p.zx ? __float2int_rn(__ldg(p.zx)) : 0;
     // output grid of the weight-only epilogue (device scalars; 1 / s by IEEE division as the
     // reference's fake_quantize computes it for a tensor scale)
-    const float fq_s = (WO && p.fq_scale) ? __ldg(p.fq_scale) : 1.0f;
+    const float fq_s = (MODE != kModeI8 && p.fq_scale) ? __ldg(p.fq_scale) : 1.0f;
     const float fq_inv = __fdiv_rn(1.0f, fq_s);
-    const float fq_z = (WO && p.fq_zp) ? __ldg(p.fq_zp) : 0.0f;
+    const float fq_z = (MODE != kModeI8 && p.fq_zp) ? __ldg(p.fq_zp) : 0.0f;
     int64_t it = 0;
     for (int64_t t = pair_id; t < num_tiles; t += num_pairs, ++it) {
       int64_t tm, tn;
@@ -919,7 +977,7 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool in = n < p.N;
         s_sw[j] = (in && p.sw) ? __ldg(p.sw + n) : 1.0f;
         s_bias[j] = (in && p.bias) ? __ldg(p.bias + n) : 0.0f;
-        if constexpr (WO)
+        if constexpr (MODE != kModeI8)
           reinterpret_cast<float*>(s_corr)[j] = (in && p.colcorr) ? __ldg(p.colcorr + n) : 0.0f;
         else
           s_corr[j] = (in && p.wsum) ? zx_i * __ldg(p.wsum + n) : 0;
@@ -933,8 +991,9 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after();
       const int64_t row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const float sxr = WO ? ((p.rowsum && row_ok) ? __ldg(p.rowsum + row) : 0.0f)
-                           : (p.sx_per_row ? (row_ok ? __ldg(p.sx + row) : 0.0f) : sx_scalar);
+      const float sxr = MODE == kModeDigits ? 0.0f  // per-row values are read where the digits are combined
+                        : MODE == kModeF16 ? ((p.rowsum && row_ok) ? __ldg(p.rowsum + row) : 0.0f)
+                                           : (p.sx_per_row ? (row_ok ? __ldg(p.sx + row) : 0.0f) : sx_scalar);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                              static_cast<uint32_t>(as * BN);
 #pragma unroll 1
@@ -943,9 +1002,13 @@ qlinear_i8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tc_ld_32x32(t_row + static_cast<uint32_t>(c * 32), r);
         tc_wait_ld();
         if (n0 + c * 32 < p.N) {
-          if constexpr (WO)
+          if constexpr (MODE == kModeF16)
             drain_chunk_wo(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, reinterpret_cast<const float*>(s_corr),
                            fq_s, fq_inv, fq_z, stg);
+          else if constexpr (MODE == kModeDigits)
+            drain_chunk_digits(p, r, c, m0 >> 2, n0, q, lane, s_sw, s_bias, reinterpret_cast<const float*>(s_corr), fq_s,
+                               fq_inv, fq_z, stg - (warp - 2) * STG_WARP_WORDS + ((warp - 2) >> 2) * 4 * STG_WARP_WORDS,
+                               2 + ((warp - 2) >> 2));
           else
             drain(p, r, c, m0 + q * 32, n0, lane, sxr, s_sw, s_bias, s_corr, stg);
         }
@@ -991,14 +1054,18 @@ static int32_t ensure_smem_attr() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return fail(LC_ERR_CUDA, "no current CUDA device");
   std::call_once(flags[dev], [dev]() {
-    cudaError_t e = reserve_smem(qlinear_i8_kernel<256, false>, NarrowCfg<256>::kSmemBytes);
-    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<64, false>, NarrowCfg<64>::kSmemBytes);
-    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<32, false>, NarrowCfg<32>::kSmemBytes);
-    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_pair_kernel<false>, pair::SMEM_BYTES2);
-    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<256, true>, NarrowCfg<256>::kSmemBytes);
-    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<64, true>, NarrowCfg<64>::kSmemBytes);
-    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<32, true>, NarrowCfg<32>::kSmemBytes);
-    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_pair_kernel<true>, pair::SMEM_BYTES2);
+    cudaError_t e = reserve_smem(qlinear_i8_kernel<256, kModeI8>, NarrowCfg<256>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<64, kModeI8>, NarrowCfg<64>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<32, kModeI8>, NarrowCfg<32>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_pair_kernel<kModeI8>, pair::SMEM_BYTES2);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<256, kModeF16>, NarrowCfg<256>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<64, kModeF16>, NarrowCfg<64>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<32, kModeF16>, NarrowCfg<32>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_pair_kernel<kModeF16>, pair::SMEM_BYTES2);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<256, kModeDigits>, NarrowCfg<256>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<64, kModeDigits>, NarrowCfg<64>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_kernel<32, kModeDigits>, NarrowCfg<32>::kSmemBytes);
+    if (e == cudaSuccess) e = reserve_smem(qlinear_i8_pair_kernel<kModeDigits>, pair::SMEM_BYTES2);
     results[dev] = e;
   });
   if (results[dev] != cudaSuccess)
@@ -1018,7 +1085,7 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(bool bf16, int n, int m) {
 // Picks the kernel (CTA pair or single CTA at one of three tile widths) and launches it; shared
 // by the int8 and the weight-only entry points.  `weight_bytes` decides between latency-bound and
 // bandwidth-bound tile widths of the single-CTA kernel.
-template <bool WO>
+template <int MODE>
 static int32_t launch_gemm(const void* a, int64_t a_row_bytes, int64_t lda_bytes, const void* b,
                            int64_t b_row_bytes, int64_t ldb_bytes, Params& p, int variant, uint32_t idesc_pair,
                            bool idesc_a_flag, int64_t weight_bytes, cudaStream_t st, const char* what) {
@@ -1046,23 +1113,23 @@ static int32_t launch_gemm(const void* a, int64_t a_row_bytes, int64_t lda_bytes
     const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
     // launched so that its set-up (barriers, TMEM allocation) may overlap the tail of the kernel
     // that produced its operands; it waits for that kernel before its first load
-    const cudaError_t err = launch_overlapped(qlinear_i8_pair_kernel<WO>, dim3(static_cast<unsigned>(2 * pairs)),
+    const cudaError_t err = launch_overlapped(qlinear_i8_pair_kernel<MODE>, dim3(static_cast<unsigned>(2 * pairs)),
                                               dim3(NUM_THREADS), pair::SMEM_BYTES2, st, map_a, map_b, p, idesc_pair);
     if (err != cudaSuccess) return fail(LC_ERR_CUDA, "%s (cta pair): %s", what, cudaGetErrorString(err));
     return check_launch(what);
   }
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + bnt - 1) / bnt);
   const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
-  const uint32_t idesc = WO ? make_idesc_f16(idesc_a_flag, bnt, BM) : make_idesc(idesc_a_flag, bnt);
+  const uint32_t idesc = MODE == kModeF16 ? make_idesc_f16(idesc_a_flag, bnt, BM) : make_idesc(idesc_a_flag, bnt);
   cudaError_t err;
   if (bnt == 256)
-    err = launch_overlapped(qlinear_i8_kernel<256, WO>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<256>::kSmemBytes, st,
+    err = launch_overlapped(qlinear_i8_kernel<256, MODE>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<256>::kSmemBytes, st,
                             map_a, map_b, p, idesc);
   else if (bnt == 64)
-    err = launch_overlapped(qlinear_i8_kernel<64, WO>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<64>::kSmemBytes, st,
+    err = launch_overlapped(qlinear_i8_kernel<64, MODE>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<64>::kSmemBytes, st,
                             map_a, map_b, p, idesc);
   else
-    err = launch_overlapped(qlinear_i8_kernel<32, WO>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<32>::kSmemBytes, st,
+    err = launch_overlapped(qlinear_i8_kernel<32, MODE>, dim3(grid), dim3(NUM_THREADS), NarrowCfg<32>::kSmemBytes, st,
                             map_a, map_b, p, idesc);
   if (err != cudaSuccess) return fail(LC_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
   return check_launch(what);
@@ -1147,6 +1214,7 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
   p.fast_f32 = (out_dtype == LC_F32 && sw && n_out == 1 && p.out_vec) ? 1 + (zx ? 1 : 0) + (bias ? 2 : 0) : 0;
 
   p.wait_test = wait_test;
+  p.rows_out = M;
   p.kb_wrap = 1;
   p.rowsum = nullptr;
   p.colcorr = nullptr;
@@ -1154,7 +1222,7 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
   p.fq_scale = nullptr;
   p.fq_zp = nullptr;
   p.fq_min = p.fq_max = 0.0f;
-  return launch_gemm<false>(a, K, lda, b, K, ldb, p, variant, make_idesc_pair(a_unsigned != 0), a_unsigned != 0,
+  return launch_gemm<kModeI8>(a, K, lda, b, K, ldb, p, variant, make_idesc_pair(a_unsigned != 0), a_unsigned != 0,
                             N * K, as_stream(stream), "qlinear_i8");
 }
 
@@ -1226,6 +1294,7 @@ extern "C" int32_t lc_wo_gemm_16(const void* a, int32_t a_dtype, int32_t n_terms
   p.fast_f32 = 0;
   p.status = status;
   p.wait_test = wait_test;
+  p.rows_out = M;
   p.kb_wrap = static_cast<int>(kblocks);
   p.rowsum = rowsum;
   p.colcorr = colcorr;
@@ -1235,6 +1304,65 @@ extern "C" int32_t lc_wo_gemm_16(const void* a, int32_t a_dtype, int32_t n_terms
   p.fq_min = static_cast<float>(quant_min);
   p.fq_max = static_cast<float>(quant_max);
   const bool bf16 = a_dtype == LC_BF16;
-  return launch_gemm<true>(a, n_terms * K * 2, lda * 2, w16, K * 2, ldw * 2, p, variant,
+  return launch_gemm<kModeF16>(a, n_terms * K * 2, lda * 2, w16, K * 2, ldw * 2, p, variant,
                            make_idesc_f16(bf16, BN, 2 * BM), bf16, N * K * 2, as_stream(stream), "wo_gemm_16");
+}
+
+// Weight-only Linear for fp32 activations on exact integer arithmetic (see the header of this file).
+extern "C" int32_t lc_wo_gemm_digits(const int8_t* digits, int64_t ldd, const float* row_scale, const int8_t* wq,
+                                     int64_t ldw, int64_t M, int64_t N, int64_t K, const float* sw,
+                                     const float* bias, const float* rowsum, const float* colcorr, int32_t relu,
+                                     const float* out_scale, const float* out_zp, int32_t quant_min,
+                                     int32_t quant_max, float* out, int64_t ldo, int32_t* status, int32_t variant,
+                                     void* stream) {
+  using namespace lc::gemm;
+  if (M < 0 || N < 0 || K <= 0) return fail(LC_ERR_INVALID_ARG, "wo_gemm_digits: bad shape");
+  if (M == 0 || N == 0) return LC_OK;
+  if (!digits || !row_scale || !wq || !out) return fail(LC_ERR_INVALID_ARG, "wo_gemm_digits: null pointer");
+  const int wait_test = (variant & LC_QLINEAR_WAIT_TEST) ? 1 : 0;
+  variant &= ~LC_QLINEAR_WAIT_TEST;
+  if (wait_test && !status) return fail(LC_ERR_INVALID_ARG, "wo_gemm_digits: the wait test needs a status word");
+  if (variant < 0 || variant > 2) return fail(LC_ERR_INVALID_ARG, "wo_gemm_digits: variant must be 0, 1 or 2");
+  if (ldd < K || ldw < K || ldo < N) return fail(LC_ERR_INVALID_ARG, "wo_gemm_digits: leading dimension too small");
+  if (ldd % 16 || ldw % 16 || !aligned(digits, 16) || !aligned(wq, 16))
+    return fail(LC_ERR_UNSUPPORTED, "wo_gemm_digits: operand rows must start on 16-byte boundaries (pad ldd/ldw to 16)");
+  if ((rowsum == nullptr) != (colcorr == nullptr))
+    return fail(LC_ERR_INVALID_ARG, "wo_gemm_digits: rowsum and colcorr go together");
+  if ((out_scale == nullptr) != (out_zp == nullptr))
+    return fail(LC_ERR_INVALID_ARG, "wo_gemm_digits: out_scale and out_zp go together");
+  const int64_t plane_rows = lc_wo_digit_rows(M);
+  if (plane_rows > 0x7fffffffLL - 2 * BM || N > 0x7fffffffLL - BN || K > 0x7fffffffLL - BK)
+    return fail(LC_ERR_UNSUPPORTED, "wo_gemm_digits: dimension exceeds the TMA coordinate range");
+  // |sum| <= K * 2^30 * 128 must stay inside the 64-bit recombination and each plane's int32 sum
+  if (K > (int64_t{1} << 17)) return fail(LC_ERR_UNSUPPORTED, "wo_gemm_digits: K above 131072 could overflow int32");
+
+  Params p;
+  p.M = plane_rows;
+  p.N = N;
+  p.K = K;
+  p.sx = row_scale;
+  p.sx_per_row = 1;
+  p.zx = nullptr;
+  p.wsum = nullptr;
+  p.sw = sw;
+  p.bias = bias;
+  for (int i = 0; i < 8; ++i) p.outs[i] = i == 0 ? out : nullptr;
+  p.n_out = 1;
+  p.out_dtype = LC_F32;
+  p.ldo = ldo;
+  p.out_vec = 0;
+  p.fast_f32 = 0;
+  p.status = status;
+  p.wait_test = wait_test;
+  p.rows_out = M;
+  p.kb_wrap = 1;
+  p.rowsum = rowsum;
+  p.colcorr = colcorr;
+  p.relu = relu ? 1 : 0;
+  p.fq_scale = out_scale;
+  p.fq_zp = out_zp;
+  p.fq_min = static_cast<float>(quant_min);
+  p.fq_max = static_cast<float>(quant_max);
+  return launch_gemm<kModeDigits>(digits, K, ldd, wq, K, ldw, p, variant, make_idesc_pair(false), false, N * K,
+                                  as_stream(stream), "wo_gemm_digits");
 }

@@ -98,6 +98,101 @@ split_f32_bf16x3_kernel(const float* __restrict__ x, int64_t cols, int64_t ldx, 
   }
 }
 
+// fp32 row -> four signed base-256 digit planes of round(x * 2^e), 2^e the power of two that puts the
+// row's largest magnitude into [2^29, 2^30).  One CTA per row: pass 1 finds the maximum, pass 2
+// re-reads the row (from L1/L2) and writes the digits of 4 elements as one 4-byte store per plane.
+// Plane d of row m = 32t + r lives in row 128t + 32d + r of `digits`: the digit planes of 32 rows
+// make up one 128-row GEMM tile, plane d in accumulator lanes 32d .. 32d+31.
+template <bool VEC>
+__global__ void __launch_bounds__(kPrepThreads)
+split_f32_digits_kernel(const float* __restrict__ x, int64_t cols, int64_t ldx, int8_t* __restrict__ digits,
+                        int64_t ldd, float* __restrict__ row_scale, float* __restrict__ rowsum) {
+  __shared__ float red[2 * (kPrepThreads / 32)];
+  __shared__ float s_mul;
+  const int64_t r = blockIdx.x;
+  const float* xr = x + r * ldx;
+  float mx = 0.0f, sum = 0.0f;
+  bool bad = false;
+  for (int64_t k = static_cast<int64_t>(threadIdx.x) * 4; k < cols; k += kPrepThreads * 4) {
+    float v[4];
+    if (VEC && k + 4 <= cols) {
+      const float4 f = __ldg(reinterpret_cast<const float4*>(xr + k));
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = k + e < cols ? xr[k + e] : 0.0f;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      mx = fmaxf(mx, fabsf(v[e]));
+      bad |= !(fabsf(v[e]) <= 3.402823466e38f);  // NaN or infinity
+      sum += v[e];
+    }
+  }
+  if (bad) mx = INFINITY;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    red[threadIdx.x >> 5] = mx;
+    red[kPrepThreads / 32 + (threadIdx.x >> 5)] = sum;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = 0.0f, s = 0.0f;
+    for (int w = 0; w < kPrepThreads / 32; ++w) {
+      m = fmaxf(m, red[w]);
+      s += red[kPrepThreads / 32 + w];
+    }
+    // m = f * 2^ex with f in [0.5, 1): x * 2^(30 - ex) has magnitude below 2^30.  A non-finite row gets
+    // a NaN scale (its outputs become NaN); an all-zero row any scale.  e is capped so that 2^e and
+    // 2^-e stay normal numbers.
+    int ex = 0;
+    float mul = 1.0f, inv = 1.0f;
+    if (m > 3.402823466e38f) {
+      mul = 0.0f;
+      inv = __int_as_float(0x7fc00000);
+    } else if (m > 0.0f) {
+      frexpf(m, &ex);
+      int e = 30 - ex;
+      e = e > 126 ? 126 : e;
+      mul = __int_as_float((127 + e) << 23);
+      inv = __int_as_float((127 - e) << 23);
+    }
+    s_mul = mul;
+    row_scale[r] = inv;
+    if (rowsum) rowsum[r] = s;
+  }
+  __syncthreads();
+  const float mul = s_mul;
+  int8_t* base = digits + ((r >> 5) * 128 + (r & 31)) * ldd;
+  for (int64_t k = static_cast<int64_t>(threadIdx.x) * 4; k < ldd; k += kPrepThreads * 4) {
+    float v[4];
+    if (VEC && k + 4 <= cols) {
+      const float4 f = __ldg(reinterpret_cast<const float4*>(xr + k));
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = k + e < cols ? xr[k + e] : 0.0f;
+    }
+    uint32_t plane[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      int X = __float2int_rn(__fmul_rn(v[e], mul));  // the product is exact: mul is a power of two
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        const int digit = ((X + 128) & 255) - 128;  // signed digit in [-128, 127]
+        plane[d] |= static_cast<uint32_t>(digit & 255) << (8 * e);
+        X = (X - digit) >> 8;                        // exact: X - digit is a multiple of 256
+      }
+    }
+#pragma unroll
+    for (int d = 0; d < 4; ++d) *reinterpret_cast<uint32_t*>(base + static_cast<int64_t>(d) * 32 * ldd + k) = plane[d];
+  }
+}
+
 }  // namespace
 }  // namespace lc
 
@@ -141,4 +236,25 @@ extern "C" int32_t lc_split_f32_bf16x3(const float* x, int64_t rows, int64_t col
   else
     split_f32_bf16x3_kernel<false><<<static_cast<unsigned>(rows), kPrepThreads, 0, st>>>(x, cols, ldx, t, kp, rowsum);
   return check_launch("split_f32_bf16x3");
+}
+
+extern "C" int64_t lc_wo_digit_rows(int64_t rows) { return rows <= 0 ? 0 : (rows + 31) / 32 * 128; }
+
+extern "C" int32_t lc_split_f32_digits(const float* x, int64_t rows, int64_t cols, int64_t ldx, int8_t* digits,
+                                       int64_t ldd, float* row_scale, float* rowsum, void* stream) {
+  if (rows < 0 || cols <= 0 || ldx < cols || ldd < cols || ldd % 16)
+    return fail(LC_ERR_INVALID_ARG, "split_f32_digits: bad shape (ldd must be a multiple of 16 and >= cols)");
+  if (rows == 0) return LC_OK;
+  if (!x || !digits || !row_scale) return fail(LC_ERR_INVALID_ARG, "split_f32_digits: null pointer");
+  if (rows > 0x7fffffffLL) return fail(LC_ERR_UNSUPPORTED, "split_f32_digits: too many rows");
+  if (!aligned(digits, 4)) return fail(LC_ERR_UNSUPPORTED, "split_f32_digits: digits must be 4-byte aligned");
+  const bool vec = ldx % 4 == 0 && aligned(x, 16);
+  cudaStream_t st = as_stream(stream);
+  if (vec)
+    split_f32_digits_kernel<true><<<static_cast<unsigned>(rows), kPrepThreads, 0, st>>>(x, cols, ldx, digits, ldd,
+                                                                                        row_scale, rowsum);
+  else
+    split_f32_digits_kernel<false><<<static_cast<unsigned>(rows), kPrepThreads, 0, st>>>(x, cols, ldx, digits, ldd,
+                                                                                         row_scale, rowsum);
+  return check_launch("split_f32_digits");
 }

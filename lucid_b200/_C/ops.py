@@ -482,6 +482,55 @@ def split_f32_bf16x3(x2d: torch.Tensor, want_rowsum: bool = False):
     return terms, rowsum
 
 
+def split_f32_digits(x2d: torch.Tensor, want_rowsum: bool = False):
+    """fp32 ``[M, K]`` -> ``(digits, row_scale [M], rowsum [M] or None)``: each row scaled by a power
+    of two (``1 / row_scale``) into the 31-bit integer range and cut into four signed base-256
+    digit planes, ``digits`` being the int8 ``[128 * ceil(M / 32), pad16(K)]`` operand of
+    :func:`wo_gemm_digits` (plane d of row 32 t + r in row 128 t + 32 d + r)."""
+    dev = _need_cuda(x2d)
+    if x2d.dtype != torch.float32 or x2d.dim() != 2:
+        raise TypeError("split_f32_digits: expected a 2-D fp32 tensor")
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    m, k = x2d.shape
+    digits = torch.empty((int(lib.lc_wo_digit_rows(m)), _pad16(k)), dtype=torch.int8, device=dev)
+    row_scale = torch.empty((m,), dtype=torch.float32, device=dev)
+    rowsum = torch.empty((m,), dtype=torch.float32, device=dev) if want_rowsum else None
+    with _on(dev):
+        check(lib.lc_split_f32_digits(x2d.data_ptr(), m, k, x2d.stride(0), digits.data_ptr(), digits.stride(0),
+                                      row_scale.data_ptr(), _ptr(rowsum), _stream(dev)))
+    return digits, row_scale, rowsum
+
+
+def wo_gemm_digits(digits: torch.Tensor, row_scale: torch.Tensor, wq: torch.Tensor, sw=None, bias=None, rowsum=None,
+                   colcorr=None, relu: bool = False, out_scale=None, out_zp=None, quant_min: int = 0,
+                   quant_max: int = 255, status=None, variant: int = 0, wait_test: bool = False):
+    """Exact weight-only Linear for fp32 activations: ``digits`` / ``row_scale`` from
+    :func:`split_f32_digits`, ``wq`` int8 codes ``[N, K]`` with a 16-byte row pitch.  Returns fp32
+    ``requant(relu(sum * row_scale * sw + rowsum x colcorr + bias))``, the dot product being exact."""
+    dev = _need_cuda(digits, row_scale, wq, sw, bias, rowsum, colcorr, out_scale, out_zp, status)
+    if digits.dtype != torch.int8 or wq.dtype != torch.int8 or digits.stride(1) != 1 or wq.stride(1) != 1:
+        raise TypeError("wo_gemm_digits: digits and wq must be int8 with unit column stride")
+    m = row_scale.numel()
+    n, k = wq.shape
+    if digits.shape[0] != int(lib.lc_wo_digit_rows(m)) or digits.shape[1] < k:
+        raise ValueError("wo_gemm_digits: digits do not belong to these rows / this K")
+    out = torch.empty((m, n), dtype=torch.float32, device=dev)
+    sw_c = None if sw is None else _f32c(sw)
+    bias_c = None if bias is None else _f32c(bias)
+    rs_c = None if rowsum is None else _f32c(rowsum)
+    cc_c = None if colcorr is None else _f32c(colcorr)
+    os_c = None if out_scale is None else _f32c(out_scale)
+    oz_c = None if out_zp is None else _f32c(out_zp)
+    with _on(dev):
+        check(lib.lc_wo_gemm_digits(digits.data_ptr(), digits.stride(0), _f32c(row_scale).data_ptr(), wq.data_ptr(),
+                                    wq.stride(0), m, n, k, _ptr(sw_c), _ptr(bias_c), _ptr(rs_c), _ptr(cc_c),
+                                    1 if relu else 0, _ptr(os_c), _ptr(oz_c), int(quant_min), int(quant_max),
+                                    out.data_ptr(), n, _ptr(status),
+                                    int(variant) | (LC_QLINEAR_WAIT_TEST if wait_test else 0), _stream(dev)))
+    return out
+
+
 def wo_gemm_16(a: torch.Tensor, n_terms: int, w16: torch.Tensor, sw=None, bias=None, rowsum=None, colcorr=None,
                relu: bool = False, out_scale=None, out_zp=None, quant_min: int = 0, quant_max: int = 255,
                out_dtype: torch.dtype = torch.float32, status=None, variant: int = 0, wait_test: bool = False):

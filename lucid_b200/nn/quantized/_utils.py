@@ -70,11 +70,12 @@ class StaticWeightCache:
     them changes (new storage or in-place version): the scale as one value per output row, the
     zero-point term of the epilogue (``None`` for the usual symmetric weights; the one
     device-to-host read that decides this happens here, once per weight, never in a forward), and
-    -- made on first use by a batch too large for the GEMV kernel -- the codes widened to bf16."""
+    -- made on first use by a batch too large for the GEMV kernel -- the codes with rows on
+    16-byte boundaries (the buffer itself when ``in_features`` is a multiple of 16)."""
 
     def __init__(self) -> None:
         self._key = None
-        self._w16 = None
+        self._codes16 = None
 
     def get(self, codes: torch.Tensor, scale: torch.Tensor, zero_point: torch.Tensor, ch_axis: int):
         key = tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in (codes, scale, zero_point)) + (ch_axis,)
@@ -100,14 +101,14 @@ class StaticWeightCache:
                 raise ValueError(f"weight_scale of {scale.numel()} entries does not fit a [{n}, {k}] weight "
                                  f"quantized along axis {ch_axis}")
             self.gemv_ok = self.col_scale is None and self.colcorr is None
-            self._w16 = None
+            self._codes16 = None
             self._key = key
         return self
 
-    def w16(self, codes: torch.Tensor) -> torch.Tensor:
-        if self._w16 is None:
-            self._w16 = _backend.ops().widen_s8(codes, torch.bfloat16)
-        return self._w16
+    def codes16(self, codes: torch.Tensor) -> torch.Tensor:
+        if self._codes16 is None:
+            self._codes16 = _backend.ops().pad_rows_to_16(codes)
+        return self._codes16
 
 
 class Int8WeightCache:

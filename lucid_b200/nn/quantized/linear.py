@@ -4,9 +4,10 @@ the calibrated activation grid.  The reference dequantizes the whole weight on e
 forward, calls a float GEMM and then runs the fake-quantize chain
 (``linear.py:206-214``); here the whole forward is one kernel: decode batches go
 through the weight-only GEMV kernel (the weight is read once as int8), larger ones
-through the tensor-core kernel on the exact three-term bf16 split of the fp32
-activations (``lc_wo_gemm_16``), and in both the scale, bias, ReLU and output
-requantization are the kernel's epilogue.  No fp32 copy of the weight is made.
+through the tensor-core kernel on exact integer arithmetic (``lc_wo_gemm_digits``: the
+fp32 activations as four int8 digit planes, int32 accumulation, one rounding), and in
+both the scale, bias, ReLU and output requantization are the kernel's epilogue.  No
+floating-point copy of the weight is made.
 """
 from __future__ import annotations
 
@@ -63,9 +64,9 @@ class Linear(nn.Module):
                 x2 = x2 * w.col_scale
                 if w.col_zp is not None:
                     rowsum = (x2 * w.col_zp).sum(1)
-            terms, rs = ops.split_f32_bf16x3(x2, want_rowsum=w.colcorr is not None and rowsum is None)
-            y = ops.wo_gemm_16(terms, 3, w.w16(wq), sw=w.row_scale, bias=bias,
-                               rowsum=rowsum if rowsum is not None else rs, colcorr=w.colcorr, **grid)
+            digits, row_scale, rs = ops.split_f32_digits(x2, want_rowsum=w.colcorr is not None and rowsum is None)
+            y = ops.wo_gemm_digits(digits, row_scale, w.codes16(wq), sw=w.row_scale, bias=bias,
+                                   rowsum=rowsum if rowsum is not None else rs, colcorr=w.colcorr, **grid)
         y = y.reshape(*xd.shape[:-1], self.out_features)
         return y if x.is_cuda else y.to(x.device)
 

@@ -11,7 +11,7 @@ import torch
 from torch import nn
 
 from lucid_b200 import _backend
-from lucid_b200.quantization._functional import dequantize, quantize
+from lucid_b200.quantization._functional import quantize
 from lucid_b200.quantization._qscheme import QDtype, per_channel_symmetric, qint8
 
 _GEMV_MAX_ROWS = 32
@@ -34,6 +34,26 @@ class _SettledBuffers:
         return settled
 
 
+def wide_product(x2: torch.Tensor, codes: torch.Tensor, scale: torch.Tensor, bias, cache: dict) -> torch.Tensor:
+    """``x2 @ (codes * scale)^T + bias`` for more rows than the GEMV kernel takes, without a float copy
+    of the weight: bf16 / f16 activations against the codes widened (exactly) to the same type on
+    ``lc_wo_gemm_16``; fp32 activations as int8 digit planes on ``lc_wo_gemm_digits`` (exact).
+    ``cache`` keeps the operand form of the weight per (kind, storage, version)."""
+    ops = _backend.ops()
+    k = x2.shape[1]
+    halves = x2.dtype in (torch.bfloat16, torch.float16) and k % 8 == 0
+    key = (x2.dtype if halves else "s8", codes.data_ptr(), codes._version)
+    if cache.get("key") != key:
+        cache["key"] = key
+        cache["w"] = ops.widen_s8(codes, x2.dtype)[:, :k] if halves else ops.pad_rows_to_16(codes)
+    if halves:
+        if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+            x2 = x2.contiguous()
+        return ops.wo_gemm_16(x2, 1, cache["w"], sw=scale, bias=bias, out_dtype=x2.dtype)
+    digits, row_scale, _ = ops.split_f32_digits(x2.float())
+    return ops.wo_gemm_digits(digits, row_scale, cache["w"], sw=scale, bias=bias).to(x2.dtype)
+
+
 def _quantize_rows(weight: torch.Tensor, dtype: QDtype):
     from lucid_b200.quantization.observer import PerChannelMinMaxObserver
 
@@ -54,6 +74,7 @@ class WeightOnlyLinear(nn.Module):
         else:
             self.bias = None
         self._settled = _SettledBuffers()
+        self._wide_cache = {}
 
     @classmethod
     def from_float(cls, mod: nn.Module, dtype: QDtype = qint8) -> "WeightOnlyLinear":
@@ -72,11 +93,15 @@ class WeightOnlyLinear(nn.Module):
             y = _backend.ops().wo_linear_s8(
                 x2, self.weight_int8, self.weight_scale, self.bias,
                 overlap_previous=self._settled(self.weight_int8, self.weight_scale, self.bias))
-        else:  # compute-bound batches: decode the weight once, dense product
-            w = dequantize(self.weight_int8, self.weight_scale, 0.0, ch_axis=0).to(x2.dtype)
-            y = torch.nn.functional.linear(x2, w, None if self.bias is None else self.bias.to(x2.dtype))
+        elif x2.shape[0] == 0:
+            y = x2.new_zeros((0, self.out_features))
+        else:  # compute-bound batches: the tensor-core weight-only kernels
+            y = self._wide(x2)
         y = y.reshape(*xd.shape[:-1], self.out_features)
         return y if x.is_cuda else y.to(x.device)
+
+    def _wide(self, x2: torch.Tensor) -> torch.Tensor:
+        return wide_product(x2, self.weight_int8, self.weight_scale, self.bias, self._wide_cache)
 
     def extra_repr(self) -> str:
         return f"in_features={self.in_features}, out_features={self.out_features}, weight_only=int8"
@@ -96,6 +121,7 @@ class WeightOnlySwiGLU(nn.Module):
         self.register_buffer("gate_up_scale", torch.ones(2 * intermediate))
         self.down = WeightOnlyLinear(intermediate, hidden, bias=False)
         self._settled = _SettledBuffers()
+        self._wide_cache = {}
 
     @classmethod
     def from_float(cls, gate: nn.Linear, up: nn.Linear, down: nn.Linear, dtype: QDtype = qint8) -> "WeightOnlySwiGLU":
@@ -121,9 +147,9 @@ class WeightOnlySwiGLU(nn.Module):
                 x2, self.gate_up_int8, self.gate_up_scale,
                 overlap_previous=self._settled(self.gate_up_int8, self.gate_up_scale))
         else:
-            (wg, wu), (sg, su) = self._split(self.gate_up_int8), self._split(self.gate_up_scale)
-            g = torch.nn.functional.linear(x2, dequantize(wg.contiguous(), sg.contiguous(), 0.0, ch_axis=0).to(x2.dtype))
-            u = torch.nn.functional.linear(x2, dequantize(wu.contiguous(), su.contiguous(), 0.0, ch_axis=0).to(x2.dtype))
-            h = torch.nn.functional.silu(g) * u
+            # one product against the interleaved weight; output columns come in blocks of 8 gate / 8 up
+            gu = wide_product(x2, self.gate_up_int8, self.gate_up_scale, None, self._wide_cache)
+            gu = gu.reshape(x2.shape[0], self.intermediate // 8, 2, 8)
+            h = (torch.nn.functional.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(x2.shape[0], self.intermediate)
         y = self.down(h).reshape(*xd.shape[:-1], self.hidden)
         return y if x.is_cuda else y.to(x.device)

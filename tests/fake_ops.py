@@ -160,6 +160,23 @@ def split_f32_bf16x3(x2d, want_rowsum=False):
     return terms, (x2d.float().sum(1) if want_rowsum else None)
 
 
+def split_f32_digits(x2d, want_rowsum=False):
+    """Stand-in: the 'digits' are the fp32 rows themselves (the host logic only passes them on)."""
+    return x2d.float(), torch.ones(x2d.shape[0]), (x2d.float().sum(1) if want_rowsum else None)
+
+
+def wo_gemm_digits(digits, row_scale, wq, sw=None, bias=None, rowsum=None, colcorr=None, relu=False, out_scale=None,
+                   out_zp=None, quant_min=0, quant_max=255, status=None, variant=0, wait_test=False):
+    y = _np(digits).astype(np.float64) @ _np(wq).astype(np.float64).T
+    if sw is not None:
+        y = y * _np(sw).astype(np.float64)[None, :]
+    if rowsum is not None:
+        y = y + _np(rowsum).astype(np.float64)[:, None] * _np(colcorr).astype(np.float64)[None, :]
+    if bias is not None:
+        y = y + _np(bias).astype(np.float64)[None, :]
+    return torch.tensor(_finish(y, relu, out_scale, out_zp, quant_min, quant_max))
+
+
 def wo_gemm_16(a, n_terms, w16, sw=None, bias=None, rowsum=None, colcorr=None, relu=False, out_scale=None,
                out_zp=None, quant_min=0, quant_max=255, out_dtype=torch.float32, status=None, variant=0,
                wait_test=False):

@@ -23,7 +23,8 @@ def ops():
 def accumulation_bound(x, wq, sw, K):
     """A-priori bound of an fp32-accumulated dot product against its exact value, per output:
     (number of accumulation steps) * 2^-23 * sum_k |x_k| |w_k| * s.  Steps: 3 K / 16 tensor-core
-    instructions of the three-term kernel, K / 8 for a blocked host sgemm, a few for the epilogue."""
+    instructions of the three-term bf16 kernel, K / 8 for a blocked host sgemm (what the oracle
+    runs), a few for the epilogue."""
     terms = (np.abs(x).astype(np.float64) @ np.abs(wq).astype(np.float64).T) * np.asarray(sw, np.float64)[None, :]
     return (3 * K / 16 + K / 8 + 16) * 2.0 ** -23 * terms
 
@@ -79,6 +80,62 @@ def test_wo_gemm_three_term_product(ops, M, N, K, variant):
     w = O.dequantize(wq, sw, np.zeros(N, np.float32), ch_axis=0)
     err_o = np.abs(y.cpu().numpy().astype(np.float64) - O.linear_f32(x, w, bias))
     assert (err_o <= 2 * bound).all()
+
+
+@pytest.mark.parametrize("M,K", [(1, 16), (33, 100), (300, 512), (64, 4100)])
+def test_digit_planes_reassemble_the_rows(ops, M, K):
+    """sum_d digit_d * 256^d * row_scale gives back every entry within 2^-6 of its row's maximum
+    exactly, and every other entry to 2^-31 of that maximum; digits of the padding are zero."""
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    x = torch.randn(M, K, device="cuda", generator=g) * torch.logspace(-6, 2, K, device="cuda")
+    x[0] = 0.0
+    digits, scale, rs = ops.split_f32_digits(x, want_rowsum=True)
+    kp = (K + 15) // 16 * 16
+    assert tuple(digits.shape) == ((M + 31) // 32 * 128, kp) and digits.dtype == torch.int8
+    d = digits.cpu().numpy().astype(np.int64).reshape(-1, 4, 32, kp)          # [tile, digit, row, k]
+    X = sum(d[:, i] * 256 ** i for i in range(4)).reshape(-1, kp)[:M]
+    assert not X[:, K:].any()
+    s = scale.double().cpu().numpy()[:, None]
+    assert np.all(np.log2(s[1:]) == np.round(np.log2(s[1:]))), "row scales are powers of two"
+    back = X[:, :K] * s
+    xh = x.double().cpu().numpy()
+    rowmax = np.abs(xh).max(1, keepdims=True)
+    big = np.abs(xh) >= rowmax * 2.0 ** -6
+    assert np.array_equal(back[big], xh[big])
+    assert (np.abs(back - xh) <= rowmax * 2.0 ** -31).all()
+    assert (np.abs(X).max(1)[1:] >= 2 ** 29).all() and (np.abs(X) < 2 ** 30).all()
+    assert torch.allclose(rs.double(), x.double().sum(1), rtol=1e-5, atol=1e-5 * float(x.abs().sum(1).max()))
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (33, 200, 320), (128, 256, 512), (129, 300, 1000), (600, 1000, 256),
+                                   (2048, 512, 2048), (100, 260, 8192)])
+def test_wo_gemm_digits_is_exact(ops, M, N, K, variant):
+    """fp32 activations x int8 codes through the digit planes: the result equals the float64 value
+    of sum_k X[m,k] * w[n,k] (X the integer image of the row), rounded once -- checked as
+    |y - exact| <= 1.5 ulp of the three epilogue roundings -- and sits far inside fp32-GEMM error."""
+    r = np.random.default_rng(M + N + K)
+    x = (r.standard_normal((M, K)) * np.exp(r.standard_normal((M, K)))).astype(np.float32)
+    wq = r.integers(-128, 128, (N, K)).astype(np.int8)
+    sw = (r.random(N) * 0.01 + 1e-3).astype(np.float32)
+    bias = r.standard_normal(N).astype(np.float32)
+    xt, wt = torch.tensor(x, device="cuda"), ops.pad_rows_to_16(torch.tensor(wq, device="cuda"))
+    digits, scale, _ = ops.split_f32_digits(xt)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    y = ops.wo_gemm_digits(digits, scale, wt, sw=torch.tensor(sw, device="cuda"), bias=torch.tensor(bias, device="cuda"),
+                           status=status, variant=variant)
+    ops.qlinear_check_status(status)
+    s = scale.double().cpu().numpy()[:, None]
+    X = np.rint(x.astype(np.float64) / s)                       # the integers the kernel multiplies
+    acc = X @ wq.astype(np.float64).T                            # exact: |acc| < 2^53
+    prod = acc * s * sw.astype(np.float64)[None, :]
+    ref = prod + bias[None, :]
+    got = y.double().cpu().numpy()
+    ulp = lambda v: 2.0 ** (np.floor(np.log2(np.maximum(np.abs(v), 1e-300))) - 23)
+    assert (np.abs(got - ref) <= 1.5 * ulp(prod) + 0.5 * ulp(ref)).all()
+    exact = (x.astype(np.float64) @ wq.astype(np.float64).T) * sw.astype(np.float64)[None, :] + bias[None, :]
+    err = np.abs(got - exact)
+    assert np.sqrt((err ** 2).mean()) <= 2e-7 * np.sqrt((exact ** 2).mean())
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -223,3 +280,11 @@ def test_bounded_waits_run_out_and_report(ops):
         y = ops.wo_gemm_16(x, 1, ops.widen_s8(b), status=status)
         ops.qlinear_check_status(status)
         assert torch.allclose(y.double(), x.double() @ b.double().T, rtol=1e-5, atol=1e-3)
+        digits, scale, _ = ops.split_f32_digits(x.float())
+        ops.wo_gemm_digits(digits, scale, b, status=status, wait_test=True)
+        with pytest.raises(LucidCudaError) as info:
+            ops.qlinear_check_status(status)
+        assert info.value.code == LC_ERR_TIMEOUT
+        y = ops.wo_gemm_digits(digits, scale, b, status=status)
+        ops.qlinear_check_status(status)
+        assert torch.allclose(y.double(), x.double() @ b.double().T, rtol=1e-6, atol=1e-4)
