@@ -327,7 +327,7 @@ int32_t lc_wo_gemm_16(const void* a, int32_t a_dtype, int32_t n_terms, int64_t l
 /* The same Linear for fp32 activations on EXACT integer arithmetic (tcgen05 kind::i8).  Every row of
  * x is scaled by a power of two so that its largest magnitude lies in [2^29, 2^30), rounded to an
  * integer X and cut into four signed base-256 digits (lc_split_f32_digits): entries within 2^-6 of
- * the row maximum keep all 24 bits, the absolute error of smaller ones is below 2^-31 of the row
+ * the row maximum keep all 24 bits, the absolute error of smaller ones is below 2^-30 of the row
  * maximum.  The four digit planes ride through one int8 GEMM with int32 accumulation and are put
  * back together in 64-bit integers in the epilogue, so sum_k X[m,k] * wq[n,k] is exact and
  *   y = f32(sum) * row_scale[m] * sw[n] + rowsum[m] * colcorr[n] + bias[n]

@@ -15,7 +15,7 @@
 // rows than a GEMV handles, in two more instantiations:
 //  * kModeDigits, for fp32 activations: every row of x is scaled by a power of two (exact) so that
 //    its largest entry lies in [2^29, 2^30), rounded to an integer (every entry within 2^-6 of the
-//    row maximum keeps all 24 bits; the absolute error of the rest is below 2^-31 of the row maximum)
+//    row maximum keeps all 24 bits; the absolute error of the rest is below 2^-30 of the row maximum)
 //    and cut into four signed base-256 digits.  The digit planes of 32 rows form one 128-row tile of
 //    A (lanes 32d .. 32d+31 of the accumulator hold digit d), the product runs on kind::i8 with exact
 //    int32 accumulation, and the epilogue recombines ((a3*256 + a2)*256 + a1)*256 + a0 in 64-bit

@@ -85,7 +85,7 @@ def test_wo_gemm_three_term_product(ops, M, N, K, variant):
 @pytest.mark.parametrize("M,K", [(1, 16), (33, 100), (300, 512), (64, 4100)])
 def test_digit_planes_reassemble_the_rows(ops, M, K):
     """sum_d digit_d * 256^d * row_scale gives back every entry within 2^-6 of its row's maximum
-    exactly, and every other entry to 2^-31 of that maximum; digits of the padding are zero."""
+    exactly, and every other entry to 2^-30 of that maximum; digits of the padding are zero."""
     g = torch.Generator(device="cuda").manual_seed(M + K)
     x = torch.randn(M, K, device="cuda", generator=g) * torch.logspace(-6, 2, K, device="cuda")
     x[0] = 0.0
@@ -102,7 +102,7 @@ def test_digit_planes_reassemble_the_rows(ops, M, K):
     rowmax = np.abs(xh).max(1, keepdims=True)
     big = np.abs(xh) >= rowmax * 2.0 ** -6
     assert np.array_equal(back[big], xh[big])
-    assert (np.abs(back - xh) <= rowmax * 2.0 ** -31).all()
+    assert (np.abs(back - xh) <= rowmax * 2.0 ** -30).all()
     assert (np.abs(X).max(1)[1:] >= 2 ** 29).all() and (np.abs(X) < 2 ** 30).all()
     assert torch.allclose(rs.double(), x.double().sum(1), rtol=1e-5, atol=1e-5 * float(x.abs().sum(1).max()))
 
