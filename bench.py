@@ -1,13 +1,15 @@
 """Benchmark of the int8 quantized-inference path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras] [--profile-case NAME]
+                    [--gather auto|fused|multimem|copy|nccl] [--sustain-seconds S]
 
 Headline workload ("prefill"): the prefill-shaped dynamic int8 Linear, x fp32 [16384, 8192]
 ~N(0,1) quantized per token, W [28672, 8192] ~N(0,0.02) quantized per output channel, int32
 accumulation, fp32 dequantized output; over N GPUs the weight is sharded by output
-columns and the output shards are exchanged inside the GEMM epilogue by peer stores over
-NVLink (symmetric memory), or with an NCCL all-gather (--gather nccl).  One step = quantize
-activations + GEMM (+ all-gather).  metric: int8 qLinear TOPS = 2*M*N*K / step time,
+columns and the output shards are exchanged by the column-parallel module: peer stores or
+multimem stores from the GEMM epilogue, copy-engine pushes of finished row bands, or an NCCL
+all-gather (--gather; "auto" times each once and keeps the fastest).  One step = quantize
+activations + GEMM (+ exchange).  metric: int8 qLinear TOPS = 2*M*N*K / step time,
 whole job.  At N = 1 the line also carries the HBM-bound companions of the metric (the
 [8192, 8192] quantize / dequantize roundtrip and the decode-shaped weight-only MLP) under
 "extras", the roofline of the dominant kernel and a CPU baseline timed on this host.
@@ -58,7 +60,7 @@ class ClockSampler:
     NOTED = {"sw_power_cap": 0x4}
 
     def __init__(self, index: int) -> None:
-        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self.index, self.samples, self.reasons, self.max_mhz, self.capped = index, [], set(), None, 0
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -77,6 +79,7 @@ class ClockSampler:
             try:
                 self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
                 mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                self.capped += 1 if mask & self.NOTED["sw_power_cap"] else 0
                 for name, bit in {**self.BAD, **self.NOTED}.items():
                     if mask & bit:
                         self.reasons.add(name)
@@ -97,17 +100,58 @@ class ClockSampler:
 
     def summary(self) -> dict:
         return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
-                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples),
+                "sw_power_cap_share": (self.capped / len(self.samples)) if self.samples else None}
 
 
 # ----------------------------------------------------------------------------------------
 # CPU reference arm (the reference's own formulation, restated in oracle/, on host cores)
 # ----------------------------------------------------------------------------------------
-def cpu_prefill_reference(steps: int, warmup: int, sample_rows: int = 512) -> dict:
+WORKLOAD = "prefill_qlinear_16384x28672x8192_per_token_int8"
+
+
+def workload_config() -> dict:
+    """Keys both arms print, so that their `config` can be compared field by field."""
+    return {"workload": WORKLOAD, "M": M_PREFILL, "N": N_PREFILL, "K": K_PREFILL,
+            "activation_quant": "dynamic per-token symmetric int8 (absmax/127.5, [-128,127])",
+            "weight_quant": "per-output-channel symmetric int8", "output": "fp32"}
+
+
+def host_cores() -> int:
+    return len(os.sched_getaffinity(0))
+
+
+def use_all_host_threads() -> None:
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm wants every core
+    it may run on.  Must be called before NumPy is imported."""
+    n = str(host_cores())
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[var] = n
+
+
+def blas_info() -> dict:
+    """Vendor and thread count of the BLAS NumPy actually runs on."""
+    try:
+        from threadpoolctl import threadpool_info
+
+        pools = [p for p in threadpool_info() if p.get("user_api") == "blas"]
+        if pools:
+            return {"blas": pools[0].get("internal_api"), "blas_version": pools[0].get("version"),
+                    "blas_threads": pools[0].get("num_threads")}
+    except Exception:
+        pass
+    return {"blas": "unknown", "blas_threads": None}
+
+
+def cpu_prefill_reference(steps: int, warmup: int, sample_rows: int = 512, budget_s: float = 60.0,
+                          single_thread_too: bool = True) -> dict:
     """Times the reference's dynamic Linear forward (fake-quantize x per row, dequantize the
     whole weight, fp32 GEMM) on `sample_rows` rows of the prefill workload against the full
-    [28672, 8192] weight, with all host threads NumPy's BLAS takes."""
+    [28672, 8192] weight, with all host threads NumPy's BLAS takes.  The reference's timing
+    contract (tools/_bench_timing.py:33-52): warm-ups, then median / p5 / p95 with the output
+    materialised; `steps` iterations unless `budget_s` of wall time runs out first (reported)."""
     import numpy as np
+    from threadpoolctl import threadpool_limits
 
     from oracle import oracle as O
 
@@ -117,37 +161,67 @@ def cpu_prefill_reference(steps: int, warmup: int, sample_rows: int = 512) -> di
     w *= np.float32(0.02)
     wq, sw, zw = O.quantize_weight_per_channel(w)
     del w
-    times = []
-    for i in range(warmup + steps):
+
+    def once() -> float:
         t0 = time.perf_counter()
         y = O.dynamic_linear_float(x, wq, sw, zw, None, "token_symmetric", O.qint8)
         float(y[0, 0])
-        if i >= warmup:
-            times.append(time.perf_counter() - t0)
-    t = statistics.median(times)
+        return time.perf_counter() - t0
+
+    def run(n_warm: int, n_steps: int, budget: float):
+        began = time.perf_counter()
+        for _ in range(n_warm):
+            once()
+        times = []
+        while len(times) < n_steps and (not times or time.perf_counter() - began < budget):
+            times.append(once())
+        return sorted(times)
+
+    with threadpool_limits(limits=host_cores(), user_api="blas"):
+        info = blas_info()
+        times = run(warmup, steps, budget_s)
     ops = 2.0 * sample_rows * N_PREFILL * K_PREFILL
-    return {"value": ops / t / 1e12, "unit": "TOPS", "cores": len(os.sched_getaffinity(0)), "kind": "port",
-            "sample": f"{sample_rows} of {M_PREFILL} rows of x against the full W [{N_PREFILL},{K_PREFILL}], "
-                      f"reference float formulation (per-forward weight dequantize + sgemm), median of {steps}",
-            "seconds_per_sample": t}
+    t = statistics.median(times)
+    out = {"value": ops / t / 1e12, "unit": "TOPS", "cores": int(info.get("blas_threads") or host_cores()),
+           "kind": "port",
+           "sample": f"{sample_rows} of {M_PREFILL} rows of x against the full W [{N_PREFILL},{K_PREFILL}], "
+                     f"reference float formulation (per-forward weight dequantize + sgemm), median of {len(times)}",
+           "seconds_per_sample": t, "p5_s": times[int(len(times) * 0.05)], "p95_s": times[min(len(times) - 1, int(len(times) * 0.95))],
+           "iterations": len(times), "iterations_asked": steps, "wall_budget_s": budget_s,
+           "host_cores_available": host_cores(), **info}
+    try:
+        import torch
+
+        out["torch_num_threads"] = torch.get_num_threads()
+    except Exception:
+        pass
+    if single_thread_too:
+        with threadpool_limits(limits=1, user_api="blas"):
+            t1 = statistics.median(run(1, 2, budget_s / 4))
+        out["single_thread"] = {"value": ops / t1 / 1e12, "unit": "TOPS", "cores": 1, "seconds_per_sample": t1}
+    return out
 
 
 def run_reference_arm(args) -> int:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    steps = max(1, min(args.steps, 3))
-    warmup = max(1, min(args.warmup, 1))
-    base = cpu_prefill_reference(steps, warmup)
+    use_all_host_threads()
+    steps, warmup = max(1, args.steps), max(1, args.warmup)
+    base = cpu_prefill_reference(steps, warmup, budget_s=90.0)
+    keep = ("value", "unit", "cores", "kind", "sample", "blas", "blas_threads", "torch_num_threads",
+            "host_cores_available", "single_thread", "p5_s", "p95_s", "iterations")
     line = {
         "impl": "reference", "metric": "int8_qlinear_tops", "value": base["value"], "unit": "TOPS",
-        "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "n_gpus": args.gpus, "steps": base["iterations"], "warmup": warmup,
+        "steps_note": None if base["iterations"] == steps else
+        f"{steps} steps asked; stopped after {base['iterations']} when the {base['wall_budget_s']:.0f} s wall budget ran out",
         "ms_per_step": base["seconds_per_sample"] * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "prefill_qlinear_16384x28672x8192_per_token_int8",
-                   "note": "reference engine is Apple-only; its Python-level CPU formulation restated in "
-                           "oracle/ is timed on a bounded row sample"},
-        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "config": {**workload_config(),
+                   "note": "reference engine is Apple-only; its Python-level CPU formulation restated in oracle/ is "
+                           "timed on a bounded row sample of this workload (see cpu_baseline.sample)"},
+        "cpu_baseline": {k: base[k] for k in keep if k in base},
         "e2e": {"value": base["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -527,6 +601,169 @@ def run_profile_case(args) -> int:
     return 0
 
 
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "qlinear_i8_pair_gemm_4096x7168x8192.traffic.json")
+
+
+def gemm_dram_traffic(ops_per_launch: float):
+    """DRAM bytes of one launch of the dominant kernel: the profiler's read + write counters of a
+    small launch of the same kernel (same K, same tile shape), scaled by the operations ratio."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            t = json.load(f)
+        return (t["dram_bytes_read"] + t["dram_bytes_write"]) / t["ops"] * ops_per_launch
+    except Exception:
+        return None
+
+
+def check_rows_cols(M: int, N: int, n_local: int, world: int):
+    """Sample of the full-size output that the oracle recomputes: rows at the first / last tile,
+    both sides of the 128- and 256-row tile edges, the start and end of a 16-tile band (rows
+    4095 / 4096) and the last wave; columns at the first / last tile and the 255 / 256 edge of
+    EVERY rank's shard, plus seeded random ones: at least 64 of each."""
+    import numpy as np
+
+    rows = {0, 1, 127, 128, 255, 256, 257, 511, 512, 4095, 4096, M // 2 - 1, M // 2, M - 4097, M - 4096,
+            M - 513, M - 512, M - 257, M - 256, M - 129, M - 128, M - 2, M - 1}
+    rng = np.random.default_rng(7)
+    rows.update(int(r) for r in rng.choice(M, 64, replace=False))
+    cols = set()
+    for r in range(world):
+        base = r * n_local
+        cols.update(base + c for c in (0, 1, 255, 256, n_local // 2, n_local - 257, n_local - 256, n_local - 1))
+        cols.update(base + int(c) for c in rng.choice(n_local, max(4, 64 // world), replace=False))
+    return np.array(sorted(r for r in rows if 0 <= r < M)), np.array(sorted(c for c in cols if 0 <= c < N))
+
+
+def oracle_check(torch, ops, x, xq, sx, wq, sw, result, rank: int, world: int, n_local: int):
+    """The full-size launch against the oracle, outside the timed region: this rank's activation
+    codes and scales are bit-compared with the oracle's on the sampled rows, the int32 accumulator
+    of this rank's shard (a second launch with raw integer output) must EQUAL the oracle's exact
+    integer product on the sampled rows x this shard's sampled columns, and the fp32 values of the
+    timed path, for ALL ranks' sampled columns in this rank's copy of the result, must be within
+    rtol 1e-5 of f32(acc) * sx * sw evaluated in float64."""
+    import numpy as np
+
+    from oracle import oracle as O
+
+    M, N = x.shape[0], n_local * world
+    rows, cols = check_rows_cols(M, N, n_local, world)
+    rt = torch.tensor(rows, device=x.device)
+    xs = x[rt].cpu().numpy()
+    mn, mx = O.minmax_channel(xs, 0)
+    sx_o, zx_o = O.calculate_qparams(mn, mx, True, O.qint8)
+    xq_o = O.quantize(xs, sx_o, zx_o, O.qint8, ch_axis=0)
+    K = xs.shape[1]
+    ok = bool(np.array_equal(xq[rt][:, :K].cpu().numpy(), xq_o)) and bool(np.array_equal(sx[rt].cpu().numpy(), sx_o))
+    mine = cols[(cols >= rank * n_local) & (cols < (rank + 1) * n_local)] - rank * n_local
+    ct = torch.tensor(mine, device=x.device)
+    acc = ops.qlinear_i8(xq, wq, None, None, out_dtype=torch.int32)
+    acc_o = O.int_gemm_exact(xq_o, wq[ct][:, :K].cpu().numpy())
+    ok = ok and bool(np.array_equal(acc[rt][:, ct].cpu().numpy(), acc_o))
+    del acc
+    # fp32 outputs of the timed path: every rank's columns as they arrived in this rank's buffer
+    sw_all = [torch.empty_like(sw) for _ in range(world)]
+    wq_cols = []
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_gather(sw_all, sw)
+        for r in range(world):  # sampled weight rows of every shard, broadcast from their owner
+            sel = cols[(cols >= r * n_local) & (cols < (r + 1) * n_local)] - r * n_local
+            part = wq[torch.tensor(sel, device=x.device)][:, :K].contiguous() if r == rank else torch.empty(
+                (len(sel), K), dtype=torch.int8, device=x.device)
+            dist.broadcast(part, src=r)
+            wq_cols.append(part)
+    else:
+        sw_all, wq_cols = [sw], [wq[ct][:, :K]]
+    w_s = torch.cat(wq_cols).cpu().numpy()
+    sw_s = torch.cat(sw_all).cpu().numpy()[cols]
+    y_o = O.int_gemm_exact(xq_o, w_s).astype(np.float64) * sx_o.astype(np.float64)[:, None] * sw_s.astype(np.float64)[None, :]
+    got = result[rt][:, torch.tensor(cols, device=x.device)].cpu().numpy().astype(np.float64)
+    ok = ok and bool(np.allclose(got, y_o, rtol=1e-5, atol=1e-7))
+    return ok, {"rows": int(len(rows)), "cols": int(len(cols)), "cols_of_this_shard": int(len(mine))}
+
+
+def replica_companions(torch, ops, peaks, steps: int = 30) -> dict:
+    """The HBM-bound companions of the metric on THIS GPU (they do not shard: at N GPUs every rank
+    runs its own replica on independent data): the [8192, 8192] per-channel quantize / dequantize
+    (335.6 / 335.5 MB per call) and the decode-shaped weight-only SwiGLU MLP (176.3 MB per call)."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    hbm = peaks["hbm_gbs"]
+    g = torch.Generator(device=dev).manual_seed(20260922 + torch.cuda.current_device())
+    x = torch.randn(8192, 8192, device=dev, generator=g)
+    idx = torch.randint(0, x.numel(), (x.numel() // 1000,), device=dev, generator=g)
+    x.view(-1)[idx] *= 50.0
+    q, s, z = ops.dynamic_quantize_rows(x, True, -128, 127, True)
+    out = {}
+    for name, fn, nbytes in (("quantize_per_channel_GBs", lambda: ops.dynamic_quantize_rows(x, True, -128, 127, True),
+                              x.numel() * 5 + 8192 * 4),
+                             ("quantize_per_tensor_GBs", lambda: ops.dynamic_quantize_tensor(x, True, -128, 127, True, 1e-8, torch.int8),
+                              x.numel() * 9),
+                             ("dequantize_per_channel_GBs", lambda: ops.dequantize(q, s, z, ch_axis=0), x.numel() * 5)):
+        ms = time_loop(torch, fn, steps, 5)
+        out[name] = nbytes / ms / 1e6
+        out[name.replace("_GBs", "_frac_of_measured_hbm")] = nbytes / ms / 1e6 / hbm
+    del x, q, s, z
+    H, F = 4096, 14336
+    sets = []
+    for _ in range(3):
+        quantized = []
+        for (n, k) in ((F, H), (F, H), (H, F)):
+            w = torch.randn(n, k, device=dev, generator=g) * 0.02
+            quantized.append(ops.dynamic_quantize_rows(w, True, -128, 127, True)[:2])
+            del w
+        (wg, sg), (wu, su), (wd, sd) = quantized
+        sets.append(((ops.interleave_gate_up(wg, wu), ops.interleave_gate_up(sg, su)), (wd, sd)))
+        del quantized, wg, wu
+    nbytes = 3 * H * F + (2 * F + H) * 4
+    for batch in (1, 4, 16):
+        xb = torch.randn(batch, H, device=dev, generator=g).to(torch.bfloat16)
+        counter = [0]
+
+        def mlp_step():
+            (wgu, sgu), (wd, sd) = sets[counter[0] % 3]
+            counter[0] += 1
+            h = ops.wo_swiglu_s8(xb, wgu, sgu, overlap_previous=True)
+            return ops.wo_linear_s8(h, wd, sd, overlap_previous=True)
+
+        try:
+            ms = graph_time(torch, mlp_step, reps=6, replays=10)
+        except Exception:
+            ms = time_loop(torch, mlp_step, 60, 6)
+        out[f"decode_mlp_batch_{batch}_GBs"] = nbytes / ms / 1e6
+        out[f"decode_mlp_batch_{batch}_frac_of_measured_hbm"] = nbytes / ms / 1e6 / hbm
+    del sets
+    torch.cuda.empty_cache()
+    return out
+
+
+def shared_pinned_result(torch, world: int, rank: int, M: int, n_local: int):
+    """One host array [P, M, N/P] fp32 shared by the ranks (POSIX shared memory, page-locked in every
+    process), rank r owning block r; falls back to a private pinned block per rank."""
+    path = f"/dev/shm/lucid_b200_bench_{os.environ.get('MASTER_PORT', '0')}_{M}_{n_local}_{world}"
+    try:
+        import torch.distributed as dist
+
+        total = world * M * n_local
+        if rank == 0:
+            whole = torch.from_file(path, shared=True, size=total, dtype=torch.float32)
+        if world > 1:
+            dist.barrier()
+        if rank != 0:
+            whole = torch.from_file(path, shared=True, size=total, dtype=torch.float32)
+        rc = torch.cuda.cudart().cudaHostRegister(whole.data_ptr(), total * 4, 0)
+        if int(rc) != 0:
+            raise RuntimeError(f"cudaHostRegister: {rc}")
+        if world > 1:
+            dist.barrier()
+        if rank == 0:
+            os.unlink(path)
+        return whole.view(world, M, n_local)[rank], "one [P, M, N/P] host array in shared memory, rank r writes block r", whole
+    except Exception as e:  # noqa: BLE001
+        return (torch.empty((M, n_local), dtype=torch.float32).pin_memory(),
+                f"a private pinned [M, N/P] block per rank (shared mapping unavailable: {repr(e)[:80]})", None)
+
+
 def run_ours(args) -> int:
     import torch
     import torch.distributed as dist
@@ -562,55 +799,59 @@ def run_ours(args) -> int:
     torch.cuda.empty_cache()
     wq, _ = qlin._cache.get(qlin.weight_int8)
     sw = qlin.weight_scale
-    # ---- output exchange at N > 1 ------------------------------------------------------
-    # "fused": every rank's GEMM epilogue stores its column slice straight into every rank's
-    # [M, N] result (peer stores over NVLink through symmetric memory), so the all-gather is
-    # part of the kernel; "nccl": local shard + ncclAllGather, the plain baseline.
-    gathered = None
-    gather_mode, gather_note, out_ptrs, symm_hdl, full = "none", "", None, None, None
-    if world > 1:
-        gather_mode = args.gather
-        if gather_mode in ("auto", "fused"):
-            try:
-                import torch.distributed._symmetric_memory as symm
-
-                full = symm.empty((M, N), dtype=torch.float32, device=dev)
-                symm_hdl = symm.rendezvous(full, dist.group.WORLD)
-                order = [(rank + i) % world for i in range(world)]  # own buffer first, peers rotated
-                out_ptrs = [int(symm_hdl.buffer_ptrs[r]) + rank * n_local * 4 for r in order]
-                gather_mode = "fused"
-            except Exception as e:  # reported in the JSON line, never silent
-                if args.gather == "fused":
-                    raise
-                gather_mode, gather_note = "nccl", f"symmetric memory unavailable: {repr(e)[:120]}"
-        if gather_mode == "nccl":
-            gathered = torch.empty((world, M, n_local), dtype=torch.float32, device=dev)
-
-    gemm_ms = []
-
-    def step(record: bool = False):
-        xq, sx, _ = ops.dynamic_quantize_rows(x, True, -128, 127, True, 1e-8, torch.int8, pad_rows_to_16=True)
-        if record:
-            a, b = _events(torch)
-            a.record()
-        if gather_mode == "fused":
-            ops.qlinear_i8_into(xq, wq, sx, sw, out_ptrs, N)
-            y = full
-        else:
-            y = ops.qlinear_i8(xq, wq, sx, sw)
-        if record:
-            b.record()
-            gemm_ms.append((a, b))
-        if gather_mode == "fused":
-            symm_hdl.barrier()  # every rank's slices have landed in this rank's result
-        elif gather_mode == "nccl":
-            dist.all_gather_into_tensor(gathered.view(-1), y.view(-1))
-        return y
 
     def sync_all():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def quantize_x():
+        return ops.dynamic_quantize_rows(x, True, -128, 127, True, 1e-8, torch.int8, pad_rows_to_16=True)
+
+    # ---- the step -----------------------------------------------------------------------------
+    # N = 1: per-token quantize + GEMM.  N > 1: the column-parallel module (quantize, barrier, GEMM
+    # with the exchange mode's stores / copies, barrier); every rank ends with the whole [M, N].
+    gemm_ms, cp, mode, mode_ms, mode_note = [], None, "none", {}, ""
+    if world > 1:
+        from lucid_b200.nn.quantized.column_parallel import ColumnParallelLinear
+
+        cp = ColumnParallelLinear(qlin, N, gather="fused")
+        candidates = ["fused", "copy", "multimem"] if args.gather == "auto" else [args.gather]
+        for cand in candidates:  # a few untimed-by-the-metric steps of each way to exchange; keep the fastest
+            cp.gather = cand
+            try:
+                for _ in range(2):
+                    cp(x)
+                sync_all()
+                t = torch.tensor([time_loop(torch, lambda: cp(x), 3, 0)], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                cp.check()
+                mode_ms[cand] = float(t.item())
+            except Exception as e:  # noqa: BLE001  (reported in the line, never silent)
+                mode_note += f"{cand}: {repr(e)[:100]}; "
+                failed = torch.tensor([1.0], device=dev)
+            else:
+                failed = torch.tensor([0.0], device=dev)
+            dist.all_reduce(failed, op=dist.ReduceOp.MAX)  # a mode must work on every rank
+            if failed.item() and cand in mode_ms:
+                del mode_ms[cand]
+        if not mode_ms:
+            raise SystemExit(f"no exchange mode works: {mode_note}")
+        mode = min(mode_ms, key=mode_ms.get)
+        cp.gather = mode
+
+    def step(record: bool = False):
+        if world > 1:
+            return cp(x)
+        xq, sx, _ = quantize_x()
+        if record:
+            a, b = _events(torch)
+            a.record()
+        y = ops.qlinear_i8(xq, wq, sx, sw)
+        if record:
+            b.record()
+            gemm_ms.append((a, b))
+        return y
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -620,60 +861,101 @@ def run_ours(args) -> int:
         sync_all()
         e0.record()
         for _ in range(args.steps):
-            step(record=True)
+            result = step(record=True)
         e1.record()
         sync_all()
     total_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     ms_per_step = float(total_ms.item()) / args.steps
-    gemm_avg_ms = sum(a.elapsed_time(b) for a, b in gemm_ms) / len(gemm_ms)
     value = 2.0 * M * N * K / ms_per_step / 1e9
+    if cp is not None:
+        cp.check()
 
-    # ---- N > 1: check the exchange, and time the GEMM phase without it ------------------
-    exchange_verified, gemm_only_ms = None, None
-    cp_module = None
-    if world > 1:
-        from lucid_b200.nn.quantized.column_parallel import ColumnParallelLinear
-
-        xq, sx, _ = ops.dynamic_quantize_rows(x, True, -128, 127, True, 1e-8, torch.int8, pad_rows_to_16=True)
-        y_local = ops.qlinear_i8(xq, wq, sx, sw)
-        result = step()
-        sync_all()
-        if gather_mode == "fused":
-            mine = result[:, rank * n_local:(rank + 1) * n_local]
-            whole = result
-        else:
-            mine = gathered[rank]
-            whole = gathered
-        ok_local = bool(torch.equal(mine, y_local))
-        checksum = whole.view(torch.int32).sum(dtype=torch.int64).reshape(1)
-        sums = [torch.zeros_like(checksum) for _ in range(world)]
-        dist.all_gather(sums, checksum)
-        flags = torch.tensor([int(ok_local)], device=dev)
-        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
-        exchange_verified = bool(flags.item()) and all(int(v) == int(sums[0]) for v in sums)
+    # ---- the GEMM launch alone (the kernel the roofline is about) ---------------------------------
+    xq, sx, _ = quantize_x()
+    if world == 1:
+        gemm_avg_ms = sum(a.elapsed_time(b) for a, b in gemm_ms) / len(gemm_ms)
+    else:  # same shard GEMM writing only the local buffer, timed on its own: max over ranks
         t = torch.tensor([time_loop(torch, lambda: ops.qlinear_i8(xq, wq, sx, sw), 5, 2)], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        gemm_only_ms = float(t.item())
-        del y_local
-        cp_module = ColumnParallelLinear(qlin, N, gather="fused" if gather_mode == "fused" else "nccl")
+        gemm_avg_ms = float(t.item())
 
-    # ---- end to end through the module API with host buffers --------------------------
+    # ---- parity at full size, outside the timed region -------------------------------------------
+    try:
+        checked, check_shape = oracle_check(torch, ops, x, xq, sx, wq, sw, result, rank, world, n_local)
+    except Exception as e:  # noqa: BLE001
+        checked, check_shape = False, {"error": repr(e)[:200]}
+    flag = torch.tensor([int(checked)], device=dev)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        # every rank's copy of the gathered result holds the same bits
+        checksum = result.view(torch.int32).sum(dtype=torch.int64).reshape(1)
+        sums = [torch.zeros_like(checksum) for _ in range(world)]
+        dist.all_gather(sums, checksum)
+        identical = all(int(v) == int(sums[0]) for v in sums)
+    else:
+        identical = None
+    oracle_checked = bool(flag.item())
+    del result
+
+    # ---- sustained figure (N = 1): the same step for seconds, clocks sampled throughout -----------
+    sustained = None
+    if world == 1 and args.sustain_seconds > 0:
+        n_sus = max(50, int(args.sustain_seconds * 1e3 / ms_per_step))
+        with ClockSampler(local) as sclk:
+            s0, s1 = _events(torch)
+            torch.cuda.synchronize()
+            s0.record()
+            for _ in range(n_sus):
+                step()
+            s1.record()
+            torch.cuda.synchronize()
+        sus_ms = s0.elapsed_time(s1) / n_sus
+        ck = sclk.summary()
+        sus_tops = 2.0 * M * N * K / sus_ms / 1e9
+        sustained = {"seconds": s0.elapsed_time(s1) / 1e3, "steps": n_sus, "ms_per_step": sus_ms, "TOPS": sus_tops,
+                     "sm_mhz_median": ck["sm_mhz"], "sw_power_cap_share": ck["sw_power_cap_share"],
+                     "reasons": ck["reasons"],
+                     "TOPS_per_GHz": sus_tops / (ck["sm_mhz"] / 1e3) if ck["sm_mhz"] else None,
+                     "peak": 2.0 * peaks["bf16_tflops_sustained"],
+                     "frac": sus_tops / (2.0 * peaks["bf16_tflops_sustained"]),
+                     "peak_source": f"2 x bf16_tflops_sustained ({peaks['source']}): whole step (quantize + GEMM) against "
+                                    "the driver's seconds-long cuBLAS figure"}
+
+    # ---- companions: every rank runs its own replica of the HBM-bound configurations ---------------
+    companions = None
+    if not args.no_extras:
+        mine = replica_companions(torch, ops, peaks)
+        keys = sorted(mine)
+        vec = torch.tensor([mine[k] for k in keys], device=dev, dtype=torch.float64)
+        if world > 1:
+            allv = [torch.zeros_like(vec) for _ in range(world)]
+            dist.all_gather(allv, vec)
+            stack = torch.stack(allv)
+        else:
+            stack = vec[None]
+        companions = {"scaling": "replicas only: these configurations do not shard; every GPU runs its own copy on its "
+                                 "own data, no exchange", "replicas": world}
+        for i, k in enumerate(keys):
+            col = stack[:, i]
+            if k.endswith("_GBs"):
+                companions[k] = {"per_replica_min": float(col.min()), "per_replica_mean": float(col.mean()),
+                                 "aggregate": float(col.sum())}
+            else:
+                companions[k] = float(col.min())
+
+    # ---- end to end through the module API with host buffers --------------------------------------
+    # Every rank streams ITS column shard: x chunks host -> device, the shard's Linear, result chunks
+    # device -> its block of the host result; P PCIe links work in parallel and nothing crosses NVLink.
     from lucid_b200.nn.quantized.streaming import forward_from_host
 
     x_host = x.cpu().pin_memory()
-    y_host = torch.empty((M, N), dtype=torch.float32).pin_memory() if rank == 0 else None
-    x_dev = torch.empty_like(x)
+    y_host, y_host_note, keep_alive = (torch.empty((M, N), dtype=torch.float32).pin_memory(), "one pinned [M, N] array", None) \
+        if world == 1 else shared_pinned_result(torch, world, rank, M, n_local)
 
     def e2e_step():
-        if world == 1:  # chunked: H2D of chunk i+1, layer on chunk i and D2H of chunk i-1 overlap
-            forward_from_host(qlin, x_host, y_host, chunk_rows=2048)
-            return
-        x_dev.copy_(x_host, non_blocking=True)
-        y = cp_module(x_dev)
-        if rank == 0:
-            y_host.copy_(y, non_blocking=True)
+        forward_from_host(qlin, x_host, y_host, chunk_rows=2048)
 
     e2e_steps = max(3, min(args.steps, 10))
     for _ in range(2):
@@ -693,46 +975,50 @@ def run_ours(args) -> int:
     if rank == 0:
         int8_peak = 2.0 * peaks["bf16_tflops"]
         achieved = 2.0 * M * n_local * K / gemm_avg_ms / 1e9
+        exchange_bytes = (world - 1) * M * n_local * 4
         line = {
             "metric": "int8_qlinear_tops", "value": value, "unit": "TOPS", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "s8xs8->s32",
-            "data": "synthetic",
-            "config": {"workload": "prefill_qlinear_16384x28672x8192_per_token_int8", "M": M, "N": N, "K": K,
-                       "activation_quant": "dynamic per-token symmetric int8 (absmax/127.5, [-128,127])",
-                       "weight_quant": "per-output-channel symmetric int8", "output": "fp32",
-                       "parallelism": f"column-parallel x{world}" + (
-                           "" if world == 1 else " + all-gather fused into the GEMM epilogue (peer stores)"
-                           if gather_mode == "fused" else " + NCCL all-gather"),
-                       "gather": gather_mode, "gather_note": gather_note,
-                       "l2": "inputs exceed L2 (x 537 MB, W 235 MB, y 1879 MB vs 126 MB)"},
+            "data": "synthetic", "oracle_checked": oracle_checked,
+            "config": {**workload_config(),
+                       "parallelism": f"column-parallel x{world}" + ("" if world == 1 else f" + all-gather ({mode})"),
+                       "gather": mode, "l2": "inputs exceed L2 (x 537 MB, W 235 MB, y 1879 MB vs 126 MB)",
+                       "oracle_check": check_shape},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
                          "frac": achieved / int8_peak,
-                         # dram__bytes_read+write of a 1/16-size launch of the same kernel (same K and tile
-                         # shape: profiles/qlinear_i8_pair_gemm_4096x7168x8192.md) scaled by the ops ratio
-                         "traffic": 3.41e9 if world == 1 else None,
+                         "traffic": gemm_dram_traffic(2.0 * M * n_local * K),
                          "kernel": "qlinear_i8_pair_kernel", "kernel_ms": gemm_avg_ms,
                          "peak_source": f"2 x bf16_tflops ({peaks['source']}, burst): tcgen05 issues dense int8 at "
                                         "twice the bf16 rate; no int8 figure is measured by the driver",
                          "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS},
             "e2e": {"value": 2.0 * M * N * K / e2e_ms_per_step / 1e9, "unit": "TOPS",
-                    "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4,
-                    "ms_per_step": e2e_ms_per_step, "api": "lucid_b200.nn.quantized.streaming.forward_from_host(dynamic.Linear, ...), 2048-row chunks" if world == 1 else
-                           "lucid_b200.nn.quantized.column_parallel.ColumnParallelLinear.forward"},
-            "gpu_launches": args.steps * 2,
+                    "h2d_bytes_per_step": M * K * 4 * world, "d2h_bytes_per_step": M * N * 4,
+                    "ms_per_step": e2e_ms_per_step,
+                    "api": "lucid_b200.nn.quantized.streaming.forward_from_host(dynamic.Linear shard, ...), 2048-row chunks, "
+                           "one call per rank on its own column shard",
+                    "result": y_host_note},
+            "gpu_launches": args.steps * (2 if world == 1 else 4),
             "exchange": None if world == 1 else {
-                "mode": gather_mode, "bytes_out_per_gpu": (world - 1) * M * n_local * 4,
-                "GB/s_out_per_gpu_during_gemm_kernel": (world - 1) * M * n_local * 4 / gemm_avg_ms / 1e6,
-                "nvlink_peer_copy_peak_GB/s": 770.0, "verified_bit_identical_on_all_ranks": exchange_verified,
-                "gemm_phase_only": {"ms": gemm_only_ms, "aggregate_TOPS": 2.0 * M * N * K / gemm_only_ms / 1e9,
-                                    "note": "same shard GEMM writing only the local buffer (no exchange), max over ranks"},
-                "note": "fused: the GEMM kernel's duration includes the peer stores, so at large N it is "
-                        "bound by NVLink, not by the tensor cores" if gather_mode == "fused" else
-                        "nccl: the exchange runs after the GEMM kernel"},
+                "mode": mode, "ms_per_step_by_mode": mode_ms, "mode_note": mode_note,
+                "bytes_in_per_gpu": exchange_bytes,
+                "GB/s_in_per_gpu": exchange_bytes / ms_per_step / 1e6,
+                "nvlink_peer_copy_measured_GB/s": 770.0, "nvlink_nominal_GB/s": 900.0,
+                "identical_on_all_ranks": identical,
+                "gemm_phase_ms": gemm_avg_ms,
+                "gemm_phase_aggregate_TOPS": 2.0 * M * N * K / gemm_avg_ms / 1e9,
+                "gemm_phase_efficiency_note": "T1_kernel / (P * T_P,gemm): divide the N = 1 line's roofline.kernel_ms by "
+                                              "P times gemm_phase_ms",
+                "note": "every GPU must receive (P-1)/P of the fp32 [M, N] result: the step is bound by NVLink, "
+                        "not by the tensor cores"},
             "clocks": clocks.summary(),
         }
+        if sustained is not None:
+            line["sustained"] = sustained
+        if companions is not None:
+            line["companions"] = companions
         if world == 1:
-            del x_host, y_host, x_dev
+            del x_host, y_host
             torch.cuda.empty_cache()
         if world == 1 and not args.no_extras:
             try:  # library comparator (cuBLASLt through torch), for context only
@@ -742,7 +1028,9 @@ def run_ours(args) -> int:
             except Exception as e:
                 line["library_int8_gemm_tops_8192x8192x8192"] = f"unavailable: {repr(e)[:80]}"
             line["extras"] = extras_single_gpu(torch, ops, peaks)
-            line["cpu_baseline"] = {k: v for k, v in cpu_prefill_reference(3, 1).items() if k != "seconds_per_sample"}
+            use_all_host_threads()
+            line["cpu_baseline"] = {k: v for k, v in cpu_prefill_reference(3, 1, budget_s=30.0).items()
+                                    if k not in ("seconds_per_sample", "wall_budget_s", "iterations_asked")}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -762,8 +1050,10 @@ def main() -> int:
                     help="run a small fixed case of one kernel (gemm, quantize_rows, quantize_tensor, "
                          "dequantize, quantize_given_scale, histc, merge, embedding, embedding_bag, gemm_small, gemm_shortk, wo_gemv) for a profiler capture; prints no bench line")
     ap.add_argument("--profile-batch", default=4)
-    ap.add_argument("--gather", choices=("auto", "fused", "nccl"), default="auto",
-                    help="N > 1: how output shards are exchanged (auto = fused if symmetric memory works)")
+    ap.add_argument("--gather", choices=("auto", "fused", "multimem", "copy", "nccl"), default="auto",
+                    help="N > 1: how output shards are exchanged (auto = time fused / copy / multimem once, keep the fastest)")
+    ap.add_argument("--sustain-seconds", type=float, default=2.5,
+                    help="N = 1: length of the sustained loop that follows the timed steps (0 = skip)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -773,7 +1063,7 @@ def main() -> int:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29531", os.path.abspath(__file__),
                "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup),
-               "--gather", args.gather]
+               "--gather", args.gather] + (["--no-extras"] if args.no_extras else [])
         return subprocess.call(cmd)
     return run_ours(args)
 

@@ -248,12 +248,38 @@ int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_t lda, cons
  * spins without a bound; the next ordinary launch is unaffected. */
 #define LC_QLINEAR_WAIT_TEST 256
 
+/* Bit of `variant` for lc_qlinear_i8_multi with n_out == 1: host_outs[0] is a MULTICAST address of
+ * the result buffer (NVLink SHARP / NVLS: one virtual address bound to the same buffer on every
+ * GPU of the group).  Every output segment then leaves the GPU once, as a multimem.st, and the
+ * NVSwitch writes it into every GPU's copy, this GPU's included: the all-gather of a
+ * column-parallel Linear with one store per tile instead of one per peer.  fp32 output only. */
+#define LC_QLINEAR_MULTICAST_OUT 512
+
 /* Reads the device status word of the kernels above on the host: synchronises `stream`, returns
  * LC_OK when the word is 0 and LC_ERR_TIMEOUT (with the role that gave up in lc_last_error) when a
  * bounded device-side wait ran out; clear != 0 resets the word.  The reference's engine reports
  * failures as exceptions from a synchronous call (lucid/_C/ops/quantized/QuantizedMatmul.cpp:42-45);
  * this is the asynchronous counterpart. */
 int32_t lc_qlinear_check_status(const int32_t* status, int32_t clear, void* stream);
+
+/* ---- multi-GPU plumbing of the column-parallel Linear (no counterpart in the reference) ----
+ * Barrier between the `world` (<= 16) ranks of one node, one rank per GPU.  host_flags is a HOST
+ * array of `world` device pointers: entry r is rank r's flag array (world x uint32, zero-filled
+ * once, in memory every rank can store to: peer-mapped or symmetric memory) as mapped in this
+ * process.  The kernel publishes `epoch` in this rank's slot of every rank's array after a
+ * system-wide fence (so that output tiles this GPU stored into its peers' buffers are visible
+ * first) and waits until every rank has published an epoch >= `epoch` in this rank's array.  Use a
+ * new, larger epoch for every barrier.  The wait is BOUNDED: after wait_cycles SM cycles the kernel
+ * writes 4 into *status (device int32, may be NULL) and returns, so a rank that died or never
+ * joined cannot hang this GPU; lc_qlinear_check_status reports it as LC_ERR_TIMEOUT. */
+int32_t lc_peer_barrier(void* const* host_flags, int32_t rank, int32_t world, uint32_t epoch,
+                        int64_t wait_cycles, int32_t* status, void* stream);
+
+/* rows x width_bytes from src (row pitch src_pitch bytes) to dst (row pitch dst_pitch), device to
+ * device on the copy engines (cudaMemcpy2DAsync); either side may be a peer GPU's memory mapped
+ * into this process.  Moves a rank's column block of a row-major result into a peer's copy. */
+int32_t lc_copy_2d_async(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch,
+                         int64_t width_bytes, int64_t rows, void* stream);
 
 /* row sums of an int8 matrix as int32 (the zero-point correction term) */
 int32_t lc_rowsum_s8(const int8_t* b, int64_t rows, int64_t cols, int64_t ldb, int32_t* out,

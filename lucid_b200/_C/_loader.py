@@ -19,6 +19,7 @@ LC_OK = 0
 LC_ERR_INVALID_ARG, LC_ERR_UNSUPPORTED, LC_ERR_CUDA, LC_ERR_TIMEOUT, LC_ERR_WORKSPACE = -1, -2, -3, -4, -5
 LC_F32, LC_BF16, LC_F16, LC_S8, LC_U8, LC_S16, LC_S32 = range(7)
 LC_QLINEAR_WAIT_TEST = 256
+LC_QLINEAR_MULTICAST_OUT = 512
 
 
 class LucidCudaError(RuntimeError):
@@ -64,6 +65,8 @@ SIGNATURES = {
     "lc_qlinear_i8_multi": (_i32, [_p, _i32, _i64, _p, _i64, _i64, _i64, _i64, _p, _i32, _p, _p, _p, _p,
                                    C.POINTER(C.c_void_p), _i32, _i32, _i64, _p, _i32, _p]),
     "lc_qlinear_check_status": (_i32, [_p, _i32, _p]),
+    "lc_peer_barrier": (_i32, [C.POINTER(C.c_void_p), _i32, _i32, C.c_uint32, _i64, _p, _p]),
+    "lc_copy_2d_async": (_i32, [_p, _i64, _p, _i64, _i64, _i64, _p]),
     "lc_rowsum_s8": (_i32, [_p, _i64, _i64, _i64, _p, _p]),
     "lc_wo_gemm_16": (_i32, [_p, _i32, _i32, _i64, _p, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _i32, _p, _p, _i32, _i32,
                              _p, _i32, _i64, _p, _i32, _p]),

@@ -21,7 +21,7 @@ OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(HERE, "liblucid_cuda.so")
 
 SOURCES = ["api.cu", "quant_kernels.cu", "hist_kernels.cu", "embed_kernels.cu", "qlinear_tcgen05.cu", "wo_kernels.cu",
-           "wo_prep_kernels.cu"]
+           "wo_prep_kernels.cu", "peer_kernels.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

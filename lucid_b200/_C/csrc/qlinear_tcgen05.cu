@@ -83,6 +83,7 @@ struct Params {
   int out_vec;          // rows of `out` allow 16-byte stores
   int fast_f32;         // 0, or 1 + (zero-point correction) + 2 * (bias): the compiled-in fp32 epilogue applies
   int32_t* status;
+  int multicast;        // outs[0] is a multicast address: stores go out as multimem.st and the switch replicates them
   int wait_test;        // test hook: the producer role issues nothing and every wait gives up after a few thousand cycles
   // weight-only instantiations (kModeF16, kModeDigits) only
   int64_t rows_out;     // kModeDigits: rows of the output (M counts digit-plane rows, 4 per output row)
@@ -300,7 +301,13 @@ __device__ __forceinline__ void store_staged(const Params& p, const uint32_t* st
       const uint4 w = *reinterpret_cast<const uint4*>(stg + rloc * STG_PITCH + sub * 4);
       if (row < p.M && col < p.N) {
         if (p.n_out == 1 && p.out_vec && col + 4 <= p.N) {
-          *reinterpret_cast<uint4*>(static_cast<uint32_t*>(p.outs[0]) + row * p.ldo + col) = w;
+          uint32_t* o = static_cast<uint32_t*>(p.outs[0]) + row * p.ldo + col;
+          if (p.multicast)  // one store; NVSwitch writes it into every GPU's copy of the buffer
+            asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(__uint_as_float(w.x)),
+                         "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
+                         : "memory");
+          else
+            *reinterpret_cast<uint4*>(o) = w;
           continue;
         }
         for (int d = 0; d < p.n_out; ++d) {
@@ -1174,8 +1181,12 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
   // bit 8 of `variant` is the wait test: the producer role issues no loads and every wait gives up
   // after a few thousand cycles, so the kernel records a code in `status` and returns
   const int wait_test = (variant & LC_QLINEAR_WAIT_TEST) ? 1 : 0;
-  variant &= ~LC_QLINEAR_WAIT_TEST;
+  const int multicast = (variant & LC_QLINEAR_MULTICAST_OUT) ? 1 : 0;
+  variant &= ~(LC_QLINEAR_WAIT_TEST | LC_QLINEAR_MULTICAST_OUT);
   if (wait_test && !status) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: the wait test needs a status word");
+  if (multicast && (n_out != 1 || out_dtype != LC_F32 || N % 4 || (ldo * 4) % 16 || !aligned(host_outs[0], 16)))
+    return fail(LC_ERR_UNSUPPORTED, "qlinear_i8: a multicast output needs one fp32 buffer, N a multiple of 4 and "
+                                    "16-byte aligned rows");
   if (variant < 0 || variant > 2) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: variant must be 0, 1 or 2");
   if (M < 0 || N < 0 || K <= 0) return fail(LC_ERR_INVALID_ARG, "qlinear_i8: bad shape");
   if (M == 0 || N == 0) return LC_OK;
@@ -1211,7 +1222,8 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
   for (int i = 0; i < n_out; ++i)
     if (!aligned(host_outs[i], 16)) p.out_vec = 0;
   p.status = status;
-  p.fast_f32 = (out_dtype == LC_F32 && sw && n_out == 1 && p.out_vec) ? 1 + (zx ? 1 : 0) + (bias ? 2 : 0) : 0;
+  p.fast_f32 = (out_dtype == LC_F32 && sw && n_out == 1 && p.out_vec && !multicast) ? 1 + (zx ? 1 : 0) + (bias ? 2 : 0) : 0;
+  p.multicast = multicast;
 
   p.wait_test = wait_test;
   p.rows_out = M;
@@ -1237,9 +1249,10 @@ extern "C" int32_t lc_qlinear_check_status(const int32_t* status, int32_t clear,
     err = cudaMemsetAsync(const_cast<int32_t*>(status), 0, sizeof(code), st);
   if (err != cudaSuccess) return fail(LC_ERR_CUDA, "qlinear_check_status: %s", cudaGetErrorString(err));
   if (code == 0) return LC_OK;
-  static const char* const kRole[] = {"", "the TMA producer", "the MMA issuer", "an epilogue warp"};
+  static const char* const kRole[] = {"", "the TMA producer", "the MMA issuer", "an epilogue warp",
+                                      "the barrier between ranks (a peer never arrived)"};
   return fail(LC_ERR_TIMEOUT, "a bounded device-side wait of %s ran out (status %d); the kernel returned early and "
-                              "its output is incomplete", code >= 1 && code <= 3 ? kRole[code] : "a kernel role", code);
+                              "its output is incomplete", code >= 1 && code <= 4 ? kRole[code] : "a kernel role", code);
 }
 
 // Weight-only Linear on the tensor cores (see the header of this file).
@@ -1293,6 +1306,7 @@ extern "C" int32_t lc_wo_gemm_16(const void* a, int32_t a_dtype, int32_t n_terms
   p.out_vec = ((ldo * esz) % 16 == 0 && aligned(out, 16)) ? 1 : 0;
   p.fast_f32 = 0;
   p.status = status;
+  p.multicast = 0;
   p.wait_test = wait_test;
   p.rows_out = M;
   p.kb_wrap = static_cast<int>(kblocks);
@@ -1353,6 +1367,7 @@ extern "C" int32_t lc_wo_gemm_digits(const int8_t* digits, int64_t ldd, const fl
   p.out_vec = 0;
   p.fast_f32 = 0;
   p.status = status;
+  p.multicast = 0;
   p.wait_test = wait_test;
   p.rows_out = M;
   p.kb_wrap = 1;

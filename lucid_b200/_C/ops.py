@@ -11,7 +11,7 @@ import math
 
 import torch
 
-from ._loader import (LC_BF16, LC_F16, LC_F32, LC_QLINEAR_WAIT_TEST, LC_S8, LC_S16, LC_S32, LC_U8, LucidCudaError, check,
+from ._loader import (LC_BF16, LC_F16, LC_F32, LC_QLINEAR_MULTICAST_OUT, LC_QLINEAR_WAIT_TEST, LC_S8, LC_S16, LC_S32, LC_U8, LucidCudaError, check,
                       lib)
 
 _DTYPE = {
@@ -409,11 +409,13 @@ def qlinear_i8(a, b, sx, sw, bias=None, zx=None, wsum=None, out_dtype: torch.dty
 
 
 def qlinear_i8_into(a, b, sx, sw, out_ptrs, ldo: int, out_dtype: torch.dtype = torch.float32, bias=None, zx=None,
-                    wsum=None, status: torch.Tensor | None = None, variant: int = 0) -> None:
+                    wsum=None, status: torch.Tensor | None = None, variant: int = 0, multicast: bool = False) -> None:
     """:func:`qlinear_i8` writing each output tile to every buffer in ``out_ptrs`` (1..8 raw
     device addresses, row pitch ``ldo`` elements): the caller's own buffer and, for a
     column-parallel Linear, the same column slice of every peer GPU's result buffer, so the
-    all-gather of the shards happens inside the GEMM's epilogue."""
+    all-gather of the shards happens inside the GEMM's epilogue.  With ``multicast`` the single
+    entry of ``out_ptrs`` is a multicast address: each tile leaves the GPU once (``multimem.st``)
+    and the NVSwitch writes it into every GPU's buffer."""
     import ctypes
 
     dev = _need_cuda(a, b, sx, sw, bias, zx, wsum, status)
@@ -432,7 +434,33 @@ def qlinear_i8_into(a, b, sx, sw, out_ptrs, ldo: int, out_dtype: torch.dtype = t
         check(lib.lc_qlinear_i8_multi(a.data_ptr(), int(a.dtype == torch.uint8), a.stride(0), b.data_ptr(),
                                       b.stride(0), M, N, K, _ptr(sx), per_row, _ptr(zx_c), _ptr(wsum_c),
                                       _ptr(sw_c), _ptr(bias_c), arr, len(out_ptrs), _lc_dtype(out_dtype),
-                                      int(ldo), _ptr(status), int(variant), _stream(dev)))
+                                      int(ldo), _ptr(status), int(variant) | (LC_QLINEAR_MULTICAST_OUT if multicast else 0),
+                                      _stream(dev)))
+
+
+def peer_barrier(flag_ptrs, rank: int, epoch: int, status: torch.Tensor | None = None,
+                 wait_cycles: int = 2_000_000_000, device: torch.device | None = None) -> None:
+    """Barrier between the ranks of one node on the current stream of ``device``: ``flag_ptrs[r]`` is
+    the address, in this process, of rank r's flag array (one uint32 per rank, zero-filled once).
+    ``epoch`` must grow with every call.  The device-side wait gives up after ``wait_cycles`` SM
+    cycles (about a second by default) and records code 4 in ``status``."""
+    import ctypes
+
+    dev = device if device is not None else (status.device if status is not None else torch.device(
+        "cuda", torch.cuda.current_device()))
+    arr = (ctypes.c_void_p * len(flag_ptrs))(*[int(p) for p in flag_ptrs])
+    with _on(dev):
+        check(lib.lc_peer_barrier(arr, int(rank), len(flag_ptrs), int(epoch) & 0xFFFFFFFF, int(wait_cycles), _ptr(status),
+                                  _stream(dev)))
+
+
+def copy_2d(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, width_bytes: int, rows: int,
+            device: torch.device) -> None:
+    """``rows`` x ``width_bytes`` between two device buffers (either may belong to a peer GPU) on the
+    copy engines, on the current stream of ``device``."""
+    with _on(device):
+        check(lib.lc_copy_2d_async(int(dst_ptr), int(dst_pitch), int(src_ptr), int(src_pitch), int(width_bytes), int(rows),
+                                   _stream(device)))
 
 
 def qlinear_check_status(status: torch.Tensor, clear: bool = True) -> None:
