@@ -87,7 +87,9 @@ int32_t lc_observe_tensor_f32(const float* x, int64_t n, float* min_out, float* 
  *  - at most lc_observe_tensor_static_max_elems() (2^30) elements per call; larger inputs
  *    are rejected with LC_ERR_UNSUPPORTED -- use the workspace variant for those;
  *  - the first call on each device looks up the array's device address (with that device
- *    current); make that first call before starting any stream capture;
+ *    current); make that first call before starting any stream capture.  The address is cached
+ *    while the device's primary context lives; after a context teardown (cudaDeviceReset) the
+ *    next call notices the stale address and looks it up again;
  *  - all calls on a device share the one array: two calls whose kernels can overlap on the
  *    GPU (different streams, no dependency) race on it.  Serialise them. */
 int64_t lc_observe_tensor_static_max_elems(void);

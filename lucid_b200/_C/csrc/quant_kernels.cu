@@ -875,22 +875,30 @@ static __device__ __align__(256) unsigned char g_observe_static_scratch[sizeof(T
 
 constexpr int64_t kObserveStaticMaxElems = int64_t{1} << 30;
 
-static int32_t static_scratch_address(TensorObserveScratch** out) {
+// The address is looked up under a per-device mutex and cached only when the lookup succeeded, so
+// a failed first call (no context yet, a transient error) is retried by the next one.  The cached
+// address belongs to the device's primary context: `refresh` drops it, which the entry point asks
+// for when the first use of the address fails (the context was torn down and rebuilt, e.g. by
+// cudaDeviceReset, and the old address is stale).
+static int32_t static_scratch_address(TensorObserveScratch** out, bool refresh) {
   constexpr int kMaxDevices = 64;
-  static std::once_flag flags[kMaxDevices];
-  static cudaError_t results[kMaxDevices];
+  static std::mutex locks[kMaxDevices];
   static void* addrs[kMaxDevices];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return fail(LC_ERR_CUDA, "observe_tensor_static: no current CUDA device");
-  std::call_once(flags[dev], [dev]() {
+  std::lock_guard<std::mutex> hold(locks[dev]);
+  if (refresh) addrs[dev] = nullptr;
+  if (addrs[dev] == nullptr) {
     void* p = nullptr;
-    results[dev] = cudaGetSymbolAddress(&p, g_observe_static_scratch);
+    const cudaError_t err = cudaGetSymbolAddress(&p, g_observe_static_scratch);
+    if (err != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return fail(LC_ERR_CUDA, "observe_tensor_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+                  cudaGetErrorString(err));
+    }
     addrs[dev] = p;
-  });
-  if (results[dev] != cudaSuccess || addrs[dev] == nullptr)
-    return fail(LC_ERR_CUDA, "observe_tensor_static: cudaGetSymbolAddress failed on device %d: %s", dev,
-                cudaGetErrorString(results[dev]));
+  }
   *out = static_cast<TensorObserveScratch*>(addrs[dev]);
   return LC_OK;
 }
@@ -913,11 +921,16 @@ extern "C" int32_t lc_observe_tensor_static_f32(const float* x, int64_t n, float
                 "use lc_observe_tensor_f32 with a caller workspace",
                 (long long)n, (long long)kObserveStaticMaxElems);
   TensorObserveScratch* ws = nullptr;
-  if (int32_t rc = static_scratch_address(&ws)) return rc;
+  if (int32_t rc = static_scratch_address(&ws, false)) return rc;
   cudaStream_t st = as_stream(stream);
   // the array keeps whatever the previous call left: the ticket has to start at zero
-  if (cudaMemsetAsync(ws, 0, 16, st) != cudaSuccess)
-    return fail(LC_ERR_CUDA, "observe_tensor_static: %s", cudaGetErrorString(cudaGetLastError()));
+  if (cudaMemsetAsync(ws, 0, 16, st) != cudaSuccess) {
+    // a cached address that no longer belongs to a live context: look it up again, once
+    cudaGetLastError();
+    if (int32_t rc = static_scratch_address(&ws, true)) return rc;
+    if (cudaMemsetAsync(ws, 0, 16, st) != cudaSuccess)
+      return fail(LC_ERR_CUDA, "observe_tensor_static: %s", cudaGetErrorString(cudaGetLastError()));
+  }
   QParamSpec spec = make_qparam_spec(symmetric, quant_min, quant_max, is_signed, eps);
   observe_tensor_kernel<<<observe_grid(n), kThreads, 0, st>>>(x, n, aligned(x, 16) ? 1 : 0, min_out,
                                                               max_out, accumulate, scale_out != nullptr,

@@ -122,9 +122,18 @@ class Int8WeightCache:
         self.codes = None
         self.rowsum = None
 
-    def get(self, weight_int8: torch.Tensor):
-        key = (weight_int8.data_ptr(), weight_int8._version, weight_int8.device, tuple(weight_int8.shape))
+    def get(self, weight_int8: torch.Tensor, weight_zero_point: torch.Tensor | None = None):
+        key = (weight_int8.data_ptr(), weight_int8._version, weight_int8.device, tuple(weight_int8.shape),
+               None if weight_zero_point is None else (weight_zero_point.data_ptr(), weight_zero_point._version))
         if key != self._key:
+            # checked when the operand views are (re)built, never in an ordinary forward: the integer
+            # GEMM computes sum_k xq * wq, which equals the reference's (q - z_w) * s_w form only for
+            # symmetric weights (what from_float produces)
+            if weight_zero_point is not None and bool((weight_zero_point != 0).any()):
+                raise NotImplementedError(
+                    "dynamic Linear: weight_zero_point is not all zero (weights quantized on an affine grid); "
+                    "the int8 GEMM path takes symmetric per-row weights only -- re-quantize the float weights with "
+                    "a symmetric weight observer (nnqd.Linear.from_float does)")
             self.codes = _backend.ops().pad_rows_to_16(weight_int8)
             self.rowsum = _backend.ops().rowsum_s8(self.codes)
             self._key = key

@@ -127,7 +127,7 @@ class ColumnParallelLinear(nn.Module):
         buf, hdl = ex.buffers[which], ex.handles[which]
         per = self.out_features // self.world
         col_bytes = self.rank * per * 4
-        wq, wsum = sh._cache.get(sh.weight_int8)
+        wq, wsum = sh._cache.get(sh.weight_int8, sh.weight_zero_point)
         xq, sx, zx = sh._quantize_activations(x2)
         kw = dict(bias=sh.bias, zx=zx, wsum=wsum if zx is not None else None, status=ex.status)
         # nobody's consumers still read this buffer (their result n - 2) once every rank is here

@@ -16,6 +16,8 @@ no host synchronisation.
 """
 from __future__ import annotations
 
+import contextlib
+import threading
 import weakref
 
 import torch
@@ -29,38 +31,63 @@ from lucid_b200.quantization._qscheme import QDtype, per_channel_symmetric, qint
 _ACT_SCHEMES = ("tensor_affine", "tensor_symmetric", "token_symmetric")
 
 
-class _LastQuantizedInput:
-    """The codes of the most recently quantized activation tensor, so that sibling layers fed
-    the same tensor (the q / k / v projections of an attention block, the gate and up
-    projections of an MLP) quantize it once.  A hit needs the same tensor object (held weakly:
-    a tensor that has died can never match, whatever memory a new one is given) at the same
-    in-place version and the same grid, in the same execution context: codes recorded while
-    a CUDA graph is being captured exist only inside that graph, so entries carry the id of the
-    capture they were made in (0: eager) and only match there.  One entry; it is dropped when
-    the tensor dies or the next input replaces it."""
+class _SharedInputCodes:
+    """Codes of the activation tensor quantized last inside a :func:`share_quantized_input` block,
+    so that sibling layers fed the same tensor there (the q / k / v projections of an attention
+    block, the gate and up projections of an MLP) quantize it once.  Sharing is OFF outside such a
+    block: the only evidence that two calls see the same values is the tensor object and its
+    in-place version counter, and writes that bypass the counter (a producer replayed from a CUDA
+    graph, a peer GPU storing into the buffer, any raw-pointer kernel) would be missed.  Inside a
+    block the caller vouches that the tensor is not rewritten between the sibling calls.  A hit
+    needs the same tensor object (held weakly), version, shape, dtype, grid, CUDA stream and
+    graph-capture id; the entry is dropped when the block ends."""
 
     def __init__(self) -> None:
-        self._entry = None  # (weak reference, key, value): replaced as a whole, so readers in other threads see one entry
+        self._local = threading.local()
 
-    def get(self, x: torch.Tensor, grid):
-        entry = self._entry
-        if entry is not None and entry[0]() is x and entry[1] == (x._version, tuple(x.shape), x.dtype, grid):
+    @property
+    def active(self) -> bool:
+        return getattr(self._local, "depth", 0) > 0
+
+    def enter(self) -> None:
+        self._local.depth = getattr(self._local, "depth", 0) + 1
+
+    def leave(self) -> None:
+        self._local.depth -= 1
+        if self._local.depth == 0:
+            self._local.entry = None
+
+    def get(self, x: torch.Tensor, key):
+        entry = getattr(self._local, "entry", None)
+        if entry is not None and entry[0]() is x and entry[1] == (x._version, tuple(x.shape), x.dtype, key):
             return entry[2]
         return None
 
-    def put(self, x: torch.Tensor, grid, val) -> None:
-        self._entry = (weakref.ref(x, self._dropped), (x._version, tuple(x.shape), x.dtype, grid), val)
-
-    def _dropped(self, ref) -> None:
-        entry = self._entry
-        if entry is not None and entry[0] is ref:
-            self._entry = None
+    def put(self, x: torch.Tensor, key, val) -> None:
+        self._local.entry = (weakref.ref(x), (x._version, tuple(x.shape), x.dtype, key), val)
 
     def clear(self) -> None:
-        self._entry = None
+        self._local.entry = None
 
 
-_last_input = _LastQuantizedInput()
+_shared_input = _SharedInputCodes()
+
+
+@contextlib.contextmanager
+def share_quantized_input():
+    """Within this block, dynamic Linears that are handed the SAME tensor object reuse its int8
+    codes instead of quantizing it again::
+
+        with share_quantized_input():
+            q, k, v = self.q(x), self.k(x), self.v(x)
+
+    The caller promises that ``x`` is not written to between those calls by anything torch's
+    version counter cannot see (graph replays, peer stores, raw-pointer kernels)."""
+    _shared_input.enter()
+    try:
+        yield
+    finally:
+        _shared_input.leave()
 
 
 class Linear(nn.Module):
@@ -109,17 +136,21 @@ class Linear(nn.Module):
         x2 = xd.reshape(-1, self.in_features)
         if x2.dtype != torch.float32:
             x2 = x2.float()
-        wq, wsum = self._cache.get(_backend.on_cuda(self.weight_int8))
+        wq, wsum = self._cache.get(_backend.on_cuda(self.weight_int8), self.weight_zero_point)
         if x2.shape[0] == 0:
             y = torch.zeros((0, self.out_features), dtype=self.out_dtype, device=xd.device)
         else:
-            grid = (self.act_scheme, self.act_qdtype.name, self.in_features,
-                    _backend.ops().capture_id(xd.device) if x.is_cuda else 0)
-            hit = _last_input.get(x, grid) if x.is_cuda else None
+            hit = None
+            if x.is_cuda and _shared_input.active:
+                ops = _backend.ops()
+                key = (self.act_scheme, self.act_qdtype.name, self.in_features, ops.capture_id(xd.device),
+                       torch.cuda.current_stream(xd.device).cuda_stream)
+                hit = _shared_input.get(x, key)
+                if hit is None:
+                    hit = self._quantize_activations(x2)
+                    _shared_input.put(x, key, hit)
             if hit is None:
                 hit = self._quantize_activations(x2)
-                if x.is_cuda:
-                    _last_input.put(x, grid, hit)
             xq, sx, zx = hit
             y = _backend.ops().qlinear_i8(xq, wq, sx, _backend.on_cuda(self.weight_scale),
                                  bias=None if self.bias is None else _backend.on_cuda(self.bias), zx=zx,

@@ -45,6 +45,29 @@ class _QuantizedTable(nn.Module):
         return (_backend.on_cuda(self.weight_int8), _backend.on_cuda(self.weight_scale),
                 _backend.on_cuda(self.weight_zero_point))
 
+    def _status_word(self, device) -> torch.Tensor:
+        """Device int32 the lookup kernels set to 1 when they meet an index outside the table (the
+        row they write for it is all zeros; the table is never read out of bounds).  Kept across
+        forwards and read only by :meth:`check_indices`, so the forward itself never waits for the GPU."""
+        word = self.__dict__.get("_index_status")
+        if word is None or word.device != device:
+            word = torch.zeros(1, dtype=torch.int32, device=device)
+            self.__dict__["_index_status"] = word
+        return word
+
+    def check_indices(self) -> None:
+        """Raise ``IndexError`` if any forward since the last check saw an index outside
+        ``[0, num_embeddings)`` (the reference refuses such an index at once, on the host,
+        ``lucid/_C/backend/cpu/IndexBounds.h:89-93``); synchronises the device and clears the record.
+        With ``validate = True`` every forward ends with this check."""
+        word = self.__dict__.get("_index_status")
+        if word is not None and int(word.item()) != 0:
+            word.zero_()
+            raise IndexError(f"{type(self).__name__}: an index outside [0, {self.num_embeddings}) was looked up "
+                             "(its output rows are zeros)")
+
+    validate = False
+
     def _fill(self, mod: nn.Module) -> None:
         codes, scale, zero_point = _quantize_table(mod)
         self.register_buffer("weight_int8", codes)
@@ -61,7 +84,10 @@ class Embedding(_QuantizedTable):
         if indices.is_floating_point():
             raise TypeError("quantized.Embedding: indices must be an integer tensor")
         table, scale, zero_point = self._table()
-        out = _backend.ops().embedding_s8(table, scale, zero_point, _backend.on_cuda(indices))
+        out = _backend.ops().embedding_s8(table, scale, zero_point, _backend.on_cuda(indices),
+                                          status=self._status_word(table.device))
+        if self.validate:
+            self.check_indices()
         return out if indices.is_cuda else out.to(indices.device)
 
     @classmethod
@@ -109,7 +135,10 @@ class EmbeddingBag(_QuantizedTable):
         psw = None if per_sample_weights is None else _backend.on_cuda(per_sample_weights).reshape(-1)
         table, scale, zero_point = self._table()
         out = _backend.ops().embedding_bag_s8(table, scale, zero_point, idx.reshape(-1), off, self.mode,
-                                              self.padding_idx, psw, include_last)
+                                              self.padding_idx, psw, include_last,
+                                              status=self._status_word(table.device))
+        if self.validate:
+            self.check_indices()
         return out if indices.is_cuda else out.to(indices.device)
 
     @classmethod

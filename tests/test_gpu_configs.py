@@ -85,7 +85,8 @@ def test_config3_encoder_every_linear():
 
         def forward(self, x):
             b, s, _ = x.shape
-            q, k, v = (m(x).view(b, s, H, D // H).transpose(1, 2) for m in (self.q, self.k, self.v))
+            with nnqd.share_quantized_input():
+                q, k, v = [m(x).view(b, s, H, D // H).transpose(1, 2) for m in (self.q, self.k, self.v)]
             a = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, s, D)
             x = self.norm1(x + self.o(a))
             return self.norm2(x + self.linear2(torch.nn.functional.gelu(self.linear1(x))))
@@ -120,7 +121,8 @@ def test_config3_encoder_full_size():
 
         def forward(self, x):
             b, s, _ = x.shape
-            q, k, v = (m(x).view(b, s, H, D // H).transpose(1, 2) for m in (self.q, self.k, self.v))
+            with nnqd.share_quantized_input():
+                q, k, v = [m(x).view(b, s, H, D // H).transpose(1, 2) for m in (self.q, self.k, self.v)]
             a = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, s, D)
             x = self.norm1(x + self.o(a))
             return self.norm2(x + self.linear2(torch.nn.functional.gelu(self.linear1(x))))
@@ -194,9 +196,10 @@ def test_graphed_module_replays_the_quantized_forward():
 
 
 def test_sibling_layers_share_one_activation_quantization():
-    """q / k / v style siblings fed the same tensor reuse its codes; a new tensor, an in-place
-    change or another grid does not."""
-    from lucid_b200.nn.quantized.dynamic import linear as dl
+    """Inside a share_quantized_input() block q / k / v style siblings fed the same tensor reuse its
+    codes; a new tensor, an in-place change or another grid does not; outside a block nothing is
+    shared (writes that bypass torch's version counter could not be seen)."""
+    from lucid_b200.nn.quantized.dynamic import share_quantized_input
 
     torch.manual_seed(0)
     a, b = (Q.quantize_dynamic(nn.Linear(256, 128).cuda()) for _ in range(2))
@@ -210,25 +213,30 @@ def test_sibling_layers_share_one_activation_quantization():
 
     nnqd.Linear._quantize_activations = counting
     try:
-        dl._last_input.clear()
-        ya, yb = a(x), b(x)
-        assert len(calls) == 1
-        x.mul_(2.0)  # in-place change: new version
-        ya2 = a(x)
-        assert len(calls) == 2
-        a(x.clone())  # another tensor
-        assert len(calls) == 3
-        b.set_activation_scheme("token_symmetric")
-        b(x)  # same tensor, other grid (replaces the entry)
-        a(x)
-        assert len(calls) == 5
+        ya0, yb0 = a(x), b(x)
+        assert len(calls) == 2  # no sharing outside a block
+        with share_quantized_input():
+            ya, yb = a(x), b(x)
+            assert len(calls) == 3
+            x.mul_(2.0)  # in-place change: new version
+            ya2 = a(x)
+            assert len(calls) == 4
+            a(x.clone())  # another tensor
+            assert len(calls) == 5
+            b.set_activation_scheme("token_symmetric")
+            b(x)  # same tensor, other grid (replaces the entry)
+            a(x)
+            assert len(calls) == 7
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                a(x)  # same tensor on another stream: its codes were produced on the first one
+            torch.cuda.current_stream().wait_stream(side)
+            assert len(calls) == 8
+        with share_quantized_input():
+            a(x)  # a new block starts empty
+        assert len(calls) == 9
     finally:
         nnqd.Linear._quantize_activations = orig
-        dl._last_input.clear()
-    fresh_a = Q.quantize_dynamic  # results are those of independent quantization
-    dl._last_input.clear()
+    assert torch.equal(ya, ya0) and torch.equal(yb, yb0)  # shared codes give the bits of independent quantization
     assert torch.equal(a(x), ya2)
-    xb = x / 2.0
-    dl._last_input.clear()
-    b.set_activation_scheme("tensor_affine")
-    assert torch.allclose(b(xb), yb, rtol=1e-5, atol=1e-6)

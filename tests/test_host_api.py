@@ -447,3 +447,14 @@ def test_reference_module_paths_resolve_to_the_same_modules():
     assert AliasQatLinear is QatLinear
     with pytest.raises(ModuleNotFoundError):
         importlib.import_module("lucid.no_such_module")
+
+
+def test_dynamic_linear_refuses_affine_weights(device):
+    """The integer GEMM form equals the reference's (q - z_w) * s_w dequantization only for z_w = 0;
+    a state dict carrying a non-zero weight zero-point must not be computed silently wrong."""
+    q = Q.quantize_dynamic(nn.Linear(32, 8))
+    x = torch.randn(4, 32).to(device)
+    q(x)
+    q.weight_zero_point[3] = 2.0
+    with pytest.raises(NotImplementedError, match="weight_zero_point"):
+        q(x)
