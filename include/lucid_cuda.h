@@ -283,6 +283,21 @@ int32_t lc_peer_barrier(void* const* host_flags, int32_t rank, int32_t world, ui
 int32_t lc_copy_2d_async(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch,
                          int64_t width_bytes, int64_t rows, void* stream);
 
+/* The whole forward of the dynamic Linear (lucid/nn/quantized/dynamic/linear.py:85-92) from ONE call:
+ * dynamic activation quantization of x [M, K] fp32 (act_scheme 0: per-tensor affine, the reference's
+ * default with quint8; 1: per-tensor symmetric; 2: per-row symmetric) followed by lc_qlinear_i8
+ * against wq / sw / bias (wsum = row sums of wq, needed whenever the grid has a zero-point).  Codes,
+ * scales and the scratch of the range kernel live in `workspace` (lc_dynamic_linear_workspace_bytes,
+ * 256-byte aligned, reusable by later calls of at most the same M and K on the same stream); pass
+ * workspace_is_fresh != 0 the first time a buffer is used (its scratch part is then zero-filled).
+ * Results are those of the separate calls; what this saves is host time per layer. */
+int64_t lc_dynamic_linear_workspace_bytes(int64_t M, int64_t K);
+int32_t lc_dynamic_linear_f32(const float* x, int64_t ldx, int64_t M, int64_t K, int32_t act_scheme,
+                              int32_t quant_min, int32_t quant_max, int32_t is_signed, float eps,
+                              const int8_t* wq, int64_t ldw, int64_t N, const float* sw, const float* bias,
+                              const int32_t* wsum, void* out, int32_t out_dtype, int64_t ldo, void* workspace,
+                              int64_t workspace_bytes, int32_t workspace_is_fresh, int32_t* status, void* stream);
+
 /* row sums of an int8 matrix as int32 (the zero-point correction term) */
 int32_t lc_rowsum_s8(const int8_t* b, int64_t rows, int64_t cols, int64_t ldb, int32_t* out,
                      void* stream);
@@ -311,7 +326,21 @@ int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K
 int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
                            const int8_t* wq, int64_t ldw, int64_t N, const float* sw, const float* bias,
                            int32_t relu, const float* out_scale, const float* out_zp, int32_t quant_min,
-                           int32_t quant_max, void* y, int64_t ldy, int32_t flags, void* stream);
+                           int32_t quant_max, void* y, int64_t ldy, int32_t flags, void* workspace,
+                           int64_t workspace_bytes, void* stream);
+
+/* Scratch for the _ex weight-only entry points (may be NULL).  With it, the kernel that streams large
+ * weights gives every SM the same number of bytes whatever the shape: work is cut into (32-row box,
+ * 1024-byte K chunk) units, every CTA takes an equal contiguous run of them, and a box whose K range
+ * two or more CTAs share is finished by the one that arrives last (each parks its raw sums in its own
+ * slot of the scratch; the sums are added in CTA order, so results do not depend on timing).  Without
+ * it every CTA takes whole boxes, which leaves SMs idle when the boxes do not divide evenly (a
+ * [4096, 14336] matrix occupies 128 of 148 SMs).  Sums over a split K range are added in a different
+ * order than in one pass, so the last bits of an output may differ between the two schedules.
+ * lc_wo_linear_workspace_bytes(N) bytes, 16-byte aligned, zero-filled once by the caller; the kernel
+ * leaves it zero.  One scratch per stream: launches that can overlap on the GPU must not share it.
+ * If lc_wo_linear_status reports a wait that ran out, zero the scratch again before reusing it. */
+int64_t lc_wo_linear_workspace_bytes(int64_t N);
 
 /* Gate and up projection of a SwiGLU MLP in one pass over the weights, with the activation
  * fused: wq is [N2 = 2F, K] with rows interleaved in blocks of 8 (rows 16t..16t+7 are gate
@@ -324,6 +353,11 @@ int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_
 int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
                         const int8_t* wq, int64_t ldw, int64_t N2, const float* sw, const float* bias,
                         void* y, int64_t ldy, int32_t flags, void* stream);
+/* the same with scratch for the balanced schedule (see lc_wo_linear_workspace_bytes; size it for N2) */
+int32_t lc_wo_swiglu_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
+                           const int8_t* wq, int64_t ldw, int64_t N2, const float* sw, const float* bias,
+                           void* y, int64_t ldy, int32_t flags, void* workspace, int64_t workspace_bytes,
+                           void* stream);
 
 /* ---- weight-only Linear on the tensor cores, for more rows than a GEMV handles ----
  * The statically quantized Linear's forward, dequantize(W) -> F.linear -> (ReLU) -> fake_quantize

@@ -67,6 +67,9 @@ SIGNATURES = {
     "lc_qlinear_check_status": (_i32, [_p, _i32, _p]),
     "lc_peer_barrier": (_i32, [C.POINTER(C.c_void_p), _i32, _i32, C.c_uint32, _i64, _p, _p]),
     "lc_copy_2d_async": (_i32, [_p, _i64, _p, _i64, _i64, _i64, _p]),
+    "lc_dynamic_linear_workspace_bytes": (_i64, [_i64, _i64]),
+    "lc_dynamic_linear_f32": (_i32, [_p, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _f, _p, _i64, _i64, _p, _p, _p, _p, _i32,
+                                     _i64, _p, _i64, _i32, _p, _p]),
     "lc_rowsum_s8": (_i32, [_p, _i64, _i64, _i64, _p, _p]),
     "lc_wo_gemm_16": (_i32, [_p, _i32, _i32, _i64, _p, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _i32, _p, _p, _i32, _i32,
                              _p, _i32, _i64, _p, _i32, _p]),
@@ -78,7 +81,9 @@ SIGNATURES = {
     "lc_split_f32_bf16x3": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _p, _p]),
     "lc_wo_linear_s8": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _i32, _p]),
     "lc_wo_linear_s8_ex": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _i32, _p, _p, _i32, _i32, _p, _i64,
-                                  _i32, _p]),
+                                  _i32, _p, _i64, _p]),
+    "lc_wo_linear_workspace_bytes": (_i64, [_i64]),
+    "lc_wo_swiglu_s8_ex": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _i32, _p, _i64, _p]),
     "lc_wo_swiglu_s8": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _i32, _p]),
     "lc_wo_linear_status": (_i32, [C.POINTER(_i32), _i32]),
     "lc_group_quantize_f32": (_i32, [_p, _i64, _i64, _i32, _i32, _p, _p, _p, _p]),

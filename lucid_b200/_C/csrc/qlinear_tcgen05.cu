@@ -1381,3 +1381,66 @@ extern "C" int32_t lc_wo_gemm_digits(const int8_t* digits, int64_t ldd, const fl
   return launch_gemm<kModeDigits>(digits, K, ldd, wq, K, ldw, p, variant, make_idesc_pair(false), false, N * K,
                                   as_stream(stream), "wo_gemm_digits");
 }
+
+// ---- the dynamic Linear forward as ONE call ------------------------------------------------------
+// Activation quantization (per tensor or per row) and the GEMM, issued back to back on the stream from
+// one entry point with one caller workspace: an eager framework pays the host cost of a call (argument
+// marshalling, allocator, stream query) once per layer instead of three times.
+namespace {
+constexpr int64_t kDynAlign = 256;
+inline int64_t dyn_round(int64_t v) { return (v + kDynAlign - 1) / kDynAlign * kDynAlign; }
+inline int64_t dyn_pad16(int64_t k) { return (k + 15) / 16 * 16; }
+}  // namespace
+
+extern "C" int64_t lc_dynamic_linear_workspace_bytes(int64_t M, int64_t K) {
+  if (M < 0 || K <= 0) return 0;
+  // codes [M, pad16(K)], per-row scales and zero-points, {min, max}, scratch of the global-range kernel
+  return dyn_round(M * dyn_pad16(K)) + 2 * dyn_round(M * 4 + 4) + dyn_round(16) +
+         dyn_round(lc_observe_tensor_workspace_bytes());
+}
+
+extern "C" int32_t lc_dynamic_linear_f32(const float* x, int64_t ldx, int64_t M, int64_t K, int32_t act_scheme,
+                                         int32_t quant_min, int32_t quant_max, int32_t is_signed, float eps,
+                                         const int8_t* wq, int64_t ldw, int64_t N, const float* sw,
+                                         const float* bias, const int32_t* wsum, void* out, int32_t out_dtype,
+                                         int64_t ldo, void* workspace, int64_t workspace_bytes,
+                                         int32_t workspace_is_fresh, int32_t* status, void* stream) {
+  if (act_scheme < 0 || act_scheme > 2)
+    return fail(LC_ERR_INVALID_ARG, "dynamic_linear: act_scheme must be 0 (tensor affine), 1 (tensor symmetric) or "
+                                    "2 (token symmetric)");
+  if (M < 0 || N < 0 || K <= 0 || ldx < K) return fail(LC_ERR_INVALID_ARG, "dynamic_linear: bad shape");
+  if (M == 0 || N == 0) return LC_OK;
+  if (!x || !wq || !out || !workspace) return fail(LC_ERR_INVALID_ARG, "dynamic_linear: null pointer");
+  if (workspace_bytes < lc_dynamic_linear_workspace_bytes(M, K) || !aligned(workspace, 256))
+    return fail(LC_ERR_WORKSPACE, "dynamic_linear: workspace of %lld bytes (256-byte aligned) required",
+                (long long)lc_dynamic_linear_workspace_bytes(M, K));
+  uint8_t* base = static_cast<uint8_t*>(workspace);
+  const int64_t ldq = dyn_pad16(K);
+  void* codes = base;
+  float* scale = reinterpret_cast<float*>(base + dyn_round(M * ldq));
+  float* zp = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scale) + dyn_round(M * 4 + 4));
+  float* minmax = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(zp) + dyn_round(M * 4 + 4));
+  void* observe_ws = reinterpret_cast<uint8_t*>(minmax) + dyn_round(16);
+  const int64_t observe_bytes = lc_observe_tensor_workspace_bytes();
+  const int code_dtype = is_signed ? LC_S8 : LC_U8;
+  if (act_scheme == 2) {
+    if (int32_t rc = lc_dynamic_quantize_rows_f32(x, M, K, ldx, 1, quant_min, quant_max, is_signed, eps, codes,
+                                                  code_dtype, ldq, scale, zp, stream))
+      return rc;
+    return lc_qlinear_i8(codes, is_signed ? 0 : 1, ldq, wq, ldw, M, N, K, scale, 1, nullptr, nullptr, sw, bias, out,
+                         out_dtype, ldo, status, stream);
+  }
+  // the global-range kernel wants its scratch zero-filled before its first use and leaves it zero
+  if (workspace_is_fresh &&
+      cudaMemsetAsync(observe_ws, 0, static_cast<size_t>(observe_bytes), as_stream(stream)) != cudaSuccess)
+    return fail(LC_ERR_CUDA, "dynamic_linear: %s", cudaGetErrorString(cudaGetLastError()));
+  const int symmetric = act_scheme == 1;
+  if (int32_t rc = lc_dynamic_quantize_tensor_f32(x, M, K, ldx, symmetric, quant_min, quant_max, is_signed, eps,
+                                                  codes, code_dtype, ldq, scale, zp, minmax, observe_ws,
+                                                  observe_bytes, stream))
+    return rc;
+  const bool needs_zp = !(symmetric && is_signed);
+  if (needs_zp && !wsum) return fail(LC_ERR_INVALID_ARG, "dynamic_linear: this activation grid needs wsum");
+  return lc_qlinear_i8(codes, is_signed ? 0 : 1, ldq, wq, ldw, M, N, K, scale, 0, needs_zp ? zp : nullptr,
+                       needs_zp ? wsum : nullptr, sw, bias, out, out_dtype, ldo, status, stream);
+}

@@ -217,7 +217,7 @@ wo_linear_mma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx
 }
 
 // ---- ring variant for weight matrices that do not fit the caches ------------------------
-// A persistent CTA owns `tiles_per_cta` consecutive 16-row tiles.  A producer thread streams
+// A persistent CTA owns a contiguous share of the matrix (see RingPlan).  A producer thread streams
 // their weights (and, per K chunk, the activations) into shared memory with tiled TMA loads
 // (one 16- or 32-row x 1024-byte box per item; per-row 1-D bulk copies were tried first and are
 // limited by the copy engine's per-request cost), so ~150 KB of loads are in flight per SM
@@ -315,6 +315,60 @@ struct RawOperand<__nv_bfloat16> {
   }
 };
 
+// Work of the ring kernel is counted in units of (box, K chunk), a box being GRP vertically adjacent
+// row tiles.  CTA c owns the contiguous unit range [c*U/G, (c+1)*U/G) in box-major order, so all CTAs
+// stream the same number of bytes (+-1 unit) whatever the matrix shape; a range is walked as passes:
+// a first box it enters in the middle of K, runs of whole boxes (up to TMAX tiles at a time, K outermost
+// inside a pass so that an activation chunk is loaded once for all of them), and a last box it leaves
+// in the middle of K.  A box whose K range is shared by several CTAs is finished by whichever of them
+// arrives last: each parks the raw sums of its K range in its own slot of a small workspace (no
+// atomics on data), takes a ticket of the box, and the holder of the last ticket adds the slots in CTA
+// order -- a fixed order, so results do not depend on timing -- and applies the epilogue.
+struct RingPlan {
+  long long units_real;   // boxes * K chunks
+  long long units;        // what the CTA ranges divide: units_real, or a whole number of boxes per CTA (no workspace)
+  int grid;               // G
+  float* partial;         // [G][2][GRP*16*COLS] raw sums: slot 0 = a pass that starts inside its box, 1 = one that starts it
+  int* tickets;           // [boxes], zero before the launch and zero again after it
+};
+
+struct RingPass {
+  int tile0, n_tiles, kc0, kc1;
+  long long box;
+  bool partial;
+};
+
+template <int TMAX, int GRP>
+struct RingWalk {
+  long long u, u_end, tiles_total;
+  int num_kc;
+  __device__ bool next(RingPass& p) {
+    if (u >= u_end) return false;
+    const long long box = u / num_kc, left = u_end - u;
+    const int kc0 = static_cast<int>(u % num_kc);
+    const long long t0 = box * GRP;
+    if (kc0 != 0 || left < num_kc) {
+      const int kc1 = left < num_kc - kc0 ? kc0 + static_cast<int>(left) : num_kc;
+      const long long nt = tiles_total - t0 < GRP ? tiles_total - t0 : GRP;
+      p = {static_cast<int>(t0), static_cast<int>(nt), kc0, kc1, box, true};
+      u += kc1 - kc0;
+    } else {
+      long long nb = left / num_kc;
+      nb = nb < TMAX / GRP ? nb : TMAX / GRP;
+      const long long nt = tiles_total - t0 < nb * GRP ? tiles_total - t0 : nb * GRP;
+      p = {static_cast<int>(t0), static_cast<int>(nt), 0, num_kc, box, false};
+      u += nb * num_kc;
+    }
+    return true;
+  }
+};
+
+__device__ __forceinline__ long long ring_first_unit(long long c, long long units, int grid) { return c * units / grid; }
+// the CTA whose range holds unit u
+__device__ __forceinline__ int ring_owner(long long u, long long units, int grid) {
+  return static_cast<int>(((u + 1) * grid + units - 1) / units - 1);
+}
+
 // XB = number of activation-chunk buffers: with few row tiles per CTA a K chunk holds little
 // weight data, so more chunks must be in flight to keep the ring full.
 // GRP = row tiles per TMA box (1 or 2): the copy engine of an SM completes boxes one after the
@@ -325,7 +379,7 @@ __global__ void __launch_bounds__(ring::kThreads, 1)
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w1,
                       const __grid_constant__ CUtensorMap tmap_x,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
-                      const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, int tiles_per_cta,
+                      const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, const RingPlan plan,
                       int overlap, const WoEpilogue epi) {
   using namespace ring;
   constexpr int S = stages(NT, TMAX, XB, GRP);
@@ -344,13 +398,15 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   auto xempty_bar = [&](int s) { return bar_base + 8u * (2 * S + XB + s); };
   float* red = reinterpret_cast<float*>(wo_smem_raw + (red_base - wo_smem_u32(wo_smem_raw)));
 
+  __shared__ int s_last_ticket;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t tiles_total = (N + 15) >> 4;
-  const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * tiles_per_cta;
-  const int my_tiles =
-      static_cast<int>(tiles_total - tile0 < tiles_per_cta ? tiles_total - tile0 : tiles_per_cta);
   const int num_kc = static_cast<int>((K + KC - 1) / KC);
   const int nb = static_cast<int>(B);
+  long long u_begin = ring_first_unit(blockIdx.x, plan.units, plan.grid);
+  long long u_end = ring_first_unit(blockIdx.x + 1, plan.units, plan.grid);
+  u_begin = u_begin < plan.units_real ? u_begin : plan.units_real;
+  u_end = u_end < plan.units_real ? u_end : plan.units_real;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -383,21 +439,25 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       // activation chunk must not queue behind a ring-full of weights).
       int prefilled = 0;
       if (overlap) {
-        const int pass0 = my_tiles < TMAX ? my_tiles : TMAX;
-        for (int kc = 0; kc < num_kc && prefilled < S; ++kc)
-          for (int j = 0; j < pass0 && prefilled < S; j += GRP, ++prefilled) {
-            const bool whole = j + GRP <= pass0;
-            wo_mbar_expect(full_bar(prefilled), whole ? GSTAGE : STAGE);
-            wo_tma_load_2d(base + prefilled * GSTAGE, whole ? &tmap_w : &tmap_w1, kc * (KC / 4),
-                           static_cast<int>((tile0 + j) << 4), full_bar(prefilled));
-            armed_mask |= 1u << prefilled;  // parity 0
-          }
+        RingWalk<TMAX, GRP> first = {u_begin, u_end, tiles_total, num_kc};
+        RingPass ps;
+        if (first.next(ps)) {
+          for (int kc = ps.kc0; kc < ps.kc1 && prefilled < S; ++kc)
+            for (int j = 0; j < ps.n_tiles && prefilled < S; j += GRP, ++prefilled) {
+              const bool whole = j + GRP <= ps.n_tiles;
+              wo_mbar_expect(full_bar(prefilled), whole ? GSTAGE : STAGE);
+              wo_tma_load_2d(base + prefilled * GSTAGE, whole ? &tmap_w : &tmap_w1, kc * (KC / 4),
+                             (ps.tile0 + j) << 4, full_bar(prefilled));
+              armed_mask |= 1u << prefilled;  // parity 0
+            }
+        }
       }
       asm volatile("griddepcontrol.wait;" ::: "memory");
       int issued = 0;  // weight items walked so far (the first `prefilled` are already in flight)
-      for (int t0 = 0; t0 < my_tiles && ok; t0 += TMAX) {
-        const int pass_tiles = my_tiles - t0 < TMAX ? my_tiles - t0 : TMAX;
-        for (int kc = 0; kc < num_kc && ok; ++kc, ++xi) {
+      RingWalk<TMAX, GRP> walk = {u_begin, u_end, tiles_total, num_kc};
+      RingPass ps;
+      while (ok && walk.next(ps)) {
+        for (int kc = ps.kc0; kc < ps.kc1 && ok; ++kc, ++xi) {
           const int xb = xi % XB;
           const uint32_t xphase = static_cast<uint32_t>((xi / XB) & 1);
           if (!wo_mbar_wait(xempty_bar(xb), xphase ^ 1u)) {
@@ -410,17 +470,17 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           wo_tma_load_2d(x_base + xb * COLS * X_PITCH, &tmap_x, kc * (KC / 4), 0, xfull_bar(xb));
           xarmed_mask |= 1u << xb;
           xarmed_parity = (xarmed_parity & ~(1u << xb)) | (xphase << xb);
-          for (int j = 0; j < pass_tiles; j += GRP, ++issued) {
+          for (int j = 0; j < ps.n_tiles; j += GRP, ++issued) {
             if (issued >= prefilled) {
               if (!wo_mbar_wait(empty_bar(stage), phase ^ 1u)) {
                 atomicCAS(&g_wo_status, 0, 1);
                 ok = false;
                 break;
               }
-              const int row0 = static_cast<int>((tile0 + t0 + j) << 4);
-              const bool whole = j + GRP <= pass_tiles;
+              const bool whole = j + GRP <= ps.n_tiles;
               wo_mbar_expect(full_bar(stage), whole ? GSTAGE : STAGE);
-              wo_tma_load_2d(base + stage * GSTAGE, whole ? &tmap_w : &tmap_w1, kc * (KC / 4), row0, full_bar(stage));
+              wo_tma_load_2d(base + stage * GSTAGE, whole ? &tmap_w : &tmap_w1, kc * (KC / 4), (ps.tile0 + j) << 4,
+                             full_bar(stage));
               armed_mask |= 1u << stage;
               armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
             }
@@ -447,8 +507,10 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     int stage = 0, xi = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int t0 = 0; t0 < my_tiles; t0 += TMAX) {
-      const int pass_tiles = my_tiles - t0 < TMAX ? my_tiles - t0 : TMAX;
+    RingWalk<TMAX, GRP> walk = {u_begin, u_end, tiles_total, num_kc};
+    RingPass ps;
+    while (walk.next(ps)) {
+      const int pass_tiles = ps.n_tiles;
       float acc[TMAX][NT][4];
 #pragma unroll
       for (int j = 0; j < TMAX; ++j)
@@ -462,7 +524,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
 #pragma unroll
         for (int i = 0; i < 4; ++i) xsum[nt][i] = 0.0f;
 
-      for (int kc = 0; kc < num_kc && ok; ++kc, ++xi) {
+      for (int kc = ps.kc0; kc < ps.kc1 && ok; ++kc, ++xi) {
         const int xb = xi % XB;
         const uint32_t xphase = static_cast<uint32_t>((xi / XB) & 1);
         const bool k_ok = static_cast<int64_t>(kc) * KC + koff < K;               // this lane
@@ -560,41 +622,82 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         }
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-      if (SWIGLU) {
-        // rows r and r+8 of a tile are the gate and the up projection of the same hidden unit:
-        // out[b, 8*tile + r] = silu(gate) * up, one rounding to the activation type
-        for (int o = threadIdx.x; o < pass_tiles * 8 * COLS; o += kConsumerThreads) {
-          const int r = o & 7, bcol = (o >> 3) % COLS, j = (o >> 3) / COLS;
-          const int64_t tile = tile0 + t0 + j;
-          const int64_t ng = (tile << 4) + r, nu = ng + 8, h = (tile << 3) + r;
-          if (nu < N && bcol < nb) {
-            const float* src = red + j * kConsumerWarps * 16 * RP + r * RP + bcol;
-            float gs = 0.0f, us = 0.0f;
-#pragma unroll
-            for (int wp = 0; wp < kConsumerWarps; ++wp) {
-              gs += src[wp * 16 * RP];
-              us += src[wp * 16 * RP + 8 * RP];
-            }
-            float gv = gs * (sw ? __ldg(sw + ng) : 1.0f), uv = us * (sw ? __ldg(sw + nu) : 1.0f);
-            if (bias) {
-              gv += __ldg(bias + ng);
-              uv += __ldg(bias + nu);
-            }
-            y[static_cast<int64_t>(bcol) * ldy + h] = from_float<XT>(gv / (1.0f + __expf(-gv)) * uv);
-          }
-        }
-      } else {
-        for (int o = threadIdx.x; o < pass_tiles * 16 * COLS; o += kConsumerThreads) {
-          const int r = o & 15, bcol = (o >> 4) % COLS, j = (o >> 4) / COLS;
-          const int64_t n = ((tile0 + t0 + j) << 4) + r;
-          if (n < N && bcol < nb) {
+
+      // For a pass over part of K: park the CTA's raw sums in its workspace slot, take a ticket of
+      // the box, and go on only if every other CTA that shares the box has already parked its own.
+      constexpr int kSlotFloats = GRP * 16 * COLS;
+      int n_sharers = 1, first_sharer = 0;
+      bool finish = true;
+      if (ps.partial) {
+        const long long box_first = ps.box * num_kc;
+        first_sharer = ring_owner(box_first, plan.units, plan.grid);
+        n_sharers = ring_owner(box_first + num_kc - 1, plan.units, plan.grid) - first_sharer + 1;
+        float* slot = plan.partial + (static_cast<size_t>(blockIdx.x) * 2 + (u_begin > box_first ? 0 : 1)) * kSlotFloats;
+        {
+          for (int o = threadIdx.x; o < pass_tiles * 16 * COLS; o += kConsumerThreads) {
+            const int r = o & 15, bcol = (o >> 4) % COLS, j = (o >> 4) / COLS;
             const float* src = red + j * kConsumerWarps * 16 * RP + r * RP + bcol;
             float sum = 0.0f;
 #pragma unroll
             for (int wp = 0; wp < kConsumerWarps; ++wp) sum += src[wp * 16 * RP];
-            float v = sum * (sw ? __ldg(sw + n) : 1.0f);
-            if (bias) v += __ldg(bias + n);
-            y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(wo_finish(v, epi));
+            slot[(j * 16 + r) * COLS + bcol] = sum;
+          }
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+        if (threadIdx.x == 0) {
+          const int old = atomicAdd(plan.tickets + ps.box, 1);
+          s_last_ticket = old == n_sharers - 1;
+          if (old == n_sharers - 1) plan.tickets[ps.box] = 0;  // every sharer has drawn: ready for the next launch
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+        finish = s_last_ticket != 0;
+        if (finish) __threadfence();
+      }
+      if (finish) {
+        // sum over the 16 warps (a pass over all of K) or over the sharers' slots, in CTA order
+        auto total = [&](int j, int r, int bcol) -> float {
+          if (!ps.partial) {
+            const float* src = red + j * kConsumerWarps * 16 * RP + r * RP + bcol;
+            float sum = 0.0f;
+#pragma unroll
+            for (int wp = 0; wp < kConsumerWarps; ++wp) sum += src[wp * 16 * RP];
+            return sum;
+          }
+          float sum = 0.0f;
+          for (int c = 0; c < n_sharers; ++c) {
+            const long long cta = first_sharer + c;
+            const int which = ring_first_unit(cta, plan.units, plan.grid) > ps.box * num_kc ? 0 : 1;
+            sum += __ldcg(plan.partial + (static_cast<size_t>(cta) * 2 + which) * kSlotFloats + (j * 16 + r) * COLS + bcol);
+          }
+          return sum;
+        };
+        if (SWIGLU) {
+          // rows r and r+8 of a tile are the gate and the up projection of the same hidden unit:
+          // out[b, 8*tile + r] = silu(gate) * up, one rounding to the activation type
+          for (int o = threadIdx.x; o < pass_tiles * 8 * COLS; o += kConsumerThreads) {
+            const int r = o & 7, bcol = (o >> 3) % COLS, j = (o >> 3) / COLS;
+            const int64_t tile = ps.tile0 + j;
+            const int64_t ng = (tile << 4) + r, nu = ng + 8, h = (tile << 3) + r;
+            if (nu < N && bcol < nb) {
+              const float gs = total(j, r, bcol), us = total(j, r + 8, bcol);
+              float gv = gs * (sw ? __ldg(sw + ng) : 1.0f), uv = us * (sw ? __ldg(sw + nu) : 1.0f);
+              if (bias) {
+                gv += __ldg(bias + ng);
+                uv += __ldg(bias + nu);
+              }
+              y[static_cast<int64_t>(bcol) * ldy + h] = from_float<XT>(gv / (1.0f + __expf(-gv)) * uv);
+            }
+          }
+        } else {
+          for (int o = threadIdx.x; o < pass_tiles * 16 * COLS; o += kConsumerThreads) {
+            const int r = o & 15, bcol = (o >> 4) % COLS, j = (o >> 4) / COLS;
+            const int64_t n = ((static_cast<int64_t>(ps.tile0) + j) << 4) + r;
+            if (n < N && bcol < nb) {
+              float v = total(j, r, bcol) * (sw ? __ldg(sw + n) : 1.0f);
+              if (bias) v += __ldg(bias + n);
+              y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(wo_finish(v, epi));
+            }
           }
         }
       }
@@ -811,10 +914,18 @@ static int32_t launch_wo_mma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
   return check_launch("wo_linear_s8 (mma)");
 }
 
+// scratch of the balanced schedule: per CTA two slots of raw sums, then one ticket per box
+struct RingScratch {
+  void* ptr;
+  int64_t bytes;
+};
+constexpr int64_t kRingSlotBytes = 2 * 16 * 32 * 4;  // largest GRP * 16 rows * COLS floats
+
 template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP>
 static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                    int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
-                                   int64_t ldy, bool overlap, const WoEpilogue& epi, cudaStream_t st) {
+                                   int64_t ldy, bool overlap, const WoEpilogue& epi, const RingScratch& scratch,
+                                   cudaStream_t st) {
   auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU, GRP>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
@@ -840,13 +951,28 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
                                         static_cast<uint64_t>(B), static_cast<uint64_t>(ldx) * 2, ring::KC / 4,
                                         NT * 8, CU_TENSOR_MAP_SWIZZLE_NONE))
     return rc;
-  // an evenly divided persistent grid: every CTA gets the same number of row tiles
-  const int64_t tiles = (N + 15) / 16;
+  const int64_t tiles = (N + 15) / 16, boxes = (tiles + GRP - 1) / GRP;
+  const int64_t num_kc = (K + ring::KC - 1) / ring::KC;
   const int64_t sms = sm_count();
-  const int64_t per = (tiles + sms - 1) / sms;
-  const unsigned grid = static_cast<unsigned>((tiles + per - 1) / per);
+  RingPlan plan;
+  plan.units_real = boxes * num_kc;
+  const int64_t need = sms * 2 * kRingSlotBytes + boxes * 4;
+  if (scratch.ptr && scratch.bytes >= need && aligned(scratch.ptr, 16)) {
+    // every CTA the same number of (box, K chunk) units, boxes shared along K where ranges meet
+    plan.grid = static_cast<int>(plan.units_real < sms ? plan.units_real : sms);
+    plan.units = plan.units_real;
+    plan.partial = static_cast<float*>(scratch.ptr);
+    plan.tickets = reinterpret_cast<int*>(static_cast<uint8_t*>(scratch.ptr) + sms * 2 * kRingSlotBytes);
+  } else {
+    // no scratch: whole boxes only, the same number for every CTA
+    const int64_t per = (boxes + sms - 1) / sms;
+    plan.grid = static_cast<int>((boxes + per - 1) / per);
+    plan.units = plan.grid * per * num_kc;
+    plan.partial = nullptr;
+    plan.tickets = nullptr;
+  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
+  cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
   cfg.blockDim = dim3(ring::kThreads);
   cfg.dynamicSmemBytes = ring::kSmemBudget;
   cfg.stream = st;
@@ -855,8 +981,8 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = overlap ? 1 : 0;
-  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_w1, map_x, B, K, N, sw, bias, y, ldy,
-                                             static_cast<int>(per), overlap ? 1 : 0, epi);
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_w1, map_x, B, K, N, sw, bias, y, ldy, plan,
+                                             overlap ? 1 : 0, epi);
   if (err != cudaSuccess) return fail(LC_ERR_CUDA, "wo_linear_s8 (ring): %s", cudaGetErrorString(err));
   return check_launch("wo_linear_s8 (ring)");
 }
@@ -864,19 +990,19 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
 template <typename XT, bool SWIGLU = false>
 static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w, int64_t ldw,
                              int64_t N, const float* sw, const float* bias, XT* y, int64_t ldy,
-                             bool overlap, const WoEpilogue& epi, cudaStream_t st) {
+                             bool overlap, const WoEpilogue& epi, const RingScratch& scratch, cudaStream_t st) {
   // few row tiles per CTA (short, wide matrices): small reduction buffer, more activation chunks in flight
   const int64_t tiles = (N + 15) / 16, sms = sm_count();
   const bool few = (tiles + sms - 1) / sms <= 2;
   // two row tiles per TMA box where the ring stays at least three boxes deep (batches up to 8);
   // measured on the decode MLP: 40.8 us against 41.6 us with one tile per box
   if (B <= 8)
-    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, st)
-               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, st);
+    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st)
+               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
   if (B <= 16)
-    return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, st)
-               : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, st);
-  return launch_wo_ring_inst<XT, 4, 1, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, st);
+    return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st)
+               : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
+  return launch_wo_ring_inst<XT, 4, 1, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
 }
 
 template <typename XT>
@@ -896,7 +1022,8 @@ static int32_t launch_wo_fma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
 template <typename XT>
 static int32_t wo_linear_typed(const void* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                int64_t ldw, int64_t N, const float* sw, const float* bias, void* y,
-                               int64_t ldy, bool overlap, const WoEpilogue& epi, cudaStream_t st) {
+                               int64_t ldy, bool overlap, const WoEpilogue& epi, const RingScratch& scratch,
+                               cudaStream_t st) {
   const XT* xt = static_cast<const XT*>(x);
   XT* yt = static_cast<XT*>(y);
   const bool mma_ok = sizeof(XT) == 2 && K % 16 == 0 && ldw % 16 == 0 && ldx % 8 == 0 &&
@@ -909,7 +1036,7 @@ static int32_t wo_linear_typed(const void* x, int64_t B, int64_t K, int64_t ldx,
       // are latency-bound and use the direct-load kernel
       const bool big = N * K >= (int64_t{4} << 20);
       rc = !mma_ok ? launch_wo_fma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, epi, st)
-           : big   ? launch_wo_tma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, overlap, epi, st)
+           : big   ? launch_wo_tma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, overlap, epi, scratch, st)
                    : launch_wo_mma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, epi, st);
     } else {
       rc = launch_wo_fma<XT>(xt + b0 * ldx, bc, K, ldx, w, ldw, N, sw, bias, yt + b0 * ldy, ldy, epi, st);
@@ -954,13 +1081,19 @@ extern "C" int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch
                                    const float* sw, const float* bias, void* y, int64_t ldy,
                                    int32_t flags, void* stream) {
   return lc_wo_linear_s8_ex(x, x_dtype, batch, K, ldx, wq, ldw, N, sw, bias, 0, nullptr, nullptr, 0, 0, y, ldy, flags,
-                            stream);
+                            nullptr, 0, stream);
+}
+
+extern "C" int64_t lc_wo_linear_workspace_bytes(int64_t N) {
+  if (N < 0) return 0;
+  return static_cast<int64_t>(sm_count()) * 2 * kRingSlotBytes + ((N + 15) / 16) * 4;
 }
 
 extern "C" int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
                                       const int8_t* wq, int64_t ldw, int64_t N, const float* sw, const float* bias,
                                       int32_t relu, const float* out_scale, const float* out_zp, int32_t quant_min,
-                                      int32_t quant_max, void* y, int64_t ldy, int32_t flags, void* stream) {
+                                      int32_t quant_max, void* y, int64_t ldy, int32_t flags, void* workspace,
+                                      int64_t workspace_bytes, void* stream) {
   const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;
   if (batch < 0 || N < 0 || K <= 0 || ldx < K || ldw < K || ldy < N)
     return fail(LC_ERR_INVALID_ARG, "wo_linear_s8: bad shape");
@@ -971,13 +1104,14 @@ extern "C" int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t ba
   cudaStream_t st = as_stream(stream);
   const WoEpilogue epi = {relu ? 1 : 0, out_scale, out_zp, static_cast<float>(quant_min),
                           static_cast<float>(quant_max)};
+  const RingScratch scratch = {workspace, workspace ? workspace_bytes : 0};
   switch (x_dtype) {
     case LC_F32:
-      return wo_linear_typed<float>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, epi, st);
+      return wo_linear_typed<float>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
     case LC_BF16:
-      return wo_linear_typed<__nv_bfloat16>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, epi, st);
+      return wo_linear_typed<__nv_bfloat16>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
     case LC_F16:
-      return wo_linear_typed<__half>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, epi, st);
+      return wo_linear_typed<__half>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
   }
   return fail(LC_ERR_UNSUPPORTED, "wo_linear_s8: x_dtype %d not supported", x_dtype);
 }
@@ -985,6 +1119,13 @@ extern "C" int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t ba
 extern "C" int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
                                    const int8_t* wq, int64_t ldw, int64_t N2, const float* sw,
                                    const float* bias, void* y, int64_t ldy, int32_t flags, void* stream) {
+  return lc_wo_swiglu_s8_ex(x, x_dtype, batch, K, ldx, wq, ldw, N2, sw, bias, y, ldy, flags, nullptr, 0, stream);
+}
+
+extern "C" int32_t lc_wo_swiglu_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
+                                      const int8_t* wq, int64_t ldw, int64_t N2, const float* sw,
+                                      const float* bias, void* y, int64_t ldy, int32_t flags, void* workspace,
+                                      int64_t workspace_bytes, void* stream) {
   const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;
   if (batch < 0 || N2 < 0 || K <= 0 || ldx < K || ldw < K || ldy < N2 / 2)
     return fail(LC_ERR_INVALID_ARG, "wo_swiglu_s8: bad shape");
@@ -996,12 +1137,13 @@ extern "C" int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch
     return fail(LC_ERR_UNSUPPORTED, "wo_swiglu_s8: K, ldw must be multiples of 16, ldx of 8, pointers 16-byte aligned");
   cudaStream_t st = as_stream(stream);
   const WoEpilogue none = {0, nullptr, nullptr, 0.0f, 0.0f};
+  const RingScratch scratch = {workspace, workspace ? workspace_bytes : 0};
   if (x_dtype == LC_BF16)
     return launch_wo_tma<__nv_bfloat16, true>(static_cast<const __nv_bfloat16*>(x), batch, K, ldx, wq, ldw, N2, sw,
-                                              bias, static_cast<__nv_bfloat16*>(y), ldy, overlap, none, st);
+                                              bias, static_cast<__nv_bfloat16*>(y), ldy, overlap, none, scratch, st);
   if (x_dtype == LC_F16)
     return launch_wo_tma<__half, true>(static_cast<const __half*>(x), batch, K, ldx, wq, ldw, N2, sw, bias,
-                                       static_cast<__half*>(y), ldy, overlap, none, st);
+                                       static_cast<__half*>(y), ldy, overlap, none, scratch, st);
   return fail(LC_ERR_UNSUPPORTED, "wo_swiglu_s8: activations must be bf16 or f16");
 }
 

@@ -408,6 +408,33 @@ def qlinear_i8(a, b, sx, sw, bias=None, zx=None, wsum=None, out_dtype: torch.dty
     return out
 
 
+_ACT_SCHEME_ID = {"tensor_affine": 0, "tensor_symmetric": 1, "token_symmetric": 2}
+
+
+def dynamic_linear_workspace(rows: int, cols: int, dev: torch.device) -> torch.Tensor:
+    """Uninitialised scratch for :func:`dynamic_linear` (codes, scales, range scratch) for inputs of up
+    to ``rows`` x ``cols``; pass ``fresh=True`` with it once."""
+    return torch.empty(int(lib.lc_dynamic_linear_workspace_bytes(rows, cols)), dtype=torch.uint8, device=dev)
+
+
+def dynamic_linear(x2d: torch.Tensor, act_scheme: str, qmin: int, qmax: int, signed: bool, wq: torch.Tensor, sw, bias,
+                   wsum, workspace: torch.Tensor, fresh: bool, out_dtype: torch.dtype = torch.float32,
+                   eps: float = 1e-8, status=None) -> torch.Tensor:
+    """Forward of the dynamic Linear from one library call: quantize the fp32 ``x2d`` on the grid
+    ``act_scheme`` and run the int8 GEMM against ``wq`` (16-byte row pitch), ``sw``, ``bias``.
+    Arguments are taken as they are (contiguous fp32 tensors on one device); this is the
+    low-overhead path of :class:`lucid_b200.nn.quantized.dynamic.Linear`."""
+    dev = x2d.device
+    m, k = x2d.shape
+    n = wq.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=dev)
+    check(lib.lc_dynamic_linear_f32(x2d.data_ptr(), x2d.stride(0), m, k, _ACT_SCHEME_ID[act_scheme], int(qmin), int(qmax),
+                                    1 if signed else 0, float(eps), wq.data_ptr(), wq.stride(0), n, _ptr(sw), _ptr(bias),
+                                    _ptr(wsum), out.data_ptr(), _lc_dtype(out_dtype), n, workspace.data_ptr(),
+                                    workspace.numel(), 1 if fresh else 0, _ptr(status), _stream(dev)))
+    return out
+
+
 def qlinear_i8_into(a, b, sx, sw, out_ptrs, ldo: int, out_dtype: torch.dtype = torch.float32, bias=None, zx=None,
                     wsum=None, status: torch.Tensor | None = None, variant: int = 0, multicast: bool = False) -> None:
     """:func:`qlinear_i8` writing each output tile to every buffer in ``out_ptrs`` (1..8 raw
@@ -594,15 +621,34 @@ def wo_gemm_16(a: torch.Tensor, n_terms: int, w16: torch.Tensor, sw=None, bias=N
 # ----------------------------------------------------------------------------
 # weight-only paths
 # ----------------------------------------------------------------------------
+_WO_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+_WO_WORKSPACE_ROWS = 1 << 20  # tickets for weights of up to this many rows; larger ones run without scratch
+
+
+def wo_workspace(dev: torch.device, rows: int):
+    """Zero-filled scratch of the weight-streaming kernels' balanced schedule, one per (device,
+    stream): launches on one stream are ordered, so they can share it.  ``None`` for weights with
+    more rows than the scratch has tickets for (the kernel then hands out whole boxes)."""
+    if rows > _WO_WORKSPACE_ROWS:
+        return None
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev))
+    ws = _WO_WORKSPACES.get(key)
+    if ws is None:
+        ws = torch.zeros(int(lib.lc_wo_linear_workspace_bytes(_WO_WORKSPACE_ROWS)), dtype=torch.uint8, device=dev)
+        _WO_WORKSPACES[key] = ws
+    return ws
+
+
 def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous: bool = False, relu: bool = False, out_scale=None,
-                 out_zp=None, quant_min: int = 0, quant_max: int = 255):
+                 out_zp=None, quant_min: int = 0, quant_max: int = 255, balanced: bool = True):
     """``y = (x @ wq^T) * sw + bias`` with float activations; ``y`` has ``x``'s dtype.  With
     ``relu`` / ``out_scale`` and ``out_zp`` (device scalars) the same kernel goes on to apply the
     ReLU and the fake-quantize onto the calibrated output grid of a static Linear.
 
     ``overlap_previous`` lets the kernel start (and prefetch weights) while the kernel before
     it on the stream drains; the caller asserts that ``wq``, ``sw`` and ``bias`` were complete
-    before that kernel started."""
+    before that kernel started.  ``balanced`` (default) gives the weight-streaming kernel its scratch, so
+    that every SM streams the same number of bytes; without it whole 32-row boxes are dealt out."""
     dev = _need_cuda(x2d, wq, sw, bias, out_scale, out_zp)
     if x2d.dtype not in (torch.float32, torch.bfloat16, torch.float16):
         raise TypeError(f"wo_linear_s8: activations must be fp32/bf16/fp16, got {x2d.dtype}")
@@ -621,10 +667,12 @@ def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous: bool = False, relu: b
     os_c = None if out_scale is None else _f32c(out_scale)
     oz_c = None if out_zp is None else _f32c(out_zp)
     with _on(dev):
+        ws = wo_workspace(dev, N) if balanced else None
         check(lib.lc_wo_linear_s8_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq.data_ptr(),
                                      wq.stride(0), N, _ptr(sw_c), _ptr(bias_c), 1 if relu else 0, _ptr(os_c),
                                      _ptr(oz_c), int(quant_min), int(quant_max), y.data_ptr(), N,
-                                     1 if overlap_previous else 0, _stream(dev)))
+                                     1 if overlap_previous else 0, _ptr(ws), 0 if ws is None else ws.numel(),
+                                     _stream(dev)))
     return y
 
 
@@ -640,7 +688,7 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.cat([g, u], dim=1).reshape(2 * f, *gate.shape[1:]).contiguous()
 
 
-def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None, overlap_previous: bool = False):
+def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None, overlap_previous: bool = False, balanced: bool = True):
     """``silu(x @ Wg^T * sg) * (x @ Wu^T * su)`` with interleaved int8 gate/up weights
     (see :func:`interleave_gate_up`); bf16 / f16 activations, batch <= 32.
     ``overlap_previous`` as for :func:`wo_linear_s8`."""
@@ -652,9 +700,11 @@ def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None, overlap_previous: bool = False
     sw_c = None if sw_gu is None else _f32c(sw_gu)
     bias_c = None if bias_gu is None else _f32c(bias_gu)
     with _on(dev):
-        check(lib.lc_wo_swiglu_s8(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq_gu.data_ptr(),
-                                  wq_gu.stride(0), N2, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N2 // 2,
-                                  1 if overlap_previous else 0, _stream(dev)))
+        ws = wo_workspace(dev, N2) if balanced else None
+        check(lib.lc_wo_swiglu_s8_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq_gu.data_ptr(),
+                                     wq_gu.stride(0), N2, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N2 // 2,
+                                     1 if overlap_previous else 0, _ptr(ws), 0 if ws is None else ws.numel(),
+                                     _stream(dev)))
     return y
 
 

@@ -107,6 +107,7 @@ class Linear(nn.Module):
         else:
             self.bias = None
         self._cache = Int8WeightCache()
+        self._scratches = {}
 
     def set_activation_scheme(self, scheme: str, qdtype: QDtype | None = None) -> "Linear":
         """Choose the activation grid; symmetric schemes default to ``qint8``."""
@@ -129,7 +130,30 @@ class Linear(nn.Module):
         needs_zp = not (symmetric and qd.signed)
         return xq, sx, (zx if needs_zp else None)
 
+    def _scratch(self, rows: int, device: torch.device, stream: int):
+        """Workspace of the single-call forward, one per (device, stream) this layer has been used
+        on, grown when a larger batch arrives.  Returns ``(buffer, fresh)``."""
+        key = (device, stream)
+        have = self._scratches.get(key)
+        if have is not None and have[0] >= rows:
+            return have[1], False
+        buf = _backend.ops().dynamic_linear_workspace(rows, self.in_features, device)
+        self._scratches[key] = (rows, buf)
+        return buf, True
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        ops = _backend.ops()
+        if (x.is_cuda and x.dtype is torch.float32 and not _shared_input.active and x.is_contiguous()
+                and self.weight_int8.device == x.device and x.numel() > 0 and hasattr(ops, "dynamic_linear")
+                and torch.cuda.current_device() == x.device.index):
+            # the common eager case in one library call: no intermediate tensors, one stream query
+            x2 = x.view(-1, self.in_features)
+            wq, wsum = self._cache.get(self.weight_int8, self.weight_zero_point)
+            ws, fresh = self._scratch(x2.shape[0], x.device, torch.cuda.current_stream(x.device).cuda_stream)
+            qd = self.act_qdtype
+            y = ops.dynamic_linear(x2, self.act_scheme, qd.quant_min, qd.quant_max, qd.signed, wq, self.weight_scale,
+                                   self.bias, wsum, ws, fresh, self.out_dtype)
+            return y.view(*x.shape[:-1], self.out_features)
         if self.weight_zero_point.is_cuda and x.is_cuda and x.device != self.weight_int8.device:
             raise RuntimeError(f"input on {x.device} but weights on {self.weight_int8.device}")
         xd = _backend.on_cuda(x)
@@ -142,7 +166,6 @@ class Linear(nn.Module):
         else:
             hit = None
             if x.is_cuda and _shared_input.active:
-                ops = _backend.ops()
                 key = (self.act_scheme, self.act_qdtype.name, self.in_features, ops.capture_id(xd.device),
                        torch.cuda.current_stream(xd.device).cuda_stream)
                 hit = _shared_input.get(x, key)
@@ -152,9 +175,9 @@ class Linear(nn.Module):
             if hit is None:
                 hit = self._quantize_activations(x2)
             xq, sx, zx = hit
-            y = _backend.ops().qlinear_i8(xq, wq, sx, _backend.on_cuda(self.weight_scale),
-                                 bias=None if self.bias is None else _backend.on_cuda(self.bias), zx=zx,
-                                 wsum=wsum if zx is not None else None, out_dtype=self.out_dtype)
+            y = ops.qlinear_i8(xq, wq, sx, _backend.on_cuda(self.weight_scale),
+                               bias=None if self.bias is None else _backend.on_cuda(self.bias), zx=zx,
+                               wsum=wsum if zx is not None else None, out_dtype=self.out_dtype)
         y = y.reshape(*xd.shape[:-1], self.out_features)
         return y if x.is_cuda else y.to(x.device)
 

@@ -247,3 +247,45 @@ def test_quantized_matmul_backward(transpose, bits):
         assert torch.allclose(gx, gx2, rtol=1e-4, atol=1e-4 * float(gx2.abs().max()))
     with torch.no_grad():
         assert not G.quantized_matmul(torch.randn(2, 128, device="cuda"), wq, sc, bi, group_size=64, bits=bits).requires_grad
+
+
+@pytest.mark.parametrize("B,N,K", [(1, 4096, 14336), (4, 28672, 4096), (16, 4096, 14336), (8, 2048, 2048), (3, 2050, 2064),
+                                   (5, 16, 262144), (2, 37000, 128), (32, 6000, 3008)])
+def test_balanced_schedule_agrees_with_whole_boxes(ops, B, N, K):
+    """The schedule that cuts K between CTAs (equal bytes per SM) against the one that deals out whole
+    boxes: both within the rounding bound of the float64 product, equal to each other up to the last
+    bits (sums over a split K range are added in another order), bit-identical from launch to launch,
+    and the scratch (tickets) back at zero after every launch."""
+    g = torch.Generator(device="cuda").manual_seed(B + N + K)
+    wq = torch.randint(-128, 128, (N, K), device="cuda", dtype=torch.int8, generator=g)
+    sw = torch.rand(N, device="cuda", generator=g) * 0.01 + 0.001
+    x = torch.randn(B, K, device="cuda", generator=g).to(torch.bfloat16)
+    ref = ((x.double() @ wq.double().T) * sw.double()[None, :]).cpu().numpy()
+    whole = ops.wo_linear_s8(x, wq, sw, balanced=False)
+    split = ops.wo_linear_s8(x, wq, sw, balanced=True)
+    for y in (whole, split):
+        assert_rounded_product(y, ref, abs_terms(x, wq, sw), K, torch.bfloat16)
+    assert (whole.float() - split.float()).abs().max() <= 2.0 ** -7 * whole.float().abs().max()
+    for i in range(10):
+        again = ops.wo_linear_s8(x, wq, sw, balanced=True, overlap_previous=bool(i & 1))
+        assert torch.equal(again.view(torch.int16), split.view(torch.int16))
+    torch.cuda.synchronize()
+    ws = ops.wo_workspace(x.device, N)
+    tickets = ws[-(ops._WO_WORKSPACE_ROWS // 16) * 4:]  # the tail of the scratch holds the tickets
+    assert not bool(tickets.any())
+    assert ops.wo_linear_status() == 0
+
+
+@pytest.mark.parametrize("B,F,K", [(1, 14336, 4096), (16, 14336, 4096), (9, 4096, 2064)])
+def test_balanced_swiglu_agrees_with_whole_boxes(ops, B, F, K):
+    g = torch.Generator(device="cuda").manual_seed(F + K + B)
+    wgu = torch.randint(-128, 128, (2 * F, K), device="cuda", dtype=torch.int8, generator=g)
+    sgu = torch.rand(2 * F, device="cuda", generator=g) * 2e-3
+    x = torch.randn(B, K, device="cuda", generator=g).to(torch.bfloat16)
+    whole = ops.wo_swiglu_s8(x, wgu, sgu, balanced=False)
+    split = ops.wo_swiglu_s8(x, wgu, sgu, balanced=True)
+    assert torch.allclose(whole.float(), split.float(), rtol=2.0 ** -6, atol=2.0 ** -7 * float(whole.float().abs().max()))
+    for i in range(6):
+        assert torch.equal(ops.wo_swiglu_s8(x, wgu, sgu, balanced=True, overlap_previous=bool(i & 1)).view(torch.int16),
+                           split.view(torch.int16))
+    assert ops.wo_linear_status() == 0
