@@ -476,6 +476,72 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
         dec[f"batch_{batch}"] = entry
     out["decode_mlp_4096x14336_w8a16"] = dec
     del sets
+    # ---- statically quantized Linear of an FFN shape (8192 x 2048 x 512, fp32 in and out): the fused
+    # forward (digit split + exact int8 tensor-core product with scale / bias / requant epilogue) against
+    # the reference's formulation run on the same GPU (dequantize W, fp32 GEMM, fake-quantize chain)
+    try:
+        Ms, Ns, Ks = 8192, 2048, 512
+        xs = torch.randn(Ms, Ks, device=dev, generator=g)
+        wq_s = torch.randint(-128, 128, (Ns, Ks), device=dev, dtype=torch.int8, generator=g)
+        sw_s = torch.rand(Ns, device=dev, generator=g) * 1e-3 + 1e-4
+        b_s = torch.randn(Ns, device=dev, generator=g) * 0.1
+        S, Z = torch.tensor(0.02, device=dev), torch.tensor(128.0, device=dev)
+
+        def fused():
+            digits, rs, _ = ops.split_f32_digits(xs)
+            return ops.wo_gemm_digits(digits, rs, wq_s, sw=sw_s, bias=b_s, out_scale=S, out_zp=Z, quant_min=0, quant_max=255)
+
+        prev_tf32 = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+
+        def chain():
+            w = ops.dequantize(wq_s, sw_s, torch.zeros_like(sw_s), ch_axis=0)
+            return ops.fake_quantize(torch.nn.functional.linear(xs, w, b_s), S, Z, 0, 255)[0]
+
+        t_f, t_c = time_loop(torch, fused, 30, 5), time_loop(torch, chain, 30, 5)
+        digits, rs, _ = ops.split_f32_digits(xs)
+        t_g = time_loop(torch, lambda: ops.wo_gemm_digits(digits, rs, wq_s, sw=sw_s, bias=b_s, out_scale=S, out_zp=Z), 30, 5)
+        torch.backends.cuda.matmul.allow_tf32 = prev_tf32
+        flipped = float((fused() != chain()).float().mean())
+        out["static_linear_8192x2048x512"] = {
+            "fused_us": t_f * 1e3, "gemm_kernel_us": t_g * 1e3, "split_kernel_us": (t_f - t_g) * 1e3,
+            "dequantize_sgemm_fake_quantize_chain_us": t_c * 1e3, "speedup": t_c / t_f,
+            "effective_TFLOPs": 2.0 * Ms * Ns * Ks / t_f / 1e9,
+            "int8_TOPS_of_the_digit_product": 4 * 2.0 * Ms * Ns * Ks / t_g / 1e9,
+            "outputs_one_grid_step_apart_from_the_fp32_chain": flipped}
+        del xs, wq_s, digits
+    except Exception as e:  # noqa: BLE001
+        out["static_linear_8192x2048x512"] = {"error": repr(e)[:300]}
+    # ---- group-wise 8-bit weights [14336, 4096], groups of 64, bf16 activations (the decode shape of the
+    # reference's packed path): packed bytes + scales + biases once per call
+    try:
+        Ng, Kg = 14336, 4096
+        packs = []
+        for _ in range(4):  # 4 x 66 MB rotate so that no call finds its weights in L2
+            w = torch.randn(Ng, Kg, device=dev, generator=g) * 0.02
+            packs.append(ops.group_quantize(w, 64, 8))
+            del w
+        gm = {}
+        for batch in (1, 4, 16):
+            xg = torch.randn(batch, Kg, device=dev, generator=g).to(torch.bfloat16)
+            turn = [0]
+
+            def gstep():
+                p_, s_, b_ = packs[turn[0] % 4]
+                turn[0] += 1
+                return ops.group_matmul(xg, p_, s_, b_, 64, 8, overlap_previous=True)
+
+            nbytes = Ng * Kg + 2 * Ng * (Kg // 64) * 4
+            try:
+                ms = graph_time(torch, gstep, reps=8, replays=10)
+            except Exception:
+                ms = time_loop(torch, gstep, 40, 5)
+            gm[f"batch_{batch}"] = {"us": ms * 1e3, "GB/s": nbytes / ms / 1e6, "algorithmic_bytes": nbytes,
+                                    "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}
+        out["group_matmul_14336x4096_gs64_8bit"] = gm
+        del packs
+    except Exception as e:  # noqa: BLE001
+        out["group_matmul_14336x4096_gs64_8bit"] = {"error": repr(e)[:300]}
     # ---- small transformer encoder, every Linear dynamic int8 (6 layers, d 512, 8 heads, FFN 2048)
     try:
         out["encoder_6x512_b32_s256"] = encoder_extras(torch, dev, g)
@@ -581,6 +647,35 @@ def run_profile_case(args) -> int:
               "quantize_tensor": lambda: ops.dynamic_quantize_tensor(x, True, -128, 127, True, 1e-8, torch.int8),
               "dequantize": lambda: ops.dequantize(q, s, z, ch_axis=0),
               "quantize_given_scale": lambda: ops.quantize(x, s, z, -128, 127, torch.int8, ch_axis=0)}[case]
+    elif case == "static_linear":
+        xs = torch.randn(8192, 512, device=dev, generator=g)
+        wq_s = torch.randint(-128, 128, (2048, 512), device=dev, dtype=torch.int8, generator=g)
+        sw_s, b_s = torch.rand(2048, device=dev) * 1e-3, torch.randn(2048, device=dev)
+        S, Z = torch.tensor(0.02, device=dev), torch.tensor(128.0, device=dev)
+
+        def fn():
+            digits, rs, _ = ops.split_f32_digits(xs)
+            return ops.wo_gemm_digits(digits, rs, wq_s, sw=sw_s, bias=b_s, out_scale=S, out_zp=Z)
+    elif case == "static_linear_longk":
+        xs = torch.randn(4096, 8192, device=dev, generator=g)
+        wq_s = torch.randint(-128, 128, (7168, 8192), device=dev, dtype=torch.int8, generator=g)
+        sw_s, b_s = torch.rand(7168, device=dev) * 1e-3, torch.randn(7168, device=dev)
+
+        def fn():
+            digits, rs, _ = ops.split_f32_digits(xs)
+            return ops.wo_gemm_digits(digits, rs, wq_s, sw=sw_s, bias=b_s)
+    elif case == "group_gemv":
+        packs = []
+        for _ in range(4):
+            w = torch.randn(14336, 4096, device=dev, generator=g) * 0.02
+            packs.append(ops.group_quantize(w, 64, 8))
+        xb = torch.randn(int(args.profile_batch), 4096, device=dev, generator=g).to(torch.bfloat16)
+        i = [0]
+
+        def fn():
+            p_, s_, b_ = packs[i[0] % 4]
+            i[0] += 1
+            return ops.group_matmul(xb, p_, s_, b_, 64, 8)
     elif case == "wo_gemv":
         ws = []
         for _ in range(4):
@@ -1052,7 +1147,8 @@ def main() -> int:
                     help="headline workload only: skip the companion workloads and the CPU baseline")
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed case of one kernel (gemm, quantize_rows, quantize_tensor, "
-                         "dequantize, quantize_given_scale, histc, merge, embedding, embedding_bag, gemm_small, gemm_shortk, wo_gemv) for a profiler capture; prints no bench line")
+                         "dequantize, quantize_given_scale, histc, merge, embedding, embedding_bag, gemm_small, gemm_shortk, wo_gemv, "
+                         "static_linear, static_linear_longk, group_gemv) for a profiler capture; prints no bench line")
     ap.add_argument("--profile-batch", default=4)
     ap.add_argument("--gather", choices=("auto", "fused", "multimem", "copy", "nccl"), default="auto",
                     help="N > 1: how output shards are exchanged (auto = time fused / copy / multimem once, keep the fastest)")

@@ -88,6 +88,7 @@ SIGNATURES = {
     "lc_wo_linear_status": (_i32, [C.POINTER(_i32), _i32]),
     "lc_group_quantize_f32": (_i32, [_p, _i64, _i64, _i32, _i32, _p, _p, _p, _p]),
     "lc_group_dequantize": (_i32, [_p, _p, _p, _i64, _i64, _i32, _i32, _p, _p]),
+    "lc_group_matmul_ex": (_i32, [_p, _i32, _i64, _i64, _p, _p, _p, _i64, _i32, _i32, _p, _i32, _p, _i64, _p]),
     "lc_group_matmul": (_i32, [_p, _i32, _i64, _i64, _p, _p, _p, _i64, _i32, _i32, _p, _p]),
     "lc_embedding_s8_f32": (_i32, [_p, _p, _p, _p, _i64, _i64, _i64, _p, _p, _p]),
     "lc_embedding_bag_s8_f32": (_i32, [_p, _p, _p, _p, _i64, _p, _i64, _p, _i64, _i64, _i32, _i64, _i32, _p, _p, _p]),

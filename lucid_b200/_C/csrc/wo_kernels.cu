@@ -374,13 +374,21 @@ __device__ __forceinline__ int ring_owner(long long u, long long units, int grid
 // GRP = row tiles per TMA box (1 or 2): the copy engine of an SM completes boxes one after the
 // other at a rate that hardly depends on their size, so 32-row boxes double what one SM can pull
 // from DRAM.  tmap_w has GRP*16-row boxes; tmap_w1 has 16-row boxes for the odd last tile of a pass.
-template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP>
+// GS = 0: per-output-channel symmetric int8 weights (sw = one scale per row).
+// GS = 64 or 128: the 8-bit group-wise affine format (lucid/_C/ops/quantized/QuantizedMatmul.cpp:143-207):
+// the packed words ARE the codes as unsigned bytes in K order, `sw` / `bias` are the [N, K / GS] group
+// scales and biases.  A warp's 64-byte slice of a row lies inside one group, so the four MMAs of an item
+// give the group's raw sum, which enters the running total as s * sum(x * c) + b * sum(x) -- the second
+// sum being the all-ones MMA of the chunk.
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0>
 __global__ void __launch_bounds__(ring::kThreads, 1)
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w1,
                       const __grid_constant__ CUtensorMap tmap_x,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
                       const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, const RingPlan plan,
                       int overlap, const WoEpilogue epi) {
+  static_assert(GS == 0 || GS == 64 || GS == 128, "group sizes the 64-byte warp slice fits into");
+  static_assert(GS == 0 || !SWIGLU, "the fused SwiGLU epilogue is for per-channel weights");
   using namespace ring;
   constexpr int S = stages(NT, TMAX, XB, GRP);
   constexpr int GSTAGE = STAGE * GRP;
@@ -549,6 +557,12 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
             for (int i = 0; i < 8; ++i) xa[nt][i] = 0u;
           }
         }
+        if (GS != 0) {  // sums of x are per group: restart them for this chunk
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xsum[nt][i] = 0.0f;
+        }
         if (warp_k_ok) {
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
@@ -560,6 +574,20 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                             RawOperand<XT>::kOnes, xa[nt][2 * q], xa[nt][2 * q + 1]);
           }
         }
+        // group-wise format: scale and bias of this warp's group for rows g and g + 8 of the first tile
+        // (those of tile j + 1 are fetched while tile j is being multiplied)
+        const int64_t n_groups = GS ? K / (GS ? GS : 1) : 0;
+        const int64_t grp = GS ? (static_cast<int64_t>(kc) * KC + warp * 64) / (GS ? GS : 1) : 0;
+        float gq[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // s[row g], s[row g + 8], b[row g], b[row g + 8]
+        auto fetch_group = [&](int j, float (&out)[4]) {
+          const int64_t ra = ((static_cast<int64_t>(ps.tile0) + j) << 4) + g, rb = ra + 8;
+          const bool live = warp_k_ok && j < pass_tiles;
+          out[0] = (live && ra < N) ? __ldg(sw + ra * n_groups + grp) : 0.0f;
+          out[1] = (live && rb < N) ? __ldg(sw + rb * n_groups + grp) : 0.0f;
+          out[2] = (live && ra < N) ? __ldg(bias + ra * n_groups + grp) : 0.0f;
+          out[3] = (live && rb < N) ? __ldg(bias + rb * n_groups + grp) : 0.0f;
+        };
+        if (GS != 0) fetch_group(0, gq);
 #pragma unroll
         for (int j = 0; j < TMAX; ++j) {
           if (j < pass_tiles && ok) {
@@ -578,14 +606,43 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                   w1 = wo_lds128(src + 8 * W_PITCH);
                 }
                 const uint32_t r0[4] = {w0.x, w0.y, w0.z, w0.w}, r1[4] = {w1.x, w1.y, w1.z, w1.w};
+                if constexpr (GS == 0) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const uint32_t u0 = r0[q] ^ 0x80808080u, u1 = r1[q] ^ 0x80808080u;
-                  const uint32_t a0 = __byte_perm(u0, 0u, 0x4140u), a2 = __byte_perm(u0, 0u, 0x4342u);
-                  const uint32_t a1 = __byte_perm(u1, 0u, 0x4140u), a3 = __byte_perm(u1, 0u, 0x4342u);
+                  for (int q = 0; q < 4; ++q) {
+                    const uint32_t u0 = r0[q] ^ 0x80808080u, u1 = r1[q] ^ 0x80808080u;
+                    const uint32_t a0 = __byte_perm(u0, 0u, 0x4140u), a2 = __byte_perm(u0, 0u, 0x4342u);
+                    const uint32_t a1 = __byte_perm(u1, 0u, 0x4140u), a3 = __byte_perm(u1, 0u, 0x4342u);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                      mma_16816<XT>(acc[j][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                  }
+                } else {
+                  float gnext[4];
+                  fetch_group(j + 1, gnext);  // in flight while this tile's MMAs run
+                  float part[NT][4];
 #pragma unroll
                   for (int nt = 0; nt < NT; ++nt)
-                    mma_16816<XT>(acc[j][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) part[nt][i] = 0.0f;
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {  // the codes are unsigned bytes already
+                    const uint32_t a0 = __byte_perm(r0[q], 0u, 0x4140u), a2 = __byte_perm(r0[q], 0u, 0x4342u);
+                    const uint32_t a1 = __byte_perm(r1[q], 0u, 0x4140u), a3 = __byte_perm(r1[q], 0u, 0x4342u);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+                      mma_16816<XT>(part[nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                  }
+                  // raw sums -> values: sum(x c) = part * acc_scale, sum(x) = xsum * (sum_scale / 128)
+                  const float c1 = RawOperand<XT>::acc_scale(), cx = RawOperand<XT>::sum_scale() * 0.0078125f;
+#pragma unroll
+                  for (int nt = 0; nt < NT; ++nt) {
+                    acc[j][nt][0] = fmaf(part[nt][0] * c1, gq[0], fmaf(xsum[nt][0] * cx, gq[2], acc[j][nt][0]));
+                    acc[j][nt][1] = fmaf(part[nt][1] * c1, gq[0], fmaf(xsum[nt][1] * cx, gq[2], acc[j][nt][1]));
+                    acc[j][nt][2] = fmaf(part[nt][2] * c1, gq[1], fmaf(xsum[nt][0] * cx, gq[3], acc[j][nt][2]));
+                    acc[j][nt][3] = fmaf(part[nt][3] * c1, gq[1], fmaf(xsum[nt][1] * cx, gq[3], acc[j][nt][3]));
+                  }
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) gq[i] = gnext[i];
                 }
               }
               if (j % GRP == GRP - 1 || j == pass_tiles - 1) {
@@ -613,7 +670,8 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           float* mine = red + (j * kConsumerWarps + warp) * 16 * RP;
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            const float c1 = RawOperand<XT>::acc_scale(), c2 = RawOperand<XT>::sum_scale();
+            // per-channel weights: raw sums -> sum(x * s8), the offset 128 * sum(x) taken out once per pass
+            const float c1 = GS ? 1.0f : RawOperand<XT>::acc_scale(), c2 = GS ? 0.0f : RawOperand<XT>::sum_scale();
             mine[g * RP + nt * 8 + 2 * t] = acc[j][nt][0] * c1 - xsum[nt][0] * c2;
             mine[g * RP + nt * 8 + 2 * t + 1] = acc[j][nt][1] * c1 - xsum[nt][1] * c2;
             mine[(g + 8) * RP + nt * 8 + 2 * t] = acc[j][nt][2] * c1 - xsum[nt][0] * c2;
@@ -694,8 +752,11 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
             const int r = o & 15, bcol = (o >> 4) % COLS, j = (o >> 4) / COLS;
             const int64_t n = ((static_cast<int64_t>(ps.tile0) + j) << 4) + r;
             if (n < N && bcol < nb) {
-              float v = total(j, r, bcol) * (sw ? __ldg(sw + n) : 1.0f);
-              if (bias) v += __ldg(bias + n);
+              float v = total(j, r, bcol);
+              if constexpr (GS == 0) {
+                v *= sw ? __ldg(sw + n) : 1.0f;
+                if (bias) v += __ldg(bias + n);
+              }
               y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(wo_finish(v, epi));
             }
           }
@@ -921,12 +982,12 @@ struct RingScratch {
 };
 constexpr int64_t kRingSlotBytes = 2 * 16 * 32 * 4;  // largest GRP * 16 rows * COLS floats
 
-template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP>
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0>
 static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                    int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
                                    int64_t ldy, bool overlap, const WoEpilogue& epi, const RingScratch& scratch,
                                    cudaStream_t st) {
-  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU, GRP>;
+  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU, GRP, GS>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
   int dev = 0;
@@ -1060,6 +1121,35 @@ static int32_t launch_group_matmul(const XT* x, int64_t B, int64_t K, const uint
     group_matmul_kernel<XT, BITS, 8><<<grid, kWoThreads, 0, st>>>(x, B, K, packed, scales, biases, N, gs, y);
   }
   return check_launch("group_matmul");
+}
+
+// 8-bit group-wise weights of a few MB and more on the streaming kernel (16-bit activations, groups of
+// 64 or 128): the packed words are the code bytes in K order, so the weight is streamed exactly like a
+// per-channel int8 matrix and the group scales / biases are read by the consumer warps.
+template <typename XT, int GS>
+static int32_t launch_group_ring(const XT* x, int64_t B, int64_t K, const uint8_t* codes, const float* scales,
+                                 const float* biases, int64_t N, XT* y, bool overlap, const RingScratch& scratch,
+                                 cudaStream_t st) {
+  const WoEpilogue none = {0, nullptr, nullptr, 0.0f, 0.0f};
+  const int8_t* w = reinterpret_cast<const int8_t*>(codes);
+  const int64_t tiles = (N + 15) / 16, sms = sm_count();
+  const bool few = (tiles + sms - 1) / sms <= 2;
+  for (int64_t b0 = 0; b0 < B; b0 += 32) {
+    const int64_t bc = B - b0 < 32 ? B - b0 : 32;
+    const XT* xb = x + b0 * K;
+    XT* yb = y + b0 * N;
+    int32_t rc;
+    if (bc <= 8)
+      rc = few ? launch_wo_ring_inst<XT, 1, 2, 4, false, 2, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
+               : launch_wo_ring_inst<XT, 1, 4, 2, false, 2, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+    else if (bc <= 16)
+      rc = few ? launch_wo_ring_inst<XT, 2, 2, 3, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
+               : launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+    else
+      rc = launch_wo_ring_inst<XT, 4, 1, 2, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+    if (rc) return rc;
+  }
+  return LC_OK;
 }
 
 static int32_t check_group_args(int64_t N, int64_t K, int32_t gs, int32_t bits) {
@@ -1201,12 +1291,32 @@ extern "C" int32_t lc_group_matmul(const void* x, int32_t x_dtype, int64_t batch
                                    const int32_t* packed, const float* scales, const float* biases,
                                    int64_t N, int32_t group_size, int32_t bits, void* y,
                                    void* stream) {
+  return lc_group_matmul_ex(x, x_dtype, batch, K, packed, scales, biases, N, group_size, bits, y, 0, nullptr, 0, stream);
+}
+
+extern "C" int32_t lc_group_matmul_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K,
+                                      const int32_t* packed, const float* scales, const float* biases,
+                                      int64_t N, int32_t group_size, int32_t bits, void* y, int32_t flags,
+                                      void* workspace, int64_t workspace_bytes, void* stream) {
   if (int32_t rc = check_group_args(N, K, group_size, bits)) return rc;
   if (batch < 0) return fail(LC_ERR_INVALID_ARG, "group_matmul: bad batch");
   if (batch == 0 || N == 0) return LC_OK;
   if (!x || !packed || !scales || !biases || !y) return fail(LC_ERR_INVALID_ARG, "group_matmul: null pointer");
   cudaStream_t st = as_stream(stream);
   const uint32_t* pk = reinterpret_cast<const uint32_t*>(packed);
+  // weights from a few MB up, 8-bit codes in groups of 64 / 128, 16-bit activations: the streaming kernel
+  const bool stream_ok = bits == 8 && (group_size == 64 || group_size == 128) && (x_dtype == LC_BF16 || x_dtype == LC_F16) &&
+                         K % 16 == 0 && N * K >= (int64_t{4} << 20) && aligned(packed, 16) && aligned(x, 16);
+  if (stream_ok) {
+    const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;
+    const RingScratch scratch = {workspace, workspace ? workspace_bytes : 0};
+    const uint8_t* codes = reinterpret_cast<const uint8_t*>(packed);
+#define LC_GR(XT, GS) \
+  launch_group_ring<XT, GS>(static_cast<const XT*>(x), batch, K, codes, scales, biases, N, static_cast<XT*>(y), overlap, scratch, st)
+    if (x_dtype == LC_BF16) return group_size == 64 ? LC_GR(__nv_bfloat16, 64) : LC_GR(__nv_bfloat16, 128);
+    return group_size == 64 ? LC_GR(__half, 64) : LC_GR(__half, 128);
+#undef LC_GR
+  }
 #define LC_GM(XT)                                                                                     \
   (bits == 8 ? launch_group_matmul<XT, 8>(static_cast<const XT*>(x), batch, K, pk, scales, biases, N, \
                                           group_size, static_cast<XT*>(y), st)                        \

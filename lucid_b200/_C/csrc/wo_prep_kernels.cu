@@ -99,34 +99,42 @@ split_f32_bf16x3_kernel(const float* __restrict__ x, int64_t cols, int64_t ldx, 
 }
 
 // fp32 row -> four signed base-256 digit planes of round(x * 2^e), 2^e the power of two that puts the
-// row's largest magnitude into [2^29, 2^30).  One CTA per row: pass 1 finds the maximum, pass 2
-// re-reads the row (from L1/L2) and writes the digits of 4 elements as one 4-byte store per plane.
+// row's largest magnitude into [2^29, 2^30).  One team of threads per row: pass 1 finds the maximum,
+// pass 2 re-reads the row (from L1/L2) and writes the digits of 4 elements as one 4-byte store per plane.
 // Plane d of row m = 32t + r lives in row 128t + 32d + r of `digits`: the digit planes of 32 rows
 // make up one 128-row GEMM tile, plane d in accumulator lanes 32d .. 32d+31.
-template <bool VEC>
+template <bool VEC, int TEAM>
 __global__ void __launch_bounds__(kPrepThreads)
-split_f32_digits_kernel(const float* __restrict__ x, int64_t cols, int64_t ldx, int8_t* __restrict__ digits,
-                        int64_t ldd, float* __restrict__ row_scale, float* __restrict__ rowsum) {
+split_f32_digits_kernel(const float* __restrict__ x, int64_t rows, int64_t cols, int64_t ldx,
+                        int8_t* __restrict__ digits, int64_t ldd, float* __restrict__ row_scale,
+                        float* __restrict__ rowsum) {
+  // TEAM threads share a row: a whole CTA for long rows, one warp (8 rows per CTA) for short ones
+  static_assert(TEAM == 32 || TEAM == kPrepThreads, "a warp or the whole CTA per row");
+  constexpr int kTeams = kPrepThreads / TEAM;
   __shared__ float red[2 * (kPrepThreads / 32)];
   __shared__ float s_mul;
-  const int64_t r = blockIdx.x;
-  const float* xr = x + r * ldx;
+  const int team = threadIdx.x / TEAM, tid = threadIdx.x % TEAM;
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * kTeams + team;
+  const bool row_ok = r < rows;
+  const float* xr = x + (row_ok ? r : 0) * ldx;
   float mx = 0.0f, sum = 0.0f;
   bool bad = false;
-  for (int64_t k = static_cast<int64_t>(threadIdx.x) * 4; k < cols; k += kPrepThreads * 4) {
-    float v[4];
-    if (VEC && k + 4 <= cols) {
-      const float4 f = __ldg(reinterpret_cast<const float4*>(xr + k));
-      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
-    } else {
+  if (row_ok) {
+    for (int64_t k = static_cast<int64_t>(tid) * 4; k < cols; k += TEAM * 4) {
+      float v[4];
+      if (VEC && k + 4 <= cols) {
+        const float4 f = __ldg(reinterpret_cast<const float4*>(xr + k));
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+      } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] = k + e < cols ? xr[k + e] : 0.0f;
-    }
+        for (int e = 0; e < 4; ++e) v[e] = k + e < cols ? xr[k + e] : 0.0f;
+      }
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      mx = fmaxf(mx, fabsf(v[e]));
-      bad |= !(fabsf(v[e]) <= 3.402823466e38f);  // NaN or infinity
-      sum += v[e];
+      for (int e = 0; e < 4; ++e) {
+        mx = fmaxf(mx, fabsf(v[e]));
+        bad |= !(fabsf(v[e]) <= 3.402823466e38f);  // NaN or infinity
+        sum += v[e];
+      }
     }
   }
   if (bad) mx = INFINITY;
@@ -135,40 +143,42 @@ split_f32_digits_kernel(const float* __restrict__ x, int64_t cols, int64_t ldx, 
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     sum += __shfl_xor_sync(0xffffffffu, sum, o);
   }
-  if ((threadIdx.x & 31) == 0) {
-    red[threadIdx.x >> 5] = mx;
-    red[kPrepThreads / 32 + (threadIdx.x >> 5)] = sum;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float m = 0.0f, s = 0.0f;
+  if (TEAM != 32) {
+    if ((threadIdx.x & 31) == 0) {
+      red[threadIdx.x >> 5] = mx;
+      red[kPrepThreads / 32 + (threadIdx.x >> 5)] = sum;
+    }
+    __syncthreads();
+    mx = 0.0f;
+    sum = 0.0f;
     for (int w = 0; w < kPrepThreads / 32; ++w) {
-      m = fmaxf(m, red[w]);
-      s += red[kPrepThreads / 32 + w];
+      mx = fmaxf(mx, red[w]);
+      sum += red[kPrepThreads / 32 + w];
     }
-    // m = f * 2^ex with f in [0.5, 1): x * 2^(30 - ex) has magnitude below 2^30.  A non-finite row gets
-    // a NaN scale (its outputs become NaN); an all-zero row any scale.  e is capped so that 2^e and
-    // 2^-e stay normal numbers.
-    int ex = 0;
-    float mul = 1.0f, inv = 1.0f;
-    if (m > 3.402823466e38f) {
-      mul = 0.0f;
-      inv = __int_as_float(0x7fc00000);
-    } else if (m > 0.0f) {
-      frexpf(m, &ex);
-      int e = 30 - ex;
-      e = e > 126 ? 126 : e;
-      mul = __int_as_float((127 + e) << 23);
-      inv = __int_as_float((127 - e) << 23);
-    }
-    s_mul = mul;
-    row_scale[r] = inv;
-    if (rowsum) rowsum[r] = s;
   }
-  __syncthreads();
-  const float mul = s_mul;
+  // mx = f * 2^ex with f in [0.5, 1): x * 2^(30 - ex) has magnitude below 2^30.  A non-finite row gets
+  // a NaN scale (its outputs become NaN); an all-zero row any scale.  e is capped so that 2^e and
+  // 2^-e stay normal numbers.
+  float mul = 1.0f, inv = 1.0f;
+  if (mx > 3.402823466e38f) {
+    mul = 0.0f;
+    inv = __int_as_float(0x7fc00000);
+  } else if (mx > 0.0f) {
+    int ex = 0;
+    frexpf(mx, &ex);
+    int e = 30 - ex;
+    e = e > 126 ? 126 : e;
+    mul = __int_as_float((127 + e) << 23);
+    inv = __int_as_float((127 - e) << 23);
+  }
+  (void)s_mul;
+  if (!row_ok) return;
+  if (tid == 0) {
+    row_scale[r] = inv;
+    if (rowsum) rowsum[r] = sum;
+  }
   int8_t* base = digits + ((r >> 5) * 128 + (r & 31)) * ldd;
-  for (int64_t k = static_cast<int64_t>(threadIdx.x) * 4; k < ldd; k += kPrepThreads * 4) {
+  for (int64_t k = static_cast<int64_t>(tid) * 4; k < ldd; k += TEAM * 4) {
     float v[4];
     if (VEC && k + 4 <= cols) {
       const float4 f = __ldg(reinterpret_cast<const float4*>(xr + k));
@@ -250,11 +260,16 @@ extern "C" int32_t lc_split_f32_digits(const float* x, int64_t rows, int64_t col
   if (!aligned(digits, 4)) return fail(LC_ERR_UNSUPPORTED, "split_f32_digits: digits must be 4-byte aligned");
   const bool vec = ldx % 4 == 0 && aligned(x, 16);
   cudaStream_t st = as_stream(stream);
-  if (vec)
-    split_f32_digits_kernel<true><<<static_cast<unsigned>(rows), kPrepThreads, 0, st>>>(x, cols, ldx, digits, ldd,
-                                                                                        row_scale, rowsum);
-  else
-    split_f32_digits_kernel<false><<<static_cast<unsigned>(rows), kPrepThreads, 0, st>>>(x, cols, ldx, digits, ldd,
-                                                                                         row_scale, rowsum);
+  // a warp per row while a row is at most 16 elements per lane and step (2048 columns), else a CTA per row
+  const bool warp_rows = cols <= 2048;
+  const unsigned grid = static_cast<unsigned>(warp_rows ? (rows + kPrepThreads / 32 - 1) / (kPrepThreads / 32) : rows);
+#define LC_SPLIT(V, T) \
+  split_f32_digits_kernel<V, T><<<grid, kPrepThreads, 0, st>>>(x, rows, cols, ldx, digits, ldd, row_scale, rowsum)
+  if (vec) {
+    if (warp_rows) LC_SPLIT(true, 32); else LC_SPLIT(true, kPrepThreads);
+  } else {
+    if (warp_rows) LC_SPLIT(false, 32); else LC_SPLIT(false, kPrepThreads);
+  }
+#undef LC_SPLIT
   return check_launch("split_f32_digits");
 }

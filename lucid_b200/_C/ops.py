@@ -417,9 +417,14 @@ def dynamic_linear_workspace(rows: int, cols: int, dev: torch.device) -> torch.T
     return torch.empty(int(lib.lc_dynamic_linear_workspace_bytes(rows, cols)), dtype=torch.uint8, device=dev)
 
 
+def raw_stream(dev: torch.device) -> int:
+    """The current stream of ``dev`` as the integer value of its ``cudaStream_t``."""
+    return _stream(dev)
+
+
 def dynamic_linear(x2d: torch.Tensor, act_scheme: str, qmin: int, qmax: int, signed: bool, wq: torch.Tensor, sw, bias,
                    wsum, workspace: torch.Tensor, fresh: bool, out_dtype: torch.dtype = torch.float32,
-                   eps: float = 1e-8, status=None) -> torch.Tensor:
+                   eps: float = 1e-8, status=None, stream: int | None = None) -> torch.Tensor:
     """Forward of the dynamic Linear from one library call: quantize the fp32 ``x2d`` on the grid
     ``act_scheme`` and run the int8 GEMM against ``wq`` (16-byte row pitch), ``sw``, ``bias``.
     Arguments are taken as they are (contiguous fp32 tensors on one device); this is the
@@ -431,7 +436,8 @@ def dynamic_linear(x2d: torch.Tensor, act_scheme: str, qmin: int, qmax: int, sig
     check(lib.lc_dynamic_linear_f32(x2d.data_ptr(), x2d.stride(0), m, k, _ACT_SCHEME_ID[act_scheme], int(qmin), int(qmax),
                                     1 if signed else 0, float(eps), wq.data_ptr(), wq.stride(0), n, _ptr(sw), _ptr(bias),
                                     _ptr(wsum), out.data_ptr(), _lc_dtype(out_dtype), n, workspace.data_ptr(),
-                                    workspace.numel(), 1 if fresh else 0, _ptr(status), _stream(dev)))
+                                    workspace.numel(), 1 if fresh else 0, _ptr(status),
+                                    _stream(dev) if stream is None else stream))
     return out
 
 
@@ -640,15 +646,17 @@ def wo_workspace(dev: torch.device, rows: int):
 
 
 def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous: bool = False, relu: bool = False, out_scale=None,
-                 out_zp=None, quant_min: int = 0, quant_max: int = 255, balanced: bool = True):
+                 out_zp=None, quant_min: int = 0, quant_max: int = 255, balanced: bool = False):
     """``y = (x @ wq^T) * sw + bias`` with float activations; ``y`` has ``x``'s dtype.  With
     ``relu`` / ``out_scale`` and ``out_zp`` (device scalars) the same kernel goes on to apply the
     ReLU and the fake-quantize onto the calibrated output grid of a static Linear.
 
     ``overlap_previous`` lets the kernel start (and prefetch weights) while the kernel before
     it on the stream drains; the caller asserts that ``wq``, ``sw`` and ``bias`` were complete
-    before that kernel started.  ``balanced`` (default) gives the weight-streaming kernel its scratch, so
-    that every SM streams the same number of bytes; without it whole 32-row boxes are dealt out."""
+    before that kernel started.  ``balanced`` gives the weight-streaming kernel its scratch, so that every
+    SM streams the same number of bytes (K is cut between CTAs); by default whole 32-row boxes are dealt
+    out, which measures faster on B200 for the decode shapes (the ticketed finish of the shared boxes
+    costs more than the idle SMs it removes: decode MLP 53 us against 41 us)."""
     dev = _need_cuda(x2d, wq, sw, bias, out_scale, out_zp)
     if x2d.dtype not in (torch.float32, torch.bfloat16, torch.float16):
         raise TypeError(f"wo_linear_s8: activations must be fp32/bf16/fp16, got {x2d.dtype}")
@@ -688,7 +696,7 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.cat([g, u], dim=1).reshape(2 * f, *gate.shape[1:]).contiguous()
 
 
-def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None, overlap_previous: bool = False, balanced: bool = True):
+def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None, overlap_previous: bool = False, balanced: bool = False):
     """``silu(x @ Wg^T * sg) * (x @ Wu^T * su)`` with interleaved int8 gate/up weights
     (see :func:`interleave_gate_up`); bf16 / f16 activations, batch <= 32.
     ``overlap_previous`` as for :func:`wo_linear_s8`."""
@@ -747,7 +755,11 @@ def group_dequantize(packed, scales, biases, group_size: int = 64, bits: int = 8
     return out
 
 
-def group_matmul(x2d, packed, scales, biases, group_size: int = 64, bits: int = 8):
+def group_matmul(x2d, packed, scales, biases, group_size: int = 64, bits: int = 8, overlap_previous: bool = False):
+    """``y[b, n] = sum_k x[b, k] * (code[n, k] * scale[n, g] + bias[n, g])`` for the packed group-wise
+    format; ``y`` has ``x``'s dtype.  8-bit weights of 4 MB and more (groups of 64 / 128, bf16 / f16
+    activations) are streamed once through shared memory; ``overlap_previous`` as for
+    :func:`wo_linear_s8`."""
     dev = _need_cuda(x2d, packed, scales, biases)
     x2d = x2d.contiguous()
     packed = packed.contiguous()
@@ -758,8 +770,23 @@ def group_matmul(x2d, packed, scales, biases, group_size: int = 64, bits: int = 
     y = torch.empty((B, N), dtype=x2d.dtype, device=dev)
     sc, bi = _f32c(scales), _f32c(biases)
     with _on(dev):
-        check(lib.lc_group_matmul(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, packed.data_ptr(), sc.data_ptr(),
-                                  bi.data_ptr(), N, group_size, bits, y.data_ptr(), _stream(dev)))
+        ws = None  # whole boxes per CTA: measured faster than the K-cutting schedule
+        check(lib.lc_group_matmul_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, packed.data_ptr(), sc.data_ptr(),
+                                     bi.data_ptr(), N, group_size, bits, y.data_ptr(), 1 if overlap_previous else 0,
+                                     _ptr(ws), 0 if ws is None else ws.numel(), _stream(dev)))
+    return y
+
+
+def group_matmul_lean(x2d, packed, scales, biases, group_size: int, bits: int):
+    """:func:`group_matmul` for callers that have already established what it checks: all four
+    tensors live on the current CUDA device, are contiguous, ``scales`` / ``biases`` are fp32 and the
+    shapes agree.  One allocation, one stream query, one library call: the decode-time dispatch path."""
+    B, K = x2d.shape
+    N = packed.shape[0]
+    y = torch.empty((B, N), dtype=x2d.dtype, device=x2d.device)
+    check(lib.lc_group_matmul_ex(x2d.data_ptr(), _DTYPE[x2d.dtype], B, K, packed.data_ptr(), scales.data_ptr(),
+                                 biases.data_ptr(), N, group_size, bits, y.data_ptr(), 0, None, 0,
+                                 _stream(x2d.device)))
     return y
 
 

@@ -144,15 +144,16 @@ class Linear(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         ops = _backend.ops()
         if (x.is_cuda and x.dtype is torch.float32 and not _shared_input.active and x.is_contiguous()
-                and self.weight_int8.device == x.device and x.numel() > 0 and hasattr(ops, "dynamic_linear")
+                and self.weight_int8.device == x.device and x.numel() > 0 and hasattr(ops, "raw_stream")
                 and torch.cuda.current_device() == x.device.index):
             # the common eager case in one library call: no intermediate tensors, one stream query
             x2 = x.view(-1, self.in_features)
             wq, wsum = self._cache.get(self.weight_int8, self.weight_zero_point)
-            ws, fresh = self._scratch(x2.shape[0], x.device, torch.cuda.current_stream(x.device).cuda_stream)
+            stream = ops.raw_stream(x.device)
+            ws, fresh = self._scratch(x2.shape[0], x.device, stream)
             qd = self.act_qdtype
             y = ops.dynamic_linear(x2, self.act_scheme, qd.quant_min, qd.quant_max, qd.signed, wq, self.weight_scale,
-                                   self.bias, wsum, ws, fresh, self.out_dtype)
+                                   self.bias, wsum, ws, fresh, self.out_dtype, stream=stream)
             return y.view(*x.shape[:-1], self.out_features)
         if self.weight_zero_point.is_cuda and x.is_cuda and x.device != self.weight_int8.device:
             raise RuntimeError(f"input on {x.device} but weights on {self.weight_int8.device}")

@@ -13,6 +13,8 @@ import torch
 
 from lucid_b200 import _backend
 
+_FLOATS = (torch.float32, torch.bfloat16, torch.float16)
+
 
 def is_available() -> bool:
     try:
@@ -76,6 +78,16 @@ def quantized_matmul(x, wq, scales, biases, transpose: bool = True, group_size: 
     """``x @ w_hat.T`` (``transpose=True``, the Linear form) or ``x @ w_hat`` with the
     weight decoded inside the kernel; float activations, result in ``x``'s dtype.
     Differentiable with respect to ``x``."""
+    if (transpose and x.is_cuda and wq.is_cuda and not (x.requires_grad and torch.is_grad_enabled())
+            and x.dim() == 2 and x.shape[0] <= 32 and x.is_contiguous() and wq.is_contiguous()
+            and scales.dtype is torch.float32 and scales.is_contiguous() and biases.dtype is torch.float32
+            and biases.is_contiguous() and x.device == wq.device == scales.device == biases.device
+            and x.device.index == torch.cuda.current_device() and x.dtype in _FLOATS
+            and wq.shape[1] * 32 // bits == x.shape[1]):
+        # decode-time dispatch: everything the general path would normalise is already in place
+        lean = getattr(_backend.ops(), "group_matmul_lean", None)
+        if lean is not None:
+            return lean(x, wq, scales, biases, group_size, bits)
     xd = _backend.on_cuda(x)
     wq, scales, biases = _backend.on_cuda(wq), _backend.on_cuda(scales), _backend.on_cuda(biases)
     if xd.requires_grad and torch.is_grad_enabled():

@@ -289,3 +289,24 @@ def test_balanced_swiglu_agrees_with_whole_boxes(ops, B, F, K):
         assert torch.equal(ops.wo_swiglu_s8(x, wgu, sgu, balanced=True, overlap_previous=bool(i & 1)).view(torch.int16),
                            split.view(torch.int16))
     assert ops.wo_linear_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("gs", [64, 128])
+@pytest.mark.parametrize("B,N,K", [(1, 14336, 4096), (4, 4096, 14336), (16, 4096, 4096), (32, 2064, 2048), (3, 2050, 2176)])
+def test_group_matmul_streaming_kernel(ops, dtype, gs, B, N, K):
+    """8-bit group-wise weights of 4 MB and more go through the streaming kernel: against the oracle's
+    float64 product of the SAME packed codes, scales and biases, within the rounding bound of an
+    fp32-accumulated result in the activation type (the bound counts |x| * (255 s + |b|) per term)."""
+    g = torch.Generator(device="cuda").manual_seed(B + N + K + gs)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.05
+    p, s, b = ops.group_quantize(w, gs, 8)
+    x = torch.randn(B, K, device="cuda", generator=g).to(dtype)
+    y = ops.group_matmul(x, p, s, b, gs, 8)
+    assert y.dtype == dtype and y.shape == (B, N)
+    ref = O.group_matmul(x.double().cpu().numpy(), p.cpu().numpy(), host(s), host(b), gs, 8)
+    mag = (x.double().abs() @ (255.0 * s.double().repeat_interleave(gs, 1) + b.double().abs().repeat_interleave(gs, 1)).T)
+    assert_rounded_product(y, ref, mag.cpu().numpy(), K, dtype)
+    again = ops.group_matmul(x, p, s, b, gs, 8, overlap_previous=True)
+    assert torch.equal(again.view(torch.int16), y.view(torch.int16))
+    assert ops.wo_linear_status() == 0
