@@ -315,49 +315,46 @@ struct RawOperand<__nv_bfloat16> {
   }
 };
 
-// Work of the ring kernel is counted in units of (box, K chunk), a box being GRP vertically adjacent
-// row tiles.  CTA c owns the contiguous unit range [c*U/G, (c+1)*U/G) in box-major order, so all CTAs
-// stream the same number of bytes (+-1 unit) whatever the matrix shape; a range is walked as passes:
-// a first box it enters in the middle of K, runs of whole boxes (up to TMAX tiles at a time, K outermost
-// inside a pass so that an activation chunk is loaded once for all of them), and a last box it leaves
-// in the middle of K.  A box whose K range is shared by several CTAs is finished by whichever of them
-// arrives last: each parks the raw sums of its K range in its own slot of a small workspace (no
-// atomics on data), takes a ticket of the box, and the holder of the last ticket adds the slots in CTA
-// order -- a fixed order, so results do not depend on timing -- and applies the epilogue.
+// Work of the ring kernel is counted in units of (16-row tile, K chunk).  CTA c owns the contiguous unit
+// range [c*U/G, (c+1)*U/G) in tile-major order and walks it as passes: a first tile it enters in the
+// middle of K, runs of whole tiles (up to TMAX at a time, K outermost inside a pass so that an
+// activation chunk is loaded once for all of them, tiles fetched GRP per TMA box), and a last tile it
+// leaves in the middle of K.  With U a whole number of tiles per CTA (no scratch) there are only whole
+// tiles.  With scratch, U/G may be fractional: every CTA then streams the same number of bytes (+-1
+// unit) whatever the matrix shape, and a tile whose K range is shared by several CTAs is finished by
+// whichever of them arrives last: each parks the raw sums of its K range in its own slot of the
+// scratch (no atomics on data), takes a ticket of the tile, and the holder of the last ticket adds the
+// slots in CTA order -- a fixed order, so results do not depend on timing -- and applies the epilogue.
 struct RingPlan {
-  long long units_real;   // boxes * K chunks
-  long long units;        // what the CTA ranges divide: units_real, or a whole number of boxes per CTA (no workspace)
+  long long units_real;   // tiles * K chunks
+  long long units;        // what the CTA ranges divide: units_real, or a whole number of tiles per CTA (no scratch)
   int grid;               // G
-  float* partial;         // [G][2][GRP*16*COLS] raw sums: slot 0 = a pass that starts inside its box, 1 = one that starts it
-  int* tickets;           // [boxes], zero before the launch and zero again after it
+  float* partial;         // [G][2][16*COLS] raw sums: slot 0 = a pass that starts inside its tile, 1 = one that starts it
+  int* tickets;           // [tiles], zero before the launch and zero again after it
 };
 
 struct RingPass {
   int tile0, n_tiles, kc0, kc1;
-  long long box;
   bool partial;
 };
 
-template <int TMAX, int GRP>
+template <int TMAX>
 struct RingWalk {
-  long long u, u_end, tiles_total;
+  long long u, u_end;
   int num_kc;
   __device__ bool next(RingPass& p) {
     if (u >= u_end) return false;
-    const long long box = u / num_kc, left = u_end - u;
+    const long long tile = u / num_kc, left = u_end - u;
     const int kc0 = static_cast<int>(u % num_kc);
-    const long long t0 = box * GRP;
     if (kc0 != 0 || left < num_kc) {
       const int kc1 = left < num_kc - kc0 ? kc0 + static_cast<int>(left) : num_kc;
-      const long long nt = tiles_total - t0 < GRP ? tiles_total - t0 : GRP;
-      p = {static_cast<int>(t0), static_cast<int>(nt), kc0, kc1, box, true};
+      p = {static_cast<int>(tile), 1, kc0, kc1, true};
       u += kc1 - kc0;
     } else {
-      long long nb = left / num_kc;
-      nb = nb < TMAX / GRP ? nb : TMAX / GRP;
-      const long long nt = tiles_total - t0 < nb * GRP ? tiles_total - t0 : nb * GRP;
-      p = {static_cast<int>(t0), static_cast<int>(nt), 0, num_kc, box, false};
-      u += nb * num_kc;
+      long long nt = left / num_kc;
+      nt = nt < TMAX ? nt : TMAX;
+      p = {static_cast<int>(tile), static_cast<int>(nt), 0, num_kc, false};
+      u += nt * num_kc;
     }
     return true;
   }
@@ -447,7 +444,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       // activation chunk must not queue behind a ring-full of weights).
       int prefilled = 0;
       if (overlap) {
-        RingWalk<TMAX, GRP> first = {u_begin, u_end, tiles_total, num_kc};
+        RingWalk<TMAX> first = {u_begin, u_end, num_kc};
         RingPass ps;
         if (first.next(ps)) {
           for (int kc = ps.kc0; kc < ps.kc1 && prefilled < S; ++kc)
@@ -462,7 +459,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       }
       asm volatile("griddepcontrol.wait;" ::: "memory");
       int issued = 0;  // weight items walked so far (the first `prefilled` are already in flight)
-      RingWalk<TMAX, GRP> walk = {u_begin, u_end, tiles_total, num_kc};
+      RingWalk<TMAX> walk = {u_begin, u_end, num_kc};
       RingPass ps;
       while (ok && walk.next(ps)) {
         for (int kc = ps.kc0; kc < ps.kc1 && ok; ++kc, ++xi) {
@@ -515,7 +512,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     int stage = 0, xi = 0;
     uint32_t phase = 0;
     bool ok = true;
-    RingWalk<TMAX, GRP> walk = {u_begin, u_end, tiles_total, num_kc};
+    RingWalk<TMAX> walk = {u_begin, u_end, num_kc};
     RingPass ps;
     while (walk.next(ps)) {
       const int pass_tiles = ps.n_tiles;
@@ -587,7 +584,39 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           out[2] = (live && ra < N) ? __ldg(bias + ra * n_groups + grp) : 0.0f;
           out[3] = (live && rb < N) ? __ldg(bias + rb * n_groups + grp) : 0.0f;
         };
-        if (GS != 0) fetch_group(0, gq);
+        if (GS != 0) {
+          fetch_group(0, gq);
+          // The group parameters of the NEXT chunk are pulled into L2 now (no registers involved): a first
+          // touch comes from DRAM, about a microsecond away, far more than the tile-ahead fetch above hides.
+          // Lane (g, t) covers rows g and g + 8 of tiles t, t + 4, ... of the pass.
+          int pf_tile0 = ps.tile0, pf_tiles = pass_tiles, pf_kc = kc + 1;
+          if (pf_kc >= ps.kc1) {  // last chunk of this pass: look at the first chunk of the next one
+            RingWalk<TMAX> peek = walk;
+            RingPass nx;
+            if (peek.next(nx)) {
+              pf_tile0 = nx.tile0;
+              pf_tiles = nx.n_tiles;
+              pf_kc = nx.kc0;
+            } else {
+              pf_tiles = 0;
+            }
+          }
+          const int64_t nk = static_cast<int64_t>(pf_kc) * KC + warp * 64;
+          if (nk < K) {
+            const int64_t ngrp = nk / (GS ? GS : 1);
+            for (int j = t; j < pf_tiles; j += 4) {
+              const int64_t ra = ((static_cast<int64_t>(pf_tile0) + j) << 4) + g, rb = ra + 8;
+              if (ra < N) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(sw + ra * n_groups + ngrp));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(bias + ra * n_groups + ngrp));
+              }
+              if (rb < N) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(sw + rb * n_groups + ngrp));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(bias + rb * n_groups + ngrp));
+              }
+            }
+          }
+        }
 #pragma unroll
         for (int j = 0; j < TMAX; ++j) {
           if (j < pass_tiles && ok) {
@@ -681,13 +710,13 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 
-      // For a pass over part of K: park the CTA's raw sums in its workspace slot, take a ticket of
-      // the box, and go on only if every other CTA that shares the box has already parked its own.
-      constexpr int kSlotFloats = GRP * 16 * COLS;
+      // For a pass over part of K: park the CTA's raw sums in its scratch slot, take a ticket of
+      // the tile, and go on only if every other CTA that shares the tile has already parked its own.
+      constexpr int kSlotFloats = 16 * COLS;
       int n_sharers = 1, first_sharer = 0;
       bool finish = true;
       if (ps.partial) {
-        const long long box_first = ps.box * num_kc;
+        const long long box_first = static_cast<long long>(ps.tile0) * num_kc;
         first_sharer = ring_owner(box_first, plan.units, plan.grid);
         n_sharers = ring_owner(box_first + num_kc - 1, plan.units, plan.grid) - first_sharer + 1;
         float* slot = plan.partial + (static_cast<size_t>(blockIdx.x) * 2 + (u_begin > box_first ? 0 : 1)) * kSlotFloats;
@@ -704,9 +733,9 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
         if (threadIdx.x == 0) {
-          const int old = atomicAdd(plan.tickets + ps.box, 1);
+          const int old = atomicAdd(plan.tickets + ps.tile0, 1);
           s_last_ticket = old == n_sharers - 1;
-          if (old == n_sharers - 1) plan.tickets[ps.box] = 0;  // every sharer has drawn: ready for the next launch
+          if (old == n_sharers - 1) plan.tickets[ps.tile0] = 0;  // every sharer has drawn: ready for the next launch
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
         finish = s_last_ticket != 0;
@@ -725,7 +754,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           float sum = 0.0f;
           for (int c = 0; c < n_sharers; ++c) {
             const long long cta = first_sharer + c;
-            const int which = ring_first_unit(cta, plan.units, plan.grid) > ps.box * num_kc ? 0 : 1;
+            const int which = ring_first_unit(cta, plan.units, plan.grid) > static_cast<long long>(ps.tile0) * num_kc ? 0 : 1;
             sum += __ldcg(plan.partial + (static_cast<size_t>(cta) * 2 + which) * kSlotFloats + (j * 16 + r) * COLS + bcol);
           }
           return sum;
@@ -975,12 +1004,12 @@ static int32_t launch_wo_mma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
   return check_launch("wo_linear_s8 (mma)");
 }
 
-// scratch of the balanced schedule: per CTA two slots of raw sums, then one ticket per box
+// scratch of the balanced schedule: per CTA two slots of raw sums, then one ticket per tile
 struct RingScratch {
   void* ptr;
   int64_t bytes;
 };
-constexpr int64_t kRingSlotBytes = 2 * 16 * 32 * 4;  // largest GRP * 16 rows * COLS floats
+constexpr int64_t kRingSlotBytes = 16 * 32 * 4;  // 16 rows * largest COLS floats
 
 template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0>
 static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
@@ -1012,22 +1041,22 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
                                         static_cast<uint64_t>(B), static_cast<uint64_t>(ldx) * 2, ring::KC / 4,
                                         NT * 8, CU_TENSOR_MAP_SWIZZLE_NONE))
     return rc;
-  const int64_t tiles = (N + 15) / 16, boxes = (tiles + GRP - 1) / GRP;
+  const int64_t tiles = (N + 15) / 16;
   const int64_t num_kc = (K + ring::KC - 1) / ring::KC;
   const int64_t sms = sm_count();
   RingPlan plan;
-  plan.units_real = boxes * num_kc;
-  const int64_t need = sms * 2 * kRingSlotBytes + boxes * 4;
+  plan.units_real = tiles * num_kc;
+  const int64_t need = sms * 2 * kRingSlotBytes + tiles * 4;
   if (scratch.ptr && scratch.bytes >= need && aligned(scratch.ptr, 16)) {
-    // every CTA the same number of (box, K chunk) units, boxes shared along K where ranges meet
+    // every CTA the same number of (tile, K chunk) units, tiles shared along K where ranges meet
     plan.grid = static_cast<int>(plan.units_real < sms ? plan.units_real : sms);
     plan.units = plan.units_real;
     plan.partial = static_cast<float*>(scratch.ptr);
     plan.tickets = reinterpret_cast<int*>(static_cast<uint8_t*>(scratch.ptr) + sms * 2 * kRingSlotBytes);
   } else {
-    // no scratch: whole boxes only, the same number for every CTA
-    const int64_t per = (boxes + sms - 1) / sms;
-    plan.grid = static_cast<int>((boxes + per - 1) / per);
+    // no scratch: whole tiles only, the same number for every CTA
+    const int64_t per = (tiles + sms - 1) / sms;
+    plan.grid = static_cast<int>((tiles + per - 1) / per);
     plan.units = plan.grid * per * num_kc;
     plan.partial = nullptr;
     plan.tickets = nullptr;

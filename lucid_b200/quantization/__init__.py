@@ -1,7 +1,7 @@
 """``lucid.quantization`` on the CUDA backend: the reference's public names
 (``lucid/quantization/__init__.py:74-125``) with the hot path on sm_100a kernels.
 
-Graph mode (``prepare_fx`` / ``convert_fx``) is a tracing front end over the reference's own
+Graph mode (``prepare_fx`` / ``convert_fx``) wraps the model in its quantization boundaries and runs the eager flow,
 graph capture; the names are exported for compatibility and raise ``NotImplementedError``.
 """
 from lucid_b200.quantization import _qgemm, observer, qconfig  # noqa: F401
@@ -22,18 +22,26 @@ from lucid_b200.quantization.qconfig import (QConfig, QConfigMapping, get_defaul
                                              get_default_qconfig_mapping)
 
 
-def _not_on_this_backend(name: str):
-    def stub(*_args, **_kwargs):
-        raise NotImplementedError(
-            f"{name} is a tracing / training front end with no kernels; it is not part of the CUDA "
-            "inference backend")
+def prepare_fx(model, qconfig_mapping=None, example_inputs=None, inplace: bool = False):
+    """Graph-mode entry of static PTQ (``lucid/quantization/_quantize_fx.py:30-109``): no hand-placed
+    stubs -- the model is wrapped in a :class:`~lucid_b200.nn.quantized.QuantWrapper` (input quantized,
+    output dequantized) and then prepared like the eager flow.  Calibrate the result, then
+    :func:`convert_fx`.  ``example_inputs`` is accepted for signature compatibility; nothing is traced
+    (the reference reaches graph mode by compiling the converted module-level composites, and a model
+    converted here is captured whole by ``lucid_b200.cuda.make_graphed``)."""
+    import copy
 
-    stub.__name__ = name
-    return stub
+    from lucid_b200.nn.quantized import QuantWrapper
+
+    del example_inputs
+    return prepare(QuantWrapper(model if inplace else copy.deepcopy(model)), qconfig_mapping, inplace=True)
 
 
-prepare_fx = _not_on_this_backend("prepare_fx")
-convert_fx = _not_on_this_backend("convert_fx")
+def convert_fx(model, inplace: bool = False):
+    """Graph-mode convert (``_quantize_fx.py:112-170``): the eager :func:`convert` of a model that
+    :func:`prepare_fx` produced."""
+    return convert(model, inplace=inplace)
+
 
 __all__ = [
     "QScheme", "per_tensor_affine", "per_tensor_symmetric", "per_channel_affine", "per_channel_symmetric",

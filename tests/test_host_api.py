@@ -458,3 +458,19 @@ def test_dynamic_linear_refuses_affine_weights(device):
     q.weight_zero_point[3] = 2.0
     with pytest.raises(NotImplementedError, match="weight_zero_point"):
         q(x)
+
+
+def test_prepare_fx_convert_fx(device):
+    """Graph-mode names (lucid/quantization/_quantize_fx.py:30,112): boundaries are added for the
+    caller, then the eager flow runs underneath."""
+    model = mlp()
+    prepared = Q.prepare_fx(model, example_inputs=torch.randn(2, 32))
+    assert isinstance(prepared, nnq.QuantWrapper) and hasattr(prepared.module[0], "activation_post_process")
+    assert not hasattr(model[0], "activation_post_process")  # the caller's model is untouched
+    prepared = prepared.to(device)
+    x = torch.randn(16, 32)
+    prepared(x.to(device))
+    qm = Q.convert_fx(prepared)
+    assert isinstance(qm.module[0], nnq.Linear) and isinstance(qm.quant, nnq.Quantize)
+    out = qm(x.to(device)).cpu()
+    assert (out - model(x)).abs().mean() / model(x).abs().mean() < 0.1
