@@ -218,9 +218,9 @@ def run_reference_arm(args) -> int:
         f"{steps} steps asked; stopped after {base['iterations']} when the {base['wall_budget_s']:.0f} s wall budget ran out",
         "ms_per_step": base["seconds_per_sample"] * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {**workload_config(),
-                   "note": "reference engine is Apple-only; its Python-level CPU formulation restated in oracle/ is "
-                           "timed on a bounded row sample of this workload (see cpu_baseline.sample)"},
+        "config": workload_config(),
+        "run": {"note": "reference engine is Apple-only; its Python-level CPU formulation restated in oracle/ is "
+                        "timed on a bounded row sample of this workload (see cpu_baseline.sample)"},
         "cpu_baseline": {k: base[k] for k in keep if k in base},
         "e2e": {"value": base["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -1080,10 +1080,10 @@ def run_ours(args) -> int:
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "s8xs8->s32",
             "data": "synthetic", "oracle_checked": oracle_checked,
-            "config": {**workload_config(),
-                       "parallelism": f"column-parallel x{world}" + ("" if world == 1 else f" + all-gather ({mode})"),
-                       "gather": mode, "l2": "inputs exceed L2 (x 537 MB, W 235 MB, y 1879 MB vs 126 MB)",
-                       "oracle_check": check_shape},
+            "config": workload_config(),  # the same keys and values as the reference arm prints
+            "run": {"parallelism": f"column-parallel x{world}" + ("" if world == 1 else f" + all-gather ({mode})"),
+                    "gather": mode, "l2": "inputs exceed L2 (x 537 MB, W 235 MB, y 1879 MB vs 126 MB)",
+                    "oracle_check": check_shape},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
                          "frac": achieved / int8_peak,
                          "traffic": gemm_dram_traffic(2.0 * M * n_local * K),

@@ -575,7 +575,10 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         // (those of tile j + 1 are fetched while tile j is being multiplied)
         const int64_t n_groups = GS ? K / (GS ? GS : 1) : 0;
         const int64_t grp = GS ? (static_cast<int64_t>(kc) * KC + warp * 64) / (GS ? GS : 1) : 0;
-        float gq[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // s[row g], s[row g + 8], b[row g], b[row g + 8]
+        // s[row g], s[row g + 8], b[row g], b[row g + 8] of every tile of the pass: requested here, used after
+        // the chunk's MMAs, so their latency hides behind the barrier waits and the tensor work
+        float gq[GS ? TMAX : 1][4];
+        float part[GS ? TMAX : 1][NT][4];  // raw sums of this chunk, one set per tile (independent MMA chains)
         auto fetch_group = [&](int j, float (&out)[4]) {
           const int64_t ra = ((static_cast<int64_t>(ps.tile0) + j) << 4) + g, rb = ra + 8;
           const bool live = warp_k_ok && j < pass_tiles;
@@ -585,7 +588,14 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           out[3] = (live && rb < N) ? __ldg(bias + rb * n_groups + grp) : 0.0f;
         };
         if (GS != 0) {
-          fetch_group(0, gq);
+#pragma unroll
+          for (int j = 0; j < (GS ? TMAX : 1); ++j) {
+            fetch_group(j, gq[j]);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) part[j][nt][i] = 0.0f;
+          }
           // The group parameters of the NEXT chunk are pulled into L2 now (no registers involved): a first
           // touch comes from DRAM, about a microsecond away, far more than the tile-ahead fetch above hides.
           // Lane (g, t) covers rows g and g + 8 of tiles t, t + 4, ... of the pass.
@@ -646,32 +656,15 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                       mma_16816<XT>(acc[j][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
                   }
                 } else {
-                  float gnext[4];
-                  fetch_group(j + 1, gnext);  // in flight while this tile's MMAs run
-                  float part[NT][4];
-#pragma unroll
-                  for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) part[nt][i] = 0.0f;
+                  constexpr int jj = GS ? 1 : 0;  // (keeps the index in range when this branch is not instantiated)
 #pragma unroll
                   for (int q = 0; q < 4; ++q) {  // the codes are unsigned bytes already
                     const uint32_t a0 = __byte_perm(r0[q], 0u, 0x4140u), a2 = __byte_perm(r0[q], 0u, 0x4342u);
                     const uint32_t a1 = __byte_perm(r1[q], 0u, 0x4140u), a3 = __byte_perm(r1[q], 0u, 0x4342u);
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt)
-                      mma_16816<XT>(part[nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                      mma_16816<XT>(part[j * jj][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
                   }
-                  // raw sums -> values: sum(x c) = part * acc_scale, sum(x) = xsum * (sum_scale / 128)
-                  const float c1 = RawOperand<XT>::acc_scale(), cx = RawOperand<XT>::sum_scale() * 0.0078125f;
-#pragma unroll
-                  for (int nt = 0; nt < NT; ++nt) {
-                    acc[j][nt][0] = fmaf(part[nt][0] * c1, gq[0], fmaf(xsum[nt][0] * cx, gq[2], acc[j][nt][0]));
-                    acc[j][nt][1] = fmaf(part[nt][1] * c1, gq[0], fmaf(xsum[nt][1] * cx, gq[2], acc[j][nt][1]));
-                    acc[j][nt][2] = fmaf(part[nt][2] * c1, gq[1], fmaf(xsum[nt][0] * cx, gq[3], acc[j][nt][2]));
-                    acc[j][nt][3] = fmaf(part[nt][3] * c1, gq[1], fmaf(xsum[nt][1] * cx, gq[3], acc[j][nt][3]));
-                  }
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) gq[i] = gnext[i];
                 }
               }
               if (j % GRP == GRP - 1 || j == pass_tiles - 1) {
@@ -681,6 +674,22 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                   stage = 0;
                   phase ^= 1u;
                 }
+              }
+            }
+          }
+        }
+        if (GS != 0 && warp_k_ok) {
+          // raw sums -> values: sum(x c) = part * acc_scale, sum(x) = xsum * (sum_scale / 128)
+          const float c1 = RawOperand<XT>::acc_scale(), cx = RawOperand<XT>::sum_scale() * 0.0078125f;
+#pragma unroll
+          for (int j = 0; j < (GS ? TMAX : 1); ++j) {
+            if (j < pass_tiles) {
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                acc[j][nt][0] = fmaf(part[j][nt][0] * c1, gq[j][0], fmaf(xsum[nt][0] * cx, gq[j][2], acc[j][nt][0]));
+                acc[j][nt][1] = fmaf(part[j][nt][1] * c1, gq[j][0], fmaf(xsum[nt][1] * cx, gq[j][2], acc[j][nt][1]));
+                acc[j][nt][2] = fmaf(part[j][nt][2] * c1, gq[j][1], fmaf(xsum[nt][0] * cx, gq[j][3], acc[j][nt][2]));
+                acc[j][nt][3] = fmaf(part[j][nt][3] * c1, gq[j][1], fmaf(xsum[nt][1] * cx, gq[j][3], acc[j][nt][3]));
               }
             }
           }
@@ -1172,8 +1181,7 @@ static int32_t launch_group_ring(const XT* x, int64_t B, int64_t K, const uint8_
       rc = few ? launch_wo_ring_inst<XT, 1, 2, 4, false, 2, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
                : launch_wo_ring_inst<XT, 1, 4, 2, false, 2, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
     else if (bc <= 16)
-      rc = few ? launch_wo_ring_inst<XT, 2, 2, 3, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
-               : launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+      rc = launch_wo_ring_inst<XT, 2, 2, 3, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
     else
       rc = launch_wo_ring_inst<XT, 4, 1, 2, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
     if (rc) return rc;
@@ -1331,6 +1339,10 @@ extern "C" int32_t lc_group_matmul_ex(const void* x, int32_t x_dtype, int64_t ba
   if (batch < 0) return fail(LC_ERR_INVALID_ARG, "group_matmul: bad batch");
   if (batch == 0 || N == 0) return LC_OK;
   if (!x || !packed || !scales || !biases || !y) return fail(LC_ERR_INVALID_ARG, "group_matmul: null pointer");
+  // the kernels read 4 or 8 activations per load instruction: rows must start on 16-byte boundaries
+  // (K is a multiple of the group size, so every row does once the first one does)
+  if (!aligned(x, 16) || !aligned(packed, 4) || !aligned(scales, 4) || !aligned(biases, 4))
+    return fail(LC_ERR_UNSUPPORTED, "group_matmul: x must be 16-byte aligned (packed, scales, biases 4-byte aligned)");
   cudaStream_t st = as_stream(stream);
   const uint32_t* pk = reinterpret_cast<const uint32_t*>(packed);
   // weights from a few MB up, 8-bit codes in groups of 64 / 128, 16-bit activations: the streaming kernel

@@ -762,6 +762,8 @@ def group_matmul(x2d, packed, scales, biases, group_size: int = 64, bits: int = 
     :func:`wo_linear_s8`."""
     dev = _need_cuda(x2d, packed, scales, biases)
     x2d = x2d.contiguous()
+    if x2d.data_ptr() % 16:  # a contiguous view that starts inside a larger storage: the kernels load 16 bytes at a time
+        x2d = x2d.clone()
     packed = packed.contiguous()
     B, K = x2d.shape
     N = packed.shape[0]
@@ -783,6 +785,8 @@ def group_matmul_lean(x2d, packed, scales, biases, group_size: int, bits: int):
     shapes agree.  One allocation, one stream query, one library call: the decode-time dispatch path."""
     B, K = x2d.shape
     N = packed.shape[0]
+    if x2d.data_ptr() % 16:
+        x2d = x2d.clone()
     y = torch.empty((B, N), dtype=x2d.dtype, device=x2d.device)
     check(lib.lc_group_matmul_ex(x2d.data_ptr(), _DTYPE[x2d.dtype], B, K, packed.data_ptr(), scales.data_ptr(),
                                  biases.data_ptr(), N, group_size, bits, y.data_ptr(), 0, None, 0,

@@ -1,8 +1,8 @@
 """``lucid.quantization`` on the CUDA backend: the reference's public names
 (``lucid/quantization/__init__.py:74-125``) with the hot path on sm_100a kernels.
 
-Graph mode (``prepare_fx`` / ``convert_fx``) wraps the model in its quantization boundaries and runs the eager flow,
-graph capture; the names are exported for compatibility and raise ``NotImplementedError``.
+Graph mode (``prepare_fx`` / ``convert_fx``) wraps the model in its quantization boundaries and
+runs the eager flow underneath, as the reference's does.
 """
 from lucid_b200.quantization import _qgemm, observer, qconfig  # noqa: F401
 from lucid_b200.quantization._fake_quantize import FakeQuantize

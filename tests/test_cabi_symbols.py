@@ -64,6 +64,17 @@ def test_argument_validation_without_gpu(capi):
     assert rc == capi.LC_ERR_UNSUPPORTED and "16-byte" in capi.last_error()
     rc = L.lc_wo_linear_s8(p, 99, 1, 16, 16, p, 16, 1, None, None, p, 1, 0, None)
     assert rc == capi.LC_ERR_UNSUPPORTED
+    # activations that do not start on a 16-byte boundary are refused before anything is launched
+    rc = L.lc_group_matmul(p + 2, capi.LC_BF16, 1, 64, p, p, p, 1, 64, 8, p, None)
+    assert rc == capi.LC_ERR_UNSUPPORTED and "16-byte aligned" in capi.last_error()
+    # the new entry points validate their arguments the same way
+    assert L.lc_wo_gemm_digits(p, 24, p, p, 32, 1, 1, 24, None, None, None, None, 0, None, None, 0, 255, p, 1, None, 0,
+                               None) == capi.LC_ERR_UNSUPPORTED
+    assert L.lc_wo_gemm_16(p, capi.LC_BF16, 3, 96, p, 32, 1, 1, 32, None, None, None, None, 0, None, None, 0, 255, p,
+                           capi.LC_F32, 1, None, 0, None) == capi.LC_ERR_INVALID_ARG  # several terms need K % 64 == 0
+    assert L.lc_peer_barrier(None, 0, 1, 1, 1000, None, None) == capi.LC_ERR_INVALID_ARG
+    assert L.lc_dynamic_linear_workspace_bytes(64, 1024) >= 64 * 1024
+    assert L.lc_wo_digit_rows(33) == 256
 
 
 def test_ops_refuse_cpu_tensors(capi):

@@ -310,3 +310,16 @@ def test_group_matmul_streaming_kernel(ops, dtype, gs, B, N, K):
     again = ops.group_matmul(x, p, s, b, gs, 8, overlap_previous=True)
     assert torch.equal(again.view(torch.int16), y.view(torch.int16))
     assert ops.wo_linear_status() == 0
+
+
+def test_group_matmul_accepts_a_view_that_starts_off_a_16_byte_boundary(ops):
+    """A contiguous activation view into a larger storage (here: starting one element in) is copied to an
+    aligned buffer by the front end instead of reaching the kernels' 16-byte loads."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    w = torch.randn(64, 128, device="cuda", generator=g)
+    p, s, b = ops.group_quantize(w, 64, 8)
+    store = torch.randn(2 * 128 + 8, device="cuda", generator=g).to(torch.bfloat16)
+    x = store[1:1 + 2 * 128].view(2, 128)
+    assert x.data_ptr() % 16 != 0 and x.is_contiguous()
+    y = ops.group_matmul(x, p, s, b, 64, 8)
+    assert torch.equal(y, ops.group_matmul(x.clone(), p, s, b, 64, 8))

@@ -300,12 +300,6 @@ def test_group_engine_routing(device):
     assert torch.allclose(fresh(x.to(device)).cpu(), out, atol=1e-4)
 
 
-def test_unsupported_front_ends_raise():
-    for fn in (Q.prepare_fx, Q.convert_fx):
-        with pytest.raises(NotImplementedError):
-            fn(nn.Linear(2, 2))
-
-
 @pytest.mark.gpu
 def test_forward_from_host_matches_whole_batch():
     from lucid_b200.nn.quantized.streaming import forward_from_host
