@@ -575,10 +575,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         // (those of tile j + 1 are fetched while tile j is being multiplied)
         const int64_t n_groups = GS ? K / (GS ? GS : 1) : 0;
         const int64_t grp = GS ? (static_cast<int64_t>(kc) * KC + warp * 64) / (GS ? GS : 1) : 0;
-        // s[row g], s[row g + 8], b[row g], b[row g + 8] of every tile of the pass: requested here, used after
-        // the chunk's MMAs, so their latency hides behind the barrier waits and the tensor work
-        float gq[GS ? TMAX : 1][4];
-        float part[GS ? TMAX : 1][NT][4];  // raw sums of this chunk, one set per tile (independent MMA chains)
+        float gq[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // s[row g], s[row g + 8], b[row g], b[row g + 8]
         auto fetch_group = [&](int j, float (&out)[4]) {
           const int64_t ra = ((static_cast<int64_t>(ps.tile0) + j) << 4) + g, rb = ra + 8;
           const bool live = warp_k_ok && j < pass_tiles;
@@ -588,14 +585,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           out[3] = (live && rb < N) ? __ldg(bias + rb * n_groups + grp) : 0.0f;
         };
         if (GS != 0) {
-#pragma unroll
-          for (int j = 0; j < (GS ? TMAX : 1); ++j) {
-            fetch_group(j, gq[j]);
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-              for (int i = 0; i < 4; ++i) part[j][nt][i] = 0.0f;
-          }
+          fetch_group(0, gq);
           // The group parameters of the NEXT chunk are pulled into L2 now (no registers involved): a first
           // touch comes from DRAM, about a microsecond away, far more than the tile-ahead fetch above hides.
           // Lane (g, t) covers rows g and g + 8 of tiles t, t + 4, ... of the pass.
@@ -656,15 +646,32 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                       mma_16816<XT>(acc[j][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
                   }
                 } else {
-                  constexpr int jj = GS ? 1 : 0;  // (keeps the index in range when this branch is not instantiated)
+                  float gnext[4];
+                  fetch_group(j + 1, gnext);  // in flight while this tile's MMAs run
+                  float part[NT][4];
+#pragma unroll
+                  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) part[nt][i] = 0.0f;
 #pragma unroll
                   for (int q = 0; q < 4; ++q) {  // the codes are unsigned bytes already
                     const uint32_t a0 = __byte_perm(r0[q], 0u, 0x4140u), a2 = __byte_perm(r0[q], 0u, 0x4342u);
                     const uint32_t a1 = __byte_perm(r1[q], 0u, 0x4140u), a3 = __byte_perm(r1[q], 0u, 0x4342u);
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt)
-                      mma_16816<XT>(part[j * jj][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                      mma_16816<XT>(part[nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
                   }
+                  // raw sums -> values: sum(x c) = part * acc_scale, sum(x) = xsum * (sum_scale / 128)
+                  const float c1 = RawOperand<XT>::acc_scale(), cx = RawOperand<XT>::sum_scale() * 0.0078125f;
+#pragma unroll
+                  for (int nt = 0; nt < NT; ++nt) {
+                    acc[j][nt][0] = fmaf(part[nt][0] * c1, gq[0], fmaf(xsum[nt][0] * cx, gq[2], acc[j][nt][0]));
+                    acc[j][nt][1] = fmaf(part[nt][1] * c1, gq[0], fmaf(xsum[nt][1] * cx, gq[2], acc[j][nt][1]));
+                    acc[j][nt][2] = fmaf(part[nt][2] * c1, gq[1], fmaf(xsum[nt][0] * cx, gq[3], acc[j][nt][2]));
+                    acc[j][nt][3] = fmaf(part[nt][3] * c1, gq[1], fmaf(xsum[nt][1] * cx, gq[3], acc[j][nt][3]));
+                  }
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) gq[i] = gnext[i];
                 }
               }
               if (j % GRP == GRP - 1 || j == pass_tiles - 1) {
@@ -674,22 +681,6 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                   stage = 0;
                   phase ^= 1u;
                 }
-              }
-            }
-          }
-        }
-        if (GS != 0 && warp_k_ok) {
-          // raw sums -> values: sum(x c) = part * acc_scale, sum(x) = xsum * (sum_scale / 128)
-          const float c1 = RawOperand<XT>::acc_scale(), cx = RawOperand<XT>::sum_scale() * 0.0078125f;
-#pragma unroll
-          for (int j = 0; j < (GS ? TMAX : 1); ++j) {
-            if (j < pass_tiles) {
-#pragma unroll
-              for (int nt = 0; nt < NT; ++nt) {
-                acc[j][nt][0] = fmaf(part[j][nt][0] * c1, gq[j][0], fmaf(xsum[nt][0] * cx, gq[j][2], acc[j][nt][0]));
-                acc[j][nt][1] = fmaf(part[j][nt][1] * c1, gq[j][0], fmaf(xsum[nt][1] * cx, gq[j][2], acc[j][nt][1]));
-                acc[j][nt][2] = fmaf(part[j][nt][2] * c1, gq[j][1], fmaf(xsum[nt][0] * cx, gq[j][3], acc[j][nt][2]));
-                acc[j][nt][3] = fmaf(part[j][nt][3] * c1, gq[j][1], fmaf(xsum[nt][1] * cx, gq[j][3], acc[j][nt][3]));
               }
             }
           }
@@ -1181,7 +1172,8 @@ static int32_t launch_group_ring(const XT* x, int64_t B, int64_t K, const uint8_
       rc = few ? launch_wo_ring_inst<XT, 1, 2, 4, false, 2, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
                : launch_wo_ring_inst<XT, 1, 4, 2, false, 2, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
     else if (bc <= 16)
-      rc = launch_wo_ring_inst<XT, 2, 2, 3, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+      rc = few ? launch_wo_ring_inst<XT, 2, 2, 3, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
+               : launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
     else
       rc = launch_wo_ring_inst<XT, 4, 1, 2, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
     if (rc) return rc;
