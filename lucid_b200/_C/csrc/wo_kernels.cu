@@ -242,9 +242,12 @@ constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 2 GHz
 // split-K partials of a whole pass: [tile][warp][16 rows][8*nt + 1]
 __host__ __device__ constexpr int red_bytes(int nt, int tmax) { return tmax * kConsumerWarps * 16 * (nt * 8 + 1) * 4; }
 __host__ __device__ constexpr int x_bytes(int nt, int xb) { return xb * nt * 8 * X_PITCH; }
+// group-wise format: two buffers x {scales, biases} x tmax*16 rows x (groups per K chunk, padded to 17)
+constexpr int GP_PITCH = 17;
+__host__ __device__ constexpr int group_bytes(int gs, int tmax) { return gs ? 2 * 2 * tmax * 16 * GP_PITCH * 4 : 0; }
 // a ring stage holds `grp` vertically adjacent 16-row tiles of one K chunk, fetched by one TMA box
-__host__ __device__ constexpr int stages(int nt, int tmax, int xb, int grp) {
-  return (kSmemBudget - 512 - red_bytes(nt, tmax) - x_bytes(nt, xb)) / (STAGE * grp);
+__host__ __device__ constexpr int stages(int nt, int tmax, int xb, int grp, int gs = 0) {
+  return (kSmemBudget - 512 - red_bytes(nt, tmax) - x_bytes(nt, xb) - group_bytes(gs, tmax)) / (STAGE * grp);
 }
 }  // namespace ring
 
@@ -387,7 +390,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   static_assert(GS == 0 || GS == 64 || GS == 128, "group sizes the 64-byte warp slice fits into");
   static_assert(GS == 0 || !SWIGLU, "the fused SwiGLU epilogue is for per-channel weights");
   using namespace ring;
-  constexpr int S = stages(NT, TMAX, XB, GRP);
+  constexpr int S = stages(NT, TMAX, XB, GRP, GS);
   constexpr int GSTAGE = STAGE * GRP;
   static_assert(S >= 3, "ring too shallow");
   static_assert(GRP == 1 || GRP == 2, "one or two row tiles per box");
@@ -396,12 +399,14 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   const uint32_t base = (wo_smem_u32(wo_smem_raw) + 127u) & ~127u;
   const uint32_t x_base = base + S * GSTAGE;
   const uint32_t red_base = x_base + x_bytes(NT, XB);
-  const uint32_t bar_base = red_base + red_bytes(NT, TMAX);
+  const uint32_t gp_base = red_base + red_bytes(NT, TMAX);
+  const uint32_t bar_base = gp_base + group_bytes(GS, TMAX);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
   auto xfull_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
   auto xempty_bar = [&](int s) { return bar_base + 8u * (2 * S + XB + s); };
   float* red = reinterpret_cast<float*>(wo_smem_raw + (red_base - wo_smem_u32(wo_smem_raw)));
+  float* gp = reinterpret_cast<float*>(wo_smem_raw + (gp_base - wo_smem_u32(wo_smem_raw)));
 
   __shared__ int s_last_ticket;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -529,11 +534,48 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
 #pragma unroll
         for (int i = 0; i < 4; ++i) xsum[nt][i] = 0.0f;
 
-      for (int kc = ps.kc0; kc < ps.kc1 && ok; ++kc, ++xi) {
+      // Group-wise format: the scales and biases of a chunk -- 16 rows x (KC / GS) groups per tile and
+      // array -- are fetched by all 512 consumer threads together, one element each per tile, so that a
+      // warp's load covers whole 64-byte row pieces, and handed around through shared memory.  (Each warp
+      // fetching its own group's values touches 8 separate sectors per load: the L1 then limits the
+      // kernel to a third of the HBM rate.)  The values of chunk kc + 1 are requested at the top of
+      // iteration kc and parked after it, so their latency hides behind the chunk's work.
+      constexpr int GPC = GS ? KC / (GS ? GS : 1) : 1;          // groups per K chunk: 16 or 8
+      constexpr int GP_ARRAY = TMAX * 16 * GP_PITCH;            // floats per array and buffer
+      const int64_t n_groups = GS ? K / (GS ? GS : 1) : 0;
+      float gfetch[GS ? TMAX : 1];
+      auto request_groups = [&](int kc_for) {  // thread -> (array, row, group) of every tile of the pass
+        const int et = threadIdx.x, arr = et >> 8, r = (et >> 4) & 15, c = et & 15;
+        const float* src = arr ? bias : sw;
+#pragma unroll
+        for (int j = 0; j < (GS ? TMAX : 1); ++j) {
+          const int64_t row = ((static_cast<int64_t>(ps.tile0) + j) << 4) + r;
+          const int64_t grp_i = static_cast<int64_t>(kc_for) * GPC + c;
+          gfetch[j] = (c < GPC && j < pass_tiles && row < N && grp_i < n_groups) ? __ldg(src + row * n_groups + grp_i) : 0.0f;
+        }
+      };
+      auto park_groups = [&](int buf) {
+        const int et = threadIdx.x, arr = et >> 8, r = (et >> 4) & 15, c = et & 15;
+        if (c < GPC) {
+#pragma unroll
+          for (int j = 0; j < (GS ? TMAX : 1); ++j) gp[(buf * 2 + arr) * GP_ARRAY + (j * 16 + r) * GP_PITCH + c] = gfetch[j];
+        }
+      };
+      int gbuf = 0;
+      if (GS != 0) {  // first chunk of the pass: nothing to hide behind
+        request_groups(ps.kc0);
+        park_groups(0);
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+      }
+
+      for (int kc = ps.kc0; kc < ps.kc1 && (GS != 0 || ok); ++kc, ++xi) {
         const int xb = xi % XB;
         const uint32_t xphase = static_cast<uint32_t>((xi / XB) & 1);
         const bool k_ok = static_cast<int64_t>(kc) * KC + koff < K;               // this lane
         const bool warp_k_ok = static_cast<int64_t>(kc) * KC + warp * 64 < K;     // any lane of the warp
+        if (GS != 0 && kc + 1 < ps.kc1) request_groups(kc + 1);
+        do {  // (a warp whose wait ran out still takes part in the barriers below)
+        if (!ok) break;
         if (!wo_mbar_wait(xfull_bar(xb), xphase)) {
           atomicCAS(&g_wo_status, 0, 2);
           ok = false;
@@ -571,52 +613,17 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                             RawOperand<XT>::kOnes, xa[nt][2 * q], xa[nt][2 * q + 1]);
           }
         }
-        // group-wise format: scale and bias of this warp's group for rows g and g + 8 of the first tile
-        // (those of tile j + 1 are fetched while tile j is being multiplied)
-        const int64_t n_groups = GS ? K / (GS ? GS : 1) : 0;
-        const int64_t grp = GS ? (static_cast<int64_t>(kc) * KC + warp * 64) / (GS ? GS : 1) : 0;
-        float gq[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // s[row g], s[row g + 8], b[row g], b[row g + 8]
-        auto fetch_group = [&](int j, float (&out)[4]) {
-          const int64_t ra = ((static_cast<int64_t>(ps.tile0) + j) << 4) + g, rb = ra + 8;
-          const bool live = warp_k_ok && j < pass_tiles;
-          out[0] = (live && ra < N) ? __ldg(sw + ra * n_groups + grp) : 0.0f;
-          out[1] = (live && rb < N) ? __ldg(sw + rb * n_groups + grp) : 0.0f;
-          out[2] = (live && ra < N) ? __ldg(bias + ra * n_groups + grp) : 0.0f;
-          out[3] = (live && rb < N) ? __ldg(bias + rb * n_groups + grp) : 0.0f;
+        // this warp's group inside the chunk; its scale and bias for rows g and g + 8 of tile j come from
+        // the shared-memory copy (pitch 17: the eight rows of a quad column fall into different banks)
+        const int gcol = GS ? (warp * 64) / (GS ? GS : 1) : 0;
+        const float* gcur = gp + gbuf * 2 * GP_ARRAY;
+        auto read_group = [&](int j, float (&out)[4]) {  // s[row g], s[row g + 8], b[row g], b[row g + 8]
+          const float* sc = gcur + (j * 16 + g) * GP_PITCH + gcol;
+          out[0] = sc[0];
+          out[1] = sc[8 * GP_PITCH];
+          out[2] = sc[GP_ARRAY];
+          out[3] = sc[GP_ARRAY + 8 * GP_PITCH];
         };
-        if (GS != 0) {
-          fetch_group(0, gq);
-          // The group parameters of the NEXT chunk are pulled into L2 now (no registers involved): a first
-          // touch comes from DRAM, about a microsecond away, far more than the tile-ahead fetch above hides.
-          // Lane (g, t) covers rows g and g + 8 of tiles t, t + 4, ... of the pass.
-          int pf_tile0 = ps.tile0, pf_tiles = pass_tiles, pf_kc = kc + 1;
-          if (pf_kc >= ps.kc1) {  // last chunk of this pass: look at the first chunk of the next one
-            RingWalk<TMAX> peek = walk;
-            RingPass nx;
-            if (peek.next(nx)) {
-              pf_tile0 = nx.tile0;
-              pf_tiles = nx.n_tiles;
-              pf_kc = nx.kc0;
-            } else {
-              pf_tiles = 0;
-            }
-          }
-          const int64_t nk = static_cast<int64_t>(pf_kc) * KC + warp * 64;
-          if (nk < K) {
-            const int64_t ngrp = nk / (GS ? GS : 1);
-            for (int j = t; j < pf_tiles; j += 4) {
-              const int64_t ra = ((static_cast<int64_t>(pf_tile0) + j) << 4) + g, rb = ra + 8;
-              if (ra < N) {
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(sw + ra * n_groups + ngrp));
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(bias + ra * n_groups + ngrp));
-              }
-              if (rb < N) {
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(sw + rb * n_groups + ngrp));
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(bias + rb * n_groups + ngrp));
-              }
-            }
-          }
-        }
 #pragma unroll
         for (int j = 0; j < TMAX; ++j) {
           if (j < pass_tiles && ok) {
@@ -646,8 +653,8 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                       mma_16816<XT>(acc[j][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
                   }
                 } else {
-                  float gnext[4];
-                  fetch_group(j + 1, gnext);  // in flight while this tile's MMAs run
+                  float gq[4];
+                  read_group(j, gq);
                   float part[NT][4];
 #pragma unroll
                   for (int nt = 0; nt < NT; ++nt)
@@ -670,8 +677,6 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                     acc[j][nt][2] = fmaf(part[nt][2] * c1, gq[1], fmaf(xsum[nt][0] * cx, gq[3], acc[j][nt][2]));
                     acc[j][nt][3] = fmaf(part[nt][3] * c1, gq[1], fmaf(xsum[nt][1] * cx, gq[3], acc[j][nt][3]));
                   }
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) gq[i] = gnext[i];
                 }
               }
               if (j % GRP == GRP - 1 || j == pass_tiles - 1) {
@@ -687,6 +692,12 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         }
         __syncwarp();
         if (lane == 0 && ok) wo_mbar_arrive(xempty_bar(xb));
+        } while (false);
+        if (GS != 0) {
+          if (kc + 1 < ps.kc1) park_groups(gbuf ^ 1);
+          asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");  // parked values visible; old buffer free
+          gbuf ^= 1;
+        }
       }
 
       // ---- split-K reduction of this pass across the 16 consumer warps ----

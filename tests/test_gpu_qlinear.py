@@ -158,3 +158,33 @@ def test_multi_destination_epilogue(ops):
         assert torch.equal(full0[:, N:2 * N], want) and torch.equal(full1[:, 2 * N:], want)
         assert not full0[:, :N].any() and not full0[:, 2 * N:].any() and not full1[:, :2 * N].any()
     assert torch.equal(ref, ops.qlinear_i8(a, b, sx, sw, variant=1))
+
+
+@pytest.mark.parametrize("scheme,qmin,qmax,signed", [("tensor_affine", 0, 255, False), ("tensor_symmetric", -128, 127, True),
+                                                     ("token_symmetric", -128, 127, True)])
+@pytest.mark.parametrize("M,N,K", [(1, 64, 16), (64, 4096, 1024), (300, 200, 328)])
+def test_single_call_dynamic_linear_equals_the_separate_calls(scheme, qmin, qmax, signed, M, N, K):
+    """lc_dynamic_linear_f32 (quantize + GEMM from one entry point, one workspace) gives the bits of
+    the separate quantize and GEMM calls, call after call on a reused workspace."""
+    from lucid_b200._C import ops
+
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    wq = ops.pad_rows_to_16(torch.randint(-128, 128, (N, K), device="cuda", dtype=torch.int8, generator=g))
+    sw = torch.rand(N, device="cuda", generator=g) * 0.01 + 1e-3
+    bias = torch.randn(N, device="cuda", generator=g)
+    wsum = ops.rowsum_s8(wq)
+    ws = ops.dynamic_linear_workspace(M, K, torch.device("cuda", torch.cuda.current_device()))
+    ws.fill_(0xFF)  # the entry point must not rely on what the buffer holds
+    for i in range(3):
+        x = torch.randn(M, K, device="cuda", generator=g) * (i + 1)
+        y = ops.dynamic_linear(x, scheme, qmin, qmax, signed, wq, sw, bias, wsum, ws, fresh=(i == 0))
+        code_dtype = torch.int8 if signed else torch.uint8
+        if scheme == "token_symmetric":
+            xq, sx, _ = ops.dynamic_quantize_rows(x, True, qmin, qmax, signed, 1e-8, code_dtype, pad_rows_to_16=True)
+            want = ops.qlinear_i8(xq, wq, sx, sw, bias=bias)
+        else:
+            sym = scheme == "tensor_symmetric"
+            xq, sx, zx, _ = ops.dynamic_quantize_tensor(x, sym, qmin, qmax, signed, 1e-8, code_dtype, pad_rows_to_16=True)
+            needs_zp = not (sym and signed)
+            want = ops.qlinear_i8(xq, wq, sx, sw, bias=bias, zx=zx if needs_zp else None, wsum=wsum if needs_zp else None)
+        assert torch.equal(y, want)
