@@ -384,9 +384,18 @@ template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 
 __global__ void __launch_bounds__(ring::kThreads, 1)
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w1,
                       const __grid_constant__ CUtensorMap tmap_x,
+                      const XT* __restrict__ xg, int64_t ldx,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
                       const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, const RingPlan plan,
                       int overlap, const WoEpilogue epi) {
+  // XB = 0 (batches of up to 8): the consumer lanes load their activation fragments straight from
+  // global memory (a warp reads 128 contiguous bytes of each of its 8 batch rows; the activations are
+  // L2-resident and the loads of chunk kc + 1 are issued at the top of chunk kc), instead of having the
+  // producer stage every chunk in shared memory.  That takes the activation boxes out of the SM's TMA
+  // queue -- for a long-K matrix they were every second request -- and gives their shared memory to the ring.
+  constexpr bool XDIRECT = XB == 0;
+  static_assert(!XDIRECT || NT == 1, "direct activation loads keep one batch tile in registers");
+  constexpr int XBN = XB > 0 ? XB : 1;  // (divisor of dead code in the direct instantiation)
   static_assert(GS == 0 || GS == 64 || GS == 128, "group sizes the 64-byte warp slice fits into");
   static_assert(GS == 0 || !SWIGLU, "the fused SwiGLU epilogue is for per-channel weights");
   using namespace ring;
@@ -468,18 +477,20 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       RingPass ps;
       while (ok && walk.next(ps)) {
         for (int kc = ps.kc0; kc < ps.kc1 && ok; ++kc, ++xi) {
-          const int xb = xi % XB;
-          const uint32_t xphase = static_cast<uint32_t>((xi / XB) & 1);
-          if (!wo_mbar_wait(xempty_bar(xb), xphase ^ 1u)) {
+          const int xb = xi % XBN;
+          const uint32_t xphase = static_cast<uint32_t>((xi / XBN) & 1);
+          if (!XDIRECT && !wo_mbar_wait(xempty_bar(xb), xphase ^ 1u)) {
             atomicCAS(&g_wo_status, 0, 1);
             ok = false;
             break;
           }
           // activations: [COLS rows x KC elements] box of 8-byte units, rows >= B read as zero
-          wo_mbar_expect(xfull_bar(xb), COLS * X_PITCH);
-          wo_tma_load_2d(x_base + xb * COLS * X_PITCH, &tmap_x, kc * (KC / 4), 0, xfull_bar(xb));
-          xarmed_mask |= 1u << xb;
-          xarmed_parity = (xarmed_parity & ~(1u << xb)) | (xphase << xb);
+          if (!XDIRECT) {
+            wo_mbar_expect(xfull_bar(xb), COLS * X_PITCH);
+            wo_tma_load_2d(x_base + xb * COLS * X_PITCH, &tmap_x, kc * (KC / 4), 0, xfull_bar(xb));
+            xarmed_mask |= 1u << xb;
+            xarmed_parity = (xarmed_parity & ~(1u << xb)) | (xphase << xb);
+          }
           for (int j = 0; j < ps.n_tiles; j += GRP, ++issued) {
             if (issued >= prefilled) {
               if (!wo_mbar_wait(empty_bar(stage), phase ^ 1u)) {
@@ -561,6 +572,21 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           for (int j = 0; j < (GS ? TMAX : 1); ++j) gp[(buf * 2 + arr) * GP_ARRAY + (j * 16 + r) * GP_PITCH + c] = gfetch[j];
         }
       };
+      // direct activation loads: lane (g, t) takes elements [kc * KC + koff, +16) of batch row g
+      uint32_t xnext[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+      auto load_x = [&](int kc_for, uint32_t (&out)[8]) {
+        const int64_t k = static_cast<int64_t>(kc_for) * KC + koff;
+        if (kc_for >= 0 && k < K && g < nb) {
+          const uint4* px = reinterpret_cast<const uint4*>(xg + static_cast<int64_t>(g) * ldx + k);
+          const uint4 lo = __ldg(px), hi = __ldg(px + 1);
+          out[0] = lo.x; out[1] = lo.y; out[2] = lo.z; out[3] = lo.w;
+          out[4] = hi.x; out[5] = hi.y; out[6] = hi.z; out[7] = hi.w;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) out[i] = 0u;
+        }
+      };
+      if (XDIRECT) load_x(ps.kc0, xnext);
       int gbuf = 0;
       if (GS != 0) {  // first chunk of the pass: nothing to hide behind
         request_groups(ps.kc0);
@@ -569,31 +595,37 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       }
 
       for (int kc = ps.kc0; kc < ps.kc1 && (GS != 0 || ok); ++kc, ++xi) {
-        const int xb = xi % XB;
-        const uint32_t xphase = static_cast<uint32_t>((xi / XB) & 1);
+        const int xb = xi % XBN;
+        const uint32_t xphase = static_cast<uint32_t>((xi / XBN) & 1);
         const bool k_ok = static_cast<int64_t>(kc) * KC + koff < K;               // this lane
         const bool warp_k_ok = static_cast<int64_t>(kc) * KC + warp * 64 < K;     // any lane of the warp
         if (GS != 0 && kc + 1 < ps.kc1) request_groups(kc + 1);
         do {  // (a warp whose wait ran out still takes part in the barriers below)
         if (!ok) break;
-        if (!wo_mbar_wait(xfull_bar(xb), xphase)) {
+        if (!XDIRECT && !wo_mbar_wait(xfull_bar(xb), xphase)) {
           atomicCAS(&g_wo_status, 0, 2);
           ok = false;
           break;
         }
         // activation fragments of this chunk: 16 consecutive elements per batch row
         uint32_t xa[NT][8];
+        if constexpr (XDIRECT) {
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const int b = nt * 8 + g;
-          if (k_ok && b < nb) {
-            const uint32_t xs = x_base + (xb * COLS + b) * X_PITCH + koff * 2;
-            const uint4 lo = wo_lds128(xs), hi = wo_lds128(xs + 16);
-            xa[nt][0] = lo.x; xa[nt][1] = lo.y; xa[nt][2] = lo.z; xa[nt][3] = lo.w;
-            xa[nt][4] = hi.x; xa[nt][5] = hi.y; xa[nt][6] = hi.z; xa[nt][7] = hi.w;
-          } else {
+          for (int i = 0; i < 8; ++i) xa[0][i] = xnext[i];
+          load_x(kc + 1 < ps.kc1 ? kc + 1 : -1, xnext);  // in flight while this chunk is multiplied
+        } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) xa[nt][i] = 0u;
+          for (int nt = 0; nt < NT; ++nt) {
+            const int b = nt * 8 + g;
+            if (k_ok && b < nb) {
+              const uint32_t xs = x_base + (xb * COLS + b) * X_PITCH + koff * 2;
+              const uint4 lo = wo_lds128(xs), hi = wo_lds128(xs + 16);
+              xa[nt][0] = lo.x; xa[nt][1] = lo.y; xa[nt][2] = lo.z; xa[nt][3] = lo.w;
+              xa[nt][4] = hi.x; xa[nt][5] = hi.y; xa[nt][6] = hi.z; xa[nt][7] = hi.w;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) xa[nt][i] = 0u;
+            }
           }
         }
         if (GS != 0) {  // sums of x are per group: restart them for this chunk
@@ -691,7 +723,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           }
         }
         __syncwarp();
-        if (lane == 0 && ok) wo_mbar_arrive(xempty_bar(xb));
+        if (!XDIRECT && lane == 0 && ok) wo_mbar_arrive(xempty_bar(xb));
         } while (false);
         if (GS != 0) {
           if (kc + 1 < ps.kc1) park_groups(gbuf ^ 1);
@@ -1082,7 +1114,7 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = overlap ? 1 : 0;
-  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_w1, map_x, B, K, N, sw, bias, y, ldy, plan,
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_w1, map_x, x, ldx, B, K, N, sw, bias, y, ldy, plan,
                                              overlap ? 1 : 0, epi);
   if (err != cudaSuccess) return fail(LC_ERR_CUDA, "wo_linear_s8 (ring): %s", cudaGetErrorString(err));
   return check_launch("wo_linear_s8 (ring)");
@@ -1097,9 +1129,9 @@ static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
   const bool few = (tiles + sms - 1) / sms <= 2;
   // two row tiles per TMA box where the ring stays at least three boxes deep (batches up to 8);
   // measured on the decode MLP: 40.8 us against 41.6 us with one tile per box
-  if (B <= 8)
-    return few ? launch_wo_ring_inst<XT, 1, 2, 4, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st)
-               : launch_wo_ring_inst<XT, 1, 8, 2, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
+  if (B <= 8)  // XB = 0: activation fragments loaded by the consumer lanes themselves
+    return few ? launch_wo_ring_inst<XT, 1, 2, 0, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st)
+               : launch_wo_ring_inst<XT, 1, 8, 0, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
   if (B <= 16)
     return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st)
                : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
@@ -1180,8 +1212,8 @@ static int32_t launch_group_ring(const XT* x, int64_t B, int64_t K, const uint8_
     XT* yb = y + b0 * N;
     int32_t rc;
     if (bc <= 8)
-      rc = few ? launch_wo_ring_inst<XT, 1, 2, 4, false, 2, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
-               : launch_wo_ring_inst<XT, 1, 4, 2, false, 2, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+      rc = few ? launch_wo_ring_inst<XT, 1, 2, 0, false, 2, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
+               : launch_wo_ring_inst<XT, 1, 4, 0, false, 2, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
     else if (bc <= 16)
       rc = few ? launch_wo_ring_inst<XT, 2, 2, 3, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
                : launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
