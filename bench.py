@@ -452,12 +452,11 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
         counter = [0]
         overlap = [True]  # weights are constants: each kernel may prefetch them while the one before drains
 
-        def mlp_step():  # a decode loop: every kernel knows which weights stream next (L2 prefetch hint)
+        def mlp_step():
             (wgu, sgu), (wd, sd) = sets[counter[0] % 3]
-            after = sets[(counter[0] + 1) % 3][0][0]
             counter[0] += 1
-            h = ops.wo_swiglu_s8(xb, wgu, sgu, overlap_previous=overlap[0], next_weight=wd)
-            return ops.wo_linear_s8(h, wd, sd, overlap_previous=overlap[0], next_weight=after)
+            h = ops.wo_swiglu_s8(xb, wgu, sgu, overlap_previous=overlap[0])
+            return ops.wo_linear_s8(h, wd, sd, overlap_previous=overlap[0])
 
         nbytes = 3 * H * F + (2 * F + H) * 4
         eager_ms = time_loop(torch, mlp_step, 60, 6)
@@ -818,12 +817,11 @@ def replica_companions(torch, ops, peaks, steps: int = 30) -> dict:
         xb = torch.randn(batch, H, device=dev, generator=g).to(torch.bfloat16)
         counter = [0]
 
-        def mlp_step():  # a decode loop: every kernel knows which weights stream next (L2 prefetch hint)
+        def mlp_step():
             (wgu, sgu), (wd, sd) = sets[counter[0] % 3]
-            after = sets[(counter[0] + 1) % 3][0][0]
             counter[0] += 1
-            h = ops.wo_swiglu_s8(xb, wgu, sgu, overlap_previous=True, next_weight=wd)
-            return ops.wo_linear_s8(h, wd, sd, overlap_previous=True, next_weight=after)
+            h = ops.wo_swiglu_s8(xb, wgu, sgu, overlap_previous=True)
+            return ops.wo_linear_s8(h, wd, sd, overlap_previous=True)
 
         try:
             ms = graph_time(torch, mlp_step, reps=6, replays=10)

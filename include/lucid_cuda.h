@@ -327,13 +327,7 @@ int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_
                            const int8_t* wq, int64_t ldw, int64_t N, const float* sw, const float* bias,
                            int32_t relu, const float* out_scale, const float* out_zp, int32_t quant_min,
                            int32_t quant_max, void* y, int64_t ldy, int32_t flags, void* workspace,
-                           int64_t workspace_bytes, const int8_t* next_wq, int64_t next_ldw, int64_t next_N,
-                           int64_t next_K, void* stream);
-/* next_wq / next_ldw / next_N / next_K (NULL / 0: none) name the int8 weight [next_N, next_K] of the
- * weight-streaming launch that will follow this one on the stream (the down projection after gate /
- * up, the next layer's first matrix after this layer's last).  Each CTA, once it has issued its own
- * last load, asks the L2 for the first boxes its successor will read, so HBM keeps working while one
- * kernel winds down and the next starts up.  A pure prefetch hint: results never depend on it. */
+                           int64_t workspace_bytes, void* stream);
 
 /* Scratch for the _ex weight-only entry points (may be NULL).  With it, the kernel that streams large
  * weights gives every SM the same number of bytes whatever the shape: work is cut into (16-row tile,
@@ -365,7 +359,7 @@ int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K
 int32_t lc_wo_swiglu_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
                            const int8_t* wq, int64_t ldw, int64_t N2, const float* sw, const float* bias,
                            void* y, int64_t ldy, int32_t flags, void* workspace, int64_t workspace_bytes,
-                           const int8_t* next_wq, int64_t next_ldw, int64_t next_N, int64_t next_K, void* stream);
+                           void* stream);
 
 /* ---- weight-only Linear on the tensor cores, for more rows than a GEMV handles ----
  * The statically quantized Linear's forward, dequantize(W) -> F.linear -> (ReLU) -> fake_quantize

@@ -81,10 +81,9 @@ SIGNATURES = {
     "lc_split_f32_bf16x3": (_i32, [_p, _i64, _i64, _i64, _p, _i64, _p, _p]),
     "lc_wo_linear_s8": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _i32, _p]),
     "lc_wo_linear_s8_ex": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _i32, _p, _p, _i32, _i32, _p, _i64,
-                                  _i32, _p, _i64, _p, _i64, _i64, _i64, _p]),
+                                  _i32, _p, _i64, _p]),
     "lc_wo_linear_workspace_bytes": (_i64, [_i64]),
-    "lc_wo_swiglu_s8_ex": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _i32, _p, _i64, _p, _i64,
-                                  _i64, _i64, _p]),
+    "lc_wo_swiglu_s8_ex": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _i32, _p, _i64, _p]),
     "lc_wo_swiglu_s8": (_i32, [_p, _i32, _i64, _i64, _i64, _p, _i64, _i64, _p, _p, _p, _i64, _i32, _p]),
     "lc_wo_linear_status": (_i32, [C.POINTER(_i32), _i32]),
     "lc_group_quantize_f32": (_i32, [_p, _i64, _i64, _i32, _i32, _p, _p, _p, _p]),

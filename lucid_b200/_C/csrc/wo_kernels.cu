@@ -341,18 +341,6 @@ struct RingPass {
   bool partial;
 };
 
-// Hint for the time between two weight-streaming kernels: when a CTA has issued its last load it asks
-// the L2 for the first boxes the same-numbered CTA of the NEXT kernel will want (that kernel's weights
-// are known to the host -- the down projection after gate / up, the next layer after this one), so HBM
-// keeps working while this CTA reduces and exits and the next one starts up, and the next kernel's ring
-// fills from L2.  Pure prefetches: no effect on results.
-struct RingPrefetch {
-  int ctas;          // CTAs of the next launch (0: no hint)
-  int row_stride;    // rows between the shares of consecutive CTAs
-  int rows;          // rows of a share to prefetch (multiple of 16)
-  int kchunks;       // 1024-byte K chunks to prefetch
-};
-
 template <int TMAX>
 struct RingWalk {
   long long u, u_end;
@@ -395,8 +383,8 @@ __device__ __forceinline__ int ring_owner(long long u, long long units, int grid
 template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0>
 __global__ void __launch_bounds__(ring::kThreads, 1)
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w1,
-                      const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_next,
-                      const RingPrefetch pf, const XT* __restrict__ xg, int64_t ldx,
+                      const __grid_constant__ CUtensorMap tmap_x,
+                      const XT* __restrict__ xg, int64_t ldx,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
                       const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, const RingPlan plan,
                       int overlap, const WoEpilogue epi) {
@@ -524,14 +512,6 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           }
         }
       }
-      // every load of this CTA is issued: start pulling the next kernel's first boxes into L2
-      for (int c2 = blockIdx.x; c2 < pf.ctas; c2 += gridDim.x)
-        for (int kc = 0; kc < pf.kchunks; ++kc)
-          for (int r = 0; r < pf.rows; r += 16)
-            asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
-                             reinterpret_cast<uint64_t>(&tmap_next)),
-                         "r"(kc * (KC / 4)), "r"(c2 * pf.row_stride + r)
-                         : "memory");
       // do not leave while one of this CTA's bulk copies may still be landing
       for (int s = 0; s < S; ++s)
         if (armed_mask & (1u << s)) wo_mbar_wait(full_bar(s), (armed_parity >> s) & 1u);
@@ -1071,8 +1051,6 @@ static int32_t launch_wo_mma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
 struct RingScratch {
   void* ptr;
   int64_t bytes;
-  const int8_t* next_w = nullptr;  // weights of the streaming launch that follows on the stream, or null
-  int64_t next_ldw = 0, next_N = 0, next_K = 0;
 };
 constexpr int64_t kRingSlotBytes = 16 * 32 * 4;  // 16 rows * largest COLS floats
 
@@ -1136,25 +1114,7 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = overlap ? 1 : 0;
-  // prefetch hint: the first ~192 KB of every CTA's share of the next launch (same batch class assumed:
-  // whole tiles per CTA, up to 8 of them per pass for batches of up to 8, 4 / 1 above)
-  CUtensorMap map_next = map_w1;
-  RingPrefetch pf = {0, 0, 0, 0};
-  if (scratch.next_w && scratch.next_N > 0 && scratch.next_K >= 16 && scratch.next_ldw % 16 == 0 &&
-      aligned(scratch.next_w, 16)) {
-    const int64_t ntiles = (scratch.next_N + 15) / 16, nper = (ntiles + sms - 1) / sms;
-    const int64_t pass_tiles = NT == 1 ? (nper <= 2 ? 2 : 8) : NT == 2 ? (nper <= 2 ? 2 : 4) : 1;
-    const int64_t rows = 16 * (nper < pass_tiles ? nper : pass_tiles);
-    const int64_t nkc = (scratch.next_K + ring::KC - 1) / ring::KC;
-    int64_t kch = (192 * 1024 + rows * ring::KC - 1) / (rows * ring::KC);
-    kch = kch < nkc ? kch : nkc;
-    if (encode_tensor_map_2d(&map_next, CU_TENSOR_MAP_DATA_TYPE_UINT32, scratch.next_w,
-                             static_cast<uint64_t>(scratch.next_K / 4), static_cast<uint64_t>(scratch.next_N),
-                             static_cast<uint64_t>(scratch.next_ldw), ring::KC / 4, 16, CU_TENSOR_MAP_SWIZZLE_NONE) == LC_OK)
-      pf = {static_cast<int>((ntiles + nper - 1) / nper), static_cast<int>(nper * 16), static_cast<int>(rows),
-            static_cast<int>(kch)};
-  }
-  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_w1, map_x, map_next, pf, x, ldx, B, K, N, sw, bias, y, ldy, plan,
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_w1, map_x, x, ldx, B, K, N, sw, bias, y, ldy, plan,
                                              overlap ? 1 : 0, epi);
   if (err != cudaSuccess) return fail(LC_ERR_CUDA, "wo_linear_s8 (ring): %s", cudaGetErrorString(err));
   return check_launch("wo_linear_s8 (ring)");
@@ -1283,7 +1243,7 @@ extern "C" int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch
                                    const float* sw, const float* bias, void* y, int64_t ldy,
                                    int32_t flags, void* stream) {
   return lc_wo_linear_s8_ex(x, x_dtype, batch, K, ldx, wq, ldw, N, sw, bias, 0, nullptr, nullptr, 0, 0, y, ldy, flags,
-                            nullptr, 0, nullptr, 0, 0, 0, stream);
+                            nullptr, 0, stream);
 }
 
 extern "C" int64_t lc_wo_linear_workspace_bytes(int64_t N) {
@@ -1295,8 +1255,7 @@ extern "C" int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t ba
                                       const int8_t* wq, int64_t ldw, int64_t N, const float* sw, const float* bias,
                                       int32_t relu, const float* out_scale, const float* out_zp, int32_t quant_min,
                                       int32_t quant_max, void* y, int64_t ldy, int32_t flags, void* workspace,
-                                      int64_t workspace_bytes, const int8_t* next_wq, int64_t next_ldw,
-                                      int64_t next_N, int64_t next_K, void* stream) {
+                                      int64_t workspace_bytes, void* stream) {
   const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;
   if (batch < 0 || N < 0 || K <= 0 || ldx < K || ldw < K || ldy < N)
     return fail(LC_ERR_INVALID_ARG, "wo_linear_s8: bad shape");
@@ -1307,7 +1266,7 @@ extern "C" int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t ba
   cudaStream_t st = as_stream(stream);
   const WoEpilogue epi = {relu ? 1 : 0, out_scale, out_zp, static_cast<float>(quant_min),
                           static_cast<float>(quant_max)};
-  const RingScratch scratch = {workspace, workspace ? workspace_bytes : 0, next_wq, next_ldw, next_N, next_K};
+  const RingScratch scratch = {workspace, workspace ? workspace_bytes : 0};
   switch (x_dtype) {
     case LC_F32:
       return wo_linear_typed<float>(x, batch, K, ldx, wq, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
@@ -1322,15 +1281,13 @@ extern "C" int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t ba
 extern "C" int32_t lc_wo_swiglu_s8(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
                                    const int8_t* wq, int64_t ldw, int64_t N2, const float* sw,
                                    const float* bias, void* y, int64_t ldy, int32_t flags, void* stream) {
-  return lc_wo_swiglu_s8_ex(x, x_dtype, batch, K, ldx, wq, ldw, N2, sw, bias, y, ldy, flags, nullptr, 0, nullptr, 0, 0, 0,
-                            stream);
+  return lc_wo_swiglu_s8_ex(x, x_dtype, batch, K, ldx, wq, ldw, N2, sw, bias, y, ldy, flags, nullptr, 0, stream);
 }
 
 extern "C" int32_t lc_wo_swiglu_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
                                       const int8_t* wq, int64_t ldw, int64_t N2, const float* sw,
                                       const float* bias, void* y, int64_t ldy, int32_t flags, void* workspace,
-                                      int64_t workspace_bytes, const int8_t* next_wq, int64_t next_ldw,
-                                      int64_t next_N, int64_t next_K, void* stream) {
+                                      int64_t workspace_bytes, void* stream) {
   const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;
   if (batch < 0 || N2 < 0 || K <= 0 || ldx < K || ldw < K || ldy < N2 / 2)
     return fail(LC_ERR_INVALID_ARG, "wo_swiglu_s8: bad shape");
@@ -1342,7 +1299,7 @@ extern "C" int32_t lc_wo_swiglu_s8_ex(const void* x, int32_t x_dtype, int64_t ba
     return fail(LC_ERR_UNSUPPORTED, "wo_swiglu_s8: K, ldw must be multiples of 16, ldx of 8, pointers 16-byte aligned");
   cudaStream_t st = as_stream(stream);
   const WoEpilogue none = {0, nullptr, nullptr, 0.0f, 0.0f};
-  const RingScratch scratch = {workspace, workspace ? workspace_bytes : 0, next_wq, next_ldw, next_N, next_K};
+  const RingScratch scratch = {workspace, workspace ? workspace_bytes : 0};
   if (x_dtype == LC_BF16)
     return launch_wo_tma<__nv_bfloat16, true>(static_cast<const __nv_bfloat16*>(x), batch, K, ldx, wq, ldw, N2, sw,
                                               bias, static_cast<__nv_bfloat16*>(y), ldy, overlap, none, scratch, st);

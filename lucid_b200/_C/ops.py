@@ -646,7 +646,7 @@ def wo_workspace(dev: torch.device, rows: int):
 
 
 def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous: bool = False, relu: bool = False, out_scale=None,
-                 out_zp=None, quant_min: int = 0, quant_max: int = 255, balanced: bool = False, next_weight=None):
+                 out_zp=None, quant_min: int = 0, quant_max: int = 255, balanced: bool = False):
     """``y = (x @ wq^T) * sw + bias`` with float activations; ``y`` has ``x``'s dtype.  With
     ``relu`` / ``out_scale`` and ``out_zp`` (device scalars) the same kernel goes on to apply the
     ReLU and the fake-quantize onto the calibrated output grid of a static Linear.
@@ -656,9 +656,7 @@ def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous: bool = False, relu: b
     before that kernel started.  ``balanced`` gives the weight-streaming kernel its scratch, so that every
     SM streams the same number of bytes (K is cut between CTAs); by default whole 32-row boxes are dealt
     out, which measures faster on B200 for the decode shapes (the ticketed finish of the shared boxes
-    costs more than the idle SMs it removes: decode MLP 53 us against 41 us).  ``next_weight``: the int8
-    weight of the weight-streaming call that follows on the stream, as an L2 prefetch hint (no effect on
-    results)."""
+    costs more than the idle SMs it removes: decode MLP 53 us against 41 us)."""
     dev = _need_cuda(x2d, wq, sw, bias, out_scale, out_zp)
     if x2d.dtype not in (torch.float32, torch.bfloat16, torch.float16):
         raise TypeError(f"wo_linear_s8: activations must be fp32/bf16/fp16, got {x2d.dtype}")
@@ -682,16 +680,8 @@ def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous: bool = False, relu: b
                                      wq.stride(0), N, _ptr(sw_c), _ptr(bias_c), 1 if relu else 0, _ptr(os_c),
                                      _ptr(oz_c), int(quant_min), int(quant_max), y.data_ptr(), N,
                                      1 if overlap_previous else 0, _ptr(ws), 0 if ws is None else ws.numel(),
-                                     *_next_weight_args(next_weight), _stream(dev)))
+                                     _stream(dev)))
     return y
-
-
-def _next_weight_args(next_weight):
-    """(pointer, row pitch, rows, columns) of the int8 weight the next weight-streaming launch on the
-    stream will read, for the kernels' L2 prefetch hint; zeros when there is none."""
-    if next_weight is None or next_weight.dtype != torch.int8 or next_weight.dim() != 2 or next_weight.stride(1) != 1:
-        return None, 0, 0, 0
-    return next_weight.data_ptr(), next_weight.stride(0), next_weight.shape[0], next_weight.shape[1]
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -706,8 +696,7 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.cat([g, u], dim=1).reshape(2 * f, *gate.shape[1:]).contiguous()
 
 
-def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None, overlap_previous: bool = False, balanced: bool = False,
-                 next_weight=None):
+def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None, overlap_previous: bool = False, balanced: bool = False):
     """``silu(x @ Wg^T * sg) * (x @ Wu^T * su)`` with interleaved int8 gate/up weights
     (see :func:`interleave_gate_up`); bf16 / f16 activations, batch <= 32.
     ``overlap_previous`` as for :func:`wo_linear_s8`."""
@@ -723,7 +712,7 @@ def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None, overlap_previous: bool = False
         check(lib.lc_wo_swiglu_s8_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq_gu.data_ptr(),
                                      wq_gu.stride(0), N2, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N2 // 2,
                                      1 if overlap_previous else 0, _ptr(ws), 0 if ws is None else ws.numel(),
-                                     *_next_weight_args(next_weight), _stream(dev)))
+                                     _stream(dev)))
     return y
 
 

@@ -75,10 +75,6 @@ class WeightOnlyLinear(nn.Module):
             self.bias = None
         self._settled = _SettledBuffers()
         self._wide_cache = {}
-        # int8 weight of the weight-only layer that runs next on the stream (the next decoder layer's first
-        # matrix), if the caller knows it: the decode kernel then warms the L2 with that layer's first boxes
-        # while it winds down.  A hint only; results do not depend on it.
-        self.next_weight_hint: torch.Tensor | None = None
 
     @classmethod
     def from_float(cls, mod: nn.Module, dtype: QDtype = qint8) -> "WeightOnlyLinear":
@@ -96,8 +92,7 @@ class WeightOnlyLinear(nn.Module):
         if 0 < x2.shape[0] <= _GEMV_MAX_ROWS:
             y = _backend.ops().wo_linear_s8(
                 x2, self.weight_int8, self.weight_scale, self.bias,
-                overlap_previous=self._settled(self.weight_int8, self.weight_scale, self.bias),
-                next_weight=self.next_weight_hint)
+                overlap_previous=self._settled(self.weight_int8, self.weight_scale, self.bias))
         elif x2.shape[0] == 0:
             y = x2.new_zeros((0, self.out_features))
         else:  # compute-bound batches: the tensor-core weight-only kernels
@@ -150,8 +145,7 @@ class WeightOnlySwiGLU(nn.Module):
         if fused_ok:
             h = _backend.ops().wo_swiglu_s8(
                 x2, self.gate_up_int8, self.gate_up_scale,
-                overlap_previous=self._settled(self.gate_up_int8, self.gate_up_scale),
-                next_weight=self.down.weight_int8)  # the down projection streams next
+                overlap_previous=self._settled(self.gate_up_int8, self.gate_up_scale))
         else:
             # one product against the interleaved weight; output columns come in blocks of 8 gate / 8 up
             gu = wide_product(x2, self.gate_up_int8, self.gate_up_scale, None, self._wide_cache)

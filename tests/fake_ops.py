@@ -136,7 +136,7 @@ def _finish(y, relu, out_scale, out_zp, quant_min, quant_max):
 
 
 def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous=False, relu=False, out_scale=None, out_zp=None,
-                 quant_min=0, quant_max=255, balanced=False, next_weight=None):
+                 quant_min=0, quant_max=255, balanced=False):
     y = O.weight_only_linear_perchannel(_np(x2d.float()), _np(wq), _np(sw), None if bias is None else _np(bias))
     return torch.tensor(_finish(y, relu, out_scale, out_zp, quant_min, quant_max)).to(x2d.dtype)
 
