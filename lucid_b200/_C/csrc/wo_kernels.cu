@@ -532,18 +532,28 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     RingPass ps;
     while (walk.next(ps)) {
       const int pass_tiles = ps.n_tiles;
-      float acc[TMAX][NT][4];
+      // Dependent mma.sync instructions issue about 150 cycles apart, and a tile's four MMAs per chunk
+      // all add into the same accumulator: with few tiles per pass a warp mostly waits for its own
+      // previous MMA.  So the MMAs of a box are issued tile-inner (neighbouring instructions are
+      // independent) and, where registers allow (at most two tile x batch accumulators), even and odd
+      // K steps add into separate accumulator sets that are summed when the pass is parked.
+      constexpr int AS = (GS == 0 && TMAX * NT <= 2) ? 2 : 1;
+      float acc[AS][TMAX][NT][4];
 #pragma unroll
-      for (int j = 0; j < TMAX; ++j)
+      for (int a = 0; a < AS; ++a)
+#pragma unroll
+        for (int j = 0; j < TMAX; ++j)
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[a][j][nt][i] = 0.0f;
+      float xsum2[2][NT][4];  // per batch column: sums of the activations over this warp's K slices (two chains)
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) acc[j][nt][i] = 0.0f;
-      float xsum[NT][4];  // per batch column: sum over this warp's K slices of the activations
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) xsum[nt][i] = 0.0f;
+          for (int i = 0; i < 4; ++i) xsum2[a][nt][i] = 0.0f;
 
       // Group-wise format: the scales and biases of a chunk -- 16 rows x (KC / GS) groups per tile and
       // array -- are fetched by all 512 consumer threads together, one element each per tile, so that a
@@ -630,20 +640,23 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         }
         if (GS != 0) {  // sums of x are per group: restart them for this chunk
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
+          for (int a = 0; a < 2; ++a)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) xsum[nt][i] = 0.0f;
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) xsum2[a][nt][i] = 0.0f;
         }
         if (warp_k_ok) {
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
+          for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int i = 0; i < 8; ++i) RawOperand<XT>::prescale(xa[nt][i]);
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-              mma_16816<XT>(xsum[nt], RawOperand<XT>::kOnes, RawOperand<XT>::kOnes, RawOperand<XT>::kOnes,
+          for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+              mma_16816<XT>(xsum2[q & 1][nt], RawOperand<XT>::kOnes, RawOperand<XT>::kOnes, RawOperand<XT>::kOnes,
                             RawOperand<XT>::kOnes, xa[nt][2 * q], xa[nt][2 * q + 1]);
-          }
         }
         // this warp's group inside the chunk; its scale and bias for rows g and g + 8 of tile j come from
         // the shared-memory copy (pitch 17: the eight rows of a quad column fall into different banks)
@@ -657,67 +670,89 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           out[3] = sc[GP_ARRAY + 8 * GP_PITCH];
         };
 #pragma unroll
-        for (int j = 0; j < TMAX; ++j) {
-          if (j < pass_tiles && ok) {
-            // the first tile of a box waits for it, the last one (or the last of the pass) frees it
-            if (j % GRP == 0 && !wo_mbar_wait(full_bar(stage), phase)) {
+        for (int jb = 0; jb < TMAX; jb += GRP) {
+          if (jb < pass_tiles && ok) {
+            if (!wo_mbar_wait(full_bar(stage), phase)) {
               atomicCAS(&g_wo_status, 0, 2);
               ok = false;
             } else {
               // warp-uniform skip (mma.sync needs the whole warp); lanes past the end of K
               // inside a live warp contribute zero weights (raw 0 is code 0 in offset binary)
               if (warp_k_ok) {
-                const uint32_t src = base + stage * GSTAGE + (j % GRP) * STAGE + g * W_PITCH + koff;
-                uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = make_uint4(0u, 0u, 0u, 0u);
-                if (k_ok) {
-                  w0 = wo_lds128(src);
-                  w1 = wo_lds128(src + 8 * W_PITCH);
+                uint32_t wr[GRP][2][4];  // per tile of the box: 16 bytes of row g and of row g + 8
+#pragma unroll
+                for (int jj = 0; jj < GRP; ++jj) {
+                  uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = make_uint4(0u, 0u, 0u, 0u);
+                  if (k_ok && jb + jj < pass_tiles) {
+                    const uint32_t src = base + stage * GSTAGE + jj * STAGE + g * W_PITCH + koff;
+                    w0 = wo_lds128(src);
+                    w1 = wo_lds128(src + 8 * W_PITCH);
+                  }
+                  wr[jj][0][0] = w0.x; wr[jj][0][1] = w0.y; wr[jj][0][2] = w0.z; wr[jj][0][3] = w0.w;
+                  wr[jj][1][0] = w1.x; wr[jj][1][1] = w1.y; wr[jj][1][2] = w1.z; wr[jj][1][3] = w1.w;
                 }
-                const uint32_t r0[4] = {w0.x, w0.y, w0.z, w0.w}, r1[4] = {w1.x, w1.y, w1.z, w1.w};
                 if constexpr (GS == 0) {
 #pragma unroll
                   for (int q = 0; q < 4; ++q) {
-                    const uint32_t u0 = r0[q] ^ 0x80808080u, u1 = r1[q] ^ 0x80808080u;
-                    const uint32_t a0 = __byte_perm(u0, 0u, 0x4140u), a2 = __byte_perm(u0, 0u, 0x4342u);
-                    const uint32_t a1 = __byte_perm(u1, 0u, 0x4140u), a3 = __byte_perm(u1, 0u, 0x4342u);
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
-                      mma_16816<XT>(acc[j][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                    for (int jj = 0; jj < GRP; ++jj) {
+                      if (jb + jj < pass_tiles) {
+                        const uint32_t u0 = wr[jj][0][q] ^ 0x80808080u, u1 = wr[jj][1][q] ^ 0x80808080u;
+                        const uint32_t a0 = __byte_perm(u0, 0u, 0x4140u), a2 = __byte_perm(u0, 0u, 0x4342u);
+                        const uint32_t a1 = __byte_perm(u1, 0u, 0x4140u), a3 = __byte_perm(u1, 0u, 0x4342u);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+                          mma_16816<XT>(acc[q % AS][(jb + jj) % TMAX][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                      }
+                    }
                   }
                 } else {
-                  float gq[4];
-                  read_group(j, gq);
-                  float part[NT][4];
+                  float gq[GRP][4];
+                  float part[GRP][NT][4];
 #pragma unroll
-                  for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) part[nt][i] = 0.0f;
-#pragma unroll
-                  for (int q = 0; q < 4; ++q) {  // the codes are unsigned bytes already
-                    const uint32_t a0 = __byte_perm(r0[q], 0u, 0x4140u), a2 = __byte_perm(r0[q], 0u, 0x4342u);
-                    const uint32_t a1 = __byte_perm(r1[q], 0u, 0x4140u), a3 = __byte_perm(r1[q], 0u, 0x4342u);
+                  for (int jj = 0; jj < GRP; ++jj) {
+                    read_group((jb + jj) % TMAX, gq[jj]);
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt)
-                      mma_16816<XT>(part[nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+#pragma unroll
+                      for (int i = 0; i < 4; ++i) part[jj][nt][i] = 0.0f;
+                  }
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {  // the codes are unsigned bytes already
+#pragma unroll
+                    for (int jj = 0; jj < GRP; ++jj) {
+                      if (jb + jj < pass_tiles) {
+                        const uint32_t a0 = __byte_perm(wr[jj][0][q], 0u, 0x4140u), a2 = __byte_perm(wr[jj][0][q], 0u, 0x4342u);
+                        const uint32_t a1 = __byte_perm(wr[jj][1][q], 0u, 0x4140u), a3 = __byte_perm(wr[jj][1][q], 0u, 0x4342u);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+                          mma_16816<XT>(part[jj][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                      }
+                    }
                   }
                   // raw sums -> values: sum(x c) = part * acc_scale, sum(x) = xsum * (sum_scale / 128)
                   const float c1 = RawOperand<XT>::acc_scale(), cx = RawOperand<XT>::sum_scale() * 0.0078125f;
 #pragma unroll
-                  for (int nt = 0; nt < NT; ++nt) {
-                    acc[j][nt][0] = fmaf(part[nt][0] * c1, gq[0], fmaf(xsum[nt][0] * cx, gq[2], acc[j][nt][0]));
-                    acc[j][nt][1] = fmaf(part[nt][1] * c1, gq[0], fmaf(xsum[nt][1] * cx, gq[2], acc[j][nt][1]));
-                    acc[j][nt][2] = fmaf(part[nt][2] * c1, gq[1], fmaf(xsum[nt][0] * cx, gq[3], acc[j][nt][2]));
-                    acc[j][nt][3] = fmaf(part[nt][3] * c1, gq[1], fmaf(xsum[nt][1] * cx, gq[3], acc[j][nt][3]));
+                  for (int jj = 0; jj < GRP; ++jj) {
+                    if (jb + jj < pass_tiles) {
+                      float (&tot)[NT][4] = acc[0][(jb + jj) % TMAX];
+#pragma unroll
+                      for (int nt = 0; nt < NT; ++nt) {
+                        const float x0 = (xsum2[0][nt][0] + xsum2[1][nt][0]) * cx, x1 = (xsum2[0][nt][1] + xsum2[1][nt][1]) * cx;
+                        tot[nt][0] = fmaf(part[jj][nt][0] * c1, gq[jj][0], fmaf(x0, gq[jj][2], tot[nt][0]));
+                        tot[nt][1] = fmaf(part[jj][nt][1] * c1, gq[jj][0], fmaf(x1, gq[jj][2], tot[nt][1]));
+                        tot[nt][2] = fmaf(part[jj][nt][2] * c1, gq[jj][1], fmaf(x0, gq[jj][3], tot[nt][2]));
+                        tot[nt][3] = fmaf(part[jj][nt][3] * c1, gq[jj][1], fmaf(x1, gq[jj][3], tot[nt][3]));
+                      }
+                    }
                   }
                 }
               }
-              if (j % GRP == GRP - 1 || j == pass_tiles - 1) {
-                __syncwarp();
-                if (lane == 0) wo_mbar_arrive(empty_bar(stage));
-                if (++stage == S) {
-                  stage = 0;
-                  phase ^= 1u;
-                }
+              __syncwarp();
+              if (lane == 0) wo_mbar_arrive(empty_bar(stage));
+              if (++stage == S) {
+                stage = 0;
+                phase ^= 1u;
               }
             }
           }
@@ -744,10 +779,14 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           for (int nt = 0; nt < NT; ++nt) {
             // per-channel weights: raw sums -> sum(x * s8), the offset 128 * sum(x) taken out once per pass
             const float c1 = GS ? 1.0f : RawOperand<XT>::acc_scale(), c2 = GS ? 0.0f : RawOperand<XT>::sum_scale();
-            mine[g * RP + nt * 8 + 2 * t] = acc[j][nt][0] * c1 - xsum[nt][0] * c2;
-            mine[g * RP + nt * 8 + 2 * t + 1] = acc[j][nt][1] * c1 - xsum[nt][1] * c2;
-            mine[(g + 8) * RP + nt * 8 + 2 * t] = acc[j][nt][2] * c1 - xsum[nt][0] * c2;
-            mine[(g + 8) * RP + nt * 8 + 2 * t + 1] = acc[j][nt][3] * c1 - xsum[nt][1] * c2;
+            float a4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a4[i] = AS == 2 ? acc[0][j][nt][i] + acc[AS - 1][j][nt][i] : acc[0][j][nt][i];
+            const float x0 = xsum2[0][nt][0] + xsum2[1][nt][0], x1 = xsum2[0][nt][1] + xsum2[1][nt][1];
+            mine[g * RP + nt * 8 + 2 * t] = a4[0] * c1 - x0 * c2;
+            mine[g * RP + nt * 8 + 2 * t + 1] = a4[1] * c1 - x1 * c2;
+            mine[(g + 8) * RP + nt * 8 + 2 * t] = a4[2] * c1 - x0 * c2;
+            mine[(g + 8) * RP + nt * 8 + 2 * t + 1] = a4[3] * c1 - x1 * c2;
           }
         }
       }
