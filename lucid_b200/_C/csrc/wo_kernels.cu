@@ -679,18 +679,40 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
               // warp-uniform skip (mma.sync needs the whole warp); lanes past the end of K
               // inside a live warp contribute zero weights (raw 0 is code 0 in offset binary)
               if (warp_k_ok) {
-                uint32_t wr[GRP][2][4];  // per tile of the box: 16 bytes of row g and of row g + 8
-#pragma unroll
-                for (int jj = 0; jj < GRP; ++jj) {
+                // weights of one tile of the box: 16 bytes of row g and of row g + 8
+                auto load_tile = [&](int jj, uint32_t (&w)[2][4]) {
                   uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = make_uint4(0u, 0u, 0u, 0u);
                   if (k_ok && jb + jj < pass_tiles) {
                     const uint32_t src = base + stage * GSTAGE + jj * STAGE + g * W_PITCH + koff;
                     w0 = wo_lds128(src);
                     w1 = wo_lds128(src + 8 * W_PITCH);
                   }
-                  wr[jj][0][0] = w0.x; wr[jj][0][1] = w0.y; wr[jj][0][2] = w0.z; wr[jj][0][3] = w0.w;
-                  wr[jj][1][0] = w1.x; wr[jj][1][1] = w1.y; wr[jj][1][2] = w1.z; wr[jj][1][3] = w1.w;
-                }
+                  w[0][0] = w0.x; w[0][1] = w0.y; w[0][2] = w0.z; w[0][3] = w0.w;
+                  w[1][0] = w1.x; w[1][1] = w1.y; w[1][2] = w1.z; w[1][3] = w1.w;
+                };
+                if constexpr (GS == 0 && AS == 1) {
+                  // many tiles per pass: their accumulator chains already overlap; one tile at a time keeps
+                  // the register count down (interleaving the box measured slower here: 27.4 against 24.9 us)
+#pragma unroll
+                  for (int jj = 0; jj < GRP; ++jj) {
+                    if (jb + jj < pass_tiles) {
+                      uint32_t w[2][4];
+                      load_tile(jj, w);
+#pragma unroll
+                      for (int q = 0; q < 4; ++q) {
+                        const uint32_t u0 = w[0][q] ^ 0x80808080u, u1 = w[1][q] ^ 0x80808080u;
+                        const uint32_t a0 = __byte_perm(u0, 0u, 0x4140u), a2 = __byte_perm(u0, 0u, 0x4342u);
+                        const uint32_t a1 = __byte_perm(u1, 0u, 0x4140u), a3 = __byte_perm(u1, 0u, 0x4342u);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+                          mma_16816<XT>(acc[0][(jb + jj) % TMAX][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                      }
+                    }
+                  }
+                } else {
+                uint32_t wr[GRP][2][4];
+#pragma unroll
+                for (int jj = 0; jj < GRP; ++jj) load_tile(jj, wr[jj]);
                 if constexpr (GS == 0) {
 #pragma unroll
                   for (int q = 0; q < 4; ++q) {
@@ -746,6 +768,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                       }
                     }
                   }
+                }
                 }
               }
               __syncwarp();
