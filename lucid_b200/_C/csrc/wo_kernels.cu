@@ -118,6 +118,18 @@ __device__ __forceinline__ float wo_finish(float v, const WoEpilogue& e) {
   return v;
 }
 
+// both halves of a packed 16-bit pair, widened exactly to fp32
+template <typename XT>
+__device__ __forceinline__ float2 unpack_pair(uint32_t v);
+template <>
+__device__ __forceinline__ float2 unpack_pair<__nv_bfloat16>(uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack_pair<__half>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+
 constexpr int kWoWarps = 8;
 constexpr int kWoThreads = kWoWarps * 32;
 
@@ -547,7 +559,10 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[a][j][nt][i] = 0.0f;
-      float xsum2[2][NT][4];  // per batch column: sums of the activations over this warp's K slices (two chains)
+      float xlane[NT][2];     // per-channel weights: this lane's share of sum_k x[batch nt*8+g][k], two chains
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) xlane[nt][0] = xlane[nt][1] = 0.0f;
+      float xsum2[2][NT][4];  // group-wise weights: per batch column sums of the chunk's activations (two MMA chains)
 #pragma unroll
       for (int a = 0; a < 2; ++a)
 #pragma unroll
@@ -647,16 +662,34 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
               for (int i = 0; i < 4; ++i) xsum2[a][nt][i] = 0.0f;
         }
         if (warp_k_ok) {
+          if constexpr (GS == 0) {
+            // Per-channel weights: only sum_k x over the whole pass is needed (the 128 of the offset-binary
+            // codes comes out once, when the pass is parked), so every lane adds up its own 16 activations
+            // of the chunk on the FP32 pipe, in two chains, and the lanes are combined at the end of the
+            // pass.  (An all-ones MMA per K step did this before: a third of the MMAs of a two-tile pass,
+            // and mma.sync throughput is what bounds this kernel.)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+              for (int i = 0; i < 8; i += 2) {
+                const float2 p0 = unpack_pair<XT>(xa[nt][i]), p1 = unpack_pair<XT>(xa[nt][i + 1]);
+                xlane[nt][0] += p0.x + p0.y;
+                xlane[nt][1] += p1.x + p1.y;
+              }
+            }
+          }
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int i = 0; i < 8; ++i) RawOperand<XT>::prescale(xa[nt][i]);
+          if constexpr (GS != 0) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
+            for (int q = 0; q < 4; ++q)
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-              mma_16816<XT>(xsum2[q & 1][nt], RawOperand<XT>::kOnes, RawOperand<XT>::kOnes, RawOperand<XT>::kOnes,
-                            RawOperand<XT>::kOnes, xa[nt][2 * q], xa[nt][2 * q + 1]);
+              for (int nt = 0; nt < NT; ++nt)
+                mma_16816<XT>(xsum2[q & 1][nt], RawOperand<XT>::kOnes, RawOperand<XT>::kOnes, RawOperand<XT>::kOnes,
+                              RawOperand<XT>::kOnes, xa[nt][2 * q], xa[nt][2 * q + 1]);
+          }
         }
         // this warp's group inside the chunk; its scale and bias for rows g and g + 8 of tile j come from
         // the shared-memory copy (pitch 17: the eight rows of a quad column fall into different banks)
@@ -794,6 +827,17 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       // every warp parks its partial sums of all tiles of the pass, one barrier, then the
       // 512 threads add the 16 partials of each output in a fixed order (deterministic)
       asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");  // previous pass fully summed
+      // sum_k x of this warp's K slices for the batch columns 2t and 2t+1 this lane's accumulators belong to:
+      // the lane sums (batch row g, slice t) are added over the quad, then fetched from quads 2t and 2t+1
+      float xcol[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float sq = xlane[nt][0] + xlane[nt][1];
+        sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+        sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+        xcol[nt][0] = __shfl_sync(0xffffffffu, sq, (2 * t) * 4);
+        xcol[nt][1] = __shfl_sync(0xffffffffu, sq, (2 * t + 1) * 4);
+      }
 #pragma unroll
       for (int j = 0; j < TMAX; ++j) {
         if (j < pass_tiles) {
@@ -801,11 +845,11 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             // per-channel weights: raw sums -> sum(x * s8), the offset 128 * sum(x) taken out once per pass
-            const float c1 = GS ? 1.0f : RawOperand<XT>::acc_scale(), c2 = GS ? 0.0f : RawOperand<XT>::sum_scale();
+            const float c1 = GS ? 1.0f : RawOperand<XT>::acc_scale(), c2 = GS ? 0.0f : 128.0f;
             float a4[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) a4[i] = AS == 2 ? acc[0][j][nt][i] + acc[AS - 1][j][nt][i] : acc[0][j][nt][i];
-            const float x0 = xsum2[0][nt][0] + xsum2[1][nt][0], x1 = xsum2[0][nt][1] + xsum2[1][nt][1];
+            const float x0 = xcol[nt][0], x1 = xcol[nt][1];
             mine[g * RP + nt * 8 + 2 * t] = a4[0] * c1 - x0 * c2;
             mine[g * RP + nt * 8 + 2 * t + 1] = a4[1] * c1 - x1 * c2;
             mine[(g + 8) * RP + nt * 8 + 2 * t] = a4[2] * c1 - x0 * c2;
