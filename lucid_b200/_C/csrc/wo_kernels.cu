@@ -241,25 +241,33 @@ wo_linear_mma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx
 // Every mbarrier wait is bounded; a wait that runs out records a code in g_wo_status and the
 // CTA drains its copies and returns.
 namespace ring {
-constexpr int kConsumerWarps = 16;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;
-constexpr int kSmemBudget = 225 * 1024;
 constexpr int KC = 1024;               // bytes of K per item (and per activation chunk)
 constexpr int W_PITCH = KC;            // dense TMA box rows (the 2-way bank conflict of the two
                                        // 16-byte loads per item is not measurable)
 constexpr int STAGE = 16 * W_PITCH;    // 16384
 constexpr int X_PITCH = KC * 2;        // activation row pitch (16-bit elements)
 constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 2 GHz
-// split-K partials of a whole pass: [tile][warp][16 rows][8*nt + 1]
-__host__ __device__ constexpr int red_bytes(int nt, int tmax) { return tmax * kConsumerWarps * 16 * (nt * 8 + 1) * 4; }
+// A CTA is one producer warp and CW consumer warps; the consumer warps split the KC bytes of an item
+// row into 64-byte units, KC / (64 * CW) per warp.
+//   CW = 16: one CTA per SM with all of its shared memory.
+//   CW = 8:  two CTAs per SM, half the shared memory each and two units per warp.  The serial stretches
+//            of a pass (activation chunk set-up, split-K reduction, epilogue, the wait for the preceding
+//            grid) then overlap with the other CTA's streaming, and the CTAs of the next launch move in
+//            one at a time while this launch still runs on the other half of the SM.
+__host__ __device__ constexpr int threads(int cw) { return cw * 32 + 32; }
+__host__ __device__ constexpr int ctas_per_sm(int cw) { return cw == 16 ? 1 : 2; }
+// dynamic shared memory of a CTA; two CTAs of 115456 + 1 KB (system) + static fit into an SM's 228 KB
+__host__ __device__ constexpr int smem_budget(int cw) { return cw == 16 ? 225 * 1024 : 115456; }
+// split-K partials of a whole pass: [tile][warp][16 rows][pitch]; the half-size CTA has no room for padding
+__host__ __device__ constexpr int red_pitch(int nt, int cw) { return cw == 16 ? nt * 8 + 1 : nt * 8; }
+__host__ __device__ constexpr int red_bytes(int nt, int tmax, int cw) { return tmax * cw * 16 * red_pitch(nt, cw) * 4; }
 __host__ __device__ constexpr int x_bytes(int nt, int xb) { return xb * nt * 8 * X_PITCH; }
 // group-wise format: two buffers x {scales, biases} x tmax*16 rows x (groups per K chunk, padded to 17)
 constexpr int GP_PITCH = 17;
 __host__ __device__ constexpr int group_bytes(int gs, int tmax) { return gs ? 2 * 2 * tmax * 16 * GP_PITCH * 4 : 0; }
 // a ring stage holds `grp` vertically adjacent 16-row tiles of one K chunk, fetched by one TMA box
-__host__ __device__ constexpr int stages(int nt, int tmax, int xb, int grp, int gs = 0) {
-  return (kSmemBudget - 512 - red_bytes(nt, tmax) - x_bytes(nt, xb) - group_bytes(gs, tmax)) / (STAGE * grp);
+__host__ __device__ constexpr int stages(int nt, int tmax, int xb, int grp, int gs, int cw) {
+  return (smem_budget(cw) - 512 - red_bytes(nt, tmax, cw) - x_bytes(nt, xb) - group_bytes(gs, tmax)) / (STAGE * grp);
 }
 }  // namespace ring
 
@@ -381,46 +389,49 @@ __device__ __forceinline__ int ring_owner(long long u, long long units, int grid
   return static_cast<int>(((u + 1) * grid + units - 1) / units - 1);
 }
 
-// XB = number of activation-chunk buffers: with few row tiles per CTA a K chunk holds little
-// weight data, so more chunks must be in flight to keep the ring full.
+// XB = number of activation-chunk buffers staged in shared memory by the producer; XB = 0 (one batch
+// tile): the consumer lanes load their activation fragments straight from global memory.
 // GRP = row tiles per TMA box (1 or 2): the copy engine of an SM completes boxes one after the
 // other at a rate that hardly depends on their size, so 32-row boxes double what one SM can pull
 // from DRAM.  tmap_w has GRP*16-row boxes; tmap_w1 has 16-row boxes for the odd last tile of a pass.
 // GS = 0: per-output-channel symmetric int8 weights (sw = one scale per row).
 // GS = 64 or 128: the 8-bit group-wise affine format (lucid/_C/ops/quantized/QuantizedMatmul.cpp:143-207):
 // the packed words ARE the codes as unsigned bytes in K order, `sw` / `bias` are the [N, K / GS] group
-// scales and biases.  A warp's 64-byte slice of a row lies inside one group, so the four MMAs of an item
+// scales and biases.  A 64-byte unit of a row lies inside one group, so the four MMAs of a unit
 // give the group's raw sum, which enters the running total as s * sum(x * c) + b * sum(x) -- the second
-// sum being the all-ones MMA of the chunk.
-template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0>
-__global__ void __launch_bounds__(ring::kThreads, 1)
+// sum being an all-ones MMA over the unit's activations.
+// CW = consumer warps per CTA (16, or 8 with two CTAs per SM): see namespace ring.
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0, int CW = 16>
+__global__ void __launch_bounds__(ring::threads(CW), ring::ctas_per_sm(CW))
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w1,
                       const __grid_constant__ CUtensorMap tmap_x,
                       const XT* __restrict__ xg, int64_t ldx,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
                       const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, const RingPlan plan,
                       int overlap, const WoEpilogue epi) {
-  // XB = 0 (batches of up to 8): the consumer lanes load their activation fragments straight from
-  // global memory (a warp reads 128 contiguous bytes of each of its 8 batch rows; the activations are
-  // L2-resident and the loads of chunk kc + 1 are issued at the top of chunk kc), instead of having the
-  // producer stage every chunk in shared memory.  That takes the activation boxes out of the SM's TMA
-  // queue -- for a long-K matrix they were every second request -- and gives their shared memory to the ring.
+  // XB = 0 (batches of up to 8): a warp reads 128 contiguous bytes per unit of each of its 8 batch rows;
+  // the activations are L2-resident and the loads of chunk kc + 1 are issued at the top of chunk kc.
+  // That takes the activation boxes out of the SM's TMA queue -- for a long-K matrix they were every
+  // second request -- and gives their shared memory to the ring.
   constexpr bool XDIRECT = XB == 0;
   static_assert(!XDIRECT || NT == 1, "direct activation loads keep one batch tile in registers");
   constexpr int XBN = XB > 0 ? XB : 1;  // (divisor of dead code in the direct instantiation)
-  static_assert(GS == 0 || GS == 64 || GS == 128, "group sizes the 64-byte warp slice fits into");
+  static_assert(GS == 0 || GS == 64 || GS == 128, "group sizes a 64-byte unit fits into");
   static_assert(GS == 0 || !SWIGLU, "the fused SwiGLU epilogue is for per-channel weights");
+  static_assert(CW == 16 || CW == 8, "16 consumer warps, or 8 with two CTAs per SM");
   using namespace ring;
-  constexpr int S = stages(NT, TMAX, XB, GRP, GS);
+  constexpr int kConsumerWarps = CW, kConsumerThreads = CW * 32;
+  constexpr int U = KC / (64 * CW);  // 64-byte units of an item row per warp
+  constexpr int S = stages(NT, TMAX, XB, GRP, GS, CW);
   constexpr int GSTAGE = STAGE * GRP;
   static_assert(S >= 3, "ring too shallow");
-  static_assert(GRP == 1 || GRP == 2, "one or two row tiles per box");
-  constexpr int COLS = NT * 8, RP = COLS + 1;
+  static_assert(GRP == 1 || (GRP == 2 && TMAX % 2 == 0), "one or two row tiles per box");
+  constexpr int COLS = NT * 8, RP = red_pitch(NT, CW);
   extern __shared__ uint8_t wo_smem_raw[];
   const uint32_t base = (wo_smem_u32(wo_smem_raw) + 127u) & ~127u;
   const uint32_t x_base = base + S * GSTAGE;
   const uint32_t red_base = x_base + x_bytes(NT, XB);
-  const uint32_t gp_base = red_base + red_bytes(NT, TMAX);
+  const uint32_t gp_base = red_base + red_bytes(NT, TMAX, CW);
   const uint32_t bar_base = gp_base + group_bytes(GS, TMAX);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
@@ -431,7 +442,6 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
 
   __shared__ int s_last_ticket;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t tiles_total = (N + 15) >> 4;
   const int num_kc = static_cast<int>((K + KC - 1) / KC);
   const int nb = static_cast<int>(B);
   long long u_begin = ring_first_unit(blockIdx.x, plan.units, plan.grid);
@@ -536,7 +546,8 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     // only once the preceding grid is complete
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int g = lane >> 2, t = lane & 3;
-    const int koff = warp * 64 + t * 16;  // this lane's byte offset inside an item row
+    const int kwarp = warp * (64 * U);   // first byte of this warp's units inside an item row
+    const int kbase = kwarp + t * 16;    // this lane's 16 bytes of unit 0; unit u lies 64 u bytes further
     int stage = 0, xi = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -544,11 +555,10 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     RingPass ps;
     while (walk.next(ps)) {
       const int pass_tiles = ps.n_tiles;
-      // Dependent mma.sync instructions issue about 150 cycles apart, and a tile's four MMAs per chunk
-      // all add into the same accumulator: with few tiles per pass a warp mostly waits for its own
-      // previous MMA.  So the MMAs of a box are issued tile-inner (neighbouring instructions are
-      // independent) and, where registers allow (at most two tile x batch accumulators), even and odd
-      // K steps add into separate accumulator sets that are summed when the pass is parked.
+      // A tile's MMAs of one unit all add into the same accumulator.  With very few accumulators per warp
+      // (at most two tile x batch combinations) even and odd K steps add into separate sets that are
+      // summed when the pass is parked; otherwise the MMAs of a box are issued tile-inner and the other
+      // warps fill the tensor pipe between dependent instructions.
       constexpr int AS = (GS == 0 && TMAX * NT <= 2) ? 2 : 1;
       float acc[AS][TMAX][NT][4];
 #pragma unroll
@@ -559,56 +569,63 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[a][j][nt][i] = 0.0f;
-      float xlane[NT][2];     // per-channel weights: this lane's share of sum_k x[batch nt*8+g][k], two chains
+      float xlane[NT][2];  // per-channel weights: this lane's share of sum_k x[batch nt*8+g][k], two chains
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) xlane[nt][0] = xlane[nt][1] = 0.0f;
-      float xsum2[2][NT][4];  // group-wise weights: per batch column sums of the chunk's activations (two MMA chains)
-#pragma unroll
-      for (int a = 0; a < 2; ++a)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) xsum2[a][nt][i] = 0.0f;
 
       // Group-wise format: the scales and biases of a chunk -- 16 rows x (KC / GS) groups per tile and
-      // array -- are fetched by all 512 consumer threads together, one element each per tile, so that a
-      // warp's load covers whole 64-byte row pieces, and handed around through shared memory.  (Each warp
-      // fetching its own group's values touches 8 separate sectors per load: the L1 then limits the
-      // kernel to a third of the HBM rate.)  The values of chunk kc + 1 are requested at the top of
-      // iteration kc and parked after it, so their latency hides behind the chunk's work.
+      // array -- are fetched by all consumer threads together so that a warp's load covers whole 64-byte
+      // row pieces, and handed around through shared memory.  (Each warp fetching its own group's values
+      // touches 8 separate sectors per load: the L1 then limits the kernel to a third of the HBM rate.)
+      // The values of chunk kc + 1 are requested at the top of iteration kc and parked after it, so their
+      // latency hides behind the chunk's work.
       constexpr int GPC = GS ? KC / (GS ? GS : 1) : 1;          // groups per K chunk: 16 or 8
       constexpr int GP_ARRAY = TMAX * 16 * GP_PITCH;            // floats per array and buffer
+      constexpr int GFETCH = GS ? 512 / kConsumerThreads : 1;   // (array, row, group) slots per thread and tile
       const int64_t n_groups = GS ? K / (GS ? GS : 1) : 0;
-      float gfetch[GS ? TMAX : 1];
-      auto request_groups = [&](int kc_for) {  // thread -> (array, row, group) of every tile of the pass
-        const int et = threadIdx.x, arr = et >> 8, r = (et >> 4) & 15, c = et & 15;
-        const float* src = arr ? bias : sw;
+      float gfetch[GS ? TMAX : 1][GFETCH];
+      auto request_groups = [&](int kc_for) {  // slot -> (array, row, group) of every tile of the pass
 #pragma unroll
-        for (int j = 0; j < (GS ? TMAX : 1); ++j) {
-          const int64_t row = ((static_cast<int64_t>(ps.tile0) + j) << 4) + r;
-          const int64_t grp_i = static_cast<int64_t>(kc_for) * GPC + c;
-          gfetch[j] = (c < GPC && j < pass_tiles && row < N && grp_i < n_groups) ? __ldg(src + row * n_groups + grp_i) : 0.0f;
+        for (int e = 0; e < GFETCH; ++e) {
+          const int et = threadIdx.x + e * kConsumerThreads, arr = et >> 8, r = (et >> 4) & 15, c = et & 15;
+          const float* src = arr ? bias : sw;
+#pragma unroll
+          for (int j = 0; j < (GS ? TMAX : 1); ++j) {
+            const int64_t row = ((static_cast<int64_t>(ps.tile0) + j) << 4) + r;
+            const int64_t grp_i = static_cast<int64_t>(kc_for) * GPC + c;
+            gfetch[j][e] = (c < GPC && j < pass_tiles && row < N && grp_i < n_groups) ? __ldg(src + row * n_groups + grp_i) : 0.0f;
+          }
         }
       };
       auto park_groups = [&](int buf) {
-        const int et = threadIdx.x, arr = et >> 8, r = (et >> 4) & 15, c = et & 15;
-        if (c < GPC) {
 #pragma unroll
-          for (int j = 0; j < (GS ? TMAX : 1); ++j) gp[(buf * 2 + arr) * GP_ARRAY + (j * 16 + r) * GP_PITCH + c] = gfetch[j];
+        for (int e = 0; e < GFETCH; ++e) {
+          const int et = threadIdx.x + e * kConsumerThreads, arr = et >> 8, r = (et >> 4) & 15, c = et & 15;
+          if (c < GPC) {
+#pragma unroll
+            for (int j = 0; j < (GS ? TMAX : 1); ++j) gp[(buf * 2 + arr) * GP_ARRAY + (j * 16 + r) * GP_PITCH + c] = gfetch[j][e];
+          }
         }
       };
-      // direct activation loads: lane (g, t) takes elements [kc * KC + koff, +16) of batch row g
-      uint32_t xnext[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-      auto load_x = [&](int kc_for, uint32_t (&out)[8]) {
-        const int64_t k = static_cast<int64_t>(kc_for) * KC + koff;
-        if (kc_for >= 0 && k < K && g < nb) {
-          const uint4* px = reinterpret_cast<const uint4*>(xg + static_cast<int64_t>(g) * ldx + k);
-          const uint4 lo = __ldg(px), hi = __ldg(px + 1);
-          out[0] = lo.x; out[1] = lo.y; out[2] = lo.z; out[3] = lo.w;
-          out[4] = hi.x; out[5] = hi.y; out[6] = hi.z; out[7] = hi.w;
-        } else {
+      // direct activation loads: lane (g, t) takes elements [kc * KC + kbase + 64 u, +16) of batch row g
+      uint32_t xnext[U][8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) out[i] = 0u;
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xnext[u][i] = 0u;
+      auto load_x = [&](int kc_for, uint32_t (&out)[U][8]) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t k = static_cast<int64_t>(kc_for) * KC + kbase + 64 * u;
+          if (kc_for >= 0 && k < K && g < nb) {
+            const uint4* px = reinterpret_cast<const uint4*>(xg + static_cast<int64_t>(g) * ldx + k);
+            const uint4 lo = __ldg(px), hi = __ldg(px + 1);
+            out[u][0] = lo.x; out[u][1] = lo.y; out[u][2] = lo.z; out[u][3] = lo.w;
+            out[u][4] = hi.x; out[u][5] = hi.y; out[u][6] = hi.z; out[u][7] = hi.w;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) out[u][i] = 0u;
+          }
         }
       };
       if (XDIRECT) load_x(ps.kc0, xnext);
@@ -622,8 +639,6 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       for (int kc = ps.kc0; kc < ps.kc1 && (GS != 0 || ok); ++kc, ++xi) {
         const int xb = xi % XBN;
         const uint32_t xphase = static_cast<uint32_t>((xi / XBN) & 1);
-        const bool k_ok = static_cast<int64_t>(kc) * KC + koff < K;               // this lane
-        const bool warp_k_ok = static_cast<int64_t>(kc) * KC + warp * 64 < K;     // any lane of the warp
         if (GS != 0 && kc + 1 < ps.kc1) request_groups(kc + 1);
         do {  // (a warp whose wait ran out still takes part in the barriers below)
         if (!ok) break;
@@ -632,70 +647,80 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           ok = false;
           break;
         }
-        // activation fragments of this chunk: 16 consecutive elements per batch row
-        uint32_t xa[NT][8];
+        // activation fragments of this chunk: 16 consecutive elements per unit and batch row.  Elements past
+        // the end of K and batch rows past B are zero (the direct loads are guarded, the staged boxes are
+        // zero-filled by the copy engine), and so are the weights past the end of K: nothing below needs a
+        // guard on k.
+        uint32_t xa[NT][U][8];
         if constexpr (XDIRECT) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) xa[0][i] = xnext[i];
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xa[0][u][i] = xnext[u][i];
           load_x(kc + 1 < ps.kc1 ? kc + 1 : -1, xnext);  // in flight while this chunk is multiplied
         } else {
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            const int b = nt * 8 + g;
-            if (k_ok && b < nb) {
-              const uint32_t xs = x_base + (xb * COLS + b) * X_PITCH + koff * 2;
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const uint32_t xs = x_base + (xb * COLS + nt * 8 + g) * X_PITCH + (kbase + 64 * u) * 2;
               const uint4 lo = wo_lds128(xs), hi = wo_lds128(xs + 16);
-              xa[nt][0] = lo.x; xa[nt][1] = lo.y; xa[nt][2] = lo.z; xa[nt][3] = lo.w;
-              xa[nt][4] = hi.x; xa[nt][5] = hi.y; xa[nt][6] = hi.z; xa[nt][7] = hi.w;
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) xa[nt][i] = 0u;
+              xa[nt][u][0] = lo.x; xa[nt][u][1] = lo.y; xa[nt][u][2] = lo.z; xa[nt][u][3] = lo.w;
+              xa[nt][u][4] = hi.x; xa[nt][u][5] = hi.y; xa[nt][u][6] = hi.z; xa[nt][u][7] = hi.w;
             }
-          }
         }
-        if (GS != 0) {  // sums of x are per group: restart them for this chunk
-#pragma unroll
-          for (int a = 0; a < 2; ++a)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-              for (int i = 0; i < 4; ++i) xsum2[a][nt][i] = 0.0f;
-        }
-        if (warp_k_ok) {
-          if constexpr (GS == 0) {
-            // Per-channel weights: only sum_k x over the whole pass is needed (the 128 of the offset-binary
-            // codes comes out once, when the pass is parked), so every lane adds up its own 16 activations
-            // of the chunk on the FP32 pipe, in two chains, and the lanes are combined at the end of the
-            // pass.  (An all-ones MMA per K step did this before: a third of the MMAs of a two-tile pass,
-            // and mma.sync throughput is what bounds this kernel.)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-              for (int i = 0; i < 8; i += 2) {
-                const float2 p0 = unpack_pair<XT>(xa[nt][i]), p1 = unpack_pair<XT>(xa[nt][i + 1]);
-                xlane[nt][0] += p0.x + p0.y;
-                xlane[nt][1] += p1.x + p1.y;
-              }
-            }
-          }
+        if constexpr (GS == 0) {
+          // Per-channel weights: only sum_k x over the whole pass is needed (the 128 of the offset-binary
+          // codes comes out once, when the pass is parked), so every lane adds up its own activations of the
+          // chunk on the FP32 pipe, in two chains, and the lanes are combined at the end of the pass.
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) RawOperand<XT>::prescale(xa[nt][i]);
-          if constexpr (GS != 0) {
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+              for (int i = 0; i < 8; i += 2) {
+                const float2 p0 = unpack_pair<XT>(xa[nt][u][i]), p1 = unpack_pair<XT>(xa[nt][u][i + 1]);
+                xlane[nt][0] += p0.x + p0.y;
+                xlane[nt][1] += p1.x + p1.y;
+              }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) RawOperand<XT>::prescale(xa[nt][u][i]);
+        // group-wise weights: sum of the activations of every unit (= of a piece of one group), per batch column
+        // 2t and 2t + 1, from an all-ones MMA in two chains; already scaled to sum(x)
+        float xgrp[GS ? U : 1][NT][2];
+        if constexpr (GS != 0) {
+          const float cx = RawOperand<XT>::sum_scale() * 0.0078125f;
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            float s2[2][NT][4];
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s2[a][nt][i] = 0.0f;
 #pragma unroll
             for (int q = 0; q < 4; ++q)
 #pragma unroll
               for (int nt = 0; nt < NT; ++nt)
-                mma_16816<XT>(xsum2[q & 1][nt], RawOperand<XT>::kOnes, RawOperand<XT>::kOnes, RawOperand<XT>::kOnes,
-                              RawOperand<XT>::kOnes, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                mma_16816<XT>(s2[q & 1][nt], RawOperand<XT>::kOnes, RawOperand<XT>::kOnes, RawOperand<XT>::kOnes,
+                              RawOperand<XT>::kOnes, xa[nt][u][2 * q], xa[nt][u][2 * q + 1]);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              xgrp[u][nt][0] = (s2[0][nt][0] + s2[1][nt][0]) * cx;
+              xgrp[u][nt][1] = (s2[0][nt][1] + s2[1][nt][1]) * cx;
+            }
           }
         }
-        // this warp's group inside the chunk; its scale and bias for rows g and g + 8 of tile j come from
-        // the shared-memory copy (pitch 17: the eight rows of a quad column fall into different banks)
-        const int gcol = GS ? (warp * 64) / (GS ? GS : 1) : 0;
+        // group-wise weights: scale and bias of rows g and g + 8 of tile j for the group a unit lies in come
+        // from the shared-memory copy (pitch 17: the eight rows of a quad column fall into different banks)
         const float* gcur = gp + gbuf * 2 * GP_ARRAY;
-        auto read_group = [&](int j, float (&out)[4]) {  // s[row g], s[row g + 8], b[row g], b[row g + 8]
+        auto read_group = [&](int j, int gcol, float (&out)[4]) {  // s[row g], s[row g + 8], b[row g], b[row g + 8]
           const float* sc = gcur + (j * 16 + g) * GP_PITCH + gcol;
           out[0] = sc[0];
           out[1] = sc[8 * GP_PITCH];
@@ -709,64 +734,44 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
               atomicCAS(&g_wo_status, 0, 2);
               ok = false;
             } else {
-              // warp-uniform skip (mma.sync needs the whole warp); lanes past the end of K
-              // inside a live warp contribute zero weights (raw 0 is code 0 in offset binary)
-              if (warp_k_ok) {
-                // weights of one tile of the box: 16 bytes of row g and of row g + 8
-                auto load_tile = [&](int jj, uint32_t (&w)[2][4]) {
-                  uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = make_uint4(0u, 0u, 0u, 0u);
-                  if (k_ok && jb + jj < pass_tiles) {
-                    const uint32_t src = base + stage * GSTAGE + jj * STAGE + g * W_PITCH + koff;
-                    w0 = wo_lds128(src);
-                    w1 = wo_lds128(src + 8 * W_PITCH);
-                  }
-                  w[0][0] = w0.x; w[0][1] = w0.y; w[0][2] = w0.z; w[0][3] = w0.w;
-                  w[1][0] = w1.x; w[1][1] = w1.y; w[1][2] = w1.z; w[1][3] = w1.w;
-                };
-                if constexpr (GS == 0 && AS == 1) {
-                  // many tiles per pass: their accumulator chains already overlap; one tile at a time keeps
-                  // the register count down (interleaving the box measured slower here: 27.4 against 24.9 us)
+              const uint32_t lane_src = base + stage * GSTAGE + g * W_PITCH + kbase;
 #pragma unroll
-                  for (int jj = 0; jj < GRP; ++jj) {
-                    if (jb + jj < pass_tiles) {
-                      uint32_t w[2][4];
-                      load_tile(jj, w);
-#pragma unroll
-                      for (int q = 0; q < 4; ++q) {
-                        const uint32_t u0 = w[0][q] ^ 0x80808080u, u1 = w[1][q] ^ 0x80808080u;
-                        const uint32_t a0 = __byte_perm(u0, 0u, 0x4140u), a2 = __byte_perm(u0, 0u, 0x4342u);
-                        const uint32_t a1 = __byte_perm(u1, 0u, 0x4140u), a3 = __byte_perm(u1, 0u, 0x4342u);
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt)
-                          mma_16816<XT>(acc[0][(jb + jj) % TMAX][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
-                      }
-                    }
-                  }
-                } else {
+              for (int u = 0; u < U; ++u) {
+                // weights of the box's tiles for this unit: 16 bytes of row g and of row g + 8 each; the second
+                // tile of a box may be absent (odd last tile of a pass: warp-uniform skip)
                 uint32_t wr[GRP][2][4];
 #pragma unroll
-                for (int jj = 0; jj < GRP; ++jj) load_tile(jj, wr[jj]);
+                for (int jj = 0; jj < GRP; ++jj) {
+                  uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = make_uint4(0u, 0u, 0u, 0u);
+                  if (GRP == 1 || jb + jj < pass_tiles) {
+                    w0 = wo_lds128(lane_src + jj * STAGE + 64 * u);
+                    w1 = wo_lds128(lane_src + jj * STAGE + 64 * u + 8 * W_PITCH);
+                  }
+                  wr[jj][0][0] = w0.x; wr[jj][0][1] = w0.y; wr[jj][0][2] = w0.z; wr[jj][0][3] = w0.w;
+                  wr[jj][1][0] = w1.x; wr[jj][1][1] = w1.y; wr[jj][1][2] = w1.z; wr[jj][1][3] = w1.w;
+                }
                 if constexpr (GS == 0) {
 #pragma unroll
                   for (int q = 0; q < 4; ++q) {
 #pragma unroll
                     for (int jj = 0; jj < GRP; ++jj) {
-                      if (jb + jj < pass_tiles) {
+                      if (GRP == 1 || jb + jj < pass_tiles) {
                         const uint32_t u0 = wr[jj][0][q] ^ 0x80808080u, u1 = wr[jj][1][q] ^ 0x80808080u;
                         const uint32_t a0 = __byte_perm(u0, 0u, 0x4140u), a2 = __byte_perm(u0, 0u, 0x4342u);
                         const uint32_t a1 = __byte_perm(u1, 0u, 0x4140u), a3 = __byte_perm(u1, 0u, 0x4342u);
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt)
-                          mma_16816<XT>(acc[q % AS][(jb + jj) % TMAX][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                          mma_16816<XT>(acc[q % AS][jb + jj][nt], a0, a1, a2, a3, xa[nt][u][2 * q], xa[nt][u][2 * q + 1]);
                       }
                     }
                   }
                 } else {
+                  const int gcol = (kwarp + 64 * u) / (GS ? GS : 1);
                   float gq[GRP][4];
                   float part[GRP][NT][4];
 #pragma unroll
                   for (int jj = 0; jj < GRP; ++jj) {
-                    read_group((jb + jj) % TMAX, gq[jj]);
+                    read_group(jb + jj, gcol, gq[jj]);
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -776,24 +781,24 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                   for (int q = 0; q < 4; ++q) {  // the codes are unsigned bytes already
 #pragma unroll
                     for (int jj = 0; jj < GRP; ++jj) {
-                      if (jb + jj < pass_tiles) {
+                      if (GRP == 1 || jb + jj < pass_tiles) {
                         const uint32_t a0 = __byte_perm(wr[jj][0][q], 0u, 0x4140u), a2 = __byte_perm(wr[jj][0][q], 0u, 0x4342u);
                         const uint32_t a1 = __byte_perm(wr[jj][1][q], 0u, 0x4140u), a3 = __byte_perm(wr[jj][1][q], 0u, 0x4342u);
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt)
-                          mma_16816<XT>(part[jj][nt], a0, a1, a2, a3, xa[nt][2 * q], xa[nt][2 * q + 1]);
+                          mma_16816<XT>(part[jj][nt], a0, a1, a2, a3, xa[nt][u][2 * q], xa[nt][u][2 * q + 1]);
                       }
                     }
                   }
-                  // raw sums -> values: sum(x c) = part * acc_scale, sum(x) = xsum * (sum_scale / 128)
-                  const float c1 = RawOperand<XT>::acc_scale(), cx = RawOperand<XT>::sum_scale() * 0.0078125f;
+                  // raw sums -> values: sum(x c) = part * acc_scale; sum(x) is xgrp
+                  const float c1 = RawOperand<XT>::acc_scale();
 #pragma unroll
                   for (int jj = 0; jj < GRP; ++jj) {
-                    if (jb + jj < pass_tiles) {
-                      float (&tot)[NT][4] = acc[0][(jb + jj) % TMAX];
+                    if (GRP == 1 || jb + jj < pass_tiles) {
+                      float (&tot)[NT][4] = acc[0][jb + jj];
 #pragma unroll
                       for (int nt = 0; nt < NT; ++nt) {
-                        const float x0 = (xsum2[0][nt][0] + xsum2[1][nt][0]) * cx, x1 = (xsum2[0][nt][1] + xsum2[1][nt][1]) * cx;
+                        const float x0 = xgrp[u][nt][0], x1 = xgrp[u][nt][1];
                         tot[nt][0] = fmaf(part[jj][nt][0] * c1, gq[jj][0], fmaf(x0, gq[jj][2], tot[nt][0]));
                         tot[nt][1] = fmaf(part[jj][nt][1] * c1, gq[jj][0], fmaf(x1, gq[jj][2], tot[nt][1]));
                         tot[nt][2] = fmaf(part[jj][nt][2] * c1, gq[jj][1], fmaf(x0, gq[jj][3], tot[nt][2]));
@@ -801,7 +806,6 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                       }
                     }
                   }
-                }
                 }
               }
               __syncwarp();
@@ -823,9 +827,29 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         }
       }
 
-      // ---- split-K reduction of this pass across the 16 consumer warps ----
+      // ---- split-K reduction of this pass across the consumer warps ----
       // every warp parks its partial sums of all tiles of the pass, one barrier, then the
-      // 512 threads add the 16 partials of each output in a fixed order (deterministic)
+      // consumer threads add the partials of each output in a fixed order (deterministic)
+      //
+      // The scales and biases of the outputs this thread will finish are requested first: their latency
+      // (global memory, about a microsecond under load) passes while the sums are parked.
+      constexpr int OUT_ROWS = SWIGLU ? 8 : 16, HALVES = SWIGLU ? 2 : 1;
+      constexpr int PT = (TMAX * OUT_ROWS * COLS + kConsumerThreads - 1) / kConsumerThreads;
+      float p_scale[PT][HALVES], p_bias[PT][HALVES];
+      if constexpr (GS == 0) {
+#pragma unroll
+        for (int i = 0; i < PT; ++i) {
+          const int o = threadIdx.x + i * kConsumerThreads;
+          const int r = o % OUT_ROWS, j = (o / OUT_ROWS) / COLS;
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h) {
+            const int64_t n = ((static_cast<int64_t>(ps.tile0) + j) << 4) + r + 8 * h;
+            const bool live = j < pass_tiles && n < N;
+            p_scale[i][h] = (live && sw) ? __ldg(sw + n) : 1.0f;
+            p_bias[i][h] = (live && bias) ? __ldg(bias + n) : 0.0f;
+          }
+        }
+      }
       asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");  // previous pass fully summed
       // sum_k x of this warp's K slices for the batch columns 2t and 2t+1 this lane's accumulators belong to:
       // the lane sums (batch row g, slice t) are added over the quad, then fetched from quads 2t and 2t+1
@@ -891,7 +915,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         if (finish) __threadfence();
       }
       if (finish) {
-        // sum over the 16 warps (a pass over all of K) or over the sharers' slots, in CTA order
+        // sum over the consumer warps (a pass over all of K) or over the sharers' slots, in CTA order
         auto total = [&](int j, int r, int bcol) -> float {
           if (!ps.partial) {
             const float* src = red + j * kConsumerWarps * 16 * RP + r * RP + bcol;
@@ -908,34 +932,35 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           }
           return sum;
         };
-        if (SWIGLU) {
-          // rows r and r+8 of a tile are the gate and the up projection of the same hidden unit:
-          // out[b, 8*tile + r] = silu(gate) * up, one rounding to the activation type
-          for (int o = threadIdx.x; o < pass_tiles * 8 * COLS; o += kConsumerThreads) {
-            const int r = o & 7, bcol = (o >> 3) % COLS, j = (o >> 3) / COLS;
-            const int64_t tile = ps.tile0 + j;
-            const int64_t ng = (tile << 4) + r, nu = ng + 8, h = (tile << 3) + r;
-            if (nu < N && bcol < nb) {
-              const float gs = total(j, r, bcol), us = total(j, r + 8, bcol);
-              float gv = gs * (sw ? __ldg(sw + ng) : 1.0f), uv = us * (sw ? __ldg(sw + nu) : 1.0f);
-              if (bias) {
-                gv += __ldg(bias + ng);
-                uv += __ldg(bias + nu);
+#pragma unroll
+        for (int i = 0; i < PT; ++i) {
+          const int o = threadIdx.x + i * kConsumerThreads;
+          if (o < pass_tiles * OUT_ROWS * COLS) {
+            const int r = o % OUT_ROWS, bcol = (o / OUT_ROWS) % COLS, j = (o / OUT_ROWS) / COLS;
+            const int64_t tile = static_cast<int64_t>(ps.tile0) + j;
+            if constexpr (SWIGLU) {
+              // rows r and r+8 of a tile are the gate and the up projection of the same hidden unit:
+              // out[b, 8*tile + r] = silu(gate) * up, one rounding to the activation type
+              const int64_t nu = (tile << 4) + r + 8, h = (tile << 3) + r;
+              if (nu < N && bcol < nb) {
+                float gv = __fmul_rn(total(j, r, bcol), p_scale[i][0]);
+                float uv = __fmul_rn(total(j, r + 8, bcol), p_scale[i][HALVES - 1]);
+                if (bias) {
+                  gv = __fadd_rn(gv, p_bias[i][0]);
+                  uv = __fadd_rn(uv, p_bias[i][HALVES - 1]);
+                }
+                y[static_cast<int64_t>(bcol) * ldy + h] = from_float<XT>(gv / (1.0f + __expf(-gv)) * uv);
               }
-              y[static_cast<int64_t>(bcol) * ldy + h] = from_float<XT>(gv / (1.0f + __expf(-gv)) * uv);
-            }
-          }
-        } else {
-          for (int o = threadIdx.x; o < pass_tiles * 16 * COLS; o += kConsumerThreads) {
-            const int r = o & 15, bcol = (o >> 4) % COLS, j = (o >> 4) / COLS;
-            const int64_t n = ((static_cast<int64_t>(ps.tile0) + j) << 4) + r;
-            if (n < N && bcol < nb) {
-              float v = total(j, r, bcol);
-              if constexpr (GS == 0) {
-                v *= sw ? __ldg(sw + n) : 1.0f;
-                if (bias) v += __ldg(bias + n);
+            } else {
+              const int64_t n = (tile << 4) + r;
+              if (n < N && bcol < nb) {
+                float v = total(j, r, bcol);
+                if constexpr (GS == 0) {
+                  v = __fmul_rn(v, p_scale[i][0]);
+                  if (bias) v = __fadd_rn(v, p_bias[i][0]);
+                }
+                y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(wo_finish(v, epi));
               }
-              y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(wo_finish(v, epi));
             }
           }
         }
@@ -1160,18 +1185,20 @@ struct RingScratch {
 };
 constexpr int64_t kRingSlotBytes = 16 * 32 * 4;  // 16 rows * largest COLS floats
 
-template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0>
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0, int CW = 16>
 static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                    int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
                                    int64_t ldy, bool overlap, const WoEpilogue& epi, const RingScratch& scratch,
                                    cudaStream_t st) {
-  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU, GRP, GS>;
+  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU, GRP, GS, CW>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(LC_ERR_CUDA, "no current CUDA device");
   std::call_once(flags[dev], [&]() {
-    results[dev] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ring::kSmemBudget);
+    results[dev] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ring::smem_budget(CW));
+    if (results[dev] == cudaSuccess && ring::ctas_per_sm(CW) > 1)  // room for both CTAs of an SM
+      results[dev] = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   });
   if (results[dev] != cudaSuccess)
     return fail(LC_ERR_CUDA, "wo_linear_s8: cannot reserve shared memory: %s", cudaGetErrorString(results[dev]));
@@ -1192,7 +1219,7 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
     return rc;
   const int64_t tiles = (N + 15) / 16;
   const int64_t num_kc = (K + ring::KC - 1) / ring::KC;
-  const int64_t sms = sm_count();
+  const int64_t sms = static_cast<int64_t>(sm_count()) * ring::ctas_per_sm(CW);  // CTAs resident at once
   RingPlan plan;
   plan.units_real = tiles * num_kc;
   const int64_t need = sms * 2 * kRingSlotBytes + tiles * 4;
@@ -1212,8 +1239,8 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
-  cfg.blockDim = dim3(ring::kThreads);
-  cfg.dynamicSmemBytes = ring::kSmemBudget;
+  cfg.blockDim = dim3(ring::threads(CW));
+  cfg.dynamicSmemBytes = ring::smem_budget(CW);
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1230,14 +1257,18 @@ template <typename XT, bool SWIGLU = false>
 static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w, int64_t ldw,
                              int64_t N, const float* sw, const float* bias, XT* y, int64_t ldy,
                              bool overlap, const WoEpilogue& epi, const RingScratch& scratch, cudaStream_t st) {
-  // few row tiles per CTA (short, wide matrices): small reduction buffer, more activation chunks in flight
   const int64_t tiles = (N + 15) / 16, sms = sm_count();
+  // Batches of up to 8: two half-size CTAs per SM (8 consumer warps, two 64-byte units per warp and row).
+  // One row tile per CTA (short, wide matrices) streams 16-row boxes through a six-deep ring with even and
+  // odd K steps in separate accumulators; otherwise passes of up to four tiles in 32-row boxes, three deep.
+  if (B <= 8) {
+    const bool single = (tiles + 2 * sms - 1) / (2 * sms) <= 1;
+    return single ? launch_wo_ring_inst<XT, 1, 1, 0, SWIGLU, 1, 0, 8>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st)
+                  : launch_wo_ring_inst<XT, 1, 4, 0, SWIGLU, 2, 0, 8>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
+  }
+  // larger batches: one CTA per SM, activations staged in shared memory; few row tiles per CTA get a small
+  // reduction buffer and more activation chunks in flight
   const bool few = (tiles + sms - 1) / sms <= 2;
-  // two row tiles per TMA box where the ring stays at least three boxes deep (batches up to 8);
-  // measured on the decode MLP: 40.8 us against 41.6 us with one tile per box
-  if (B <= 8)  // XB = 0: activation fragments loaded by the consumer lanes themselves
-    return few ? launch_wo_ring_inst<XT, 1, 2, 0, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st)
-               : launch_wo_ring_inst<XT, 1, 8, 0, SWIGLU, 2>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
   if (B <= 16)
     return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st)
                : launch_wo_ring_inst<XT, 2, 4, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
@@ -1354,7 +1385,7 @@ extern "C" int32_t lc_wo_linear_s8(const void* x, int32_t x_dtype, int64_t batch
 
 extern "C" int64_t lc_wo_linear_workspace_bytes(int64_t N) {
   if (N < 0) return 0;
-  return static_cast<int64_t>(sm_count()) * 2 * kRingSlotBytes + ((N + 15) / 16) * 4;
+  return static_cast<int64_t>(sm_count()) * 2 * 2 * kRingSlotBytes + ((N + 15) / 16) * 4;  // two CTAs per SM at most
 }
 
 extern "C" int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K, int64_t ldx,
