@@ -1259,13 +1259,15 @@ static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
                              int64_t N, const float* sw, const float* bias, XT* y, int64_t ldy,
                              bool overlap, const WoEpilogue& epi, const RingScratch& scratch, cudaStream_t st) {
   const int64_t tiles = (N + 15) / 16, sms = sm_count();
-  // Batches of up to 8: two half-size CTAs per SM (8 consumer warps, two 64-byte units per warp and row).
-  // One row tile per CTA (short, wide matrices) streams 16-row boxes through a six-deep ring with even and
-  // odd K steps in separate accumulators; otherwise passes of up to four tiles in 32-row boxes, three deep.
+  // Batches of up to 8: two half-size CTAs per SM (8 consumer warps, two 64-byte units per warp and row), 16-row
+  // boxes through a six-deep ring.  One row tile per CTA (short, wide matrices) keeps even and odd K steps in
+  // separate accumulators; otherwise passes of up to four tiles.  Measured on the decode MLP (batch 1, us): 34.7
+  // so, 35.9 with 32-row boxes three deep, 38.4 with passes of eight tiles (register spills), 38.9 with one
+  // full-size CTA per SM.
   if (B <= 8) {
     const bool single = (tiles + 2 * sms - 1) / (2 * sms) <= 1;
     return single ? launch_wo_ring_inst<XT, 1, 1, 0, SWIGLU, 1, 0, 8>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st)
-                  : launch_wo_ring_inst<XT, 1, 4, 0, SWIGLU, 2, 0, 8>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
+                  : launch_wo_ring_inst<XT, 1, 4, 0, SWIGLU, 1, 0, 8>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
   }
   // larger batches: one CTA per SM, activations staged in shared memory; few row tiles per CTA get a small
   // reduction buffer and more activation chunks in flight
