@@ -230,16 +230,17 @@ wo_linear_mma_kernel(const XT* __restrict__ x, int64_t B, int64_t K, int64_t ldx
 
 // ---- ring variant for weight matrices that do not fit the caches ------------------------
 // A persistent CTA owns a contiguous share of the matrix (see RingPlan).  A producer thread streams
-// their weights (and, per K chunk, the activations) into shared memory with tiled TMA loads
-// (one 16- or 32-row x 1024-byte box per item; per-row 1-D bulk copies were tried first and are
-// limited by the copy engine's per-request cost), so ~150 KB of loads are in flight per SM
-// without living in registers.  Rows and columns outside the matrix are zero-filled by TMA.  16 consumer warps split every item along K (warp w
-// takes bytes [64w, 64w+64) of each row), widen the int8 weights to the activation type and
-// feed mma.sync m16n8k16 with fp32 accumulation.  Row tiles are processed in passes of at
-// most TMAX tiles so the per-warp partial sums stay in registers; each pass runs over all of
-// K and ends with a split-K reduction across the warps through shared memory.
-// Every mbarrier wait is bounded; a wait that runs out records a code in g_wo_status and the
-// CTA drains its copies and returns.
+// the weights into shared memory with tiled TMA loads (one 16- or 32-row x 1024-byte box per item;
+// per-row 1-D bulk copies were tried first and are limited by the copy engine's per-request cost),
+// so ~190 KB of loads are in flight per SM without living in registers.  Rows and columns outside the
+// matrix are zero-filled by TMA.  The consumer warps split every item along K into 64-byte units (16
+// warps: one unit each; 8 warps, with two CTAs per SM: two units each), hand the int8 weights to
+// mma.sync m16n8k16 as 16-bit patterns (see RawOperand) and accumulate in fp32.  Activations are loaded
+// by the consumer lanes themselves for one batch tile, or staged per K chunk by the producer for more.
+// Row tiles are processed in passes of at most TMAX tiles so the per-warp partial sums stay in
+// registers; each pass runs over all of K and ends with a split-K reduction across the warps through
+// shared memory.  Every mbarrier wait is bounded; a wait that runs out records a code in g_wo_status
+// and the CTA drains its copies and returns.
 namespace ring {
 constexpr int KC = 1024;               // bytes of K per item (and per activation chunk)
 constexpr int W_PITCH = KC;            // dense TMA box rows (the 2-way bank conflict of the two
@@ -316,10 +317,11 @@ __device__ __forceinline__ uint4 wo_lds128(uint32_t addr) {
 // Raw-operand scheme of the ring kernel: the offset-binary byte u = s8 + 128 is fed to the
 // tensor core as the 16-bit pattern 0x00uu, which reads as u * 2^-24 in f16 and u * 2^-133 in
 // bf16 (subnormals joining the first normals linearly), so widening a pair of weights is one
-// byte-permute and no arithmetic.  The sum over k of x * 128 is obtained per K chunk from one
-// extra MMA against an all-ones operand and subtracted, with the power-of-two scale, when the
-// partial sums are parked: y = C1 * sum(x*u') - 128 * C2 * sum(x').  bf16 activations are
-// multiplied by 2^32 first (exact) so that no product falls into the fp32 subnormal range.
+// byte-permute and no arithmetic.  The sum over k of x * 128 (per-lane FP32 sums of the activations for
+// per-channel weights, an all-ones MMA per unit for group-wise ones) is subtracted, with the
+// power-of-two scale, when the partial sums are parked: y = C1 * sum(x*u') - 128 * sum(x).  bf16
+// activations are multiplied by 2^32 first (exact) so that no product falls into the fp32 subnormal
+// range.
 template <typename XT>
 struct RawOperand;
 template <>
@@ -392,9 +394,9 @@ __device__ __forceinline__ int ring_owner(long long u, long long units, int grid
 
 // XB = number of activation-chunk buffers staged in shared memory by the producer; XB = 0 (one batch
 // tile): the consumer lanes load their activation fragments straight from global memory.
-// GRP = row tiles per TMA box (1 or 2): the copy engine of an SM completes boxes one after the
-// other at a rate that hardly depends on their size, so 32-row boxes double what one SM can pull
-// from DRAM.  tmap_w has GRP*16-row boxes; tmap_w1 has 16-row boxes for the odd last tile of a pass.
+// GRP = row tiles per TMA box (1 or 2).  tmap_w has GRP*16-row boxes; tmap_w1 has 16-row boxes for the odd
+// last tile of a pass.  (With one CTA per SM the 32-row box measured 2 % faster; with two CTAs per SM the
+// 16-row box, twice as many stages deep, measured 3 % faster.)
 // GS = 0: per-output-channel symmetric int8 weights (sw = one scale per row).
 // GS = 64 or 128: the 8-bit group-wise affine format (lucid/_C/ops/quantized/QuantizedMatmul.cpp:143-207):
 // the packed words ARE the codes as unsigned bytes in K order, `sw` / `bias` are the [N, K / GS] group
