@@ -334,8 +334,8 @@ int32_t lc_wo_linear_s8_ex(const void* x, int32_t x_dtype, int64_t batch, int64_
  * 1024-byte K chunk) units, every CTA takes an equal contiguous run of them, and a tile whose K range
  * two or more CTAs share is finished by the one that arrives last (each parks its raw sums in its own
  * slot of the scratch; the sums are added in CTA order, so results do not depend on timing).  Without
- * it every CTA takes whole tiles, which leaves SMs idle when the tiles do not divide evenly (a
- * [4096, 14336] matrix occupies 128 of 148 SMs).  Sums over a split K range are added in a different
+ * it every CTA takes whole tiles, which leaves CTA slots idle when the tiles do not divide evenly (a
+ * [4096, 14336] matrix fills 256 of the 296 slots of two CTAs per SM).  Sums over a split K range are added in a different
  * order than in one pass, so the last bits of an output may differ between the two schedules.
  * Measured on B200 the shared tiles' ticketed finish costs more than the idle SMs it removes (decode
  * MLP 53 us against 41 us), so the host layer leaves the scratch out by default.
