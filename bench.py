@@ -562,11 +562,11 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
             lin.bias.normal_(0, 0.01, generator=g)
         qlin = Q.quantize_dynamic(lin)
         x1 = torch.randn(64, 1024, device=dev, generator=g)
-        # a fresh tensor object per call, as in real use (the layer reuses the codes of an input it
-        # has just seen, which a loop over one tensor object would turn into a no-op)
+        # a fresh tensor object per call, as in real use
         ms = time_loop(torch, lambda: qlin(x1.detach()), 200, 20)
         entry = {"us_per_forward": ms * 1e3, "TOPS": 2 * 64 * 4096 * 1024 / ms / 1e9,
-                 "note": "eager: host-bound (two launches per forward, their output allocations and argument checks)"}
+                 "note": "eager: host-bound (one library call per forward that issues the quantize and GEMM launches; "
+                         "the rest is the module's Python, the output allocation and torch's dispatch)"}
         try:  # the same module captured in a CUDA graph (one launch per forward, input copied in)
             import lucid_b200
 
