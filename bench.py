@@ -913,9 +913,18 @@ def run_ours(args) -> int:
         from lucid_b200.nn.quantized.column_parallel import ColumnParallelLinear
 
         cp = ColumnParallelLinear(qlin, N, gather="fused")
-        candidates = ["fused", "copy", "multimem"] if args.gather == "auto" else [args.gather]
+        # "copy/R": the copy-engine exchange with bands of R rows (smaller bands leave a shorter last copy
+        # uncovered by the GEMM, but cost more launches)
+        candidates = (["fused", "copy/4096", "copy/2048", "copy/1024", "multimem"] if args.gather == "auto"
+                      else ["copy/4096" if args.gather == "copy" else args.gather])
+
+        def select(cand: str) -> None:
+            cp.gather, _, rows = cand.partition("/")
+            if rows:
+                cp.band_rows = int(rows)
+
         for cand in candidates:  # a few untimed-by-the-metric steps of each way to exchange; keep the fastest
-            cp.gather = cand
+            select(cand)
             try:
                 for _ in range(2):
                     cp(x)
@@ -935,7 +944,7 @@ def run_ours(args) -> int:
         if not mode_ms:
             raise SystemExit(f"no exchange mode works: {mode_note}")
         mode = min(mode_ms, key=mode_ms.get)
-        cp.gather = mode
+        select(mode)
 
     def step(record: bool = False):
         if world > 1:
@@ -1097,7 +1106,8 @@ def run_ours(args) -> int:
                     "api": "lucid_b200.nn.quantized.streaming.forward_from_host(dynamic.Linear shard, ...), 2048-row chunks, "
                            "one call per rank on its own column shard",
                     "result": y_host_note},
-            "gpu_launches": args.steps * (2 if world == 1 else 4),
+            # N = 1: quantize + GEMM.  N > 1: quantize, barrier, GEMM (one per row band in the copy mode), barrier
+            "gpu_launches": args.steps * (2 if world == 1 else 3 + (-(-M // cp.band_rows) if mode.startswith("copy") else 1)),
             "exchange": None if world == 1 else {
                 "mode": mode, "ms_per_step_by_mode": mode_ms, "mode_note": mode_note,
                 "bytes_in_per_gpu": exchange_bytes,
