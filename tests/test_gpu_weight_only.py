@@ -207,6 +207,54 @@ def test_launch_overlap_is_bit_identical(ops, B):
     assert ops.wo_linear_status() == 0
 
 
+@pytest.mark.parametrize("B", [1, 8, 9, 16, 32])
+@pytest.mark.parametrize("N,K", [(4096, 14336), (28672, 4096)])
+def test_streaming_kernel_cold_and_warm_launches_agree(ops, B, N, K):
+    """A launch that finds nothing in L2 (weights, activations and scales all come from DRAM, boxes land slowly and
+    the warps of a CTA drift apart) gives the bits of a launch that finds everything cached: a ring slot read
+    before its copy has landed, or reused before every warp has left it, shows up here and not in back-to-back
+    launches.  Covers one and several row tiles per CTA, one and two CTAs per SM, passes with an odd last tile."""
+    g = torch.Generator(device="cuda").manual_seed(B + N + K)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+    wq, sw, _ = ops.dynamic_quantize_rows(w, True, -128, 127, True)
+    del w
+    x = torch.randn(B, K, device="cuda", generator=g).to(torch.bfloat16)
+    flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device="cuda")  # three times the L2
+    warm = ops.wo_linear_s8(x, wq, sw)
+    warm = ops.wo_linear_s8(x, wq, sw)
+    ref = (x.double() @ wq.double().T) * sw.double()[None, :]
+    assert_rounded_product(warm, ref.cpu().numpy(), abs_terms(x, wq, sw), K, torch.bfloat16)
+    for i in range(4):
+        flush.fill_(i)
+        torch.cuda.synchronize()
+        cold = ops.wo_linear_s8(x, wq, sw)
+        assert torch.equal(cold.view(torch.int16), warm.view(torch.int16)), f"cold launch {i} differs from the warm one"
+    assert ops.wo_linear_status() == 0
+
+
+@pytest.mark.parametrize("B", [1, 16])
+def test_fused_and_group_streaming_cold_and_warm_launches_agree(ops, B):
+    """The same for the fused gate / up / SwiGLU epilogue and for the group-wise 8-bit format."""
+    g = torch.Generator(device="cuda").manual_seed(B)
+    F, K = 14336, 4096
+    wg = torch.randint(-128, 128, (F, K), device="cuda", dtype=torch.int8, generator=g)
+    wu = torch.randint(-128, 128, (F, K), device="cuda", dtype=torch.int8, generator=g)
+    wgu = ops.interleave_gate_up(wg, wu)
+    sgu = torch.rand(2 * F, device="cuda", generator=g) * 1e-3 + 1e-4
+    packed, scales, biases = ops.group_quantize(torch.randn(F, K, device="cuda", generator=g) * 0.02, 64, 8)
+    x = torch.randn(B, K, device="cuda", generator=g).to(torch.bfloat16)
+    flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    calls = (lambda: ops.wo_swiglu_s8(x, wgu, sgu), lambda: ops.group_matmul(x, packed, scales, biases, 64, 8))
+    for call in calls:
+        call()
+        warm = call()
+        for i in range(3):
+            flush.fill_(i)
+            torch.cuda.synchronize()
+            assert torch.equal(call().view(torch.int16), warm.view(torch.int16)), f"cold launch {i} differs from the warm one"
+    assert ops.wo_linear_status() == 0
+
+
 @pytest.mark.parametrize("B,N,K", [(1, 4096, 14336), (4, 14336, 4096), (16, 512, 65536), (32, 6000, 3000 * 16 // 16 * 16)])
 def test_streaming_kernel_is_deterministic(ops, B, N, K):
     """The split-K sums of the streaming kernel are added in a fixed order: 25 back-to-back
