@@ -923,7 +923,12 @@ def run_ours(args) -> int:
             if rows:
                 cp.band_rows = int(rows)
 
+        if args.gather == "auto":
+            candidates.append("nccl")  # timed only if none of the symmetric-memory modes works on this box
+
         for cand in candidates:  # a few untimed-by-the-metric steps of each way to exchange; keep the fastest
+            if cand == "nccl" and args.gather == "auto" and mode_ms:
+                continue
             select(cand)
             try:
                 for _ in range(2):
@@ -1054,8 +1059,9 @@ def run_ours(args) -> int:
                 companions[k] = float(col.min())
 
     # ---- end to end through the module API with host buffers --------------------------------------
-    # Every rank streams ITS column shard: x chunks host -> device, the shard's Linear, result chunks
-    # device -> its block of the host result; P PCIe links work in parallel and nothing crosses NVLink.
+    # Every rank streams ITS column shard: x chunks host -> device (each rank uploads 1/P of a chunk's rows,
+    # the ranks all-gather the chunk over NVLink: the host delivers x once, not P times), the shard's Linear,
+    # result chunks device -> its block of the host result; P PCIe links work in parallel.
     from lucid_b200.nn.quantized.streaming import forward_from_host
 
     x_host = x.cpu().pin_memory()
@@ -1063,7 +1069,7 @@ def run_ours(args) -> int:
         if world == 1 else shared_pinned_result(torch, world, rank, M, n_local)
 
     def e2e_step():
-        forward_from_host(qlin, x_host, y_host, chunk_rows=2048)
+        forward_from_host(qlin, x_host, y_host, chunk_rows=2048, group=dist.group.WORLD if world > 1 else None)
 
     e2e_steps = max(3, min(args.steps, 10))
     for _ in range(2):
@@ -1101,10 +1107,11 @@ def run_ours(args) -> int:
                                         "twice the bf16 rate; no int8 figure is measured by the driver",
                          "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS},
             "e2e": {"value": 2.0 * M * N * K / e2e_ms_per_step / 1e9, "unit": "TOPS",
-                    "h2d_bytes_per_step": M * K * 4 * world, "d2h_bytes_per_step": M * N * 4,
+                    "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4,
                     "ms_per_step": e2e_ms_per_step,
                     "api": "lucid_b200.nn.quantized.streaming.forward_from_host(dynamic.Linear shard, ...), 2048-row chunks, "
-                           "one call per rank on its own column shard",
+                           "one call per rank on its own column shard"
+                           + ("" if world == 1 else "; a rank uploads 1/P of each chunk, the chunk is all-gathered over NVLink"),
                     "result": y_host_note},
             # N = 1: quantize + GEMM.  N > 1: quantize, barrier, GEMM (one per row band in the copy mode), barrier
             "gpu_launches": args.steps * (2 if world == 1 else 3 + (-(-M // cp.band_rows) if mode.startswith("copy") else 1)),

@@ -92,6 +92,21 @@ def _two_gpu_worker(rank: int, world: int, port: int, out_dir: str) -> None:
             if mode != "multimem" or "multicast" not in str(e):
                 raise
     assert "fused" in tried and "copy" in tried
+    # host-to-host streaming of this rank's column shard: uploading 1/P of every chunk and all-gathering it
+    # gives the bits of uploading the whole chunk (700 rows: chunks of 256, 256 and an odd 188 -> whole upload)
+    from lucid_b200.nn.quantized.streaming import forward_from_host
+
+    xh = torch.cat([xs[0], xs[1][:68]]).pin_memory()  # 768 rows
+    shard = cp.shard
+    outs = []
+    for grp, nrows in ((None, 768), (dist.group.WORLD, 768), (dist.group.WORLD, 700)):
+        out = torch.empty((nrows, shard.out_features), dtype=torch.float32).pin_memory()
+        forward_from_host(shard, xh[:nrows], out, chunk_rows=256, device=dev, group=grp)
+        torch.cuda.synchronize(dev)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0][:700], outs[2]), f"rank {rank}: sharded upload differs"
+    per = shard.out_features
+    assert torch.equal(outs[0][:700].to(dev), want[0][:, rank * per:(rank + 1) * per]), f"rank {rank}: shard result differs"
     with open(os.path.join(out_dir, f"ok_{rank}"), "w") as f:
         f.write(",".join(tried))
     dist.barrier()
