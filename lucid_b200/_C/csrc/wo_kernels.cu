@@ -364,22 +364,26 @@ struct RingPass {
   bool partial;
 };
 
+// (unit indices fit 32 bits -- the launcher refuses matrices of 2^31 units, 32 TB, and more -- and 32-bit
+// divisions keep the walk off the critical path between a CTA's start and its first copy)
 template <int TMAX>
 struct RingWalk {
-  long long u, u_end;
-  int num_kc;
+  unsigned u, u_end;
+  unsigned num_kc;
+  __device__ RingWalk(long long begin, long long end, int chunks)
+      : u(static_cast<unsigned>(begin)), u_end(static_cast<unsigned>(end)), num_kc(static_cast<unsigned>(chunks)) {}
   __device__ bool next(RingPass& p) {
     if (u >= u_end) return false;
-    const long long tile = u / num_kc, left = u_end - u;
-    const int kc0 = static_cast<int>(u % num_kc);
+    const unsigned tile = u / num_kc, left = u_end - u;
+    const unsigned kc0 = u - tile * num_kc;
     if (kc0 != 0 || left < num_kc) {
-      const int kc1 = left < num_kc - kc0 ? kc0 + static_cast<int>(left) : num_kc;
-      p = {static_cast<int>(tile), 1, kc0, kc1, true};
+      const unsigned kc1 = left < num_kc - kc0 ? kc0 + left : num_kc;
+      p = {static_cast<int>(tile), 1, static_cast<int>(kc0), static_cast<int>(kc1), true};
       u += kc1 - kc0;
     } else {
-      long long nt = left / num_kc;
+      unsigned nt = left / num_kc;
       nt = nt < TMAX ? nt : TMAX;
-      p = {static_cast<int>(tile), static_cast<int>(nt), 0, num_kc, false};
+      p = {static_cast<int>(tile), static_cast<int>(nt), 0, static_cast<int>(num_kc), false};
       u += nt * num_kc;
     }
     return true;
@@ -445,6 +449,12 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
 
   __shared__ int s_last_ticket;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the copy engine's first use of a tensor map costs a fetch of its 128 bytes: start it before anything else
+  if (warp == CW && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
+    if (GRP > 1) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w1)) : "memory");
+    if (XB > 0) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+  }
   const int num_kc = static_cast<int>((K + KC - 1) / KC);
   const int nb = static_cast<int>(B);
   long long u_begin = ring_first_unit(blockIdx.x, plan.units, plan.grid);
@@ -483,7 +493,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       // activation chunk must not queue behind a ring-full of weights).
       int prefilled = 0;
       if (overlap) {
-        RingWalk<TMAX> first = {u_begin, u_end, num_kc};
+        RingWalk<TMAX> first(u_begin, u_end, num_kc);
         RingPass ps;
         if (first.next(ps)) {
           for (int kc = ps.kc0; kc < ps.kc1 && prefilled < S; ++kc)
@@ -498,7 +508,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       }
       asm volatile("griddepcontrol.wait;" ::: "memory");
       int issued = 0;  // weight items walked so far (the first `prefilled` are already in flight)
-      RingWalk<TMAX> walk = {u_begin, u_end, num_kc};
+      RingWalk<TMAX> walk(u_begin, u_end, num_kc);
       RingPass ps;
       while (ok && walk.next(ps)) {
         for (int kc = ps.kc0; kc < ps.kc1 && ok; ++kc, ++xi) {
@@ -554,7 +564,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     int stage = 0, xi = 0;
     uint32_t phase = 0;
     bool ok = true;
-    RingWalk<TMAX> walk = {u_begin, u_end, num_kc};
+    RingWalk<TMAX> walk(u_begin, u_end, num_kc);
     RingPass ps;
     while (walk.next(ps)) {
       const int pass_tiles = ps.n_tiles;
@@ -1225,6 +1235,8 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   const int64_t sms = static_cast<int64_t>(sm_count()) * ring::ctas_per_sm(CW);  // CTAs resident at once
   RingPlan plan;
   plan.units_real = tiles * num_kc;
+  if (plan.units_real >= (int64_t{1} << 31))
+    return fail(LC_ERR_UNSUPPORTED, "wo_linear_s8 (ring): %lld (tile, K chunk) units exceed 2^31", (long long)plan.units_real);
   const int64_t need = sms * 2 * kRingSlotBytes + tiles * 4;
   if (scratch.ptr && scratch.bytes >= need && aligned(scratch.ptr, 16)) {
     // every CTA the same number of (tile, K chunk) units, tiles shared along K where ranges meet
