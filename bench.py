@@ -964,21 +964,54 @@ def run_ours(args) -> int:
             gemm_ms.append((a, b))
         return y
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    sync_all()
-    e0, e1 = _events(torch)
-    with ClockSampler(local) as clocks:
+    def timed_region(warmup: int):
+        """`warmup` untimed steps, then exactly args.steps steps between two events; max over ranks."""
+        gemm_ms.clear()
+        for _ in range(warmup):
+            step()
         sync_all()
-        e0.record()
-        for _ in range(args.steps):
-            result = step(record=True)
-        e1.record()
-        sync_all()
-    total_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(total_ms.item()) / args.steps
+        e0, e1 = _events(torch)
+        with ClockSampler(local) as clk:
+            sync_all()
+            e0.record()
+            res = None
+            for _ in range(args.steps):
+                res = None  # one output alive at a time: the allocator hands the same block back, no cudaMalloc in here
+                res = step(record=True)
+            e1.record()
+            sync_all()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        per_step = [a.elapsed_time(b) for a, b in gemm_ms]
+        return float(t.item()) / args.steps, clk, res, per_step
+
+    def disturbed(clk, per_step) -> str:
+        """Why this measurement must be taken again (the rules of the timing contract), or ''."""
+        c = clk.summary()
+        bad = [r for r in c["reasons"] if r != "sw_power_cap"]
+        why = ""
+        if bad:
+            why = "throttle reasons " + ",".join(bad)
+        elif c["sm_mhz"] and c["sm_max_mhz"] and c["sm_mhz"] < 0.9 * c["sm_max_mhz"] and not c["reasons"]:
+            why = f"SM clock {c['sm_mhz']} MHz below maximum with no reason active"
+        elif per_step and max(per_step) > 1.25 * min(per_step):
+            why = (f"GEMM launches of one timed region between {min(per_step):.3f} and {max(per_step):.3f} ms "
+                   "(a transient on the box: clocks, power or a neighbour)")
+        flag = torch.tensor([1.0 if why else 0.0], device=dev)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        return why or ("another rank saw a disturbance" if flag.item() else "")
+
+    ms_per_step, clocks, result, kernel_times = timed_region(max(args.warmup, 3))
+    remeasured = None
+    why = disturbed(clocks, kernel_times)
+    if why:  # rejected and measured once more, as the timing rules say; both figures are reported
+        first = ms_per_step
+        del result
+        time.sleep(2.0)
+        ms_per_step, clocks, result, kernel_times = timed_region(max(args.warmup, 3))
+        remeasured = {"reason": why, "first_ms_per_step": first, "still_disturbed": disturbed(clocks, kernel_times) or None}
     value = 2.0 * M * N * K / ms_per_step / 1e9
     if cp is not None:
         cp.check()
@@ -1103,6 +1136,7 @@ def run_ours(args) -> int:
                          "frac": achieved / int8_peak,
                          "traffic": gemm_dram_traffic(2.0 * M * n_local * K),
                          "kernel": "qlinear_i8_pair_kernel", "kernel_ms": gemm_avg_ms,
+                         "kernel_ms_min_max": [min(kernel_times), max(kernel_times)] if kernel_times else None,
                          "peak_source": f"2 x bf16_tflops ({peaks['source']}, burst): tcgen05 issues dense int8 at "
                                         "twice the bf16 rate; no int8 figure is measured by the driver",
                          "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS},
@@ -1129,6 +1163,8 @@ def run_ours(args) -> int:
                         "not by the tensor cores"},
             "clocks": clocks.summary(),
         }
+        if remeasured is not None:
+            line["remeasured"] = remeasured
         if sustained is not None:
             line["sustained"] = sustained
         if companions is not None:
