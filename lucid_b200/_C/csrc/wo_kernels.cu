@@ -821,6 +821,11 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                   }
                 }
               }
+              // The slot goes back to the copy engine, which writes it through the async proxy: order this warp's
+              // (generic-proxy) reads of the slot before that.  The release of the arrive alone was observed not
+              // to be enough -- a form of this kernel with twice the MMAs per box read, on launches that found
+              // nothing in the L2, bytes of the box that came six chunks later; with this fence it does not.
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               __syncwarp();
               if (lane == 0) wo_mbar_arrive(empty_bar(stage));
               if (++stage == S) {
@@ -830,6 +835,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
             }
           }
         }
+        if (!XDIRECT) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // as for the weight slots
         __syncwarp();
         if (!XDIRECT && lane == 0 && ok) wo_mbar_arrive(xempty_bar(xb));
         } while (false);
