@@ -1308,7 +1308,11 @@ static int32_t launch_wo_tma(const XT* x, int64_t B, int64_t K, int64_t ldx, con
   if (B <= 16)  // many tiles per CTA: the two-CTA form with two batch tiles (activation fragments loaded where needed)
     return few ? launch_wo_ring_inst<XT, 2, 2, 3, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st)
                : launch_wo_ring_inst<XT, 2, 4, 0, SWIGLU, 1, 0, 8>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
-  return launch_wo_ring_inst<XT, 4, 1, 2, SWIGLU, 1>(x, B, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st);
+  // 17..32 rows: two passes over the weights with at most 16 rows each (measured on the decode MLP at batch 32:
+  // 97 us against 128 us for one pass with four batch tiles, whose passes hold a single row tile).  The
+  // second launch reads nothing the first one writes, so it may always prefetch its weights under it.
+  if (int32_t rc = launch_wo_tma<XT, SWIGLU>(x, 16, K, ldx, w, ldw, N, sw, bias, y, ldy, overlap, epi, scratch, st)) return rc;
+  return launch_wo_tma<XT, SWIGLU>(x + 16 * ldx, B - 16, K, ldx, w, ldw, N, sw, bias, y + 16 * ldy, ldy, true, epi, scratch, st);
 }
 
 template <typename XT>
@@ -1390,8 +1394,12 @@ static int32_t launch_group_ring(const XT* x, int64_t B, int64_t K, const uint8_
     else if (bc <= 16)
       rc = few ? launch_wo_ring_inst<XT, 2, 2, 3, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
                : launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
-    else
-      rc = launch_wo_ring_inst<XT, 4, 1, 2, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+    else {  // two passes with at most 16 rows each, as for per-channel weights
+      rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS>(xb, 16, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+      if (!rc)
+        rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS>(xb + 16 * K, bc - 16, K, K, w, K, N, scales, biases, yb + 16 * N, N,
+                                                            true, none, scratch, st);
+    }
     if (rc) return rc;
   }
   return LC_OK;
