@@ -232,6 +232,23 @@ def test_streaming_kernel_cold_and_warm_launches_agree(ops, B, N, K):
     assert ops.wo_linear_status() == 0
 
 
+@pytest.mark.parametrize("B", [17, 24, 32])
+def test_rows_17_to_32_equal_two_passes_of_16(ops, B):
+    """17..32 rows run as two passes over the weights of at most 16 rows each: the result is, bit for bit, what
+    the two row blocks give when the caller passes them separately, for the plain and the fused SwiGLU form."""
+    g = torch.Generator(device="cuda").manual_seed(B)
+    N, K = 8192, 4096
+    wq = torch.randint(-128, 128, (N, K), device="cuda", dtype=torch.int8, generator=g)
+    sw = torch.rand(N, device="cuda", generator=g) * 0.01 + 0.001
+    bias = torch.randn(N, device="cuda", generator=g) * 0.1
+    x = torch.randn(B, K, device="cuda", generator=g).to(torch.bfloat16)
+    for call in (lambda v: ops.wo_linear_s8(v, wq, sw, bias), lambda v: ops.wo_swiglu_s8(v, wq, sw)):
+        whole = call(x)
+        parts = torch.cat([call(x[:16].contiguous()), call(x[16:].contiguous())])
+        assert torch.equal(whole.view(torch.int16), parts.view(torch.int16))
+    assert ops.wo_linear_status() == 0
+
+
 @pytest.mark.parametrize("B", [1, 16])
 def test_fused_and_group_streaming_cold_and_warm_launches_agree(ops, B):
     """The same for the fused gate / up / SwiGLU epilogue and for the group-wise 8-bit format."""
