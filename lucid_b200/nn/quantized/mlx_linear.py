@@ -9,7 +9,7 @@ import torch
 from torch import nn
 
 from lucid_b200 import _backend
-from lucid_b200.quantization._qgemm import quantize, quantized_matmul
+from lucid_b200.quantization._qgemm import quantize, quantized_matmul, wide_group_product
 
 
 class QuantizedLinearMLX(nn.Module):
@@ -28,9 +28,20 @@ class QuantizedLinearMLX(nn.Module):
             self.register_buffer("bias", torch.zeros(out_features))
         else:
             self.bias = None
+        self._wide_cache = {}
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         xd = _backend.on_cuda(x)
+        rows = xd.numel() // max(self.in_features, 1)
+        if rows > 32 and not (xd.requires_grad and torch.is_grad_enabled()):
+            # compute-bound batches: the weight decoded once per module, bias and ReLU in the GEMM's epilogue
+            y = wide_group_product(xd.reshape(-1, self.in_features), self.packed_weight, self.scales, self.biases,
+                                   self.group_size, self.bits, cache=self._wide_cache,
+                                   bias=None if self.bias is None else _backend.on_cuda(self.bias), relu=self.relu)
+            y = y.reshape(*xd.shape[:-1], self.out_features)
+            if y.dtype != x.dtype:
+                y = y.to(x.dtype)
+            return y if x.is_cuda else y.to(x.device)
         y = quantized_matmul(xd, self.packed_weight, self.scales, self.biases, transpose=True,
                              group_size=self.group_size, bits=self.bits)
         if self.bias is not None:

@@ -34,6 +34,33 @@ def dequantize(wq, scales, biases, group_size: int = 64, bits: int = 8):
     return _backend.ops().group_dequantize(_backend.on_cuda(wq), _backend.on_cuda(scales), _backend.on_cuda(biases), group_size, bits)
 
 
+def wide_group_product(x2, wq, scales, biases, group_size: int, bits: int, cache=None, bias=None, relu: bool = False):
+    """``relu(x2 @ w_hat.T + bias)`` for more rows than the streaming kernel takes.  The reference
+    hands every shape to one engine call (``lucid/quantization/_qgemm.py:311-314``) and names the
+    decode-then-multiply form as its exact counterpart (``_qgemm.py:289-291``); at these sizes the
+    product, not the weight's bytes, is what costs, so the weight is decoded to the activation type
+    and bf16 / f16 activations then run on the
+    library's own tensor-core kernel (``lc_wo_gemm_16``, fp32 accumulation, bias and ReLU in its
+    epilogue); fp32 activations take torch's fp32 product.  ``cache`` (a dict owned by the caller)
+    keeps the decoded weight per (type, storages, in-place versions), so that a module decodes once."""
+    ops = _backend.ops()
+    key = (x2.dtype,) + tuple((t.data_ptr(), t._version) for t in (wq, scales, biases))
+    if cache is not None and cache.get("key") == key:
+        dense = cache["w"]
+    else:
+        dense = ops.group_dequantize(wq, scales, biases, group_size, bits).to(x2.dtype)
+        if cache is not None:
+            cache["key"], cache["w"] = key, dense
+    if x2.dtype in (torch.bfloat16, torch.float16) and x2.shape[1] % 8 == 0:
+        if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+            x2 = x2.contiguous()
+        return ops.wo_gemm_16(x2, 1, dense, bias=bias, relu=relu, out_dtype=x2.dtype)
+    y = x2 @ dense.T
+    if bias is not None:
+        y = y + bias.to(y.dtype)
+    return torch.relu(y) if relu else y
+
+
 def _forward(xd, wq, scales, biases, transpose: bool, group_size: int, bits: int):
     lead = xd.shape[:-1]
     x2 = xd.reshape(-1, xd.shape[-1])
@@ -42,10 +69,8 @@ def _forward(xd, wq, scales, biases, transpose: bool, group_size: int, bits: int
         return (x2 @ dense).reshape(*lead, dense.shape[1])
     if x2.shape[0] <= 32:
         y = _backend.ops().group_matmul(x2, wq, scales, biases, group_size, bits)
-    else:
-        # compute-bound shapes: decode the weight once, then a dense product
-        dense = _backend.ops().group_dequantize(wq, scales, biases, group_size, bits).to(xd.dtype)
-        y = x2 @ dense.T
+    else:  # compute-bound shapes
+        y = wide_group_product(x2, wq, scales, biases, group_size, bits)
     return y.reshape(*lead, wq.shape[0])
 
 

@@ -388,3 +388,44 @@ def test_group_matmul_accepts_a_view_that_starts_off_a_16_byte_boundary(ops):
     assert x.data_ptr() % 16 != 0 and x.is_contiguous()
     y = ops.group_matmul(x, p, s, b, 64, 8)
     assert torch.equal(y, ops.group_matmul(x.clone(), p, s, b, 64, 8))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("bits,gs", [(8, 64), (4, 32)])
+@pytest.mark.parametrize("M,N,K", [(33, 256, 512), (200, 1000, 1024)])
+def test_group_wide_product_matches_the_decoded_weight(ops, dtype, bits, gs, M, N, K):
+    """More than 32 rows: ``x @ decode(W)^T`` with the weight decoded to the activation type; 16-bit
+    activations run on the library's tensor-core kernel (fp32 accumulation, one rounding of the result),
+    so the output is the fp64 product of the same operands within that rounding; the module adds bias
+    and ReLU in the same kernel and decodes once."""
+    from lucid_b200.nn.quantized.mlx_linear import QuantizedLinearMLX
+    from lucid_b200.quantization import _qgemm
+
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + bits)
+    w = torch.randn(N, K, device="cuda", generator=g)
+    p, s, b = ops.group_quantize(w, gs, bits)
+    dense = ops.group_dequantize(p, s, b, gs, bits).to(dtype)
+    x = torch.randn(M, K, device="cuda", generator=g).to(dtype)
+    ref = x.double() @ dense.double().T
+    eps = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -24}[dtype]
+    # fp32 accumulation of K terms plus one rounding to the output type
+    bound = (x.double().abs() @ dense.double().abs().T) * (K * 2.0 ** -24) + ref.abs() * eps + 1e-30
+    y = _qgemm.quantized_matmul(x, p, s, b, transpose=True, group_size=gs, bits=bits)
+    assert y.dtype == dtype and y.shape == (M, N)
+    assert bool(((y.double() - ref).abs() <= bound).all())
+
+    lin = torch.nn.Linear(K, N).cuda()
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    m = QuantizedLinearMLX.from_float(lin, bits=bits, group_size=gs, relu=True)
+    refm = torch.relu(ref + lin.bias.double())
+    boundm = bound + refm.abs() * eps + lin.bias.double().abs() * 2.0 ** -23
+    y1 = m(x)
+    assert bool(((y1.double() - refm).abs() <= boundm).all())
+    held = m._wide_cache["w"]
+    assert torch.equal(m(x), y1) and m._wide_cache["w"] is held  # second forward: no second decode
+    m.scales.mul_(2.0)  # an in-place change of a buffer invalidates the decoded copy
+    y2 = m(x)
+    assert m._wide_cache["w"] is not held
+    ref2 = torch.relu(x.double() @ ops.group_dequantize(p, m.scales, b, gs, bits).to(dtype).double().T + lin.bias.double())
+    assert float((y2.double() - ref2).abs().max()) <= float(ref2.abs().max()) * 4 * eps + 1e-3
