@@ -100,6 +100,26 @@ for _name, (_res, _args) in SIGNATURES.items():
     _fn.argtypes = _args
 
 
+# The four entry points a decode-time forward calls once per layer, behind a CPython module that spares
+# ctypes' marshalling (about 3 us per call with twenty arguments); ctypes serves them when the module has
+# not been built.  Same arguments, same status code.
+FAST_ENTRY_POINTS = ("lc_dynamic_linear_f32", "lc_group_matmul_ex", "lc_wo_linear_s8_ex", "lc_wo_swiglu_s8_ex")
+try:
+    from . import _fastcall as fast
+except ImportError:
+    fast = None
+else:
+    for _name in FAST_ENTRY_POINTS:
+        fast.bind(_name, C.cast(getattr(lib, _name), C.c_void_p).value)
+
+
+def entry(name: str):
+    """The callable for ``lc_<name>``: the fast binding when there is one, else the ctypes function."""
+    if fast is not None and "lc_" + name in FAST_ENTRY_POINTS:
+        return getattr(fast, name)
+    return getattr(lib, "lc_" + name)
+
+
 def last_error() -> str:
     buf = C.create_string_buffer(512)
     lib.lc_last_error(buf, 512)

@@ -1,4 +1,5 @@
-"""Builds liblucid_cuda.so (sm_100a) next to this file with nvcc.
+"""Builds liblucid_cuda.so (sm_100a) next to this file with nvcc, and the small CPython module
+``_fastcall`` (gcc) that binds a few of its entry points without ctypes' per-call cost.
 
     python -m lucid_b200._C.build [--force]
 
@@ -11,6 +12,7 @@ import os
 import shutil
 import subprocess
 import sys
+import sysconfig
 from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -19,6 +21,8 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(HERE, "liblucid_cuda.so")
+FASTCALL_SRC = os.path.join(CSRC, "fastcall.c")
+FASTCALL_PATH = os.path.join(HERE, "_fastcall" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 
 SOURCES = ["api.cu", "quant_kernels.cu", "hist_kernels.cu", "embed_kernels.cu", "qlinear_tcgen05.cu", "wo_kernels.cu",
            "wo_prep_kernels.cu", "peer_kernels.cu"]
@@ -64,12 +68,18 @@ def build(force: bool = False, verbose: bool = False) -> str:
             print(" ".join(cmd), flush=True)
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
-            raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+            raise RuntimeError(f"compiler failed:\n{' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
 
     with ThreadPoolExecutor(max_workers=4) as pool:
         list(pool.map(run, jobs))
     if force or jobs or not _newer(LIB_PATH, objs):
         run([nvcc, "-shared", "-o", LIB_PATH, *objs, "-gencode", "arch=compute_100a,code=sm_100a"])
+    if force or not _newer(FASTCALL_PATH, [FASTCALL_SRC, os.path.join(INCLUDE, "lucid_cuda.h")]):
+        cc = shutil.which("gcc") or shutil.which("cc")
+        if cc is None:
+            raise RuntimeError("gcc not found; the _fastcall module cannot be built")
+        run([cc, "-O2", "-shared", "-fPIC", "-Wall", "-I", sysconfig.get_paths()["include"], "-I", INCLUDE,
+             FASTCALL_SRC, "-o", FASTCALL_PATH])
     return LIB_PATH
 
 

@@ -12,7 +12,12 @@ import math
 import torch
 
 from ._loader import (LC_BF16, LC_F16, LC_F32, LC_QLINEAR_MULTICAST_OUT, LC_QLINEAR_WAIT_TEST, LC_S8, LC_S16, LC_S32, LC_U8, LucidCudaError, check,
-                      lib)
+                      entry, lib)
+
+_dynamic_linear_f32 = entry("dynamic_linear_f32")
+_group_matmul_ex = entry("group_matmul_ex")
+_wo_linear_s8_ex = entry("wo_linear_s8_ex")
+_wo_swiglu_s8_ex = entry("wo_swiglu_s8_ex")
 
 _DTYPE = {
     torch.float32: LC_F32,
@@ -433,7 +438,7 @@ def dynamic_linear(x2d: torch.Tensor, act_scheme: str, qmin: int, qmax: int, sig
     m, k = x2d.shape
     n = wq.shape[0]
     out = torch.empty((m, n), dtype=out_dtype, device=dev)
-    check(lib.lc_dynamic_linear_f32(x2d.data_ptr(), x2d.stride(0), m, k, _ACT_SCHEME_ID[act_scheme], int(qmin), int(qmax),
+    check(_dynamic_linear_f32(x2d.data_ptr(), x2d.stride(0), m, k, _ACT_SCHEME_ID[act_scheme], int(qmin), int(qmax),
                                     1 if signed else 0, float(eps), wq.data_ptr(), wq.stride(0), n, _ptr(sw), _ptr(bias),
                                     _ptr(wsum), out.data_ptr(), _lc_dtype(out_dtype), n, workspace.data_ptr(),
                                     workspace.numel(), 1 if fresh else 0, _ptr(status),
@@ -676,7 +681,7 @@ def wo_linear_s8(x2d, wq, sw, bias=None, overlap_previous: bool = False, relu: b
     oz_c = None if out_zp is None else _f32c(out_zp)
     with _on(dev):
         ws = wo_workspace(dev, N) if balanced else None
-        check(lib.lc_wo_linear_s8_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq.data_ptr(),
+        check(_wo_linear_s8_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq.data_ptr(),
                                      wq.stride(0), N, _ptr(sw_c), _ptr(bias_c), 1 if relu else 0, _ptr(os_c),
                                      _ptr(oz_c), int(quant_min), int(quant_max), y.data_ptr(), N,
                                      1 if overlap_previous else 0, _ptr(ws), 0 if ws is None else ws.numel(),
@@ -709,7 +714,7 @@ def wo_swiglu_s8(x2d, wq_gu, sw_gu, bias_gu=None, overlap_previous: bool = False
     bias_c = None if bias_gu is None else _f32c(bias_gu)
     with _on(dev):
         ws = wo_workspace(dev, N2) if balanced else None
-        check(lib.lc_wo_swiglu_s8_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq_gu.data_ptr(),
+        check(_wo_swiglu_s8_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, x2d.stride(0), wq_gu.data_ptr(),
                                      wq_gu.stride(0), N2, _ptr(sw_c), _ptr(bias_c), y.data_ptr(), N2 // 2,
                                      1 if overlap_previous else 0, _ptr(ws), 0 if ws is None else ws.numel(),
                                      _stream(dev)))
@@ -773,7 +778,7 @@ def group_matmul(x2d, packed, scales, biases, group_size: int = 64, bits: int = 
     sc, bi = _f32c(scales), _f32c(biases)
     with _on(dev):
         ws = None  # whole boxes per CTA: measured faster than the K-cutting schedule
-        check(lib.lc_group_matmul_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, packed.data_ptr(), sc.data_ptr(),
+        check(_group_matmul_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, packed.data_ptr(), sc.data_ptr(),
                                      bi.data_ptr(), N, group_size, bits, y.data_ptr(), 1 if overlap_previous else 0,
                                      _ptr(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return y
@@ -788,7 +793,7 @@ def group_matmul_lean(x2d, packed, scales, biases, group_size: int, bits: int):
     if x2d.data_ptr() % 16:
         x2d = x2d.clone()
     y = torch.empty((B, N), dtype=x2d.dtype, device=x2d.device)
-    check(lib.lc_group_matmul_ex(x2d.data_ptr(), _DTYPE[x2d.dtype], B, K, packed.data_ptr(), scales.data_ptr(),
+    check(_group_matmul_ex(x2d.data_ptr(), _DTYPE[x2d.dtype], B, K, packed.data_ptr(), scales.data_ptr(),
                                  biases.data_ptr(), N, group_size, bits, y.data_ptr(), 0, None, 0,
                                  _stream(x2d.device)))
     return y

@@ -77,6 +77,36 @@ def test_argument_validation_without_gpu(capi):
     assert L.lc_wo_digit_rows(33) == 256
 
 
+def test_fast_bindings_agree_with_ctypes(capi):
+    """The CPython module built beside the library serves the per-layer entry points: it is bound to the
+    addresses ctypes resolved, returns the library's own status codes, and refuses arguments of the wrong
+    number or kind before anything is called."""
+    fast, L = capi.fast, capi.lib
+    assert fast is not None, "lucid_b200/_C/_fastcall was not built"
+    for name in capi.FAST_ENTRY_POINTS:
+        assert capi.entry(name[3:]) is getattr(fast, name[3:])
+    assert capi.entry("quantize_f32") is not None and not hasattr(fast, "quantize_f32")  # everything else: ctypes
+    buf = ctypes.create_string_buffer(64)
+    p = (ctypes.addressof(buf) + 15) // 16 * 16
+    cases = {
+        "dynamic_linear_f32": (p, 0, -1, 0, 0, 0, 0, 0, 1e-8, p, 0, 0, None, None, None, p, 0, 0, p, 0, 0, None, None),
+        "group_matmul_ex": (p + 2, capi.LC_BF16, 1, 64, p, p, p, 1, 64, 8, p, 0, None, 0, None),
+        "wo_linear_s8_ex": (p, 99, 1, 16, 16, p, 16, 1, None, None, 0, None, None, -128, 127, p, 1, 0, None, 0, None),
+        "wo_swiglu_s8_ex": (p, 99, 1, 16, 16, p, 16, 16, None, None, p, 8, 0, None, 0, None),
+    }
+    for name, args in cases.items():
+        expected = getattr(L, "lc_" + name)(*args)
+        message = capi.last_error()
+        assert expected != capi.LC_OK
+        assert getattr(fast, name)(*args) == expected and capi.last_error() == message, name
+        with pytest.raises(TypeError):
+            getattr(fast, name)(*args[:-1])
+        with pytest.raises(TypeError):
+            getattr(fast, name)("x", *args[1:])
+    with pytest.raises(KeyError):
+        fast.bind("lc_quantize_f32", 0)
+
+
 def test_ops_refuse_cpu_tensors(capi):
     import torch
 
