@@ -300,6 +300,26 @@ def test_group_engine_routing(device):
     assert torch.allclose(fresh(x.to(device)).cpu(), out, atol=1e-4)
 
 
+def test_group_linear_above_32_rows_decodes_once(device):
+    """More than 32 rows: the module hands the decoded weight, its bias and ReLU to the tensor-core product and
+    keeps the decoded copy until a buffer changes in place; the rows agree with the 32-row path."""
+    torch.manual_seed(5)
+    lin = nn.Linear(128, 48)
+    m = nnq.QuantizedLinearMLX.from_float(lin, bits=8, group_size=64, relu=True)
+    x = torch.randn(3, 20, 128).to(torch.bfloat16).to(device)
+    wide = m(x)
+    assert wide.shape == (3, 20, 48) and wide.dtype is torch.bfloat16
+    held = m._wide_cache["w"]
+    assert held.dtype is torch.bfloat16 and tuple(held.shape) == (48, 128)
+    m(x)
+    assert m._wide_cache["w"] is held
+    narrow = torch.cat([m(x[i]) for i in range(3)]).reshape(3, 20, 48)
+    assert (wide.float() - narrow.float()).abs().max() <= 0.02 * narrow.float().abs().max()
+    m.biases.add_(0.01)
+    m(x)
+    assert m._wide_cache["w"] is not held
+
+
 @pytest.mark.gpu
 def test_forward_from_host_matches_whole_batch():
     from lucid_b200.nn.quantized.streaming import forward_from_host
