@@ -1262,7 +1262,10 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
     plan.partial = static_cast<float*>(scratch.ptr);
     plan.tickets = reinterpret_cast<int*>(static_cast<uint8_t*>(scratch.ptr) + sms * 2 * kRingSlotBytes);
   } else {
-    // no scratch: whole tiles only, the same number for every CTA
+    // no scratch: whole tiles only, the same number for every CTA.  (Filling every resident CTA slot with
+    // counts at most one apart -- 296 CTAs of 6 or 7 tiles instead of 256 of 7 for the decode MLP's gate / up
+    // matrix -- measured 1.0-1.4 us SLOWER at batches of up to 8, equal at 16: the shorter second passes cost
+    // more than the idle slots, which the next launch's CTAs use to prefetch.)
     const int64_t per = (tiles + sms - 1) / sms;
     plan.grid = static_cast<int>((tiles + per - 1) / per);
     plan.units = plan.grid * per * num_kc;
