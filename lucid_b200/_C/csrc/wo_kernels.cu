@@ -267,9 +267,11 @@ __host__ __device__ constexpr int x_bytes(int nt, int xb) { return xb * nt * 8 *
 constexpr int GP_PITCH = 17;
 __host__ __device__ constexpr int group_bytes(int gs, int tmax) { return gs ? 2 * 2 * tmax * 16 * GP_PITCH * 4 : 0; }
 // a ring stage holds `grp` vertically adjacent 16-row tiles of one K chunk, fetched by one TMA box
-__host__ __device__ constexpr int stages(int nt, int tmax, int xb, int grp, int gs, int cw) {
+// (`bits` = 4: two codes per byte, so the KC elements of an item row are KC / 2 bytes and a tile half a STAGE)
+__host__ __device__ constexpr int stages(int nt, int tmax, int xb, int grp, int gs, int cw, int bits = 8) {
   // 256 bytes: alignment of the ring to 128 bytes and the mbarriers (at most 2 * 9 + 2 * 3 of 8 bytes)
-  return (smem_budget(cw) - 256 - red_bytes(nt, tmax, cw) - x_bytes(nt, xb) - group_bytes(gs, tmax)) / (STAGE * grp);
+  return (smem_budget(cw) - 256 - red_bytes(nt, tmax, cw) - x_bytes(nt, xb) - group_bytes(gs, tmax)) /
+         (STAGE * bits / 8 * grp);
 }
 }  // namespace ring
 
@@ -307,6 +309,11 @@ __device__ __forceinline__ void wo_tma_load_2d(uint32_t dst, const CUtensorMap* 
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+__device__ __forceinline__ uint2 wo_lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
 }
 __device__ __forceinline__ uint4 wo_lds128(uint32_t addr) {
   uint4 v;
@@ -408,7 +415,12 @@ __device__ __forceinline__ int ring_owner(long long u, long long units, int grid
 // give the group's raw sum, which enters the running total as s * sum(x * c) + b * sum(x) -- the second
 // sum being an all-ones MMA over the unit's activations.
 // CW = consumer warps per CTA (16, or 8 with two CTAs per SM): see namespace ring.
-template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0, int CW = 16>
+// BITS = 4 (group-wise format only): eight codes per packed word, first code in the low bits.  An item row
+// is still KC elements, now KC / 2 bytes, so a 16 KB box holds two row tiles (GRP = 2); a lane reads the 8
+// bytes that hold its 16 codes, masks out code pairs (c0, c4), (c1, c5), (c2, c6), (c3, c7) of each word
+// -- a nibble in the low bits of a 16-bit half is the raw operand pattern as it stands -- and its
+// activation fragments are permuted once per chunk to match.
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0, int CW = 16, int BITS = 8>
 __global__ void __launch_bounds__(ring::threads(CW), ring::ctas_per_sm(CW))
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w1,
                       const __grid_constant__ CUtensorMap tmap_x,
@@ -431,9 +443,12 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   static_assert(CW == 16 || CW == 8, "16 consumer warps, or 8 with two CTAs per SM");
   using namespace ring;
   constexpr int kConsumerWarps = CW, kConsumerThreads = CW * 32;
-  constexpr int U = KC / (64 * CW);  // 64-byte units of an item row per warp
-  constexpr int S = stages(NT, TMAX, XB, GRP, GS, CW);
-  constexpr int GSTAGE = STAGE * GRP;
+  constexpr int U = KC / (64 * CW);  // 64-element units of an item row per warp
+  constexpr int S = stages(NT, TMAX, XB, GRP, GS, CW, BITS);
+  constexpr int WP = W_PITCH * BITS / 8;  // bytes of an item row
+  constexpr int TSTAGE = STAGE * BITS / 8;  // bytes of one 16-row tile of an item
+  constexpr int GSTAGE = TSTAGE * GRP;
+  static_assert(BITS == 8 || (BITS == 4 && GS != 0), "4-bit codes come in the group-wise format only");
   static_assert(S >= 3, "ring too shallow");
   static_assert(GRP == 1 || (GRP == 2 && TMAX % 2 == 0), "one or two row tiles per box");
   constexpr int COLS = NT * 8, RP = red_pitch(NT, CW);
@@ -502,8 +517,8 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           for (int kc = ps.kc0; kc < ps.kc1 && prefilled < S; ++kc)
             for (int j = 0; j < ps.n_tiles && prefilled < S; j += GRP, ++prefilled) {
               const bool whole = j + GRP <= ps.n_tiles;
-              wo_mbar_expect(full_bar(prefilled), whole ? GSTAGE : STAGE);
-              wo_tma_load_2d(base + prefilled * GSTAGE, whole ? &tmap_w : &tmap_w1, kc * (KC / 4),
+              wo_mbar_expect(full_bar(prefilled), whole ? GSTAGE : TSTAGE);
+              wo_tma_load_2d(base + prefilled * GSTAGE, whole ? &tmap_w : &tmap_w1, kc * (WP / 4),
                              (ps.tile0 + j) << 4, full_bar(prefilled));
               armed_mask |= 1u << prefilled;  // parity 0
             }
@@ -537,8 +552,8 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                 break;
               }
               const bool whole = j + GRP <= ps.n_tiles;
-              wo_mbar_expect(full_bar(stage), whole ? GSTAGE : STAGE);
-              wo_tma_load_2d(base + stage * GSTAGE, whole ? &tmap_w : &tmap_w1, kc * (KC / 4), (ps.tile0 + j) << 4,
+              wo_mbar_expect(full_bar(stage), whole ? GSTAGE : TSTAGE);
+              wo_tma_load_2d(base + stage * GSTAGE, whole ? &tmap_w : &tmap_w1, kc * (WP / 4), (ps.tile0 + j) << 4,
                              full_bar(stage));
               armed_mask |= 1u << stage;
               armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
@@ -714,6 +729,22 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           for (int u = 0; u < U; ++u)
 #pragma unroll
             for (int i = 0; i < 8; ++i) RawOperand<XT>::prescale(xa[nt][u][i]);
+        if constexpr (BITS == 4) {
+          // element pairs (0,1)(2,3)(4,5)(6,7) of every eight -> (0,4)(1,5)(2,6)(3,7), the order the masked
+          // nibbles of a packed word come in
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+              for (int h = 0; h < 8; h += 4) {
+                const uint32_t r0 = xa[nt][u][h], r1 = xa[nt][u][h + 1], r2 = xa[nt][u][h + 2], r3 = xa[nt][u][h + 3];
+                xa[nt][u][h] = __byte_perm(r0, r2, 0x5410u);
+                xa[nt][u][h + 1] = __byte_perm(r0, r2, 0x7632u);
+                xa[nt][u][h + 2] = __byte_perm(r1, r3, 0x5410u);
+                xa[nt][u][h + 3] = __byte_perm(r1, r3, 0x7632u);
+              }
+        }
         // group-wise weights: sum of the activations of every unit (= of a piece of one group), per batch column
         // 2t and 2t + 1, from an all-ones MMA in two chains; already scaled to sum(x)
         float xgrp[GS ? U : 1][NT][2];
@@ -758,7 +789,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
               atomicCAS(&g_wo_status, 0, 2);
               ok = false;
             } else {
-              const uint32_t lane_src = base + stage * GSTAGE + g * W_PITCH + kbase;
+              const uint32_t lane_src = base + stage * GSTAGE + g * WP + kbase * BITS / 8;
 #pragma unroll
               for (int u = 0; u < U; ++u) {
                 // weights of the box's tiles for this unit: 16 bytes of row g and of row g + 8 each; the second
@@ -768,8 +799,15 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                 for (int jj = 0; jj < GRP; ++jj) {
                   uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = make_uint4(0u, 0u, 0u, 0u);
                   if (GRP == 1 || jb + jj < pass_tiles) {
-                    w0 = wo_lds128(lane_src + jj * STAGE + 64 * u);
-                    w1 = wo_lds128(lane_src + jj * STAGE + 64 * u + 8 * W_PITCH);
+                    if constexpr (BITS == 8) {
+                      w0 = wo_lds128(lane_src + jj * TSTAGE + 64 * u);
+                      w1 = wo_lds128(lane_src + jj * TSTAGE + 64 * u + 8 * WP);
+                    } else {  // 16 codes = 8 bytes; .x / .y hold them, .z / .w stay unused
+                      const uint2 h0 = wo_lds64(lane_src + jj * TSTAGE + 32 * u);
+                      const uint2 h1 = wo_lds64(lane_src + jj * TSTAGE + 32 * u + 8 * WP);
+                      w0.x = h0.x; w0.y = h0.y;
+                      w1.x = h1.x; w1.y = h1.y;
+                    }
                   }
                   wr[jj][0][0] = w0.x; wr[jj][0][1] = w0.y; wr[jj][0][2] = w0.z; wr[jj][0][3] = w0.w;
                   wr[jj][1][0] = w1.x; wr[jj][1][1] = w1.y; wr[jj][1][2] = w1.z; wr[jj][1][3] = w1.w;
@@ -806,8 +844,15 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
 #pragma unroll
                     for (int jj = 0; jj < GRP; ++jj) {
                       if (GRP == 1 || jb + jj < pass_tiles) {
-                        const uint32_t a0 = __byte_perm(wr[jj][0][q], 0u, 0x4140u), a2 = __byte_perm(wr[jj][0][q], 0u, 0x4342u);
-                        const uint32_t a1 = __byte_perm(wr[jj][1][q], 0u, 0x4140u), a3 = __byte_perm(wr[jj][1][q], 0u, 0x4342u);
+                        uint32_t a0, a1, a2, a3;
+                        if constexpr (BITS == 8) {
+                          a0 = __byte_perm(wr[jj][0][q], 0u, 0x4140u), a2 = __byte_perm(wr[jj][0][q], 0u, 0x4342u);
+                          a1 = __byte_perm(wr[jj][1][q], 0u, 0x4140u), a3 = __byte_perm(wr[jj][1][q], 0u, 0x4342u);
+                        } else {  // MMA q takes codes 4 (q & 1) .. + 3 and four further on of word q / 2
+                          const uint32_t v0 = wr[jj][0][q >> 1] >> (8 * (q & 1)), v1 = wr[jj][1][q >> 1] >> (8 * (q & 1));
+                          a0 = v0 & 0x000F000Fu, a2 = (v0 >> 4) & 0x000F000Fu;
+                          a1 = v1 & 0x000F000Fu, a3 = (v1 >> 4) & 0x000F000Fu;
+                        }
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt)
                           mma_16816<XT>(part[jj][nt], a0, a1, a2, a3, xa[nt][u][2 * q], xa[nt][u][2 * q + 1]);
@@ -1215,12 +1260,12 @@ struct RingScratch {
 };
 constexpr int64_t kRingSlotBytes = 16 * 32 * 4;  // 16 rows * largest COLS floats
 
-template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0, int CW = 16>
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0, int CW = 16, int BITS = 8>
 static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                    int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
                                    int64_t ldy, bool overlap, const WoEpilogue& epi, const RingScratch& scratch,
                                    cudaStream_t st) {
-  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU, GRP, GS, CW>;
+  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU, GRP, GS, CW, BITS>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
   int dev = 0;
@@ -1235,13 +1280,14 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   // weights as [N, K/4] 4-byte units (box 256 x 16*GRP = 1024 bytes x 16*GRP rows), activations as
   // [B, K/4] 8-byte units (box 256 x COLS = 2048 bytes per row)
   CUtensorMap map_w, map_w1, map_x;
-  if (int32_t rc = encode_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, w, static_cast<uint64_t>(K / 4),
-                                        static_cast<uint64_t>(N), static_cast<uint64_t>(ldw), ring::KC / 4, 16 * GRP,
-                                        CU_TENSOR_MAP_SWIZZLE_NONE))
+  // (K and ldw count elements; a row of 4-bit codes is half as many bytes)
+  if (int32_t rc = encode_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, w, static_cast<uint64_t>(K * BITS / 32),
+                                        static_cast<uint64_t>(N), static_cast<uint64_t>(ldw * BITS / 8),
+                                        ring::KC * BITS / 32, 16 * GRP, CU_TENSOR_MAP_SWIZZLE_NONE))
     return rc;
-  if (int32_t rc = encode_tensor_map_2d(&map_w1, CU_TENSOR_MAP_DATA_TYPE_UINT32, w, static_cast<uint64_t>(K / 4),
-                                        static_cast<uint64_t>(N), static_cast<uint64_t>(ldw), ring::KC / 4, 16,
-                                        CU_TENSOR_MAP_SWIZZLE_NONE))
+  if (int32_t rc = encode_tensor_map_2d(&map_w1, CU_TENSOR_MAP_DATA_TYPE_UINT32, w, static_cast<uint64_t>(K * BITS / 32),
+                                        static_cast<uint64_t>(N), static_cast<uint64_t>(ldw * BITS / 8),
+                                        ring::KC * BITS / 32, 16, CU_TENSOR_MAP_SWIZZLE_NONE))
     return rc;
   if (int32_t rc = encode_tensor_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_INT64, x, static_cast<uint64_t>(K / 4),
                                         static_cast<uint64_t>(B), static_cast<uint64_t>(ldx) * 2, ring::KC / 4,
@@ -1375,10 +1421,11 @@ static int32_t launch_group_matmul(const XT* x, int64_t B, int64_t K, const uint
   return check_launch("group_matmul");
 }
 
-// 8-bit group-wise weights of a few MB and more on the streaming kernel (16-bit activations, groups of
-// 64 or 128): the packed words are the code bytes in K order, so the weight is streamed exactly like a
-// per-channel int8 matrix and the group scales / biases are read by the consumer warps.
-template <typename XT, int GS>
+// Group-wise weights of a few MB and more on the streaming kernel (16-bit activations; 8-bit codes in
+// groups of 64 or 128, 4-bit codes in groups of 64): the packed words are the codes in K order, so the
+// weight is streamed exactly like a per-channel int8 matrix -- an item row of 1024 elements being 1024 or
+// 512 bytes -- and the group scales / biases are read by the consumer warps.
+template <typename XT, int GS, int BITS>
 static int32_t launch_group_ring(const XT* x, int64_t B, int64_t K, const uint8_t* codes, const float* scales,
                                  const float* biases, int64_t N, XT* y, bool overlap, const RingScratch& scratch,
                                  cudaStream_t st) {
@@ -1391,8 +1438,21 @@ static int32_t launch_group_ring(const XT* x, int64_t B, int64_t K, const uint8_
     const XT* xb = x + b0 * K;
     XT* yb = y + b0 * N;
     int32_t rc;
-    if (bc <= 8)  // two half-size CTAs per SM, passes of four tiles in 16-row boxes, four deep (measured: 19.7 us on
-                  // [14336, 4096] at group size 64 against 22.5 us with passes of two tiles in 32-row boxes)
+    if constexpr (BITS == 4) {
+      // 16 KB boxes of two row tiles; up to 8 rows on two half-size CTAs per SM, 9..16 with the activations
+      // staged in shared memory, more as two such passes
+      (void)few;
+      if (bc <= 8) {
+        rc = launch_wo_ring_inst<XT, 1, 4, 0, false, 2, GS, 8, 4>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+      } else {
+        const int64_t first = bc < 16 ? bc : 16;
+        rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 2, GS, 16, 4>(xb, first, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+        if (!rc && bc > 16)
+          rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 2, GS, 16, 4>(xb + 16 * K, bc - 16, K, K, w, K, N, scales, biases, yb + 16 * N, N,
+                                                                     true, none, scratch, st);
+      }
+    } else if (bc <= 8)  // two half-size CTAs per SM, passes of four tiles in 16-row boxes, four deep (measured: 19.7 us on
+                         // [14336, 4096] at group size 64 against 22.5 us with passes of two tiles in 32-row boxes)
       rc = launch_wo_ring_inst<XT, 1, 4, 0, false, 1, GS, 8>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
     else if (bc <= 16)
       rc = few ? launch_wo_ring_inst<XT, 2, 2, 3, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
@@ -1564,17 +1624,20 @@ extern "C" int32_t lc_group_matmul_ex(const void* x, int32_t x_dtype, int64_t ba
     return fail(LC_ERR_UNSUPPORTED, "group_matmul: x must be 16-byte aligned (packed, scales, biases 4-byte aligned)");
   cudaStream_t st = as_stream(stream);
   const uint32_t* pk = reinterpret_cast<const uint32_t*>(packed);
-  // weights from a few MB up, 8-bit codes in groups of 64 / 128, 16-bit activations: the streaming kernel
-  const bool stream_ok = bits == 8 && (group_size == 64 || group_size == 128) && (x_dtype == LC_BF16 || x_dtype == LC_F16) &&
-                         K % 16 == 0 && N * K >= (int64_t{4} << 20) && aligned(packed, 16) && aligned(x, 16);
+  // weights from a few MB up, 8-bit codes in groups of 64 / 128 or 4-bit codes in groups of 64, 16-bit
+  // activations: the streaming kernel
+  const bool stream_ok = ((bits == 8 && (group_size == 64 || group_size == 128)) || (bits == 4 && group_size == 64)) &&
+                         (x_dtype == LC_BF16 || x_dtype == LC_F16) && K % 32 == 0 &&
+                         N * K * bits >= (int64_t{32} << 20) && aligned(packed, 16) && aligned(x, 16);
   if (stream_ok) {
     const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;
     const RingScratch scratch = {workspace, workspace ? workspace_bytes : 0};
     const uint8_t* codes = reinterpret_cast<const uint8_t*>(packed);
-#define LC_GR(XT, GS) \
-  launch_group_ring<XT, GS>(static_cast<const XT*>(x), batch, K, codes, scales, biases, N, static_cast<XT*>(y), overlap, scratch, st)
-    if (x_dtype == LC_BF16) return group_size == 64 ? LC_GR(__nv_bfloat16, 64) : LC_GR(__nv_bfloat16, 128);
-    return group_size == 64 ? LC_GR(__half, 64) : LC_GR(__half, 128);
+#define LC_GR(XT, GS, BITS) \
+  launch_group_ring<XT, GS, BITS>(static_cast<const XT*>(x), batch, K, codes, scales, biases, N, static_cast<XT*>(y), overlap, scratch, st)
+    if (bits == 4) return x_dtype == LC_BF16 ? LC_GR(__nv_bfloat16, 64, 4) : LC_GR(__half, 64, 4);
+    if (x_dtype == LC_BF16) return group_size == 64 ? LC_GR(__nv_bfloat16, 64, 8) : LC_GR(__nv_bfloat16, 128, 8);
+    return group_size == 64 ? LC_GR(__half, 64, 8) : LC_GR(__half, 128, 8);
 #undef LC_GR
   }
 #define LC_GM(XT)                                                                                     \

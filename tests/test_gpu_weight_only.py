@@ -377,6 +377,58 @@ def test_group_matmul_streaming_kernel(ops, dtype, gs, B, N, K):
     assert ops.wo_linear_status() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,N,K", [(1, 14336, 4096), (4, 4096, 14336), (8, 2064, 4160), (9, 4096, 4096), (16, 14336, 4096),
+                                   (32, 2064, 4096), (3, 4100, 2176)])
+def test_group_matmul_streaming_kernel_4bit(ops, dtype, B, N, K):
+    """4-bit codes in groups of 64, 4 MB of packed words and more: the streaming kernel, against the oracle's
+    float64 product of the same packed words, scales and biases within the rounding bound of an
+    fp32-accumulated result (|x| * (15 s + |b|) per term), and against the direct kernel, which serves the
+    same words below that size; cold and warm launches agree bit for bit."""
+    g = torch.Generator(device="cuda").manual_seed(B + N + K)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.05
+    p, s, b = ops.group_quantize(w, 64, 4)
+    assert p.shape == (N, K // 8) and N * K // 2 >= 4 << 20
+    x = torch.randn(B, K, device="cuda", generator=g).to(dtype)
+    y = ops.group_matmul(x, p, s, b, 64, 4)
+    assert y.dtype == dtype and y.shape == (B, N)
+    ref = O.group_matmul(x.double().cpu().numpy(), p.cpu().numpy(), host(s), host(b), 64, 4)
+    mag = (x.double().abs() @ (15.0 * s.double().repeat_interleave(64, 1) + b.double().abs().repeat_interleave(64, 1)).T)
+    assert_rounded_product(y, ref, mag.cpu().numpy(), K, dtype)
+    # every distinct nibble position: one-hot activations pick single columns of a row block
+    rows = min(N, 64)
+    small = ops.group_matmul(x, p[:rows].contiguous(), s[:rows].contiguous(), b[:rows].contiguous(), 64, 4)  # direct kernel
+    assert_rounded_product(small, ref[:, :rows], mag[:, :rows].cpu().numpy(), K, dtype)
+    again = ops.group_matmul(x, p, s, b, 64, 4, overlap_previous=True)
+    assert torch.equal(again.view(torch.int16), y.view(torch.int16))
+    flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for i in range(2):
+        flush.fill_(i)
+        torch.cuda.synchronize()
+        assert torch.equal(ops.group_matmul(x, p, s, b, 64, 4).view(torch.int16), y.view(torch.int16))
+    assert ops.wo_linear_status() == 0
+
+
+def test_group_matmul_4bit_streaming_places_every_nibble(ops):
+    """One-hot activations against unit scales and zero biases return the codes themselves: every nibble of
+    every word position of a K chunk lands in its own column."""
+    N, K = 4096, 2048
+    k = torch.arange(K, device="cuda").view(1, -1)
+    n = torch.arange(N, device="cuda").view(-1, 1)
+    codes = ((n * 5 + k * 3 + (k // 8)) % 16).to(torch.int64)
+    words = (codes.view(N, K // 8, 8) << (4 * torch.arange(8, device="cuda"))).sum(-1)
+    packed = words.to(torch.int32) if int(words.max()) < 2 ** 31 else (words - (words >= 2 ** 31) * 2 ** 32).to(torch.int32)
+    s = torch.ones(N, K // 64, device="cuda")
+    b = torch.zeros(N, K // 64, device="cuda")
+    assert torch.equal(ops.group_dequantize(packed, s, b, 64, 4), codes.float())
+    for start in range(0, K, 8):
+        x = torch.zeros(8, K, device="cuda", dtype=torch.bfloat16)
+        x[torch.arange(8), start + torch.arange(8)] = 1.0
+        y = ops.group_matmul(x, packed, s, b, 64, 4)
+        assert torch.equal(y.float(), codes[:, start:start + 8].T.float()), start
+    assert ops.wo_linear_status() == 0
+
+
 def test_group_matmul_accepts_a_view_that_starts_off_a_16_byte_boundary(ops):
     """A contiguous activation view into a larger storage (here: starting one element in) is copied to an
     aligned buffer by the front end instead of reaching the kernels' 16-byte loads."""
