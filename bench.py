@@ -512,36 +512,38 @@ def extras_single_gpu(torch, ops, peaks) -> dict:
         del xs, wq_s, digits
     except Exception as e:  # noqa: BLE001
         out["static_linear_8192x2048x512"] = {"error": repr(e)[:300]}
-    # ---- group-wise 8-bit weights [14336, 4096], groups of 64, bf16 activations (the decode shape of the
-    # reference's packed path): packed bytes + scales + biases once per call
-    try:
-        Ng, Kg = 14336, 4096
-        packs = []
-        for _ in range(4):  # 4 x 66 MB rotate so that no call finds its weights in L2
-            w = torch.randn(Ng, Kg, device=dev, generator=g) * 0.02
-            packs.append(ops.group_quantize(w, 64, 8))
-            del w
-        gm = {}
-        for batch in (1, 4, 16):
-            xg = torch.randn(batch, Kg, device=dev, generator=g).to(torch.bfloat16)
-            turn = [0]
+    # ---- group-wise 8-bit and 4-bit weights [14336, 4096], groups of 64, bf16 activations (the decode shape
+    # of the reference's packed path): packed bytes + scales + biases once per call
+    for gbits in (8, 4):
+        key = f"group_matmul_14336x4096_gs64_{gbits}bit"
+        try:
+            Ng, Kg = 14336, 4096
+            packs = []
+            for _ in range(4):  # four copies rotate so that no call finds its weights in L2
+                w = torch.randn(Ng, Kg, device=dev, generator=g) * 0.02
+                packs.append(ops.group_quantize(w, 64, gbits))
+                del w
+            gm = {}
+            for batch in (1, 4, 16):
+                xg = torch.randn(batch, Kg, device=dev, generator=g).to(torch.bfloat16)
+                turn = [0]
 
-            def gstep():
-                p_, s_, b_ = packs[turn[0] % 4]
-                turn[0] += 1
-                return ops.group_matmul(xg, p_, s_, b_, 64, 8, overlap_previous=True)
+                def gstep():
+                    p_, s_, b_ = packs[turn[0] % 4]
+                    turn[0] += 1
+                    return ops.group_matmul(xg, p_, s_, b_, 64, gbits, overlap_previous=True)
 
-            nbytes = Ng * Kg + 2 * Ng * (Kg // 64) * 4
-            try:
-                ms = graph_time(torch, gstep, reps=8, replays=10)
-            except Exception:
-                ms = time_loop(torch, gstep, 40, 5)
-            gm[f"batch_{batch}"] = {"us": ms * 1e3, "GB/s": nbytes / ms / 1e6, "algorithmic_bytes": nbytes,
-                                    "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}
-        out["group_matmul_14336x4096_gs64_8bit"] = gm
-        del packs
-    except Exception as e:  # noqa: BLE001
-        out["group_matmul_14336x4096_gs64_8bit"] = {"error": repr(e)[:300]}
+                nbytes = Ng * Kg * gbits // 8 + 2 * Ng * (Kg // 64) * 4
+                try:
+                    ms = graph_time(torch, gstep, reps=8, replays=10)
+                except Exception:
+                    ms = time_loop(torch, gstep, 40, 5)
+                gm[f"batch_{batch}"] = {"us": ms * 1e3, "GB/s": nbytes / ms / 1e6, "algorithmic_bytes": nbytes,
+                                        "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}
+            out[key] = gm
+            del packs
+        except Exception as e:  # noqa: BLE001
+            out[key] = {"error": repr(e)[:300]}
     # ---- small transformer encoder, every Linear dynamic int8 (6 layers, d 512, 8 heads, FFN 2048)
     try:
         out["encoder_6x512_b32_s256"] = encoder_extras(torch, dev, g)
