@@ -263,9 +263,13 @@ __host__ __device__ constexpr int smem_budget(int cw) { return cw == 16 ? 225 * 
 __host__ __device__ constexpr int red_pitch(int nt, int cw) { return cw == 16 ? nt * 8 + 1 : nt * 8; }
 __host__ __device__ constexpr int red_bytes(int nt, int tmax, int cw) { return tmax * cw * 16 * red_pitch(nt, cw) * 4; }
 __host__ __device__ constexpr int x_bytes(int nt, int xb) { return xb * nt * 8 * X_PITCH; }
-// group-wise format: two buffers x {scales, biases} x tmax*16 rows x (groups per K chunk, padded to 17)
-constexpr int GP_PITCH = 17;
-__host__ __device__ constexpr int group_bytes(int gs, int tmax) { return gs ? 2 * 2 * tmax * 16 * GP_PITCH * 4 : 0; }
+// group-wise format: GP_STAGES slots x {scales, biases} x tmax*16 rows x (groups per K chunk) floats, filled by
+// the copy engine as swizzled boxes (1 KB for their alignment, 64 bytes for the slots' mbarriers)
+constexpr int GP_STAGES = 3;
+__host__ __device__ constexpr int group_array_bytes(int gs, int tmax) { return gs ? tmax * 16 * (KC / gs) * 4 : 0; }
+__host__ __device__ constexpr int group_bytes(int gs, int tmax) {
+  return gs ? GP_STAGES * 2 * group_array_bytes(gs, tmax) + 1024 + 64 : 0;
+}
 // a ring stage holds `grp` vertically adjacent 16-row tiles of one K chunk, fetched by one TMA box
 // (`bits` = 4: two codes per byte, so the KC elements of an item row are KC / 2 bytes and a tile half a STAGE)
 __host__ __device__ constexpr int stages(int nt, int tmax, int xb, int grp, int gs, int cw, int bits = 8) {
@@ -309,6 +313,11 @@ __device__ __forceinline__ void wo_tma_load_2d(uint32_t dst, const CUtensorMap* 
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+__device__ __forceinline__ float wo_lds32f(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
 }
 __device__ __forceinline__ uint2 wo_lds64(uint32_t addr) {
   uint2 v;
@@ -423,7 +432,8 @@ __device__ __forceinline__ int ring_owner(long long u, long long units, int grid
 template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0, int CW = 16, int BITS = 8>
 __global__ void __launch_bounds__(ring::threads(CW), ring::ctas_per_sm(CW))
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w1,
-                      const __grid_constant__ CUtensorMap tmap_x,
+                      const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_gs,
+                      const __grid_constant__ CUtensorMap tmap_gb,
                       const XT* __restrict__ xg, int64_t ldx,
                       int64_t B, int64_t K, int64_t N, const float* __restrict__ sw,
                       const float* __restrict__ bias, XT* __restrict__ y, int64_t ldy, const RingPlan plan,
@@ -456,14 +466,20 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   const uint32_t base = (wo_smem_u32(wo_smem_raw) + 127u) & ~127u;
   const uint32_t x_base = base + S * GSTAGE;
   const uint32_t red_base = x_base + x_bytes(NT, XB);
-  const uint32_t gp_base = red_base + red_bytes(NT, TMAX, CW);
-  const uint32_t bar_base = gp_base + group_bytes(GS, TMAX);
+  // group scales / biases: boxes of [16 TMAX rows x groups of a K chunk] floats per array, swizzled by the copy
+  // engine so that the eight rows a warp reads at one group column fall into eight different banks
+  constexpr int GPC = GS ? KC / (GS ? GS : 1) : 1;  // groups per K chunk: 16 or 8
+  constexpr int GA = group_array_bytes(GS, TMAX);
+  const uint32_t gp_base = (red_base + red_bytes(NT, TMAX, CW) + 1023u) & ~1023u;
+  const uint32_t gbar_base = gp_base + GP_STAGES * 2 * GA;
+  auto gfull_bar = [&](int s) { return gbar_base + 8u * s; };
+  auto gempty_bar = [&](int s) { return gbar_base + 8u * (GP_STAGES + s); };
+  const uint32_t bar_base = red_base + red_bytes(NT, TMAX, CW) + group_bytes(GS, TMAX);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
   auto xfull_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
   auto xempty_bar = [&](int s) { return bar_base + 8u * (2 * S + XB + s); };
   float* red = reinterpret_cast<float*>(wo_smem_raw + (red_base - wo_smem_u32(wo_smem_raw)));
-  float* gp = reinterpret_cast<float*>(wo_smem_raw + (gp_base - wo_smem_u32(wo_smem_raw)));
 
   __shared__ int s_last_ticket;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -472,6 +488,10 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
     if (GRP > 1) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w1)) : "memory");
     if (XB > 0) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+    if (GS != 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_gs)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_gb)) : "memory");
+    }
   }
   const int num_kc = static_cast<int>((K + KC - 1) / KC);
   const int nb = static_cast<int>(B);
@@ -489,6 +509,10 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(xfull_bar(s)), "r"(1) : "memory");
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(xempty_bar(s)), "r"(kConsumerWarps) : "memory");
     }
+    for (int s = 0; s < (GS ? GP_STAGES : 0); ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gfull_bar(s)), "r"(1) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(gempty_bar(s)), "r"(kConsumerWarps) : "memory");
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -500,9 +524,10 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   if (warp == kConsumerWarps) {
     // ===================== producer =====================
     if (lane == 0) {
-      int stage = 0, xi = 0;
-      uint32_t phase = 0;
+      int stage = 0, xi = 0, gstage = 0;
+      uint32_t phase = 0, gphase = 0;
       uint32_t armed_mask = 0, armed_parity = 0, xarmed_mask = 0, xarmed_parity = 0;  // bit per stage
+      uint32_t garmed_mask = 0, garmed_parity = 0;
       bool ok = true;
       // Weights do not depend on the kernel before this one: when the launch may overlap it,
       // fill the ring with the first items of the first pass (in consumption order), and only
@@ -537,6 +562,24 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
             ok = false;
             break;
           }
+          // group-wise format: scales and biases of the pass's rows for the groups of this chunk (rows past N
+          // and groups past K read as zero)
+          if (GS != 0) {
+            if (!wo_mbar_wait(gempty_bar(gstage), gphase ^ 1u)) {
+              atomicCAS(&g_wo_status, 0, 1);
+              ok = false;
+              break;
+            }
+            wo_mbar_expect(gfull_bar(gstage), 2 * GA);
+            wo_tma_load_2d(gp_base + gstage * 2 * GA, &tmap_gs, kc * GPC, ps.tile0 << 4, gfull_bar(gstage));
+            wo_tma_load_2d(gp_base + gstage * 2 * GA + GA, &tmap_gb, kc * GPC, ps.tile0 << 4, gfull_bar(gstage));
+            garmed_mask |= 1u << gstage;
+            garmed_parity = (garmed_parity & ~(1u << gstage)) | (gphase << gstage);
+            if (++gstage == GP_STAGES) {
+              gstage = 0;
+              gphase ^= 1u;
+            }
+          }
           // activations: [COLS rows x KC elements] box of 8-byte units, rows >= B read as zero
           if (!XDIRECT) {
             wo_mbar_expect(xfull_bar(xb), COLS * X_PITCH);
@@ -570,6 +613,8 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         if (armed_mask & (1u << s)) wo_mbar_wait(full_bar(s), (armed_parity >> s) & 1u);
       for (int s = 0; s < XB; ++s)
         if (xarmed_mask & (1u << s)) wo_mbar_wait(xfull_bar(s), (xarmed_parity >> s) & 1u);
+      for (int s = 0; s < (GS ? GP_STAGES : 0); ++s)
+        if (garmed_mask & (1u << s)) wo_mbar_wait(gfull_bar(s), (garmed_parity >> s) & 1u);
     }
   } else {
     // ===================== consumers =====================
@@ -579,8 +624,8 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     const int g = lane >> 2, t = lane & 3;
     const int kwarp = warp * (64 * U);   // first byte of this warp's units inside an item row
     const int kbase = kwarp + t * 16;    // this lane's 16 bytes of unit 0; unit u lies 64 u bytes further
-    int stage = 0, xi = 0;
-    uint32_t phase = 0;
+    int stage = 0, xi = 0, gstage = 0;
+    uint32_t phase = 0, gphase = 0;
     bool ok = true;
     RingWalk<TMAX> walk(u_begin, u_end, num_kc);
     RingPass ps;
@@ -604,40 +649,6 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) xlane[nt][0] = xlane[nt][1] = 0.0f;
 
-      // Group-wise format: the scales and biases of a chunk -- 16 rows x (KC / GS) groups per tile and
-      // array -- are fetched by all consumer threads together so that a warp's load covers whole 64-byte
-      // row pieces, and handed around through shared memory.  (Each warp fetching its own group's values
-      // touches 8 separate sectors per load: the L1 then limits the kernel to a third of the HBM rate.)
-      // The values of chunk kc + 1 are requested at the top of iteration kc and parked after it, so their
-      // latency hides behind the chunk's work.
-      constexpr int GPC = GS ? KC / (GS ? GS : 1) : 1;          // groups per K chunk: 16 or 8
-      constexpr int GP_ARRAY = TMAX * 16 * GP_PITCH;            // floats per array and buffer
-      constexpr int GFETCH = GS ? 512 / kConsumerThreads : 1;   // (array, row, group) slots per thread and tile
-      const int64_t n_groups = GS ? K / (GS ? GS : 1) : 0;
-      float gfetch[GS ? TMAX : 1][GFETCH];
-      auto request_groups = [&](int kc_for) {  // slot -> (array, row, group) of every tile of the pass
-#pragma unroll
-        for (int e = 0; e < GFETCH; ++e) {
-          const int et = threadIdx.x + e * kConsumerThreads, arr = et >> 8, r = (et >> 4) & 15, c = et & 15;
-          const float* src = arr ? bias : sw;
-#pragma unroll
-          for (int j = 0; j < (GS ? TMAX : 1); ++j) {
-            const int64_t row = ((static_cast<int64_t>(ps.tile0) + j) << 4) + r;
-            const int64_t grp_i = static_cast<int64_t>(kc_for) * GPC + c;
-            gfetch[j][e] = (c < GPC && j < pass_tiles && row < N && grp_i < n_groups) ? __ldg(src + row * n_groups + grp_i) : 0.0f;
-          }
-        }
-      };
-      auto park_groups = [&](int buf) {
-#pragma unroll
-        for (int e = 0; e < GFETCH; ++e) {
-          const int et = threadIdx.x + e * kConsumerThreads, arr = et >> 8, r = (et >> 4) & 15, c = et & 15;
-          if (c < GPC) {
-#pragma unroll
-            for (int j = 0; j < (GS ? TMAX : 1); ++j) gp[(buf * 2 + arr) * GP_ARRAY + (j * 16 + r) * GP_PITCH + c] = gfetch[j][e];
-          }
-        }
-      };
       // direct activation loads: lane (g, t) takes elements [kc * KC + kbase + 64 u, +16) of batch rows nt * 8 + g
       constexpr int XN = XDIRECT ? NT : 1;
       uint32_t xnext[XPREF ? XN : 1][U][8];
@@ -666,20 +677,18 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           }
       };
       if constexpr (XPREF) load_x(ps.kc0, xnext);
-      int gbuf = 0;
-      if (GS != 0) {  // first chunk of the pass: nothing to hide behind
-        request_groups(ps.kc0);
-        park_groups(0);
-        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-      }
 
       for (int kc = ps.kc0; kc < ps.kc1 && (GS != 0 || ok); ++kc, ++xi) {
         const int xb = xi % XBN;
         const uint32_t xphase = static_cast<uint32_t>((xi / XBN) & 1);
-        if (GS != 0 && kc + 1 < ps.kc1) request_groups(kc + 1);
         do {  // (a warp whose wait ran out still takes part in the barriers below)
         if (!ok) break;
         if (!XDIRECT && !wo_mbar_wait(xfull_bar(xb), xphase)) {
+          atomicCAS(&g_wo_status, 0, 2);
+          ok = false;
+          break;
+        }
+        if (GS != 0 && !wo_mbar_wait(gfull_bar(gstage), gphase)) {  // this chunk's group scales and biases
           atomicCAS(&g_wo_status, 0, 2);
           ok = false;
           break;
@@ -773,14 +782,19 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           }
         }
         // group-wise weights: scale and bias of rows g and g + 8 of tile j for the group a unit lies in come
-        // from the shared-memory copy (pitch 17: the eight rows of a quad column fall into different banks)
-        const float* gcur = gp + gbuf * 2 * GP_ARRAY;
+        // from the box the copy engine wrote: rows of GPC floats whose 16-byte pieces it exchanged by row
+        // (64-byte rows: piece ^= (row >> 1) & 3; 32-byte rows: piece ^= (row >> 2) & 1)
+        const uint32_t gcur = gp_base + gstage * 2 * GA;
+        auto group_at = [&](int row, int gcol) {
+          const int piece = (gcol >> 2) ^ (GPC == 16 ? (row >> 1) & 3 : (row >> 2) & 1);
+          return static_cast<uint32_t>(row * (GPC * 4) + (piece << 4) + ((gcol & 3) << 2));
+        };
         auto read_group = [&](int j, int gcol, float (&out)[4]) {  // s[row g], s[row g + 8], b[row g], b[row g + 8]
-          const float* sc = gcur + (j * 16 + g) * GP_PITCH + gcol;
-          out[0] = sc[0];
-          out[1] = sc[8 * GP_PITCH];
-          out[2] = sc[GP_ARRAY];
-          out[3] = sc[GP_ARRAY + 8 * GP_PITCH];
+          const uint32_t lo = gcur + group_at(j * 16 + g, gcol), hi = gcur + group_at(j * 16 + g + 8, gcol);
+          out[0] = wo_lds32f(lo);
+          out[1] = wo_lds32f(hi);
+          out[2] = wo_lds32f(lo + GA);
+          out[3] = wo_lds32f(hi + GA);
         };
 #pragma unroll
         for (int jb = 0; jb < TMAX; jb += GRP) {
@@ -895,10 +909,14 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         __syncwarp();
         if (!XDIRECT && lane == 0 && ok) wo_mbar_arrive(xempty_bar(xb));
         } while (false);
-        if (GS != 0) {
-          if (kc + 1 < ps.kc1) park_groups(gbuf ^ 1);
-          asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");  // parked values visible; old buffer free
-          gbuf ^= 1;
+        if (GS != 0) {  // the slot of the group parameters goes back to the copy engine (as for the weight slots)
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) wo_mbar_arrive(gempty_bar(gstage));
+          if (++gstage == GP_STAGES) {
+            gstage = 0;
+            gphase ^= 1u;
+          }
         }
       }
 
@@ -1293,6 +1311,19 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
                                         static_cast<uint64_t>(B), static_cast<uint64_t>(ldx) * 2, ring::KC / 4,
                                         NT * 8, CU_TENSOR_MAP_SWIZZLE_NONE))
     return rc;
+  // group-wise format: sw / bias are the [N, K / GS] scales and biases; a box is the groups of one K chunk for the
+  // rows of a whole pass, swizzled for conflict-free reads (other formats: placeholders, never dereferenced)
+  CUtensorMap map_gs = map_w, map_gb = map_w;
+  if (GS != 0) {
+    const uint64_t n_groups = static_cast<uint64_t>(K / (GS ? GS : 1));
+    const CUtensorMapSwizzle swz = GS == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+    if (int32_t rc = encode_tensor_map_2d(&map_gs, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, sw, n_groups, static_cast<uint64_t>(N),
+                                          n_groups * 4, ring::KC / (GS ? GS : 1), 16 * TMAX, swz))
+      return rc;
+    if (int32_t rc = encode_tensor_map_2d(&map_gb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, bias, n_groups, static_cast<uint64_t>(N),
+                                          n_groups * 4, ring::KC / (GS ? GS : 1), 16 * TMAX, swz))
+      return rc;
+  }
   const int64_t tiles = (N + 15) / 16;
   const int64_t num_kc = (K + ring::KC - 1) / ring::KC;
   const int64_t sms = static_cast<int64_t>(sm_count()) * ring::ctas_per_sm(CW);  // CTAs resident at once
@@ -1328,7 +1359,7 @@ static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ld
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = overlap ? 1 : 0;
-  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_w1, map_x, x, ldx, B, K, N, sw, bias, y, ldy, plan,
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, map_w, map_w1, map_x, map_gs, map_gb, x, ldx, B, K, N, sw, bias, y, ldy, plan,
                                              overlap ? 1 : 0, epi);
   if (err != cudaSuccess) return fail(LC_ERR_CUDA, "wo_linear_s8 (ring): %s", cudaGetErrorString(err));
   return check_launch("wo_linear_s8 (ring)");
@@ -1627,8 +1658,9 @@ extern "C" int32_t lc_group_matmul_ex(const void* x, int32_t x_dtype, int64_t ba
   // weights from a few MB up, 8-bit codes in groups of 64 / 128 or 4-bit codes in groups of 64, 16-bit
   // activations: the streaming kernel
   const bool stream_ok = ((bits == 8 && (group_size == 64 || group_size == 128)) || (bits == 4 && group_size == 64)) &&
-                         (x_dtype == LC_BF16 || x_dtype == LC_F16) && K % 32 == 0 &&
-                         N * K * bits >= (int64_t{32} << 20) && aligned(packed, 16) && aligned(x, 16);
+                         (x_dtype == LC_BF16 || x_dtype == LC_F16) && K % (4 * group_size) == 0 &&
+                         N * K * bits >= (int64_t{32} << 20) && aligned(packed, 16) && aligned(x, 16) &&
+                         aligned(scales, 16) && aligned(biases, 16);  // (rows of group parameters in 16-byte steps)
   if (stream_ok) {
     const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;
     const RingScratch scratch = {workspace, workspace ? workspace_bytes : 0};
