@@ -666,18 +666,19 @@ def run_profile_case(args) -> int:
         def fn():
             digits, rs, _ = ops.split_f32_digits(xs)
             return ops.wo_gemm_digits(digits, rs, wq_s, sw=sw_s, bias=b_s)
-    elif case == "group_gemv":
+    elif case in ("group_gemv", "group_gemv_4bit"):
+        gbits = 4 if case.endswith("4bit") else 8
         packs = []
         for _ in range(4):
             w = torch.randn(14336, 4096, device=dev, generator=g) * 0.02
-            packs.append(ops.group_quantize(w, 64, 8))
+            packs.append(ops.group_quantize(w, 64, gbits))
         xb = torch.randn(int(args.profile_batch), 4096, device=dev, generator=g).to(torch.bfloat16)
         i = [0]
 
         def fn():
             p_, s_, b_ = packs[i[0] % 4]
             i[0] += 1
-            return ops.group_matmul(xb, p_, s_, b_, 64, 8)
+            return ops.group_matmul(xb, p_, s_, b_, 64, gbits)
     elif case == "wo_gemv":
         ws = []
         for _ in range(4):
@@ -1203,7 +1204,7 @@ def main() -> int:
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed case of one kernel (gemm, quantize_rows, quantize_tensor, "
                          "dequantize, quantize_given_scale, histc, merge, embedding, embedding_bag, gemm_small, gemm_shortk, wo_gemv, "
-                         "static_linear, static_linear_longk, group_gemv) for a profiler capture; prints no bench line")
+                         "static_linear, static_linear_longk, group_gemv, group_gemv_4bit) for a profiler capture; prints no bench line")
     ap.add_argument("--profile-batch", default=4)
     ap.add_argument("--gather", choices=("auto", "fused", "multimem", "copy", "nccl"), default="auto",
                     help="N > 1: how output shards are exchanged (auto = time fused / copy / multimem once, keep the fastest)")
