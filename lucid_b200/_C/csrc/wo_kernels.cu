@@ -1452,8 +1452,8 @@ static int32_t launch_group_matmul(const XT* x, int64_t B, int64_t K, const uint
   return check_launch("group_matmul");
 }
 
-// Group-wise weights of a few MB and more on the streaming kernel (16-bit activations; 8-bit codes in
-// groups of 64 or 128, 4-bit codes in groups of 64): the packed words are the codes in K order, so the
+// Group-wise weights of a few MB and more on the streaming kernel (16-bit activations; 8-bit or 4-bit codes
+// in groups of 64 or 128): the packed words are the codes in K order, so the
 // weight is streamed exactly like a per-channel int8 matrix -- an item row of 1024 elements being 1024 or
 // 512 bytes -- and the group scales / biases are read by the consumer warps.
 template <typename XT, int GS, int BITS>
@@ -1655,9 +1655,8 @@ extern "C" int32_t lc_group_matmul_ex(const void* x, int32_t x_dtype, int64_t ba
     return fail(LC_ERR_UNSUPPORTED, "group_matmul: x must be 16-byte aligned (packed, scales, biases 4-byte aligned)");
   cudaStream_t st = as_stream(stream);
   const uint32_t* pk = reinterpret_cast<const uint32_t*>(packed);
-  // weights from a few MB up, 8-bit codes in groups of 64 / 128 or 4-bit codes in groups of 64, 16-bit
-  // activations: the streaming kernel
-  const bool stream_ok = ((bits == 8 && (group_size == 64 || group_size == 128)) || (bits == 4 && group_size == 64)) &&
+  // weights from a few MB up, codes in groups of 64 / 128, 16-bit activations: the streaming kernel
+  const bool stream_ok = (group_size == 64 || group_size == 128) &&
                          (x_dtype == LC_BF16 || x_dtype == LC_F16) && K % (4 * group_size) == 0 &&
                          N * K * bits >= (int64_t{32} << 20) && aligned(packed, 16) && aligned(x, 16) &&
                          aligned(scales, 16) && aligned(biases, 16);  // (rows of group parameters in 16-byte steps)
@@ -1667,7 +1666,10 @@ extern "C" int32_t lc_group_matmul_ex(const void* x, int32_t x_dtype, int64_t ba
     const uint8_t* codes = reinterpret_cast<const uint8_t*>(packed);
 #define LC_GR(XT, GS, BITS) \
   launch_group_ring<XT, GS, BITS>(static_cast<const XT*>(x), batch, K, codes, scales, biases, N, static_cast<XT*>(y), overlap, scratch, st)
-    if (bits == 4) return x_dtype == LC_BF16 ? LC_GR(__nv_bfloat16, 64, 4) : LC_GR(__half, 64, 4);
+    if (bits == 4) {
+      if (x_dtype == LC_BF16) return group_size == 64 ? LC_GR(__nv_bfloat16, 64, 4) : LC_GR(__nv_bfloat16, 128, 4);
+      return group_size == 64 ? LC_GR(__half, 64, 4) : LC_GR(__half, 128, 4);
+    }
     if (x_dtype == LC_BF16) return group_size == 64 ? LC_GR(__nv_bfloat16, 64, 8) : LC_GR(__nv_bfloat16, 128, 8);
     return group_size == 64 ? LC_GR(__half, 64, 8) : LC_GR(__half, 128, 8);
 #undef LC_GR

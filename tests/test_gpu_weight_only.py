@@ -378,34 +378,36 @@ def test_group_matmul_streaming_kernel(ops, dtype, gs, B, N, K):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("gs", [64, 128])
 @pytest.mark.parametrize("B,N,K", [(1, 14336, 4096), (4, 4096, 14336), (8, 2064, 4160), (9, 4096, 4096), (16, 14336, 4096),
                                    (32, 2064, 4096), (3, 4100, 2176)])
-def test_group_matmul_streaming_kernel_4bit(ops, dtype, B, N, K):
-    """4-bit codes in groups of 64, 4 MB of packed words and more: the streaming kernel, against the oracle's
+def test_group_matmul_streaming_kernel_4bit(ops, dtype, gs, B, N, K):
+    """4-bit codes in groups of 64 or 128, 4 MB of packed words and more: the streaming kernel, against the oracle's
     float64 product of the same packed words, scales and biases within the rounding bound of an
     fp32-accumulated result (|x| * (15 s + |b|) per term), and against the direct kernel, which serves the
     same words below that size; cold and warm launches agree bit for bit."""
-    g = torch.Generator(device="cuda").manual_seed(B + N + K)
+    if K % gs:
+        pytest.skip("K is not a whole number of groups")
+    g = torch.Generator(device="cuda").manual_seed(B + N + K + gs)
     w = torch.randn(N, K, device="cuda", generator=g) * 0.05
-    p, s, b = ops.group_quantize(w, 64, 4)
+    p, s, b = ops.group_quantize(w, gs, 4)
     assert p.shape == (N, K // 8) and N * K // 2 >= 4 << 20
     x = torch.randn(B, K, device="cuda", generator=g).to(dtype)
-    y = ops.group_matmul(x, p, s, b, 64, 4)
+    y = ops.group_matmul(x, p, s, b, gs, 4)
     assert y.dtype == dtype and y.shape == (B, N)
-    ref = O.group_matmul(x.double().cpu().numpy(), p.cpu().numpy(), host(s), host(b), 64, 4)
-    mag = (x.double().abs() @ (15.0 * s.double().repeat_interleave(64, 1) + b.double().abs().repeat_interleave(64, 1)).T)
+    ref = O.group_matmul(x.double().cpu().numpy(), p.cpu().numpy(), host(s), host(b), gs, 4)
+    mag = (x.double().abs() @ (15.0 * s.double().repeat_interleave(gs, 1) + b.double().abs().repeat_interleave(gs, 1)).T)
     assert_rounded_product(y, ref, mag.cpu().numpy(), K, dtype)
-    # every distinct nibble position: one-hot activations pick single columns of a row block
-    rows = min(N, 64)
-    small = ops.group_matmul(x, p[:rows].contiguous(), s[:rows].contiguous(), b[:rows].contiguous(), 64, 4)  # direct kernel
+    rows = min(N, 64)  # a slice this small goes to the direct kernel
+    small = ops.group_matmul(x, p[:rows].contiguous(), s[:rows].contiguous(), b[:rows].contiguous(), gs, 4)
     assert_rounded_product(small, ref[:, :rows], mag[:, :rows].cpu().numpy(), K, dtype)
-    again = ops.group_matmul(x, p, s, b, 64, 4, overlap_previous=True)
+    again = ops.group_matmul(x, p, s, b, gs, 4, overlap_previous=True)
     assert torch.equal(again.view(torch.int16), y.view(torch.int16))
     flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     for i in range(2):
         flush.fill_(i)
         torch.cuda.synchronize()
-        assert torch.equal(ops.group_matmul(x, p, s, b, 64, 4).view(torch.int16), y.view(torch.int16))
+        assert torch.equal(ops.group_matmul(x, p, s, b, gs, 4).view(torch.int16), y.view(torch.int16))
     assert ops.wo_linear_status() == 0
 
 
