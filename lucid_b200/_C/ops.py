@@ -762,8 +762,8 @@ def group_dequantize(packed, scales, biases, group_size: int = 64, bits: int = 8
 
 def group_matmul(x2d, packed, scales, biases, group_size: int = 64, bits: int = 8, overlap_previous: bool = False):
     """``y[b, n] = sum_k x[b, k] * (code[n, k] * scale[n, g] + bias[n, g])`` for the packed group-wise
-    format; ``y`` has ``x``'s dtype.  8-bit weights of 4 MB and more (groups of 64 / 128, bf16 / f16
-    activations) are streamed once through shared memory; ``overlap_previous`` as for
+    format; ``y`` has ``x``'s dtype.  Packed weights of 4 MB and more (8-bit or 4-bit codes in groups of 64 / 128,
+    bf16 / f16 activations) are streamed once through shared memory; ``overlap_previous`` as for
     :func:`wo_linear_s8`."""
     dev = _need_cuda(x2d, packed, scales, biases)
     x2d = x2d.contiguous()

@@ -9,6 +9,7 @@ import torch
 from torch import nn
 
 from lucid_b200 import _backend
+from lucid_b200.nn.quantized.weight_only import _SettledBuffers
 from lucid_b200.quantization._qgemm import quantize, quantized_matmul, wide_group_product
 
 
@@ -29,6 +30,7 @@ class QuantizedLinearMLX(nn.Module):
         else:
             self.bias = None
         self._wide_cache = {}
+        self._settled = _SettledBuffers()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         xd = _backend.on_cuda(x)
@@ -41,6 +43,20 @@ class QuantizedLinearMLX(nn.Module):
             y = y.reshape(*xd.shape[:-1], self.out_features)
             if y.dtype != x.dtype:
                 y = y.to(x.dtype)
+            return y if x.is_cuda else y.to(x.device)
+        if (0 < rows <= 32 and xd.dtype in (torch.bfloat16, torch.float16) and self.packed_weight.is_cuda
+                and not (xd.requires_grad and torch.is_grad_enabled())):
+            # decode batches: the streaming kernel may fetch this layer's weights while the kernel before it on the
+            # stream drains, once the buffers are known to have been complete before that kernel started
+            x2 = xd.reshape(-1, self.in_features)
+            y = _backend.ops().group_matmul(
+                x2, self.packed_weight, self.scales, self.biases, self.group_size, self.bits,
+                overlap_previous=self._settled(self.packed_weight, self.scales, self.biases))
+            y = y.reshape(*xd.shape[:-1], self.out_features)
+            if self.bias is not None:
+                y = y + _backend.on_cuda(self.bias).to(y.dtype)
+            if self.relu:
+                y = torch.relu(y)
             return y if x.is_cuda else y.to(x.device)
         y = quantized_matmul(xd, self.packed_weight, self.scales, self.biases, transpose=True,
                              group_size=self.group_size, bits=self.bits)

@@ -201,7 +201,7 @@ def group_dequantize(packed, scales, biases, group_size=64, bits=8):
     return torch.tensor(O.group_dequantize(_np(packed), _np(scales), _np(biases), group_size, bits))
 
 
-def group_matmul(x2d, packed, scales, biases, group_size=64, bits=8):
+def group_matmul(x2d, packed, scales, biases, group_size=64, bits=8, overlap_previous=False):
     y = O.group_matmul(_np(x2d.float()), _np(packed), _np(scales), _np(biases), group_size, bits)
     return torch.tensor(y).to(x2d.dtype)
 

@@ -483,3 +483,33 @@ def test_group_wide_product_matches_the_decoded_weight(ops, dtype, bits, gs, M, 
     assert m._wide_cache["w"] is not held
     ref2 = torch.relu(x.double() @ ops.group_dequantize(p, m.scales, b, gs, bits).to(dtype).double().T + lin.bias.double())
     assert float((y2.double() - ref2).abs().max()) <= float(ref2.abs().max()) * 4 * eps + 1e-3
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_group_linear_modules_chain_with_launch_overlap(ops, bits):
+    """Two group-wise Linear modules back to back at a decode batch: from the second forward on the modules let
+    each kernel fetch its weights while its predecessor drains; eager and CUDA-graph results stay those of the
+    first forward."""
+    from lucid_b200.nn.quantized.mlx_linear import QuantizedLinearMLX
+
+    torch.manual_seed(bits)
+    up = QuantizedLinearMLX.from_float(torch.nn.Linear(4096, 8192).cuda(), bits=bits, group_size=64, relu=True)
+    down = QuantizedLinearMLX.from_float(torch.nn.Linear(8192, 4096).cuda(), bits=bits, group_size=64)
+    x = (torch.randn(4, 4096, device="cuda") * 0.5).to(torch.bfloat16)
+    first = down(up(x))
+    dense = down(up(x.float())).to(torch.bfloat16)  # fp32 activations: the direct kernel
+    assert float((first.float() - dense.float()).abs().max()) <= 0.02 * float(dense.float().abs().max()) + 1e-3
+    for _ in range(3):
+        assert torch.equal(down(up(x)).view(torch.int16), first.view(torch.int16))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            out = down(up(x))
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), first.view(torch.int16))
+    assert ops.wo_linear_status() == 0
