@@ -448,8 +448,9 @@ int32_t lc_group_matmul(const void* x, int32_t x_dtype, int64_t batch, int64_t K
                         const int32_t* packed, const float* scales, const float* biases,
                         int64_t N, int32_t group_size, int32_t bits, void* y, void* stream);
 /* lc_group_matmul with the flags and scratch of the weight-streaming kernel (LC_WO_OVERLAP_PREVIOUS;
- * lc_wo_linear_workspace_bytes(N), may be NULL).  Packed weights of 4 MB and more -- 8-bit or 4-bit codes
- * in groups of 64 or 128, K a multiple of four groups -- with bf16 / f16 activations are streamed through
+ * lc_wo_linear_workspace_bytes(N), may be NULL).  Packed weights of 4 MB and more (smaller ones from five
+ * rows on) -- 8-bit or 4-bit codes in groups of 64 or 128, K a multiple of four groups -- with bf16 / f16
+ * activations are streamed through
  * shared memory once, like per-channel int8 weights (the packed words are the codes in K order, first
  * code in the low bits); every other case runs the direct kernel. */
 int32_t lc_group_matmul_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K,

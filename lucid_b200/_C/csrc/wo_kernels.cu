@@ -1655,10 +1655,14 @@ extern "C" int32_t lc_group_matmul_ex(const void* x, int32_t x_dtype, int64_t ba
     return fail(LC_ERR_UNSUPPORTED, "group_matmul: x must be 16-byte aligned (packed, scales, biases 4-byte aligned)");
   cudaStream_t st = as_stream(stream);
   const uint32_t* pk = reinterpret_cast<const uint32_t*>(packed);
-  // weights from a few MB up, codes in groups of 64 / 128, 16-bit activations: the streaming kernel
+  // codes in groups of 64 / 128, 16-bit activations: the streaming kernel for packed weights of 4 MB and more,
+  // and for smaller ones from five rows on, where the direct kernel's FP32 multiply-adds take over its time
+  // (measured, N = K = 1024 / 2048, 4-bit codes: 8 rows 6.2 / 10.9 us direct against 4.3 / 5.4 us streamed, 32 rows
+  // 12.6 / 32.8 against 8.8 / 11.9 us; one row 2.9 / 4.8 against 4.2 / 5.2 us)
   const bool stream_ok = (group_size == 64 || group_size == 128) &&
                          (x_dtype == LC_BF16 || x_dtype == LC_F16) && K % (4 * group_size) == 0 &&
-                         N * K * bits >= (int64_t{32} << 20) && aligned(packed, 16) && aligned(x, 16) &&
+                         (N * K * bits >= (int64_t{32} << 20) || (batch >= 5 && N >= 1024 && K >= 1024)) &&
+                         aligned(packed, 16) && aligned(x, 16) &&
                          aligned(scales, 16) && aligned(biases, 16);  // (rows of group parameters in 16-byte steps)
   if (stream_ok) {
     const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;

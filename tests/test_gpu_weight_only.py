@@ -513,3 +513,22 @@ def test_group_linear_modules_chain_with_launch_overlap(ops, bits):
         torch.cuda.synchronize()
         assert torch.equal(out.view(torch.int16), first.view(torch.int16))
     assert ops.wo_linear_status() == 0
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("gs", [64, 128])
+@pytest.mark.parametrize("B,N,K", [(5, 1024, 1024), (8, 1040, 2048), (16, 1024, 1024), (32, 2048, 1024), (4, 1024, 1024)])
+def test_group_matmul_small_matrices_from_five_rows_on(ops, bits, gs, B, N, K):
+    """Packed weights below 4 MB go to the streaming kernel from five rows on (four rows: the direct kernel);
+    either way the result is the oracle's product of the same packed words within the rounding bound."""
+    g = torch.Generator(device="cuda").manual_seed(B + N + K + gs + bits)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.05
+    p, s, b = ops.group_quantize(w, gs, bits)
+    x = torch.randn(B, K, device="cuda", generator=g).to(torch.bfloat16)
+    y = ops.group_matmul(x, p, s, b, gs, bits)
+    ref = O.group_matmul(x.double().cpu().numpy(), p.cpu().numpy(), host(s), host(b), gs, bits)
+    top = float(2 ** bits - 1)
+    mag = (x.double().abs() @ (top * s.double().repeat_interleave(gs, 1) + b.double().abs().repeat_interleave(gs, 1)).T)
+    assert_rounded_product(y, ref, mag.cpu().numpy(), K, torch.bfloat16)
+    assert torch.equal(ops.group_matmul(x, p, s, b, gs, bits, overlap_previous=True).view(torch.int16), y.view(torch.int16))
+    assert ops.wo_linear_status() == 0
