@@ -1660,7 +1660,7 @@ extern "C" int32_t lc_group_matmul_ex(const void* x, int32_t x_dtype, int64_t ba
   // (measured, N = K = 1024 / 2048, 4-bit codes: 8 rows 6.2 / 10.9 us direct against 4.3 / 5.4 us streamed, 32 rows
   // 12.6 / 32.8 against 8.8 / 11.9 us; one row 2.9 / 4.8 against 4.2 / 5.2 us)
   const bool stream_ok = (group_size == 64 || group_size == 128) &&
-                         (x_dtype == LC_BF16 || x_dtype == LC_F16) && K % (4 * group_size) == 0 &&
+                         (x_dtype == LC_BF16 || x_dtype == LC_F16) && K % (4 * group_size) == 0 && K >= ring::KC &&
                          (N * K * bits >= (int64_t{32} << 20) || (batch >= 5 && N >= 1024 && K >= 1024)) &&
                          aligned(packed, 16) && aligned(x, 16) &&
                          aligned(scales, 16) && aligned(biases, 16);  // (rows of group parameters in 16-byte steps)
