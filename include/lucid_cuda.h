@@ -308,7 +308,11 @@ int32_t lc_rowsum_s8(const int8_t* b, int64_t rows, int64_t cols, int64_t ldb, i
  * Replaces the dequantize-then-F.linear forward of the quantized Linear at
  * small batch (lucid/nn/quantized/linear.py:206-214) and is the per-channel
  * counterpart of quantized_matmul_op (lucid/_C/ops/quantized/QuantizedMatmul.cpp:143-207).
- * x_dtype / y dtype: LC_F32, LC_BF16 or LC_F16.
+ * x_dtype / y dtype: LC_F32, LC_BF16 or LC_F16.  bf16 / f16 activations run on the tensor cores
+ * (weights of 4 MB and more streamed through shared memory once); LC_F32 activations are served by plain
+ * FP32 multiply-adds, one warp per output row, meant for up to four rows of a small weight -- from five
+ * rows on, or for weights of tens of MB, call lc_split_f32_digits + lc_wo_gemm_digits instead (exact,
+ * tensor cores: [4096, 4096] at 32 rows 20 us against 557 us), as the host layer does.
  * flags: LC_WO_OVERLAP_PREVIOUS lets the kernel start while the kernel before it on the
  * stream is still draining (programmatic dependent launch): it prefetches weights into
  * shared memory and waits for that kernel before it reads x or writes y.  The caller asserts that wq, sw and bias were completely written before that

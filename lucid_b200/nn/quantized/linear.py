@@ -2,8 +2,9 @@
 int8 weights with a per-channel scale, float input, and the output fake-quantized onto
 the calibrated activation grid.  The reference dequantizes the whole weight on every
 forward, calls a float GEMM and then runs the fake-quantize chain
-(``linear.py:206-214``); here the whole forward is one kernel: decode batches go
-through the weight-only GEMV kernel (the weight is read once as int8), larger ones
+(``linear.py:206-214``); here the whole forward is one kernel: up to four rows of a
+weight below 32 M elements go through the weight-only GEMV kernel (the weight is read
+once as int8), everything else
 through the tensor-core kernel on exact integer arithmetic (``lc_wo_gemm_digits``: the
 fp32 activations as four int8 digit planes, int32 accumulation, one rounding), and in
 both the scale, bias, ReLU and output requantization are the kernel's epilogue.  No
@@ -16,9 +17,9 @@ from torch import nn
 
 from lucid_b200 import _backend
 from lucid_b200.nn.quantized._utils import StaticWeightCache, activation_qparams, quantize_weight, wire_inner
+from lucid_b200.nn.quantized.weight_only import fp32_rows_take_the_gemv
 from lucid_b200.quantization._qscheme import QDtype, quint8
 
-_GEMV_MAX_ROWS = 32
 
 
 class Linear(nn.Module):
@@ -56,7 +57,7 @@ class Linear(nn.Module):
         rows = x2.shape[0]
         if rows == 0:
             y = torch.zeros((0, self.out_features), dtype=torch.float32, device=x2.device)
-        elif rows <= _GEMV_MAX_ROWS and w.gemv_ok:
+        elif w.gemv_ok and fp32_rows_take_the_gemv(rows, wq.numel()):
             y = ops.wo_linear_s8(x2, wq, w.row_scale, bias, **grid)
         else:
             rowsum = None

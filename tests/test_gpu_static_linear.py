@@ -208,9 +208,9 @@ def check_against_oracle(qlin, x, relu):
 
 
 @pytest.mark.parametrize("relu", [False, True])
-@pytest.mark.parametrize("rows", [4, 256])
+@pytest.mark.parametrize("rows", [1, 4, 5, 32, 256])
 def test_static_linear_matches_oracle(relu, rows):
-    """Both routes (GEMV kernel for 4 rows, tensor-core kernel for 256) of Linear and LinearReLU:
+    """Both routes (GEMV kernel for up to 4 rows, tensor-core kernel from 5 on) of Linear and LinearReLU:
     equal to the oracle everywhere except within the fp32 accumulation tolerance of a grid edge,
     where one grid step is allowed."""
     qm, x = calibrated(relu, rows)
@@ -220,7 +220,7 @@ def test_static_linear_matches_oracle(relu, rows):
     assert differ <= edge
 
 
-@pytest.mark.parametrize("rows", [4, 256])
+@pytest.mark.parametrize("rows", [4, 7, 256])
 @pytest.mark.parametrize("ch_axis", [0, 1])
 def test_static_linear_affine_weights(rows, ch_axis):
     """Weight grids with a zero-point (affine weight observer) and scales along the input axis go

@@ -532,3 +532,24 @@ def test_group_matmul_small_matrices_from_five_rows_on(ops, bits, gs, B, N, K):
     assert_rounded_product(y, ref, mag.cpu().numpy(), K, torch.bfloat16)
     assert torch.equal(ops.group_matmul(x, p, s, b, gs, bits, overlap_previous=True).view(torch.int16), y.view(torch.int16))
     assert ops.wo_linear_status() == 0
+
+
+@pytest.mark.parametrize("rows", [1, 4, 5, 17, 32])
+@pytest.mark.parametrize("N,K", [(300, 328), (4096, 1024)])
+def test_weight_only_linear_fp32_activations_route(ops, rows, N, K):
+    """fp32 activations: up to four rows on the FP32 multiply-add kernel, five and more on the exact digit-plane
+    product; both are the float64 product of the same codes within fp32 rounding of the result and of the
+    accumulation."""
+    from lucid_b200.nn.quantized.weight_only import WeightOnlyLinear, fp32_rows_take_the_gemv
+
+    assert fp32_rows_take_the_gemv(4, N * K) and not fp32_rows_take_the_gemv(5, N * K)
+    assert not fp32_rows_take_the_gemv(1, 14336 * 4096)
+    torch.manual_seed(rows + N)
+    m = WeightOnlyLinear.from_float(torch.nn.Linear(K, N).cuda())
+    x = torch.randn(rows, K, device="cuda")
+    y = m(x)
+    assert y.dtype == torch.float32 and y.shape == (rows, N)
+    w = m.weight_int8.double() * m.weight_scale.double()[:, None]
+    ref = x.double() @ w.T + m.bias.double()
+    bound = (x.double().abs() @ w.abs().T) * (K * 2.0 ** -24) + ref.abs() * 2.0 ** -23 + 1e-30
+    assert bool(((y.double() - ref).abs() <= bound).all())
