@@ -99,8 +99,11 @@ class WeightOnlyLinear(nn.Module):
         xd = _backend.on_cuda(x)
         x2 = xd.reshape(-1, self.in_features)
         rows = x2.shape[0]
+        # (16-bit activations reach the tensor-core GEMV kernels only with rows of K % 16 == 0; other K are served
+        # by the same multiply-add kernel as fp32)
+        on_tensor_cores = x2.dtype in (torch.bfloat16, torch.float16) and self.in_features % 16 == 0
         gemv = 0 < rows <= _GEMV_MAX_ROWS and (
-            x2.dtype != torch.float32 or fp32_rows_take_the_gemv(rows, self.weight_int8.numel()))
+            on_tensor_cores or fp32_rows_take_the_gemv(rows, self.weight_int8.numel()))
         if gemv:
             y = _backend.ops().wo_linear_s8(
                 x2, self.weight_int8, self.weight_scale, self.bias,

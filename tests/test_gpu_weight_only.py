@@ -553,3 +553,24 @@ def test_weight_only_linear_fp32_activations_route(ops, rows, N, K):
     ref = x.double() @ w.T + m.bias.double()
     bound = (x.double().abs() @ w.abs().T) * (K * 2.0 ** -24) + ref.abs() * 2.0 ** -23 + 1e-30
     assert bool(((y.double() - ref).abs() <= bound).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows", [3, 9, 32])
+@pytest.mark.parametrize("N,K", [(520, 1000), (300, 1001)])
+def test_weight_only_linear_rows_of_odd_length(ops, dtype, rows, N, K):
+    """K that is not a multiple of 16 keeps 16-bit activations off the tensor-core GEMV kernels too: few rows on
+    the multiply-add kernel, more on the wide products; the result is the float64 product within the rounding of
+    the activation type."""
+    from lucid_b200.nn.quantized.weight_only import WeightOnlyLinear
+
+    torch.manual_seed(rows + K)
+    m = WeightOnlyLinear.from_float(torch.nn.Linear(K, N).cuda())
+    x = torch.randn(rows, K, device="cuda").to(dtype)
+    y = m(x)
+    assert y.dtype == dtype and y.shape == (rows, N)
+    w = m.weight_int8.double() * m.weight_scale.double()[:, None]
+    ref = x.double() @ w.T + m.bias.double()
+    eps = 2.0 ** -8 if dtype is torch.bfloat16 else 2.0 ** -23
+    bound = (x.double().abs() @ w.abs().T) * (K * 2.0 ** -24) + ref.abs() * eps + 1e-6
+    assert bool(((y.double() - ref).abs() <= bound).all())
