@@ -457,6 +457,11 @@ int32_t lc_group_matmul(const void* x, int32_t x_dtype, int64_t batch, int64_t K
  * activations are streamed through
  * shared memory once, like per-channel int8 weights (the packed words are the codes in K order, first
  * code in the low bits); every other case runs the direct kernel. */
+/* flag of lc_group_matmul_ex: x is LC_BF16 and y receives fp32 (row pitch N floats).  For fp32 activations on
+ * the streaming kernel: lc_split_f32_bf16x3 writes every fp32 row as three bf16 rows that add up to it exactly,
+ * this call multiplies the 3 * batch rows, and the caller adds each row's three results.  Refused
+ * (LC_ERR_UNSUPPORTED) where the streaming kernel does not apply. */
+#define LC_GROUP_OUT_F32 2
 int32_t lc_group_matmul_ex(const void* x, int32_t x_dtype, int64_t batch, int64_t K,
                            const int32_t* packed, const float* scales, const float* biases,
                            int64_t N, int32_t group_size, int32_t bits, void* y, int32_t flags,

@@ -429,7 +429,11 @@ __device__ __forceinline__ int ring_owner(long long u, long long units, int grid
 // bytes that hold its 16 codes, masks out code pairs (c0, c4), (c1, c5), (c2, c6), (c3, c7) of each word
 // -- a nibble in the low bits of a 16-bit half is the raw operand pattern as it stands -- and its
 // activation fragments are permuted once per chunk to match.
-template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0, int CW = 16, int BITS = 8>
+// YF32: the result is written as fp32 although the activations are 16-bit (`y` then points to floats, `ldy` counts
+// floats): what a caller needs who hands in an fp32 activation as bf16 addends in separate rows and adds the
+// rows of the result up afterwards.
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0, int CW = 16, int BITS = 8,
+          bool YF32 = false>
 __global__ void __launch_bounds__(ring::threads(CW), ring::ctas_per_sm(CW))
 wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w1,
                       const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_gs,
@@ -459,6 +463,7 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   constexpr int TSTAGE = STAGE * BITS / 8;  // bytes of one 16-row tile of an item
   constexpr int GSTAGE = TSTAGE * GRP;
   static_assert(BITS == 8 || (BITS == 4 && GS != 0), "4-bit codes come in the group-wise format only");
+  static_assert(!YF32 || (GS != 0 && !SWIGLU), "fp32 results of 16-bit activations: group-wise format only");
   static_assert(S >= 3, "ring too shallow");
   static_assert(GRP == 1 || (GRP == 2 && TMAX % 2 == 0), "one or two row tiles per box");
   constexpr int COLS = NT * 8, RP = red_pitch(NT, CW);
@@ -1052,7 +1057,10 @@ wo_linear_ring_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                   v = __fmul_rn(v, p_scale[i][0]);
                   if (bias) v = __fadd_rn(v, p_bias[i][0]);
                 }
-                y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(wo_finish(v, epi));
+                if constexpr (YF32)
+                  reinterpret_cast<float*>(y)[static_cast<int64_t>(bcol) * ldy + n] = wo_finish(v, epi);
+                else
+                  y[static_cast<int64_t>(bcol) * ldy + n] = from_float<XT>(wo_finish(v, epi));
               }
             }
           }
@@ -1278,12 +1286,13 @@ struct RingScratch {
 };
 constexpr int64_t kRingSlotBytes = 16 * 32 * 4;  // 16 rows * largest COLS floats
 
-template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0, int CW = 16, int BITS = 8>
+template <typename XT, int NT, int TMAX, int XB, bool SWIGLU, int GRP, int GS = 0, int CW = 16, int BITS = 8,
+          bool YF32 = false>
 static int32_t launch_wo_ring_inst(const XT* x, int64_t B, int64_t K, int64_t ldx, const int8_t* w,
                                    int64_t ldw, int64_t N, const float* sw, const float* bias, XT* y,
                                    int64_t ldy, bool overlap, const WoEpilogue& epi, const RingScratch& scratch,
                                    cudaStream_t st) {
-  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU, GRP, GS, CW, BITS>;
+  auto kernel = wo_linear_ring_kernel<XT, NT, TMAX, XB, SWIGLU, GRP, GS, CW, BITS, YF32>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
   int dev = 0;
@@ -1456,7 +1465,7 @@ static int32_t launch_group_matmul(const XT* x, int64_t B, int64_t K, const uint
 // in groups of 64 or 128): the packed words are the codes in K order, so the
 // weight is streamed exactly like a per-channel int8 matrix -- an item row of 1024 elements being 1024 or
 // 512 bytes -- and the group scales / biases are read by the consumer warps.
-template <typename XT, int GS, int BITS>
+template <typename XT, int GS, int BITS, bool YF32 = false>
 static int32_t launch_group_ring(const XT* x, int64_t B, int64_t K, const uint8_t* codes, const float* scales,
                                  const float* biases, int64_t N, XT* y, bool overlap, const RingScratch& scratch,
                                  cudaStream_t st) {
@@ -1464,35 +1473,39 @@ static int32_t launch_group_ring(const XT* x, int64_t B, int64_t K, const uint8_
   const int8_t* w = reinterpret_cast<const int8_t*>(codes);
   const int64_t tiles = (N + 15) / 16, sms = sm_count();
   const bool few = (tiles + sms - 1) / sms <= 2;
+  // row r of the result (fp32 results: `y` points to floats)
+  auto yrow = [&](int64_t r) {
+    return YF32 ? reinterpret_cast<XT*>(reinterpret_cast<float*>(y) + r * N) : y + r * N;
+  };
   for (int64_t b0 = 0; b0 < B; b0 += 32) {
     const int64_t bc = B - b0 < 32 ? B - b0 : 32;
     const XT* xb = x + b0 * K;
-    XT* yb = y + b0 * N;
+    XT* yb = yrow(b0);
     int32_t rc;
     if constexpr (BITS == 4) {
       // 16 KB boxes of two row tiles; up to 8 rows on two half-size CTAs per SM, 9..16 with the activations
       // staged in shared memory, more as two such passes
       (void)few;
       if (bc <= 8) {
-        rc = launch_wo_ring_inst<XT, 1, 4, 0, false, 2, GS, 8, 4>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+        rc = launch_wo_ring_inst<XT, 1, 4, 0, false, 2, GS, 8, 4, YF32>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
       } else {
         const int64_t first = bc < 16 ? bc : 16;
-        rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 2, GS, 16, 4>(xb, first, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+        rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 2, GS, 16, 4, YF32>(xb, first, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
         if (!rc && bc > 16)
-          rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 2, GS, 16, 4>(xb + 16 * K, bc - 16, K, K, w, K, N, scales, biases, yb + 16 * N, N,
-                                                                     true, none, scratch, st);
+          rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 2, GS, 16, 4, YF32>(xb + 16 * K, bc - 16, K, K, w, K, N, scales, biases, yrow(b0 + 16), N,
+                                                                           true, none, scratch, st);
       }
     } else if (bc <= 8)  // two half-size CTAs per SM, passes of four tiles in 16-row boxes, four deep (measured: 19.7 us on
                          // [14336, 4096] at group size 64 against 22.5 us with passes of two tiles in 32-row boxes)
-      rc = launch_wo_ring_inst<XT, 1, 4, 0, false, 1, GS, 8>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+      rc = launch_wo_ring_inst<XT, 1, 4, 0, false, 1, GS, 8, 8, YF32>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
     else if (bc <= 16)
-      rc = few ? launch_wo_ring_inst<XT, 2, 2, 3, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
-               : launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+      rc = few ? launch_wo_ring_inst<XT, 2, 2, 3, false, 1, GS, 16, 8, YF32>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st)
+               : launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS, 16, 8, YF32>(xb, bc, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
     else {  // two passes with at most 16 rows each, as for per-channel weights
-      rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS>(xb, 16, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
+      rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS, 16, 8, YF32>(xb, 16, K, K, w, K, N, scales, biases, yb, N, overlap, none, scratch, st);
       if (!rc)
-        rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS>(xb + 16 * K, bc - 16, K, K, w, K, N, scales, biases, yb + 16 * N, N,
-                                                            true, none, scratch, st);
+        rc = launch_wo_ring_inst<XT, 2, 4, 2, false, 1, GS, 16, 8, YF32>(xb + 16 * K, bc - 16, K, K, w, K, N, scales, biases, yrow(b0 + 16), N,
+                                                                         true, none, scratch, st);
     }
     if (rc) return rc;
   }
@@ -1664,12 +1677,24 @@ extern "C" int32_t lc_group_matmul_ex(const void* x, int32_t x_dtype, int64_t ba
                          (N * K * bits >= (int64_t{32} << 20) || (batch >= 5 && N >= 1024 && K >= 1024)) &&
                          aligned(packed, 16) && aligned(x, 16) &&
                          aligned(scales, 16) && aligned(biases, 16);  // (rows of group parameters in 16-byte steps)
+  const bool out_f32 = (flags & LC_GROUP_OUT_F32) != 0;
+  if (out_f32 && !(stream_ok && x_dtype == LC_BF16))
+    return fail(LC_ERR_UNSUPPORTED, "group_matmul: fp32 results of bf16 activations are written by the streaming kernel only "
+                                    "(packed weights of 4 MB and more, groups of 64 / 128, K a multiple of four groups)");
   if (stream_ok) {
     const bool overlap = (flags & LC_WO_OVERLAP_PREVIOUS) != 0;
     const RingScratch scratch = {workspace, workspace ? workspace_bytes : 0};
     const uint8_t* codes = reinterpret_cast<const uint8_t*>(packed);
 #define LC_GR(XT, GS, BITS) \
   launch_group_ring<XT, GS, BITS>(static_cast<const XT*>(x), batch, K, codes, scales, biases, N, static_cast<XT*>(y), overlap, scratch, st)
+#define LC_GRF(GS, BITS) \
+  launch_group_ring<__nv_bfloat16, GS, BITS, true>(static_cast<const __nv_bfloat16*>(x), batch, K, codes, scales, biases, N, \
+                                                   static_cast<__nv_bfloat16*>(y), overlap, scratch, st)
+    if (out_f32) {
+      if (bits == 4) return group_size == 64 ? LC_GRF(64, 4) : LC_GRF(128, 4);
+      return group_size == 64 ? LC_GRF(64, 8) : LC_GRF(128, 8);
+    }
+#undef LC_GRF
     if (bits == 4) {
       if (x_dtype == LC_BF16) return group_size == 64 ? LC_GR(__nv_bfloat16, 64, 4) : LC_GR(__nv_bfloat16, 128, 4);
       return group_size == 64 ? LC_GR(__half, 64, 4) : LC_GR(__half, 128, 4);

@@ -760,6 +760,17 @@ def group_dequantize(packed, scales, biases, group_size: int = 64, bits: int = 8
     return out
 
 
+LC_GROUP_OUT_F32 = 2
+
+
+def group_fp32_rows_stream(dtype, rows: int, n: int, k: int, group_size: int, bits: int) -> bool:
+    """Whether fp32 activations go through the streaming kernel as bf16 addends: packed weights of 4 MB and more
+    in a layout that kernel takes.  The direct kernel's FP32 multiply-adds need 46 / 101 / 240 / 489 us for
+    1 / 4 / 16 / 32 rows against ``[14336, 4096]`` 8-bit codes; the three-addend form 23 / 29 / 72 / 135 us."""
+    return (dtype is torch.float32 and 0 < rows <= 32 and n * k * bits >= (32 << 20) and group_size in (64, 128)
+            and k % (4 * group_size) == 0 and k >= 1024)
+
+
 def group_matmul(x2d, packed, scales, biases, group_size: int = 64, bits: int = 8, overlap_previous: bool = False):
     """``y[b, n] = sum_k x[b, k] * (code[n, k] * scale[n, g] + bias[n, g])`` for the packed group-wise
     format; ``y`` has ``x``'s dtype.  Packed weights of 4 MB and more (8-bit or 4-bit codes in groups of 64 / 128,
@@ -774,8 +785,19 @@ def group_matmul(x2d, packed, scales, biases, group_size: int = 64, bits: int = 
     N = packed.shape[0]
     if packed.shape[1] * 32 // bits != K:
         raise ValueError("group_matmul: packed weight does not match x's inner dimension")
-    y = torch.empty((B, N), dtype=x2d.dtype, device=dev)
     sc, bi = _f32c(scales), _f32c(biases)
+    if group_fp32_rows_stream(x2d.dtype, B, N, K, group_size, bits):
+        # fp32 activations against a large packed weight: every row as three bf16 rows that add up to it exactly
+        # (rows 3 b .. 3 b + 2 of the [3 B, K] view), one pass of the streaming kernel with fp32 results, and the
+        # three results of a row added up
+        terms, _ = split_f32_bf16x3(x2d)
+        y3 = torch.empty((3 * B, N), dtype=torch.float32, device=dev)
+        with _on(dev):
+            check(_group_matmul_ex(terms.data_ptr(), LC_BF16, 3 * B, K, packed.data_ptr(), sc.data_ptr(), bi.data_ptr(), N,
+                                   group_size, bits, y3.data_ptr(), LC_GROUP_OUT_F32 | (1 if overlap_previous else 0),
+                                   None, 0, _stream(dev)))
+        return y3.view(B, 3, N).sum(1)
+    y = torch.empty((B, N), dtype=x2d.dtype, device=dev)
     with _on(dev):
         ws = None  # whole boxes per CTA: measured faster than the K-cutting schedule
         check(_group_matmul_ex(x2d.data_ptr(), _lc_dtype(x2d.dtype), B, K, packed.data_ptr(), sc.data_ptr(),

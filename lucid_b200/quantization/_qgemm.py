@@ -108,7 +108,8 @@ def quantized_matmul(x, wq, scales, biases, transpose: bool = True, group_size: 
             and scales.dtype is torch.float32 and scales.is_contiguous() and biases.dtype is torch.float32
             and biases.is_contiguous() and x.device == wq.device == scales.device == biases.device
             and x.device.index == torch.cuda.current_device() and x.dtype in _FLOATS
-            and wq.shape[1] * 32 // bits == x.shape[1]):
+            and wq.shape[1] * 32 // bits == x.shape[1]
+            and not (x.dtype is torch.float32 and wq.numel() >= (1 << 20))):  # (large weights, fp32 rows: see group_matmul)
         # decode-time dispatch: everything the general path would normalise is already in place
         lean = getattr(_backend.ops(), "group_matmul_lean", None)
         if lean is not None:

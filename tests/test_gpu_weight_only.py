@@ -574,3 +574,32 @@ def test_weight_only_linear_rows_of_odd_length(ops, dtype, rows, N, K):
     eps = 2.0 ** -8 if dtype is torch.bfloat16 else 2.0 ** -23
     bound = (x.double().abs() @ w.abs().T) * (K * 2.0 ** -24) + ref.abs() * eps + 1e-6
     assert bool(((y.double() - ref).abs() <= bound).all())
+
+
+@pytest.mark.parametrize("bits,gs", [(8, 64), (4, 64), (8, 128), (4, 128)])
+@pytest.mark.parametrize("B,N,K", [(1, 14336, 4096), (4, 4096, 14336), (11, 8200, 4096), (32, 4096, 8192)])
+def test_group_matmul_fp32_rows_on_the_streaming_kernel(ops, bits, gs, B, N, K):
+    """fp32 activations against a packed weight of 4 MB and more: three bf16 addends per row through the streaming
+    kernel with fp32 results.  The addends are exact, so the result is the oracle's float64 product within fp32
+    accumulation error -- tighter than what a single 16-bit rounding of the activations would allow -- and the
+    module and the functional entry point take the same route."""
+    from lucid_b200._C.ops import group_fp32_rows_stream
+    from lucid_b200.quantization import _qgemm
+
+    assert group_fp32_rows_stream(torch.float32, B, N, K, gs, bits)
+    assert not group_fp32_rows_stream(torch.float32, B, 1024, 1024, gs, bits)
+    g = torch.Generator(device="cuda").manual_seed(B + N + K + gs + bits)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.05
+    p, s, b = ops.group_quantize(w, gs, bits)
+    x = torch.randn(B, K, device="cuda", generator=g)
+    y = ops.group_matmul(x, p, s, b, gs, bits)
+    assert y.dtype == torch.float32 and y.shape == (B, N)
+    ref = O.group_matmul(x.double().cpu().numpy(), p.cpu().numpy(), host(s), host(b), gs, bits)
+    top = float(2 ** bits - 1)
+    mag = (x.double().abs() @ (top * s.double().repeat_interleave(gs, 1) + b.double().abs().repeat_interleave(gs, 1)).T)
+    err = np.abs(host(y).astype(np.float64) - ref)
+    assert (err <= mag.cpu().numpy() * (K * 2.0 ** -24) + np.abs(ref) * 2.0 ** -22).all()
+    assert float(err.max()) <= 2e-6 * float(mag.max())  # far inside a 16-bit rounding of x (2^-9)
+    assert torch.equal(_qgemm.quantized_matmul(x, p, s, b, transpose=True, group_size=gs, bits=bits), y)
+    assert torch.equal(ops.group_matmul(x, p, s, b, gs, bits, overlap_previous=True), y)
+    assert ops.wo_linear_status() == 0
