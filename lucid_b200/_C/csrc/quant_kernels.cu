@@ -356,6 +356,96 @@ dequantize_strided_kernel(const InT* __restrict__ q, OutT* __restrict__ out, int
   }
 }
 
+// ---- short inner extents (channel axis last, or a few elements per channel) --------------
+// The tensor is [outer][L = channels * inner]: column j belongs to channel j / inner.  A thread owns
+// four adjacent columns, loads their parameters once and walks down kColsRows rows; a warp reads 512
+// contiguous bytes per row and nothing is divided per element (the element-wise kernels below spend
+// their time on a 64-bit divide and modulo per element: 1.3 TB/s on an [8192, 8192] tensor with the
+// channel axis last).
+constexpr int kColsRows = 16;  // rows per CTA
+
+struct ColumnWalk {
+  int64_t j, r0, r1;
+  bool live;
+};
+__device__ __forceinline__ ColumnWalk column_walk(int64_t outer, int64_t L) {
+  ColumnWalk w;
+  w.j = (static_cast<int64_t>(blockIdx.y) * kThreads + threadIdx.x) * 4;
+  w.r0 = static_cast<int64_t>(blockIdx.x) * kColsRows;
+  w.r1 = w.r0 + kColsRows < outer ? w.r0 + kColsRows : outer;
+  w.live = w.j < L;
+  return w;
+}
+__device__ __forceinline__ void load_params4(const ChannelParams& p, int64_t j, int64_t inner, float (&s)[4],
+                                             float (&inv)[4], float (&z)[4]) {
+  const int64_t c = j / inner;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) load_params(p, inner == 1 ? c + i : (j + i) / inner, s[i], inv[i], z[i]);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads)
+quantize_cols_kernel(const float* __restrict__ x, OutT* __restrict__ out, int64_t outer, int64_t L,
+                     int64_t inner, ChannelParams p, float qmin, float qmax) {
+  const ColumnWalk w = column_walk(outer, L);
+  if (!w.live) return;
+  float s[4], inv[4], z[4];
+  load_params4(p, w.j, inner, s, inv, z);
+  for (int64_t r = w.r0; r < w.r1; r += kUnroll) {
+    float4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (r + u < w.r1) v[u] = __ldcs(reinterpret_cast<const float4*>(x + (r + u) * L + w.j));
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (r + u < w.r1)
+        store4<OutT>(out + (r + u) * L + w.j, code_to_int(grid_code(v[u].x, inv[0], z[0]), qmin, qmax),
+                     code_to_int(grid_code(v[u].y, inv[1], z[1]), qmin, qmax),
+                     code_to_int(grid_code(v[u].z, inv[2], z[2]), qmin, qmax),
+                     code_to_int(grid_code(v[u].w, inv[3], z[3]), qmin, qmax));
+  }
+}
+
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(kThreads)
+dequantize_cols_kernel(const InT* __restrict__ q, OutT* __restrict__ out, int64_t outer, int64_t L,
+                       int64_t inner, ChannelParams p) {
+  const ColumnWalk w = column_walk(outer, L);
+  if (!w.live) return;
+  float s[4], inv[4], z[4];
+  load_params4(p, w.j, inner, s, inv, z);
+  for (int64_t r = w.r0; r < w.r1; r += kUnroll) {
+    int a[kUnroll][4];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (r + u < w.r1) load4<InT>(q + (r + u) * L + w.j, a[u][0], a[u][1], a[u][2], a[u][3]);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (r + u < w.r1) {
+        OutT* o = out + (r + u) * L + w.j;
+        const float r0 = dequant_one(a[u][0], s[0], z[0]), r1 = dequant_one(a[u][1], s[1], z[1]);
+        const float r2 = dequant_one(a[u][2], s[2], z[2]), r3 = dequant_one(a[u][3], s[3], z[3]);
+        if (sizeof(OutT) == 4) {
+          __stcs(reinterpret_cast<float4*>(o), make_float4(r0, r1, r2, r3));
+        } else {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(r0, r1), hi = __floats2bfloat162_rn(r2, r3);
+          uint2 pk;
+          pk.x = *reinterpret_cast<unsigned int*>(&lo);
+          pk.y = *reinterpret_cast<unsigned int*>(&hi);
+          *reinterpret_cast<uint2*>(o) = pk;
+        }
+      }
+  }
+}
+
+// whether the column kernels apply, and their grid: rows in x (no 65535 limit), column blocks in y
+static bool columns_ok(int64_t outer, int64_t L, dim3* grid) {
+  const int64_t col_blocks = (L / 4 + kThreads - 1) / kThreads, row_blocks = (outer + kColsRows - 1) / kColsRows;
+  if (L % 4 != 0 || outer < 4 || col_blocks > 65535 || row_blocks > 0x7fffffffLL) return false;
+  *grid = dim3(static_cast<unsigned>(row_blocks), static_cast<unsigned>(col_blocks));
+  return true;
+}
+
 // (clip(code) - z) * s and the straight-through mask
 // (lucid/quantization/_functional.py:326-333)
 __device__ __forceinline__ float fake_one(float x, float s, float inv, float z, float qmin,
@@ -474,6 +564,32 @@ fake_quantize_strided_kernel(const float* __restrict__ x, float* __restrict__ ou
     load_params(p, (e / inner) % channels, s, inv, z);
     out[e] = fake_one(__ldg(x + e), s, inv, z, qmin, qmax, m);
     if (mask_out) mask_out[e] = m;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+fake_quantize_cols_kernel(const float* __restrict__ x, float* __restrict__ out, float* __restrict__ mask_out,
+                          int64_t outer, int64_t L, int64_t inner, ChannelParams p, float qmin, float qmax) {
+  const ColumnWalk w = column_walk(outer, L);
+  if (!w.live) return;
+  float s[4], inv[4], z[4];
+  load_params4(p, w.j, inner, s, inv, z);
+  for (int64_t r = w.r0; r < w.r1; r += kUnroll) {
+    float4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (r + u < w.r1) v[u] = __ldcs(reinterpret_cast<const float4*>(x + (r + u) * L + w.j));
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (r + u < w.r1) {
+        float4 m, o;
+        o.x = fake_one(v[u].x, s[0], inv[0], z[0], qmin, qmax, m.x);
+        o.y = fake_one(v[u].y, s[1], inv[1], z[1], qmin, qmax, m.y);
+        o.z = fake_one(v[u].z, s[2], inv[2], z[2], qmin, qmax, m.z);
+        o.w = fake_one(v[u].w, s[3], inv[3], z[3], qmin, qmax, m.w);
+        __stcs(reinterpret_cast<float4*>(out + (r + u) * L + w.j), o);
+        if (mask_out) __stcs(reinterpret_cast<float4*>(mask_out + (r + u) * L + w.j), m);
+      }
   }
 }
 
@@ -747,9 +863,13 @@ static int32_t launch_quantize(const float* x, int64_t outer, int64_t channels, 
       quantize_seg_kernel<OutT, false><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(
           x, out, channels, inner, in_stride, out_stride, cps, p, qmin, qmax, reverse);
   } else {
-    const int64_t total = segs * inner;
-    quantize_strided_kernel<OutT><<<strided_grid(total), kThreads, 0, st>>>(x, out, total, channels,
-                                                                           inner, p, qmin, qmax);
+    const int64_t total = segs * inner, L = channels * inner;
+    dim3 grid;
+    if (columns_ok(outer, L, &grid) && aligned(x, 16) && aligned(out, 4 * sizeof(OutT)))
+      quantize_cols_kernel<OutT><<<grid, kThreads, 0, st>>>(x, out, outer, L, inner, p, qmin, qmax);
+    else
+      quantize_strided_kernel<OutT><<<strided_grid(total), kThreads, 0, st>>>(x, out, total, channels,
+                                                                             inner, p, qmin, qmax);
   }
   return check_launch("quantize");
 }
@@ -771,9 +891,13 @@ static int32_t launch_dequantize(const InT* q, int64_t outer, int64_t channels, 
       dequantize_seg_kernel<InT, OutT, false>
           <<<static_cast<unsigned>(grid), kThreads, 0, st>>>(q, out, channels, inner, cps, p);
   } else {
-    const int64_t total = segs * inner;
-    dequantize_strided_kernel<InT, OutT>
-        <<<strided_grid(total), kThreads, 0, st>>>(q, out, total, channels, inner, p);
+    const int64_t total = segs * inner, L = channels * inner;
+    dim3 grid;
+    if (columns_ok(outer, L, &grid) && aligned(q, 4 * sizeof(InT)) && aligned(out, 4 * sizeof(OutT)))
+      dequantize_cols_kernel<InT, OutT><<<grid, kThreads, 0, st>>>(q, out, outer, L, inner, p);
+    else
+      dequantize_strided_kernel<InT, OutT>
+          <<<strided_grid(total), kThreads, 0, st>>>(q, out, total, channels, inner, p);
   }
   return check_launch("dequantize");
 }
@@ -1099,9 +1223,13 @@ extern "C" int32_t lc_fake_quantize_f32(const float* x, int64_t outer, int64_t c
       fake_quantize_seg_kernel<false><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(
           x, out, mask_out, channels, inner, cps, p, qmin, qmax);
   } else {
-    const int64_t total = segs * inner;
-    fake_quantize_strided_kernel<<<strided_grid(total), kThreads, 0, st>>>(
-        x, out, mask_out, total, channels, inner, p, qmin, qmax);
+    const int64_t total = segs * inner, L = channels * inner;
+    dim3 grid;
+    if (columns_ok(outer, L, &grid) && aligned(x, 16) && aligned(out, 16) && (!mask_out || aligned(mask_out, 16)))
+      fake_quantize_cols_kernel<<<grid, kThreads, 0, st>>>(x, out, mask_out, outer, L, inner, p, qmin, qmax);
+    else
+      fake_quantize_strided_kernel<<<strided_grid(total), kThreads, 0, st>>>(
+          x, out, mask_out, total, channels, inner, p, qmin, qmax);
   }
   return check_launch("fake_quantize");
 }

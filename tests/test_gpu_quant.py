@@ -111,7 +111,11 @@ def test_running_observers(ops):
 
 @pytest.mark.parametrize("shape,axis", [((7,), None), ((1, 1), None), ((129, 513), None), ((4096, 1024), 0),
                                         ((3, 5, 7), 1), ((2, 300, 130), 1), ((64, 4100), 0), ((70, 9), 1),
-                                        ((1000, 1003), 0), ((16, 8192), 0), ((5, 16388), 0)])
+                                        ((1000, 1003), 0), ((16, 8192), 0), ((5, 16388), 0),
+                                        # channel axis last / short inner extents: the column kernels (rows of
+                                        # channels * inner elements, a multiple of 4, at least 4 of them)
+                                        ((70, 12), 1), ((37, 1024), 1), ((5, 7, 9, 64), 3), ((6, 20, 6), 1),
+                                        ((33, 8, 2), 1), ((3, 16), 1), ((2000, 260), 1), ((4, 2052), 1)])
 @pytest.mark.parametrize("qd", ["qint8", "quint8", "qint4", "qint8_narrow"])
 def test_quantize_dequantize_matches_oracle(ops, shape, axis, qd):
     qdt = getattr(O, qd)
