@@ -438,10 +438,16 @@ dequantize_cols_kernel(const InT* __restrict__ q, OutT* __restrict__ out, int64_
   }
 }
 
-// whether the column kernels apply, and their grid: rows in x (no 65535 limit), column blocks in y
-static bool columns_ok(int64_t outer, int64_t L, dim3* grid) {
+// whether the column kernels apply, and their grid: rows in x (no 65535 limit), column blocks in y.
+// Below kSegModeMinInner elements per channel they replace the element-wise kernels; up to 2048 they replace
+// the segment kernels too when there are rows to walk down (a segment kernel's CTA of 4096 slots holds one
+// segment: [32, 4096, 1024] ran at 3.0 TB/s).
+static bool columns_ok(int64_t outer, int64_t channels, int64_t inner, dim3* grid) {
+  const int64_t L = channels * inner;
   const int64_t col_blocks = (L / 4 + kThreads - 1) / kThreads, row_blocks = (outer + kColsRows - 1) / kColsRows;
-  if (L % 4 != 0 || outer < 4 || col_blocks > 65535 || row_blocks > 0x7fffffffLL) return false;
+  if (channels == 1) return false;  // one set of parameters: the segment kernels
+  if (L % 4 != 0 || col_blocks > 65535 || row_blocks > 0x7fffffffLL) return false;
+  if (inner < kSegModeMinInner ? outer < 4 : (inner >= 2048 || outer < 8)) return false;
   *grid = dim3(static_cast<unsigned>(row_blocks), static_cast<unsigned>(col_blocks));
   return true;
 }
@@ -850,7 +856,10 @@ static int32_t launch_quantize(const float* x, int64_t outer, int64_t channels, 
   const int64_t segs = outer * channels;
   if (segs == 0 || inner == 0) return LC_OK;
   const bool dense = (in_stride == inner && out_stride == inner);
-  if (inner >= kSegModeMinInner || channels == 1 || !dense) {
+  dim3 cgrid;
+  if (dense && columns_ok(outer, channels, inner, &cgrid) && aligned(x, 16) && aligned(out, 4 * sizeof(OutT))) {
+    quantize_cols_kernel<OutT><<<cgrid, kThreads, 0, st>>>(x, out, outer, channels * inner, inner, p, qmin, qmax);
+  } else if (inner >= kSegModeMinInner || channels == 1 || !dense) {
     const int cps = chunks_for(inner);
     const int64_t grid = segs * cps;
     if (grid > 0x7fffffffLL) return fail(LC_ERR_UNSUPPORTED, "tensor too large for one launch");
@@ -863,13 +872,9 @@ static int32_t launch_quantize(const float* x, int64_t outer, int64_t channels, 
       quantize_seg_kernel<OutT, false><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(
           x, out, channels, inner, in_stride, out_stride, cps, p, qmin, qmax, reverse);
   } else {
-    const int64_t total = segs * inner, L = channels * inner;
-    dim3 grid;
-    if (columns_ok(outer, L, &grid) && aligned(x, 16) && aligned(out, 4 * sizeof(OutT)))
-      quantize_cols_kernel<OutT><<<grid, kThreads, 0, st>>>(x, out, outer, L, inner, p, qmin, qmax);
-    else
-      quantize_strided_kernel<OutT><<<strided_grid(total), kThreads, 0, st>>>(x, out, total, channels,
-                                                                             inner, p, qmin, qmax);
+    const int64_t total = segs * inner;
+    quantize_strided_kernel<OutT><<<strided_grid(total), kThreads, 0, st>>>(x, out, total, channels,
+                                                                           inner, p, qmin, qmax);
   }
   return check_launch("quantize");
 }
@@ -879,7 +884,10 @@ static int32_t launch_dequantize(const InT* q, int64_t outer, int64_t channels, 
                                  const ChannelParams& p, OutT* out, cudaStream_t st) {
   const int64_t segs = outer * channels;
   if (segs == 0 || inner == 0) return LC_OK;
-  if (inner >= kSegModeMinInner || channels == 1) {
+  dim3 cgrid;
+  if (columns_ok(outer, channels, inner, &cgrid) && aligned(q, 4 * sizeof(InT)) && aligned(out, 4 * sizeof(OutT))) {
+    dequantize_cols_kernel<InT, OutT><<<cgrid, kThreads, 0, st>>>(q, out, outer, channels * inner, inner, p);
+  } else if (inner >= kSegModeMinInner || channels == 1) {
     const int cps = chunks_for(inner);
     const int64_t grid = segs * cps;
     if (grid > 0x7fffffffLL) return fail(LC_ERR_UNSUPPORTED, "tensor too large for one launch");
@@ -891,13 +899,9 @@ static int32_t launch_dequantize(const InT* q, int64_t outer, int64_t channels, 
       dequantize_seg_kernel<InT, OutT, false>
           <<<static_cast<unsigned>(grid), kThreads, 0, st>>>(q, out, channels, inner, cps, p);
   } else {
-    const int64_t total = segs * inner, L = channels * inner;
-    dim3 grid;
-    if (columns_ok(outer, L, &grid) && aligned(q, 4 * sizeof(InT)) && aligned(out, 4 * sizeof(OutT)))
-      dequantize_cols_kernel<InT, OutT><<<grid, kThreads, 0, st>>>(q, out, outer, L, inner, p);
-    else
-      dequantize_strided_kernel<InT, OutT>
-          <<<strided_grid(total), kThreads, 0, st>>>(q, out, total, channels, inner, p);
+    const int64_t total = segs * inner;
+    dequantize_strided_kernel<InT, OutT>
+        <<<strided_grid(total), kThreads, 0, st>>>(q, out, total, channels, inner, p);
   }
   return check_launch("dequantize");
 }
@@ -1210,7 +1214,11 @@ extern "C" int32_t lc_fake_quantize_f32(const float* x, int64_t outer, int64_t c
   const float qmin = static_cast<float>(quant_min), qmax = static_cast<float>(quant_max);
   cudaStream_t st = as_stream(stream);
   const int64_t segs = outer * channels;
-  if (inner >= kSegModeMinInner || channels == 1) {
+  dim3 cgrid;
+  if (columns_ok(outer, channels, inner, &cgrid) && aligned(x, 16) && aligned(out, 16) &&
+      (!mask_out || aligned(mask_out, 16))) {
+    fake_quantize_cols_kernel<<<cgrid, kThreads, 0, st>>>(x, out, mask_out, outer, channels * inner, inner, p, qmin, qmax);
+  } else if (inner >= kSegModeMinInner || channels == 1) {
     const int cps = chunks_for(inner);
     const int64_t grid = segs * cps;
     if (grid > 0x7fffffffLL) return fail(LC_ERR_UNSUPPORTED, "tensor too large for one launch");
@@ -1223,13 +1231,9 @@ extern "C" int32_t lc_fake_quantize_f32(const float* x, int64_t outer, int64_t c
       fake_quantize_seg_kernel<false><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(
           x, out, mask_out, channels, inner, cps, p, qmin, qmax);
   } else {
-    const int64_t total = segs * inner, L = channels * inner;
-    dim3 grid;
-    if (columns_ok(outer, L, &grid) && aligned(x, 16) && aligned(out, 16) && (!mask_out || aligned(mask_out, 16)))
-      fake_quantize_cols_kernel<<<grid, kThreads, 0, st>>>(x, out, mask_out, outer, L, inner, p, qmin, qmax);
-    else
-      fake_quantize_strided_kernel<<<strided_grid(total), kThreads, 0, st>>>(
-          x, out, mask_out, total, channels, inner, p, qmin, qmax);
+    const int64_t total = segs * inner;
+    fake_quantize_strided_kernel<<<strided_grid(total), kThreads, 0, st>>>(
+        x, out, mask_out, total, channels, inner, p, qmin, qmax);
   }
   return check_launch("fake_quantize");
 }

@@ -115,7 +115,8 @@ def test_running_observers(ops):
                                         # channel axis last / short inner extents: the column kernels (rows of
                                         # channels * inner elements, a multiple of 4, at least 4 of them)
                                         ((70, 12), 1), ((37, 1024), 1), ((5, 7, 9, 64), 3), ((6, 20, 6), 1),
-                                        ((33, 8, 2), 1), ((3, 16), 1), ((2000, 260), 1), ((4, 2052), 1)])
+                                        ((33, 8, 2), 1), ((3, 16), 1), ((2000, 260), 1), ((4, 2052), 1),
+                                        ((16, 6, 256), 1), ((9, 5, 1024), 1), ((7, 5, 1024), 1), ((8, 3, 2048), 1)])
 @pytest.mark.parametrize("qd", ["qint8", "quint8", "qint4", "qint8_narrow"])
 def test_quantize_dequantize_matches_oracle(ops, shape, axis, qd):
     qdt = getattr(O, qd)
