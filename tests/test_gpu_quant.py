@@ -161,7 +161,9 @@ def test_empty_inputs(ops):
 
 
 @pytest.mark.parametrize("rows,cols", [(1, 4), (64, 1024), (33, 512), (17, 200), (9, 4100), (5, 8192),
-                                       (3, 16384), (2, 20000), (7, 1023)])
+                                       (3, 16384), (2, 20000), (7, 1023),
+                                       # rows of up to 2048 elements: a warp per row, eight rows per CTA
+                                       (1000, 64), (9, 128), (37, 132), (15, 256), (21, 1028), (11, 2048), (10, 2052)])
 @pytest.mark.parametrize("mode", ["sym_s8", "sym_narrow", "affine_u8"])
 def test_dynamic_quantize_rows(ops, rows, cols, mode):
     x = rand((rows, cols), rows * 31 + cols)
