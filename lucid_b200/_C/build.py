@@ -25,7 +25,7 @@ FASTCALL_SRC = os.path.join(CSRC, "fastcall.c")
 FASTCALL_PATH = os.path.join(HERE, "_fastcall" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 
 SOURCES = ["api.cu", "quant_kernels.cu", "hist_kernels.cu", "embed_kernels.cu", "qlinear_tcgen05.cu", "wo_kernels.cu",
-           "wo_prep_kernels.cu", "peer_kernels.cu"]
+           "wo_prep_kernels.cu", "peer_kernels.cu", "qgemv_kernels.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

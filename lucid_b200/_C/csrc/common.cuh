@@ -24,6 +24,15 @@ int32_t encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, const 
                              uint64_t rows, uint64_t stride_bytes, uint32_t box_inner, uint32_t box_rows,
                              CUtensorMapSwizzle swizzle);
 
+// GEMV-shaped int8 x int8 product for up to 32 rows against a weight of 4 MB and more (qgemv_kernels.cu): same
+// arguments and bit-identical results as the tensor-core GEMM behind lc_qlinear_i8
+bool qgemv_i8_applies(int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, const void* a, const void* b,
+                      int32_t out_dtype);
+int32_t launch_qgemv_i8(const void* a, int32_t a_unsigned, int64_t lda, const int8_t* b, int64_t ldb, int64_t M,
+                        int64_t N, int64_t K, const float* sx, int32_t sx_per_row, const float* zx, const int32_t* wsum,
+                        const float* sw, const float* bias, void* out, int32_t out_dtype, int64_t ldo, int32_t* status,
+                        cudaStream_t st);
+
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 

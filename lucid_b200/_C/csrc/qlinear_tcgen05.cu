@@ -1203,6 +1203,11 @@ extern "C" int32_t lc_qlinear_i8_multi(const void* a, int32_t a_unsigned, int64_
   if (M > 0x7fffffffLL - BM || N > 0x7fffffffLL - BN || K > 0x7fffffffLL - BK)
     return fail(LC_ERR_UNSUPPORTED, "qlinear_i8: dimension exceeds the TMA coordinate range");
 
+  // decode batches against a large weight: the weight-streaming GEMV-shaped kernel (identical results)
+  if (n_out == 1 && !multicast && !wait_test && variant == 0 && qgemv_i8_applies(M, N, K, lda, ldb, a, b, out_dtype))
+    return launch_qgemv_i8(a, a_unsigned, lda, b, ldb, M, N, K, sx, sx_per_row, zx, wsum, sw, bias, out, out_dtype, ldo,
+                           status, as_stream(stream));
+
   Params p;
   p.M = M;
   p.N = N;

@@ -188,3 +188,36 @@ def test_single_call_dynamic_linear_equals_the_separate_calls(scheme, qmin, qmax
             needs_zp = not (sym and signed)
             want = ops.qlinear_i8(xq, wq, sx, sw, bias=bias, zx=zx if needs_zp else None, wsum=wsum if needs_zp else None)
         assert torch.equal(y, want)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("N,K", [(4096, 1024), (2064, 2048), (1030, 4112), (4096, 14336)])
+@pytest.mark.parametrize("a_unsigned", [False, True])
+def test_decode_batches_take_the_streaming_kernel_with_identical_results(ops, M, N, K, a_unsigned):
+    """Up to 32 rows against a weight of 4 MB and more: the GEMV-shaped `mma.sync` kernel.  Integer
+    accumulation is exact, so the int32 accumulator equals the oracle's and the fp32 output equals, bit for bit,
+    what the tensor-core GEMM (variant 1, which never takes this route) writes -- zero-point correction, per-row
+    and per-tensor activation scales, bias; cold and warm launches agree."""
+    r = np.random.default_rng(M * 7 + N * 3 + K + int(a_unsigned))
+    a = r.integers(0, 256, (M, K)).astype(np.uint8) if a_unsigned else r.integers(-128, 128, (M, K)).astype(np.int8)
+    b = r.integers(-128, 128, (N, K)).astype(np.int8)
+    at, bt = dev(a), dev(b)
+    st = status_word()
+    acc = ops.qlinear_i8(at, bt, None, None, out_dtype=torch.int32, status=st)
+    want = (a.astype(np.float64) @ b.astype(np.float64).T).astype(np.int64)  # exact: |sum| < 2^53
+    np.testing.assert_array_equal(host(acc).astype(np.int64), want)
+    sw = dev(r.random(N).astype(np.float32) * 0.01 + 1e-3)
+    bias = dev(r.standard_normal(N).astype(np.float32))
+    wsum = ops.rowsum_s8(bt)
+    flush = torch.empty(300 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for per_row in (False, True):
+        sx = dev(r.random(M if per_row else 1).astype(np.float32) * 0.05 + 1e-3)
+        zx = dev(np.array([3.0 if a_unsigned else 0.0], np.float32))
+        kw = dict(bias=bias, zx=zx if a_unsigned else None, wsum=wsum if a_unsigned else None, status=st)
+        y = ops.qlinear_i8(at, bt, sx, sw, **kw)
+        ref = ops.qlinear_i8(at, bt, sx, sw, variant=1, **kw)
+        assert torch.equal(y, ref)
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        assert torch.equal(ops.qlinear_i8(at, bt, sx, sw, **kw), y)
+    assert int(host(st)[0]) == 0
