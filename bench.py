@@ -679,6 +679,16 @@ def run_profile_case(args) -> int:
             p_, s_, b_ = packs[i[0] % 4]
             i[0] += 1
             return ops.group_matmul(xb, p_, s_, b_, 64, gbits)
+    elif case == "dyn_gemv":  # decode rows of the dynamic Linear: int8 codes against a long-K, narrow-N int8 weight
+        bs = [torch.randint(-128, 128, (4096, 14336), device=dev, dtype=torch.int8, generator=g) for _ in range(4)]
+        rows = int(args.profile_batch)
+        a_codes = torch.randint(-128, 128, (rows, 14336), device=dev, dtype=torch.int8, generator=g)
+        sx_, sw_ = torch.rand(rows, device=dev) * 1e-2, torch.rand(4096, device=dev) * 1e-2
+        i = [0]
+
+        def fn():
+            i[0] += 1
+            return ops.qlinear_i8(a_codes, bs[i[0] % 4], sx_, sw_)
     elif case == "wo_gemv":
         ws = []
         for _ in range(4):
@@ -1204,7 +1214,7 @@ def main() -> int:
     ap.add_argument("--profile-case", default=None,
                     help="run a small fixed case of one kernel (gemm, quantize_rows, quantize_tensor, "
                          "dequantize, quantize_given_scale, histc, merge, embedding, embedding_bag, gemm_small, gemm_shortk, wo_gemv, "
-                         "static_linear, static_linear_longk, group_gemv, group_gemv_4bit) for a profiler capture; prints no bench line")
+                         "static_linear, static_linear_longk, group_gemv, group_gemv_4bit, dyn_gemv) for a profiler capture; prints no bench line")
     ap.add_argument("--profile-batch", default=4)
     ap.add_argument("--gather", choices=("auto", "fused", "multimem", "copy", "nccl"), default="auto",
                     help="N > 1: how output shards are exchanged (auto = time fused / copy / multimem once, keep the fastest)")

@@ -180,8 +180,10 @@ qgemv_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const QgemvParams p)
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][nt][i] = 0;
-    // activation codes of this lane: 16 bytes per unit and batch row nt * 8 + g, one chunk ahead
-    uint4 xn[NT][2];
+    // activation codes of this lane: 16 bytes per unit and batch row nt * 8 + g, fetched D chunks ahead (a chunk
+    // of a single-tile pass is one 16 KB box, shorter than a round trip to the L2)
+    constexpr int D = NT == 1 ? 2 : 1;
+    uint4 xq[D][NT][2];
     auto load_x = [&](int kc, uint4 (&dst)[NT][2]) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
@@ -194,14 +196,19 @@ qgemv_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const QgemvParams p)
                            : make_uint4(0u, 0u, 0u, 0u);
         }
     };
-    load_x(0, xn);
+#pragma unroll
+    for (int d = 0; d < D; ++d) load_x(d, xq[d]);
     for (int kc = 0; kc < num_kc; ++kc) {
       uint4 xc[NT][2];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int u = 0; u < 2; ++u) xc[nt][u] = xn[nt][u];
-      load_x(kc + 1, xn);
+        for (int u = 0; u < 2; ++u) {
+          xc[nt][u] = xq[0][nt][u];
+#pragma unroll
+          for (int d = 0; d + 1 < D; ++d) xq[d][nt][u] = xq[d + 1][nt][u];
+        }
+      load_x(kc + D, xq[D - 1]);
 #pragma unroll
       for (int j = 0; j < TMAX; ++j) {
         if (j < pass_tiles && ok) {
