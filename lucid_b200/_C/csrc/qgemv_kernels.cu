@@ -23,11 +23,11 @@ constexpr int KC = 1024;          // bytes of K per box row
 constexpr int STAGE = 16 * KC;    // one box: a 16-row tile of one K chunk
 constexpr int CW = 8;             // consumer warps
 constexpr int THREADS = CW * 32 + 32;
-constexpr int TMAX = 4;           // row tiles per pass
 constexpr int SMEM = 115584;      // two CTAs per SM
 constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s
-__host__ __device__ constexpr int red_bytes(int nt) { return TMAX * CW * 16 * nt * 8 * 4; }
-__host__ __device__ constexpr int stages(int nt) { return (SMEM - 256 - red_bytes(nt)) / STAGE; }
+// (tm = row tiles per pass, nt = batch tiles of 8 rows)
+__host__ __device__ constexpr int red_bytes(int nt, int tm) { return tm * CW * 16 * nt * 8 * 4; }
+__host__ __device__ constexpr int stages(int nt, int tm) { return (SMEM - 256 - red_bytes(nt, tm)) / STAGE; }
 }  // namespace gv
 
 struct QgemvParams {
@@ -98,17 +98,17 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// XU: activation codes are unsigned bytes.  NT: batch tiles of 8 rows (1 or 2).
-template <bool XU, int NT>
+// XU: activation codes are unsigned bytes.  NT: batch tiles of 8 rows (1, 2 or 4).  TMAX: row tiles per pass.
+template <bool XU, int NT, int TMAX>
 __global__ void __launch_bounds__(gv::THREADS, 2)
 qgemv_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const QgemvParams p) {
   using namespace gv;
-  constexpr int S = stages(NT), COLS = NT * 8;
+  constexpr int S = stages(NT, TMAX), COLS = NT * 8;
   static_assert(S >= 3, "ring too shallow");
   extern __shared__ uint8_t gv_smem_raw[];
   const uint32_t base = (gv_smem(gv_smem_raw) + 127u) & ~127u;
   const uint32_t red_base = base + S * STAGE;
-  const uint32_t bar_base = red_base + red_bytes(NT);
+  const uint32_t bar_base = red_base + red_bytes(NT, TMAX);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
   int* red = reinterpret_cast<int*>(gv_smem_raw + (red_base - gv_smem(gv_smem_raw)));
@@ -182,8 +182,9 @@ qgemv_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const QgemvParams p)
         for (int i = 0; i < 4; ++i) acc[j][nt][i] = 0;
     // activation codes of this lane: 16 bytes per unit and batch row nt * 8 + g, fetched D chunks ahead (a chunk
     // of a single-tile pass is one 16 KB box, shorter than a round trip to the L2)
-    constexpr int D = NT == 1 ? 2 : 1;
-    uint4 xq[D][NT][2];
+    // (four batch tiles leave no registers for a second set: they load where the codes are needed)
+    constexpr int D = NT == 1 ? 2 : (NT == 2 ? 1 : 0);
+    uint4 xq[D > 0 ? D : 1][NT][2];
     auto load_x = [&](int kc, uint4 (&dst)[NT][2]) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
@@ -200,15 +201,19 @@ qgemv_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const QgemvParams p)
     for (int d = 0; d < D; ++d) load_x(d, xq[d]);
     for (int kc = 0; kc < num_kc; ++kc) {
       uint4 xc[NT][2];
+      if constexpr (D == 0) {
+        load_x(kc, xc);
+      } else {
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          xc[nt][u] = xq[0][nt][u];
+          for (int u = 0; u < 2; ++u) {
+            xc[nt][u] = xq[0][nt][u];
 #pragma unroll
-          for (int d = 0; d + 1 < D; ++d) xq[d][nt][u] = xq[d + 1][nt][u];
-        }
-      load_x(kc + D, xq[D - 1]);
+            for (int d = 0; d + 1 < D; ++d) xq[d][nt][u] = xq[d + 1][nt][u];
+          }
+        load_x(kc + D, xq[D > 0 ? D - 1 : 0]);
+      }
 #pragma unroll
       for (int j = 0; j < TMAX; ++j) {
         if (j < pass_tiles && ok) {
@@ -271,9 +276,9 @@ qgemv_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const QgemvParams p)
   }
 }
 
-template <bool XU, int NT>
+template <bool XU, int NT, int TMAX>
 int32_t launch_qgemv_inst(const CUtensorMap& map, const QgemvParams& p, unsigned grid, cudaStream_t st) {
-  auto kernel = qgemv_i8_kernel<XU, NT>;
+  auto kernel = qgemv_i8_kernel<XU, NT, TMAX>;
   static std::once_flag flags[64];
   static cudaError_t results[64];
   int dev = 0;
@@ -293,9 +298,9 @@ int32_t launch_qgemv_inst(const CUtensorMap& map, const QgemvParams& p, unsigned
 
 bool qgemv_i8_applies(int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, const void* a, const void* b,
                       int32_t out_dtype) {
-  // 17..32 rows are two launches of 16: worth it against the GEMM's 128 x 32 tiles only while N gives those few
-  // CTAs (measured at 32 rows, us: [4096, 14336] 28 against 52, [4096, 4096] 12 against 14, but [14336, 4096]
-  // 26 against 20 and [28672, 4096] 52 against 25)
+  // 17..32 rows (four batch tiles, eight MMAs per unit: the consumer warps set the pace) are worth it against the
+  // GEMM's 128 x 32 tiles only while N gives those few CTAs (measured at 32 rows, us: [4096, 14336] 22 against 52,
+  // [4096, 4096] 10 against 14, but [14336, 4096] 24 against 20 and [28672, 4096] 43 against 25)
   if (!(M >= 1 && (M <= 16 || (M <= 32 && N < 8192)))) return false;
   return K % 16 == 0 && N * K >= (int64_t{4} << 20) && lda % 16 == 0 && ldb % 16 == 0 &&
          aligned(a, 16) && aligned(b, 16) && (out_dtype == LC_F32 || out_dtype == LC_S32) &&
@@ -315,11 +320,13 @@ int32_t launch_qgemv_i8(const void* a, int32_t a_unsigned, int64_t lda, const in
   const int64_t per = (tiles + slots - 1) / slots;
   const unsigned grid = static_cast<unsigned>((tiles + per - 1) / per);
   const size_t esz = 4;  // fp32 and int32 outputs alike
-  for (int64_t m0 = 0; m0 < M; m0 += 16) {
+  // up to 8 / 16 / 32 rows: one / two / four batch tiles per launch (the last with passes of two row tiles)
+  const int64_t rows_per_launch = 32;
+  for (int64_t m0 = 0; m0 < M; m0 += rows_per_launch) {
     QgemvParams p;
     p.a = static_cast<const uint8_t*>(a) + m0 * lda;
     p.lda = lda;
-    p.M = M - m0 < 16 ? M - m0 : 16;
+    p.M = M - m0 < rows_per_launch ? M - m0 : rows_per_launch;
     p.N = N;
     p.K = K;
     p.sx = sx ? sx + (sx_per_row ? m0 : 0) : nullptr;
@@ -335,9 +342,11 @@ int32_t launch_qgemv_i8(const void* a, int32_t a_unsigned, int64_t lda, const in
     p.tiles_per_cta = static_cast<int>(per);
     int32_t rc;
     if (p.M <= 8)
-      rc = a_unsigned ? launch_qgemv_inst<true, 1>(map, p, grid, st) : launch_qgemv_inst<false, 1>(map, p, grid, st);
+      rc = a_unsigned ? launch_qgemv_inst<true, 1, 4>(map, p, grid, st) : launch_qgemv_inst<false, 1, 4>(map, p, grid, st);
+    else if (p.M <= 16)
+      rc = a_unsigned ? launch_qgemv_inst<true, 2, 4>(map, p, grid, st) : launch_qgemv_inst<false, 2, 4>(map, p, grid, st);
     else
-      rc = a_unsigned ? launch_qgemv_inst<true, 2>(map, p, grid, st) : launch_qgemv_inst<false, 2>(map, p, grid, st);
+      rc = a_unsigned ? launch_qgemv_inst<true, 4, 2>(map, p, grid, st) : launch_qgemv_inst<false, 4, 2>(map, p, grid, st);
     if (rc) return rc;
   }
   return LC_OK;
