@@ -438,6 +438,42 @@ dequantize_cols_kernel(const InT* __restrict__ q, OutT* __restrict__ out, int64_
   }
 }
 
+// per-channel range over [outer][channels * inner] for 128..2047 elements per channel (a multiple of 128): a warp's
+// 128 adjacent columns lie in one channel, every lane walks its four columns down kColsRows rows, the warp
+// reduces with shuffles and one lane merges into the channel's running values (a segment kernel's CTA holds one
+// such short segment: [32, 4096, 1024] ran at 2.8 TB/s)
+__global__ void __launch_bounds__(kThreads)
+observe_channel_cols_kernel(const float* __restrict__ x, int64_t outer, int64_t L, int64_t inner,
+                            float* min_out, float* max_out) {
+  const ColumnWalk w = column_walk(outer, L);
+  float mn = INFINITY, mx = -INFINITY;
+  if (w.live) {
+    for (int64_t r = w.r0; r < w.r1; r += kUnroll) {
+      float4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        v[u] = (r + u < w.r1) ? __ldg(reinterpret_cast<const float4*>(x + (r + u) * L + w.j))
+                              : make_float4(INFINITY, INFINITY, INFINITY, INFINITY);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (r + u < w.r1) {
+          mn = fminf(fminf(mn, fminf(v[u].x, v[u].y)), fminf(v[u].z, v[u].w));
+          mx = fmaxf(fmaxf(mx, fmaxf(v[u].x, v[u].y)), fmaxf(v[u].z, v[u].w));
+        }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if ((threadIdx.x & 31) == 0 && w.live) {  // (L is a multiple of 128: a warp is live or not as a whole)
+    const int64_t c = w.j / inner;
+    atomic_min_float(min_out + c, mn);
+    atomic_max_float(max_out + c, mx);
+  }
+}
+
 // whether the column kernels apply, and their grid: rows in x (no 65535 limit), column blocks in y.
 // Below kSegModeMinInner elements per channel they replace the element-wise kernels; up to 2048 they replace
 // the segment kernels too when there are rows to walk down (a segment kernel's CTA of 4096 slots holds one
@@ -1149,7 +1185,10 @@ extern "C" int32_t lc_observe_channel_f32(const float* x, int64_t outer, int64_t
     fill_minmax_kernel<<<static_cast<unsigned>((channels + 255) / 256), 256, 0, st>>>(min_out, max_out,
                                                                                      channels);
   }
-  if (inner >= kSegModeMinInner) {
+  dim3 cgrid;
+  if (inner % 128 == 0 && aligned(x, 16) && columns_ok(outer, channels, inner, &cgrid)) {
+    observe_channel_cols_kernel<<<cgrid, kThreads, 0, st>>>(x, outer, channels * inner, inner, min_out, max_out);
+  } else if (inner >= kSegModeMinInner) {
     const int cps = chunks_for(inner);
     const int64_t grid = outer * channels * cps;
     if (grid > 0x7fffffffLL) return fail(LC_ERR_UNSUPPORTED, "tensor too large for one launch");

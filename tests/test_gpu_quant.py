@@ -109,6 +109,23 @@ def test_running_observers(ops):
         np.testing.assert_array_equal(host(mx), omx)
 
 
+@pytest.mark.parametrize("shape,axis", [((9, 5, 1024), 1), ((8, 3, 128), 1), ((20, 6, 384), 1), ((7, 5, 1024), 1), ((16, 2, 1920), 1),
+                                        ((64, 4, 256), 1), ((3, 8, 64, 2), 1)])
+def test_channel_observer_layouts(ops, shape, axis):
+    """Per-channel running ranges for 128..2047 elements per channel (the column-walk kernel from 8 outer rows
+    on) and the neighbouring layouts, accumulated over two batches; equal to the oracle's."""
+    a, b = rand(shape, sum(shape)), rand(shape, sum(shape) + 1) * 2.0
+    c = shape[axis]
+    mn = torch.full((c,), float("inf"), device="cuda")
+    mx = torch.full((c,), float("-inf"), device="cuda")
+    ops.observe_channel(dev(a), axis, mn, mx, accumulate=False)
+    ops.observe_channel(dev(b), axis, mn, mx, accumulate=True)
+    amn, amx = O.minmax_channel(a, axis)
+    bmn, bmx = O.minmax_channel(b, axis)
+    np.testing.assert_array_equal(host(mn), np.minimum(amn, bmn))
+    np.testing.assert_array_equal(host(mx), np.maximum(amx, bmx))
+
+
 @pytest.mark.parametrize("shape,axis", [((7,), None), ((1, 1), None), ((129, 513), None), ((4096, 1024), 0),
                                         ((3, 5, 7), 1), ((2, 300, 130), 1), ((64, 4100), 0), ((70, 9), 1),
                                         ((1000, 1003), 0), ((16, 8192), 0), ((5, 16388), 0),
